@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the quantised-GEMV hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extra]
+
+One "step" is one decode GEMV of the headline workload: Q4_0 weights [262144, 1152] (the Gemma-3
+vocabulary head, 170 MB — larger than L2, so every step streams from HBM) times one f32 activation
+row. The printed value is algorithmic GB/s = (N*K/32*18 + 4K + 4N) bytes / step time. At N > 1 GPUs
+the output rows are split evenly across ranks and each step ends with an all-gather of the outputs
+(strong scaling: the total work is fixed).
+
+`--impl reference` times the CPU restatement of zig-nn's own path for the same workload on the
+host cores (zig-nn is Zig and cannot be built here; see oracle/).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+WORKLOAD = dict(qtype="q4_0", out_dim=262144, in_dim=1152, m_rows=1)
+BPB = {"q4_0": 18, "q4_1": 20, "q8_0": 34}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, from the ncu capture
+# summarised in profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES = None
+
+
+def algorithmic_bytes(qtype, n, k, m=1):
+    return n * (k // 32) * BPB[qtype] + 4 * m * k + 4 * m * n
+
+
+def measured_peak():
+    p = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                for name, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def load_oracle(native=True):
+    """The CPU checker / baseline. Tries a host-tuned build first (same sources, -march=native)."""
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import oracle
+    if native:
+        try:
+            out = os.path.join(REPO, "oracle", "_build", "libzq_oracle_native.so")
+            oracle.build(arch="native", out=out)
+            oracle.lib(out)
+            return oracle, "native"
+        except Exception:
+            pass
+    oracle.lib()
+    return oracle, "x86-64-v3"
+
+
+def make_weight_bytes(qtype_name, n, k, seed, device):
+    import torch
+    from zignn_b200 import ggml
+    g = torch.Generator(device=device).manual_seed(seed)
+    chunks = []
+    step = max(1, min(n, (1 << 26) // k))  # <= 64 Mi weights (256 MB f32) at a time
+    for r0 in range(0, n, step):
+        w = torch.randn(min(step, n - r0), k, generator=g, device=device) * 0.02
+        chunks.append(ggml.quantize(ggml.TYPE_IDS[qtype_name], w))
+    return torch.cat(chunks)
+
+
+def cpu_baseline(qtype_name, n, k, target_seconds=12.0):
+    """Times the oracle's f32-activation matmul (zig-nn dequant.zig:170-309) with all host threads on the
+    same [n, k] weight; bounded to about `target_seconds` of CPU work."""
+    import numpy as np
+    import torch
+    from zignn_b200 import ggml
+    oracle, build = load_oracle()
+    threads = host_threads()
+    raw = make_weight_bytes(qtype_name, n, k, 42, "cpu").numpy()
+    x = np.random.default_rng(43).standard_normal(k).astype(np.float32)
+    t = ggml.TYPE_IDS[qtype_name]
+    oracle.matmul_f32(t, raw, x, n, k, threads)  # warm
+    calls, t0 = 0, time.perf_counter()
+    while True:
+        oracle.matmul_f32(t, raw, x, n, k, threads)
+        calls += 1
+        el = time.perf_counter() - t0
+        if el > target_seconds or calls >= 200:
+            break
+    gbs = algorithmic_bytes(qtype_name, n, k) * calls / el / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "%d GEMV calls of %s [%d,%d] x f32[1,%d] in %.1f s (oracle build: %s)"
+                      % (calls, qtype_name, n, k, k, el, build)}
+
+
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    import numpy as np
+    from zignn_b200 import ggml
+    oracle, build = load_oracle()
+    q, n, k = WORKLOAD["qtype"], WORKLOAD["out_dim"], WORKLOAD["in_dim"]
+    threads = host_threads()
+    raw = make_weight_bytes(q, n, k, 42, "cpu").numpy()
+    x = np.random.default_rng(43).standard_normal(k).astype(np.float32)
+    t = ggml.TYPE_IDS[q]
+    for _ in range(args.warmup):
+        oracle.matmul_f32(t, raw, x, n, k, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.matmul_f32(t, raw, x, n, k, threads)
+    el = time.perf_counter() - t0
+    ms = el / args.steps * 1e3
+    gbs = algorithmic_bytes(q, n, k) / (ms * 1e-3) / 1e9
+    line = {
+        "impl": "reference", "metric": "q4_0_gemv_algorithmic_gbs", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": dict(workload="configs[1]: Q4_0 GEMV 1152->262144, M=1, f32 activations",
+                       note="CPU restatement of zig-nn matmul_q4_0_f32 (dequant.zig:170-182), row-split over host threads"),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "%d timed GEMV calls (oracle build: %s)" % (args.steps, build)},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_region(torch, fn, steps, sync):
+    """K calls bracketed by sync + CUDA events on the current stream; returns total ms."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    sync()
+    return e0.elapsed_time(e1)
+
+
+def sweep_extra(torch, zq, ggml, steps=50):
+    """configs[1] M=1 shapes x types, HBM-cold: weights rotate through > L2-size distinct copies."""
+    out = []
+    shapes = [(768, 2304), (768, 3072), (3072, 768), (1152, 6912), (6912, 1152), (1152, 262144)]
+    for qname in ("q4_0", "q4_1", "q8_0"):
+        for k, n in shapes:
+            nbytes = algorithmic_bytes(qname, n, k)
+            copies = max(1, min(64, int(320e6 // nbytes) + 1))
+            raw = make_weight_bytes(qname, n, k, 42, "cuda")
+            ws = [zq.QuantWeight(raw, ggml.TYPE_IDS[qname], n, k) for _ in range(copies)]
+            x = torch.randn(1, k, device="cuda")
+            y = torch.empty(1, n, device="cuda")
+            for mode, mname in ((zq.ACT_F32, "f32"), (zq.ACT_Q8, "q8")):
+                i = [0]
+
+                def fn():
+                    zq.quant_matmul_no_grad(x, ws[i[0] % copies], mode, out=y)
+                    i[0] += 1
+                for _ in range(5):
+                    fn()
+                ms = time_region(torch, fn, steps, torch.cuda.synchronize) / steps
+                out.append({"type": qname, "k": k, "n": n, "act": mname, "us": round(ms * 1e3, 2),
+                            "gbs": round(nbytes / ms / 1e6, 1), "copies": copies})
+            del ws, raw
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the sweep / cpu baseline side measurements")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import zignn_b200
+    from zignn_b200 import api as zq
+    from zignn_b200 import ggml
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    q, n, k = WORKLOAD["qtype"], WORKLOAD["out_dim"], WORKLOAD["in_dim"]
+    n_local = n // world
+    # every rank draws the same full-weight stream and keeps its row slice
+    raw_full = make_weight_bytes(q, n, k, 42, "cuda")
+    row_bytes = (k // 32) * BPB[q]
+    raw = raw_full[rank * n_local * row_bytes:(rank + 1) * n_local * row_bytes].contiguous()
+    del raw_full
+    qw = zq.QuantWeight(raw, ggml.TYPE_IDS[q], n_local, k)
+    del raw
+    x = torch.randn(1, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(43))
+    y_local = torch.empty(1, n_local, device="cuda")
+    y_full = torch.empty(world, n_local, device="cuda") if use_dist else y_local
+
+    def step():
+        zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, out=y_local)
+        if use_dist:
+            dist.all_gather_into_tensor(y_full, y_local)
+
+    def sync():
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    total_ms = time_region(torch, step, args.steps, sync)
+    clocks = sampler.stop() if sampler else None
+    if use_dist:
+        tmax = torch.tensor([total_ms], device="cuda")
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        total_ms = float(tmax.item())
+    ms = total_ms / args.steps
+    bytes_step = algorithmic_bytes(q, n, k)
+    value = bytes_step / (ms * 1e-3) / 1e9
+
+    # end to end through the public call with host buffers: pinned x -> device, GEMV, y -> pinned host
+    hx = torch.randn(1, k).pin_memory()
+    hy = torch.empty(1, n_local).pin_memory()
+
+    def e2e_step():
+        x.copy_(hx, non_blocking=True)
+        step()
+        hy.copy_(y_local, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads hy
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = time_region(torch, e2e_step, args.steps, sync)
+    if use_dist:
+        tmax = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tmax.item())
+    e2e_value = bytes_step / (e2e_ms / args.steps * 1e-3) / 1e9
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        kernel_ms = ms
+        if use_dist:  # the GEMV alone, for the roofline of the dominant kernel
+            kernel_ms = time_region(torch, lambda: zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, out=y_local),
+                                    args.steps, torch.cuda.synchronize) / args.steps
+        local_bytes = algorithmic_bytes(q, n_local, k)
+        achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": "q4_0_gemv_algorithmic_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(workload="configs[1]: Q4_0 GEMV 1152->262144, M=1, f32 activations",
+                           weights="N(0,0.02) seed 42 quantised q4_0", l2="weights (170 MB) larger than L2 (126 MB)",
+                           sharding="rows split over %d rank(s)%s" % (world, ", NCCL all-gather of outputs" if use_dist else "")),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_launch": local_bytes, "kernel": "gemv_f32_kernel<q4_0>"},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k, "d2h_bytes_per_step": 4 * n_local},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        if not args.no_extra and world == 1:
+            try:
+                line["cpu_baseline"] = cpu_baseline(q, n, k)
+            except Exception as e:  # the baseline is informational; never lose the GPU line
+                line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": host_threads(), "kind": "port",
+                                        "sample": "failed: %r" % (e,)}
+            try:
+                line["extra"] = {"sweep_m1_hbm_cold": sweep_extra(torch, zq, ggml)}
+            except Exception as e:
+                line["extra"] = {"error": repr(e)}
+        print(json.dumps(line), flush=True)
+    if use_dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

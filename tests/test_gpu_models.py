@@ -1,0 +1,108 @@
+"""Decode engines against the oracle's model loops: logits within rel-L2 1e-3 and identical greedy
+tokens for the first 64 steps (the stated bar), on small and on full-size configurations."""
+import numpy as np
+import pytest
+import torch
+
+from zignn_b200 import ggml, hostmodel
+
+pytestmark = pytest.mark.gpu
+
+GPT2_TINY = dict(vocab=1000, embed=128, head=4, layer=2, ctx=96, ffn=512)
+GEMMA_TINY = dict(vocab=2048, embed=128, head=4, head_kv=1, head_dim=32, layer=7, ctx=96, ffn=256,
+                  rope_base=1000000.0, sliding_window=16, rms_eps=1e-6, global_every=6)
+
+
+def rel_l2(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def run_parity(zq_engine, oracle_model, prompt, n_steps, logits_tol=1e-3):
+    """Greedy decoding on both sides; returns (gpu tokens, cpu tokens, worst logits rel-L2 while the
+    token streams agree)."""
+    lg = zq_engine.prefill(prompt).cpu().numpy()
+    lc = oracle_model.prefill(prompt)
+    worst = rel_l2(lg, lc)
+    gt, ct = [], []
+    for _ in range(n_steps):
+        tg, tc = int(np.argmax(lg)), int(np.argmax(lc))
+        gt.append(tg)
+        ct.append(tc)
+        if tg != tc:
+            break
+        lg = zq_engine.decode_next(tg).cpu().numpy()
+        lc = oracle_model.decode_next(tc)
+        worst = max(worst, rel_l2(lg, lc))
+    return gt, ct, worst
+
+
+def test_gpt2_tiny_parity(zq, oracle):
+    host = hostmodel.Gpt2Host.synthetic(GPT2_TINY, seed=42, std=0.08).randomize_small_params()
+    prompt = np.random.default_rng(44).integers(0, GPT2_TINY["vocab"], size=20)
+    gt, ct, worst = run_parity(zq.Gpt2(host), oracle.Gpt2(host, 4), prompt, 64)
+    assert gt == ct
+    assert worst <= 1e-3, worst
+
+
+@pytest.mark.parametrize("qtypes", [(ggml.Q8_0, ggml.Q8_0, ggml.Q8_0), (ggml.Q4_0, ggml.Q8_0, ggml.Q4_1),
+                                    (ggml.Q4_1, ggml.Q4_1, ggml.Q4_1)])
+def test_gemma3_tiny_parity(zq, oracle, qtypes):
+    q, embd, down = qtypes
+    host = hostmodel.Gemma3Host.synthetic(GEMMA_TINY, qtype=q, embd_qtype=embd, down_qtype=down, seed=42,
+                                          std=0.08).randomize_small_params()
+    prompt = np.random.default_rng(44).integers(0, GEMMA_TINY["vocab"], size=24)  # beyond the window of 16
+    gt, ct, worst = run_parity(zq.Gemma3(host), oracle.Gemma3(host, 4), prompt, 64)
+    assert gt == ct
+    assert worst <= 1e-3, worst
+
+
+def test_device_greedy_loop_matches_stepwise(zq):
+    host = hostmodel.Gemma3Host.synthetic(GEMMA_TINY, qtype=ggml.Q8_0, seed=3, std=0.08)
+    prompt = np.random.default_rng(1).integers(0, GEMMA_TINY["vocab"], size=8)
+    a, b = zq.Gemma3(host), zq.Gemma3(host)
+    first = int(a.prefill(prompt).argmax().item())
+    b.prefill(prompt)
+    toks = a.decode_greedy(first, 20)
+    step, tok = [], first
+    for _ in range(20):
+        tok = int(b.decode_next(tok).argmax().item())
+        step.append(tok)
+    assert list(toks) == step
+    assert a.seq_len == b.seq_len == 28
+
+
+def test_sequence_error_statuses(zq):
+    from zignn_b200 import _lib
+    host = hostmodel.Gpt2Host.synthetic(dict(vocab=64, embed=32, head=2, layer=1, ctx=8, ffn=64), seed=1)
+    m = zq.Gpt2(host)
+    for bad in ([], np.zeros(9, np.uint32)):
+        with pytest.raises(_lib.ZqError) as e:
+            m.prefill(bad)
+        assert e.value.status == 6  # EmptySequence / SequenceTooLong
+    m.prefill(np.zeros(8, np.uint32))
+    with pytest.raises(_lib.ZqError) as e:
+        m.decode_next(0)
+    assert e.value.status == 6  # ContextFull
+    m.reset_cache()
+    assert m.seq_len == 0
+    m.decode_next(3)
+    assert m.seq_len == 1
+
+
+def test_gpt2_small_full_size_greedy_64(zq, oracle):
+    """GPT-2 small, Q4_0, seed 42, 32-token prompt, first 64 greedy tokens identical."""
+    host = hostmodel.Gpt2Host.synthetic(hostmodel.GPT2_SMALL, qtype=ggml.Q4_0, seed=42, std=0.02, device="cuda")
+    prompt = np.random.default_rng(44).integers(0, 50257, size=32)
+    gt, ct, worst = run_parity(zq.Gpt2(host), oracle.Gpt2(host, 8), prompt, 64)
+    assert gt == ct, (len(gt), gt[-1], ct[-1])
+    assert worst <= 1e-3, worst
+
+
+def test_gemma3_1b_full_size_greedy_64(zq, oracle):
+    """Gemma-3-1B shape, Q8_0, seed 42, 16-token prompt, first 64 greedy tokens identical."""
+    host = hostmodel.Gemma3Host.synthetic(hostmodel.GEMMA3_1B, qtype=ggml.Q8_0, seed=42, std=0.02, device="cuda")
+    prompt = np.random.default_rng(44).integers(0, 262144, size=16)
+    gt, ct, worst = run_parity(zq.Gemma3(host), oracle.Gemma3(host, 8), prompt, 64)
+    assert gt == ct, (len(gt), gt[-1], ct[-1])
+    assert worst <= 1e-3, worst

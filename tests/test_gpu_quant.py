@@ -1,0 +1,236 @@
+"""Parity of the CUDA quantised linears with the CPU oracle, through the C ABI.
+
+Bars: dequantised weights bit-exact; Q8-activation outputs bit-exact; f32-activation outputs
+rel-L2 <= 1e-3 (the stated bar) — and <= 2e-6 as an implementation guard, since both sides
+compute in f32."""
+import numpy as np
+import pytest
+import torch
+
+from zignn_b200 import ggml
+
+pytestmark = pytest.mark.gpu
+
+TYPES = [ggml.Q4_0, ggml.Q4_1, ggml.Q8_0]
+REL_L2_BAR = 1e-3
+REL_L2_GUARD = 2e-6
+
+
+def rel_l2(a, b):
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def make_weight(oracle, qtype, n, k, seed=42, std=0.02):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((n, k)) * std).astype(np.float32)
+    return oracle.quantize(qtype, w)
+
+
+def make_x(m, k, seed=43):
+    return np.random.default_rng(seed).standard_normal((m, k)).astype(np.float32)
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("n,k", [(64, 256), (33, 96), (1, 32), (5, 1152)])
+def test_dequant_bit_exact_and_raw_round_trip(zq, oracle, qtype, n, k):
+    raw = make_weight(oracle, qtype, n, k)
+    qw = zq.QuantWeight(raw, qtype, n, k)
+    got = qw.dequantize().cpu().numpy().reshape(-1)
+    want = oracle.dequantize(qtype, raw, n * k)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(qw.raw_bytes().cpu().numpy(), raw)
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_weight_from_device_bytes(zq, oracle, qtype):
+    raw = make_weight(oracle, qtype, 48, 128)
+    qw = zq.QuantWeight(torch.from_numpy(raw).cuda(), qtype, 48, 128)
+    want = oracle.dequantize(qtype, raw, 48 * 128)
+    assert np.array_equal(qw.dequantize().cpu().numpy().reshape(-1), want)
+
+
+def test_reference_known_answers_through_the_gpu(zq):
+    """The block-level known answers of src/gguf/dequant.zig:449-685 run on the device."""
+    def f16b(v):
+        return np.array([v], np.float16).view(np.uint8)
+    ones = torch.ones(1, 32, device="cuda")
+    # q4_0: scale 1, nibbles 9 -> 32.0 ; scale 0.5, nibbles 10 -> 32.0
+    w = np.concatenate([f16b(1.0), np.full(16, 0x99, np.uint8), f16b(0.5), np.full(16, 0xAA, np.uint8)])
+    qw = zq.QuantWeight(w, ggml.Q4_0, 2, 32)
+    np.testing.assert_allclose(zq.quant_matmul_no_grad(ones, qw).cpu().numpy()[0], [32.0, 32.0], atol=0.01)
+    # q4_0 decode: scale 2, byte0 = 0x0F -> elem0 = 14, elem16 = -16
+    w = np.concatenate([f16b(2.0), np.array([0x0F], np.uint8), np.full(15, 0x88, np.uint8)])
+    d = zq.QuantWeight(w, ggml.Q4_0, 1, 32).dequantize().cpu().numpy()[0]
+    assert d[0] == 14.0 and d[16] == -16.0 and d[1] == 0.0
+    # q4_1: scale 2, min 1, nibbles 0 -> every value 1.0, dot with ones = 32
+    w = np.concatenate([f16b(2.0), f16b(1.0), np.zeros(16, np.uint8)])
+    qw = zq.QuantWeight(w, ggml.Q4_1, 1, 32)
+    assert np.all(qw.dequantize().cpu().numpy() == 1.0)
+    assert abs(zq.quant_matmul_no_grad(ones, qw).item() - 32.0) < 0.1
+    # q8_0: scale 0.5, q = {4, -3, 0...} -> {2.0, -1.5, 0}; q = 2 everywhere, scale 1 -> 64
+    w = np.concatenate([f16b(0.5), np.array([4, 0xFD], np.uint8), np.zeros(30, np.uint8)])
+    d = zq.QuantWeight(w, ggml.Q8_0, 1, 32).dequantize().cpu().numpy()[0]
+    assert d[0] == 2.0 and d[1] == -1.5 and d[2] == 0.0
+    w = np.concatenate([f16b(1.0), np.full(32, 2, np.uint8)])
+    assert abs(zq.quant_matmul_no_grad(ones, zq.QuantWeight(w, ggml.Q8_0, 1, 32)).item() - 64.0) < 0.01
+
+
+SHAPES = [(2304, 768), (768, 3072), (6912, 1152), (1152, 6912), (100, 32), (7, 64), (1, 32), (257, 1152),
+          (130, 2048), (96, 160)]
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("n,k", SHAPES)
+def test_gemv_f32_activations(zq, oracle, qtype, n, k):
+    raw = make_weight(oracle, qtype, n, k)
+    qw = zq.QuantWeight(raw, qtype, n, k)
+    x = make_x(1, k)
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_F32).cpu().numpy()
+    want = oracle.linear(qtype, raw, x, n, k, act_mode=0, n_threads=4)
+    err = rel_l2(got, want)
+    assert err <= REL_L2_BAR
+    assert err <= REL_L2_GUARD, err
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("m", [2, 4, 16])
+def test_matmul_small_batches_f32(zq, oracle, qtype, m):
+    n, k = 520, 768
+    raw = make_weight(oracle, qtype, n, k)
+    qw = zq.QuantWeight(raw, qtype, n, k)
+    x = make_x(m, k)
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_F32).cpu().numpy()
+    want = oracle.linear(qtype, raw, x, n, k, act_mode=0, n_threads=4)
+    assert got.shape == (m, n)
+    assert rel_l2(got, want) <= REL_L2_GUARD
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("n,k", SHAPES)
+def test_gemv_q8_activations_bit_exact(zq, oracle, qtype, n, k):
+    raw = make_weight(oracle, qtype, n, k)
+    qw = zq.QuantWeight(raw, qtype, n, k)
+    x = make_x(1, k)
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_Q8).cpu().numpy()
+    want = oracle.linear(qtype, raw, x, n, k, act_mode=1, n_threads=4)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), rel_l2(got, want)
+
+
+@pytest.mark.parametrize("m", [3, 16])
+def test_matmul_small_batches_q8_bit_exact(zq, oracle, m):
+    n, k = 300, 1152
+    raw = make_weight(oracle, ggml.Q4_1, n, k)
+    qw = zq.QuantWeight(raw, ggml.Q4_1, n, k)
+    x = make_x(m, k)
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_Q8).cpu().numpy()
+    want = oracle.linear(ggml.Q4_1, raw, x, n, k, act_mode=1, n_threads=4)
+    assert np.array_equal(got, want)
+
+
+def test_quantize_rows_q8_bit_exact(zq, oracle):
+    x = make_x(3, 1152)
+    x[0, :32] = 0.0                                  # all-zero block: scale 1, q 0
+    x[1, 32:64] = np.arange(32, dtype=np.float32) - 16.0  # the reference's ramp
+    x[2, 5] = 1e-30
+    q, scale, s = zq.quantize_rows_q8(torch.from_numpy(x).cuda())
+    for m in range(3):
+        oq, oscale, osum, _ = oracle.quantize_row_q8(x[m])
+        assert np.array_equal(q[m].cpu().numpy().reshape(-1, 32), oq)
+        assert np.array_equal(scale[m].cpu().numpy().view(np.uint32), oscale.view(np.uint32))
+        assert np.array_equal(s[m].cpu().numpy(), osum)
+    assert scale[0, 0].item() == 1.0 and q[1, 32].item() == -127 and q[1, 48].item() == 0
+
+
+@pytest.mark.parametrize("act", [0, 1])
+def test_epilogue_bias_gelu_mul_residual(zq, oracle, act):
+    n, k = 384, 256
+    raw = make_weight(oracle, ggml.Q4_0, n, k, std=0.1)
+    qw = zq.QuantWeight(raw, ggml.Q4_0, n, k)
+    x = make_x(1, k)
+    rng = np.random.default_rng(5)
+    bias, mul, res = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    base = oracle.linear(ggml.Q4_0, raw, x, n, k, act_mode=act, n_threads=2)[0]
+    want = oracle.gelu(base + bias) * mul + res
+    t = lambda a: torch.from_numpy(a).cuda()
+    got = zq.quant_matmul_no_grad(t(x), qw, act, bias=t(bias), gelu=True, mul=t(mul[None]), residual=t(res[None]))
+    assert rel_l2(got.cpu().numpy()[0], want) <= 1e-5
+    # residual may alias the output (x += W h, src/models/gpt2.zig:495-496)
+    y = t(res[None].copy())
+    zq.quant_matmul_no_grad(t(x), qw, act, bias=t(bias), residual=y, out=y)
+    assert rel_l2(y.cpu().numpy()[0], base + bias + res) <= 1e-6
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_vocab_head_full_size(zq, oracle, qtype):
+    """1152 -> 262144, the largest GEMV of the path (Gemma-3 logits, gemma3.zig:830-846)."""
+    n, k = 262144, 1152
+    g = torch.Generator(device="cuda").manual_seed(42)
+    w = torch.randn(n, k, generator=g, device="cuda") * 0.02
+    raw_d = ggml.quantize(qtype, w)
+    del w
+    qw = zq.QuantWeight(raw_d, qtype, n, k)
+    raw = raw_d.cpu().numpy()
+    x = make_x(1, k)
+    xd = torch.from_numpy(x).cuda()
+    got32 = zq.quant_matmul_no_grad(xd, qw, zq.ACT_F32).cpu().numpy()
+    gotq8 = zq.quant_matmul_no_grad(xd, qw, zq.ACT_Q8).cpu().numpy()
+    want32 = oracle.linear(qtype, raw, x, n, k, act_mode=0, n_threads=8)
+    wantq8 = oracle.linear(qtype, raw, x, n, k, act_mode=1, n_threads=8)
+    assert rel_l2(got32, want32) <= REL_L2_GUARD
+    assert np.array_equal(gotq8, wantq8)
+    assert int(zq.argmax(torch.from_numpy(got32[0]).cuda()).item()) == oracle.argmax(want32[0])
+
+
+def test_large_k_f32(zq, oracle):
+    """14336 -> 4096 (sharded-GEMM shape); K beyond the reference thread pool's 8192 limit, so only
+    the f32-activation path has a CPU counterpart."""
+    n, k = 512, 14336
+    raw = make_weight(oracle, ggml.Q4_0, n, k)
+    qw = zq.QuantWeight(raw, ggml.Q4_0, n, k)
+    x = make_x(1, k)
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_F32).cpu().numpy()
+    want = oracle.linear(ggml.Q4_0, raw, x, n, k, act_mode=0, n_threads=4)
+    assert rel_l2(got, want) <= REL_L2_GUARD
+
+
+def test_linearity_property(zq, oracle):
+    """W(a x1 + x2) == a W x1 + W x2 to f32 accuracy — a size-independent check of the f32 path."""
+    n, k = 4096, 4096
+    raw = make_weight(oracle, ggml.Q8_0, n, k)
+    qw = zq.QuantWeight(raw, ggml.Q8_0, n, k)
+    x1, x2 = torch.from_numpy(make_x(1, k, 1)).cuda(), torch.from_numpy(make_x(1, k, 2)).cuda()
+    lhs = zq.quant_matmul_no_grad(2.0 * x1 + x2, qw)
+    rhs = 2.0 * zq.quant_matmul_no_grad(x1, qw) + zq.quant_matmul_no_grad(x2, qw)
+    assert rel_l2(lhs.cpu().numpy(), rhs.cpu().numpy()) <= 1e-5
+
+
+def test_error_statuses(zq):
+    from zignn_b200 import _lib
+    with pytest.raises(_lib.ZqError) as e:
+        zq.QuantWeight(np.zeros(22, np.uint8), 6, 1, 32)  # q5_0
+    assert e.value.status == 2
+    with pytest.raises(_lib.ZqError) as e:
+        zq.QuantWeight(np.zeros(27, np.uint8), ggml.Q4_0, 1, 48)
+    assert e.value.status == 1
+    qw = zq.QuantWeight(np.zeros(18, np.uint8), ggml.Q4_0, 1, 32)
+    with pytest.raises(ValueError):
+        zq.quant_matmul_no_grad(torch.zeros(1, 64, device="cuda"), qw)
+    # zero rows is a no-op
+    assert zq.quant_matmul_no_grad(torch.zeros(0, 32, device="cuda"), qw).shape == (0, 1)
+
+
+def test_matvec_f32_and_argmax(zq, oracle):
+    rng = np.random.default_rng(9)
+    w = (rng.standard_normal((5003, 768)) * 0.02).astype(np.float32)
+    x = rng.standard_normal(768).astype(np.float32)
+    got = zq.matvec_f32(torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()).cpu().numpy()
+    want = oracle.matmul_f32(0, w.view(np.uint8), x, 5003, 768, 4)
+    assert rel_l2(got, want) <= REL_L2_GUARD
+    assert int(zq.argmax(torch.from_numpy(want).cuda()).item()) == oracle.argmax(want)
+    ties = np.array([1, 7, 7, 7, -2], np.float32)
+    assert int(zq.argmax(torch.from_numpy(ties).cuda()).item()) == 1
+    big = np.zeros(300000, np.float32)
+    big[[250000, 123456]] = 3.0
+    assert int(zq.argmax(torch.from_numpy(big).cuda()).item()) == 123456

@@ -1,0 +1,340 @@
+"""Host-side mirror of zig-nn's quantised-inference interface on top of libzq's C ABI.
+
+Names follow the reference: QuantWeight / quant_matmul_no_grad (src/diff/mps_runtime.zig:1164-1205),
+MetalContext.dispatch_* (src/backend/metal.zig:729-1096), cuda_ops.zig dispatchers, and the
+gpt2(C) / gemma3(C) engines (src/models). torch is used for device memory and streams only.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib, ggml
+from . import structs as S
+
+ACT_F32, ACT_Q8, ACT_F16 = 0, 1, 2
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _dev_f32(t):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+        raise ValueError("expected a contiguous float32 CUDA tensor")
+    return t
+
+
+class QuantWeight:
+    """A GGUF-quantised weight [out_dim, in_dim] resident on the device."""
+
+    def __init__(self, raw, quant_type, out_dim, in_dim):
+        """raw: the GGUF tensor bytes — uint8 numpy array / CPU tensor (host) or CUDA uint8 tensor."""
+        lib = _lib.load()
+        self.quant_type, self.out_dim, self.in_dim = int(quant_type), int(out_dim), int(in_dim)
+        nbytes = ggml.tensor_bytes(self.quant_type, self.out_dim * self.in_dim)
+        h = C.c_void_p()
+        if isinstance(raw, torch.Tensor) and raw.is_cuda:
+            raw = raw.contiguous().view(torch.uint8).reshape(-1)
+            if raw.numel() != nbytes and nbytes:
+                raise ValueError("raw byte count %d != %d" % (raw.numel(), nbytes))
+            rc = lib.zq_weight_from_device(_ptr(raw), self.quant_type, self.out_dim, self.in_dim,
+                                           _stream(), C.byref(h))
+            torch.cuda.current_stream().synchronize()  # raw may be freed by the caller afterwards
+        else:
+            if isinstance(raw, torch.Tensor):
+                raw = raw.numpy()
+            raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+            if raw.size != nbytes and nbytes:
+                raise ValueError("raw byte count %d != %d" % (raw.size, nbytes))
+            rc = lib.zq_weight_upload(raw.ctypes.data_as(C.c_void_p), self.quant_type, self.out_dim,
+                                      self.in_dim, _stream(), C.byref(h))
+        _lib.check(rc, "zq_weight_upload")
+        self._h = h
+
+    @property
+    def handle(self):
+        return self._h
+
+    def device_bytes(self):
+        return _lib.load().zq_weight_device_bytes(self._h)
+
+    def raw_bytes(self):
+        """The original GGUF bytes, rebuilt on the device (uint8 CUDA tensor)."""
+        n = ggml.tensor_bytes(self.quant_type, self.out_dim * self.in_dim)
+        out = torch.empty(n, dtype=torch.uint8, device="cuda")
+        _lib.check(_lib.load().zq_weight_download_raw(self._h, _ptr(out), _stream()), "zq_weight_download_raw")
+        return out
+
+    def dequantize(self):
+        out = torch.empty(self.out_dim, self.in_dim, dtype=torch.float32, device="cuda")
+        _lib.check(_lib.load().zq_dequantize(self._h, _ptr(out), _stream()), "zq_dequantize")
+        return out
+
+    def dequant_rows_scaled(self, token_ids, scale):
+        ids = token_ids.to(device="cuda", dtype=torch.int32).contiguous()
+        out = torch.empty(ids.numel(), self.in_dim, dtype=torch.float32, device="cuda")
+        _lib.check(_lib.load().zq_dequant_rows_scaled(self._h, _ptr(ids), ids.numel(), float(scale),
+                                                      _ptr(out), _stream()), "zq_dequant_rows_scaled")
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _lib.load().zq_weight_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def quant_matmul_no_grad(x, qw, act_mode=ACT_F32, bias=None, gelu=False, mul=None, residual=None,
+                         out=None, workspace=None):
+    """x [..., in_dim] f32 CUDA -> [..., out_dim]; quantised weight times activations."""
+    lib = _lib.load()
+    x = _dev_f32(x)
+    if x.shape[-1] != qw.in_dim:
+        raise ValueError("last dim %d != in_dim %d" % (x.shape[-1], qw.in_dim))
+    m = x.numel() // qw.in_dim
+    y = out if out is not None else torch.empty(*x.shape[:-1], qw.out_dim, dtype=torch.float32, device=x.device)
+    ep = S.Epilogue(_ptr(bias), int(bool(gelu)), _ptr(mul), _ptr(residual))
+    need = lib.zq_matmul_workspace_bytes(qw.handle, m, act_mode)
+    ws = workspace
+    if need and (ws is None or ws.numel() < need):
+        ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+    rc = lib.zq_matmul(qw.handle, _ptr(x), _ptr(y), m, act_mode, C.byref(ep), _ptr(ws) if need else None,
+                       need, _stream())
+    _lib.check(rc, "zq_matmul")
+    return y
+
+
+def quantize_rows_q8(x):
+    x = _dev_f32(x)
+    k = x.shape[-1]
+    m = x.numel() // k
+    q = torch.empty(m, k, dtype=torch.int8, device=x.device)
+    scale = torch.empty(m, k // 32, dtype=torch.float32, device=x.device)
+    s = torch.empty(m, k // 32, dtype=torch.int32, device=x.device)
+    _lib.check(_lib.load().zq_quantize_rows_q8(_ptr(x), m, k, _ptr(q), _ptr(scale), _ptr(s), _stream()),
+               "zq_quantize_rows_q8")
+    return q, scale, s
+
+
+def matvec_f32(w, x):
+    w, x = _dev_f32(w), _dev_f32(x)
+    y = torch.empty(w.shape[0], dtype=torch.float32, device=w.device)
+    _lib.check(_lib.load().zq_matvec_f32(_ptr(w), _ptr(x), _ptr(y), w.shape[0], w.shape[1], _stream()),
+               "zq_matvec_f32")
+    return y
+
+
+def argmax(logits):
+    logits = _dev_f32(logits)
+    out = torch.empty(1, dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.load().zq_argmax(_ptr(logits), logits.numel(), _ptr(out), _stream()), "zq_argmax")
+    return out
+
+
+def rms_norm(x, w, eps):
+    x = _dev_f32(x)
+    out = torch.empty_like(x)
+    dim = x.shape[-1]
+    _lib.check(_lib.load().zq_rms_norm(_ptr(x), _ptr(_dev_f32(w)), _ptr(out), dim, x.numel() // dim, eps,
+                                       _stream()), "zq_rms_norm")
+    return out
+
+
+def rms_norm_residual(x, w, residual, eps):
+    x, residual = _dev_f32(x), _dev_f32(residual)
+    dim = x.shape[-1]
+    _lib.check(_lib.load().zq_rms_norm_residual(_ptr(x), _ptr(_dev_f32(w)), _ptr(residual), dim,
+                                                x.numel() // dim, eps, _stream()), "zq_rms_norm_residual")
+    return residual
+
+
+def rms_norm_in_place(x, w, dim, eps):
+    x = _dev_f32(x)
+    _lib.check(_lib.load().zq_rms_norm_in_place(_ptr(x), _ptr(_dev_f32(w)), dim, x.numel() // dim, eps,
+                                                _stream()), "zq_rms_norm_in_place")
+    return x
+
+
+def rope_freqs(head_dim, base):
+    f = np.empty(head_dim // 2, dtype=np.float32)
+    _lib.check(_lib.load().zq_rope_freqs_host(head_dim, base, f.ctypes.data_as(C.c_void_p)), "zq_rope_freqs_host")
+    return f
+
+
+def rope(x, freqs, n_heads, pos):
+    x, freqs = _dev_f32(x), _dev_f32(freqs)
+    _lib.check(_lib.load().zq_rope(_ptr(x), _ptr(freqs), freqs.numel(), n_heads, float(pos), _stream()), "zq_rope")
+    return x
+
+
+def gelu_mul(gate, up):
+    gate, up = _dev_f32(gate), _dev_f32(up)
+    _lib.check(_lib.load().zq_gelu_mul(_ptr(gate), _ptr(up), gate.numel(), _stream()), "zq_gelu_mul")
+    return gate
+
+
+def write_kv_cache(k, v, k_cache, v_cache, pos):
+    _lib.check(_lib.load().zq_write_kv_cache(_ptr(_dev_f32(k)), _ptr(_dev_f32(v)), _ptr(_dev_f32(k_cache)),
+                                             _ptr(_dev_f32(v_cache)), pos, k.numel(), _stream()),
+               "zq_write_kv_cache")
+
+
+def attention_decode(q, k_cache, v_cache, n_head, n_kv_head, head_dim, kv_start, kv_end):
+    q = _dev_f32(q)
+    out = torch.empty(n_head * head_dim, dtype=torch.float32, device=q.device)
+    _lib.check(_lib.load().zq_attention_decode(_ptr(q), _ptr(_dev_f32(k_cache)), _ptr(_dev_f32(v_cache)),
+                                               _ptr(out), n_head, n_kv_head, head_dim, kv_start, kv_end,
+                                               _stream()), "zq_attention_decode")
+    return out
+
+
+def softmax(x):
+    x = _dev_f32(x)
+    out = torch.empty_like(x)
+    cols = x.shape[-1]
+    _lib.check(_lib.load().zq_softmax_out(_ptr(out), _ptr(x), x.numel() // cols, cols, _stream()), "zq_softmax_out")
+    return out
+
+
+def softmax_(x):
+    x = _dev_f32(x)
+    cols = x.shape[-1]
+    _lib.check(_lib.load().zq_softmax(_ptr(x), x.numel() // cols, cols, _stream()), "zq_softmax")
+    return x
+
+
+def layer_norm(x, gamma, beta, eps):
+    x = _dev_f32(x)
+    out = torch.empty_like(x)
+    cols = x.shape[-1]
+    _lib.check(_lib.load().zq_layer_norm(_ptr(out), _ptr(x), _ptr(_dev_f32(gamma)), _ptr(_dev_f32(beta)),
+                                         x.numel() // cols, cols, eps, _stream()), "zq_layer_norm")
+    return out
+
+
+def gelu(x):
+    x = _dev_f32(x)
+    out = torch.empty_like(x)
+    _lib.check(_lib.load().zq_gelu(_ptr(out), _ptr(x), x.numel(), _stream()), "zq_gelu")
+    return out
+
+
+def add_broadcast(a, b):
+    a, b = _dev_f32(a), _dev_f32(b)
+    out = torch.empty_like(a)
+    _lib.check(_lib.load().zq_add_broadcast(_ptr(out), _ptr(a), _ptr(b), a.numel(), b.numel(), _stream()),
+               "zq_add_broadcast")
+    return out
+
+
+def mul_broadcast(a, b):
+    a, b = _dev_f32(a), _dev_f32(b)
+    out = torch.empty_like(a)
+    _lib.check(_lib.load().zq_mul_broadcast(_ptr(out), _ptr(a), _ptr(b), a.numel(), b.numel(), _stream()),
+               "zq_mul_broadcast")
+    return out
+
+
+def gather(table, idx):
+    table = _dev_f32(table)
+    idx = idx.to(device=table.device, dtype=torch.int32).contiguous()
+    out = torch.empty(idx.numel(), table.shape[1], dtype=torch.float32, device=table.device)
+    _lib.check(_lib.load().zq_gather(_ptr(out), _ptr(table), _ptr(idx), idx.numel(), table.shape[1], _stream()),
+               "zq_gather")
+    return out
+
+
+def scale(x, s):
+    x = _dev_f32(x)
+    out = torch.empty_like(x)
+    _lib.check(_lib.load().zq_scale(_ptr(out), _ptr(x), float(s), x.numel(), _stream()), "zq_scale")
+    return out
+
+
+class _DevicePtrView:
+    """Exposes borrowed device memory (n f32 values) through __cuda_array_interface__."""
+
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {
+            "shape": (n,), "typestr": "<f4", "data": (int(ptr), False), "version": 2, "strides": None,
+        }
+
+
+class _Engine:
+    _prefix = None
+
+    def __init__(self, host_model):
+        lib = _lib.load()
+        self._cfg = host_model.config_struct()
+        self._w = host_model.weights_struct()
+        self.vocab = self._cfg.vocab
+        h = C.c_void_p()
+        rc = getattr(lib, self._prefix + "_create")(C.byref(self._cfg), C.byref(self._w), _stream(), C.byref(h))
+        _lib.check(rc, self._prefix + "_create")
+        self._h = h
+
+    def _logits(self, ptr):
+        """Copy of the engine-owned logits buffer (valid only until the next engine call)."""
+        view = torch.as_tensor(_DevicePtrView(ptr.value, self.vocab), device="cuda")
+        return view.clone()
+
+    def reset_cache(self):
+        _lib.check(getattr(_lib.load(), self._prefix + "_reset_cache")(self._h))
+
+    @property
+    def seq_len(self):
+        n = C.c_uint32()
+        _lib.check(getattr(_lib.load(), self._prefix + "_seq_len")(self._h, C.byref(n)))
+        return n.value
+
+    def prefill(self, tokens):
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        ptr = C.c_void_p()
+        rc = getattr(_lib.load(), self._prefix + "_prefill")(self._h, toks.ctypes.data_as(C.c_void_p), toks.size,
+                                                             _stream(), C.byref(ptr))
+        _lib.check(rc, self._prefix + "_prefill")
+        return self._logits(ptr)
+
+    def decode_next(self, token):
+        ptr = C.c_void_p()
+        rc = getattr(_lib.load(), self._prefix + "_decode_next")(self._h, int(token), _stream(), C.byref(ptr))
+        _lib.check(rc, self._prefix + "_decode_next")
+        return self._logits(ptr)
+
+    def decode_greedy(self, first_token, n_steps):
+        out = np.empty(n_steps, dtype=np.uint32)
+        rc = getattr(_lib.load(), self._prefix + "_decode_greedy")(self._h, int(first_token), n_steps, _stream(),
+                                                                   out.ctypes.data_as(C.c_void_p))
+        _lib.check(rc, self._prefix + "_decode_greedy")
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None):
+            getattr(_lib.load(), self._prefix + "_free")(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Gpt2(_Engine):
+    """gpt2(C): init / prefill / decode_next (src/models/gpt2.zig:236,423,443)."""
+    _prefix = "zq_gpt2"
+
+
+class Gemma3(_Engine):
+    """gemma3(C): init / prefill / decode_next (src/models/gemma3.zig:283,551,789)."""
+    _prefix = "zq_gemma3"

@@ -1,0 +1,554 @@
+// Device-resident GPT-2 and Gemma-3 decode engines: the counterparts of zig-nn's gpt2(C)
+// (src/models/gpt2.zig:198-532), gemma3(C) (src/models/gemma3.zig:243-848) and the one-encoder
+// Metal engine (src/models/gemma3_metal.zig:189-260). All tensors are uploaded once; a decode step
+// is a fixed sequence of kernel launches on the caller's stream with no host synchronisation.
+#include <math.h>
+
+#include <new>
+#include <vector>
+
+#include "zq_internal.h"
+
+namespace zq {
+namespace {
+
+struct DeviceArena {
+    std::vector<void*> ptrs;
+    size_t total = 0;
+    ~DeviceArena() {
+        for (void* p : ptrs) cudaFree(p);
+    }
+    int alloc(void** out, size_t bytes) {
+        cudaError_t e = cudaMalloc(out, bytes ? bytes : 4);
+        if (e != cudaSuccess) {
+            g_last_cuda_error = (int)e;
+            return e == cudaErrorMemoryAllocation ? ZQ_ERR_NO_MEM : ZQ_ERR_CUDA;
+        }
+        ptrs.push_back(*out);
+        total += bytes;
+        return ZQ_OK;
+    }
+    template <typename T>
+    int alloc_n(T** out, size_t n) {
+        return alloc(reinterpret_cast<void**>(out), n * sizeof(T));
+    }
+    int upload_f32(float** out, const float* host, size_t n, cudaStream_t st) {
+        if (!host) return ZQ_ERR_BAD_ARG;
+        int rc = alloc_n(out, n);
+        if (rc != ZQ_OK) return rc;
+        ZQ_CUDA(cudaMemcpyAsync(*out, host, n * sizeof(float), cudaMemcpyHostToDevice, st));
+        return ZQ_OK;
+    }
+};
+
+// A linear layer's weight: quantised (zq_weight) or plain f32 [out_dim][in_dim]
+// (the .f32 branch of linear_forward_q, gpt2.zig:652-671).
+struct Linear {
+    zq_weight* qw = nullptr;
+    float* f32w = nullptr;
+    uint32_t out_dim = 0, in_dim = 0;
+};
+
+int upload_linear(Linear* L, const zq_tensor_ref& t, uint32_t out_dim, uint32_t in_dim,
+                  DeviceArena& arena, cudaStream_t st) {
+    if (!t.data || t.out_dim != out_dim || t.in_dim != in_dim) return ZQ_ERR_BAD_ARG;
+    L->out_dim = out_dim;
+    L->in_dim = in_dim;
+    if (t.type == ZQ_TYPE_F32)
+        return arena.upload_f32(&L->f32w, static_cast<const float*>(t.data), (size_t)out_dim * in_dim, st);
+    if (!is_quant(t.type)) return ZQ_ERR_UNSUPPORTED;
+    return zq_weight_upload(t.data, t.type, out_dim, in_dim, st, &L->qw);
+}
+
+__global__ void set_u32_kernel(uint32_t* p, uint32_t v) { *p = v; }
+
+// x = wte[token] + wpe[pos]  (gpt2.zig:449-453)
+__global__ void gpt2_embed_kernel(float* __restrict__ x, const float* __restrict__ wte,
+                                  const float* __restrict__ wpe, const uint32_t* __restrict__ token,
+                                  uint32_t pos, uint32_t embed) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < embed) x[i] = wte[(size_t)(*token) * embed + i] + wpe[(size_t)pos * embed + i];
+}
+
+__global__ void token_to_i32_kernel(int32_t* dst, const uint32_t* src) { *dst = (int32_t)*src; }
+__global__ void i32_to_token_kernel(uint32_t* dst, const int32_t* src, uint32_t* record) {
+    *dst = (uint32_t)*src;
+    if (record) *record = (uint32_t)*src;
+}
+
+}  // namespace
+}  // namespace zq
+
+using namespace zq;
+
+// ------------------------------------------------------------------------------ GPT-2
+
+struct zq_gpt2 {
+    zq_gpt2_config c;
+    DeviceArena arena;
+    float *wte = nullptr, *wpe = nullptr, *ln_f_w = nullptr, *ln_f_b = nullptr;
+    struct Block {
+        float *ln1_w, *ln1_b, *qkv_b, *proj_b, *ln2_w, *ln2_b, *fc_b, *mproj_b;
+        Linear qkv, proj, fc, mproj;
+    };
+    std::vector<Block> blocks;
+    std::vector<float*> k, v;  // per layer [ctx][embed]
+    float *x = nullptr, *ln = nullptr, *qkv = nullptr, *att = nullptr, *hid = nullptr, *logits = nullptr;
+    uint32_t* d_token = nullptr;
+    int32_t* d_arg = nullptr;
+    uint32_t* d_record = nullptr;  // ctx entries for greedy decoding
+    uint32_t seq_len = 0;
+    ~zq_gpt2() {
+        for (auto& b : blocks) {
+            zq_weight_free(b.qkv.qw);
+            zq_weight_free(b.proj.qw);
+            zq_weight_free(b.fc.qw);
+            zq_weight_free(b.mproj.qw);
+        }
+    }
+};
+
+static int gpt2_linear(const Linear& L, const float* x, float* y, const float* bias, int gelu,
+                       const float* residual, cudaStream_t st) {
+    zq_epilogue ep{bias, gelu, nullptr, residual};
+    if (L.qw) return launch_gemv_f32(L.qw, x, y, 1, &ep, st);
+    // f32 weight: matvec, then the same epilogue as separate launches
+    int rc = zq_matvec_f32(L.f32w, x, y, L.out_dim, L.in_dim, st);
+    if (rc == ZQ_OK && bias) rc = zq_add_broadcast(y, y, bias, L.out_dim, L.out_dim, st);
+    if (rc == ZQ_OK && gelu) rc = zq_gelu(y, y, L.out_dim, st);
+    if (rc == ZQ_OK && residual) rc = zq_add_broadcast(y, y, residual, L.out_dim, L.out_dim, st);
+    return rc;
+}
+
+// One decode step at position `pos`, token taken from m->d_token. Logits only when asked.
+static int gpt2_step(zq_gpt2* m, uint32_t pos, bool want_logits, cudaStream_t st) {
+    const zq_gpt2_config& C = m->c;
+    const uint32_t E = C.embed, hd = E / C.head;
+    gpt2_embed_kernel<<<(E + 255) / 256, 256, 0, st>>>(m->x, m->wte, m->wpe, m->d_token, pos, E);
+    ZQ_LAUNCH_CHECK();
+    int rc;
+    for (uint32_t l = 0; l < C.layer; ++l) {
+        const zq_gpt2::Block& b = m->blocks[l];
+        if ((rc = zq_layer_norm(m->ln, m->x, b.ln1_w, b.ln1_b, 1, E, 1e-5f, st))) return rc;
+        if ((rc = gpt2_linear(b.qkv, m->ln, m->qkv, b.qkv_b, 0, nullptr, st))) return rc;
+        if ((rc = zq_write_kv_cache(m->qkv + E, m->qkv + 2 * E, m->k[l], m->v[l], pos, E, st))) return rc;
+        if ((rc = zq_attention_decode(m->qkv, m->k[l], m->v[l], m->att, C.head, C.head, hd, 0, pos + 1, st)))
+            return rc;
+        if ((rc = gpt2_linear(b.proj, m->att, m->x, b.proj_b, 0, m->x, st))) return rc;
+        if ((rc = zq_layer_norm(m->ln, m->x, b.ln2_w, b.ln2_b, 1, E, 1e-5f, st))) return rc;
+        if ((rc = gpt2_linear(b.fc, m->ln, m->hid, b.fc_b, 1, nullptr, st))) return rc;
+        if ((rc = gpt2_linear(b.mproj, m->hid, m->x, b.mproj_b, 0, m->x, st))) return rc;
+    }
+    if (want_logits) {
+        if ((rc = zq_layer_norm(m->ln, m->x, m->ln_f_w, m->ln_f_b, 1, E, 1e-5f, st))) return rc;
+        if ((rc = zq_matvec_f32(m->wte, m->ln, m->logits, C.vocab, E, st))) return rc;
+    }
+    return ZQ_OK;
+}
+
+extern "C" {
+
+int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_stream stream,
+                   zq_gpt2** out) {
+    if (!cfg || !w || !out || !w->blocks) return ZQ_ERR_BAD_ARG;
+    *out = nullptr;
+    if (!cfg->vocab || !cfg->embed || !cfg->head || !cfg->layer || !cfg->ctx || !cfg->ffn ||
+        cfg->embed % cfg->head || cfg->embed % 32 || cfg->ffn % 32)
+        return ZQ_ERR_BAD_ARG;
+    zq_gpt2* m = new (std::nothrow) zq_gpt2;
+    if (!m) return ZQ_ERR_NO_MEM;
+    m->c = *cfg;
+    cudaStream_t st = as_stream(stream);
+    const uint32_t E = cfg->embed, F = cfg->ffn;
+    int rc = ZQ_OK;
+#define TRY(expr)                  \
+    do {                           \
+        if ((rc = (expr)) != ZQ_OK) { \
+            delete m;              \
+            return rc;             \
+        }                          \
+    } while (0)
+    TRY(m->arena.upload_f32(&m->wte, w->wte, (size_t)cfg->vocab * E, st));
+    TRY(m->arena.upload_f32(&m->wpe, w->wpe, (size_t)cfg->ctx * E, st));
+    TRY(m->arena.upload_f32(&m->ln_f_w, w->ln_f_weight, E, st));
+    TRY(m->arena.upload_f32(&m->ln_f_b, w->ln_f_bias, E, st));
+    m->blocks.resize(cfg->layer);
+    m->k.resize(cfg->layer);
+    m->v.resize(cfg->layer);
+    for (uint32_t l = 0; l < cfg->layer; ++l) {
+        const zq_gpt2_block& s = w->blocks[l];
+        zq_gpt2::Block& b = m->blocks[l];
+        TRY(m->arena.upload_f32(&b.ln1_w, s.ln1_weight, E, st));
+        TRY(m->arena.upload_f32(&b.ln1_b, s.ln1_bias, E, st));
+        TRY(m->arena.upload_f32(&b.qkv_b, s.attn_qkv_bias, 3 * (size_t)E, st));
+        TRY(m->arena.upload_f32(&b.proj_b, s.attn_proj_bias, E, st));
+        TRY(m->arena.upload_f32(&b.ln2_w, s.ln2_weight, E, st));
+        TRY(m->arena.upload_f32(&b.ln2_b, s.ln2_bias, E, st));
+        TRY(m->arena.upload_f32(&b.fc_b, s.mlp_fc_bias, F, st));
+        TRY(m->arena.upload_f32(&b.mproj_b, s.mlp_proj_bias, E, st));
+        TRY(upload_linear(&b.qkv, s.attn_qkv_weight, 3 * E, E, m->arena, st));
+        TRY(upload_linear(&b.proj, s.attn_proj_weight, E, E, m->arena, st));
+        TRY(upload_linear(&b.fc, s.mlp_fc_weight, F, E, m->arena, st));
+        TRY(upload_linear(&b.mproj, s.mlp_proj_weight, E, F, m->arena, st));
+        TRY(m->arena.alloc_n(&m->k[l], (size_t)cfg->ctx * E));
+        TRY(m->arena.alloc_n(&m->v[l], (size_t)cfg->ctx * E));
+        cudaMemsetAsync(m->k[l], 0, (size_t)cfg->ctx * E * sizeof(float), st);
+        cudaMemsetAsync(m->v[l], 0, (size_t)cfg->ctx * E * sizeof(float), st);
+    }
+    TRY(m->arena.alloc_n(&m->x, E));
+    TRY(m->arena.alloc_n(&m->ln, E));
+    TRY(m->arena.alloc_n(&m->qkv, 3 * (size_t)E));
+    TRY(m->arena.alloc_n(&m->att, E));
+    TRY(m->arena.alloc_n(&m->hid, F));
+    TRY(m->arena.alloc_n(&m->logits, cfg->vocab));
+    TRY(m->arena.alloc_n(&m->d_token, 1));
+    TRY(m->arena.alloc_n(&m->d_arg, 1));
+    TRY(m->arena.alloc_n(&m->d_record, cfg->ctx));
+#undef TRY
+    cudaError_t e = cudaStreamSynchronize(st);  // host weight buffers may be released after create
+    if (e != cudaSuccess) {
+        delete m;
+        return cuda_fail(e);
+    }
+    *out = m;
+    return ZQ_OK;
+}
+
+int zq_gpt2_free(zq_gpt2* m) {
+    delete m;
+    return ZQ_OK;
+}
+
+int zq_gpt2_reset_cache(zq_gpt2* m) {
+    if (!m) return ZQ_ERR_BAD_ARG;
+    m->seq_len = 0;
+    return ZQ_OK;
+}
+
+int zq_gpt2_seq_len(const zq_gpt2* m, uint32_t* seq_len) {
+    if (!m || !seq_len) return ZQ_ERR_BAD_ARG;
+    *seq_len = m->seq_len;
+    return ZQ_OK;
+}
+
+int zq_gpt2_prefill(zq_gpt2* m, const uint32_t* h_tokens, uint32_t n, zq_stream stream,
+                    const float** d_logits) {
+    if (!m || !h_tokens || !d_logits) return ZQ_ERR_BAD_ARG;
+    if (n == 0 || n > m->c.ctx) return ZQ_ERR_SEQUENCE;
+    cudaStream_t st = as_stream(stream);
+    m->seq_len = 0;
+    for (uint32_t t = 0; t < n; ++t) {
+        if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
+        set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, h_tokens[t]);
+        ZQ_LAUNCH_CHECK();
+        int rc = gpt2_step(m, t, t + 1 == n, st);
+        if (rc != ZQ_OK) return rc;
+    }
+    m->seq_len = n;
+    *d_logits = m->logits;
+    return ZQ_OK;
+}
+
+int zq_gpt2_decode_next(zq_gpt2* m, uint32_t token, zq_stream stream, const float** d_logits) {
+    if (!m || !d_logits) return ZQ_ERR_BAD_ARG;
+    if (m->seq_len >= m->c.ctx) return ZQ_ERR_SEQUENCE;
+    if (token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, token);
+    ZQ_LAUNCH_CHECK();
+    int rc = gpt2_step(m, m->seq_len, true, st);
+    if (rc != ZQ_OK) return rc;
+    m->seq_len += 1;
+    *d_logits = m->logits;
+    return ZQ_OK;
+}
+
+int zq_gpt2_decode_greedy(zq_gpt2* m, uint32_t first_token, uint32_t n_steps, zq_stream stream,
+                          uint32_t* h_tokens_out) {
+    if (!m || !h_tokens_out) return ZQ_ERR_BAD_ARG;
+    if (n_steps == 0) return ZQ_OK;
+    if ((uint64_t)m->seq_len + n_steps > m->c.ctx) return ZQ_ERR_SEQUENCE;
+    if (first_token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, first_token);
+    ZQ_LAUNCH_CHECK();
+    for (uint32_t s = 0; s < n_steps; ++s) {
+        int rc = gpt2_step(m, m->seq_len, true, st);
+        if (rc != ZQ_OK) return rc;
+        m->seq_len += 1;
+        if ((rc = zq_argmax(m->logits, m->c.vocab, m->d_arg, st))) return rc;
+        i32_to_token_kernel<<<1, 1, 0, st>>>(m->d_token, m->d_arg, m->d_record + s);
+        ZQ_LAUNCH_CHECK();
+    }
+    ZQ_CUDA(cudaMemcpyAsync(h_tokens_out, m->d_record, n_steps * sizeof(uint32_t),
+                            cudaMemcpyDeviceToHost, st));
+    ZQ_CUDA(cudaStreamSynchronize(st));
+    return ZQ_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------ Gemma-3
+
+struct zq_gemma3 {
+    zq_gemma3_config c;
+    DeviceArena arena;
+    zq_weight* token_embd = nullptr;
+    float* output_norm_w = nullptr;
+    struct Block {
+        float *attn_norm_w, *post_attn_norm_w, *q_norm_w, *k_norm_w, *ffn_norm_w, *post_ffw_norm_w;
+        zq_weight *q, *k, *v, *o, *gate, *up, *down;
+    };
+    std::vector<Block> blocks;
+    std::vector<float*> k, v;  // per layer [ctx][kv_dim]
+    float* freqs = nullptr;
+    float *x = nullptr, *h = nullptr, *q = nullptr, *kb = nullptr, *vb = nullptr, *att = nullptr,
+          *proj = nullptr, *gate = nullptr, *up = nullptr, *ffn = nullptr, *logits = nullptr;
+    int8_t* xq = nullptr;   // quantised activation row, max(embed, ffn, q_dim)
+    float* xscale = nullptr;
+    int32_t* xsum = nullptr;
+    uint32_t* d_token = nullptr;
+    int32_t* d_tok_i32 = nullptr;
+    int32_t* d_arg = nullptr;
+    uint32_t* d_record = nullptr;
+    uint32_t seq_len = 0;
+    ~zq_gemma3() {
+        zq_weight_free(token_embd);
+        for (auto& b : blocks) {
+            zq_weight_free(b.q);
+            zq_weight_free(b.k);
+            zq_weight_free(b.v);
+            zq_weight_free(b.o);
+            zq_weight_free(b.gate);
+            zq_weight_free(b.up);
+            zq_weight_free(b.down);
+        }
+    }
+};
+
+// Quantise the row once (thread_pool.zig:111-114), then any number of weights can consume it.
+static int gemma_quantize(zq_gemma3* m, const float* x, uint32_t dim, cudaStream_t st) {
+    return launch_quantize_rows_q8(x, 1, dim, m->xq, m->xscale, m->xsum, st);
+}
+static int gemma_gemv(zq_gemma3* m, const zq_weight* w, float* y, cudaStream_t st) {
+    return launch_gemv_q8(w, m->xq, m->xscale, m->xsum, y, 1, nullptr, st);
+}
+
+static int gemma3_step(zq_gemma3* m, uint32_t pos, bool want_logits, cudaStream_t st) {
+    const zq_gemma3_config& C = m->c;
+    const uint32_t E = C.embed, D = C.head_dim, QD = C.head * D, KD = C.head_kv * D, F = C.ffn;
+    int rc;
+    token_to_i32_kernel<<<1, 1, 0, st>>>(m->d_tok_i32, m->d_token);
+    ZQ_LAUNCH_CHECK();
+    if ((rc = zq_dequant_rows_scaled(m->token_embd, m->d_tok_i32, 1, sqrtf((float)E), m->x, st))) return rc;
+    for (uint32_t l = 0; l < C.layer; ++l) {
+        const zq_gemma3::Block& b = m->blocks[l];
+        // attention block (gemma3.zig:662-731)
+        if ((rc = zq_rms_norm(m->x, b.attn_norm_w, m->h, E, 1, C.rms_eps, st))) return rc;
+        if ((rc = gemma_quantize(m, m->h, E, st))) return rc;
+        if ((rc = gemma_gemv(m, b.q, m->q, st))) return rc;
+        if ((rc = gemma_gemv(m, b.k, m->kb, st))) return rc;
+        if ((rc = gemma_gemv(m, b.v, m->vb, st))) return rc;
+        if ((rc = zq_rms_norm_in_place(m->q, b.q_norm_w, D, C.head, C.rms_eps, st))) return rc;
+        if ((rc = zq_rms_norm_in_place(m->kb, b.k_norm_w, D, C.head_kv, C.rms_eps, st))) return rc;
+        if ((rc = zq_rope(m->q, m->freqs, D / 2, C.head, (float)pos, st))) return rc;
+        if ((rc = zq_rope(m->kb, m->freqs, D / 2, C.head_kv, (float)pos, st))) return rc;
+        if ((rc = zq_write_kv_cache(m->kb, m->vb, m->k[l], m->v[l], pos, KD, st))) return rc;
+        const bool global = (l % C.global_every) == C.global_every - 1;
+        const uint32_t kv_len = pos + 1;
+        const uint32_t window = global ? kv_len : (kv_len < C.sliding_window ? kv_len : C.sliding_window);
+        const uint32_t kv_start = kv_len - window;
+        if ((rc = zq_attention_decode(m->q, m->k[l], m->v[l], m->att, C.head, C.head_kv, D, kv_start,
+                                      kv_len, st)))
+            return rc;
+        if ((rc = gemma_quantize(m, m->att, QD, st))) return rc;
+        if ((rc = gemma_gemv(m, b.o, m->proj, st))) return rc;
+        if ((rc = zq_rms_norm_residual(m->proj, b.post_attn_norm_w, m->x, E, 1, C.rms_eps, st))) return rc;
+        // FFN block (gemma3.zig:734-773)
+        if ((rc = zq_rms_norm(m->x, b.ffn_norm_w, m->h, E, 1, C.rms_eps, st))) return rc;
+        if ((rc = gemma_quantize(m, m->h, E, st))) return rc;
+        if ((rc = gemma_gemv(m, b.gate, m->gate, st))) return rc;
+        if ((rc = gemma_gemv(m, b.up, m->up, st))) return rc;
+        if ((rc = zq_gelu_mul(m->gate, m->up, F, st))) return rc;
+        if ((rc = gemma_quantize(m, m->gate, F, st))) return rc;
+        if ((rc = gemma_gemv(m, b.down, m->ffn, st))) return rc;
+        if ((rc = zq_rms_norm_residual(m->ffn, b.post_ffw_norm_w, m->x, E, 1, C.rms_eps, st))) return rc;
+    }
+    if (want_logits) {
+        if ((rc = zq_rms_norm(m->x, m->output_norm_w, m->h, E, 1, C.rms_eps, st))) return rc;
+        if ((rc = gemma_quantize(m, m->h, E, st))) return rc;
+        if ((rc = gemma_gemv(m, m->token_embd, m->logits, st))) return rc;
+    }
+    return ZQ_OK;
+}
+
+extern "C" {
+
+int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq_stream stream,
+                     zq_gemma3** out) {
+    if (!cfg || !w || !out || !w->blocks) return ZQ_ERR_BAD_ARG;
+    *out = nullptr;
+    const zq_gemma3_config& C = *cfg;
+    if (!C.vocab || !C.embed || !C.head || !C.head_kv || !C.head_dim || !C.layer || !C.ctx || !C.ffn ||
+        !C.global_every || C.head % C.head_kv || C.embed % 32 || C.ffn % 32 || C.head_dim % 32)
+        return ZQ_ERR_BAD_ARG;
+    const uint32_t E = C.embed, D = C.head_dim, QD = C.head * D, KD = C.head_kv * D, F = C.ffn;
+    uint32_t max_dim = E > F ? E : F;
+    if (QD > max_dim) max_dim = QD;
+    if (max_dim > 16384) return ZQ_ERR_LIMIT;
+    zq_gemma3* m = new (std::nothrow) zq_gemma3;
+    if (!m) return ZQ_ERR_NO_MEM;
+    m->c = C;
+    cudaStream_t st = as_stream(stream);
+    int rc = ZQ_OK;
+#define TRY(expr)                  \
+    do {                           \
+        if ((rc = (expr)) != ZQ_OK) { \
+            delete m;              \
+            return rc;             \
+        }                          \
+    } while (0)
+    auto up_q = [&](zq_weight** dst, const zq_tensor_ref& t, uint32_t od, uint32_t id) -> int {
+        if (!t.data || t.out_dim != od || t.in_dim != id) return ZQ_ERR_BAD_ARG;
+        if (!is_quant(t.type)) return ZQ_ERR_UNSUPPORTED;
+        return zq_weight_upload(t.data, t.type, od, id, st, dst);
+    };
+    TRY(up_q(&m->token_embd, w->token_embd, C.vocab, E));
+    TRY(m->arena.upload_f32(&m->output_norm_w, w->output_norm_weight, E, st));
+    m->blocks.assign(C.layer, zq_gemma3::Block{});
+    m->k.resize(C.layer);
+    m->v.resize(C.layer);
+    for (uint32_t l = 0; l < C.layer; ++l) {
+        const zq_gemma3_block& s = w->blocks[l];
+        zq_gemma3::Block& b = m->blocks[l];
+        TRY(m->arena.upload_f32(&b.attn_norm_w, s.attn_norm_weight, E, st));
+        TRY(m->arena.upload_f32(&b.post_attn_norm_w, s.post_attention_norm_weight, E, st));
+        TRY(m->arena.upload_f32(&b.q_norm_w, s.attn_q_norm_weight, D, st));
+        TRY(m->arena.upload_f32(&b.k_norm_w, s.attn_k_norm_weight, D, st));
+        TRY(m->arena.upload_f32(&b.ffn_norm_w, s.ffn_norm_weight, E, st));
+        TRY(m->arena.upload_f32(&b.post_ffw_norm_w, s.post_ffw_norm_weight, E, st));
+        TRY(up_q(&b.q, s.attn_q_weight, QD, E));
+        TRY(up_q(&b.k, s.attn_k_weight, KD, E));
+        TRY(up_q(&b.v, s.attn_v_weight, KD, E));
+        TRY(up_q(&b.o, s.attn_output_weight, E, QD));
+        TRY(up_q(&b.gate, s.ffn_gate_weight, F, E));
+        TRY(up_q(&b.up, s.ffn_up_weight, F, E));
+        TRY(up_q(&b.down, s.ffn_down_weight, E, F));
+        TRY(m->arena.alloc_n(&m->k[l], (size_t)C.ctx * KD));
+        TRY(m->arena.alloc_n(&m->v[l], (size_t)C.ctx * KD));
+        cudaMemsetAsync(m->k[l], 0, (size_t)C.ctx * KD * sizeof(float), st);
+        cudaMemsetAsync(m->v[l], 0, (size_t)C.ctx * KD * sizeof(float), st);
+    }
+    {
+        std::vector<float> hf(D / 2);
+        zq_rope_freqs_host(D, C.rope_base, hf.data());
+        TRY(m->arena.alloc_n(&m->freqs, D / 2));
+        cudaError_t e = cudaMemcpyAsync(m->freqs, hf.data(), hf.size() * sizeof(float),
+                                        cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);  // hf goes out of scope
+        if (e != cudaSuccess) {
+            delete m;
+            return cuda_fail(e);
+        }
+    }
+    TRY(m->arena.alloc_n(&m->x, E));
+    TRY(m->arena.alloc_n(&m->h, E));
+    TRY(m->arena.alloc_n(&m->q, QD));
+    TRY(m->arena.alloc_n(&m->kb, KD));
+    TRY(m->arena.alloc_n(&m->vb, KD));
+    TRY(m->arena.alloc_n(&m->att, QD));
+    TRY(m->arena.alloc_n(&m->proj, E));
+    TRY(m->arena.alloc_n(&m->gate, F));
+    TRY(m->arena.alloc_n(&m->up, F));
+    TRY(m->arena.alloc_n(&m->ffn, E));
+    TRY(m->arena.alloc_n(&m->logits, C.vocab));
+    TRY(m->arena.alloc_n(&m->xq, max_dim));
+    TRY(m->arena.alloc_n(&m->xscale, max_dim / 32));
+    TRY(m->arena.alloc_n(&m->xsum, max_dim / 32));
+    TRY(m->arena.alloc_n(&m->d_token, 1));
+    TRY(m->arena.alloc_n(&m->d_tok_i32, 1));
+    TRY(m->arena.alloc_n(&m->d_arg, 1));
+    TRY(m->arena.alloc_n(&m->d_record, C.ctx));
+#undef TRY
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        delete m;
+        return cuda_fail(e);
+    }
+    *out = m;
+    return ZQ_OK;
+}
+
+int zq_gemma3_free(zq_gemma3* m) {
+    delete m;
+    return ZQ_OK;
+}
+
+int zq_gemma3_reset_cache(zq_gemma3* m) {
+    if (!m) return ZQ_ERR_BAD_ARG;
+    m->seq_len = 0;
+    return ZQ_OK;
+}
+
+int zq_gemma3_seq_len(const zq_gemma3* m, uint32_t* seq_len) {
+    if (!m || !seq_len) return ZQ_ERR_BAD_ARG;
+    *seq_len = m->seq_len;
+    return ZQ_OK;
+}
+
+int zq_gemma3_prefill(zq_gemma3* m, const uint32_t* h_tokens, uint32_t n, zq_stream stream,
+                      const float** d_logits) {
+    if (!m || !h_tokens || !d_logits) return ZQ_ERR_BAD_ARG;
+    if (n == 0 || n > m->c.ctx) return ZQ_ERR_SEQUENCE;
+    cudaStream_t st = as_stream(stream);
+    m->seq_len = 0;
+    for (uint32_t t = 0; t < n; ++t) {
+        if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
+        set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, h_tokens[t]);
+        ZQ_LAUNCH_CHECK();
+        int rc = gemma3_step(m, t, t + 1 == n, st);
+        if (rc != ZQ_OK) return rc;
+    }
+    m->seq_len = n;
+    *d_logits = m->logits;
+    return ZQ_OK;
+}
+
+int zq_gemma3_decode_next(zq_gemma3* m, uint32_t token, zq_stream stream, const float** d_logits) {
+    if (!m || !d_logits) return ZQ_ERR_BAD_ARG;
+    if (m->seq_len >= m->c.ctx) return ZQ_ERR_SEQUENCE;
+    if (token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, token);
+    ZQ_LAUNCH_CHECK();
+    int rc = gemma3_step(m, m->seq_len, true, st);
+    if (rc != ZQ_OK) return rc;
+    m->seq_len += 1;
+    *d_logits = m->logits;
+    return ZQ_OK;
+}
+
+int zq_gemma3_decode_greedy(zq_gemma3* m, uint32_t first_token, uint32_t n_steps, zq_stream stream,
+                            uint32_t* h_tokens_out) {
+    if (!m || !h_tokens_out) return ZQ_ERR_BAD_ARG;
+    if (n_steps == 0) return ZQ_OK;
+    if ((uint64_t)m->seq_len + n_steps > m->c.ctx) return ZQ_ERR_SEQUENCE;
+    if (first_token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, first_token);
+    ZQ_LAUNCH_CHECK();
+    for (uint32_t s = 0; s < n_steps; ++s) {
+        int rc = gemma3_step(m, m->seq_len, true, st);
+        if (rc != ZQ_OK) return rc;
+        m->seq_len += 1;
+        if ((rc = zq_argmax(m->logits, m->c.vocab, m->d_arg, st))) return rc;
+        i32_to_token_kernel<<<1, 1, 0, st>>>(m->d_token, m->d_arg, m->d_record + s);
+        ZQ_LAUNCH_CHECK();
+    }
+    ZQ_CUDA(cudaMemcpyAsync(h_tokens_out, m->d_record, n_steps * sizeof(uint32_t),
+                            cudaMemcpyDeviceToHost, st));
+    ZQ_CUDA(cudaStreamSynchronize(st));
+    return ZQ_OK;
+}
+
+}  // extern "C"

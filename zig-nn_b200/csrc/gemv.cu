@@ -1,0 +1,654 @@
+// Decode GEMV kernels: quantised weight rows streamed from HBM with 128-bit loads, dequantised
+// in registers, reduced with warp shuffles. Two activation treatments:
+//   f32  — f32 activations times weights dequantised on the fly (zig-nn src/gguf/dequant.zig:133-309)
+//   q8   — activations quantised to int8 blocks, exact int32 dots, block terms summed in block
+//          order (src/gguf/simd_dot.zig:25-152, src/gguf/thread_pool.zig:96-181): bit-identical
+//          to that CPU path.
+#include "zq_internal.h"
+
+namespace zq {
+namespace {
+
+constexpr int kThreads = 128;  // 4 warps per CTA
+constexpr int kWarps = kThreads / 32;
+constexpr int XPAD = 36;   // floats per activation block in shared memory: 32 + 4 so that lanes
+                           // reading different blocks with 128-bit loads hit different banks
+constexpr int QPAD = 48;   // bytes per int8 activation block in shared memory (32 + 16)
+
+// ---- packed f32x2 arithmetic (sm_100) --------------------------------------------------
+
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "mov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
+// A 4-bit field sitting at bit p (p <= 19) of `q`, OR-ed under the exponent of 2^(23-p), reads
+// as the float 2^(23-p) + n; subtracting 2^(23-p) + off leaves n - off exactly.
+template <int P>
+__device__ __forceinline__ float nib_as_float(uint32_t q) {
+    return __uint_as_float((q & (0xFu << P)) | ((150u - P) << 23));
+}
+template <int P>
+__device__ __forceinline__ constexpr float nib_bias(float off) {
+    return -((float)(1u << (23 - P)) + off);
+}
+
+// Dot of the eight 4-bit weights of one 32-bit quant word with their activations.
+// Word w of a block holds elements 4w..4w+3 (low nibbles) and 4w+16..4w+19 (high nibbles).
+// OFF = 8 for q4_0 (n - 8), 0 for q4_1 (n).
+template <int OFF>
+__device__ __forceinline__ void q4_word_dot(uint32_t q, float4 xlo, float4 xhi, float2& acc) {
+    const uint32_t s = q >> 12;
+    float2 a01 = make_float2(nib_as_float<0>(q), nib_as_float<8>(q));
+    float2 a23 = make_float2(nib_as_float<16>(q), nib_as_float<12>(s));
+    float2 b01 = make_float2(nib_as_float<4>(q), nib_as_float<12>(q));
+    float2 b23 = make_float2(nib_as_float<8>(s), nib_as_float<16>(s));
+    a01 = fadd2(a01, make_float2(nib_bias<0>(OFF), nib_bias<8>(OFF)));
+    a23 = fadd2(a23, make_float2(nib_bias<16>(OFF), nib_bias<12>(OFF)));
+    b01 = fadd2(b01, make_float2(nib_bias<4>(OFF), nib_bias<12>(OFF)));
+    b23 = fadd2(b23, make_float2(nib_bias<8>(OFF), nib_bias<16>(OFF)));
+    acc = ffma2(a01, make_float2(xlo.x, xlo.y), acc);
+    acc = ffma2(a23, make_float2(xlo.z, xlo.w), acc);
+    acc = ffma2(b01, make_float2(xhi.x, xhi.y), acc);
+    acc = ffma2(b23, make_float2(xhi.z, xhi.w), acc);
+}
+
+// Dot of the four int8 weights of one quant word with x[0..3]. Each byte, flipped to unsigned,
+// is dropped under the exponent of 2^23: the float reads 2^23 + (b + 128).
+__device__ __forceinline__ void q8_word_dot(uint32_t q, float4 x, float2& acc) {
+    const uint32_t u = q ^ 0x80808080u;
+    float2 a01 = make_float2(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440)),
+                             __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7441)));
+    float2 a23 = make_float2(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7442)),
+                             __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)));
+    const float2 bias = make_float2(-8388736.0f, -8388736.0f);
+    a01 = fadd2(a01, bias);
+    a23 = fadd2(a23, bias);
+    acc = ffma2(a01, make_float2(x.x, x.y), acc);
+    acc = ffma2(a23, make_float2(x.z, x.w), acc);
+}
+
+__device__ __forceinline__ float gelu_tanh(float v) {
+    // 0.5*v*(1+tanh(0.7978845608*(v+0.044715*v^3))) — src/models/gpt2.zig:690-697
+    const float inner = 0.7978845608f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+struct EpilogueArgs {
+    const float* bias;
+    const float* mul;
+    const float* residual;
+    int gelu;
+};
+
+__device__ __forceinline__ float apply_epilogue(float v, const EpilogueArgs& ep, size_t j) {
+    if (ep.bias) v += ep.bias[j];
+    if (ep.gelu) v = gelu_tanh(v);
+    if (ep.mul) v *= ep.mul[j];
+    if (ep.residual) v += ep.residual[j];
+    return v;
+}
+
+// ---- f32-activation GEMV, one activation row ---------------------------------------------
+//
+// A warp owns 32/G row groups of R consecutive rows; the G lanes of a group walk the blocks of
+// those rows (lane g takes blocks g, g+G, ...). Per step a lane issues R independent 128-bit
+// quant loads (2R for q8_0) and reuses one block of activations, read from shared memory, for
+// all R rows.
+template <int TYPE, int G, int R>
+__global__ void __launch_bounds__(kThreads)
+gemv_f32_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
+                const float* __restrict__ x, float* __restrict__ y, uint32_t N, uint32_t nb,
+                EpilogueArgs ep) {
+    extern __shared__ __align__(16) float smem[];
+    float* xs = smem;               // nb * XPAD
+    float* xsum = smem + (size_t)nb * XPAD;  // nb (q4_1 only)
+    const int tid = threadIdx.x;
+    for (uint32_t i = tid; i < nb * 32; i += kThreads) xs[(i >> 5) * XPAD + (i & 31)] = x[i];
+    __syncthreads();
+    if (TYPE == ZQ_TYPE_Q4_1) {
+        for (uint32_t b = tid; b < nb; b += kThreads) {
+            float s = 0.0f;
+            for (int j = 0; j < 32; ++j) s += xs[b * XPAD + j];
+            xsum[b] = s;
+        }
+        __syncthreads();
+    }
+
+    constexpr int GROUPS = 32 / G;
+    constexpr int ROWS_W = GROUPS * R;
+    constexpr int QB = TYPE == ZQ_TYPE_Q8_0 ? 32 : 16;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int g = lane % G, grp = lane / G;
+    const uint32_t rows_per_cta = kWarps * ROWS_W;
+
+    for (uint64_t tile = blockIdx.x; tile * rows_per_cta < N; tile += gridDim.x) {
+        const uint32_t row0 = (uint32_t)(tile * rows_per_cta) + warp * ROWS_W + grp * R;
+        float sum[R];
+        const uint8_t* qrow[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            sum[r] = 0.0f;
+            const uint32_t row = min(row0 + r, N - 1);  // clamp: out-of-range rows are never stored
+            qrow[r] = qs + (size_t)row * nb * QB;
+        }
+        for (uint32_t b = g; b < nb; b += G) {
+            uint4 q[R][QB / 16];
+            float d[R], mn[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint4* p = reinterpret_cast<const uint4*>(qrow[r] + (size_t)b * QB);
+                q[r][0] = __ldg(p);
+                if (QB == 32) q[r][QB / 16 - 1] = __ldg(p + 1);
+                const uint32_t row = min(row0 + r, N - 1);
+                if (TYPE == ZQ_TYPE_Q4_1) {
+                    const __half2 dm = __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row * nb + b);
+                    d[r] = __low2float(dm);
+                    mn[r] = __high2float(dm);
+                } else {
+                    d[r] = __half2float(__ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * nb + b));
+                    mn[r] = 0.0f;
+                }
+            }
+            const float4* xb = reinterpret_cast<const float4*>(xs + b * XPAD);
+            float4 xv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xv[i] = xb[i];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float2 acc = make_float2(0.0f, 0.0f);
+                if (TYPE == ZQ_TYPE_Q8_0) {
+                    const uint32_t w[8] = {q[r][0].x, q[r][0].y, q[r][0].z, q[r][0].w,
+                                           q[r][QB / 16 - 1].x, q[r][QB / 16 - 1].y,
+                                           q[r][QB / 16 - 1].z, q[r][QB / 16 - 1].w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) q8_word_dot(w[i], xv[i], acc);
+                    sum[r] += (acc.x + acc.y) * d[r];
+                } else {
+                    const uint32_t w[4] = {q[r][0].x, q[r][0].y, q[r][0].z, q[r][0].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        q4_word_dot<TYPE == ZQ_TYPE_Q4_0 ? 8 : 0>(w[i], xv[i], xv[4 + i], acc);
+                    if (TYPE == ZQ_TYPE_Q4_0)
+                        sum[r] += (acc.x + acc.y) * d[r];
+                    else
+                        sum[r] += (acc.x + acc.y) * d[r] + xsum[b] * mn[r];
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int off = G / 2; off > 0; off >>= 1)
+                sum[r] += __shfl_xor_sync(0xFFFFFFFFu, sum[r], off);
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (row0 + r < N) y[row0 + r] = apply_epilogue(sum[r], ep, row0 + r);
+        }
+    }
+}
+
+// ---- Q8-activation GEMV, one activation row (exact) ----------------------------------------
+//
+// Same walk as above with int8 activations and dp4a. Each step produces, per row, the G block
+// terms  t_b = (d*s)*float(idot) [+ (m*s)*float(qsum)]  of G consecutive blocks; they go through
+// a small shared-memory tile and one lane per row adds them to the row's running sum in block
+// order, which is the order (and the rounding) of the CPU loop.
+template <int TYPE, int G, int R>
+__global__ void __launch_bounds__(kThreads)
+gemv_q8_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
+               const int8_t* __restrict__ xq, const float* __restrict__ xscale,
+               const int32_t* __restrict__ xqsum, float* __restrict__ y, uint32_t N, uint32_t nb,
+               EpilogueArgs ep) {
+    constexpr int GROUPS = 32 / G;
+    constexpr int ROWS_W = GROUPS * R;
+    static_assert(ROWS_W <= 32, "one lane per row in the ordered-sum phase");
+    constexpr int QB = TYPE == ZQ_TYPE_Q8_0 ? 32 : 16;
+    constexpr int TP = G + 1;  // padded pitch of the term tile
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned char* xq_s = smem_raw;                                   // nb * QPAD
+    float* xs_s = reinterpret_cast<float*>(smem_raw + (size_t)nb * QPAD);  // nb
+    int32_t* xsum_s = reinterpret_cast<int32_t*>(xs_s + nb);          // nb
+    float* terms = reinterpret_cast<float*>(xsum_s + nb);             // kWarps * ROWS_W * TP
+
+    const int tid = threadIdx.x;
+    for (uint32_t i = tid; i < nb * 8; i += kThreads)  // 4 bytes per step
+        *reinterpret_cast<uint32_t*>(xq_s + (i >> 3) * QPAD + (i & 7) * 4) =
+            reinterpret_cast<const uint32_t*>(xq)[i];
+    for (uint32_t b = tid; b < nb; b += kThreads) {
+        xs_s[b] = xscale[b];
+        xsum_s[b] = xqsum[b];
+    }
+    __syncthreads();
+
+    const int lane = tid & 31, warp = tid >> 5;
+    const int g = lane % G, grp = lane / G;
+    float* my_terms = terms + warp * ROWS_W * TP;
+    const uint32_t rows_per_cta = kWarps * ROWS_W;
+    const uint32_t steps = (nb + G - 1) / G;
+
+    for (uint64_t tile = blockIdx.x; tile * rows_per_cta < N; tile += gridDim.x) {
+        const uint32_t wrow0 = (uint32_t)(tile * rows_per_cta) + warp * ROWS_W;
+        const uint32_t row0 = wrow0 + grp * R;
+        float run = 0.0f;  // lane l: running sum of row wrow0 + l
+        for (uint32_t st = 0; st < steps; ++st) {
+            const uint32_t b = st * G + g;
+            if (b < nb) {
+                const uint4* xp = reinterpret_cast<const uint4*>(xq_s + b * QPAD);
+                const uint4 xa = xp[0], xb4 = xp[1];
+                const int xw[8] = {(int)xa.x, (int)xa.y, (int)xa.z, (int)xa.w,
+                                   (int)xb4.x, (int)xb4.y, (int)xb4.z, (int)xb4.w};
+                const float s = xs_s[b];
+                const int qsum = xsum_s[b];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const uint32_t row = min(row0 + r, N - 1);
+                    const uint4* p =
+                        reinterpret_cast<const uint4*>(qs + ((size_t)row * nb + b) * QB);
+                    float term;
+                    if (TYPE == ZQ_TYPE_Q8_0) {
+                        const uint4 q0 = __ldg(p), q1 = __ldg(p + 1);
+                        const int w[8] = {(int)q0.x, (int)q0.y, (int)q0.z, (int)q0.w,
+                                          (int)q1.x, (int)q1.y, (int)q1.z, (int)q1.w};
+                        int idot = 0;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) idot = __dp4a(w[i], xw[i], idot);
+                        const float d = __half2float(
+                            __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * nb + b));
+                        term = __fmul_rn(__fmul_rn(d, s), (float)idot);
+                    } else {
+                        const uint4 q0 = __ldg(p);
+                        const uint32_t w[4] = {q0.x, q0.y, q0.z, q0.w};
+                        int idot = 0;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            idot = __dp4a((int)(w[i] & 0x0F0F0F0Fu), xw[i], idot);
+                            idot = __dp4a((int)((w[i] >> 4) & 0x0F0F0F0Fu), xw[4 + i], idot);
+                        }
+                        if (TYPE == ZQ_TYPE_Q4_0) {
+                            idot -= 8 * qsum;  // sum((n-8)*q) = sum(n*q) - 8*sum(q), exact
+                            const float d = __half2float(
+                                __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * nb + b));
+                            term = __fmul_rn(__fmul_rn(d, s), (float)idot);
+                        } else {
+                            const __half2 dm =
+                                __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row * nb + b);
+                            const float t1 = __fmul_rn(__fmul_rn(__low2float(dm), s), (float)idot);
+                            const float t2 = __fmul_rn(__fmul_rn(__high2float(dm), s), (float)qsum);
+                            term = __fadd_rn(t1, t2);
+                        }
+                    }
+                    my_terms[(grp * R + r) * TP + g] = term;
+                }
+            }
+            __syncwarp();
+            if (lane < ROWS_W) {
+                const uint32_t nvalid = min((uint32_t)G, nb - st * G);
+#pragma unroll
+                for (int j = 0; j < G; ++j)
+                    if ((uint32_t)j < nvalid) run = __fadd_rn(run, my_terms[lane * TP + j]);
+            }
+            __syncwarp();
+        }
+        if (lane < ROWS_W && wrow0 + lane < N)
+            y[wrow0 + lane] = apply_epilogue(run, ep, wrow0 + lane);
+    }
+}
+
+// ---- quantize_row_q8 (src/gguf/simd_dot.zig:25-64): one warp per 32-element block ---------------
+
+__global__ void quantize_q8_kernel(const float* __restrict__ x, int8_t* __restrict__ q,
+                                   float* __restrict__ scale, int32_t* __restrict__ sum,
+                                   size_t n_blocks) {
+    const size_t blk = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (blk >= n_blocks) return;
+    const float v = x[blk * 32 + lane];
+    float amax = fabsf(v);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, s);
+    float r = roundf(__fmul_rn(v, inv));  // half away from zero, as std.math.round
+    r = fminf(127.0f, fmaxf(-127.0f, r));
+    const int qi = (int)r;
+    int acc = qi;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+    q[blk * 32 + lane] = (int8_t)qi;
+    if (lane == 0) {
+        scale[blk] = s;
+        sum[blk] = acc;
+    }
+}
+
+// ---- f32 weight times one row (GPT-2 vocabulary head), one warp per output row -------------
+
+__global__ void __launch_bounds__(256)
+matvec_f32_kernel(const float* __restrict__ w, const float* __restrict__ x, float* __restrict__ y,
+                  uint32_t N, uint32_t K) {
+    extern __shared__ __align__(16) float xs[];
+    for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) xs[i] = x[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const uint32_t warps = blockDim.x >> 5;
+    const bool vec = (K % 4 == 0);
+    for (uint64_t row = (uint64_t)blockIdx.x * warps + (threadIdx.x >> 5); row < N;
+         row += (uint64_t)gridDim.x * warps) {
+        const float* wr = w + row * K;
+        float acc = 0.0f;
+        if (vec) {
+            const float4* w4 = reinterpret_cast<const float4*>(wr);
+            const float4* x4 = reinterpret_cast<const float4*>(xs);
+            for (uint32_t i = lane; i < K / 4; i += 32) {
+                const float4 a = __ldg(w4 + i), b = x4[i];
+                acc = fmaf(a.x, b.x, acc);
+                acc = fmaf(a.y, b.y, acc);
+                acc = fmaf(a.z, b.z, acc);
+                acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+            for (uint32_t i = lane; i < K; i += 32) acc = fmaf(__ldg(wr + i), xs[i], acc);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+        if (lane == 0) y[row] = acc;
+    }
+}
+
+// ---- argmax, first maximum wins (src/models/gpt2.zig:980-990) --------------------------------
+
+__device__ __forceinline__ void argmax_merge(float& v, uint32_t& i, float ov, uint32_t oi) {
+    if (ov > v || (ov == v && oi < i)) {
+        v = ov;
+        i = oi;
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, uint32_t n, int32_t* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ uint32_t si[32];
+    float v = -INFINITY;
+    uint32_t idx = 0xFFFFFFFFu;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float c = logits[i];
+        // a NaN never compares greater, as in the CPU loop; index 0 is the fallback
+        if (c > v || (c == v && i < idx)) {
+            v = c;
+            idx = i;
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, v, off);
+        const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, idx, off);
+        argmax_merge(v, idx, ov, oi);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        sv[warp] = v;
+        si[warp] = idx;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        v = lane < nw ? sv[lane] : -INFINITY;
+        idx = lane < nw ? si[lane] : 0xFFFFFFFFu;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, v, off);
+            const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, idx, off);
+            argmax_merge(v, idx, ov, oi);
+        }
+        if (lane == 0) out[0] = (idx == 0xFFFFFFFFu) ? 0 : (int32_t)idx;
+    }
+}
+
+// ---- launch helpers ----------------------------------------------------------------------
+
+// Lanes per row group: the power of two (4..32) that wastes the fewest lane-steps, larger first.
+int pick_group(uint32_t nb, int g_max) {
+    int best = 4;
+    double best_eff = -1.0;
+    for (int g = g_max; g >= 4; g >>= 1) {
+        const uint32_t steps = (nb + g - 1) / g;
+        const double eff = (double)nb / ((double)steps * g);
+        if (eff > best_eff + 1e-9) {
+            best_eff = eff;
+            best = g;
+        }
+    }
+    return best;
+}
+
+EpilogueArgs make_ep(const zq_epilogue* ep, size_t row_offset_elems) {
+    EpilogueArgs a{nullptr, nullptr, nullptr, 0};
+    if (ep) {
+        a.bias = ep->d_bias;
+        a.gelu = ep->gelu;
+        a.mul = ep->d_mul ? ep->d_mul + row_offset_elems : nullptr;
+        a.residual = ep->d_residual ? ep->d_residual + row_offset_elems : nullptr;
+    }
+    return a;
+}
+
+template <typename K>
+int set_smem(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024) {
+        if (bytes > 227 * 1024) return ZQ_ERR_LIMIT;
+        ZQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    }
+    return ZQ_OK;
+}
+
+template <int TYPE, int G, int R>
+int launch_f32_one(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
+    const size_t smem = ((size_t)w->nb * XPAD + w->nb) * sizeof(float);
+    int rc = set_smem(gemv_f32_kernel<TYPE, G, R>, smem);
+    if (rc != ZQ_OK) return rc;
+    const uint32_t rows_per_cta = kWarps * (32 / G) * R;
+    const uint64_t tiles = ((uint64_t)w->out_dim + rows_per_cta - 1) / rows_per_cta;
+    const uint64_t cap = (uint64_t)sm_count() * 8;
+    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+    gemv_f32_kernel<TYPE, G, R><<<grid, kThreads, smem, st>>>(w->qs, w->sc, x, y, w->out_dim, w->nb, ep);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+template <int TYPE, int G>
+int launch_f32_r(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
+    // Fewer rows per lane when there are not enough rows to give every SM a few warps.
+    const uint64_t warp_tiles4 = (uint64_t)w->out_dim / ((32 / G) * 4);
+    if (warp_tiles4 >= (uint64_t)sm_count() * kWarps * 2) return launch_f32_one<TYPE, G, 4>(w, x, y, ep, st);
+    const uint64_t warp_tiles2 = (uint64_t)w->out_dim / ((32 / G) * 2);
+    if (warp_tiles2 >= (uint64_t)sm_count() * kWarps) return launch_f32_one<TYPE, G, 2>(w, x, y, ep, st);
+    return launch_f32_one<TYPE, G, 1>(w, x, y, ep, st);
+}
+
+template <int TYPE>
+int launch_f32_g(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
+    switch (pick_group(w->nb, 32)) {
+        case 32: return launch_f32_r<TYPE, 32>(w, x, y, ep, st);
+        case 16: return launch_f32_r<TYPE, 16>(w, x, y, ep, st);
+        case 8: return launch_f32_r<TYPE, 8>(w, x, y, ep, st);
+        default: return launch_f32_r<TYPE, 4>(w, x, y, ep, st);
+    }
+}
+
+template <int TYPE, int G, int R>
+int launch_q8_one(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum,
+                  float* y, EpilogueArgs ep, cudaStream_t st) {
+    const size_t smem = (size_t)w->nb * QPAD + (size_t)w->nb * 8 +
+                        (size_t)kWarps * (32 / G) * R * (G + 1) * sizeof(float);
+    int rc = set_smem(gemv_q8_kernel<TYPE, G, R>, smem);
+    if (rc != ZQ_OK) return rc;
+    const uint32_t rows_per_cta = kWarps * (32 / G) * R;
+    const uint64_t tiles = ((uint64_t)w->out_dim + rows_per_cta - 1) / rows_per_cta;
+    const uint64_t cap = (uint64_t)sm_count() * 8;
+    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+    gemv_q8_kernel<TYPE, G, R><<<grid, kThreads, smem, st>>>(w->qs, w->sc, xq, xs, xsum, y,
+                                                             w->out_dim, w->nb, ep);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+template <int TYPE>
+int launch_q8_g(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum, float* y,
+                EpilogueArgs ep, cudaStream_t st) {
+    // Small groups keep the ordered-sum phase cheap (its cost grows with G).
+    const int g = pick_group(w->nb, 8);
+    const uint64_t warp_tiles = (uint64_t)w->out_dim / 32;
+    const bool big = warp_tiles >= (uint64_t)sm_count() * kWarps * 2;
+    if (g == 8) {
+        if (big) return launch_q8_one<TYPE, 8, 8>(w, xq, xs, xsum, y, ep, st);
+        return launch_q8_one<TYPE, 8, 2>(w, xq, xs, xsum, y, ep, st);
+    }
+    if (big) return launch_q8_one<TYPE, 4, 4>(w, xq, xs, xsum, y, ep, st);
+    return launch_q8_one<TYPE, 4, 1>(w, xq, xs, xsum, y, ep, st);
+}
+
+}  // namespace
+
+int launch_gemv_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
+                    const zq_epilogue* ep, cudaStream_t st) {
+    for (uint32_t m = 0; m < m_rows; ++m) {
+        const size_t xo = (size_t)m * w->in_dim, yo = (size_t)m * w->out_dim;
+        EpilogueArgs a = make_ep(ep, yo);
+        int rc;
+        switch (w->type) {
+            case ZQ_TYPE_Q4_0: rc = launch_f32_g<ZQ_TYPE_Q4_0>(w, x + xo, y + yo, a, st); break;
+            case ZQ_TYPE_Q4_1: rc = launch_f32_g<ZQ_TYPE_Q4_1>(w, x + xo, y + yo, a, st); break;
+            case ZQ_TYPE_Q8_0: rc = launch_f32_g<ZQ_TYPE_Q8_0>(w, x + xo, y + yo, a, st); break;
+            default: return ZQ_ERR_UNSUPPORTED;
+        }
+        if (rc != ZQ_OK) return rc;
+    }
+    return ZQ_OK;
+}
+
+int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum,
+                   float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st) {
+    for (uint32_t m = 0; m < m_rows; ++m) {
+        const size_t yo = (size_t)m * w->out_dim, bo = (size_t)m * w->nb;
+        EpilogueArgs a = make_ep(ep, yo);
+        const int8_t* q = xq + (size_t)m * w->in_dim;
+        int rc;
+        switch (w->type) {
+            case ZQ_TYPE_Q4_0: rc = launch_q8_g<ZQ_TYPE_Q4_0>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
+            case ZQ_TYPE_Q4_1: rc = launch_q8_g<ZQ_TYPE_Q4_1>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
+            case ZQ_TYPE_Q8_0: rc = launch_q8_g<ZQ_TYPE_Q8_0>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
+            default: return ZQ_ERR_UNSUPPORTED;
+        }
+        if (rc != ZQ_OK) return rc;
+    }
+    return ZQ_OK;
+}
+
+int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, int8_t* q,
+                            float* scale, int32_t* sum, cudaStream_t st) {
+    const size_t n_blocks = (size_t)m_rows * (in_dim / 32);
+    if (n_blocks == 0) return ZQ_OK;
+    const unsigned threads = 256;
+    const size_t grid = (n_blocks * 32 + threads - 1) / threads;
+    if (grid > 0x7FFFFFFFull) return ZQ_ERR_LIMIT;
+    quantize_q8_kernel<<<(unsigned)grid, threads, 0, st>>>(x, q, scale, sum, n_blocks);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+}  // namespace zq
+
+using namespace zq;
+
+extern "C" {
+
+size_t zq_matmul_workspace_bytes(const zq_weight* w, uint32_t m_rows, int act_mode) {
+    if (!w) return 0;
+    if (act_mode == ZQ_ACT_Q8) {
+        // int8 activations, then per-block f32 scales and int32 sums, each 256-byte aligned
+        const size_t q = ((size_t)m_rows * w->in_dim + 255) & ~(size_t)255;
+        const size_t s = ((size_t)m_rows * w->nb * 4 + 255) & ~(size_t)255;
+        return q + 2 * s;
+    }
+    return 0;
+}
+
+int zq_quantize_rows_q8(const float* d_x, uint32_t m_rows, uint32_t in_dim, int8_t* d_q,
+                        float* d_scale, int32_t* d_sum, zq_stream stream) {
+    if (!d_x || !d_q || !d_scale || !d_sum || in_dim == 0 || in_dim % 32) return ZQ_ERR_BAD_ARG;
+    return launch_quantize_rows_q8(d_x, m_rows, in_dim, d_q, d_scale, d_sum, as_stream(stream));
+}
+
+int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows, int act_mode,
+              const zq_epilogue* epilogue, void* d_workspace, size_t workspace_bytes,
+              zq_stream stream) {
+    if (!w || !d_x || !d_y) return ZQ_ERR_BAD_ARG;
+    if (m_rows == 0) return ZQ_OK;
+    cudaStream_t st = as_stream(stream);
+    if (act_mode == ZQ_ACT_F32) return launch_gemv_f32(w, d_x, d_y, m_rows, epilogue, st);
+    if (act_mode == ZQ_ACT_Q8) {
+        if (w->in_dim > 16384) return ZQ_ERR_LIMIT;
+        const size_t need = zq_matmul_workspace_bytes(w, m_rows, act_mode);
+        if (!d_workspace || workspace_bytes < need || ((uintptr_t)d_workspace & 255)) return ZQ_ERR_BAD_ARG;
+        const size_t qbytes = ((size_t)m_rows * w->in_dim + 255) & ~(size_t)255;
+        const size_t sbytes = ((size_t)m_rows * w->nb * 4 + 255) & ~(size_t)255;
+        int8_t* q = static_cast<int8_t*>(d_workspace);
+        float* sc = reinterpret_cast<float*>(static_cast<char*>(d_workspace) + qbytes);
+        int32_t* sm = reinterpret_cast<int32_t*>(static_cast<char*>(d_workspace) + qbytes + sbytes);
+        int rc = launch_quantize_rows_q8(d_x, m_rows, w->in_dim, q, sc, sm, st);
+        if (rc != ZQ_OK) return rc;
+        return launch_gemv_q8(w, q, sc, sm, d_y, m_rows, epilogue, st);
+    }
+    return ZQ_ERR_BAD_ARG;
+}
+
+int zq_matvec_f32(const float* d_w, const float* d_x, float* d_y, uint32_t out_dim, uint32_t in_dim,
+                  zq_stream stream) {
+    if (!d_w || !d_x || !d_y || out_dim == 0 || in_dim == 0) return ZQ_ERR_BAD_ARG;
+    const size_t smem = (size_t)in_dim * sizeof(float);
+    int rc = set_smem(matvec_f32_kernel, smem);
+    if (rc != ZQ_OK) return rc;
+    const uint64_t tiles = ((uint64_t)out_dim + 7) / 8;
+    const uint64_t cap = (uint64_t)sm_count() * 8;
+    matvec_f32_kernel<<<(unsigned)(tiles < cap ? tiles : cap), 256, smem, as_stream(stream)>>>(
+        d_w, d_x, d_y, out_dim, in_dim);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+int zq_argmax(const float* d_logits, uint32_t n, int32_t* d_index, zq_stream stream) {
+    if (!d_logits || !d_index || n == 0) return ZQ_ERR_BAD_ARG;
+    argmax_kernel<<<1, 1024, 0, as_stream(stream)>>>(d_logits, n, d_index);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,287 @@
+// Weight handles: upload + re-layout of GGUF quant blocks, bit-exact dequantisation.
+#include <new>
+
+#include "zq_internal.h"
+
+namespace zq {
+
+thread_local int g_last_cuda_error = 0;
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+namespace {
+
+__host__ __device__ inline uint32_t raw_bpb(int type) {
+    return type == ZQ_TYPE_Q4_0 ? 18u : type == ZQ_TYPE_Q4_1 ? 20u : 34u;
+}
+
+// One thread per block: split the GGUF block into its scale word(s) and its quant bytes.
+__global__ void repack_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ qs,
+                              uint8_t* __restrict__ sc, int type, size_t n_blocks) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const uint32_t bpb = raw_bpb(type);
+    const uint32_t hdr = type == ZQ_TYPE_Q4_1 ? 4u : 2u;
+    const uint32_t qb = bpb - hdr;
+    const uint8_t* src = raw + b * bpb;
+    for (uint32_t i = 0; i < hdr; ++i) sc[b * hdr + i] = src[i];
+    for (uint32_t i = 0; i < qb; ++i) qs[b * qb + i] = src[hdr + i];
+}
+
+__global__ void unpack_kernel(uint8_t* __restrict__ raw, const uint8_t* __restrict__ qs,
+                              const uint8_t* __restrict__ sc, int type, size_t n_blocks) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const uint32_t bpb = raw_bpb(type);
+    const uint32_t hdr = type == ZQ_TYPE_Q4_1 ? 4u : 2u;
+    const uint32_t qb = bpb - hdr;
+    uint8_t* dst = raw + b * bpb;
+    for (uint32_t i = 0; i < hdr; ++i) dst[i] = sc[b * hdr + i];
+    for (uint32_t i = 0; i < qb; ++i) dst[hdr + i] = qs[b * qb + i];
+}
+
+// One thread per element. `row_map` (optional) selects source rows; `scale_mode` multiplies the
+// dequantised value by `scale` as a second, separately rounded multiply.
+template <int TYPE>
+__global__ void dequant_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
+                               float* __restrict__ out, uint32_t nb, size_t n_rows,
+                               const int32_t* __restrict__ row_map, int scale_mode, float scale) {
+    const size_t K = (size_t)nb * 32;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_rows * K) return;
+    const size_t r = idx / K;
+    const uint32_t k = (uint32_t)(idx - r * K);
+    const size_t src_row = row_map ? (size_t)row_map[r] : r;
+    const size_t blk = src_row * nb + (k >> 5);
+    const uint32_t j = k & 31;
+    float v;
+    if (TYPE == ZQ_TYPE_Q8_0) {
+        const float d = __half2float(reinterpret_cast<const __half*>(sc)[blk]);
+        const int8_t q = reinterpret_cast<const int8_t*>(qs)[blk * 32 + j];
+        v = __fmul_rn((float)q, d);
+    } else {
+        const uint8_t byte = qs[blk * 16 + (j & 15)];
+        const int nib = (j < 16) ? (byte & 0x0F) : (byte >> 4);
+        if (TYPE == ZQ_TYPE_Q4_0) {
+            const float d = __half2float(reinterpret_cast<const __half*>(sc)[blk]);
+            v = __fmul_rn((float)(nib - 8), d);
+        } else {
+            const __half2 dm = reinterpret_cast<const __half2*>(sc)[blk];
+            // nibble*d then +m: two roundings, never contracted into an FMA
+            v = __fadd_rn(__fmul_rn((float)nib, __low2float(dm)), __high2float(dm));
+        }
+    }
+    if (scale_mode) v = __fmul_rn(v, scale);
+    out[idx] = v;
+}
+
+int make_weight(int type, uint32_t out_dim, uint32_t in_dim, zq_weight** out) {
+    if (!out) return ZQ_ERR_BAD_ARG;
+    *out = nullptr;
+    if (type != ZQ_TYPE_Q4_0 && type != ZQ_TYPE_Q4_1 && type != ZQ_TYPE_Q8_0)
+        return ZQ_ERR_UNSUPPORTED;
+    if (out_dim == 0 || in_dim == 0 || (in_dim % 32) != 0) return ZQ_ERR_BAD_ARG;
+    zq_weight* w = new (std::nothrow) zq_weight;
+    if (!w) return ZQ_ERR_NO_MEM;
+    w->type = type;
+    w->out_dim = out_dim;
+    w->in_dim = in_dim;
+    w->nb = in_dim / 32;
+    w->qb = type == ZQ_TYPE_Q8_0 ? 32 : 16;
+    const size_t n_blocks = (size_t)out_dim * w->nb;
+    const size_t qs_bytes = n_blocks * w->qb;
+    const size_t qs_pad = (qs_bytes + 255) & ~(size_t)255;
+    const size_t sc_bytes = n_blocks * (type == ZQ_TYPE_Q4_1 ? 4 : 2);
+    w->bytes = qs_pad + ((sc_bytes + 255) & ~(size_t)255);
+    cudaError_t e = cudaMalloc(&w->base, w->bytes);
+    if (e != cudaSuccess) {
+        delete w;
+        g_last_cuda_error = (int)e;
+        return e == cudaErrorMemoryAllocation ? ZQ_ERR_NO_MEM : ZQ_ERR_CUDA;
+    }
+    w->qs = static_cast<uint8_t*>(w->base);
+    w->sc = w->qs + qs_pad;
+    *out = w;
+    return ZQ_OK;
+}
+
+}  // namespace
+}  // namespace zq
+
+using namespace zq;
+
+extern "C" {
+
+const char* zq_status_string(int s) {
+    switch (s) {
+        case ZQ_OK: return "ok";
+        case ZQ_ERR_BAD_ARG: return "bad argument";
+        case ZQ_ERR_UNSUPPORTED: return "unsupported quant type";
+        case ZQ_ERR_CUDA: return "CUDA error";
+        case ZQ_ERR_NO_MEM: return "out of memory";
+        case ZQ_ERR_LIMIT: return "size limit exceeded";
+        case ZQ_ERR_SEQUENCE: return "empty sequence, sequence too long or context full";
+        case ZQ_ERR_TIMEOUT: return "device-side wait timed out";
+        case ZQ_ERR_PEER: return "peer set-up failed";
+        default: return "unknown status";
+    }
+}
+
+int zq_last_cuda_error(void) { return g_last_cuda_error; }
+int zq_abi_version(void) { return 1; }
+
+size_t zq_block_size(int t) {
+    switch (t) {
+        case ZQ_TYPE_F32:
+        case ZQ_TYPE_F16: return 1;
+        case ZQ_TYPE_Q4_0:
+        case ZQ_TYPE_Q4_1:
+        case ZQ_TYPE_Q8_0: return 32;
+        default: return 0;
+    }
+}
+
+size_t zq_bytes_per_block(int t) {
+    switch (t) {
+        case ZQ_TYPE_F32: return 4;
+        case ZQ_TYPE_F16: return 2;
+        case ZQ_TYPE_Q4_0: return 18;
+        case ZQ_TYPE_Q4_1: return 20;
+        case ZQ_TYPE_Q8_0: return 34;
+        default: return 0;
+    }
+}
+
+size_t zq_tensor_bytes(int t, size_t n) {
+    const size_t bs = zq_block_size(t);
+    return bs ? (n / bs) * zq_bytes_per_block(t) : 0;
+}
+
+int zq_weight_from_device(const void* d_raw, int type, uint32_t out_dim, uint32_t in_dim,
+                          zq_stream stream, zq_weight** out) {
+    if (!d_raw) return ZQ_ERR_BAD_ARG;
+    int rc = make_weight(type, out_dim, in_dim, out);
+    if (rc != ZQ_OK) return rc;
+    zq_weight* w = *out;
+    const size_t n_blocks = (size_t)out_dim * w->nb;
+    const unsigned threads = 256;
+    const unsigned blocks = (unsigned)((n_blocks + threads - 1) / threads);
+    repack_kernel<<<blocks, threads, 0, as_stream(stream)>>>(
+        static_cast<const uint8_t*>(d_raw), w->qs, static_cast<uint8_t*>(w->sc), type, n_blocks);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        zq_weight_free(w);
+        *out = nullptr;
+        return cuda_fail(e);
+    }
+    return ZQ_OK;
+}
+
+int zq_weight_upload(const void* h_raw, int type, uint32_t out_dim, uint32_t in_dim,
+                     zq_stream stream, zq_weight** out) {
+    if (!h_raw || !out) return ZQ_ERR_BAD_ARG;
+    *out = nullptr;
+    if (!is_quant(type)) return ZQ_ERR_UNSUPPORTED;
+    if (out_dim == 0 || in_dim == 0 || (in_dim % 32) != 0) return ZQ_ERR_BAD_ARG;
+    const size_t raw_bytes = zq_tensor_bytes(type, (size_t)out_dim * in_dim);
+    void* staging = nullptr;
+    cudaError_t e = cudaMalloc(&staging, raw_bytes);
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return e == cudaErrorMemoryAllocation ? ZQ_ERR_NO_MEM : ZQ_ERR_CUDA;
+    }
+    cudaStream_t st = as_stream(stream);
+    int rc = ZQ_OK;
+    e = cudaMemcpyAsync(staging, h_raw, raw_bytes, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) rc = cuda_fail(e);
+    if (rc == ZQ_OK) rc = zq_weight_from_device(staging, type, out_dim, in_dim, stream, out);
+    e = cudaStreamSynchronize(st);
+    if (rc == ZQ_OK && e != cudaSuccess) rc = cuda_fail(e);
+    cudaFree(staging);
+    if (rc != ZQ_OK && *out) {
+        zq_weight_free(*out);
+        *out = nullptr;
+    }
+    return rc;
+}
+
+int zq_weight_free(zq_weight* w) {
+    if (!w) return ZQ_OK;
+    cudaError_t e = cudaFree(w->base);
+    delete w;
+    if (e != cudaSuccess) return cuda_fail(e);
+    return ZQ_OK;
+}
+
+int zq_weight_info(const zq_weight* w, int* type, uint32_t* out_dim, uint32_t* in_dim) {
+    if (!w) return ZQ_ERR_BAD_ARG;
+    if (type) *type = w->type;
+    if (out_dim) *out_dim = w->out_dim;
+    if (in_dim) *in_dim = w->in_dim;
+    return ZQ_OK;
+}
+
+size_t zq_weight_device_bytes(const zq_weight* w) { return w ? w->bytes : 0; }
+
+int zq_weight_download_raw(const zq_weight* w, void* d_raw, zq_stream stream) {
+    if (!w || !d_raw) return ZQ_ERR_BAD_ARG;
+    const size_t n_blocks = (size_t)w->out_dim * w->nb;
+    const unsigned threads = 256;
+    const unsigned blocks = (unsigned)((n_blocks + threads - 1) / threads);
+    unpack_kernel<<<blocks, threads, 0, as_stream(stream)>>>(
+        static_cast<uint8_t*>(d_raw), w->qs, static_cast<const uint8_t*>(w->sc), w->type, n_blocks);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+static int dequant_launch(const zq_weight* w, float* d_out, size_t n_rows, const int32_t* row_map,
+                          int scale_mode, float scale, zq_stream stream) {
+    const size_t total = n_rows * (size_t)w->in_dim;
+    if (total == 0) return ZQ_OK;
+    const unsigned threads = 256;
+    const size_t blocks64 = (total + threads - 1) / threads;
+    if (blocks64 > 0x7FFFFFFFull) return ZQ_ERR_LIMIT;
+    const unsigned blocks = (unsigned)blocks64;
+    cudaStream_t st = as_stream(stream);
+    switch (w->type) {
+        case ZQ_TYPE_Q4_0:
+            dequant_kernel<ZQ_TYPE_Q4_0><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb,
+                                                                    n_rows, row_map, scale_mode, scale);
+            break;
+        case ZQ_TYPE_Q4_1:
+            dequant_kernel<ZQ_TYPE_Q4_1><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb,
+                                                                    n_rows, row_map, scale_mode, scale);
+            break;
+        case ZQ_TYPE_Q8_0:
+            dequant_kernel<ZQ_TYPE_Q8_0><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb,
+                                                                    n_rows, row_map, scale_mode, scale);
+            break;
+        default: return ZQ_ERR_UNSUPPORTED;
+    }
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+int zq_dequantize(const zq_weight* w, float* d_out, zq_stream stream) {
+    if (!w || !d_out) return ZQ_ERR_BAD_ARG;
+    return dequant_launch(w, d_out, w->out_dim, nullptr, 0, 1.0f, stream);
+}
+
+int zq_dequant_rows_scaled(const zq_weight* w, const int32_t* d_token_ids, uint32_t n_rows,
+                           float scale, float* d_out, zq_stream stream) {
+    if (!w || !d_token_ids || !d_out) return ZQ_ERR_BAD_ARG;
+    return dequant_launch(w, d_out, n_rows, d_token_ids, 1, scale, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,63 @@
+// Internal declarations shared by the libzq translation units (not part of the C ABI).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "zq.h"
+
+// Device-resident quantised weight. Values are those of the GGUF blocks; only the
+// arrangement differs so that the kernels can use aligned 128-bit loads:
+//   qs : [out_dim][nb][QB] quant bytes of each block, QB = 16 (q4_0, q4_1) or 32 (q8_0),
+//        in the block's own byte order; row pitch nb*QB is a multiple of 16 bytes.
+//   sc : q4_0 / q8_0: f16 d [out_dim][nb];  q4_1: (f16 d, f16 m) pairs [out_dim][nb].
+struct zq_weight {
+    int type;
+    uint32_t out_dim;
+    uint32_t in_dim;
+    uint32_t nb;       // blocks per row = in_dim / 32
+    uint32_t qb;       // quant bytes per block
+    uint8_t* qs;       // device
+    void* sc;          // device
+    void* base;        // the single allocation holding qs and sc
+    size_t bytes;      // size of that allocation
+};
+
+namespace zq {
+
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return ZQ_ERR_CUDA;
+}
+
+#define ZQ_CUDA(call)                                   \
+    do {                                                \
+        cudaError_t e__ = (call);                       \
+        if (e__ != cudaSuccess) return zq::cuda_fail(e__); \
+    } while (0)
+
+// Check the launch that was just issued.
+#define ZQ_LAUNCH_CHECK() ZQ_CUDA(cudaGetLastError())
+
+inline cudaStream_t as_stream(zq_stream s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline bool is_quant(int t) { return t == ZQ_TYPE_Q4_0 || t == ZQ_TYPE_Q4_1 || t == ZQ_TYPE_Q8_0; }
+
+int sm_count();  // multiprocessors of the current device (cached per device)
+
+// ---- launchers implemented in gemv.cu and used by the engines -------------------------
+
+// Prologue applied to the activation row before the dot products (engine fusions).
+enum Prologue { PRO_NONE = 0 };
+
+int launch_gemv_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
+                    const zq_epilogue* ep, cudaStream_t st);
+int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum,
+                   float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
+int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, int8_t* q,
+                            float* scale, int32_t* sum, cudaStream_t st);
+
+}  // namespace zq
