@@ -180,10 +180,17 @@ int zq_write_kv_cache(const float* d_k, const float* d_v, float* d_k_cache, floa
 /* gqa_cached_attention / cached_attention (src/models/gemma3.zig:1062-1120;
  * src/models/gpt2.zig:796-849; dispatch_attention_decode, metal.zig:1025).
  * q [n_head*head_dim]; caches [ctx][kv_dim]; out [n_head*head_dim]. Query head h reads the
- * KV head h / (n_head / n_kv_head). Positions kv_start <= p < kv_end. */
+ * KV head h / (n_head / n_kv_head). Positions kv_start <= p < kv_end (at most 12288 of them).
+ * d_scores: scratch of n_head*(kv_end-kv_start) floats, as the Metal dispatcher's `scores` buffer.
+ * The arithmetic order is the CPU loops' (16-lane dot products, exponentials summed one by one,
+ * values accumulated position by position), so results are bit-identical to them when exp is
+ * taken as the correctly rounded f32 exponential. flags: ZQ_ATTN_GPT2_SOFTMAX selects the GPT-2
+ * softmax, whose last (n % 16) weights are divided by the sum rather than multiplied by 1/sum. */
+#define ZQ_ATTN_GPT2_SOFTMAX 1
 int zq_attention_decode(const float* d_q, const float* d_k_cache, const float* d_v_cache,
-                        float* d_out, uint32_t n_head, uint32_t n_kv_head, uint32_t head_dim,
-                        uint32_t kv_start, uint32_t kv_end, zq_stream stream);
+                        float* d_out, float* d_scores, uint32_t n_head, uint32_t n_kv_head,
+                        uint32_t head_dim, uint32_t kv_start, uint32_t kv_end, int flags,
+                        zq_stream stream);
 
 /* ----------------------- forward kernels behind src/cuda_ops.zig dispatchers */
 

@@ -9,6 +9,16 @@
 namespace {
 constexpr size_t VL = 16;
 
+// Transcendentals are evaluated in double and rounded once to f32 (correctly rounded for all but
+// about one argument in 2^29). The reference calls Zig's own f32 routines (@exp, @cos, @sin,
+// std.math.tanh), whose last bit is implementation-defined and not reproducible without a Zig
+// toolchain; the double-rounded value is the deterministic stand-in both the oracle and the CUDA
+// kernels use.
+inline float exp_f32(float x) { return (float)std::exp((double)x); }
+inline float tanh_f32(float x) { return (float)std::tanh((double)x); }
+inline float cos_f32(float x) { return (float)std::cos((double)x); }
+inline float sin_f32(float x) { return (float)std::sin((double)x); }
+
 inline float reduce_lanes(const float* acc) {
     float s = acc[0];
     for (size_t l = 1; l < VL; ++l) s += acc[l];
@@ -110,7 +120,7 @@ void zqo_gelu_in_place(float* x, size_t n) {
     for (size_t i = 0; i < n; ++i) {
         const float v = x[i];
         const float inner = c * (v + 0.044715f * v * v * v);
-        x[i] = 0.5f * v * (1.0f + std::tanh(inner));
+        x[i] = 0.5f * v * (1.0f + tanh_f32(inner));
     }
 }
 
@@ -120,7 +130,7 @@ void zqo_softmax_gpt2(float* x, size_t n) {
         if (x[i] > mx) mx = x[i];
     float sum = 0.0f;
     for (size_t j = 0; j < n; ++j) {
-        x[j] = std::exp(x[j] - mx);
+        x[j] = exp_f32(x[j] - mx);
         sum += x[j];
     }
     const float inv = 1.0f / sum;
@@ -136,7 +146,7 @@ void zqo_softmax_gemma(float* x, size_t n) {
         if (x[i] > mx) mx = x[i];
     float sum = 0.0f;
     for (size_t j = 0; j < n; ++j) {
-        x[j] = std::exp(x[j] - mx);
+        x[j] = exp_f32(x[j] - mx);
         sum += x[j];
     }
     const float inv = 1.0f / sum;
@@ -158,7 +168,7 @@ void zqo_rope(float* x, size_t pos, const float* freqs, size_t n_freqs) {
     const float p = (float)pos;
     for (size_t i = 0; i < n_freqs; ++i) {
         const float theta = p * freqs[i];
-        const float c = std::cos(theta), s = std::sin(theta);
+        const float c = cos_f32(theta), s = sin_f32(theta);
         const float x0 = x[2 * i], x1 = x[2 * i + 1];
         x[2 * i] = x0 * c - x1 * s;
         x[2 * i + 1] = x0 * s + x1 * c;

@@ -16,6 +16,8 @@
  *     host); lane accumulators, then an in-order reduction lane 0..15.
  *   - mul and add are separate roundings (build with -ffp-contract=off).
  *   - round() is round-half-away-from-zero (std.math.round).
+ *   - exp / tanh / cos / sin are computed in double and rounded once to f32 (see ops.cpp); the
+ *     reference's own f32 routines may differ from that in the last bit.
  */
 #ifndef ZQ_ORACLE_H
 #define ZQ_ORACLE_H

@@ -18,12 +18,12 @@ def rel_l2(a, b):
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
 
 
-def run_parity(zq_engine, oracle_model, prompt, n_steps, logits_tol=1e-3):
-    """Greedy decoding on both sides; returns (gpu tokens, cpu tokens, worst logits rel-L2 while the
-    token streams agree)."""
+def run_parity(zq_engine, oracle_model, prompt, n_steps):
+    """Greedy decoding on both sides; returns (gpu tokens, cpu tokens, logits rel-L2 of every step
+    while the token streams agree)."""
     lg = zq_engine.prefill(prompt).cpu().numpy()
     lc = oracle_model.prefill(prompt)
-    worst = rel_l2(lg, lc)
+    errs = [rel_l2(lg, lc)]
     gt, ct = [], []
     for _ in range(n_steps):
         tg, tc = int(np.argmax(lg)), int(np.argmax(lc))
@@ -33,16 +33,16 @@ def run_parity(zq_engine, oracle_model, prompt, n_steps, logits_tol=1e-3):
             break
         lg = zq_engine.decode_next(tg).cpu().numpy()
         lc = oracle_model.decode_next(tc)
-        worst = max(worst, rel_l2(lg, lc))
-    return gt, ct, worst
+        errs.append(rel_l2(lg, lc))
+    return gt, ct, errs
 
 
 def test_gpt2_tiny_parity(zq, oracle):
     host = hostmodel.Gpt2Host.synthetic(GPT2_TINY, seed=42, std=0.08).randomize_small_params()
     prompt = np.random.default_rng(44).integers(0, GPT2_TINY["vocab"], size=20)
-    gt, ct, worst = run_parity(zq.Gpt2(host), oracle.Gpt2(host, 4), prompt, 64)
+    gt, ct, errs = run_parity(zq.Gpt2(host), oracle.Gpt2(host, 4), prompt, 64)
     assert gt == ct
-    assert worst <= 1e-3, worst
+    assert max(errs) <= 1e-5, max(errs)  # f32 activations: no quantiser in the loop
 
 
 @pytest.mark.parametrize("qtypes", [(ggml.Q8_0, ggml.Q8_0, ggml.Q8_0), (ggml.Q4_0, ggml.Q8_0, ggml.Q4_1),
@@ -52,9 +52,12 @@ def test_gemma3_tiny_parity(zq, oracle, qtypes):
     host = hostmodel.Gemma3Host.synthetic(GEMMA_TINY, qtype=q, embd_qtype=embd, down_qtype=down, seed=42,
                                           std=0.08).randomize_small_params()
     prompt = np.random.default_rng(44).integers(0, GEMMA_TINY["vocab"], size=24)  # beyond the window of 16
-    gt, ct, worst = run_parity(zq.Gemma3(host), oracle.Gemma3(host, 4), prompt, 64)
+    gt, ct, errs = run_parity(zq.Gemma3(host), oracle.Gemma3(host, 4), prompt, 64)
     assert gt == ct
-    assert worst <= 1e-3, worst
+    # Every op of this path is evaluated in the CPU code's order, so the logits are the same bits.
+    # (The Q8 activation quantiser makes anything less than that chaotic: one activation that differs
+    # in its last bit can round to the other integer and move the logits of a 128-wide model by 1e-2.)
+    assert max(errs) == 0.0, errs
 
 
 def test_device_greedy_loop_matches_stepwise(zq):
@@ -94,15 +97,17 @@ def test_gpt2_small_full_size_greedy_64(zq, oracle):
     """GPT-2 small, Q4_0, seed 42, 32-token prompt, first 64 greedy tokens identical."""
     host = hostmodel.Gpt2Host.synthetic(hostmodel.GPT2_SMALL, qtype=ggml.Q4_0, seed=42, std=0.02, device="cuda")
     prompt = np.random.default_rng(44).integers(0, 50257, size=32)
-    gt, ct, worst = run_parity(zq.Gpt2(host), oracle.Gpt2(host, 8), prompt, 64)
+    gt, ct, errs = run_parity(zq.Gpt2(host), oracle.Gpt2(host, 8), prompt, 64)
+    print("gpt2 full-size logits rel-L2: max %.2e median %.2e" % (max(errs), float(np.median(errs))))
     assert gt == ct, (len(gt), gt[-1], ct[-1])
-    assert worst <= 1e-3, worst
+    assert max(errs) <= 1e-3, max(errs)
 
 
 def test_gemma3_1b_full_size_greedy_64(zq, oracle):
     """Gemma-3-1B shape, Q8_0, seed 42, 16-token prompt, first 64 greedy tokens identical."""
     host = hostmodel.Gemma3Host.synthetic(hostmodel.GEMMA3_1B, qtype=ggml.Q8_0, seed=42, std=0.02, device="cuda")
     prompt = np.random.default_rng(44).integers(0, 262144, size=16)
-    gt, ct, worst = run_parity(zq.Gemma3(host), oracle.Gemma3(host, 8), prompt, 64)
+    gt, ct, errs = run_parity(zq.Gemma3(host), oracle.Gemma3(host, 8), prompt, 64)
+    print("gemma3 full-size logits rel-L2: max %.2e median %.2e" % (max(errs), float(np.median(errs))))
     assert gt == ct, (len(gt), gt[-1], ct[-1])
-    assert worst <= 1e-3, worst
+    assert max(errs) <= 1e-3, max(errs)

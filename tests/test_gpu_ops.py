@@ -25,10 +25,10 @@ RNG = np.random.default_rng(11)
 def test_rms_norm(zq, oracle, rows, dim):
     x = RNG.standard_normal((rows, dim)).astype(np.float32)
     w = (1 + 0.1 * RNG.standard_normal(dim)).astype(np.float32)
-    assert rel_l2(zq.rms_norm(t(x), t(w), 1e-6).cpu().numpy(), oracle.rms_norm_rows(x, w, 1e-6)) <= TOL
+    assert np.array_equal(zq.rms_norm(t(x), t(w), 1e-6).cpu().numpy(), oracle.rms_norm_rows(x, w, 1e-6))
     res = RNG.standard_normal((rows, dim)).astype(np.float32)
     got = zq.rms_norm_residual(t(x), t(w), t(res), 1e-6).cpu().numpy()
-    assert rel_l2(got, res + oracle.rms_norm_rows(x, w, 1e-6)) <= TOL
+    assert np.array_equal(got, res + oracle.rms_norm_rows(x, w, 1e-6))
 
 
 def test_rms_norm_known_answer(zq):  # src/models/gemma3.zig:1210-1223
@@ -42,7 +42,7 @@ def test_rms_norm_in_place_per_head(zq, oracle):
     w = (1 + 0.1 * RNG.standard_normal(256)).astype(np.float32)
     got = zq.rms_norm_in_place(t(x), t(w), 256, 1e-6).cpu().numpy()
     want = np.stack([oracle.rms_norm_in_place(x[h], w, 1e-6) for h in range(4)])
-    assert rel_l2(got, want) <= TOL
+    assert np.array_equal(got, want)
 
 
 @pytest.mark.parametrize("pos", [0, 1, 17, 2047])
@@ -54,14 +54,14 @@ def test_rope(zq, oracle, pos):
     want = np.stack([oracle.rope(x[h], pos, freqs) for h in range(4)])
     if pos == 0:  # src/models/gemma3.zig:1225-1233
         assert np.array_equal(got, x)
-    assert rel_l2(got, want) <= 1e-6
+    assert np.array_equal(got, want)
 
 
 def test_gelu_and_gelu_mul(zq, oracle):
     x = (3 * RNG.standard_normal(6912)).astype(np.float32)
     up = RNG.standard_normal(6912).astype(np.float32)
-    assert rel_l2(zq.gelu(t(x)).cpu().numpy(), oracle.gelu(x)) <= TOL
-    assert rel_l2(zq.gelu_mul(t(x), t(up)).cpu().numpy(), oracle.gelu(x) * up) <= TOL
+    assert np.array_equal(zq.gelu(t(x)).cpu().numpy(), oracle.gelu(x))
+    assert np.array_equal(zq.gelu_mul(t(x), t(up)).cpu().numpy(), oracle.gelu(x) * up)
     k = zq.gelu(t(np.array([0, 1, -1, 2, -2]))).cpu().numpy()  # src/models/gpt2.zig:1015-1028
     assert abs(k[0]) < 1e-6 and abs(k[1] - 0.8412) < 0.01 and abs(k[2] + 0.1588) < 0.01 and k[3] > 0 and abs(k[4]) < 0.1
 
@@ -69,9 +69,9 @@ def test_gelu_and_gelu_mul(zq, oracle):
 @pytest.mark.parametrize("rows,cols", [(1, 3), (7, 1000), (2, 2048), (3, 1)])
 def test_softmax(zq, oracle, rows, cols):
     x = (4 * RNG.standard_normal((rows, cols))).astype(np.float32)
-    want = oracle.softmax_forward(x)
-    assert rel_l2(zq.softmax(t(x)).cpu().numpy(), want) <= TOL
-    assert rel_l2(zq.softmax_(t(x)).cpu().numpy(), want) <= TOL
+    want = oracle.softmax_forward(x)  # sums its exponentials one by one; 2048 terms drift a few ulp
+    assert rel_l2(zq.softmax(t(x)).cpu().numpy(), want) <= 1e-5
+    assert rel_l2(zq.softmax_(t(x)).cpu().numpy(), want) <= 1e-5
     np.testing.assert_allclose(zq.softmax(t(x)).sum(dim=-1).cpu().numpy(), np.ones(rows), atol=1e-5)
 
 
@@ -103,20 +103,22 @@ def test_broadcast_gather_scale(zq):
 
 @pytest.mark.parametrize("n_head,n_kv,hd,kv_start,kv_end", [
     (12, 12, 64, 0, 1), (12, 12, 64, 0, 160), (4, 1, 256, 0, 37), (4, 1, 256, 100, 612), (4, 1, 256, 0, 2048),
-    (2, 1, 32, 3, 11)])
+    (2, 1, 32, 3, 11), (3, 1, 40, 0, 21)])
 def test_attention_decode(zq, oracle, n_head, n_kv, hd, kv_start, kv_end):
     kv_dim = n_kv * hd
     ctx = kv_end
     q = RNG.standard_normal(n_head * hd).astype(np.float32)
     kc = RNG.standard_normal((ctx, kv_dim)).astype(np.float32)
     vc = RNG.standard_normal((ctx, kv_dim)).astype(np.float32)
-    got = zq.attention_decode(t(q), t(kc), t(vc), n_head, n_kv, hd, kv_start, kv_end).cpu().numpy()
     if n_kv == n_head:
         assert kv_start == 0
+        got = zq.attention_decode(t(q), t(kc), t(vc), n_head, n_kv, hd, kv_start, kv_end,
+                                  flags=zq.ATTN_GPT2_SOFTMAX).cpu().numpy()
         want = oracle.cached_attention(q, kc, vc, kv_end, n_head, hd)
     else:
+        got = zq.attention_decode(t(q), t(kc), t(vc), n_head, n_kv, hd, kv_start, kv_end).cpu().numpy()
         want = oracle.gqa_cached_attention(q, kc, vc, kv_start, kv_end, n_head, hd, kv_dim)
-    assert rel_l2(got, want) <= 1e-5
+    assert np.array_equal(got, want), rel_l2(got, want)
 
 
 def test_attention_single_position_returns_v(zq):  # src/models/gpt2.zig:1059-1079

@@ -156,6 +156,8 @@ def test_epilogue_bias_gelu_mul_residual(zq, oracle, act):
     t = lambda a: torch.from_numpy(a).cuda()
     got = zq.quant_matmul_no_grad(t(x), qw, act, bias=t(bias), gelu=True, mul=t(mul[None]), residual=t(res[None]))
     assert rel_l2(got.cpu().numpy()[0], want) <= 1e-5
+    if act == 1:  # exact dots + exactly ordered epilogue
+        assert np.array_equal(got.cpu().numpy()[0], want)
     # residual may alias the output (x += W h, src/models/gpt2.zig:495-496)
     y = t(res[None].copy())
     zq.quant_matmul_no_grad(t(x), qw, act, bias=t(bias), residual=y, out=y)
@@ -212,7 +214,7 @@ def test_error_statuses(zq):
         zq.QuantWeight(np.zeros(22, np.uint8), 6, 1, 32)  # q5_0
     assert e.value.status == 2
     with pytest.raises(_lib.ZqError) as e:
-        zq.QuantWeight(np.zeros(27, np.uint8), ggml.Q4_0, 1, 48)
+        zq.QuantWeight(np.zeros(18, np.uint8), ggml.Q4_0, 1, 48)  # in_dim % 32 != 0
     assert e.value.status == 1
     qw = zq.QuantWeight(np.zeros(18, np.uint8), ggml.Q4_0, 1, 32)
     with pytest.raises(ValueError):

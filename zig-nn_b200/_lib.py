@@ -47,7 +47,7 @@ SIGNATURES = {
     "zq_rope_freqs_host": (i, [u32, f, vp]),
     "zq_gelu_mul": (i, [vp, vp, sz, vp]),
     "zq_write_kv_cache": (i, [vp, vp, vp, vp, u32, u32, vp]),
-    "zq_attention_decode": (i, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
+    "zq_attention_decode": (i, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, i, vp]),
     "zq_softmax": (i, [vp, u32, u32, vp]),
     "zq_softmax_out": (i, [vp, vp, u32, u32, vp]),
     "zq_layer_norm": (i, [vp, vp, vp, vp, u32, u32, f, vp]),

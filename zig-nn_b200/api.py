@@ -189,12 +189,17 @@ def write_kv_cache(k, v, k_cache, v_cache, pos):
                "zq_write_kv_cache")
 
 
-def attention_decode(q, k_cache, v_cache, n_head, n_kv_head, head_dim, kv_start, kv_end):
+ATTN_GPT2_SOFTMAX = 1
+
+
+def attention_decode(q, k_cache, v_cache, n_head, n_kv_head, head_dim, kv_start, kv_end, flags=0, scores=None):
     q = _dev_f32(q)
     out = torch.empty(n_head * head_dim, dtype=torch.float32, device=q.device)
+    if scores is None:
+        scores = torch.empty(n_head * max(1, kv_end - kv_start), dtype=torch.float32, device=q.device)
     _lib.check(_lib.load().zq_attention_decode(_ptr(q), _ptr(_dev_f32(k_cache)), _ptr(_dev_f32(v_cache)),
-                                               _ptr(out), n_head, n_kv_head, head_dim, kv_start, kv_end,
-                                               _stream()), "zq_attention_decode")
+                                               _ptr(out), _ptr(scores), n_head, n_kv_head, head_dim, kv_start,
+                                               kv_end, flags, _stream()), "zq_attention_decode")
     return out
 
 

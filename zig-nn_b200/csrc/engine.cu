@@ -94,6 +94,7 @@ struct zq_gpt2 {
     std::vector<Block> blocks;
     std::vector<float*> k, v;  // per layer [ctx][embed]
     float *x = nullptr, *ln = nullptr, *qkv = nullptr, *att = nullptr, *hid = nullptr, *logits = nullptr;
+    float* scores = nullptr;  // [head][ctx] attention scratch
     uint32_t* d_token = nullptr;
     int32_t* d_arg = nullptr;
     uint32_t* d_record = nullptr;  // ctx entries for greedy decoding
@@ -132,7 +133,8 @@ static int gpt2_step(zq_gpt2* m, uint32_t pos, bool want_logits, cudaStream_t st
         if ((rc = zq_layer_norm(m->ln, m->x, b.ln1_w, b.ln1_b, 1, E, 1e-5f, st))) return rc;
         if ((rc = gpt2_linear(b.qkv, m->ln, m->qkv, b.qkv_b, 0, nullptr, st))) return rc;
         if ((rc = zq_write_kv_cache(m->qkv + E, m->qkv + 2 * E, m->k[l], m->v[l], pos, E, st))) return rc;
-        if ((rc = zq_attention_decode(m->qkv, m->k[l], m->v[l], m->att, C.head, C.head, hd, 0, pos + 1, st)))
+        if ((rc = zq_attention_decode(m->qkv, m->k[l], m->v[l], m->att, m->scores, C.head, C.head, hd, 0, pos + 1,
+                                      ZQ_ATTN_GPT2_SOFTMAX, st)))
             return rc;
         if ((rc = gpt2_linear(b.proj, m->att, m->x, b.proj_b, 0, m->x, st))) return rc;
         if ((rc = zq_layer_norm(m->ln, m->x, b.ln2_w, b.ln2_b, 1, E, 1e-5f, st))) return rc;
@@ -201,6 +203,7 @@ int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_strea
     TRY(m->arena.alloc_n(&m->att, E));
     TRY(m->arena.alloc_n(&m->hid, F));
     TRY(m->arena.alloc_n(&m->logits, cfg->vocab));
+    TRY(m->arena.alloc_n(&m->scores, (size_t)cfg->head * cfg->ctx));
     TRY(m->arena.alloc_n(&m->d_token, 1));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, cfg->ctx));
@@ -304,6 +307,7 @@ struct zq_gemma3 {
     float* freqs = nullptr;
     float *x = nullptr, *h = nullptr, *q = nullptr, *kb = nullptr, *vb = nullptr, *att = nullptr,
           *proj = nullptr, *gate = nullptr, *up = nullptr, *ffn = nullptr, *logits = nullptr;
+    float* scores = nullptr;  // [head][ctx] attention scratch
     int8_t* xq = nullptr;   // quantised activation row, max(embed, ffn, q_dim)
     float* xscale = nullptr;
     int32_t* xsum = nullptr;
@@ -358,8 +362,8 @@ static int gemma3_step(zq_gemma3* m, uint32_t pos, bool want_logits, cudaStream_
         const uint32_t kv_len = pos + 1;
         const uint32_t window = global ? kv_len : (kv_len < C.sliding_window ? kv_len : C.sliding_window);
         const uint32_t kv_start = kv_len - window;
-        if ((rc = zq_attention_decode(m->q, m->k[l], m->v[l], m->att, C.head, C.head_kv, D, kv_start,
-                                      kv_len, st)))
+        if ((rc = zq_attention_decode(m->q, m->k[l], m->v[l], m->att, m->scores, C.head, C.head_kv, D, kv_start,
+                                      kv_len, 0, st)))
             return rc;
         if ((rc = gemma_quantize(m, m->att, QD, st))) return rc;
         if ((rc = gemma_gemv(m, b.o, m->proj, st))) return rc;
@@ -462,6 +466,7 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
     TRY(m->arena.alloc_n(&m->up, F));
     TRY(m->arena.alloc_n(&m->ffn, E));
     TRY(m->arena.alloc_n(&m->logits, C.vocab));
+    TRY(m->arena.alloc_n(&m->scores, (size_t)C.head * C.ctx));
     TRY(m->arena.alloc_n(&m->xq, max_dim));
     TRY(m->arena.alloc_n(&m->xscale, max_dim / 32));
     TRY(m->arena.alloc_n(&m->xsum, max_dim / 32));

@@ -92,10 +92,12 @@ __device__ __forceinline__ void q8_word_dot(uint32_t q, float4 x, float2& acc) {
     acc = ffma2(a23, make_float2(x.z, x.w), acc);
 }
 
+// 0.5*v*(1+tanh(0.7978845608*(v+0.044715*v*v*v))) — src/models/gpt2.zig:690-697. Every operation
+// is a separate f32 rounding in the CPU code's order; tanh is evaluated in double and rounded once.
 __device__ __forceinline__ float gelu_tanh(float v) {
-    // 0.5*v*(1+tanh(0.7978845608*(v+0.044715*v^3))) — src/models/gpt2.zig:690-697
-    const float inner = 0.7978845608f * (v + 0.044715f * v * v * v);
-    return 0.5f * v * (1.0f + tanhf(inner));
+    const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
+    const float inner = __fmul_rn(0.7978845608f, __fadd_rn(v, cube));
+    return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, (float)tanh((double)inner)));
 }
 
 struct EpilogueArgs {
@@ -106,10 +108,10 @@ struct EpilogueArgs {
 };
 
 __device__ __forceinline__ float apply_epilogue(float v, const EpilogueArgs& ep, size_t j) {
-    if (ep.bias) v += ep.bias[j];
+    if (ep.bias) v = __fadd_rn(v, ep.bias[j]);
     if (ep.gelu) v = gelu_tanh(v);
-    if (ep.mul) v *= ep.mul[j];
-    if (ep.residual) v += ep.residual[j];
+    if (ep.mul) v = __fmul_rn(v, ep.mul[j]);
+    if (ep.residual) v = __fadd_rn(ep.residual[j], v);
     return v;
 }
 
@@ -610,8 +612,9 @@ int zq_quantize_rows_q8(const float* d_x, uint32_t m_rows, uint32_t in_dim, int8
 int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows, int act_mode,
               const zq_epilogue* epilogue, void* d_workspace, size_t workspace_bytes,
               zq_stream stream) {
-    if (!w || !d_x || !d_y) return ZQ_ERR_BAD_ARG;
+    if (!w) return ZQ_ERR_BAD_ARG;
     if (m_rows == 0) return ZQ_OK;
+    if (!d_x || !d_y) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
     if (act_mode == ZQ_ACT_F32) return launch_gemv_f32(w, d_x, d_y, m_rows, epilogue, st);
     if (act_mode == ZQ_ACT_Q8) {

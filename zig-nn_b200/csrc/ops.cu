@@ -49,40 +49,78 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// Transcendentals are evaluated in double and rounded once to f32, the same definition the CPU
+// checker uses; every multiply and add below is a separate rounding (no FMA contraction), in the
+// order the CPU code performs them.
+__device__ __forceinline__ float exp_f32(float x) { return (float)exp((double)x); }
+__device__ __forceinline__ float tanh_f32(float x) { return (float)tanh((double)x); }
+
+// 0.5*v*(1+tanh(0.7978845608*(v+0.044715*v*v*v))) — src/models/gpt2.zig:690-697
 __device__ __forceinline__ float gelu_tanh(float v) {
-    const float inner = 0.7978845608f * (v + 0.044715f * v * v * v);
-    return 0.5f * v * (1.0f + tanhf(inner));
+    const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
+    const float inner = __fmul_rn(0.7978845608f, __fadd_rn(v, cube));
+    return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanh_f32(inner)));
 }
 
-// mode 0: out = norm(x)*w ; mode 1: out(residual) += norm(x)*w
+// Sum of squares in the order of the CPU loop (src/models/gemma3.zig:920-930): 16 lane
+// accumulators over the multiple-of-16 prefix (lane l takes x[l], x[l+16], ...), lanes added in
+// order 0..15, then the tail elements one by one. `xs` is the row in shared memory; the result is
+// returned to every thread through `bc`.
+__device__ __forceinline__ float sumsq_lanes16(const float* xs, uint32_t dim, float* part, float* bc) {
+    const uint32_t dim16 = dim & ~15u;
+    if (threadIdx.x < 16) {
+        float acc = 0.0f;
+        for (uint32_t i = threadIdx.x; i < dim16; i += 16) acc = __fadd_rn(acc, __fmul_rn(xs[i], xs[i]));
+        part[threadIdx.x] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float ss = part[0];
+#pragma unroll
+        for (int l = 1; l < 16; ++l) ss = __fadd_rn(ss, part[l]);
+        for (uint32_t i = dim16; i < dim; ++i) ss = __fadd_rn(ss, __fmul_rn(xs[i], xs[i]));
+        *bc = ss;
+    }
+    __syncthreads();
+    return *bc;
+}
+
+// mode 0: out = norm(x)*w ; mode 1: out(residual) += norm(x)*w.  Bit-identical to rms_norm_rows.
 __global__ void __launch_bounds__(256)
 rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
                 uint32_t dim, float eps, int mode) {
-    __shared__ float red[33];
+    extern __shared__ __align__(16) float xs[];
+    __shared__ float part[16];
+    __shared__ float bc;
     const float* row = x + (size_t)blockIdx.x * dim;
     float* o = out + (size_t)blockIdx.x * dim;
-    float ss = 0.0f;
-    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
-    ss = block_sum(ss, red);
-    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) xs[i] = row[i];
+    __syncthreads();
+    const float ss = sumsq_lanes16(xs, dim, part, &bc);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float v = __fmul_rn(__fmul_rn(row[i], inv), w[i]);
-        o[i] = mode ? o[i] + v : v;
+        const float v = __fmul_rn(__fmul_rn(xs[i], inv), w[i]);
+        o[i] = mode ? __fadd_rn(o[i], v) : v;
     }
 }
 
-// One warp per vector (per-head q/k norm, src/models/gemma3.zig:949-959).
-__global__ void rms_norm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, uint32_t dim,
-                                    uint32_t n_vec, float eps) {
-    const uint32_t v = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (v >= n_vec) return;
-    float* p = x + (size_t)v * dim;
-    float ss = 0.0f;
-    for (uint32_t i = lane; i < dim; i += 32) ss = fmaf(p[i], p[i], ss);
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-    for (uint32_t i = lane; i < dim; i += 32) p[i] = __fmul_rn(__fmul_rn(p[i], inv), w[i]);
+// One CTA of 64 threads per vector, squares summed one by one as rms_norm_in_place does
+// (src/models/gemma3.zig:949-959).
+__global__ void __launch_bounds__(64)
+rms_norm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, uint32_t dim, float eps) {
+    extern __shared__ __align__(16) float xs[];
+    __shared__ float bc;
+    float* p = x + (size_t)blockIdx.x * dim;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) xs[i] = p[i];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float ss = 0.0f;
+        for (uint32_t i = 0; i < dim; ++i) ss = __fadd_rn(ss, __fmul_rn(xs[i], xs[i]));
+        bc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+    }
+    __syncthreads();
+    const float inv = bc;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) p[i] = __fmul_rn(__fmul_rn(xs[i], inv), w[i]);
 }
 
 __global__ void rope_kernel(float* __restrict__ x, const float* __restrict__ freqs, uint32_t half_dim,
@@ -91,8 +129,7 @@ __global__ void rope_kernel(float* __restrict__ x, const float* __restrict__ fre
     if (idx >= half_dim * n_heads) return;
     const uint32_t i = idx % half_dim, h = idx / half_dim;
     const float theta = __fmul_rn(pos, freqs[i]);
-    float s, c;
-    sincosf(theta, &s, &c);
+    const float c = (float)cos((double)theta), s = (float)sin((double)theta);
     float* p = x + (size_t)h * half_dim * 2 + 2 * i;
     const float x0 = p[0], x1 = p[1];
     p[0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
@@ -105,7 +142,7 @@ __global__ void gelu_kernel(float* __restrict__ out, const float* __restrict__ x
 }
 __global__ void gelu_mul_kernel(float* __restrict__ gate, const float* __restrict__ up, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) gate[i] = gelu_tanh(gate[i]) * up[i];
+    if (i < n) gate[i] = __fmul_rn(gelu_tanh(gate[i]), up[i]);
 }
 __global__ void add_broadcast_kernel(float* __restrict__ out, const float* __restrict__ a,
                                      const float* __restrict__ b, size_t a_total, size_t b_total) {
@@ -179,69 +216,97 @@ layer_norm_kernel(float* __restrict__ out, const float* __restrict__ x, const fl
         o[i] = __fadd_rn(__fmul_rn(__fmul_rn(row[i] - mean, inv_std), gamma[i]), beta[i]);
 }
 
-// Single-query attention over a KV cache, one CTA per query head.
-// scores[p] = dot(q_h, k[p]) / sqrt(head_dim) for kv_start <= p < kv_end, softmax, out = sum w*v.
+// Single-query attention over a KV cache in the arithmetic order of gqa_cached_attention /
+// cached_attention (src/models/gemma3.zig:1062-1120, src/models/gpt2.zig:796-849), two launches.
+//
+// Scores: each dot product keeps 16 lane accumulators (lane l takes elements l, l+16, ...), adds
+// the lanes in order 0..15, then any tail elements, then multiplies by 1/sqrt(head_dim). A CTA of
+// 256 threads handles 16 positions x 16 lanes.
 __global__ void __launch_bounds__(256)
-attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ kc,
-                        const float* __restrict__ vc, float* __restrict__ out, uint32_t n_head,
-                        uint32_t n_kv_head, uint32_t head_dim, uint32_t kv_start, uint32_t kv_end) {
-    extern __shared__ __align__(16) float sm[];
+attention_scores_kernel(const float* __restrict__ q, const float* __restrict__ kc,
+                        float* __restrict__ scores, uint32_t n_head, uint32_t n_kv_head,
+                        uint32_t head_dim, uint32_t kv_start, uint32_t kv_end) {
+    __shared__ float part[16][17];
+    const uint32_t h = blockIdx.y;
+    const uint32_t kvh = h / (n_head / n_kv_head);
+    const uint32_t kv_dim = n_kv_head * head_dim;
+    const uint32_t kv_len = kv_end - kv_start;
+    const uint32_t pp = threadIdx.x >> 4, l = threadIdx.x & 15;
+    const uint32_t p = blockIdx.x * 16 + pp;
+    const uint32_t dim16 = head_dim & ~15u;
+    const float* qh = q + (size_t)h * head_dim;
+    const float* kr = kc + (size_t)(kv_start + min(p, kv_len - 1)) * kv_dim + (size_t)kvh * head_dim;
+    float acc = 0.0f;
+    for (uint32_t d = l; d < dim16; d += 16) acc = __fadd_rn(acc, __fmul_rn(qh[d], kr[d]));
+    part[pp][l] = acc;
+    __syncthreads();
+    if (l == 0 && p < kv_len) {
+        float s = part[pp][0];
+#pragma unroll
+        for (int j = 1; j < 16; ++j) s = __fadd_rn(s, part[pp][j]);
+        for (uint32_t d = dim16; d < head_dim; ++d) s = __fadd_rn(s, __fmul_rn(qh[d], kr[d]));
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)head_dim));
+        scores[(size_t)h * kv_len + p] = __fmul_rn(s, scale);
+    }
+}
+
+// Softmax and weighted sum of V, one CTA per query head: maximum, exp(s - max), the exponentials
+// added one by one, weights = e * (1/sum), then out[d] += w[p] * v[p][d] for p in order.
+// gpt2_tail: the GPT-2 softmax divides its last (n % 16) elements by the sum instead of multiplying
+// by the reciprocal (src/models/gpt2.zig:721-730).
+__global__ void __launch_bounds__(256)
+attention_softmax_v_kernel(const float* __restrict__ scores, const float* __restrict__ vc,
+                           float* __restrict__ out, uint32_t n_head, uint32_t n_kv_head,
+                           uint32_t head_dim, uint32_t kv_start, uint32_t kv_end, int gpt2_tail) {
+    extern __shared__ __align__(16) float w[];  // kv_len
     __shared__ float red[33];
+    __shared__ float bc;
     const uint32_t h = blockIdx.x;
     const uint32_t kvh = h / (n_head / n_kv_head);
     const uint32_t kv_dim = n_kv_head * head_dim;
     const uint32_t kv_len = kv_end - kv_start;
-    float* scores = sm;            // kv_len
-    float* part = sm + kv_len;     // groups * head_dim
-    const float* qh = q + (size_t)h * head_dim;
-    const float scale = 1.0f / sqrtf((float)head_dim);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-
-    for (uint32_t p = warp; p < kv_len; p += nw) {
-        const float* kr = kc + (size_t)(kv_start + p) * kv_dim + (size_t)kvh * head_dim;
-        float acc = 0.0f;
-        for (uint32_t d = lane; d < head_dim; d += 32) acc = fmaf(qh[d], kr[d], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) scores[p] = acc * scale;
-    }
-    __syncthreads();
+    const float* sh = scores + (size_t)h * kv_len;
     float mx = -INFINITY;
-    for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x) mx = fmaxf(mx, scores[p]);
-    mx = block_max(mx, red);
-    float s = 0.0f;
     for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x) {
-        const float e = expf(scores[p] - mx);
-        scores[p] = e;
-        s += e;
+        const float v = sh[p];
+        w[p] = v;
+        mx = fmaxf(mx, v);
     }
-    s = block_sum(s, red);
-    const float inv = 1.0f / s;
-    for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x) scores[p] *= inv;
+    mx = block_max(mx, red);
+    for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x) w[p] = exp_f32(__fsub_rn(w[p], mx));
     __syncthreads();
-
-    // Weighted sum of V: thread groups of head_dim lanes split the positions.
-    const uint32_t groups = blockDim.x / head_dim > 0 ? blockDim.x / head_dim : 1;
-    if (head_dim <= blockDim.x) {
-        const uint32_t grp = threadIdx.x / head_dim, d = threadIdx.x % head_dim;
-        if (grp < groups) {
-            float acc = 0.0f;
-            for (uint32_t p = grp; p < kv_len; p += groups)
-                acc = fmaf(scores[p], vc[(size_t)(kv_start + p) * kv_dim + (size_t)kvh * head_dim + d], acc);
-            part[grp * head_dim + d] = acc;
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+        uint32_t p = 0;
+        for (; p + 8 <= kv_len; p += 8) {
+            const float4 a = *reinterpret_cast<const float4*>(w + p);
+            const float4 b = *reinterpret_cast<const float4*>(w + p + 4);
+            s = __fadd_rn(s, a.x); s = __fadd_rn(s, a.y); s = __fadd_rn(s, a.z); s = __fadd_rn(s, a.w);
+            s = __fadd_rn(s, b.x); s = __fadd_rn(s, b.y); s = __fadd_rn(s, b.z); s = __fadd_rn(s, b.w);
         }
-        __syncthreads();
-        if (threadIdx.x < head_dim) {
-            float acc = 0.0f;
-            for (uint32_t g2 = 0; g2 < groups; ++g2) acc += part[g2 * head_dim + threadIdx.x];
-            out[(size_t)h * head_dim + threadIdx.x] = acc;
+        for (; p < kv_len; ++p) s = __fadd_rn(s, w[p]);
+        bc = s;
+    }
+    __syncthreads();
+    const float sum = bc;
+    const float inv = __fdiv_rn(1.0f, sum);
+    const uint32_t vec_end = gpt2_tail ? (kv_len & ~15u) : kv_len;
+    for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x)
+        w[p] = p < vec_end ? __fmul_rn(w[p], inv) : __fdiv_rn(w[p], sum);
+    __syncthreads();
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        const float* vp = vc + (size_t)kv_start * kv_dim + (size_t)kvh * head_dim + d;
+        float acc = 0.0f;
+        uint32_t p = 0;
+        for (; p + 8 <= kv_len; p += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = vp[(size_t)(p + j) * kv_dim];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, __fmul_rn(w[p + j], v[j]));
         }
-    } else {
-        for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
-            float acc = 0.0f;
-            for (uint32_t p = 0; p < kv_len; ++p)
-                acc = fmaf(scores[p], vc[(size_t)(kv_start + p) * kv_dim + (size_t)kvh * head_dim + d], acc);
-            out[(size_t)h * head_dim + d] = acc;
-        }
+        for (; p < kv_len; ++p) acc = __fadd_rn(acc, __fmul_rn(w[p], vp[(size_t)p * kv_dim]));
+        out[(size_t)h * head_dim + d] = acc;
     }
 }
 
@@ -258,7 +323,8 @@ int zq_rms_norm(const float* d_x, const float* d_w, float* d_out, uint32_t dim, 
                 float eps, zq_stream stream) {
     if (!d_x || !d_w || !d_out || dim == 0) return ZQ_ERR_BAD_ARG;
     if (rows == 0) return ZQ_OK;
-    rms_norm_kernel<<<rows, 256, 0, as_stream(stream)>>>(d_x, d_w, d_out, dim, eps, 0);
+    if (dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
+    rms_norm_kernel<<<rows, 256, dim * sizeof(float), as_stream(stream)>>>(d_x, d_w, d_out, dim, eps, 0);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -267,7 +333,8 @@ int zq_rms_norm_residual(const float* d_x, const float* d_w, float* d_residual, 
                          uint32_t rows, float eps, zq_stream stream) {
     if (!d_x || !d_w || !d_residual || dim == 0) return ZQ_ERR_BAD_ARG;
     if (rows == 0) return ZQ_OK;
-    rms_norm_kernel<<<rows, 256, 0, as_stream(stream)>>>(d_x, d_w, d_residual, dim, eps, 1);
+    if (dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
+    rms_norm_kernel<<<rows, 256, dim * sizeof(float), as_stream(stream)>>>(d_x, d_w, d_residual, dim, eps, 1);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -276,8 +343,8 @@ int zq_rms_norm_in_place(float* d_x, const float* d_w, uint32_t dim, uint32_t n_
                          zq_stream stream) {
     if (!d_x || !d_w || dim == 0) return ZQ_ERR_BAD_ARG;
     if (n_vec == 0) return ZQ_OK;
-    rms_norm_vec_kernel<<<grid1d((size_t)n_vec * 32, 128), 128, 0, as_stream(stream)>>>(d_x, d_w, dim,
-                                                                                       n_vec, eps);
+    if (dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
+    rms_norm_vec_kernel<<<n_vec, 64, dim * sizeof(float), as_stream(stream)>>>(d_x, d_w, dim, eps);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -319,21 +386,21 @@ int zq_write_kv_cache(const float* d_k, const float* d_v, float* d_k_cache, floa
 }
 
 int zq_attention_decode(const float* d_q, const float* d_k_cache, const float* d_v_cache,
-                        float* d_out, uint32_t n_head, uint32_t n_kv_head, uint32_t head_dim,
-                        uint32_t kv_start, uint32_t kv_end, zq_stream stream) {
-    if (!d_q || !d_k_cache || !d_v_cache || !d_out) return ZQ_ERR_BAD_ARG;
+                        float* d_out, float* d_scores, uint32_t n_head, uint32_t n_kv_head,
+                        uint32_t head_dim, uint32_t kv_start, uint32_t kv_end, int flags,
+                        zq_stream stream) {
+    if (!d_q || !d_k_cache || !d_v_cache || !d_out || !d_scores) return ZQ_ERR_BAD_ARG;
     if (n_head == 0 || n_kv_head == 0 || head_dim == 0 || n_head % n_kv_head) return ZQ_ERR_BAD_ARG;
     if (kv_end <= kv_start) return ZQ_ERR_BAD_ARG;
     const uint32_t kv_len = kv_end - kv_start;
-    const unsigned threads = 256;
-    const uint32_t groups = threads / head_dim > 0 ? threads / head_dim : 1;
-    const size_t smem = ((size_t)kv_len + (size_t)groups * head_dim) * sizeof(float);
-    if (smem > 200 * 1024) return ZQ_ERR_LIMIT;
-    if (smem > 48 * 1024)
-        ZQ_CUDA(cudaFuncSetAttribute(attention_decode_kernel,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attention_decode_kernel<<<n_head, threads, smem, as_stream(stream)>>>(
-        d_q, d_k_cache, d_v_cache, d_out, n_head, n_kv_head, head_dim, kv_start, kv_end);
+    if (kv_len > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
+    cudaStream_t st = as_stream(stream);
+    attention_scores_kernel<<<dim3((kv_len + 15) / 16, n_head), 256, 0, st>>>(
+        d_q, d_k_cache, d_scores, n_head, n_kv_head, head_dim, kv_start, kv_end);
+    ZQ_LAUNCH_CHECK();
+    attention_softmax_v_kernel<<<n_head, 256, kv_len * sizeof(float), st>>>(
+        d_scores, d_v_cache, d_out, n_head, n_kv_head, head_dim, kv_start, kv_end,
+        (flags & ZQ_ATTN_GPT2_SOFTMAX) ? 1 : 0);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
