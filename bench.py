@@ -203,31 +203,56 @@ def time_region(torch, fn, steps, sync):
     return e0.elapsed_time(e1)
 
 
-def sweep_extra(torch, zq, ggml, steps=50):
-    """configs[1] M=1 shapes x types, HBM-cold: weights rotate through > L2-size distinct copies."""
+def graph_time_us(torch, fns, reps=20):
+    """Average device time of one call: the calls are captured once into a CUDA graph (so host launch
+    overhead is out of the picture) and the graph is replayed `reps` times."""
+    for f in fns:
+        f()  # outside capture first: one-time function attributes are set here
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in fns:
+            f()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * len(fns))
+
+
+def sweep_extra(torch, zq, ggml, m_list=(1,)):
+    """configs[1] shapes x types, HBM-cold: each timed call uses a different weight copy and the copies
+    together exceed L2 (126 MB). Times are per call inside a CUDA graph."""
     out = []
     shapes = [(768, 2304), (768, 3072), (3072, 768), (1152, 6912), (6912, 1152), (1152, 262144)]
     for qname in ("q4_0", "q4_1", "q8_0"):
         for k, n in shapes:
-            nbytes = algorithmic_bytes(qname, n, k)
-            copies = max(1, min(64, int(320e6 // nbytes) + 1))
             raw = make_weight_bytes(qname, n, k, 42, "cuda")
+            wbytes = n * (k // 32) * BPB[qname]
+            copies = max(2, min(48, int(400e6 // wbytes) + 1))
             ws = [zq.QuantWeight(raw, ggml.TYPE_IDS[qname], n, k) for _ in range(copies)]
-            x = torch.randn(1, k, device="cuda")
-            y = torch.empty(1, n, device="cuda")
-            for mode, mname in ((zq.ACT_F32, "f32"), (zq.ACT_Q8, "q8")):
-                i = [0]
-
-                def fn():
-                    zq.quant_matmul_no_grad(x, ws[i[0] % copies], mode, out=y)
-                    i[0] += 1
-                for _ in range(5):
-                    fn()
-                ms = time_region(torch, fn, steps, torch.cuda.synchronize) / steps
-                out.append({"type": qname, "k": k, "n": n, "act": mname, "us": round(ms * 1e3, 2),
-                            "gbs": round(nbytes / ms / 1e6, 1), "copies": copies})
+            for m in m_list:
+                nbytes = algorithmic_bytes(qname, n, k, m)
+                x = torch.randn(m, k, device="cuda")
+                y = torch.empty(m, n, device="cuda")
+                for mode, mname in ((zq.ACT_F32, "f32"), (zq.ACT_Q8, "q8")):
+                    need = _lib_ws(zq, ws[0], m, mode)
+                    wsb = torch.empty(max(need, 256), dtype=torch.uint8, device="cuda")
+                    fns = [(lambda w=w: zq.quant_matmul_no_grad(x, w, mode, out=y, workspace=wsb)) for w in ws]
+                    us = graph_time_us(torch, fns)
+                    out.append({"type": qname, "k": k, "n": n, "m": m, "act": mname, "us": round(us, 2),
+                                "gbs": round(nbytes / us / 1e3, 1), "copies": copies})
             del ws, raw
     return out
+
+
+def _lib_ws(zq, w, m, mode):
+    from zignn_b200 import _lib
+    return _lib.load().zq_matmul_workspace_bytes(w.handle, m, mode)
 
 
 def main():
@@ -327,7 +352,7 @@ def main():
                            sharding="rows split over %d rank(s)%s" % (world, ", NCCL all-gather of outputs" if use_dist else "")),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES, "peak_kind": peak_kind,
-                         "algorithmic_bytes_per_launch": local_bytes, "kernel": "gemv_f32_kernel<q4_0>"},
+                         "algorithmic_bytes_per_launch": local_bytes, "kernel": "gemv_mma_kernel<q4_0>"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k, "d2h_bytes_per_step": 4 * n_local},
             "gpu_launches": args.steps,
             "clocks": clocks,
@@ -339,7 +364,7 @@ def main():
                 line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": host_threads(), "kind": "port",
                                         "sample": "failed: %r" % (e,)}
             try:
-                line["extra"] = {"sweep_m1_hbm_cold": sweep_extra(torch, zq, ggml)}
+                line["extra"] = {"sweep_hbm_cold": sweep_extra(torch, zq, ggml, m_list=(1, 4, 16))}
             except Exception as e:
                 line["extra"] = {"error": repr(e)}
         print(json.dumps(line), flush=True)

@@ -616,7 +616,23 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
     if (m_rows == 0) return ZQ_OK;
     if (!d_x || !d_y) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
-    if (act_mode == ZQ_ACT_F32) return launch_gemv_f32(w, d_x, d_y, m_rows, epilogue, st);
+    if (act_mode == ZQ_ACT_F32) {
+        if (((uintptr_t)d_x & 15) != 0) return launch_gemv_f32(w, d_x, d_y, m_rows, epilogue, st);
+        // up to 16 activation rows per pass over the weights
+        for (uint32_t m0 = 0; m0 < m_rows; m0 += 16) {
+            const uint32_t mc = m_rows - m0 < 16 ? m_rows - m0 : 16;
+            zq_epilogue ep{nullptr, 0, nullptr, nullptr};
+            if (epilogue) {
+                ep = *epilogue;
+                if (ep.d_mul) ep.d_mul += (size_t)m0 * w->out_dim;
+                if (ep.d_residual) ep.d_residual += (size_t)m0 * w->out_dim;
+            }
+            int rc = launch_gemv_mma_f32(w, d_x + (size_t)m0 * w->in_dim, d_y + (size_t)m0 * w->out_dim, mc,
+                                         epilogue ? &ep : nullptr, st);
+            if (rc != ZQ_OK) return rc;
+        }
+        return ZQ_OK;
+    }
     if (act_mode == ZQ_ACT_Q8) {
         if (w->in_dim > 16384) return ZQ_ERR_LIMIT;
         const size_t need = zq_matmul_workspace_bytes(w, m_rows, act_mode);

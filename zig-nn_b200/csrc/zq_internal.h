@@ -55,6 +55,9 @@ enum Prologue { PRO_NONE = 0 };
 
 int launch_gemv_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
                     const zq_epilogue* ep, cudaStream_t st);
+// Tensor-core f32-activation GEMV for m_rows <= 16 (gemv_mma.cu); x must be 16-byte aligned.
+int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
+                        const zq_epilogue* ep, cudaStream_t st);
 int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum,
                    float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
 int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, int8_t* q,
