@@ -48,6 +48,10 @@ const char* zq_status_string(int status);
 int zq_last_cuda_error(void);
 /* ABI version of this header; bumped on incompatible change. */
 int zq_abi_version(void);
+/* Device-side waits (on async-copy barriers) are bounded; a wait that ran out sets a flag in device
+ * memory instead of hanging. *out receives the flag (0 = never happened); clear != 0 resets it.
+ * Synchronises the device. */
+int zq_device_error(unsigned int* out, int clear);
 
 /* GGML tensor type ids — src/gguf/dequant.zig:9-20. */
 typedef enum zq_type {

@@ -24,6 +24,7 @@ SIGNATURES = {
     "zq_status_string": (C.c_char_p, [i]),
     "zq_last_cuda_error": (i, []),
     "zq_abi_version": (i, []),
+    "zq_device_error": (i, [P(u32), i]),
     "zq_block_size": (sz, [i]),
     "zq_bytes_per_block": (sz, [i]),
     "zq_tensor_bytes": (sz, [i, sz]),

@@ -112,7 +112,11 @@ struct zq_gpt2 {
 static int gpt2_linear(const Linear& L, const float* x, float* y, const float* bias, int gelu,
                        const float* residual, cudaStream_t st) {
     zq_epilogue ep{bias, gelu, nullptr, residual};
-    if (L.qw) return launch_gemv_mma_f32(L.qw, x, y, 1, &ep, st);
+    if (L.qw) {
+        int rc = launch_gemv_mma_f32(L.qw, x, y, 1, &ep, st);
+        if (rc == ZQ_ERR_LIMIT) rc = launch_gemv_f32(L.qw, x, y, 1, &ep, st);
+        return rc;
+    }
     // f32 weight: matvec, then the same epilogue as separate launches
     int rc = zq_matvec_f32(L.f32w, x, y, L.out_dim, L.in_dim, st);
     if (rc == ZQ_OK && bias) rc = zq_add_broadcast(y, y, bias, L.out_dim, L.out_dim, st);

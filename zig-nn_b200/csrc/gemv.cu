@@ -125,7 +125,7 @@ template <int TYPE, int G, int R>
 __global__ void __launch_bounds__(kThreads)
 gemv_f32_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
                 const float* __restrict__ x, float* __restrict__ y, uint32_t N, uint32_t nb,
-                EpilogueArgs ep) {
+                uint32_t scp, EpilogueArgs ep) {
     extern __shared__ __align__(16) float smem[];
     float* xs = smem;               // nb * XPAD
     float* xsum = smem + (size_t)nb * XPAD;  // nb (q4_1 only)
@@ -156,23 +156,32 @@ gemv_f32_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
         for (int r = 0; r < R; ++r) {
             sum[r] = 0.0f;
             const uint32_t row = min(row0 + r, N - 1);  // clamp: out-of-range rows are never stored
-            qrow[r] = qs + (size_t)row * nb * QB;
+            qrow[r] = qs + (size_t)row * ((nb + 3u) & ~3u) * QB;
         }
         for (uint32_t b = g; b < nb; b += G) {
             uint4 q[R][QB / 16];
             float d[R], mn[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const uint4* p = reinterpret_cast<const uint4*>(qrow[r] + (size_t)b * QB);
-                q[r][0] = __ldg(p);
-                if (QB == 32) q[r][QB / 16 - 1] = __ldg(p + 1);
+                // the block's words are interleaved with its three quad neighbours: gather them
+                const uint8_t* p = qrow[r];
+                q[r][0] = make_uint4(__ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, 0))),
+                                     __ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, 1))),
+                                     __ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, 2))),
+                                     __ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, 3))));
+                if (QB == 32)
+                    q[r][QB / 16 - 1] =
+                        make_uint4(__ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, 4))),
+                                   __ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, 5))),
+                                   __ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, 6))),
+                                   __ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, 7))));
                 const uint32_t row = min(row0 + r, N - 1);
                 if (TYPE == ZQ_TYPE_Q4_1) {
-                    const __half2 dm = __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row * nb + b);
+                    const __half2 dm = __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row * scp + b);
                     d[r] = __low2float(dm);
                     mn[r] = __high2float(dm);
                 } else {
-                    d[r] = __half2float(__ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * nb + b));
+                    d[r] = __half2float(__ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * scp + b));
                     mn[r] = 0.0f;
                 }
             }
@@ -227,7 +236,7 @@ __global__ void __launch_bounds__(kThreads)
 gemv_q8_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
                const int8_t* __restrict__ xq, const float* __restrict__ xscale,
                const int32_t* __restrict__ xqsum, float* __restrict__ y, uint32_t N, uint32_t nb,
-               EpilogueArgs ep) {
+               uint32_t scp, EpilogueArgs ep) {
     constexpr int GROUPS = 32 / G;
     constexpr int ROWS_W = GROUPS * R;
     static_assert(ROWS_W <= 32, "one lane per row in the ordered-sum phase");
@@ -272,22 +281,22 @@ gemv_q8_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const uint32_t row = min(row0 + r, N - 1);
-                    const uint4* p =
-                        reinterpret_cast<const uint4*>(qs + ((size_t)row * nb + b) * QB);
+                    const uint8_t* p = qs + (size_t)row * ((nb + 3u) & ~3u) * QB;
+                    auto word = [&](uint32_t w) {
+                        return __ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, w)));
+                    };
                     float term;
                     if (TYPE == ZQ_TYPE_Q8_0) {
-                        const uint4 q0 = __ldg(p), q1 = __ldg(p + 1);
-                        const int w[8] = {(int)q0.x, (int)q0.y, (int)q0.z, (int)q0.w,
-                                          (int)q1.x, (int)q1.y, (int)q1.z, (int)q1.w};
+                        const int w[8] = {(int)word(0), (int)word(1), (int)word(2), (int)word(3),
+                                          (int)word(4), (int)word(5), (int)word(6), (int)word(7)};
                         int idot = 0;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) idot = __dp4a(w[i], xw[i], idot);
                         const float d = __half2float(
-                            __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * nb + b));
+                            __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * scp + b));
                         term = __fmul_rn(__fmul_rn(d, s), (float)idot);
                     } else {
-                        const uint4 q0 = __ldg(p);
-                        const uint32_t w[4] = {q0.x, q0.y, q0.z, q0.w};
+                        const uint32_t w[4] = {word(0), word(1), word(2), word(3)};
                         int idot = 0;
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -297,11 +306,11 @@ gemv_q8_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
                         if (TYPE == ZQ_TYPE_Q4_0) {
                             idot -= 8 * qsum;  // sum((n-8)*q) = sum(n*q) - 8*sum(q), exact
                             const float d = __half2float(
-                                __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * nb + b));
+                                __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * scp + b));
                             term = __fmul_rn(__fmul_rn(d, s), (float)idot);
                         } else {
                             const __half2 dm =
-                                __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row * nb + b);
+                                __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row * scp + b);
                             const float t1 = __fmul_rn(__fmul_rn(__low2float(dm), s), (float)idot);
                             const float t2 = __fmul_rn(__fmul_rn(__high2float(dm), s), (float)qsum);
                             term = __fadd_rn(t1, t2);
@@ -480,7 +489,7 @@ int launch_f32_one(const zq_weight* w, const float* x, float* y, EpilogueArgs ep
     const uint64_t tiles = ((uint64_t)w->out_dim + rows_per_cta - 1) / rows_per_cta;
     const uint64_t cap = (uint64_t)sm_count() * 8;
     const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
-    gemv_f32_kernel<TYPE, G, R><<<grid, kThreads, smem, st>>>(w->qs, w->sc, x, y, w->out_dim, w->nb, ep);
+    gemv_f32_kernel<TYPE, G, R><<<grid, kThreads, smem, st>>>(w->qs, w->sc, x, y, w->out_dim, w->nb, w->scp, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -517,7 +526,7 @@ int launch_q8_one(const zq_weight* w, const int8_t* xq, const float* xs, const i
     const uint64_t cap = (uint64_t)sm_count() * 8;
     const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
     gemv_q8_kernel<TYPE, G, R><<<grid, kThreads, smem, st>>>(w->qs, w->sc, xq, xs, xsum, y,
-                                                             w->out_dim, w->nb, ep);
+                                                             w->out_dim, w->nb, w->scp, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -629,6 +638,9 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
             }
             int rc = launch_gemv_mma_f32(w, d_x + (size_t)m0 * w->in_dim, d_y + (size_t)m0 * w->out_dim, mc,
                                          epilogue ? &ep : nullptr, st);
+            if (rc == ZQ_ERR_LIMIT)  // activation image too large for shared memory: row-at-a-time kernel
+                rc = launch_gemv_f32(w, d_x + (size_t)m0 * w->in_dim, d_y + (size_t)m0 * w->out_dim, mc,
+                                     epilogue ? &ep : nullptr, st);
             if (rc != ZQ_OK) return rc;
         }
         return ZQ_OK;

@@ -1,7 +1,6 @@
 // f32-activation decode GEMV on the tensor cores (m_rows <= 16).
 //
-// The CUDA-core kernel in gemv.cu spends about four instructions per weight on turning nibbles
-// into floats, which caps it near 40 % of HBM bandwidth. Here the integer weights (n-8, n, or the
+// The integer weights (n-8, n, or the
 // int8 value — all exact in fp16) go into mma.sync.m16n8k16 A fragments with two instructions per
 // pair, and each f32 activation x is split into fp16 parts hi = fp16(x), lo = fp16(x - hi) that sit
 // in two B columns. Products are exact, accumulation is f32, and hi + lo carries 22 bits of x, so
@@ -12,11 +11,13 @@
 // into a fresh accumulator, then adds accumulator * d[row][block] into the running sums: the
 // per-block scale is applied in f32, as the reference does.
 //
-// Fragment ownership (g = lane / 4, t = lane % 4): the thread loads quant word t of the block for
+// Fragment ownership (g = lane / 4, t = lane % 4): the thread needs quant word t of every block of
 // rows g and g + 8. Word t holds elements 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles),
 // which is exactly the K footprint an m16n8k16 A fragment wants from lane (g, t), so no data moves
-// between lanes. K slots are assigned as (2t, 2t+1, 2t+8, 2t+9) <- elements (4t, 4t+2, 4t+1, 4t+3);
-// the activation fragments in shared memory are laid out with the same permutation.
+// between lanes. The device layout interleaves each group of 4 blocks so that those words are 16
+// contiguous bytes: one 128-bit load per row brings the thread's share of 4 blocks, and the 4 lanes
+// of a quad read 64 contiguous bytes. K slots are assigned as (2t, 2t+1, 2t+8, 2t+9) <- elements
+// (4t, 4t+2, 4t+1, 4t+3); the activation fragments in shared memory use the same permutation.
 #include "zq_internal.h"
 
 namespace zq {
@@ -96,23 +97,27 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Shared-memory image of the activations for one K chunk:
-//   frag[block][set][lane][4 x u32]: B fragments {MMA-low b0, b1, MMA-high b0, b1} of lane (g, t) for
-//     column g of the set = activation row 4*set + g/2, part g%2 (0 = hi, 1 = lo);
-//   xsum[block][16]: f32 sum of each activation row's 32 values (q4_1 only).
-// `pre` holds the per-row power-of-two prescale that keeps |x| inside fp16 range.
+// Shared-memory image of the activations, built once per CTA:
+//   frag[block][col][t] (uint4): B registers {low-MMA b0, b1, high-MMA b0, b1} that lane (g, t) feeds
+//     for MMA column `col` = 2 * activation row + part (0 = hi, 1 = lo); only the 2*M real columns
+//     are stored (lanes of the other columns feed zeros); blocks >= nb (row padding) are zero;
+//   xsum[block][M]: f32 sum of each activation row's 32 values (q4_1 only).
+// `pre[m]` is a power-of-two prescale that keeps |x| inside fp16 range (undone in the epilogue).
 template <bool WITH_SUM>
-__device__ void stage_activations(const float* __restrict__ x, uint32_t M, uint32_t K, uint32_t blk0,
-                                  uint32_t nblk, int ns, const float* pre, uint4* frag, float* xsum) {
-    const uint32_t total = nblk * (uint32_t)ns * 32u;
-    for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
-        const uint32_t lane = i & 31u, set = (i >> 5) % (uint32_t)ns, blk = (i >> 5) / (uint32_t)ns;
-        const uint32_t g = lane >> 2, t = lane & 3u;
-        const uint32_t m = 4u * set + (g >> 1);
-        const bool lo_part = g & 1u;
+__device__ void stage_activations(const float* __restrict__ x, uint32_t M, uint32_t K, uint32_t nb,
+                                  uint32_t nbp, const float* pre, uint4* frag, float* xsum) {
+    const uint32_t ncols = 2 * M;
+    const uint32_t total = nbp * ncols * 4;
+    const uint32_t total_up = (total + 31u) & ~31u;  // whole warps run the shuffles below
+    for (uint32_t i = threadIdx.x; i < total_up; i += blockDim.x) {
+        const bool active = i < total;
+        const uint32_t ii = active ? i : 0;
+        const uint32_t t = ii & 3u, col = (ii >> 2) % ncols, blk = (ii >> 2) / ncols;
+        const uint32_t m = col >> 1;
+        const bool lo_part = col & 1u;
         float v[8];
-        if (m < M) {
-            const float* p = x + (size_t)m * K + (size_t)(blk0 + blk) * 32u;
+        if (blk < nb) {
+            const float* p = x + (size_t)m * K + (size_t)blk * 32u;
             const float4 a = *reinterpret_cast<const float4*>(p + 4u * t);
             const float4 b = *reinterpret_cast<const float4*>(p + 16u + 4u * t);
             const float s = pre[m];
@@ -123,11 +128,10 @@ __device__ void stage_activations(const float* __restrict__ x, uint32_t M, uint3
             for (int j = 0; j < 8; ++j) v[j] = 0.0f;
         }
         if (WITH_SUM) {
-            // every lane of the quad (same g) adds its 8 values; lanes with g even publish the row sum
             float s8 = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
             s8 += __shfl_xor_sync(0xFFFFFFFFu, s8, 1);
             s8 += __shfl_xor_sync(0xFFFFFFFFu, s8, 2);
-            if (!lo_part && t == 0 && m < 16) xsum[blk * 16u + m] = s8;
+            if (active && !lo_part && t == 0) xsum[blk * M + m] = s8;
         }
         float w[8];
 #pragma unroll
@@ -135,234 +139,277 @@ __device__ void stage_activations(const float* __restrict__ x, uint32_t M, uint3
             const float hi = __half2float(__float2half_rn(v[j]));
             w[j] = lo_part ? (v[j] - hi) : hi;  // x - hi is exact in f32
         }
-        uint4 out;
-        out.x = pack_half2(w[0], w[2]);
-        out.y = pack_half2(w[1], w[3]);
-        out.z = pack_half2(w[4], w[6]);
-        out.w = pack_half2(w[5], w[7]);
-        frag[i] = out;
+        if (active)
+            frag[i] = make_uint4(pack_half2(w[0], w[2]), pack_half2(w[1], w[3]), pack_half2(w[4], w[6]),
+                                 pack_half2(w[5], w[7]));
     }
 }
 
-// Grid-stride over tiles of 16 rows x WR warps; the KS warps that share a row tile split the blocks
-// of each K chunk and are summed in a fixed order through shared memory.
-template <int TYPE, int NS, int U>
-__global__ void __launch_bounds__(256, NS == 1 ? 4 : 2)
-gemv_mma_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc, const float* __restrict__ x,
-                float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t M, uint32_t kc,
+// The quant words and scales one lane needs for one quad (4 blocks) of rows g and g + 8.
+template <bool Q8, bool Q41>
+struct QuadRegs {
+    uint4 a_lo, b_lo;  // word t of blocks 0..3, rows g / g+8
+    uint4 a_hi, b_hi;  // q8_0 only: word 4+t
+    uint4 sa, sb;      // scales: q4_0/q8_0 use .x,.y (4 x f16); q4_1 all four (4 x (d, m))
+};
+
+template <bool Q8, bool Q41>
+__device__ __forceinline__ void load_quad(QuadRegs<Q8, Q41>& r, const uint8_t* qa, const uint8_t* qb,
+                                          const uint8_t* sa, const uint8_t* sb, uint32_t q) {
+    constexpr uint32_t QUAD = Q8 ? 128 : 64;
+    r.a_lo = __ldg(reinterpret_cast<const uint4*>(qa + (size_t)q * QUAD));
+    r.b_lo = __ldg(reinterpret_cast<const uint4*>(qb + (size_t)q * QUAD));
+    if (Q8) {
+        r.a_hi = __ldg(reinterpret_cast<const uint4*>(qa + (size_t)q * QUAD + 64));
+        r.b_hi = __ldg(reinterpret_cast<const uint4*>(qb + (size_t)q * QUAD + 64));
+    }
+    if (Q41) {
+        r.sa = __ldg(reinterpret_cast<const uint4*>(sa + (size_t)q * 16));
+        r.sb = __ldg(reinterpret_cast<const uint4*>(sb + (size_t)q * 16));
+    } else {
+        const uint2 va = __ldg(reinterpret_cast<const uint2*>(sa + (size_t)q * 8));
+        const uint2 vb = __ldg(reinterpret_cast<const uint2*>(sb + (size_t)q * 8));
+        r.sa.x = va.x; r.sa.y = va.y;
+        r.sb.x = vb.x; r.sb.y = vb.y;
+    }
+}
+
+__device__ __forceinline__ uint32_t pick(const uint4& v, int j) {
+    return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
+}
+__device__ __forceinline__ float half_lo(uint32_t v) {
+    return __half2float(__ushort_as_half((unsigned short)(v & 0xFFFFu)));
+}
+__device__ __forceinline__ float half_hi(uint32_t v) {
+    return __half2float(__ushort_as_half((unsigned short)(v >> 16)));
+}
+
+// One quad (4 blocks) of rows g and g + 8 against every activation column set.
+template <int TYPE, int NS>
+__device__ __forceinline__ void compute_quad(const QuadRegs<TYPE == ZQ_TYPE_Q8_0, TYPE == ZQ_TYPE_Q4_1>& r,
+                                             uint32_t q, const uint4* __restrict__ frag,
+                                             const float* __restrict__ xsum, uint32_t ncols, uint32_t M, int g,
+                                             int t, float (&acc)[NS][4], float (&accm)[NS][2]) {
+    constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
+    constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
+    const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t a_lo[4], a_hi[4];
+        float da, db, ma = 0.0f, mb = 0.0f;
+        if (Q8) {
+            unpack_q8(pick(r.a_lo, j), a_lo[0], a_lo[2]);
+            unpack_q8(pick(r.b_lo, j), a_lo[1], a_lo[3]);
+            unpack_q8(pick(r.a_hi, j), a_hi[0], a_hi[2]);
+            unpack_q8(pick(r.b_hi, j), a_hi[1], a_hi[3]);
+        } else {
+            unpack_q4<Q41 ? 0 : 8>(pick(r.a_lo, j), a_lo[0], a_lo[2], a_hi[0], a_hi[2]);
+            unpack_q4<Q41 ? 0 : 8>(pick(r.b_lo, j), a_lo[1], a_lo[3], a_hi[1], a_hi[3]);
+        }
+        if (Q41) {
+            da = half_lo(pick(r.sa, j));
+            ma = half_hi(pick(r.sa, j));
+            db = half_lo(pick(r.sb, j));
+            mb = half_hi(pick(r.sb, j));
+        } else {
+            const uint32_t wa = j < 2 ? r.sa.x : r.sa.y, wb = j < 2 ? r.sb.x : r.sb.y;
+            da = (j & 1) ? half_hi(wa) : half_lo(wa);
+            db = (j & 1) ? half_hi(wb) : half_lo(wb);
+        }
+        const uint32_t blk = q * 4 + j;
+#pragma unroll
+        for (int c = 0; c < NS; ++c) {
+            const uint32_t col = 8 * c + g;
+            uint4 bf = make_uint4(0, 0, 0, 0);
+            if (col < ncols) bf = frag[((size_t)blk * ncols + col) * 4 + t];
+            float d1[4], d2[4];
+            mma_f16(d1, a_lo, bf.x, bf.y, zero);
+            mma_f16(d2, a_hi, bf.z, bf.w, d1);
+            acc[c][0] = fmaf(d2[0], da, acc[c][0]);
+            acc[c][1] = fmaf(d2[1], da, acc[c][1]);
+            acc[c][2] = fmaf(d2[2], db, acc[c][2]);
+            acc[c][3] = fmaf(d2[3], db, acc[c][3]);
+            if (Q41) {
+                const uint32_t m = 4 * c + t;
+                const float xs_m = m < M ? xsum[blk * M + m] : 0.0f;
+                accm[c][0] = fmaf(ma, xs_m, accm[c][0]);
+                accm[c][1] = fmaf(mb, xs_m, accm[c][1]);
+            }
+        }
+    }
+}
+
+// Grid-stride over tiles of 16 rows x WR warps; the KS warps that share a row tile split the quads
+// of a row and are summed in a fixed order through shared memory.
+template <int TYPE, int NS>
+__global__ void __launch_bounds__(256, NS == 1 ? 3 : 2)
+gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const float* __restrict__ x,
+                float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t scp, uint32_t M,
                 uint32_t WR, uint32_t KS, EpilogueArgs ep) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
-    constexpr int QB = Q8 ? 32 : 16;
+    constexpr uint32_t QB = Q8 ? 32 : 16;
+    constexpr uint32_t SB = Q41 ? 4 : 2;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint4* frag = reinterpret_cast<uint4*>(smem_raw);                       // kc * NS * 32
-    float* xsum = reinterpret_cast<float*>(frag + (size_t)kc * NS * 32);    // kc * 16 (q4_1)
-    float* red = xsum + (Q41 ? (size_t)kc * 16 : 0);                        // KS>1: WR*KS*NS*4*32 (+Q41 *2*32)
     __shared__ float pre[16], post[16];
+    __shared__ unsigned int amax_bits[16];
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t nbp = (nb + 3u) & ~3u, ncols = 2 * M;
+    uint4* frag = reinterpret_cast<uint4*>(smem_raw);
+    float* xsum = reinterpret_cast<float*>(frag + (size_t)nbp * ncols * 4);
+    float* red = xsum + (Q41 ? (size_t)nbp * M : 0);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t wr = warp % WR, ks = warp / WR;
 
-    // per activation row: power-of-two prescale so that |x| * pre < 2^15 (fp16 range), undone at the end
-    for (uint32_t m = warp; m < M; m += blockDim.x >> 5) {
+    // ---- activations: range prescale, then the fp16 hi/lo fragment image ----
+    if (tid < 16) amax_bits[tid] = 0;
+    __syncthreads();
+    for (uint32_t m = 0; m < M; ++m) {
         float amax = 0.0f;
-        for (uint32_t i = lane; i < K; i += 32) amax = fmaxf(amax, fabsf(x[(size_t)m * K + i]));
+        const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
+        for (uint32_t i = tid; i < K / 4; i += blockDim.x) {
+            const float4 v = xr[i];
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-        if (lane == 0) {
-            int e = 0;
-            if (amax >= 32768.0f && amax < INFINITY) e = ilogbf(amax) - 14;
-            pre[m] = ldexpf(1.0f, -e);
-            post[m] = ldexpf(1.0f, e);
-        }
+        if (lane == 0) atomicMax(&amax_bits[m], __float_as_uint(amax));  // non-negative floats order as ints
     }
     __syncthreads();
+    if (tid < (int)M) {
+        const float amax = __uint_as_float(amax_bits[tid]);
+        int e = 0;
+        if (amax >= 32768.0f && amax < INFINITY) e = ilogbf(amax) - 14;
+        pre[tid] = ldexpf(1.0f, -e);
+        post[tid] = ldexpf(1.0f, e);
+    }
+    __syncthreads();
+    stage_activations<Q41>(x, M, K, nb, nbp, pre, frag, xsum);
+    __syncthreads();
 
-    const uint32_t n_chunks = (nb + kc - 1) / kc;
+    const uint32_t nq = nbp / 4;
+    const uint32_t per = (nq + KS - 1) / KS;
+    const uint32_t q_lo = min(ks * per, nq), q_hi = min(q_lo + per, nq);
     const uint32_t rows_per_cta = WR * 16;
-    bool staged = false;
 
     for (uint64_t tile = blockIdx.x; tile * rows_per_cta < N; tile += gridDim.x) {
-        const uint32_t row_a = min((uint32_t)(tile * rows_per_cta) + wr * 16 + g, N - 1);
-        const uint32_t row_b = min((uint32_t)(tile * rows_per_cta) + wr * 16 + g + 8, N - 1);
-        const uint8_t* qa = qs + (size_t)row_a * nb * QB + 4 * t;
-        const uint8_t* qb = qs + (size_t)row_b * nb * QB + 4 * t;
-        float acc[NS][4];
-        float accm[NS][2];
+        const uint32_t r0 = (uint32_t)(tile * rows_per_cta) + wr * 16 + g;
+        const uint32_t row_a = min(r0, N - 1), row_b = min(r0 + 8, N - 1);
+        const uint8_t* qa = qs + (size_t)row_a * nbp * QB + 16 * t;
+        const uint8_t* qb = qs + (size_t)row_b * nbp * QB + 16 * t;
+        const uint8_t* sa = sc + (size_t)row_a * scp * SB;
+        const uint8_t* sb = sc + (size_t)row_b * scp * SB;
+        float acc[NS][4], accm[NS][2];
 #pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.0f;
-            accm[s][0] = accm[s][1] = 0.0f;
+        for (int c = 0; c < NS; ++c) {
+            acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.0f;
+            accm[c][0] = accm[c][1] = 0.0f;
         }
-
-        for (uint32_t c = 0; c < n_chunks; ++c) {
-            const uint32_t c0 = c * kc, cn = min(kc, nb - c0);
-            if (n_chunks > 1 || !staged) {
-                if (n_chunks > 1) __syncthreads();  // everyone is done with the previous chunk
-                stage_activations<Q41>(x, M, K, c0, cn, NS, pre, frag, xsum);
-                __syncthreads();
-                staged = true;
-            }
-            // this warp's share of the chunk
-            const uint32_t per = (cn + KS - 1) / KS;
-            const uint32_t b_lo = min(ks * per, cn), b_hi = min(b_lo + per, cn);
-            for (uint32_t bb = b_lo; bb < b_hi; bb += U) {
-                uint32_t wa[U][Q8 ? 2 : 1], wb[U][Q8 ? 2 : 1];
-                float da[U], db[U], ma[U], mb[U];
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const uint32_t b = c0 + min(bb + u, b_hi - 1);  // clamp; clamped copies get scale 0 below
-                    const bool live = bb + u < b_hi;
-                    wa[u][0] = __ldg(reinterpret_cast<const uint32_t*>(qa + (size_t)b * QB));
-                    wb[u][0] = __ldg(reinterpret_cast<const uint32_t*>(qb + (size_t)b * QB));
-                    if (Q8) {
-                        wa[u][Q8 ? 1 : 0] = __ldg(reinterpret_cast<const uint32_t*>(qa + (size_t)b * QB + 16));
-                        wb[u][Q8 ? 1 : 0] = __ldg(reinterpret_cast<const uint32_t*>(qb + (size_t)b * QB + 16));
-                    }
-                    if (Q41) {
-                        const __half2 sa = __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row_a * nb + b);
-                        const __half2 sb = __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row_b * nb + b);
-                        da[u] = live ? __low2float(sa) : 0.0f;
-                        ma[u] = live ? __high2float(sa) : 0.0f;
-                        db[u] = live ? __low2float(sb) : 0.0f;
-                        mb[u] = live ? __high2float(sb) : 0.0f;
-                    } else {
-                        const __half sa = __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row_a * nb + b);
-                        const __half sb = __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row_b * nb + b);
-                        da[u] = live ? __half2float(sa) : 0.0f;
-                        db[u] = live ? __half2float(sb) : 0.0f;
-                        ma[u] = mb[u] = 0.0f;
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const uint32_t bl = min(bb + u, b_hi - 1);  // block index inside the chunk
-                    uint32_t a_lo[4], a_hi[4];
-                    if (Q8) {
-                        unpack_q8(wa[u][0], a_lo[0], a_lo[2]);
-                        unpack_q8(wb[u][0], a_lo[1], a_lo[3]);
-                        unpack_q8(wa[u][Q8 ? 1 : 0], a_hi[0], a_hi[2]);
-                        unpack_q8(wb[u][Q8 ? 1 : 0], a_hi[1], a_hi[3]);
-                    } else {
-                        unpack_q4<Q41 ? 0 : 8>(wa[u][0], a_lo[0], a_lo[2], a_hi[0], a_hi[2]);
-                        unpack_q4<Q41 ? 0 : 8>(wb[u][0], a_lo[1], a_lo[3], a_hi[1], a_hi[3]);
-                    }
-#pragma unroll
-                    for (int s = 0; s < NS; ++s) {
-                        const uint4 bf = frag[((size_t)bl * NS + s) * 32 + lane];
-                        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                        float d1[4], d2[4];
-                        mma_f16(d1, a_lo, bf.x, bf.y, zero);
-                        mma_f16(d2, a_hi, bf.z, bf.w, d1);
-                        acc[s][0] = fmaf(d2[0], da[u], acc[s][0]);
-                        acc[s][1] = fmaf(d2[1], da[u], acc[s][1]);
-                        acc[s][2] = fmaf(d2[2], db[u], acc[s][2]);
-                        acc[s][3] = fmaf(d2[3], db[u], acc[s][3]);
-                        if (Q41) {
-                            const float xs_m = xsum[bl * 16 + 4 * s + t];
-                            accm[s][0] = fmaf(ma[u], xs_m, accm[s][0]);
-                            accm[s][1] = fmaf(mb[u], xs_m, accm[s][1]);
-                        }
-                    }
-                }
-            }
+        // two register sets: the loads of the next quad are in flight while this one is consumed
+        QuadRegs<Q8, Q41> ra, rb;
+        uint32_t q = q_lo;
+        if (q < q_hi) load_quad(ra, qa, qb, sa, sb, q);
+        while (q + 1 < q_hi) {
+            load_quad(rb, qa, qb, sa, sb, q + 1);
+            compute_quad<TYPE, NS>(ra, q, frag, xsum, ncols, M, g, t, acc, accm);
+            if (q + 2 < q_hi) load_quad(ra, qa, qb, sa, sb, q + 2);
+            compute_quad<TYPE, NS>(rb, q + 1, frag, xsum, ncols, M, g, t, acc, accm);
+            q += 2;
         }
+        if (q < q_hi) compute_quad<TYPE, NS>(ra, q, frag, xsum, ncols, M, g, t, acc, accm);
 
-        // hi + lo columns -> one value per (row, activation row); lane (g, t) of set s owns
-        // activation row 4s + t for weight rows g and g + 8.
+        // hi + lo columns -> one value per (row, activation row); lane (g, t) of set c owns
+        // activation row 4c + t for weight rows g and g + 8.
         float out_a[NS], out_b[NS];
 #pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            out_a[s] = acc[s][0] + acc[s][1] + accm[s][0];
-            out_b[s] = acc[s][2] + acc[s][3] + accm[s][1];
+        for (int c = 0; c < NS; ++c) {
+            out_a[c] = acc[c][0] + acc[c][1] + accm[c][0];
+            out_b[c] = acc[c][2] + acc[c][3] + accm[c][1];
         }
         if (KS > 1) {
-            __syncthreads();  // staging buffer of the last chunk is no longer read (red is separate)
             float* mine = red + ((size_t)(wr * KS + ks) * NS * 2) * 32;
 #pragma unroll
-            for (int s = 0; s < NS; ++s) {
-                mine[(s * 2 + 0) * 32 + lane] = out_a[s];
-                mine[(s * 2 + 1) * 32 + lane] = out_b[s];
+            for (int c = 0; c < NS; ++c) {
+                mine[(c * 2 + 0) * 32 + lane] = out_a[c];
+                mine[(c * 2 + 1) * 32 + lane] = out_b[c];
             }
             __syncthreads();
             if (ks == 0) {
 #pragma unroll
-                for (int s = 0; s < NS; ++s) {
-                    float sa = 0.0f, sb = 0.0f;
+                for (int c = 0; c < NS; ++c) {
+                    float va = 0.0f, vb = 0.0f;
                     for (uint32_t k2 = 0; k2 < KS; ++k2) {
                         const float* other = red + ((size_t)(wr * KS + k2) * NS * 2) * 32;
-                        sa += other[(s * 2 + 0) * 32 + lane];
-                        sb += other[(s * 2 + 1) * 32 + lane];
+                        va += other[(c * 2 + 0) * 32 + lane];
+                        vb += other[(c * 2 + 1) * 32 + lane];
                     }
-                    out_a[s] = sa;
-                    out_b[s] = sb;
+                    out_a[c] = va;
+                    out_b[c] = vb;
                 }
             }
         }
         if (ks == 0) {
-            const uint32_t r0 = (uint32_t)(tile * rows_per_cta) + wr * 16 + g;
 #pragma unroll
-            for (int s = 0; s < NS; ++s) {
-                const uint32_t m = 4 * s + t;
+            for (int c = 0; c < NS; ++c) {
+                const uint32_t m = 4 * c + t;
                 if (m < M) {
                     const float ps = post[m];
-                    if (r0 < N)
-                        y[(size_t)m * N + r0] = apply_epilogue(out_a[s] * ps, ep, r0, (size_t)m * N + r0);
+                    if (r0 < N) y[(size_t)m * N + r0] = apply_epilogue(out_a[c] * ps, ep, r0, (size_t)m * N + r0);
                     if (r0 + 8 < N)
-                        y[(size_t)m * N + r0 + 8] =
-                            apply_epilogue(out_b[s] * ps, ep, r0 + 8, (size_t)m * N + r0 + 8);
+                        y[(size_t)m * N + r0 + 8] = apply_epilogue(out_b[c] * ps, ep, r0 + 8, (size_t)m * N + r0 + 8);
                 }
             }
         }
-        if (KS > 1) __syncthreads();  // red is reused by the next tile
+        if (KS > 1) __syncthreads();  // `red` is reused by the next tile
     }
 }
 
 struct Plan {
-    uint32_t WR, KS, kc, grid;
+    uint32_t WR, KS, grid;
     size_t smem;
+    bool fits;
 };
 
-// Chooses the CTA shape: enough warps in flight on every SM, K split across warps only when there
-// are too few row tiles to do that with one warp per tile.
-Plan make_plan(const zq_weight* w, int ns, bool q41) {
-    Plan p;
+// CTA shape: enough warps in flight on every SM; K is split across warps only when there are too
+// few row tiles to do that with one warp per tile.
+Plan make_plan(const zq_weight* w, uint32_t M, int ns) {
+    Plan p{};
+    const bool q41 = w->type == ZQ_TYPE_Q4_1;
     const uint32_t tiles = (w->out_dim + 15) / 16;
     const uint32_t sms = (uint32_t)sm_count();
-    const uint32_t want_warps = sms * 16;
+    const uint32_t nq = w->nbp / 4;
     uint32_t ks = 1;
-    while (ks < 8 && tiles * ks < want_warps && w->nb / (ks * 2) >= 4) ks *= 2;
-    // 8 warps per CTA, fewer when that would leave SMs without a CTA
-    uint32_t warps = 8;
+    while (ks < 8 && tiles * ks < sms * 16 && nq / (ks * 2) >= 2) ks *= 2;
+    uint32_t warps = 8;  // per CTA; fewer when that would leave SMs without a CTA
     while (warps > ks && (tiles + warps / ks - 1) / (warps / ks) < sms) warps /= 2;
-    uint32_t wr = warps / ks;
-    if (wr == 0) wr = 1;
-    p.WR = wr;
+    p.WR = warps / ks ? warps / ks : 1;
     p.KS = ks;
-    const size_t per_block = (size_t)ns * 32 * 16 + (q41 ? 64 : 0);
-    const size_t red = ks > 1 ? (size_t)wr * ks * ns * 2 * 32 * 4 : 0;
-    const size_t budget = 64 * 1024;  // keeps several CTAs resident per SM
-    uint32_t kc = w->nb;
-    if ((size_t)kc * per_block + red > budget) kc = (uint32_t)((budget - red) / per_block);
-    if (kc < 1) kc = 1;
-    p.kc = kc;
-    p.smem = (size_t)kc * per_block + red;
-    const uint32_t cta_tiles = (tiles + wr - 1) / wr;
-    const uint32_t cap = sms * 4;
+    size_t smem = (size_t)w->nbp * 2 * M * 64;
+    if (q41) smem += (size_t)w->nbp * M * sizeof(float);
+    if (ks > 1) smem += (size_t)p.WR * ks * ns * 2 * 32 * sizeof(float);
+    p.smem = smem;
+    p.fits = smem <= 160 * 1024;
+    const uint32_t cta_tiles = (tiles + p.WR - 1) / p.WR;
+    uint32_t per_sm = (uint32_t)((200 * 1024) / (smem + 1024));
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) per_sm = 1;
+    const uint32_t cap = sms * per_sm;
     p.grid = cta_tiles < cap ? cta_tiles : cap;
     return p;
 }
 
 template <int TYPE, int NS>
 int launch_one(const zq_weight* w, const float* x, float* y, uint32_t M, EpilogueArgs ep, cudaStream_t st) {
-    const Plan p = make_plan(w, NS, TYPE == ZQ_TYPE_Q4_1);
-    auto kern = gemv_mma_kernel<TYPE, NS, 4>;
+    const Plan p = make_plan(w, M, NS);
+    if (!p.fits) return ZQ_ERR_LIMIT;
+    auto kern = gemv_mma_kernel<TYPE, NS>;
     if (p.smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
-    kern<<<p.grid, p.WR * p.KS * 32, p.smem, st>>>(w->qs, w->sc, x, y, w->out_dim, w->in_dim, w->nb, M, p.kc,
-                                                    p.WR, p.KS, ep);
+    kern<<<p.grid, p.WR * p.KS * 32, p.smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim,
+                                                    w->in_dim, w->nb, w->scp, M, p.WR, p.KS, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -380,10 +427,11 @@ int launch_ns(const zq_weight* w, const float* x, float* y, uint32_t M, Epilogue
 }  // namespace
 
 // y[m][j] for m < m_rows <= 16. Epilogue pointers `mul` / `residual` are indexed [m][j].
+// Returns ZQ_ERR_LIMIT when the activation image does not fit in shared memory.
 int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
                         const zq_epilogue* ep, cudaStream_t st) {
     if (m_rows == 0) return ZQ_OK;
-    if (m_rows > 4 * kMaxCols) return ZQ_ERR_BAD_ARG;
+    if (m_rows > 16) return ZQ_ERR_BAD_ARG;
     if (((uintptr_t)x & 15) != 0) return ZQ_ERR_BAD_ARG;  // activation rows are read as float4
     EpilogueArgs a{nullptr, nullptr, nullptr, 0};
     if (ep) {

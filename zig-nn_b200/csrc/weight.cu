@@ -7,6 +7,9 @@ namespace zq {
 
 thread_local int g_last_cuda_error = 0;
 
+// Set by a kernel whose bounded device-side wait ran out; read with zq_device_error().
+__device__ unsigned int g_device_error = 0;
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;
@@ -28,34 +31,46 @@ __host__ __device__ inline uint32_t raw_bpb(int type) {
 
 // One thread per block: split the GGUF block into its scale word(s) and its quant bytes.
 __global__ void repack_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ qs,
-                              uint8_t* __restrict__ sc, int type, size_t n_blocks) {
+                              uint8_t* __restrict__ sc, int type, size_t n_blocks, uint32_t nb,
+                              uint32_t scp) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
     const uint32_t bpb = raw_bpb(type);
     const uint32_t hdr = type == ZQ_TYPE_Q4_1 ? 4u : 2u;
     const uint32_t qb = bpb - hdr;
     const uint8_t* src = raw + b * bpb;
-    for (uint32_t i = 0; i < hdr; ++i) sc[b * hdr + i] = src[i];
-    for (uint32_t i = 0; i < qb; ++i) qs[b * qb + i] = src[hdr + i];
+    const size_t row = b / nb;
+    const uint32_t blk = (uint32_t)(b % nb);
+    const size_t sb = row * scp + blk;  // scale slot in the padded row
+    for (uint32_t i = 0; i < hdr; ++i) sc[sb * hdr + i] = src[i];
+    const uint32_t nbp = (nb + 3u) & ~3u;
+    uint8_t* qrow = qs + row * (size_t)nbp * qb;
+    for (uint32_t i = 0; i < qb; ++i) qrow[qs_word_offset(qb, blk, i >> 2) + (i & 3u)] = src[hdr + i];
 }
 
 __global__ void unpack_kernel(uint8_t* __restrict__ raw, const uint8_t* __restrict__ qs,
-                              const uint8_t* __restrict__ sc, int type, size_t n_blocks) {
+                              const uint8_t* __restrict__ sc, int type, size_t n_blocks, uint32_t nb,
+                              uint32_t scp) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
     const uint32_t bpb = raw_bpb(type);
     const uint32_t hdr = type == ZQ_TYPE_Q4_1 ? 4u : 2u;
     const uint32_t qb = bpb - hdr;
     uint8_t* dst = raw + b * bpb;
-    for (uint32_t i = 0; i < hdr; ++i) dst[i] = sc[b * hdr + i];
-    for (uint32_t i = 0; i < qb; ++i) dst[hdr + i] = qs[b * qb + i];
+    const size_t row = b / nb;
+    const uint32_t blk = (uint32_t)(b % nb);
+    const size_t sb = row * scp + blk;
+    for (uint32_t i = 0; i < hdr; ++i) dst[i] = sc[sb * hdr + i];
+    const uint32_t nbp = (nb + 3u) & ~3u;
+    const uint8_t* qrow = qs + row * (size_t)nbp * qb;
+    for (uint32_t i = 0; i < qb; ++i) dst[hdr + i] = qrow[qs_word_offset(qb, blk, i >> 2) + (i & 3u)];
 }
 
 // One thread per element. `row_map` (optional) selects source rows; `scale_mode` multiplies the
 // dequantised value by `scale` as a second, separately rounded multiply.
 template <int TYPE>
 __global__ void dequant_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
-                               float* __restrict__ out, uint32_t nb, size_t n_rows,
+                               float* __restrict__ out, uint32_t nb, uint32_t scp, size_t n_rows,
                                const int32_t* __restrict__ row_map, int scale_mode, float scale) {
     const size_t K = (size_t)nb * 32;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -63,21 +78,25 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ qs, const void* __res
     const size_t r = idx / K;
     const uint32_t k = (uint32_t)(idx - r * K);
     const size_t src_row = row_map ? (size_t)row_map[r] : r;
-    const size_t blk = src_row * nb + (k >> 5);
+    const uint32_t blk = k >> 5;
+    const size_t sblk = src_row * scp + blk;
     const uint32_t j = k & 31;
+    const uint32_t nbp = (nb + 3u) & ~3u;
+    const uint8_t* qrow = qs + src_row * (size_t)nbp * (TYPE == ZQ_TYPE_Q8_0 ? 32 : 16);
     float v;
     if (TYPE == ZQ_TYPE_Q8_0) {
-        const float d = __half2float(reinterpret_cast<const __half*>(sc)[blk]);
-        const int8_t q = reinterpret_cast<const int8_t*>(qs)[blk * 32 + j];
+        const float d = __half2float(reinterpret_cast<const __half*>(sc)[sblk]);
+        const int8_t q = (int8_t)qrow[qs_word_offset(32, blk, j >> 2) + (j & 3u)];
         v = __fmul_rn((float)q, d);
     } else {
-        const uint8_t byte = qs[blk * 16 + (j & 15)];
+        const uint32_t jb = j & 15u;
+        const uint8_t byte = qrow[qs_word_offset(16, blk, jb >> 2) + (jb & 3u)];
         const int nib = (j < 16) ? (byte & 0x0F) : (byte >> 4);
         if (TYPE == ZQ_TYPE_Q4_0) {
-            const float d = __half2float(reinterpret_cast<const __half*>(sc)[blk]);
+            const float d = __half2float(reinterpret_cast<const __half*>(sc)[sblk]);
             v = __fmul_rn((float)(nib - 8), d);
         } else {
-            const __half2 dm = reinterpret_cast<const __half2*>(sc)[blk];
+            const __half2 dm = reinterpret_cast<const __half2*>(sc)[sblk];
             // nibble*d then +m: two roundings, never contracted into an FMA
             v = __fadd_rn(__fmul_rn((float)nib, __low2float(dm)), __high2float(dm));
         }
@@ -99,10 +118,11 @@ int make_weight(int type, uint32_t out_dim, uint32_t in_dim, zq_weight** out) {
     w->in_dim = in_dim;
     w->nb = in_dim / 32;
     w->qb = type == ZQ_TYPE_Q8_0 ? 32 : 16;
-    const size_t n_blocks = (size_t)out_dim * w->nb;
-    const size_t qs_bytes = n_blocks * w->qb;
+    w->nbp = (w->nb + 3u) & ~3u;
+    const size_t qs_bytes = (size_t)out_dim * w->nbp * w->qb;
     const size_t qs_pad = (qs_bytes + 255) & ~(size_t)255;
-    const size_t sc_bytes = n_blocks * (type == ZQ_TYPE_Q4_1 ? 4 : 2);
+    w->scp = type == ZQ_TYPE_Q4_1 ? ((w->nb + 3) & ~3u) : ((w->nb + 7) & ~7u);
+    const size_t sc_bytes = (size_t)out_dim * w->scp * (type == ZQ_TYPE_Q4_1 ? 4 : 2);
     w->bytes = qs_pad + ((sc_bytes + 255) & ~(size_t)255);
     cudaError_t e = cudaMalloc(&w->base, w->bytes);
     if (e != cudaSuccess) {
@@ -139,6 +159,18 @@ const char* zq_status_string(int s) {
 }
 
 int zq_last_cuda_error(void) { return g_last_cuda_error; }
+
+int zq_device_error(unsigned int* out, int clear) {
+    if (!out) return ZQ_ERR_BAD_ARG;
+    unsigned int v = 0;
+    ZQ_CUDA(cudaMemcpyFromSymbol(&v, zq::g_device_error, sizeof(v)));
+    *out = v;
+    if (clear && v) {
+        const unsigned int z = 0;
+        ZQ_CUDA(cudaMemcpyToSymbol(zq::g_device_error, &z, sizeof(z)));
+    }
+    return ZQ_OK;
+}
 int zq_abi_version(void) { return 1; }
 
 size_t zq_block_size(int t) {
@@ -177,9 +209,17 @@ int zq_weight_from_device(const void* d_raw, int type, uint32_t out_dim, uint32_
     const size_t n_blocks = (size_t)out_dim * w->nb;
     const unsigned threads = 256;
     const unsigned blocks = (unsigned)((n_blocks + threads - 1) / threads);
-    repack_kernel<<<blocks, threads, 0, as_stream(stream)>>>(
-        static_cast<const uint8_t*>(d_raw), w->qs, static_cast<uint8_t*>(w->sc), type, n_blocks);
-    cudaError_t e = cudaGetLastError();
+    // padding blocks of the quant rows and padding slots of the scale rows read as zero
+    cudaError_t e = cudaSuccess;
+    if (w->nbp != w->nb) e = cudaMemsetAsync(w->qs, 0, (size_t)out_dim * w->nbp * w->qb, as_stream(stream));
+    if (e == cudaSuccess) e = cudaMemsetAsync(w->sc, 0, (size_t)out_dim * w->scp * (type == ZQ_TYPE_Q4_1 ? 4 : 2),
+                                    as_stream(stream));
+    if (e == cudaSuccess) {
+        repack_kernel<<<blocks, threads, 0, as_stream(stream)>>>(static_cast<const uint8_t*>(d_raw), w->qs,
+                                                                 static_cast<uint8_t*>(w->sc), type, n_blocks,
+                                                                 w->nb, w->scp);
+        e = cudaGetLastError();
+    }
     if (e != cudaSuccess) {
         zq_weight_free(w);
         *out = nullptr;
@@ -240,7 +280,8 @@ int zq_weight_download_raw(const zq_weight* w, void* d_raw, zq_stream stream) {
     const unsigned threads = 256;
     const unsigned blocks = (unsigned)((n_blocks + threads - 1) / threads);
     unpack_kernel<<<blocks, threads, 0, as_stream(stream)>>>(
-        static_cast<uint8_t*>(d_raw), w->qs, static_cast<const uint8_t*>(w->sc), w->type, n_blocks);
+        static_cast<uint8_t*>(d_raw), w->qs, static_cast<const uint8_t*>(w->sc), w->type, n_blocks, w->nb,
+        w->scp);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -256,15 +297,15 @@ static int dequant_launch(const zq_weight* w, float* d_out, size_t n_rows, const
     cudaStream_t st = as_stream(stream);
     switch (w->type) {
         case ZQ_TYPE_Q4_0:
-            dequant_kernel<ZQ_TYPE_Q4_0><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb,
+            dequant_kernel<ZQ_TYPE_Q4_0><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb, w->scp,
                                                                     n_rows, row_map, scale_mode, scale);
             break;
         case ZQ_TYPE_Q4_1:
-            dequant_kernel<ZQ_TYPE_Q4_1><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb,
+            dequant_kernel<ZQ_TYPE_Q4_1><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb, w->scp,
                                                                     n_rows, row_map, scale_mode, scale);
             break;
         case ZQ_TYPE_Q8_0:
-            dequant_kernel<ZQ_TYPE_Q8_0><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb,
+            dequant_kernel<ZQ_TYPE_Q8_0><<<blocks, threads, 0, st>>>(w->qs, w->sc, d_out, w->nb, w->scp,
                                                                     n_rows, row_map, scale_mode, scale);
             break;
         default: return ZQ_ERR_UNSUPPORTED;

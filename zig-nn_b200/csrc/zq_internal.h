@@ -7,17 +7,26 @@
 
 #include "zq.h"
 
-// Device-resident quantised weight. Values are those of the GGUF blocks; only the
-// arrangement differs so that the kernels can use aligned 128-bit loads:
-//   qs : [out_dim][nb][QB] quant bytes of each block, QB = 16 (q4_0, q4_1) or 32 (q8_0),
-//        in the block's own byte order; row pitch nb*QB is a multiple of 16 bytes.
-//   sc : q4_0 / q8_0: f16 d [out_dim][nb];  q4_1: (f16 d, f16 m) pairs [out_dim][nb].
+// Device-resident quantised weight. Values are those of the GGUF blocks; only the arrangement
+// differs so that the kernels can use aligned 128-bit loads that feed tensor-core fragments directly:
+//   qs : quant words of each row, in groups of 4 consecutive blocks ("quads"). Inside a quad the 32-bit
+//        words are interleaved so that words with the same index t of the 4 blocks are adjacent:
+//          q4_0 / q4_1 (4 words per block):  quad = 64 bytes,  word w of block j at (w*4 + j)*4
+//          q8_0 (8 words per block):         quad = 128 bytes, word w of block j at
+//                                            ((w/4)*16 + (w%4)*4 + j)*4
+//        A lane that needs word t of every block (the K footprint of an MMA A fragment) reads 16
+//        contiguous bytes per quad. Rows are padded to nbp = roundup(nb, 4) blocks (zero quants).
+//   sc : q4_0 / q8_0: f16 d [out_dim][scp];  q4_1: (f16 d, f16 m) pairs [out_dim][scp].
+//        scp >= nb is the row pitch in scale elements, padded with zeros to a multiple of 8 so that
+//        every row starts on a 16-byte boundary.
 struct zq_weight {
     int type;
     uint32_t out_dim;
     uint32_t in_dim;
     uint32_t nb;       // blocks per row = in_dim / 32
+    uint32_t nbp;      // blocks per row in the qs array (nb rounded up to a multiple of 4)
     uint32_t qb;       // quant bytes per block
+    uint32_t scp;      // scale elements per row (pitch), multiple of 8 (f16) or 4 (f16 pairs)
     uint8_t* qs;       // device
     void* sc;          // device
     void* base;        // the single allocation holding qs and sc
@@ -43,6 +52,13 @@ inline int cuda_fail(cudaError_t e) {
 #define ZQ_LAUNCH_CHECK() ZQ_CUDA(cudaGetLastError())
 
 inline cudaStream_t as_stream(zq_stream s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Byte offset of 32-bit word `w` of block `blk` inside a row of the interleaved qs array.
+__host__ __device__ inline size_t qs_word_offset(uint32_t qb, uint32_t blk, uint32_t w) {
+    const uint32_t quad = blk >> 2, j = blk & 3u;
+    if (qb == 16) return (size_t)quad * 64 + (size_t)(w * 4 + j) * 4;
+    return (size_t)quad * 128 + (size_t)((w >> 2) * 16 + (w & 3u) * 4 + j) * 4;
+}
 
 inline bool is_quant(int t) { return t == ZQ_TYPE_Q4_0 || t == ZQ_TYPE_Q4_1 || t == ZQ_TYPE_Q8_0; }
 
