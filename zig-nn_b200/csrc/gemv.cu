@@ -1,9 +1,8 @@
 // Decode GEMV kernels: quantised weight rows streamed from HBM with 128-bit loads, dequantised
 // in registers, reduced with warp shuffles. Two activation treatments:
 //   f32  — f32 activations times weights dequantised on the fly (zig-nn src/gguf/dequant.zig:133-309)
-//   q8   — activations quantised to int8 blocks, exact int32 dots, block terms summed in block
-//          order (src/gguf/simd_dot.zig:25-152, src/gguf/thread_pool.zig:96-181): bit-identical
-//          to that CPU path.
+//   q8   — the activation quantiser lives here (quantize_row_q8); the exact int8 GEMV is in
+//          gemv_q8.cu.
 #include "zq_internal.h"
 
 namespace zq {
@@ -13,7 +12,6 @@ constexpr int kThreads = 128;  // 4 warps per CTA
 constexpr int kWarps = kThreads / 32;
 constexpr int XPAD = 36;   // floats per activation block in shared memory: 32 + 4 so that lanes
                            // reading different blocks with 128-bit loads hit different banks
-constexpr int QPAD = 48;   // bytes per int8 activation block in shared memory (32 + 16)
 
 // ---- packed f32x2 arithmetic (sm_100) --------------------------------------------------
 
@@ -225,114 +223,6 @@ gemv_f32_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
     }
 }
 
-// ---- Q8-activation GEMV, one activation row (exact) ----------------------------------------
-//
-// Same walk as above with int8 activations and dp4a. Each step produces, per row, the G block
-// terms  t_b = (d*s)*float(idot) [+ (m*s)*float(qsum)]  of G consecutive blocks; they go through
-// a small shared-memory tile and one lane per row adds them to the row's running sum in block
-// order, which is the order (and the rounding) of the CPU loop.
-template <int TYPE, int G, int R>
-__global__ void __launch_bounds__(kThreads)
-gemv_q8_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc,
-               const int8_t* __restrict__ xq, const float* __restrict__ xscale,
-               const int32_t* __restrict__ xqsum, float* __restrict__ y, uint32_t N, uint32_t nb,
-               uint32_t scp, EpilogueArgs ep) {
-    constexpr int GROUPS = 32 / G;
-    constexpr int ROWS_W = GROUPS * R;
-    static_assert(ROWS_W <= 32, "one lane per row in the ordered-sum phase");
-    constexpr int QB = TYPE == ZQ_TYPE_Q8_0 ? 32 : 16;
-    constexpr int TP = G + 1;  // padded pitch of the term tile
-
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    unsigned char* xq_s = smem_raw;                                   // nb * QPAD
-    float* xs_s = reinterpret_cast<float*>(smem_raw + (size_t)nb * QPAD);  // nb
-    int32_t* xsum_s = reinterpret_cast<int32_t*>(xs_s + nb);          // nb
-    float* terms = reinterpret_cast<float*>(xsum_s + nb);             // kWarps * ROWS_W * TP
-
-    const int tid = threadIdx.x;
-    for (uint32_t i = tid; i < nb * 8; i += kThreads)  // 4 bytes per step
-        *reinterpret_cast<uint32_t*>(xq_s + (i >> 3) * QPAD + (i & 7) * 4) =
-            reinterpret_cast<const uint32_t*>(xq)[i];
-    for (uint32_t b = tid; b < nb; b += kThreads) {
-        xs_s[b] = xscale[b];
-        xsum_s[b] = xqsum[b];
-    }
-    __syncthreads();
-
-    const int lane = tid & 31, warp = tid >> 5;
-    const int g = lane % G, grp = lane / G;
-    float* my_terms = terms + warp * ROWS_W * TP;
-    const uint32_t rows_per_cta = kWarps * ROWS_W;
-    const uint32_t steps = (nb + G - 1) / G;
-
-    for (uint64_t tile = blockIdx.x; tile * rows_per_cta < N; tile += gridDim.x) {
-        const uint32_t wrow0 = (uint32_t)(tile * rows_per_cta) + warp * ROWS_W;
-        const uint32_t row0 = wrow0 + grp * R;
-        float run = 0.0f;  // lane l: running sum of row wrow0 + l
-        for (uint32_t st = 0; st < steps; ++st) {
-            const uint32_t b = st * G + g;
-            if (b < nb) {
-                const uint4* xp = reinterpret_cast<const uint4*>(xq_s + b * QPAD);
-                const uint4 xa = xp[0], xb4 = xp[1];
-                const int xw[8] = {(int)xa.x, (int)xa.y, (int)xa.z, (int)xa.w,
-                                   (int)xb4.x, (int)xb4.y, (int)xb4.z, (int)xb4.w};
-                const float s = xs_s[b];
-                const int qsum = xsum_s[b];
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const uint32_t row = min(row0 + r, N - 1);
-                    const uint8_t* p = qs + (size_t)row * ((nb + 3u) & ~3u) * QB;
-                    auto word = [&](uint32_t w) {
-                        return __ldg(reinterpret_cast<const uint32_t*>(p + qs_word_offset(QB, b, w)));
-                    };
-                    float term;
-                    if (TYPE == ZQ_TYPE_Q8_0) {
-                        const int w[8] = {(int)word(0), (int)word(1), (int)word(2), (int)word(3),
-                                          (int)word(4), (int)word(5), (int)word(6), (int)word(7)};
-                        int idot = 0;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) idot = __dp4a(w[i], xw[i], idot);
-                        const float d = __half2float(
-                            __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * scp + b));
-                        term = __fmul_rn(__fmul_rn(d, s), (float)idot);
-                    } else {
-                        const uint32_t w[4] = {word(0), word(1), word(2), word(3)};
-                        int idot = 0;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            idot = __dp4a((int)(w[i] & 0x0F0F0F0Fu), xw[i], idot);
-                            idot = __dp4a((int)((w[i] >> 4) & 0x0F0F0F0Fu), xw[4 + i], idot);
-                        }
-                        if (TYPE == ZQ_TYPE_Q4_0) {
-                            idot -= 8 * qsum;  // sum((n-8)*q) = sum(n*q) - 8*sum(q), exact
-                            const float d = __half2float(
-                                __ldg(reinterpret_cast<const __half*>(sc) + (size_t)row * scp + b));
-                            term = __fmul_rn(__fmul_rn(d, s), (float)idot);
-                        } else {
-                            const __half2 dm =
-                                __ldg(reinterpret_cast<const __half2*>(sc) + (size_t)row * scp + b);
-                            const float t1 = __fmul_rn(__fmul_rn(__low2float(dm), s), (float)idot);
-                            const float t2 = __fmul_rn(__fmul_rn(__high2float(dm), s), (float)qsum);
-                            term = __fadd_rn(t1, t2);
-                        }
-                    }
-                    my_terms[(grp * R + r) * TP + g] = term;
-                }
-            }
-            __syncwarp();
-            if (lane < ROWS_W) {
-                const uint32_t nvalid = min((uint32_t)G, nb - st * G);
-#pragma unroll
-                for (int j = 0; j < G; ++j)
-                    if ((uint32_t)j < nvalid) run = __fadd_rn(run, my_terms[lane * TP + j]);
-            }
-            __syncwarp();
-        }
-        if (lane < ROWS_W && wrow0 + lane < N)
-            y[wrow0 + lane] = apply_epilogue(run, ep, wrow0 + lane);
-    }
-}
-
 // ---- quantize_row_q8 (src/gguf/simd_dot.zig:25-64): one warp per 32-element block ---------------
 
 __global__ void quantize_q8_kernel(const float* __restrict__ x, int8_t* __restrict__ q,
@@ -514,38 +404,6 @@ int launch_f32_g(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, 
     }
 }
 
-template <int TYPE, int G, int R>
-int launch_q8_one(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum,
-                  float* y, EpilogueArgs ep, cudaStream_t st) {
-    const size_t smem = (size_t)w->nb * QPAD + (size_t)w->nb * 8 +
-                        (size_t)kWarps * (32 / G) * R * (G + 1) * sizeof(float);
-    int rc = set_smem(gemv_q8_kernel<TYPE, G, R>, smem);
-    if (rc != ZQ_OK) return rc;
-    const uint32_t rows_per_cta = kWarps * (32 / G) * R;
-    const uint64_t tiles = ((uint64_t)w->out_dim + rows_per_cta - 1) / rows_per_cta;
-    const uint64_t cap = (uint64_t)sm_count() * 8;
-    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
-    gemv_q8_kernel<TYPE, G, R><<<grid, kThreads, smem, st>>>(w->qs, w->sc, xq, xs, xsum, y,
-                                                             w->out_dim, w->nb, w->scp, ep);
-    ZQ_LAUNCH_CHECK();
-    return ZQ_OK;
-}
-
-template <int TYPE>
-int launch_q8_g(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum, float* y,
-                EpilogueArgs ep, cudaStream_t st) {
-    // Small groups keep the ordered-sum phase cheap (its cost grows with G).
-    const int g = pick_group(w->nb, 8);
-    const uint64_t warp_tiles = (uint64_t)w->out_dim / 32;
-    const bool big = warp_tiles >= (uint64_t)sm_count() * kWarps * 2;
-    if (g == 8) {
-        if (big) return launch_q8_one<TYPE, 8, 8>(w, xq, xs, xsum, y, ep, st);
-        return launch_q8_one<TYPE, 8, 2>(w, xq, xs, xsum, y, ep, st);
-    }
-    if (big) return launch_q8_one<TYPE, 4, 4>(w, xq, xs, xsum, y, ep, st);
-    return launch_q8_one<TYPE, 4, 1>(w, xq, xs, xsum, y, ep, st);
-}
-
 }  // namespace
 
 int launch_gemv_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
@@ -558,24 +416,6 @@ int launch_gemv_f32(const zq_weight* w, const float* x, float* y, uint32_t m_row
             case ZQ_TYPE_Q4_0: rc = launch_f32_g<ZQ_TYPE_Q4_0>(w, x + xo, y + yo, a, st); break;
             case ZQ_TYPE_Q4_1: rc = launch_f32_g<ZQ_TYPE_Q4_1>(w, x + xo, y + yo, a, st); break;
             case ZQ_TYPE_Q8_0: rc = launch_f32_g<ZQ_TYPE_Q8_0>(w, x + xo, y + yo, a, st); break;
-            default: return ZQ_ERR_UNSUPPORTED;
-        }
-        if (rc != ZQ_OK) return rc;
-    }
-    return ZQ_OK;
-}
-
-int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum,
-                   float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st) {
-    for (uint32_t m = 0; m < m_rows; ++m) {
-        const size_t yo = (size_t)m * w->out_dim, bo = (size_t)m * w->nb;
-        EpilogueArgs a = make_ep(ep, yo);
-        const int8_t* q = xq + (size_t)m * w->in_dim;
-        int rc;
-        switch (w->type) {
-            case ZQ_TYPE_Q4_0: rc = launch_q8_g<ZQ_TYPE_Q4_0>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
-            case ZQ_TYPE_Q4_1: rc = launch_q8_g<ZQ_TYPE_Q4_1>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
-            case ZQ_TYPE_Q8_0: rc = launch_q8_g<ZQ_TYPE_Q8_0>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
             default: return ZQ_ERR_UNSUPPORTED;
         }
         if (rc != ZQ_OK) return rc;

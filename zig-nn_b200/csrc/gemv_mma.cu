@@ -48,8 +48,7 @@ __device__ __forceinline__ float apply_epilogue(float v, const EpilogueArgs& ep,
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
                                         const float (&c)[4]) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%10,%11,%12,%13};"
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]),
@@ -153,25 +152,84 @@ struct QuadRegs {
     uint4 sa, sb;      // scales: q4_0/q8_0 use .x,.y (4 x f16); q4_1 all four (4 x (d, m))
 };
 
+// ---- per-lane cp.async ring -------------------------------------------------------------------------
+// Every lane copies the 16-byte quant pieces and the scales it will need for one quad into its own
+// slots of a shared-memory stage and, a few stages later, reads the same slots back. Nothing is
+// shared between lanes, so cp.async.wait_group is the only synchronisation, and the data in flight
+// sits in shared memory instead of registers.
 template <bool Q8, bool Q41>
-__device__ __forceinline__ void load_quad(QuadRegs<Q8, Q41>& r, const uint8_t* qa, const uint8_t* qb,
-                                          const uint8_t* sa, const uint8_t* sb, uint32_t q) {
-    constexpr uint32_t QUAD = Q8 ? 128 : 64;
-    r.a_lo = __ldg(reinterpret_cast<const uint4*>(qa + (size_t)q * QUAD));
-    r.b_lo = __ldg(reinterpret_cast<const uint4*>(qb + (size_t)q * QUAD));
+struct Ring {
+    static constexpr uint32_t kQuantArrays = Q8 ? 4 : 2;              // a, b (, a_hi, b_hi): 512 bytes each
+    static constexpr uint32_t kScaleOff = kQuantArrays * 512;
+    static constexpr uint32_t kScaleArray = Q41 ? 512 : 256;          // 16 or 8 bytes per lane
+    static constexpr uint32_t kStage = kScaleOff + 2 * kScaleArray;
+    static constexpr int kDepth = 4;  // quads in flight per lane: 3 x (32..64) bytes
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// stage: shared address of the stage for this warp; pointers already offset to this lane's 16 bytes.
+template <bool Q8, bool Q41>
+__device__ __forceinline__ void ring_issue(uint32_t stage, int lane, const uint8_t* pa, const uint8_t* pb,
+                                           const uint8_t* psa, const uint8_t* psb) {
+    using R = Ring<Q8, Q41>;
+    cp_async16(stage + lane * 16, pa);
+    cp_async16(stage + 512 + lane * 16, pb);
     if (Q8) {
-        r.a_hi = __ldg(reinterpret_cast<const uint4*>(qa + (size_t)q * QUAD + 64));
-        r.b_hi = __ldg(reinterpret_cast<const uint4*>(qb + (size_t)q * QUAD + 64));
+        cp_async16(stage + 1024 + lane * 16, pa + 64);
+        cp_async16(stage + 1536 + lane * 16, pb + 64);
     }
     if (Q41) {
-        r.sa = __ldg(reinterpret_cast<const uint4*>(sa + (size_t)q * 16));
-        r.sb = __ldg(reinterpret_cast<const uint4*>(sb + (size_t)q * 16));
+        cp_async16(stage + R::kScaleOff + lane * 16, psa);
+        cp_async16(stage + R::kScaleOff + 512 + lane * 16, psb);
     } else {
-        const uint2 va = __ldg(reinterpret_cast<const uint2*>(sa + (size_t)q * 8));
-        const uint2 vb = __ldg(reinterpret_cast<const uint2*>(sb + (size_t)q * 8));
+        cp_async8(stage + R::kScaleOff + lane * 8, psa);
+        cp_async8(stage + R::kScaleOff + 256 + lane * 8, psb);
+    }
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+template <bool Q8, bool Q41>
+__device__ __forceinline__ void ring_read(QuadRegs<Q8, Q41>& r, uint32_t stage, int lane) {
+    using R = Ring<Q8, Q41>;
+    r.a_lo = lds128(stage + lane * 16);
+    r.b_lo = lds128(stage + 512 + lane * 16);
+    if (Q8) {
+        r.a_hi = lds128(stage + 1024 + lane * 16);
+        r.b_hi = lds128(stage + 1536 + lane * 16);
+    }
+    if (Q41) {
+        r.sa = lds128(stage + R::kScaleOff + lane * 16);
+        r.sb = lds128(stage + R::kScaleOff + 512 + lane * 16);
+    } else {
+        const uint2 va = lds64(stage + R::kScaleOff + lane * 8), vb = lds64(stage + R::kScaleOff + 256 + lane * 8);
         r.sa.x = va.x; r.sa.y = va.y;
         r.sb.x = vb.x; r.sb.y = vb.y;
     }
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
 }
 
 __device__ __forceinline__ uint32_t pick(const uint4& v, int j) {
@@ -184,19 +242,41 @@ __device__ __forceinline__ float half_hi(uint32_t v) {
     return __half2float(__ushort_as_half((unsigned short)(v >> 16)));
 }
 
+__device__ __forceinline__ void unpack_half2(uint32_t v, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+    lo = f.x;
+    hi = f.y;
+}
+
 // One quad (4 blocks) of rows g and g + 8 against every activation column set.
+// faddr[c] / fstride[c]: 32-bit shared address of this lane's B fragment for the quad's first block in
+// column set c, and its per-block stride in bytes; lanes whose MMA column carries no activation point
+// at a zero slot with stride 0, so the load needs no predicate. xaddr: shared address of
+// xsum[first block][4c' + t] terms (q4_1), xstride its per-block stride.
 template <int TYPE, int NS>
 __device__ __forceinline__ void compute_quad(const QuadRegs<TYPE == ZQ_TYPE_Q8_0, TYPE == ZQ_TYPE_Q4_1>& r,
-                                             uint32_t q, const uint4* __restrict__ frag,
-                                             const float* __restrict__ xsum, uint32_t ncols, uint32_t M, int g,
-                                             int t, float (&acc)[NS][4], float (&accm)[NS][2]) {
+                                             const uint32_t (&faddr)[NS], const uint32_t (&fstride)[NS],
+                                             const uint32_t (&xaddr)[NS], const uint32_t (&xstride)[NS],
+                                             float (&acc)[NS][4], float (&accm)[NS][2]) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float da[4], db[4], ma[4], mb[4];
+    if (Q41) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            unpack_half2(pick(r.sa, j), da[j], ma[j]);
+            unpack_half2(pick(r.sb, j), db[j], mb[j]);
+        }
+    } else {
+        unpack_half2(r.sa.x, da[0], da[1]);
+        unpack_half2(r.sa.y, da[2], da[3]);
+        unpack_half2(r.sb.x, db[0], db[1]);
+        unpack_half2(r.sb.y, db[2], db[3]);
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         uint32_t a_lo[4], a_hi[4];
-        float da, db, ma = 0.0f, mb = 0.0f;
         if (Q8) {
             unpack_q8(pick(r.a_lo, j), a_lo[0], a_lo[2]);
             unpack_q8(pick(r.b_lo, j), a_lo[1], a_lo[3]);
@@ -206,34 +286,20 @@ __device__ __forceinline__ void compute_quad(const QuadRegs<TYPE == ZQ_TYPE_Q8_0
             unpack_q4<Q41 ? 0 : 8>(pick(r.a_lo, j), a_lo[0], a_lo[2], a_hi[0], a_hi[2]);
             unpack_q4<Q41 ? 0 : 8>(pick(r.b_lo, j), a_lo[1], a_lo[3], a_hi[1], a_hi[3]);
         }
-        if (Q41) {
-            da = half_lo(pick(r.sa, j));
-            ma = half_hi(pick(r.sa, j));
-            db = half_lo(pick(r.sb, j));
-            mb = half_hi(pick(r.sb, j));
-        } else {
-            const uint32_t wa = j < 2 ? r.sa.x : r.sa.y, wb = j < 2 ? r.sb.x : r.sb.y;
-            da = (j & 1) ? half_hi(wa) : half_lo(wa);
-            db = (j & 1) ? half_hi(wb) : half_lo(wb);
-        }
-        const uint32_t blk = q * 4 + j;
 #pragma unroll
         for (int c = 0; c < NS; ++c) {
-            const uint32_t col = 8 * c + g;
-            uint4 bf = make_uint4(0, 0, 0, 0);
-            if (col < ncols) bf = frag[((size_t)blk * ncols + col) * 4 + t];
+            const uint4 bf = lds128(faddr[c] + j * fstride[c]);
             float d1[4], d2[4];
             mma_f16(d1, a_lo, bf.x, bf.y, zero);
             mma_f16(d2, a_hi, bf.z, bf.w, d1);
-            acc[c][0] = fmaf(d2[0], da, acc[c][0]);
-            acc[c][1] = fmaf(d2[1], da, acc[c][1]);
-            acc[c][2] = fmaf(d2[2], db, acc[c][2]);
-            acc[c][3] = fmaf(d2[3], db, acc[c][3]);
+            acc[c][0] = fmaf(d2[0], da[j], acc[c][0]);
+            acc[c][1] = fmaf(d2[1], da[j], acc[c][1]);
+            acc[c][2] = fmaf(d2[2], db[j], acc[c][2]);
+            acc[c][3] = fmaf(d2[3], db[j], acc[c][3]);
             if (Q41) {
-                const uint32_t m = 4 * c + t;
-                const float xs_m = m < M ? xsum[blk * M + m] : 0.0f;
-                accm[c][0] = fmaf(ma, xs_m, accm[c][0]);
-                accm[c][1] = fmaf(mb, xs_m, accm[c][1]);
+                const float xs_m = lds_f32(xaddr[c] + j * xstride[c]);
+                accm[c][0] = fmaf(ma[j], xs_m, accm[c][0]);
+                accm[c][1] = fmaf(mb[j], xs_m, accm[c][1]);
             }
         }
     }
@@ -241,28 +307,78 @@ __device__ __forceinline__ void compute_quad(const QuadRegs<TYPE == ZQ_TYPE_Q8_0
 
 // Grid-stride over tiles of 16 rows x WR warps; the KS warps that share a row tile split the quads
 // of a row and are summed in a fixed order through shared memory.
+constexpr int kCtasPerSm = 2;  // more resident warps did not help: the kernel is bound by instruction work
+
 template <int TYPE, int NS>
-__global__ void __launch_bounds__(256, NS == 1 ? 3 : 2)
+__global__ void __launch_bounds__(256, kCtasPerSm)
 gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const float* __restrict__ x,
                 float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t scp, uint32_t M,
-                uint32_t WR, uint32_t KS, EpilogueArgs ep) {
+                uint32_t WR, uint32_t KS, uint32_t ring_off, EpilogueArgs ep) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QB = Q8 ? 32 : 16;
     constexpr uint32_t SB = Q41 ? 4 : 2;
 
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float pre[16], post[16];
     __shared__ unsigned int amax_bits[16];
 
     const uint32_t nbp = (nb + 3u) & ~3u, ncols = 2 * M;
-    uint4* frag = reinterpret_cast<uint4*>(smem_raw);
-    float* xsum = reinterpret_cast<float*>(frag + (size_t)nbp * ncols * 4);
-    float* red = xsum + (Q41 ? (size_t)nbp * M : 0);
+    uint4* frag = reinterpret_cast<uint4*>(smem_raw);                       // nbp * ncols * 4, then one zero slot
+    float* xsum = reinterpret_cast<float*>(frag + (size_t)nbp * ncols * 4 + 1);
+    float* red = xsum + (Q41 ? (size_t)nbp * M : 0);  // KS > 1: WR*KS*NS*2*32 floats
+    // per-warp cp.async ring, 128-byte aligned, behind everything else (offset passed by the host)
+    unsigned char* ring = smem_raw + ring_off;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t wr = warp % WR, ks = warp / WR;
+
+    const uint32_t nq = nbp / 4;
+    const uint32_t per = (nq + KS - 1) / KS;
+    const uint32_t q_lo = min(ks * per, nq), q_hi = min(q_lo + per, nq);
+    const uint32_t rows_per_cta = WR * 16;
+
+    // ---- weight stream: producer cursor runs kDepth-1 quads ahead of the consumer, across tiles;
+    //      the first copies are issued before the activations are staged so that both overlap ----
+    using R = Ring<Q8, Q41>;
+    constexpr int D = R::kDepth;
+    constexpr uint32_t QUAD = Q8 ? 128 : 64;  // quant bytes of one quad of blocks
+    constexpr uint32_t SQ = 4 * SB;           // scale bytes of one quad
+    const uint32_t ring32 = (uint32_t)__cvta_generic_to_shared(ring) + warp * D * R::kStage;
+    const uint32_t nqw = q_hi - q_lo;  // quads per tile for this warp
+
+    uint64_t p_tile = blockIdx.x;  // producer cursor
+    uint32_t p_q = 0, p_slot = 0;
+    const uint8_t *p_pa = qs, *p_pb = qs, *p_psa = sc, *p_psb = sc;
+    auto producer_set_tile = [&]() {
+        const uint32_t r = (uint32_t)(p_tile * rows_per_cta) + wr * 16 + g;
+        const uint32_t row_a = min(r, N - 1), row_b = min(r + 8, N - 1);
+        p_pa = qs + (size_t)row_a * nbp * QB + 16 * t + (size_t)q_lo * QUAD;
+        p_pb = qs + (size_t)row_b * nbp * QB + 16 * t + (size_t)q_lo * QUAD;
+        p_psa = sc + (size_t)row_a * scp * SB + (size_t)q_lo * SQ;
+        p_psb = sc + (size_t)row_b * scp * SB + (size_t)q_lo * SQ;
+    };
+    // issues the copies of the next quad (if any is left) and always closes a group, so that group
+    // number n holds quad number n of this warp's sequence
+    auto producer_step = [&]() {
+        if (nqw != 0 && p_tile * rows_per_cta < N) {
+            ring_issue<Q8, Q41>(ring32 + p_slot * R::kStage, lane, p_pa, p_pb, p_psa, p_psb);
+            p_slot = p_slot + 1 == (uint32_t)D ? 0 : p_slot + 1;
+            if (++p_q == nqw) {
+                p_q = 0;
+                p_tile += gridDim.x;
+                producer_set_tile();
+            } else {
+                p_pa += QUAD; p_pb += QUAD; p_psa += SQ; p_psb += SQ;
+            }
+        }
+        cp_async_commit();
+    };
+    producer_set_tile();
+#pragma unroll 1
+    for (int i = 0; i < D - 1; ++i) producer_step();
+    uint32_t c_slot = 0;
 
     // ---- activations: range prescale, then the fp16 hi/lo fragment image ----
     if (tid < 16) amax_bits[tid] = 0;
@@ -288,38 +404,53 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     }
     __syncthreads();
     stage_activations<Q41>(x, M, K, nb, nbp, pre, frag, xsum);
+    if (tid == 0) frag[(size_t)nbp * ncols * 4] = make_uint4(0, 0, 0, 0);
     __syncthreads();
 
-    const uint32_t nq = nbp / 4;
-    const uint32_t per = (nq + KS - 1) / KS;
-    const uint32_t q_lo = min(ks * per, nq), q_hi = min(q_lo + per, nq);
-    const uint32_t rows_per_cta = WR * 16;
+    // Per-lane shared addresses of the activation image (block 0) and strides per block. Columns /
+    // activation rows that do not exist read a zero slot with stride 0.
+    const uint32_t zero_slot = (uint32_t)__cvta_generic_to_shared(frag + (size_t)nbp * ncols * 4);
+    uint32_t fbase[NS], fstride[NS], xbase[NS], xstride[NS];
+#pragma unroll
+    for (int c = 0; c < NS; ++c) {
+        const uint32_t col = 8 * c + g;
+        const bool real = col < ncols;
+        fbase[c] = real ? (uint32_t)__cvta_generic_to_shared(frag + (size_t)col * 4 + t) : zero_slot;
+        fstride[c] = real ? ncols * 64 : 0;
+        const uint32_t m = 4 * c + t;
+        const bool xreal = Q41 && m < M;
+        xbase[c] = xreal ? (uint32_t)__cvta_generic_to_shared(xsum + m) : zero_slot;
+        xstride[c] = xreal ? M * 4 : 0;
+    }
 
     for (uint64_t tile = blockIdx.x; tile * rows_per_cta < N; tile += gridDim.x) {
         const uint32_t r0 = (uint32_t)(tile * rows_per_cta) + wr * 16 + g;
-        const uint32_t row_a = min(r0, N - 1), row_b = min(r0 + 8, N - 1);
-        const uint8_t* qa = qs + (size_t)row_a * nbp * QB + 16 * t;
-        const uint8_t* qb = qs + (size_t)row_b * nbp * QB + 16 * t;
-        const uint8_t* sa = sc + (size_t)row_a * scp * SB;
-        const uint8_t* sb = sc + (size_t)row_b * scp * SB;
+        uint32_t faddr[NS], xaddr[NS];
+#pragma unroll
+        for (int c = 0; c < NS; ++c) {
+            faddr[c] = fbase[c] + q_lo * 4 * fstride[c];
+            xaddr[c] = xbase[c] + q_lo * 4 * xstride[c];
+        }
         float acc[NS][4], accm[NS][2];
 #pragma unroll
         for (int c = 0; c < NS; ++c) {
             acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.0f;
             accm[c][0] = accm[c][1] = 0.0f;
         }
-        // two register sets: the loads of the next quad are in flight while this one is consumed
-        QuadRegs<Q8, Q41> ra, rb;
-        uint32_t q = q_lo;
-        if (q < q_hi) load_quad(ra, qa, qb, sa, sb, q);
-        while (q + 1 < q_hi) {
-            load_quad(rb, qa, qb, sa, sb, q + 1);
-            compute_quad<TYPE, NS>(ra, q, frag, xsum, ncols, M, g, t, acc, accm);
-            if (q + 2 < q_hi) load_quad(ra, qa, qb, sa, sb, q + 2);
-            compute_quad<TYPE, NS>(rb, q + 1, frag, xsum, ncols, M, g, t, acc, accm);
-            q += 2;
+#pragma unroll 1
+        for (uint32_t i = 0; i < nqw; ++i) {
+            producer_step();
+            cp_async_wait<D - 1>();  // all but the newest D-1 groups have landed: this quad is in the ring
+            QuadRegs<Q8, Q41> r;
+            ring_read<Q8, Q41>(r, ring32 + c_slot * R::kStage, lane);
+            c_slot = c_slot + 1 == (uint32_t)D ? 0 : c_slot + 1;
+            compute_quad<TYPE, NS>(r, faddr, fstride, xaddr, xstride, acc, accm);
+#pragma unroll
+            for (int c = 0; c < NS; ++c) {
+                faddr[c] += 4 * fstride[c];
+                xaddr[c] += 4 * xstride[c];
+            }
         }
-        if (q < q_hi) compute_quad<TYPE, NS>(ra, q, frag, xsum, ncols, M, g, t, acc, accm);
 
         // hi + lo columns -> one value per (row, activation row); lane (g, t) of set c owns
         // activation row 4c + t for weight rows g and g + 8.
@@ -368,7 +499,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
 }
 
 struct Plan {
-    uint32_t WR, KS, grid;
+    uint32_t WR, KS, grid, ring_off;
     size_t smem;
     bool fits;
 };
@@ -387,14 +518,20 @@ Plan make_plan(const zq_weight* w, uint32_t M, int ns) {
     while (warps > ks && (tiles + warps / ks - 1) / (warps / ks) < sms) warps /= 2;
     p.WR = warps / ks ? warps / ks : 1;
     p.KS = ks;
-    size_t smem = (size_t)w->nbp * 2 * M * 64;
+    size_t smem = (size_t)w->nbp * 2 * M * 64 + 16;  // activation image + zero slot
     if (q41) smem += (size_t)w->nbp * M * sizeof(float);
     if (ks > 1) smem += (size_t)p.WR * ks * ns * 2 * 32 * sizeof(float);
+    smem = (smem + 127) & ~(size_t)127;
+    p.ring_off = (uint32_t)smem;
+    const bool q8 = w->type == ZQ_TYPE_Q8_0;
+    const size_t stage = q8 ? Ring<true, false>::kStage : q41 ? Ring<false, true>::kStage : Ring<false, false>::kStage;
+    const size_t depth = q8 ? Ring<true, false>::kDepth : Ring<false, false>::kDepth;
+    smem += (size_t)p.WR * ks * depth * stage;
     p.smem = smem;
-    p.fits = smem <= 160 * 1024;
+    p.fits = smem <= 200 * 1024;
     const uint32_t cta_tiles = (tiles + p.WR - 1) / p.WR;
-    uint32_t per_sm = (uint32_t)((200 * 1024) / (smem + 1024));
-    if (per_sm > 8) per_sm = 8;
+    uint32_t per_sm = (uint32_t)((224 * 1024) / (smem + 1024));
+    if (per_sm > (uint32_t)kCtasPerSm) per_sm = kCtasPerSm;  // register budget set by the launch bounds
     if (per_sm < 1) per_sm = 1;
     const uint32_t cap = sms * per_sm;
     p.grid = cta_tiles < cap ? cta_tiles : cap;
@@ -409,7 +546,7 @@ int launch_one(const zq_weight* w, const float* x, float* y, uint32_t M, Epilogu
     if (p.smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
     kern<<<p.grid, p.WR * p.KS * 32, p.smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim,
-                                                    w->in_dim, w->nb, w->scp, M, p.WR, p.KS, ep);
+                                                    w->in_dim, w->nb, w->scp, M, p.WR, p.KS, p.ring_off, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }

@@ -1,0 +1,240 @@
+// Q8-activation decode GEMV: int8 activations (quantize_row_q8), exact int32 block dots with dp4a,
+// block terms (d*s)*float(idot) [+ (m*s)*float(qsum)] added in block order — the arithmetic of
+// zig-nn's ThreadPool.matmul (src/gguf/thread_pool.zig:96-181 -> src/gguf/simd_dot.zig:71-152), so the
+// outputs are bit-identical to that CPU path.
+//
+// Mapping (g = lane / 4, t = lane % 4). A warp owns 16 rows; lane (g, t) works on rows g and g + 8.
+// The device layout interleaves each group of 4 blocks (a quad) so that word t of the 4 blocks is 16
+// contiguous bytes: one 128-bit load gives the lane 8 weights of each of the 4 blocks. The lane forms
+// 4 partial integer dots; a 3-shuffle transpose-reduce inside the 4 lanes leaves the complete dot of
+// block 4q + t in lane t. That lane applies the block's scales and stores the f32 term to shared
+// memory. When every block of a row has its term, one lane adds them in block order. Because only
+// the terms (not partial sums) cross warps, K can be split over warps without changing a single bit.
+#include "zq_internal.h"
+
+namespace zq {
+namespace {
+
+struct EpilogueArgs {
+    const float* bias;
+    const float* mul;
+    const float* residual;
+    int gelu;
+};
+
+__device__ __forceinline__ float gelu_tanh(float v) {
+    const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
+    const float inner = __fmul_rn(0.7978845608f, __fadd_rn(v, cube));
+    return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, (float)tanh((double)inner)));
+}
+
+__device__ __forceinline__ float apply_epilogue(float v, const EpilogueArgs& ep, size_t j) {
+    if (ep.bias) v = __fadd_rn(v, ep.bias[j]);
+    if (ep.gelu) v = gelu_tanh(v);
+    if (ep.mul) v = __fmul_rn(v, ep.mul[j]);
+    if (ep.residual) v = __fadd_rn(ep.residual[j], v);
+    return v;
+}
+
+__device__ __forceinline__ uint32_t pick(const uint4& v, int j) {
+    return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
+}
+
+// Four partial dots p[j] (block j of the quad) held by each of the 4 lanes of a quad ->
+// the sum over the 4 lanes of p[t], delivered to lane t. Integer adds: exact in any order.
+__device__ __forceinline__ int quad_transpose_reduce(const int (&p)[4], int t) {
+    const bool upper = t & 2;
+    // lanes 0,1 keep blocks 0,1 and hand over 2,3; lanes 2,3 the other way round
+    const int keep0 = upper ? p[2] : p[0], keep1 = upper ? p[3] : p[1];
+    const int send0 = upper ? p[0] : p[2], send1 = upper ? p[1] : p[3];
+    const int a0 = keep0 + __shfl_xor_sync(0xFFFFFFFFu, send0, 2);
+    const int a1 = keep1 + __shfl_xor_sync(0xFFFFFFFFu, send1, 2);
+    const bool odd = t & 1;
+    const int keep = odd ? a1 : a0, send = odd ? a0 : a1;
+    return keep + __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+}
+
+// smem: xl[nq][4] uint4 | xh[nq][4] uint4 | xs[nbp] f32 | xsum[nbp] i32 | terms[WR][16][pitch] f32
+template <int TYPE>
+__global__ void __launch_bounds__(256)
+gemv_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const int8_t* __restrict__ xq,
+               const float* __restrict__ xscale, const int32_t* __restrict__ xqsum, float* __restrict__ y,
+               uint32_t N, uint32_t nb, uint32_t scp, uint32_t WR, uint32_t KS, EpilogueArgs ep) {
+    constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
+    constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
+    constexpr uint32_t QB = Q8 ? 32 : 16;
+    constexpr uint32_t QUAD = 4 * QB;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const uint32_t nbp = (nb + 3u) & ~3u, nq = nbp / 4;
+    const uint32_t pitch = nbp + 1;  // odd pitch: the 16 rows of a tile fall in different banks
+    uint4* xl = reinterpret_cast<uint4*>(smem_raw);
+    uint4* xh = xl + (size_t)nq * 4;
+    float* xs = reinterpret_cast<float*>(xh + (size_t)nq * 4);
+    int32_t* xsum = reinterpret_cast<int32_t*>(xs + nbp);
+    float* terms = reinterpret_cast<float*>(xsum + nbp);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t wr = warp % WR, ks = warp / WR;
+
+    // Activation image: word w of block b goes to xl/xh[b/4][w%4] component b%4 (xl: w < 4, xh: w >= 4),
+    // the same interleave as the weights. Blocks past nb (row padding) are zero with scale 1.
+    {
+        const uint32_t* xw = reinterpret_cast<const uint32_t*>(xq);
+        uint32_t* xl32 = reinterpret_cast<uint32_t*>(xl);
+        uint32_t* xh32 = reinterpret_cast<uint32_t*>(xh);
+        for (uint32_t i = tid; i < nbp * 8; i += blockDim.x) {
+            const uint32_t b = i >> 3, w = i & 7u;
+            const uint32_t v = b < nb ? xw[i] : 0u;
+            uint32_t* dst = w < 4 ? xl32 : xh32;
+            dst[((b >> 2) * 4 + (w & 3u)) * 4 + (b & 3u)] = v;
+        }
+        for (uint32_t b = tid; b < nbp; b += blockDim.x) {
+            xs[b] = b < nb ? xscale[b] : 1.0f;
+            xsum[b] = b < nb ? xqsum[b] : 0;
+        }
+    }
+    __syncthreads();
+
+    const uint32_t per = (nq + KS - 1) / KS;
+    const uint32_t q_lo = min(ks * per, nq), q_hi = min(q_lo + per, nq);
+    const uint32_t rows_per_cta = WR * 16;
+    float* my_terms = terms + (size_t)wr * 16 * pitch;
+
+    for (uint64_t tile = blockIdx.x; tile * rows_per_cta < N; tile += gridDim.x) {
+        const uint32_t r0 = (uint32_t)(tile * rows_per_cta) + wr * 16;
+        const uint32_t row_a = min(r0 + g, N - 1), row_b = min(r0 + g + 8, N - 1);
+        const uint8_t* pa = qs + (size_t)row_a * nbp * QB + 16 * t;
+        const uint8_t* pb = qs + (size_t)row_b * nbp * QB + 16 * t;
+        const uint8_t* sa = sc + (size_t)row_a * scp * (Q41 ? 4 : 2);
+        const uint8_t* sb = sc + (size_t)row_b * scp * (Q41 ? 4 : 2);
+
+#pragma unroll 2
+        for (uint32_t q = q_lo; q < q_hi; ++q) {
+            const uint4 wa = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD));
+            const uint4 wb = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD));
+            uint4 wa2 = wa, wb2 = wb;
+            if (Q8) {
+                wa2 = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD + 64));
+                wb2 = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD + 64));
+            }
+            const uint32_t blk = q * 4 + t;  // the block whose complete dot ends up in this lane
+            float da, db, ma = 0.0f, mb = 0.0f;
+            if (Q41) {
+                const __half2 ha = __ldg(reinterpret_cast<const __half2*>(sa) + blk);
+                const __half2 hb = __ldg(reinterpret_cast<const __half2*>(sb) + blk);
+                da = __low2float(ha); ma = __high2float(ha);
+                db = __low2float(hb); mb = __high2float(hb);
+            } else {
+                da = __half2float(__ldg(reinterpret_cast<const __half*>(sa) + blk));
+                db = __half2float(__ldg(reinterpret_cast<const __half*>(sb) + blk));
+            }
+            const uint4 xlo = xl[q * 4 + t], xhi = xh[q * 4 + t];
+            int pa4[4], pb4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int x0 = (int)pick(xlo, j), x1 = (int)pick(xhi, j);
+                if (Q8) {
+                    pa4[j] = __dp4a((int)pick(wa2, j), x1, __dp4a((int)pick(wa, j), x0, 0));
+                    pb4[j] = __dp4a((int)pick(wb2, j), x1, __dp4a((int)pick(wb, j), x0, 0));
+                } else {
+                    const uint32_t ua = pick(wa, j), ub = pick(wb, j);
+                    pa4[j] = __dp4a((int)((ua >> 4) & 0x0F0F0F0Fu), x1, __dp4a((int)(ua & 0x0F0F0F0Fu), x0, 0));
+                    pb4[j] = __dp4a((int)((ub >> 4) & 0x0F0F0F0Fu), x1, __dp4a((int)(ub & 0x0F0F0F0Fu), x0, 0));
+                }
+            }
+            int ia = quad_transpose_reduce(pa4, t), ib = quad_transpose_reduce(pb4, t);
+            const float s = xs[blk];
+            const int qsum = xsum[blk];
+            float ta, tb;
+            if (TYPE == ZQ_TYPE_Q4_0) {
+                ia -= 8 * qsum;  // sum((n-8)*q) = sum(n*q) - 8*sum(q), exact
+                ib -= 8 * qsum;
+            }
+            ta = __fmul_rn(__fmul_rn(da, s), (float)ia);
+            tb = __fmul_rn(__fmul_rn(db, s), (float)ib);
+            if (Q41) {
+                ta = __fadd_rn(ta, __fmul_rn(__fmul_rn(ma, s), (float)qsum));
+                tb = __fadd_rn(tb, __fmul_rn(__fmul_rn(mb, s), (float)qsum));
+            }
+            my_terms[g * pitch + blk] = ta;
+            my_terms[(g + 8) * pitch + blk] = tb;
+        }
+        if (KS > 1) __syncthreads(); else __syncwarp();
+
+        // one lane per row adds the row's terms in block order, as the CPU loop does
+        if (ks == 0 && lane < 16) {
+            const float* tr = my_terms + lane * pitch;
+            float run = 0.0f;
+            uint32_t b = 0;
+            for (; b + 4 <= nb; b += 4) {
+                const float t0 = tr[b], t1 = tr[b + 1], t2 = tr[b + 2], t3 = tr[b + 3];
+                run = __fadd_rn(run, t0); run = __fadd_rn(run, t1);
+                run = __fadd_rn(run, t2); run = __fadd_rn(run, t3);
+            }
+            for (; b < nb; ++b) run = __fadd_rn(run, tr[b]);
+            const uint32_t row = r0 + lane;
+            if (row < N) y[row] = apply_epilogue(run, ep, row);
+        }
+        if (KS > 1) __syncthreads(); else __syncwarp();  // terms are rewritten by the next tile
+    }
+}
+
+template <int TYPE>
+int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum, float* y,
+               EpilogueArgs ep, cudaStream_t st) {
+    const uint32_t tiles = (w->out_dim + 15) / 16;
+    const uint32_t sms = (uint32_t)sm_count();
+    const uint32_t nq = w->nbp / 4;
+    uint32_t ks = 1;
+    while (ks < 8 && tiles * ks < sms * 16 && nq / (ks * 2) >= 2) ks *= 2;
+    uint32_t warps = 8;
+    while (warps > ks && (tiles + warps / ks - 1) / (warps / ks) < sms) warps /= 2;
+    uint32_t wr = warps / ks ? warps / ks : 1;
+    const size_t fixed = (size_t)nq * 4 * 16 * 2 + (size_t)w->nbp * 8;
+    auto smem_for = [&](uint32_t r) { return fixed + (size_t)r * 16 * (w->nbp + 1) * sizeof(float); };
+    while (wr > 1 && smem_for(wr) > 96 * 1024) wr /= 2;
+    const size_t smem = smem_for(wr);
+    if (smem > 200 * 1024) return ZQ_ERR_LIMIT;
+    auto kern = gemv_q8_kernel<TYPE>;
+    if (smem > 48 * 1024)
+        ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const uint32_t cta_tiles = (tiles + wr - 1) / wr;
+    uint32_t per_sm = (uint32_t)((200 * 1024) / (smem + 1024));
+    if (per_sm > 4) per_sm = 4;
+    if (per_sm < 1) per_sm = 1;
+    const uint32_t cap = sms * per_sm;
+    kern<<<cta_tiles < cap ? cta_tiles : cap, wr * ks * 32, smem, st>>>(
+        w->qs, static_cast<const uint8_t*>(w->sc), xq, xs, xsum, y, w->out_dim, w->nb, w->scp, wr, ks, ep);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+}  // namespace
+
+int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum,
+                   float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st) {
+    for (uint32_t m = 0; m < m_rows; ++m) {
+        const size_t yo = (size_t)m * w->out_dim, bo = (size_t)m * w->nb;
+        EpilogueArgs a{nullptr, nullptr, nullptr, 0};
+        if (ep) {
+            a.bias = ep->d_bias;
+            a.gelu = ep->gelu;
+            a.mul = ep->d_mul ? ep->d_mul + yo : nullptr;
+            a.residual = ep->d_residual ? ep->d_residual + yo : nullptr;
+        }
+        const int8_t* q = xq + (size_t)m * w->in_dim;
+        int rc;
+        switch (w->type) {
+            case ZQ_TYPE_Q4_0: rc = launch_one<ZQ_TYPE_Q4_0>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
+            case ZQ_TYPE_Q4_1: rc = launch_one<ZQ_TYPE_Q4_1>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
+            case ZQ_TYPE_Q8_0: rc = launch_one<ZQ_TYPE_Q8_0>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
+            default: return ZQ_ERR_UNSUPPORTED;
+        }
+        if (rc != ZQ_OK) return rc;
+    }
+    return ZQ_OK;
+}
+
+}  // namespace zq
