@@ -66,21 +66,19 @@ __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
     return d;
 }
 
-// One 4-bit quant word -> fp16 pairs. lo = (e0, e2), (e1, e3) of the low nibbles, hi likewise.
-// (q & 0x000F000F) | 0x6400_6400 reads as (1024 + n, 1024 + n'); the 0x00F0 mask gives 1024 + 16 n.
-// OFF = 8 (q4_0: n - 8) or 0 (q4_1: n). All results are exact.
-template <int OFF>
+// One 4-bit quant word -> fp16 pairs (e0, e2), (e1, e3) of the low nibbles and of the high nibbles,
+// with no arithmetic at all: a nibble left in the low mantissa bits of an fp16 with exponent field 0
+// is the subnormal n * 2^-24 (low nibbles) or n * 2^-20 (high nibbles, bits 4..7). The tensor core
+// multiplies subnormals exactly; the high-nibble MMA gets activations pre-divided by 16, so both MMAs
+// accumulate sum(n * x) * 2^-24, and the factor 2^24 is applied once to the finished row. The "- 8"
+// of q4_0 becomes -8 * d * sum(x) per block, the same form as q4_1's m * sum(x).
 __device__ __forceinline__ void unpack_q4(uint32_t q, uint32_t& lo02, uint32_t& lo13, uint32_t& hi02,
                                           uint32_t& hi13) {
-    constexpr uint32_t kMagic = 0x64006400u;
-    constexpr uint32_t kSubLo = OFF == 8 ? 0x64086408u : 0x64006400u;   // 1024 + OFF
-    constexpr uint32_t kSixteenth = 0x2C002C00u;                        // 1/16
-    constexpr uint32_t kSubHi = OFF == 8 ? 0xD480D480u : 0xD400D400u;   // -(64 + OFF)
     const uint32_t s = q >> 8;
-    lo02 = hsub2_u32((q & 0x000F000Fu) | kMagic, kSubLo);
-    hi02 = hfma2_u32((q & 0x00F000F0u) | kMagic, kSixteenth, kSubHi);
-    lo13 = hsub2_u32((s & 0x000F000Fu) | kMagic, kSubLo);
-    hi13 = hfma2_u32((s & 0x00F000F0u) | kMagic, kSixteenth, kSubHi);
+    lo02 = q & 0x000F000Fu;
+    hi02 = q & 0x00F000F0u;
+    lo13 = s & 0x000F000Fu;
+    hi13 = s & 0x00F000F0u;
 }
 
 // One int8 quant word (elements e0..e3) -> fp16 pairs (e0, e2), (e1, e3), exact.
@@ -100,9 +98,10 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 //   frag[block][col][t] (uint4): B registers {low-MMA b0, b1, high-MMA b0, b1} that lane (g, t) feeds
 //     for MMA column `col` = 2 * activation row + part (0 = hi, 1 = lo); only the 2*M real columns
 //     are stored (lanes of the other columns feed zeros); blocks >= nb (row padding) are zero;
-//   xsum[block][M]: f32 sum of each activation row's 32 values (q4_1 only).
-// `pre[m]` is a power-of-two prescale that keeps |x| inside fp16 range (undone in the epilogue).
-template <bool WITH_SUM>
+//   xsum[block][M]: f32 sum of each activation row's 32 values (4-bit types).
+// `pre[m]` is a power-of-two prescale that brings the row's largest |x| just under 2^14 (undone in the
+// epilogue), so that the fp16 parts use the normal range whatever the scale of the activations.
+template <bool WITH_SUM, bool HI_DIV16>
 __device__ void stage_activations(const float* __restrict__ x, uint32_t M, uint32_t K, uint32_t nb,
                                   uint32_t nbp, const float* pre, uint4* frag, float* xsum) {
     const uint32_t ncols = 2 * M;
@@ -137,6 +136,10 @@ __device__ void stage_activations(const float* __restrict__ x, uint32_t M, uint3
         for (int j = 0; j < 8; ++j) {
             const float hi = __half2float(__float2half_rn(v[j]));
             w[j] = lo_part ? (v[j] - hi) : hi;  // x - hi is exact in f32
+        }
+        if (HI_DIV16) {  // exact: a power of two (tiny parts may round in the subnormal range)
+#pragma unroll
+            for (int j = 4; j < 8; ++j) w[j] *= 0.0625f;
         }
         if (active)
             frag[i] = make_uint4(pack_half2(w[0], w[2]), pack_half2(w[1], w[3]), pack_half2(w[4], w[6]),
@@ -198,6 +201,27 @@ __device__ __forceinline__ void ring_issue(uint32_t stage, int lane, const uint8
     }
 }
 
+// Direct global -> register load of one quad (alternative to the ring).
+template <bool Q8, bool Q41>
+__device__ __forceinline__ void load_quad_regs(QuadRegs<Q8, Q41>& r, const uint8_t* pa, const uint8_t* pb,
+                                               const uint8_t* psa, const uint8_t* psb) {
+    r.a_lo = __ldg(reinterpret_cast<const uint4*>(pa));
+    r.b_lo = __ldg(reinterpret_cast<const uint4*>(pb));
+    if (Q8) {
+        r.a_hi = __ldg(reinterpret_cast<const uint4*>(pa + 64));
+        r.b_hi = __ldg(reinterpret_cast<const uint4*>(pb + 64));
+    }
+    if (Q41) {
+        r.sa = __ldg(reinterpret_cast<const uint4*>(psa));
+        r.sb = __ldg(reinterpret_cast<const uint4*>(psb));
+    } else {
+        const uint2 va = __ldg(reinterpret_cast<const uint2*>(psa));
+        const uint2 vb = __ldg(reinterpret_cast<const uint2*>(psb));
+        r.sa.x = va.x; r.sa.y = va.y;
+        r.sb.x = vb.x; r.sb.y = vb.y;
+    }
+}
+
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -225,6 +249,28 @@ __device__ __forceinline__ void ring_read(QuadRegs<Q8, Q41>& r, uint32_t stage, 
         r.sa.x = va.x; r.sa.y = va.y;
         r.sb.x = vb.x; r.sb.y = vb.y;
     }
+}
+// Predicated forms: lanes whose stride is 0 own no column / activation row and read zeros without
+// touching shared memory (a warp-wide 128-bit load costs a wavefront per quarter warp that is active).
+__device__ __forceinline__ uint4 lds128_if(uint32_t addr, uint32_t pred) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.u32 p, %5, 0;\n\t"
+        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "r"(addr), "r"(pred));
+    return v;
+}
+__device__ __forceinline__ float lds_f32_if(uint32_t addr, uint32_t pred) {
+    float v = 0.0f;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.u32 p, %2, 0;\n\t"
+        "@p ld.shared.f32 %0, [%1];\n\t}"
+        : "+f"(v)
+        : "r"(addr), "r"(pred));
+    return v;
 }
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
     float v;
@@ -283,12 +329,12 @@ __device__ __forceinline__ void compute_quad(const QuadRegs<TYPE == ZQ_TYPE_Q8_0
             unpack_q8(pick(r.a_hi, j), a_hi[0], a_hi[2]);
             unpack_q8(pick(r.b_hi, j), a_hi[1], a_hi[3]);
         } else {
-            unpack_q4<Q41 ? 0 : 8>(pick(r.a_lo, j), a_lo[0], a_lo[2], a_hi[0], a_hi[2]);
-            unpack_q4<Q41 ? 0 : 8>(pick(r.b_lo, j), a_lo[1], a_lo[3], a_hi[1], a_hi[3]);
+            unpack_q4(pick(r.a_lo, j), a_lo[0], a_lo[2], a_hi[0], a_hi[2]);
+            unpack_q4(pick(r.b_lo, j), a_lo[1], a_lo[3], a_hi[1], a_hi[3]);
         }
 #pragma unroll
         for (int c = 0; c < NS; ++c) {
-            const uint4 bf = lds128(faddr[c] + j * fstride[c]);
+            const uint4 bf = lds128_if(faddr[c] + j * fstride[c], fstride[c]);
             float d1[4], d2[4];
             mma_f16(d1, a_lo, bf.x, bf.y, zero);
             mma_f16(d2, a_hi, bf.z, bf.w, d1);
@@ -296,10 +342,10 @@ __device__ __forceinline__ void compute_quad(const QuadRegs<TYPE == ZQ_TYPE_Q8_0
             acc[c][1] = fmaf(d2[1], da[j], acc[c][1]);
             acc[c][2] = fmaf(d2[2], db[j], acc[c][2]);
             acc[c][3] = fmaf(d2[3], db[j], acc[c][3]);
-            if (Q41) {
-                const float xs_m = lds_f32(xaddr[c] + j * xstride[c]);
-                accm[c][0] = fmaf(ma[j], xs_m, accm[c][0]);
-                accm[c][1] = fmaf(mb[j], xs_m, accm[c][1]);
+            if (!Q8) {  // q4_1: m * sum(x); q4_0: d * sum(x), times -8 at the end
+                const float xs_m = lds_f32_if(xaddr[c] + j * xstride[c], xstride[c]);
+                accm[c][0] = fmaf(Q41 ? ma[j] : da[j], xs_m, accm[c][0]);
+                accm[c][1] = fmaf(Q41 ? mb[j] : db[j], xs_m, accm[c][1]);
             }
         }
     }
@@ -309,7 +355,7 @@ __device__ __forceinline__ void compute_quad(const QuadRegs<TYPE == ZQ_TYPE_Q8_0
 // of a row and are summed in a fixed order through shared memory.
 constexpr int kCtasPerSm = 2;  // more resident warps did not help: the kernel is bound by instruction work
 
-template <int TYPE, int NS>
+template <int TYPE, int NS, bool USE_RING>
 __global__ void __launch_bounds__(256, kCtasPerSm)
 gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const float* __restrict__ x,
                 float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t scp, uint32_t M,
@@ -326,7 +372,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     const uint32_t nbp = (nb + 3u) & ~3u, ncols = 2 * M;
     uint4* frag = reinterpret_cast<uint4*>(smem_raw);                       // nbp * ncols * 4, then one zero slot
     float* xsum = reinterpret_cast<float*>(frag + (size_t)nbp * ncols * 4 + 1);
-    float* red = xsum + (Q41 ? (size_t)nbp * M : 0);  // KS > 1: WR*KS*NS*2*32 floats
+    float* red = xsum + (!Q8 ? (size_t)nbp * M : 0);  // KS > 1: WR*KS*NS*2*32 floats
     // per-warp cp.async ring, 128-byte aligned, behind everything else (offset passed by the host)
     unsigned char* ring = smem_raw + ring_off;
 
@@ -361,10 +407,15 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     };
     // issues the copies of the next quad (if any is left) and always closes a group, so that group
     // number n holds quad number n of this warp's sequence
+    QuadRegs<Q8, Q41> nxt;  // !USE_RING: the quad in flight lives in registers instead
     auto producer_step = [&]() {
         if (nqw != 0 && p_tile * rows_per_cta < N) {
-            ring_issue<Q8, Q41>(ring32 + p_slot * R::kStage, lane, p_pa, p_pb, p_psa, p_psb);
-            p_slot = p_slot + 1 == (uint32_t)D ? 0 : p_slot + 1;
+            if (USE_RING) {
+                ring_issue<Q8, Q41>(ring32 + p_slot * R::kStage, lane, p_pa, p_pb, p_psa, p_psb);
+                p_slot = p_slot + 1 == (uint32_t)D ? 0 : p_slot + 1;
+            } else {
+                load_quad_regs<Q8, Q41>(nxt, p_pa, p_pb, p_psa, p_psb);
+            }
             if (++p_q == nqw) {
                 p_q = 0;
                 p_tile += gridDim.x;
@@ -373,11 +424,11 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
                 p_pa += QUAD; p_pb += QUAD; p_psa += SQ; p_psb += SQ;
             }
         }
-        cp_async_commit();
+        if (USE_RING) cp_async_commit();
     };
     producer_set_tile();
 #pragma unroll 1
-    for (int i = 0; i < D - 1; ++i) producer_step();
+    for (int i = 0; i < (USE_RING ? D - 1 : 1); ++i) producer_step();
     uint32_t c_slot = 0;
 
     // ---- activations: range prescale, then the fp16 hi/lo fragment image ----
@@ -397,13 +448,13 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     __syncthreads();
     if (tid < (int)M) {
         const float amax = __uint_as_float(amax_bits[tid]);
-        int e = 0;
-        if (amax >= 32768.0f && amax < INFINITY) e = ilogbf(amax) - 14;
+        int e = 0;  // |x| * 2^-e < 2^14: both fp16 parts, and the parts divided by 16, stay normal
+        if (amax > 0.0f && amax < INFINITY) e = ilogbf(amax) - 13;
         pre[tid] = ldexpf(1.0f, -e);
         post[tid] = ldexpf(1.0f, e);
     }
     __syncthreads();
-    stage_activations<Q41>(x, M, K, nb, nbp, pre, frag, xsum);
+    stage_activations<!Q8, !Q8>(x, M, K, nb, nbp, pre, frag, xsum);
     if (tid == 0) frag[(size_t)nbp * ncols * 4] = make_uint4(0, 0, 0, 0);
     __syncthreads();
 
@@ -418,7 +469,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
         fbase[c] = real ? (uint32_t)__cvta_generic_to_shared(frag + (size_t)col * 4 + t) : zero_slot;
         fstride[c] = real ? ncols * 64 : 0;
         const uint32_t m = 4 * c + t;
-        const bool xreal = Q41 && m < M;
+        const bool xreal = !Q8 && m < M;
         xbase[c] = xreal ? (uint32_t)__cvta_generic_to_shared(xsum + m) : zero_slot;
         xstride[c] = xreal ? M * 4 : 0;
     }
@@ -439,11 +490,16 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
         }
 #pragma unroll 1
         for (uint32_t i = 0; i < nqw; ++i) {
-            producer_step();
-            cp_async_wait<D - 1>();  // all but the newest D-1 groups have landed: this quad is in the ring
             QuadRegs<Q8, Q41> r;
-            ring_read<Q8, Q41>(r, ring32 + c_slot * R::kStage, lane);
-            c_slot = c_slot + 1 == (uint32_t)D ? 0 : c_slot + 1;
+            if (USE_RING) {
+                producer_step();
+                cp_async_wait<D - 1>();  // all but the newest D-1 groups have landed: this quad is in the ring
+                ring_read<Q8, Q41>(r, ring32 + c_slot * R::kStage, lane);
+                c_slot = c_slot + 1 == (uint32_t)D ? 0 : c_slot + 1;
+            } else {
+                r = nxt;
+                producer_step();
+            }
             compute_quad<TYPE, NS>(r, faddr, fstride, xaddr, xstride, acc, accm);
 #pragma unroll
             for (int c = 0; c < NS; ++c) {
@@ -457,8 +513,14 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
         float out_a[NS], out_b[NS];
 #pragma unroll
         for (int c = 0; c < NS; ++c) {
-            out_a[c] = acc[c][0] + acc[c][1] + accm[c][0];
-            out_b[c] = acc[c][2] + acc[c][3] + accm[c][1];
+            if (Q8) {
+                out_a[c] = acc[c][0] + acc[c][1];
+                out_b[c] = acc[c][2] + acc[c][3];
+            } else {  // sums are in units of 2^-24; the block offsets/minimums were collected in accm
+                const float k = Q41 ? 1.0f : -8.0f;
+                out_a[c] = fmaf(acc[c][0] + acc[c][1], 16777216.0f, k * accm[c][0]);
+                out_b[c] = fmaf(acc[c][2] + acc[c][3], 16777216.0f, k * accm[c][1]);
+            }
         }
         if (KS > 1) {
             float* mine = red + ((size_t)(wr * KS + ks) * NS * 2) * 32;
@@ -506,7 +568,7 @@ struct Plan {
 
 // CTA shape: enough warps in flight on every SM; K is split across warps only when there are too
 // few row tiles to do that with one warp per tile.
-Plan make_plan(const zq_weight* w, uint32_t M, int ns) {
+Plan make_plan(const zq_weight* w, uint32_t M, int ns, bool use_ring) {
     Plan p{};
     const bool q41 = w->type == ZQ_TYPE_Q4_1;
     const uint32_t tiles = (w->out_dim + 15) / 16;
@@ -519,14 +581,14 @@ Plan make_plan(const zq_weight* w, uint32_t M, int ns) {
     p.WR = warps / ks ? warps / ks : 1;
     p.KS = ks;
     size_t smem = (size_t)w->nbp * 2 * M * 64 + 16;  // activation image + zero slot
-    if (q41) smem += (size_t)w->nbp * M * sizeof(float);
+    if (w->type != ZQ_TYPE_Q8_0) smem += (size_t)w->nbp * M * sizeof(float);
     if (ks > 1) smem += (size_t)p.WR * ks * ns * 2 * 32 * sizeof(float);
     smem = (smem + 127) & ~(size_t)127;
     p.ring_off = (uint32_t)smem;
     const bool q8 = w->type == ZQ_TYPE_Q8_0;
     const size_t stage = q8 ? Ring<true, false>::kStage : q41 ? Ring<false, true>::kStage : Ring<false, false>::kStage;
     const size_t depth = q8 ? Ring<true, false>::kDepth : Ring<false, false>::kDepth;
-    smem += (size_t)p.WR * ks * depth * stage;
+    if (use_ring) smem += (size_t)p.WR * ks * depth * stage;
     p.smem = smem;
     p.fits = smem <= 200 * 1024;
     const uint32_t cta_tiles = (tiles + p.WR - 1) / p.WR;
@@ -538,17 +600,28 @@ Plan make_plan(const zq_weight* w, uint32_t M, int ns) {
     return p;
 }
 
-template <int TYPE, int NS>
-int launch_one(const zq_weight* w, const float* x, float* y, uint32_t M, EpilogueArgs ep, cudaStream_t st) {
-    const Plan p = make_plan(w, M, NS);
+template <int TYPE, int NS, bool USE_RING>
+int launch_kernel(const zq_weight* w, const float* x, float* y, uint32_t M, EpilogueArgs ep, cudaStream_t st) {
+    const Plan p = make_plan(w, M, NS, USE_RING);
     if (!p.fits) return ZQ_ERR_LIMIT;
-    auto kern = gemv_mma_kernel<TYPE, NS>;
+    auto kern = gemv_mma_kernel<TYPE, NS, USE_RING>;
     if (p.smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
     kern<<<p.grid, p.WR * p.KS * 32, p.smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim,
                                                     w->in_dim, w->nb, w->scp, M, p.WR, p.KS, p.ring_off, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
+}
+
+// The shared-memory ring pays off on long streams of q4_0 / q8_0 rows (measured on the 170-320 MB
+// vocabulary head); q4_1 (wider scale copies) and weights of a few tens of MB run faster with the
+// next quad held in registers and more CTAs per SM.
+template <int TYPE, int NS>
+int launch_one(const zq_weight* w, const float* x, float* y, uint32_t M, EpilogueArgs ep, cudaStream_t st) {
+    const size_t quant_bytes = (size_t)w->out_dim * w->nbp * w->qb;
+    if (TYPE != ZQ_TYPE_Q4_1 && quant_bytes >= ((size_t)64 << 20))
+        return launch_kernel<TYPE, NS, true>(w, x, y, M, ep, st);
+    return launch_kernel<TYPE, NS, false>(w, x, y, M, ep, st);
 }
 
 template <int TYPE>
