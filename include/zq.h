@@ -142,6 +142,23 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
               const zq_epilogue* epilogue, void* d_workspace, size_t workspace_bytes,
               zq_stream stream);
 
+/* zq_matmul in ZQ_ACT_Q8 mode without a workspace argument and without any allocation: the scratch
+ * for the quantised activations is a fixed 320 KiB array inside the library's device image (every GPU
+ * that loads libzq holds it until the process exits). This entry point has no counterpart in the
+ * reference. It is for hosts that cannot allocate device memory at call time — a runtime that owns
+ * all device memory through its own pool, or a decode loop that must not risk cudaMalloc's implicit
+ * synchronisation or an out-of-memory error mid-request.
+ *   Limits: m_rows <= 16 and in_dim <= 16384, otherwise ZQ_ERR_LIMIT. Results are bit-identical to
+ *   zq_matmul(..., ZQ_ACT_Q8, ...).
+ *   First call on a device looks up the array's device address (cudaGetSymbolAddress) with that
+ *   device current; make that first call outside any stream capture.
+ *   All calls on a device share the one array: calls that may overlap on the GPU (different streams,
+ *   no ordering between them) race on it. Calls on one stream are safe. Nothing needs clearing
+ *   between calls: each call overwrites every entry it later reads.
+ *   Calls no cudaMalloc / cudaFree or other allocating routine. */
+int zq_matmul_q8_static(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
+                        const zq_epilogue* epilogue, zq_stream stream);
+
 /* quantize_row_q8 (src/gguf/simd_dot.zig:25-64) for m_rows rows of in_dim floats.
  * d_q: int8 [m_rows][in_dim]; d_scale: f32 [m_rows][in_dim/32]; d_sum: int32 [m_rows][in_dim/32]. */
 int zq_quantize_rows_q8(const float* d_x, uint32_t m_rows, uint32_t in_dim, int8_t* d_q,

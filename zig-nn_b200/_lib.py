@@ -38,6 +38,7 @@ SIGNATURES = {
     "zq_dequant_rows_scaled": (i, [vp, vp, u32, f, vp, vp]),
     "zq_matmul_workspace_bytes": (sz, [vp, u32, i]),
     "zq_matmul": (i, [vp, vp, vp, u32, i, P(S.Epilogue), vp, sz, vp]),
+    "zq_matmul_q8_static": (i, [vp, vp, vp, u32, P(S.Epilogue), vp]),
     "zq_quantize_rows_q8": (i, [vp, u32, u32, vp, vp, vp, vp]),
     "zq_matvec_f32": (i, [vp, vp, vp, u32, u32, vp]),
     "zq_argmax": (i, [vp, u32, vp, vp]),

@@ -114,6 +114,21 @@ def quant_matmul_no_grad(x, qw, act_mode=ACT_F32, bias=None, gelu=False, mul=Non
     return y
 
 
+def quant_matmul_q8_static(x, qw, bias=None, gelu=False, mul=None, residual=None, out=None):
+    """quant_matmul_no_grad(..., ACT_Q8) through the entry point that allocates nothing: its scratch
+    is a fixed array inside libzq (at most 16 rows, in_dim <= 16384; one call at a time per device)."""
+    lib = _lib.load()
+    x = _dev_f32(x)
+    if x.shape[-1] != qw.in_dim:
+        raise ValueError("last dim %d != in_dim %d" % (x.shape[-1], qw.in_dim))
+    m = x.numel() // qw.in_dim
+    y = out if out is not None else torch.empty(*x.shape[:-1], qw.out_dim, dtype=torch.float32, device=x.device)
+    ep = S.Epilogue(_ptr(bias), int(bool(gelu)), _ptr(mul), _ptr(residual))
+    _lib.check(lib.zq_matmul_q8_static(qw.handle, _ptr(x), _ptr(y), m, C.byref(ep), _stream()),
+               "zq_matmul_q8_static")
+    return y
+
+
 def quantize_rows_q8(x):
     x = _dev_f32(x)
     k = x.shape[-1]
