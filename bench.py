@@ -27,8 +27,8 @@ sys.path.insert(0, REPO)
 WORKLOAD = dict(qtype="q4_0", out_dim=262144, in_dim=1152, m_rows=1)
 BPB = {"q4_0": 18, "q4_1": 20, "q8_0": 34}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, from the ncu capture
-# summarised in profiles/ (None until a capture exists).
-NCU_TRAFFIC_BYTES = None
+# summarised in profiles/gemv_mma_q4_0_vocab_head_1152x262144.md (171 996 672 read + 5 198 592 written).
+NCU_TRAFFIC_BYTES = 177195264
 
 
 def algorithmic_bytes(qtype, n, k, m=1):
