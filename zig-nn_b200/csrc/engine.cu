@@ -3,6 +3,8 @@
 // Metal engine (src/models/gemma3_metal.zig:189-260). All tensors are uploaded once; a decode step
 // is a fixed sequence of kernel launches on the caller's stream with no host synchronisation.
 #include <math.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include <new>
 #include <vector>
@@ -60,21 +62,66 @@ int upload_linear(Linear* L, const zq_tensor_ref& t, uint32_t out_dim, uint32_t 
     return zq_weight_upload(t.data, t.type, out_dim, in_dim, st, &L->qw);
 }
 
-__global__ void set_u32_kernel(uint32_t* p, uint32_t v) { *p = v; }
-
-// x = wte[token] + wpe[pos]  (gpt2.zig:449-453)
-__global__ void gpt2_embed_kernel(float* __restrict__ x, const float* __restrict__ wte,
-                                  const float* __restrict__ wpe, const uint32_t* __restrict__ token,
-                                  uint32_t pos, uint32_t embed) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < embed) x[i] = wte[(size_t)(*token) * embed + i] + wpe[(size_t)pos * embed + i];
+// Step state in device memory: [0] current token, [1] its position, [2] next slot of the greedy record.
+__global__ void set_state_kernel(uint32_t* state, uint32_t token, uint32_t pos, uint32_t rec) {
+    state[0] = token;
+    state[1] = pos;
+    state[2] = rec;
+}
+// End of a greedy step: the argmax becomes the next token, is recorded, and the position advances.
+__global__ void greedy_feed_kernel(uint32_t* state, const int32_t* arg, uint32_t* record) {
+    const uint32_t tok = (uint32_t)*arg;
+    record[state[2]] = tok;
+    state[0] = tok;
+    state[1] += 1;
+    state[2] += 1;
 }
 
-__global__ void token_to_i32_kernel(int32_t* dst, const uint32_t* src) { *dst = (int32_t)*src; }
-__global__ void i32_to_token_kernel(uint32_t* dst, const int32_t* src, uint32_t* record) {
-    *dst = (uint32_t)*src;
-    if (record) *record = (uint32_t)*src;
-}
+// A decode step is a fixed launch sequence whose only varying inputs live in device memory, so it is
+// captured once per variant and replayed. The first use of a variant runs eagerly (function
+// attributes get set and launch errors surface outside capture); the second captures on the
+// engine's own stream (the caller's may be the legacy default stream, which cannot capture); every
+// use from then on is one graph launch on the caller's stream.
+enum StepVariant { STEP_CACHE_ONLY = 0, STEP_LOGITS = 1, STEP_GREEDY = 2, STEP_VARIANTS = 3 };
+
+struct StepGraphs {
+    cudaGraphExec_t exec[STEP_VARIANTS] = {nullptr, nullptr, nullptr};
+    bool warmed[STEP_VARIANTS] = {false, false, false};
+    cudaStream_t capture_stream = nullptr;
+    bool disabled = false;
+    ~StepGraphs() {
+        for (cudaGraphExec_t e : exec)
+            if (e) cudaGraphExecDestroy(e);
+        if (capture_stream) cudaStreamDestroy(capture_stream);
+    }
+    template <typename Body>
+    int run(int variant, cudaStream_t st, Body&& body) {
+        if (disabled) return body(st);
+        if (!warmed[variant]) {
+            warmed[variant] = true;
+            return body(st);
+        }
+        if (!exec[variant]) {
+            if (!capture_stream) ZQ_CUDA(cudaStreamCreateWithFlags(&capture_stream, cudaStreamNonBlocking));
+            ZQ_CUDA(cudaStreamBeginCapture(capture_stream, cudaStreamCaptureModeThreadLocal));
+            const int rc = body(capture_stream);
+            cudaGraph_t graph = nullptr;
+            const cudaError_t e = cudaStreamEndCapture(capture_stream, &graph);
+            if (rc != ZQ_OK || e != cudaSuccess) {
+                if (graph) cudaGraphDestroy(graph);
+                return rc != ZQ_OK ? rc : cuda_fail(e);
+            }
+            const cudaError_t ei = cudaGraphInstantiate(&exec[variant], graph, 0);
+            cudaGraphDestroy(graph);
+            if (ei != cudaSuccess) {
+                exec[variant] = nullptr;
+                return cuda_fail(ei);
+            }
+        }
+        ZQ_CUDA(cudaGraphLaunch(exec[variant], st));
+        return ZQ_OK;
+    }
+};
 
 }  // namespace
 }  // namespace zq
@@ -86,6 +133,7 @@ using namespace zq;
 struct zq_gpt2 {
     zq_gpt2_config c;
     DeviceArena arena;
+    StepGraphs graphs;
     float *wte = nullptr, *wpe = nullptr, *ln_f_w = nullptr, *ln_f_b = nullptr;
     struct Block {
         float *ln1_w, *ln1_b, *qkv_b, *proj_b, *ln2_w, *ln2_b, *fc_b, *mproj_b;
@@ -95,7 +143,7 @@ struct zq_gpt2 {
     std::vector<float*> k, v;  // per layer [ctx][embed]
     float *x = nullptr, *ln = nullptr, *qkv = nullptr, *att = nullptr, *hid = nullptr, *logits = nullptr;
     float* scores = nullptr;  // [head][ctx] attention scratch
-    uint32_t* d_token = nullptr;
+    uint32_t* d_state = nullptr;
     int32_t* d_arg = nullptr;
     uint32_t* d_record = nullptr;  // ctx entries for greedy decoding
     uint32_t seq_len = 0;
@@ -125,31 +173,39 @@ static int gpt2_linear(const Linear& L, const float* x, float* y, const float* b
     return rc;
 }
 
-// One decode step at position `pos`, token taken from m->d_token. Logits only when asked.
-static int gpt2_step(zq_gpt2* m, uint32_t pos, bool want_logits, cudaStream_t st) {
+// One decode step for the token and position held in m->d_state (gpt2.zig:423-509).
+static int gpt2_step(zq_gpt2* m, int variant, cudaStream_t st) {
     const zq_gpt2_config& C = m->c;
     const uint32_t E = C.embed, hd = E / C.head;
-    gpt2_embed_kernel<<<(E + 255) / 256, 256, 0, st>>>(m->x, m->wte, m->wpe, m->d_token, pos, E);
-    ZQ_LAUNCH_CHECK();
     int rc;
+    if ((rc = launch_gpt2_embed_step(m->x, m->wte, m->wpe, m->d_state, E, st))) return rc;
     for (uint32_t l = 0; l < C.layer; ++l) {
         const zq_gpt2::Block& b = m->blocks[l];
         if ((rc = zq_layer_norm(m->ln, m->x, b.ln1_w, b.ln1_b, 1, E, 1e-5f, st))) return rc;
         if ((rc = gpt2_linear(b.qkv, m->ln, m->qkv, b.qkv_b, 0, nullptr, st))) return rc;
-        if ((rc = zq_write_kv_cache(m->qkv + E, m->qkv + 2 * E, m->k[l], m->v[l], pos, E, st))) return rc;
-        if ((rc = zq_attention_decode(m->qkv, m->k[l], m->v[l], m->att, m->scores, C.head, C.head, hd, 0, pos + 1,
-                                      ZQ_ATTN_GPT2_SOFTMAX, st)))
+        if ((rc = launch_write_kv_step(m->qkv + E, m->qkv + 2 * E, m->k[l], m->v[l], m->d_state, E, st))) return rc;
+        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], m->att, nullptr, nullptr, nullptr, m->scores,
+                                        C.head, C.head, hd, m->d_state, 0, C.ctx, ZQ_ATTN_GPT2_SOFTMAX, st)))
             return rc;
         if ((rc = gpt2_linear(b.proj, m->att, m->x, b.proj_b, 0, m->x, st))) return rc;
         if ((rc = zq_layer_norm(m->ln, m->x, b.ln2_w, b.ln2_b, 1, E, 1e-5f, st))) return rc;
         if ((rc = gpt2_linear(b.fc, m->ln, m->hid, b.fc_b, 1, nullptr, st))) return rc;
         if ((rc = gpt2_linear(b.mproj, m->hid, m->x, b.mproj_b, 0, m->x, st))) return rc;
     }
-    if (want_logits) {
+    if (variant != STEP_CACHE_ONLY) {
         if ((rc = zq_layer_norm(m->ln, m->x, m->ln_f_w, m->ln_f_b, 1, E, 1e-5f, st))) return rc;
         if ((rc = zq_matvec_f32(m->wte, m->ln, m->logits, C.vocab, E, st))) return rc;
     }
+    if (variant == STEP_GREEDY) {
+        if ((rc = zq_argmax(m->logits, C.vocab, m->d_arg, st))) return rc;
+        greedy_feed_kernel<<<1, 1, 0, st>>>(m->d_state, m->d_arg, m->d_record);
+        ZQ_LAUNCH_CHECK();
+    }
     return ZQ_OK;
+}
+
+static int gpt2_run(zq_gpt2* m, int variant, cudaStream_t st) {
+    return m->graphs.run(variant, st, [&](cudaStream_t s) { return gpt2_step(m, variant, s); });
 }
 
 extern "C" {
@@ -161,9 +217,11 @@ int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_strea
     if (!cfg->vocab || !cfg->embed || !cfg->head || !cfg->layer || !cfg->ctx || !cfg->ffn ||
         cfg->embed % cfg->head || cfg->embed % 32 || cfg->ffn % 32)
         return ZQ_ERR_BAD_ARG;
+    if (cfg->ctx > 200 * 1024 / 4) return ZQ_ERR_LIMIT;  // one attention row must fit shared memory
     zq_gpt2* m = new (std::nothrow) zq_gpt2;
     if (!m) return ZQ_ERR_NO_MEM;
     m->c = *cfg;
+    m->graphs.disabled = getenv("ZQ_NO_GRAPH") != nullptr;
     cudaStream_t st = as_stream(stream);
     const uint32_t E = cfg->embed, F = cfg->ffn;
     int rc = ZQ_OK;
@@ -208,7 +266,7 @@ int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_strea
     TRY(m->arena.alloc_n(&m->hid, F));
     TRY(m->arena.alloc_n(&m->logits, cfg->vocab));
     TRY(m->arena.alloc_n(&m->scores, (size_t)cfg->head * cfg->ctx));
-    TRY(m->arena.alloc_n(&m->d_token, 1));
+    TRY(m->arena.alloc_n(&m->d_state, 4));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, cfg->ctx));
 #undef TRY
@@ -242,13 +300,14 @@ int zq_gpt2_prefill(zq_gpt2* m, const uint32_t* h_tokens, uint32_t n, zq_stream 
                     const float** d_logits) {
     if (!m || !h_tokens || !d_logits) return ZQ_ERR_BAD_ARG;
     if (n == 0 || n > m->c.ctx) return ZQ_ERR_SEQUENCE;
+    for (uint32_t t = 0; t < n; ++t)
+        if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
     m->seq_len = 0;
     for (uint32_t t = 0; t < n; ++t) {
-        if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
-        set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, h_tokens[t]);
+        set_state_kernel<<<1, 1, 0, st>>>(m->d_state, h_tokens[t], t, 0);
         ZQ_LAUNCH_CHECK();
-        int rc = gpt2_step(m, t, t + 1 == n, st);
+        int rc = gpt2_run(m, t + 1 == n ? STEP_LOGITS : STEP_CACHE_ONLY, st);
         if (rc != ZQ_OK) return rc;
     }
     m->seq_len = n;
@@ -261,9 +320,9 @@ int zq_gpt2_decode_next(zq_gpt2* m, uint32_t token, zq_stream stream, const floa
     if (m->seq_len >= m->c.ctx) return ZQ_ERR_SEQUENCE;
     if (token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
-    set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, token);
+    set_state_kernel<<<1, 1, 0, st>>>(m->d_state, token, m->seq_len, 0);
     ZQ_LAUNCH_CHECK();
-    int rc = gpt2_step(m, m->seq_len, true, st);
+    int rc = gpt2_run(m, STEP_LOGITS, st);
     if (rc != ZQ_OK) return rc;
     m->seq_len += 1;
     *d_logits = m->logits;
@@ -277,15 +336,12 @@ int zq_gpt2_decode_greedy(zq_gpt2* m, uint32_t first_token, uint32_t n_steps, zq
     if ((uint64_t)m->seq_len + n_steps > m->c.ctx) return ZQ_ERR_SEQUENCE;
     if (first_token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
-    set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, first_token);
+    set_state_kernel<<<1, 1, 0, st>>>(m->d_state, first_token, m->seq_len, 0);
     ZQ_LAUNCH_CHECK();
     for (uint32_t s = 0; s < n_steps; ++s) {
-        int rc = gpt2_step(m, m->seq_len, true, st);
+        int rc = gpt2_run(m, STEP_GREEDY, st);
         if (rc != ZQ_OK) return rc;
         m->seq_len += 1;
-        if ((rc = zq_argmax(m->logits, m->c.vocab, m->d_arg, st))) return rc;
-        i32_to_token_kernel<<<1, 1, 0, st>>>(m->d_token, m->d_arg, m->d_record + s);
-        ZQ_LAUNCH_CHECK();
     }
     ZQ_CUDA(cudaMemcpyAsync(h_tokens_out, m->d_record, n_steps * sizeof(uint32_t),
                             cudaMemcpyDeviceToHost, st));
@@ -300,33 +356,36 @@ int zq_gpt2_decode_greedy(zq_gpt2* m, uint32_t first_token, uint32_t n_steps, zq
 struct zq_gemma3 {
     zq_gemma3_config c;
     DeviceArena arena;
+    StepGraphs graphs;
     zq_weight* token_embd = nullptr;
     float* output_norm_w = nullptr;
     struct Block {
         float *attn_norm_w, *post_attn_norm_w, *q_norm_w, *k_norm_w, *ffn_norm_w, *post_ffw_norm_w;
-        zq_weight *q, *k, *v, *o, *gate, *up, *down;
+        // q|k|v and gate|up are stored as one matrix each when their types agree (rows are independent,
+        // so stacking them changes no result and saves launches); otherwise the parts stay separate.
+        zq_weight *qkv, *q, *k, *v, *o, *gate_up, *gate, *up, *down;
     };
     std::vector<Block> blocks;
     std::vector<float*> k, v;  // per layer [ctx][kv_dim]
     float* freqs = nullptr;
-    float *x = nullptr, *h = nullptr, *q = nullptr, *kb = nullptr, *vb = nullptr, *att = nullptr,
-          *proj = nullptr, *gate = nullptr, *up = nullptr, *ffn = nullptr, *logits = nullptr;
+    float *x = nullptr, *qkv = nullptr, *proj = nullptr, *gu = nullptr, *ffn = nullptr, *logits = nullptr;
     float* scores = nullptr;  // [head][ctx] attention scratch
-    int8_t* xq = nullptr;   // quantised activation row, max(embed, ffn, q_dim)
+    int8_t* xq = nullptr;     // quantised activation row, max(embed, ffn, q_dim)
     float* xscale = nullptr;
     int32_t* xsum = nullptr;
-    uint32_t* d_token = nullptr;
-    int32_t* d_tok_i32 = nullptr;
+    uint32_t* d_state = nullptr;
     int32_t* d_arg = nullptr;
     uint32_t* d_record = nullptr;
     uint32_t seq_len = 0;
     ~zq_gemma3() {
         zq_weight_free(token_embd);
         for (auto& b : blocks) {
+            zq_weight_free(b.qkv);
             zq_weight_free(b.q);
             zq_weight_free(b.k);
             zq_weight_free(b.v);
             zq_weight_free(b.o);
+            zq_weight_free(b.gate_up);
             zq_weight_free(b.gate);
             zq_weight_free(b.up);
             zq_weight_free(b.down);
@@ -334,59 +393,104 @@ struct zq_gemma3 {
     }
 };
 
-// Quantise the row once (thread_pool.zig:111-114), then any number of weights can consume it.
-static int gemma_quantize(zq_gemma3* m, const float* x, uint32_t dim, cudaStream_t st) {
-    return launch_quantize_rows_q8(x, 1, dim, m->xq, m->xscale, m->xsum, st);
-}
+// The activation row is quantised once (thread_pool.zig:111-114); any number of weights consume it.
 static int gemma_gemv(zq_gemma3* m, const zq_weight* w, float* y, cudaStream_t st) {
     return launch_gemv_q8(w, m->xq, m->xscale, m->xsum, y, 1, nullptr, st);
 }
 
-static int gemma3_step(zq_gemma3* m, uint32_t pos, bool want_logits, cudaStream_t st) {
+// One decode step for the token and position held in m->d_state (gemma3.zig:551-846), about ten
+// launches per layer: [norm+quantise] qkv | qk-norm+rope+cache | scores | softmax.V+quantise | o |
+// post-norm+residual+pre-norm+quantise | gate,up | gelu.mul+quantise | down | post-norm+residual+...
+static int gemma3_step(zq_gemma3* m, int variant, cudaStream_t st) {
     const zq_gemma3_config& C = m->c;
     const uint32_t E = C.embed, D = C.head_dim, QD = C.head * D, KD = C.head_kv * D, F = C.ffn;
     int rc;
-    token_to_i32_kernel<<<1, 1, 0, st>>>(m->d_tok_i32, m->d_token);
-    ZQ_LAUNCH_CHECK();
-    if ((rc = zq_dequant_rows_scaled(m->token_embd, m->d_tok_i32, 1, sqrtf((float)E), m->x, st))) return rc;
+    if ((rc = zq_dequant_rows_scaled(m->token_embd, reinterpret_cast<const int32_t*>(m->d_state), 1,
+                                     sqrtf((float)E), m->x, st)))
+        return rc;
+    if ((rc = launch_norm_quant(m->x, m->blocks[0].attn_norm_w, nullptr, nullptr, E, C.rms_eps, m->xq,
+                                m->xscale, m->xsum, st)))
+        return rc;
     for (uint32_t l = 0; l < C.layer; ++l) {
         const zq_gemma3::Block& b = m->blocks[l];
         // attention block (gemma3.zig:662-731)
-        if ((rc = zq_rms_norm(m->x, b.attn_norm_w, m->h, E, 1, C.rms_eps, st))) return rc;
-        if ((rc = gemma_quantize(m, m->h, E, st))) return rc;
-        if ((rc = gemma_gemv(m, b.q, m->q, st))) return rc;
-        if ((rc = gemma_gemv(m, b.k, m->kb, st))) return rc;
-        if ((rc = gemma_gemv(m, b.v, m->vb, st))) return rc;
-        if ((rc = zq_rms_norm_in_place(m->q, b.q_norm_w, D, C.head, C.rms_eps, st))) return rc;
-        if ((rc = zq_rms_norm_in_place(m->kb, b.k_norm_w, D, C.head_kv, C.rms_eps, st))) return rc;
-        if ((rc = zq_rope(m->q, m->freqs, D / 2, C.head, (float)pos, st))) return rc;
-        if ((rc = zq_rope(m->kb, m->freqs, D / 2, C.head_kv, (float)pos, st))) return rc;
-        if ((rc = zq_write_kv_cache(m->kb, m->vb, m->k[l], m->v[l], pos, KD, st))) return rc;
-        const bool global = (l % C.global_every) == C.global_every - 1;
-        const uint32_t kv_len = pos + 1;
-        const uint32_t window = global ? kv_len : (kv_len < C.sliding_window ? kv_len : C.sliding_window);
-        const uint32_t kv_start = kv_len - window;
-        if ((rc = zq_attention_decode(m->q, m->k[l], m->v[l], m->att, m->scores, C.head, C.head_kv, D, kv_start,
-                                      kv_len, 0, st)))
+        if (b.qkv) {
+            if ((rc = gemma_gemv(m, b.qkv, m->qkv, st))) return rc;
+        } else {
+            if ((rc = gemma_gemv(m, b.q, m->qkv, st))) return rc;
+            if ((rc = gemma_gemv(m, b.k, m->qkv + QD, st))) return rc;
+            if ((rc = gemma_gemv(m, b.v, m->qkv + QD + KD, st))) return rc;
+        }
+        if ((rc = launch_qk_norm_rope_kv(m->qkv, b.q_norm_w, b.k_norm_w, m->freqs, m->k[l], m->v[l], m->d_state,
+                                         C.head, C.head_kv, D, C.rms_eps, st)))
             return rc;
-        if ((rc = gemma_quantize(m, m->att, QD, st))) return rc;
+        const bool global = (l % C.global_every) == C.global_every - 1;
+        const uint32_t window = global ? 0u : C.sliding_window;
+        const uint32_t max_len = (window && window < C.ctx) ? window : C.ctx;
+        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], nullptr, m->xq, m->xscale, m->xsum, m->scores,
+                                        C.head, C.head_kv, D, m->d_state, window, max_len, 0, st)))
+            return rc;
         if ((rc = gemma_gemv(m, b.o, m->proj, st))) return rc;
-        if ((rc = zq_rms_norm_residual(m->proj, b.post_attn_norm_w, m->x, E, 1, C.rms_eps, st))) return rc;
+        if ((rc = launch_norm_quant(m->proj, b.post_attn_norm_w, m->x, b.ffn_norm_w, E, C.rms_eps, m->xq,
+                                    m->xscale, m->xsum, st)))
+            return rc;
         // FFN block (gemma3.zig:734-773)
-        if ((rc = zq_rms_norm(m->x, b.ffn_norm_w, m->h, E, 1, C.rms_eps, st))) return rc;
-        if ((rc = gemma_quantize(m, m->h, E, st))) return rc;
-        if ((rc = gemma_gemv(m, b.gate, m->gate, st))) return rc;
-        if ((rc = gemma_gemv(m, b.up, m->up, st))) return rc;
-        if ((rc = zq_gelu_mul(m->gate, m->up, F, st))) return rc;
-        if ((rc = gemma_quantize(m, m->gate, F, st))) return rc;
+        if (b.gate_up) {
+            if ((rc = gemma_gemv(m, b.gate_up, m->gu, st))) return rc;
+        } else {
+            if ((rc = gemma_gemv(m, b.gate, m->gu, st))) return rc;
+            if ((rc = gemma_gemv(m, b.up, m->gu + F, st))) return rc;
+        }
+        if ((rc = launch_gelu_mul_quant(m->gu, m->gu + F, F, m->xq, m->xscale, m->xsum, st))) return rc;
         if ((rc = gemma_gemv(m, b.down, m->ffn, st))) return rc;
-        if ((rc = zq_rms_norm_residual(m->ffn, b.post_ffw_norm_w, m->x, E, 1, C.rms_eps, st))) return rc;
+        const float* next_norm = l + 1 < C.layer ? m->blocks[l + 1].attn_norm_w
+                                 : (variant != STEP_CACHE_ONLY ? m->output_norm_w : nullptr);
+        if (next_norm) {
+            if ((rc = launch_norm_quant(m->ffn, b.post_ffw_norm_w, m->x, next_norm, E, C.rms_eps, m->xq, m->xscale,
+                                        m->xsum, st)))
+                return rc;
+        } else if ((rc = zq_rms_norm_residual(m->ffn, b.post_ffw_norm_w, m->x, E, 1, C.rms_eps, st))) {
+            return rc;
+        }
     }
-    if (want_logits) {
-        if ((rc = zq_rms_norm(m->x, m->output_norm_w, m->h, E, 1, C.rms_eps, st))) return rc;
-        if ((rc = gemma_quantize(m, m->h, E, st))) return rc;
+    if (variant != STEP_CACHE_ONLY) {
         if ((rc = gemma_gemv(m, m->token_embd, m->logits, st))) return rc;
     }
+    if (variant == STEP_GREEDY) {
+        if ((rc = zq_argmax(m->logits, C.vocab, m->d_arg, st))) return rc;
+        greedy_feed_kernel<<<1, 1, 0, st>>>(m->d_state, m->d_arg, m->d_record);
+        ZQ_LAUNCH_CHECK();
+    }
+    return ZQ_OK;
+}
+
+static int gemma3_run(zq_gemma3* m, int variant, cudaStream_t st) {
+    return m->graphs.run(variant, st, [&](cudaStream_t s) { return gemma3_step(m, variant, s); });
+}
+
+// Upload several GGUF matrices with the same in_dim and type as one matrix of stacked rows.
+static int upload_stacked(zq_weight** dst, const zq_tensor_ref* const* parts, int n_parts, uint32_t in_dim,
+                          cudaStream_t st) {
+    size_t total_rows = 0, total_bytes = 0;
+    for (int i = 0; i < n_parts; ++i) {
+        total_rows += parts[i]->out_dim;
+        total_bytes += zq_tensor_bytes(parts[i]->type, (size_t)parts[i]->out_dim * in_dim);
+    }
+    std::vector<uint8_t> host;
+    try {
+        host.resize(total_bytes);
+    } catch (...) {
+        return ZQ_ERR_NO_MEM;
+    }
+    size_t off = 0;
+    for (int i = 0; i < n_parts; ++i) {
+        const size_t nbytes = zq_tensor_bytes(parts[i]->type, (size_t)parts[i]->out_dim * in_dim);
+        memcpy(host.data() + off, parts[i]->data, nbytes);
+        off += nbytes;
+    }
+    int rc = zq_weight_upload(host.data(), parts[0]->type, (uint32_t)total_rows, in_dim, st, dst);
+    if (rc != ZQ_OK) return rc;
+    ZQ_CUDA(cudaStreamSynchronize(st));  // `host` is released on return
     return ZQ_OK;
 }
 
@@ -404,9 +508,11 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
     uint32_t max_dim = E > F ? E : F;
     if (QD > max_dim) max_dim = QD;
     if (max_dim > 16384) return ZQ_ERR_LIMIT;
+    if (C.ctx > 200 * 1024 / 4) return ZQ_ERR_LIMIT;  // one attention row must fit shared memory
     zq_gemma3* m = new (std::nothrow) zq_gemma3;
     if (!m) return ZQ_ERR_NO_MEM;
     m->c = C;
+    m->graphs.disabled = getenv("ZQ_NO_GRAPH") != nullptr;
     cudaStream_t st = as_stream(stream);
     int rc = ZQ_OK;
 #define TRY(expr)                  \
@@ -416,10 +522,14 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
             return rc;             \
         }                          \
     } while (0)
-    auto up_q = [&](zq_weight** dst, const zq_tensor_ref& t, uint32_t od, uint32_t id) -> int {
+    auto check_q = [&](const zq_tensor_ref& t, uint32_t od, uint32_t id) -> int {
         if (!t.data || t.out_dim != od || t.in_dim != id) return ZQ_ERR_BAD_ARG;
         if (!is_quant(t.type)) return ZQ_ERR_UNSUPPORTED;
-        return zq_weight_upload(t.data, t.type, od, id, st, dst);
+        return ZQ_OK;
+    };
+    auto up_q = [&](zq_weight** dst, const zq_tensor_ref& t, uint32_t od, uint32_t id) -> int {
+        int r = check_q(t, od, id);
+        return r != ZQ_OK ? r : zq_weight_upload(t.data, t.type, od, id, st, dst);
     };
     TRY(up_q(&m->token_embd, w->token_embd, C.vocab, E));
     TRY(m->arena.upload_f32(&m->output_norm_w, w->output_norm_weight, E, st));
@@ -435,12 +545,27 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
         TRY(m->arena.upload_f32(&b.k_norm_w, s.attn_k_norm_weight, D, st));
         TRY(m->arena.upload_f32(&b.ffn_norm_w, s.ffn_norm_weight, E, st));
         TRY(m->arena.upload_f32(&b.post_ffw_norm_w, s.post_ffw_norm_weight, E, st));
-        TRY(up_q(&b.q, s.attn_q_weight, QD, E));
-        TRY(up_q(&b.k, s.attn_k_weight, KD, E));
-        TRY(up_q(&b.v, s.attn_v_weight, KD, E));
+        TRY(check_q(s.attn_q_weight, QD, E));
+        TRY(check_q(s.attn_k_weight, KD, E));
+        TRY(check_q(s.attn_v_weight, KD, E));
+        if (s.attn_q_weight.type == s.attn_k_weight.type && s.attn_q_weight.type == s.attn_v_weight.type) {
+            const zq_tensor_ref* parts[3] = {&s.attn_q_weight, &s.attn_k_weight, &s.attn_v_weight};
+            TRY(upload_stacked(&b.qkv, parts, 3, E, st));
+        } else {
+            TRY(up_q(&b.q, s.attn_q_weight, QD, E));
+            TRY(up_q(&b.k, s.attn_k_weight, KD, E));
+            TRY(up_q(&b.v, s.attn_v_weight, KD, E));
+        }
         TRY(up_q(&b.o, s.attn_output_weight, E, QD));
-        TRY(up_q(&b.gate, s.ffn_gate_weight, F, E));
-        TRY(up_q(&b.up, s.ffn_up_weight, F, E));
+        TRY(check_q(s.ffn_gate_weight, F, E));
+        TRY(check_q(s.ffn_up_weight, F, E));
+        if (s.ffn_gate_weight.type == s.ffn_up_weight.type) {
+            const zq_tensor_ref* parts[2] = {&s.ffn_gate_weight, &s.ffn_up_weight};
+            TRY(upload_stacked(&b.gate_up, parts, 2, E, st));
+        } else {
+            TRY(up_q(&b.gate, s.ffn_gate_weight, F, E));
+            TRY(up_q(&b.up, s.ffn_up_weight, F, E));
+        }
         TRY(up_q(&b.down, s.ffn_down_weight, E, F));
         TRY(m->arena.alloc_n(&m->k[l], (size_t)C.ctx * KD));
         TRY(m->arena.alloc_n(&m->v[l], (size_t)C.ctx * KD));
@@ -460,22 +585,16 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
         }
     }
     TRY(m->arena.alloc_n(&m->x, E));
-    TRY(m->arena.alloc_n(&m->h, E));
-    TRY(m->arena.alloc_n(&m->q, QD));
-    TRY(m->arena.alloc_n(&m->kb, KD));
-    TRY(m->arena.alloc_n(&m->vb, KD));
-    TRY(m->arena.alloc_n(&m->att, QD));
+    TRY(m->arena.alloc_n(&m->qkv, (size_t)QD + 2 * KD));
     TRY(m->arena.alloc_n(&m->proj, E));
-    TRY(m->arena.alloc_n(&m->gate, F));
-    TRY(m->arena.alloc_n(&m->up, F));
+    TRY(m->arena.alloc_n(&m->gu, 2 * (size_t)F));
     TRY(m->arena.alloc_n(&m->ffn, E));
     TRY(m->arena.alloc_n(&m->logits, C.vocab));
     TRY(m->arena.alloc_n(&m->scores, (size_t)C.head * C.ctx));
     TRY(m->arena.alloc_n(&m->xq, max_dim));
     TRY(m->arena.alloc_n(&m->xscale, max_dim / 32));
     TRY(m->arena.alloc_n(&m->xsum, max_dim / 32));
-    TRY(m->arena.alloc_n(&m->d_token, 1));
-    TRY(m->arena.alloc_n(&m->d_tok_i32, 1));
+    TRY(m->arena.alloc_n(&m->d_state, 4));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, C.ctx));
 #undef TRY
@@ -509,13 +628,14 @@ int zq_gemma3_prefill(zq_gemma3* m, const uint32_t* h_tokens, uint32_t n, zq_str
                       const float** d_logits) {
     if (!m || !h_tokens || !d_logits) return ZQ_ERR_BAD_ARG;
     if (n == 0 || n > m->c.ctx) return ZQ_ERR_SEQUENCE;
+    for (uint32_t t = 0; t < n; ++t)
+        if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
     m->seq_len = 0;
     for (uint32_t t = 0; t < n; ++t) {
-        if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
-        set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, h_tokens[t]);
+        set_state_kernel<<<1, 1, 0, st>>>(m->d_state, h_tokens[t], t, 0);
         ZQ_LAUNCH_CHECK();
-        int rc = gemma3_step(m, t, t + 1 == n, st);
+        int rc = gemma3_run(m, t + 1 == n ? STEP_LOGITS : STEP_CACHE_ONLY, st);
         if (rc != ZQ_OK) return rc;
     }
     m->seq_len = n;
@@ -528,9 +648,9 @@ int zq_gemma3_decode_next(zq_gemma3* m, uint32_t token, zq_stream stream, const 
     if (m->seq_len >= m->c.ctx) return ZQ_ERR_SEQUENCE;
     if (token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
-    set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, token);
+    set_state_kernel<<<1, 1, 0, st>>>(m->d_state, token, m->seq_len, 0);
     ZQ_LAUNCH_CHECK();
-    int rc = gemma3_step(m, m->seq_len, true, st);
+    int rc = gemma3_run(m, STEP_LOGITS, st);
     if (rc != ZQ_OK) return rc;
     m->seq_len += 1;
     *d_logits = m->logits;
@@ -544,15 +664,12 @@ int zq_gemma3_decode_greedy(zq_gemma3* m, uint32_t first_token, uint32_t n_steps
     if ((uint64_t)m->seq_len + n_steps > m->c.ctx) return ZQ_ERR_SEQUENCE;
     if (first_token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
-    set_u32_kernel<<<1, 1, 0, st>>>(m->d_token, first_token);
+    set_state_kernel<<<1, 1, 0, st>>>(m->d_state, first_token, m->seq_len, 0);
     ZQ_LAUNCH_CHECK();
     for (uint32_t s = 0; s < n_steps; ++s) {
-        int rc = gemma3_step(m, m->seq_len, true, st);
+        int rc = gemma3_run(m, STEP_GREEDY, st);
         if (rc != ZQ_OK) return rc;
         m->seq_len += 1;
-        if ((rc = zq_argmax(m->logits, m->c.vocab, m->d_arg, st))) return rc;
-        i32_to_token_kernel<<<1, 1, 0, st>>>(m->d_token, m->d_arg, m->d_record + s);
-        ZQ_LAUNCH_CHECK();
     }
     ZQ_CUDA(cudaMemcpyAsync(h_tokens_out, m->d_record, n_steps * sizeof(uint32_t),
                             cudaMemcpyDeviceToHost, st));

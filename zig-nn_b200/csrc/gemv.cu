@@ -299,14 +299,36 @@ argmax_kernel(const float* __restrict__ logits, uint32_t n, int32_t* __restrict_
     __shared__ uint32_t si[32];
     float v = -INFINITY;
     uint32_t idx = 0xFFFFFFFFu;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const float c = logits[i];
-        // a NaN never compares greater, as in the CPU loop; index 0 is the fallback
+    // a NaN never compares greater, as in the CPU loop; index 0 is the fallback
+    auto take = [&](float c, uint32_t i) {
         if (c > v || (c == v && i < idx)) {
             v = c;
             idx = i;
         }
+    };
+    uint32_t done = 0;
+    if ((reinterpret_cast<uintptr_t>(logits) & 15u) == 0) {
+        // four independent 128-bit loads in flight per thread: one CTA reads the row at L2 speed
+        const float4* l4 = reinterpret_cast<const float4*>(logits);
+        const uint32_t n4 = n / 4, stride = blockDim.x;
+        uint32_t i = threadIdx.x;
+        for (; i + 3 * stride < n4; i += 4 * stride) {
+            float4 c[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) c[u] = __ldg(l4 + i + u * stride);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t b = (i + u * stride) * 4;
+                take(c[u].x, b); take(c[u].y, b + 1); take(c[u].z, b + 2); take(c[u].w, b + 3);
+            }
+        }
+        for (; i < n4; i += stride) {
+            const float4 c = __ldg(l4 + i);
+            take(c.x, i * 4); take(c.y, i * 4 + 1); take(c.z, i * 4 + 2); take(c.w, i * 4 + 3);
+        }
+        done = n4 * 4;
     }
+    for (uint32_t i = done + threadIdx.x; i < n; i += blockDim.x) take(logits[i], i);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
         const float ov = __shfl_xor_sync(0xFFFFFFFFu, v, off);

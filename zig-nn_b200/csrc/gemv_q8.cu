@@ -56,10 +56,10 @@ __device__ __forceinline__ int quad_transpose_reduce(const int (&p)[4], int t) {
 
 // smem: xl[nq][4] uint4 | xh[nq][4] uint4 | xs[nbp] f32 | xsum[nbp] i32 | terms[WR][16][pitch] f32
 template <int TYPE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 gemv_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const int8_t* __restrict__ xq,
                const float* __restrict__ xscale, const int32_t* __restrict__ xqsum, float* __restrict__ y,
-               uint32_t N, uint32_t nb, uint32_t scp, uint32_t WR, uint32_t KS, EpilogueArgs ep) {
+               uint32_t N, uint32_t nb, uint32_t scp, uint32_t WR, uint32_t KS, int prefetch, EpilogueArgs ep) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QB = Q8 ? 32 : 16;
@@ -77,6 +77,27 @@ gemv_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t wr = warp % WR, ks = warp / WR;
+
+    // The weights do not depend on the kernel that produces the activations: let the next kernel be
+    // scheduled, ask L2 for this CTA's rows, and only then wait for the activations.
+    pdl_launch_dependents();
+    if (prefetch) {
+        const uint32_t rows_cta = WR * 16;
+        const size_t row_bytes = (size_t)nbp * QB, sc_row_bytes = (size_t)scp * (Q41 ? 4 : 2);
+        constexpr uint32_t kChunk = 8192;
+        for (uint64_t tile = blockIdx.x; tile * rows_cta < N; tile += gridDim.x) {
+            const uint32_t row0 = (uint32_t)(tile * rows_cta);
+            const uint32_t rows = min(rows_cta, N - row0);
+            const size_t qbytes = rows * row_bytes, sbytes = rows * sc_row_bytes;
+            const uint8_t* qp = qs + (size_t)row0 * row_bytes;
+            const uint8_t* sp = sc + (size_t)row0 * sc_row_bytes;
+            for (size_t off = (size_t)tid * kChunk; off < qbytes; off += (size_t)blockDim.x * kChunk)
+                prefetch_l2_bulk(qp + off, (uint32_t)min((size_t)kChunk, qbytes - off));
+            for (size_t off = (size_t)tid * kChunk; off < sbytes; off += (size_t)blockDim.x * kChunk)
+                prefetch_l2_bulk(sp + off, (uint32_t)min((size_t)kChunk, sbytes - off));
+        }
+    }
+    pdl_wait();
 
     // Activation image: word w of block b goes to xl/xh[b/4][w%4] component b%4 (xl: w < 4, xh: w >= 4),
     // the same interleave as the weights. Blocks past nb (row padding) are zero with scale 1.
@@ -110,7 +131,7 @@ gemv_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
         const uint8_t* sa = sc + (size_t)row_a * scp * (Q41 ? 4 : 2);
         const uint8_t* sb = sc + (size_t)row_b * scp * (Q41 ? 4 : 2);
 
-#pragma unroll 2
+#pragma unroll 4
         for (uint32_t q = q_lo; q < q_hi; ++q) {
             const uint4 wa = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD));
             const uint4 wb = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD));
@@ -187,9 +208,11 @@ int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int3
     const uint32_t tiles = (w->out_dim + 15) / 16;
     const uint32_t sms = (uint32_t)sm_count();
     const uint32_t nq = w->nbp / 4;
+    // Small matrices are latency-bound: split K over up to 16 warps so that every load of a row tile is
+    // in flight at once; large ones keep whole rows per warp.
     uint32_t ks = 1;
-    while (ks < 8 && tiles * ks < sms * 16 && nq / (ks * 2) >= 2) ks *= 2;
-    uint32_t warps = 8;
+    while (ks < 16 && tiles * ks < sms * 16 && nq >= ks * 2) ks *= 2;
+    uint32_t warps = ks > 8 ? ks : 8;
     while (warps > ks && (tiles + warps / ks - 1) / (warps / ks) < sms) warps /= 2;
     uint32_t wr = warps / ks ? warps / ks : 1;
     const size_t fixed = (size_t)nq * 4 * 16 * 2 + (size_t)w->nbp * 8;
@@ -205,9 +228,11 @@ int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int3
     if (per_sm > 4) per_sm = 4;
     if (per_sm < 1) per_sm = 1;
     const uint32_t cap = sms * per_sm;
-    kern<<<cta_tiles < cap ? cta_tiles : cap, wr * ks * 32, smem, st>>>(
-        w->qs, static_cast<const uint8_t*>(w->sc), xq, xs, xsum, y, w->out_dim, w->nb, w->scp, wr, ks, ep);
-    ZQ_LAUNCH_CHECK();
+    // prefetching pays when the whole matrix can sit in L2 next to its neighbours in the step
+    const int prefetch = w->bytes <= (size_t)48 << 20;
+    ZQ_CUDA(launch_pdl(kern, dim3(cta_tiles < cap ? cta_tiles : cap), dim3(wr * ks * 32), smem, st, w->qs,
+                       static_cast<const uint8_t*>(w->sc), xq, xs, xsum, y, w->out_dim, w->nb, w->scp, wr, ks,
+                       prefetch, ep));
     return ZQ_OK;
 }
 

@@ -69,8 +69,20 @@ __device__ __forceinline__ float gelu_tanh(float v) {
 __device__ __forceinline__ float sumsq_lanes16(const float* xs, uint32_t dim, float* part, float* bc) {
     const uint32_t dim16 = dim & ~15u;
     if (threadIdx.x < 16) {
+        // eight loads and squares at a time, then the eight dependent adds: the add chain, not the
+        // shared-memory latency, sets the time
         float acc = 0.0f;
-        for (uint32_t i = threadIdx.x; i < dim16; i += 16) acc = __fadd_rn(acc, __fmul_rn(xs[i], xs[i]));
+        uint32_t i = threadIdx.x;
+        for (; i + 16 * 7 < dim16; i += 16 * 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = xs[i + 16 * u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __fmul_rn(v[u], v[u]);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, v[u]);
+        }
+        for (; i < dim16; i += 16) acc = __fadd_rn(acc, __fmul_rn(xs[i], xs[i]));
         part[threadIdx.x] = acc;
     }
     __syncthreads();
@@ -83,6 +95,24 @@ __device__ __forceinline__ float sumsq_lanes16(const float* xs, uint32_t dim, fl
     }
     __syncthreads();
     return *bc;
+}
+
+// Squares added one by one in index order (rms_norm_in_place, src/models/gemma3.zig:949-959), with the
+// loads and squares of eight elements issued ahead of their adds.
+__device__ __forceinline__ float sumsq_sequential(const float* xs, uint32_t dim) {
+    float ss = 0.0f;
+    uint32_t i = 0;
+    for (; i + 8 <= dim; i += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = xs[i + u];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __fmul_rn(v[u], v[u]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) ss = __fadd_rn(ss, v[u]);
+    }
+    for (; i < dim; ++i) ss = __fadd_rn(ss, __fmul_rn(xs[i], xs[i]));
+    return ss;
 }
 
 // mode 0: out = norm(x)*w ; mode 1: out(residual) += norm(x)*w.  Bit-identical to rms_norm_rows.
@@ -113,11 +143,7 @@ rms_norm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, uint32_t
     float* p = x + (size_t)blockIdx.x * dim;
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) xs[i] = p[i];
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float ss = 0.0f;
-        for (uint32_t i = 0; i < dim; ++i) ss = __fadd_rn(ss, __fmul_rn(xs[i], xs[i]));
-        bc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
-    }
+    if (threadIdx.x == 0) bc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq_sequential(xs, dim), (float)dim), eps)));
     __syncthreads();
     const float inv = bc;
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) p[i] = __fmul_rn(__fmul_rn(xs[i], inv), w[i]);
@@ -310,9 +336,330 @@ attention_softmax_v_kernel(const float* __restrict__ scores, const float* __rest
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Fused decode-step kernels for the engines. The sequence position lives in device memory
+// (state[1]) so that one captured launch sequence serves every step; each kernel performs the
+// same roundings in the same order as the separate kernels above, so results do not change.
+
+// quantize_row_q8 (src/gguf/simd_dot.zig:17-43) of the 32 values held one per lane of a warp.
+__device__ __forceinline__ void quantize_block_warp(float v, size_t blk, int lane, int8_t* __restrict__ q,
+                                                    float* __restrict__ scale, int32_t* __restrict__ sum) {
+    float amax = fabsf(v);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, s);
+    float r = roundf(__fmul_rn(v, inv));
+    r = fminf(127.0f, fmaxf(-127.0f, r));
+    const int qi = (int)r;
+    int acc = qi;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+    q[blk * 32 + lane] = (int8_t)qi;
+    if (lane == 0) {
+        scale[blk] = s;
+        sum[blk] = acc;
+    }
+}
+
+// RES = false:  h = rms_norm(src, w1)                               -> quantised
+// RES = true:   res += rms_norm(src, w1);  h = rms_norm(res, w2)     -> quantised
+// (gemma3.zig:662-666, 725-737, 768-773: post-norm + residual, then the next block's pre-norm.)
+// One CTA; dim is a multiple of 32.
+template <bool RES>
+__global__ void __launch_bounds__(256)
+norm_quant_kernel(const float* __restrict__ src, const float* __restrict__ w1, float* __restrict__ res,
+                  const float* __restrict__ w2, uint32_t dim, float eps, int8_t* __restrict__ q,
+                  float* __restrict__ scale, int32_t* __restrict__ sum) {
+    extern __shared__ __align__(16) float xs[];
+    __shared__ float part[16];
+    __shared__ float bc;
+    pdl_launch_dependents();
+    for (uint32_t i = threadIdx.x * 32; i < dim; i += blockDim.x * 32) {  // norm weights: one line per thread
+        prefetch_l2_line(w1 + i);
+        if (RES) prefetch_l2_line(w2 + i);
+    }
+    pdl_wait();
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) xs[i] = src[i];
+    __syncthreads();
+    float ss = sumsq_lanes16(xs, dim, part, &bc);
+    float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+    const float* wq = w1;
+    if (RES) {
+        for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
+            const float r = __fadd_rn(res[i], __fmul_rn(__fmul_rn(xs[i], inv), w1[i]));
+            res[i] = r;
+            xs[i] = r;
+        }
+        __syncthreads();
+        ss = sumsq_lanes16(xs, dim, part, &bc);
+        inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+        wq = w2;
+    }
+    const int lane = threadIdx.x & 31;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x)
+        quantize_block_warp(__fmul_rn(__fmul_rn(xs[i], inv), wq[i]), i >> 5, lane, q, scale, sum);
+}
+
+// Per-head work between the QKV projection and attention (gemma3.zig:689-716): q and k heads get
+// rms_norm_in_place then RoPE at the current position; q stays in place, k and v go to row `pos` of
+// the caches. Grid: n_head + 2 * n_kv_head CTAs (q heads, k heads, v heads).
+__global__ void __launch_bounds__(128)
+qk_norm_rope_kv_kernel(float* __restrict__ qkv, const float* __restrict__ q_norm_w,
+                       const float* __restrict__ k_norm_w, const float* __restrict__ freqs,
+                       float* __restrict__ kc, float* __restrict__ vc, const uint32_t* __restrict__ state,
+                       uint32_t n_head, uint32_t n_kv_head, uint32_t head_dim, float eps) {
+    extern __shared__ __align__(16) float xs[];
+    __shared__ float bc;
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t pos = state[1];
+    const uint32_t b = blockIdx.x, kv_dim = n_kv_head * head_dim;
+    if (b >= n_head + n_kv_head) {  // v head: copy
+        const uint32_t hv = b - n_head - n_kv_head;
+        const float* src = qkv + (size_t)(n_head + n_kv_head + hv) * head_dim;
+        float* dst = vc + (size_t)pos * kv_dim + (size_t)hv * head_dim;
+        for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = src[i];
+        return;
+    }
+    const bool is_k = b >= n_head;
+    float* p = qkv + (size_t)b * head_dim;
+    const float* w = is_k ? k_norm_w : q_norm_w;
+    for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) xs[i] = p[i];
+    __syncthreads();
+    if (threadIdx.x == 0)
+        bc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq_sequential(xs, head_dim), (float)head_dim), eps)));
+    __syncthreads();
+    const float inv = bc;
+    float* dst = is_k ? kc + (size_t)pos * kv_dim + (size_t)(b - n_head) * head_dim : p;
+    const float fpos = (float)pos;
+    for (uint32_t i = threadIdx.x; i < head_dim / 2; i += blockDim.x) {
+        const float x0 = __fmul_rn(__fmul_rn(xs[2 * i], inv), w[2 * i]);
+        const float x1 = __fmul_rn(__fmul_rn(xs[2 * i + 1], inv), w[2 * i + 1]);
+        const float theta = __fmul_rn(fpos, freqs[i]);
+        const float c = (float)cos((double)theta), s = (float)sin((double)theta);
+        dst[2 * i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        dst[2 * i + 1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    }
+}
+
+// g = gelu(gate) * up, quantised (gemma3.zig:750-765 followed by the row quantiser of the down
+// projection). One warp per 32-block.
+__global__ void __launch_bounds__(256)
+gelu_mul_quant_kernel(const float* __restrict__ gate, const float* __restrict__ up, uint32_t n_blocks,
+                      int8_t* __restrict__ q, float* __restrict__ scale, int32_t* __restrict__ sum) {
+    const uint32_t blk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (blk >= n_blocks) return;
+    const size_t i = (size_t)blk * 32 + lane;
+    quantize_block_warp(__fmul_rn(gelu_tanh(gate[i]), up[i]), blk, lane, q, scale, sum);
+}
+
+// The window a decode step attends to: positions [kv_start, pos]; `window` = 0 means all of them.
+__device__ __forceinline__ void step_window(const uint32_t* state, uint32_t window, uint32_t* kv_start,
+                                            uint32_t* kv_len) {
+    const uint32_t end = state[1] + 1;
+    const uint32_t len = (window && end > window) ? window : end;
+    *kv_start = end - len;
+    *kv_len = len;
+}
+
+// attention_scores_kernel with the window taken from the device-side position. The grid covers the
+// largest possible window; CTAs past the current one leave at once.
+__global__ void __launch_bounds__(256)
+attention_scores_step_kernel(const float* __restrict__ q, const float* __restrict__ kc,
+                             float* __restrict__ scores, uint32_t n_head, uint32_t n_kv_head,
+                             uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window) {
+    __shared__ float part[16][17];
+    pdl_launch_dependents();
+    pdl_wait();
+    uint32_t kv_start, kv_len;
+    step_window(state, window, &kv_start, &kv_len);
+    if (blockIdx.x * 16 >= kv_len) return;
+    const uint32_t h = blockIdx.y;
+    const uint32_t kvh = h / (n_head / n_kv_head);
+    const uint32_t kv_dim = n_kv_head * head_dim;
+    const uint32_t pp = threadIdx.x >> 4, l = threadIdx.x & 15;
+    const uint32_t p = blockIdx.x * 16 + pp;
+    const uint32_t dim16 = head_dim & ~15u;
+    const float* qh = q + (size_t)h * head_dim;
+    const float* kr = kc + (size_t)(kv_start + min(p, kv_len - 1)) * kv_dim + (size_t)kvh * head_dim;
+    float acc = 0.0f;
+    for (uint32_t d = l; d < dim16; d += 16) acc = __fadd_rn(acc, __fmul_rn(qh[d], kr[d]));
+    part[pp][l] = acc;
+    __syncthreads();
+    if (l == 0 && p < kv_len) {
+        float s = part[pp][0];
+#pragma unroll
+        for (int j = 1; j < 16; ++j) s = __fadd_rn(s, part[pp][j]);
+        for (uint32_t d = dim16; d < head_dim; ++d) s = __fadd_rn(s, __fmul_rn(qh[d], kr[d]));
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)head_dim));
+        scores[(size_t)h * kv_len + p] = __fmul_rn(s, scale);
+    }
+}
+
+// attention_softmax_v_kernel with the device-side window; QUANT additionally quantises the head's
+// output (head_dim is then a multiple of 32) for the output projection, f32 output optional.
+template <bool QUANT>
+__global__ void __launch_bounds__(256)
+attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* __restrict__ vc,
+                                float* __restrict__ out, int8_t* __restrict__ oq, float* __restrict__ oscale,
+                                int32_t* __restrict__ osum, uint32_t n_head, uint32_t n_kv_head,
+                                uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window,
+                                int gpt2_tail) {
+    extern __shared__ __align__(16) float w[];
+    __shared__ float red[33];
+    __shared__ float bc;
+    pdl_launch_dependents();
+    pdl_wait();
+    uint32_t kv_start, kv_len;
+    step_window(state, window, &kv_start, &kv_len);
+    const uint32_t h = blockIdx.x;
+    const uint32_t kvh = h / (n_head / n_kv_head);
+    const uint32_t kv_dim = n_kv_head * head_dim;
+    const float* sh = scores + (size_t)h * kv_len;
+    float mx = -INFINITY;
+    for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x) {
+        const float v = sh[p];
+        w[p] = v;
+        mx = fmaxf(mx, v);
+    }
+    mx = block_max(mx, red);
+    for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x) w[p] = exp_f32(__fsub_rn(w[p], mx));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+        uint32_t p = 0;
+        for (; p + 8 <= kv_len; p += 8) {
+            const float4 a = *reinterpret_cast<const float4*>(w + p);
+            const float4 b = *reinterpret_cast<const float4*>(w + p + 4);
+            s = __fadd_rn(s, a.x); s = __fadd_rn(s, a.y); s = __fadd_rn(s, a.z); s = __fadd_rn(s, a.w);
+            s = __fadd_rn(s, b.x); s = __fadd_rn(s, b.y); s = __fadd_rn(s, b.z); s = __fadd_rn(s, b.w);
+        }
+        for (; p < kv_len; ++p) s = __fadd_rn(s, w[p]);
+        bc = s;
+    }
+    __syncthreads();
+    const float sum = bc;
+    const float inv = __fdiv_rn(1.0f, sum);
+    const uint32_t vec_end = gpt2_tail ? (kv_len & ~15u) : kv_len;
+    for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x)
+        w[p] = p < vec_end ? __fmul_rn(w[p], inv) : __fdiv_rn(w[p], sum);
+    __syncthreads();
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        const float* vp = vc + (size_t)kv_start * kv_dim + (size_t)kvh * head_dim + d;
+        float acc = 0.0f;
+        uint32_t p = 0;
+        for (; p + 8 <= kv_len; p += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = vp[(size_t)(p + j) * kv_dim];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, __fmul_rn(w[p + j], v[j]));
+        }
+        for (; p < kv_len; ++p) acc = __fadd_rn(acc, __fmul_rn(w[p], vp[(size_t)p * kv_dim]));
+        const size_t o = (size_t)h * head_dim + d;
+        if (out) out[o] = acc;
+        if (QUANT) quantize_block_warp(acc, o >> 5, threadIdx.x & 31, oq, oscale, osum);
+    }
+}
+
+// GPT-2 embedding and cache write at the device-side position (gpt2.zig:449-453, 812-816).
+__global__ void gpt2_embed_step_kernel(float* __restrict__ x, const float* __restrict__ wte,
+                                       const float* __restrict__ wpe, const uint32_t* __restrict__ state,
+                                       uint32_t embed) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < embed) x[i] = wte[(size_t)state[0] * embed + i] + wpe[(size_t)state[1] * embed + i];
+}
+__global__ void write_kv_step_kernel(const float* __restrict__ k, const float* __restrict__ v,
+                                     float* __restrict__ kc, float* __restrict__ vc,
+                                     const uint32_t* __restrict__ state, uint32_t kv_dim) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t pos = state[1];
+    if (i < kv_dim) {
+        kc[(size_t)pos * kv_dim + i] = k[i];
+        vc[(size_t)pos * kv_dim + i] = v[i];
+    }
+}
+
 inline unsigned grid1d(size_t n, unsigned threads) { return (unsigned)((n + threads - 1) / threads); }
 
 }  // namespace
+
+// ---- launchers used by the engines (declared in zq_internal.h) ----------------------------
+
+int launch_norm_quant(const float* src, const float* w1, float* res, const float* w2, uint32_t dim, float eps,
+                      int8_t* q, float* scale, int32_t* sum, cudaStream_t st) {
+    if (dim == 0 || dim % 32 || dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
+    if (res)
+        ZQ_CUDA(launch_pdl(norm_quant_kernel<true>, dim3(1), dim3(256), dim * sizeof(float), st, src, w1, res, w2,
+                           dim, eps, q, scale, sum));
+    else
+        ZQ_CUDA(launch_pdl(norm_quant_kernel<false>, dim3(1), dim3(256), dim * sizeof(float), st, src, w1,
+                           nullptr, nullptr, dim, eps, q, scale, sum));
+    return ZQ_OK;
+}
+
+int launch_qk_norm_rope_kv(float* qkv, const float* q_norm_w, const float* k_norm_w, const float* freqs,
+                           float* kc, float* vc, const uint32_t* state, uint32_t n_head, uint32_t n_kv_head,
+                           uint32_t head_dim, float eps, cudaStream_t st) {
+    if (head_dim % 2 || head_dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
+    ZQ_CUDA(launch_pdl(qk_norm_rope_kv_kernel, dim3(n_head + 2 * n_kv_head), dim3(128), head_dim * sizeof(float),
+                       st, qkv, q_norm_w, k_norm_w, freqs, kc, vc, state, n_head, n_kv_head, head_dim, eps));
+    return ZQ_OK;
+}
+
+int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t* q, float* scale,
+                          int32_t* sum, cudaStream_t st) {
+    if (n % 32) return ZQ_ERR_BAD_ARG;
+    ZQ_CUDA(launch_pdl(gelu_mul_quant_kernel, dim3(grid1d(n, 256)), dim3(256), 0, st, gate, up, n / 32, q, scale,
+                       sum));
+    return ZQ_OK;
+}
+
+int launch_attention_step(const float* q, const float* kc, const float* vc, float* out, int8_t* oq,
+                          float* oscale, int32_t* osum, float* scores, uint32_t n_head, uint32_t n_kv_head,
+                          uint32_t head_dim, const uint32_t* state, uint32_t window, uint32_t max_len,
+                          int flags, cudaStream_t st) {
+    if (max_len == 0 || max_len > 200 * 1024 / 4) return ZQ_ERR_LIMIT;
+    if (oq && head_dim % 32) return ZQ_ERR_BAD_ARG;
+    const size_t smem = (size_t)max_len * sizeof(float);
+    const int tail = (flags & ZQ_ATTN_GPT2_SOFTMAX) ? 1 : 0;
+    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head), dim3(256), 0, st, q, kc,
+                       scores, n_head, n_kv_head, head_dim, state, window));
+    if (oq) {
+        auto kern = attention_softmax_v_step_kernel<true>;
+        if (smem > 48 * 1024)
+            ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        ZQ_CUDA(launch_pdl(kern, dim3(n_head), dim3(256), smem, st, scores, vc, out, oq, oscale, osum, n_head,
+                           n_kv_head, head_dim, state, window, tail));
+    } else {
+        auto kern = attention_softmax_v_step_kernel<false>;
+        if (smem > 48 * 1024)
+            ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        ZQ_CUDA(launch_pdl(kern, dim3(n_head), dim3(256), smem, st, scores, vc, out, nullptr, nullptr, nullptr,
+                           n_head, n_kv_head, head_dim, state, window, tail));
+    }
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+int launch_gpt2_embed_step(float* x, const float* wte, const float* wpe, const uint32_t* state, uint32_t embed,
+                           cudaStream_t st) {
+    gpt2_embed_step_kernel<<<grid1d(embed, 256), 256, 0, st>>>(x, wte, wpe, state, embed);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+int launch_write_kv_step(const float* k, const float* v, float* kc, float* vc, const uint32_t* state,
+                         uint32_t kv_dim, cudaStream_t st) {
+    write_kv_step_kernel<<<grid1d(kv_dim, 256), 256, 0, st>>>(k, v, kc, vc, state, kv_dim);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
 }  // namespace zq
 
 using namespace zq;

@@ -60,6 +60,41 @@ __host__ __device__ inline size_t qs_word_offset(uint32_t qb, uint32_t blk, uint
     return (size_t)quad * 128 + (size_t)((w >> 2) * 16 + (w & 3u) * 4 + j) * 4;
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------
+// Decode-step kernels are launched with the programmatic-serialisation attribute: a kernel may start
+// while its predecessor in the stream is still running. Each such kernel first calls
+// pdl_launch_dependents() (so its own successor can be scheduled early), may prefetch data that no
+// earlier kernel writes (weights), and must call pdl_wait() before it touches anything an earlier
+// kernel produces or still reads: pdl_wait() returns only when every earlier grid has completed and
+// its writes are visible. Without the launch attribute both calls do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Ask L2 to fetch `bytes` (a multiple of 16, 16-byte aligned address) without waiting for them.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2_line(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 inline bool is_quant(int t) { return t == ZQ_TYPE_Q4_0 || t == ZQ_TYPE_Q4_1 || t == ZQ_TYPE_Q8_0; }
 
 int sm_count();  // multiprocessors of the current device (cached per device)
@@ -78,5 +113,30 @@ int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, co
                    float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
 int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, int8_t* q,
                             float* scale, int32_t* sum, cudaStream_t st);
+
+// ---- fused decode-step launchers (ops.cu). `state` is device memory: state[0] = current token,
+// state[1] = its position. Kernels read the position there, so a captured launch sequence can be
+// replayed for every step.
+
+// res == nullptr: quantise rms_norm(src, w1).  Otherwise res += rms_norm(src, w1) and quantise
+// rms_norm(res, w2).
+int launch_norm_quant(const float* src, const float* w1, float* res, const float* w2, uint32_t dim, float eps,
+                      int8_t* q, float* scale, int32_t* sum, cudaStream_t st);
+// qkv = [q heads | k heads | v heads]; q is normalised and rotated in place, k and v go to the caches.
+int launch_qk_norm_rope_kv(float* qkv, const float* q_norm_w, const float* k_norm_w, const float* freqs,
+                           float* kc, float* vc, const uint32_t* state, uint32_t n_head, uint32_t n_kv_head,
+                           uint32_t head_dim, float eps, cudaStream_t st);
+int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t* q, float* scale,
+                          int32_t* sum, cudaStream_t st);
+// Single-query attention over positions [max(0, pos + 1 - window), pos] (window 0 = all); max_len is the
+// largest window any step can have. `out` (f32) and `oq/oscale/osum` (quantised) are each optional.
+int launch_attention_step(const float* q, const float* kc, const float* vc, float* out, int8_t* oq,
+                          float* oscale, int32_t* osum, float* scores, uint32_t n_head, uint32_t n_kv_head,
+                          uint32_t head_dim, const uint32_t* state, uint32_t window, uint32_t max_len,
+                          int flags, cudaStream_t st);
+int launch_gpt2_embed_step(float* x, const float* wte, const float* wpe, const uint32_t* state, uint32_t embed,
+                           cudaStream_t st);
+int launch_write_kv_step(const float* k, const float* v, float* kc, float* vc, const uint32_t* state,
+                         uint32_t kv_dim, cudaStream_t st);
 
 }  // namespace zq
