@@ -191,16 +191,27 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def time_region(torch, fn, steps, sync):
-    """K calls bracketed by sync + CUDA events on the current stream; returns total ms."""
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+def time_region(torch, fn, steps, sync, flush=None):
+    """K calls bracketed by sync + CUDA events on the current stream; returns total ms. With `flush`
+    (a callable that evicts L2) every call gets its own event pair and the flush runs between the
+    pairs, outside the timed intervals; the result is the sum of the K intervals."""
     sync()
-    e0.record()
-    for _ in range(steps):
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync()
+        return e0.elapsed_time(e1)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for e0, e1 in pairs:
+        flush()
+        e0.record()
         fn()
-    e1.record()
+        e1.record()
     sync()
-    return e0.elapsed_time(e1)
+    return sum(e0.elapsed_time(e1) for e0, e1 in pairs)
 
 
 def graph_time_us(torch, fns, reps=20):
@@ -250,6 +261,49 @@ def sweep_extra(torch, zq, ggml, m_list=(1,)):
     return out
 
 
+def decode_extra(torch, zq, ggml):
+    """Batch-1 greedy decode rates of the two model shapes (configs[0] and configs[2]) through the
+    engines, next to the CPU checker on the same synthetic weights with all host threads. The CPU leg
+    is a bounded sample: a 4-token prefill and 6 decode steps."""
+    import numpy as np
+    from zignn_b200 import hostmodel
+    oracle, build = load_oracle()
+    threads = host_threads()
+    out = []
+    cases = (("gpt2_small_q4_0", hostmodel.Gpt2Host, hostmodel.GPT2_SMALL, ggml.Q4_0, zq.Gpt2, oracle.Gpt2, 32, 128),
+             ("gemma3_1b_q8_0", hostmodel.Gemma3Host, hostmodel.GEMMA3_1B, ggml.Q8_0, zq.Gemma3, oracle.Gemma3, 512, 256))
+    for name, Host, cfg, qt, Eng, Ora, n_prompt, n_decode in cases:
+        host = Host.synthetic(cfg, qtype=qt, seed=42, device="cuda")
+        eng = Eng(host)
+        prompt = np.random.default_rng(44).integers(0, cfg["vocab"], size=n_prompt)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        logits = eng.prefill(prompt)
+        first = int(logits.argmax().item())
+        t1 = time.perf_counter()
+        eng.decode_greedy(first, 8)  # the first steps set up the replayed launch sequence
+        t2 = time.perf_counter()
+        toks = eng.decode_greedy(first, n_decode)  # returns after the tokens are on the host
+        t3 = time.perf_counter()
+        eng.close()
+        ref = Ora(host, threads)
+        c0 = time.perf_counter()
+        lc = ref.prefill(prompt[:4])
+        tok = int(np.argmax(lc))
+        c1 = time.perf_counter()
+        n_cpu = 6
+        for _ in range(n_cpu):
+            tok = int(np.argmax(ref.decode_next(tok)))
+        c2 = time.perf_counter()
+        gpu_tps, cpu_tps = n_decode / (t3 - t2), n_cpu / (c2 - c1)
+        out.append({"model": name, "prompt": n_prompt, "decode_steps": n_decode,
+                    "gpu_decode_tok_s": round(gpu_tps, 1), "gpu_prefill_ms": round((t1 - t0) * 1e3, 1),
+                    "cpu_decode_tok_s": round(cpu_tps, 2), "cpu_threads": threads, "cpu_build": build,
+                    "gpu_over_cpu": round(gpu_tps / cpu_tps, 1), "last_token": int(toks[-1])})
+        del eng, ref, host
+    return out
+
+
 def _lib_ws(zq, w, m, mode):
     from zignn_b200 import _lib
     return _lib.load().zq_matmul_workspace_bytes(w.handle, m, mode)
@@ -279,34 +333,36 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     q, n, k = WORKLOAD["qtype"], WORKLOAD["out_dim"], WORKLOAD["in_dim"]
-    n_local = n // world
-    # every rank draws the same full-weight stream and keeps its row slice
+    from zignn_b200 import sharding
+    # every rank draws the same full-weight stream and keeps its row slice (sharding.row_range)
     raw_full = make_weight_bytes(q, n, k, 42, "cuda")
-    row_bytes = (k // 32) * BPB[q]
-    raw = raw_full[rank * n_local * row_bytes:(rank + 1) * n_local * row_bytes].contiguous()
+    lin = sharding.cuda_sharded_linear(raw_full, ggml.TYPE_IDS[q], n, k, zq.ACT_F32)
     del raw_full
-    qw = zq.QuantWeight(raw, ggml.TYPE_IDS[q], n_local, k)
-    del raw
+    qw, n_local = lin.weight, lin.rows
     x = torch.randn(1, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(43))
-    y_local = torch.empty(1, n_local, device="cuda")
-    y_full = torch.empty(world, n_local, device="cuda") if use_dist else y_local
+    y_local = torch.zeros(1, lin.per, device="cuda")
 
     def step():
-        zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, out=y_local)
-        if use_dist:
-            dist.all_gather_into_tensor(y_full, y_local)
+        lin.forward_local(x, out=y_local)
+        return lin.gather(y_local) if use_dist else y_local
 
     def sync():
         if use_dist:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # one rank's shard is smaller than L2 (126 MB) from 2 ranks up: evict it between timed steps
+    local_weight_bytes = n_local * (k // 32) * BPB[q]
+    flush = None
+    if local_weight_bytes < 160e6:
+        flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        flush = lambda: flush_buf.fill_(1)
     for _ in range(max(3, args.warmup)):
         step()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    total_ms = time_region(torch, step, args.steps, sync)
+    total_ms = time_region(torch, step, args.steps, sync, flush)
     clocks = sampler.stop() if sampler else None
     if use_dist:
         tmax = torch.tensor([total_ms], device="cuda")
@@ -318,17 +374,16 @@ def main():
 
     # end to end through the public call with host buffers: pinned x -> device, GEMV, y -> pinned host
     hx = torch.randn(1, k).pin_memory()
-    hy = torch.empty(1, n_local).pin_memory()
+    hy = torch.empty(tuple(step().shape), dtype=torch.float32).pin_memory()  # the full logits row on every rank
 
     def e2e_step():
         x.copy_(hx, non_blocking=True)
-        step()
-        hy.copy_(y_local, non_blocking=True)
+        hy.copy_(step(), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads hy
 
     for _ in range(3):
         e2e_step()
-    e2e_ms = time_region(torch, e2e_step, args.steps, sync)
+    e2e_ms = time_region(torch, e2e_step, args.steps, sync, flush)
     if use_dist:
         tmax = torch.tensor([e2e_ms], device="cuda")
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -339,8 +394,8 @@ def main():
         peak, peak_kind = measured_peak()
         kernel_ms = ms
         if use_dist:  # the GEMV alone, for the roofline of the dominant kernel
-            kernel_ms = time_region(torch, lambda: zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, out=y_local),
-                                    args.steps, torch.cuda.synchronize) / args.steps
+            kernel_ms = time_region(torch, lambda: lin.forward_local(x, out=y_local), args.steps,
+                                    torch.cuda.synchronize, flush) / args.steps
         local_bytes = algorithmic_bytes(q, n_local, k)
         achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
         line = {
@@ -348,12 +403,13 @@ def main():
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": dict(workload="configs[1]: Q4_0 GEMV 1152->262144, M=1, f32 activations",
-                           weights="N(0,0.02) seed 42 quantised q4_0", l2="weights (170 MB) larger than L2 (126 MB)",
+                           weights="N(0,0.02) seed 42 quantised q4_0", l2=("weights (170 MB) larger than L2 (126 MB)" if flush is None else
+                               "256 MB write between timed steps evicts L2 (per-step event pairs)"),
                            sharding="rows split over %d rank(s)%s" % (world, ", NCCL all-gather of outputs" if use_dist else "")),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES, "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": local_bytes, "kernel": "gemv_mma_kernel<q4_0>"},
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k, "d2h_bytes_per_step": 4 * n_local},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k, "d2h_bytes_per_step": hy.numel() * 4},
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
@@ -363,10 +419,13 @@ def main():
             except Exception as e:  # the baseline is informational; never lose the GPU line
                 line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": host_threads(), "kind": "port",
                                         "sample": "failed: %r" % (e,)}
-            try:
-                line["extra"] = {"sweep_hbm_cold": sweep_extra(torch, zq, ggml, m_list=(1, 4, 16))}
-            except Exception as e:
-                line["extra"] = {"error": repr(e)}
+            line["extra"] = {}
+            for key, fn in (("sweep_hbm_cold", lambda: sweep_extra(torch, zq, ggml, m_list=(1, 4, 16))),
+                            ("decode", lambda: decode_extra(torch, zq, ggml))):
+                try:
+                    line["extra"][key] = fn()
+                except Exception as e:
+                    line["extra"][key] = {"error": repr(e)}
         print(json.dumps(line), flush=True)
     if use_dist:
         dist.barrier()

@@ -560,6 +560,291 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     }
 }
 
+// ---- single activation row (decode): the 8 MMA columns hold 4 blocks x (hi, lo) ------------------
+//
+// With one activation row only two of the eight MMA columns would carry data. This kernel instead
+// gives column pair (2j, 2j+1) the hi / lo activation parts of block j of the quad and zeros
+// elsewhere, and chains the 8 MMAs of a quad (4 blocks x low / high nibbles) into ONE accumulator:
+// column pair j then holds sum(n * x) of block j alone. Lane (g, t) owns columns 2t, 2t+1 of rows g and
+// g + 8, i.e. the finished sums of block 4q + t — so it needs one scale per row and quad (not four),
+// one multiply-add per row and quad, and one real activation-fragment load per quad (it feeds column
+// g, which is non-zero only for block g / 2). q4_0's "- 8" enters as the accumulator's initial value
+// -8 * sum(x_block) in the hi column, so no second accumulator exists. Per quad and lane: the nibble
+// unpack (40 logic ops), 8 MMAs, 4 predicated shared loads, 2 global 128-bit loads, 2 scale loads.
+// Rows are not split across warps (used when there are enough row tiles to fill the GPU).
+__device__ __forceinline__ void lds128_keep(uint4& v, uint32_t addr, uint32_t pred) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.u32 p, %5, 0;\n\t"
+        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "r"(addr), "r"(pred));
+}
+
+constexpr int kRowWarps = 8;  // warps per CTA, one 16-row tile each
+// Quads in flight per lane. They travel through a per-lane cp.async ring in shared memory: register
+// prefetch cannot go this deep (a warp has six load scoreboards), and the stream is latency-bound
+// until roughly 100 KB per SM are in flight.
+template <int TYPE> struct Rows1Depth { static constexpr int value = TYPE == ZQ_TYPE_Q8_0 ? 5 : 8; };
+
+template <bool Q8>
+struct QuadWords {
+    uint4 a, b;    // word t of blocks 0..3 of rows g / g + 8
+    uint4 a2, b2;  // q8_0: word 4 + t
+};
+
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("{\n\t.reg .u16 h;\n\tld.shared.u16 h, [%1];\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(kRowWarps * 32, kCtasPerSm)
+gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const float* __restrict__ x,
+                 float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t scp, uint32_t sc_off,
+                 uint32_t ring_off, EpilogueArgs ep) {
+    constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
+    constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
+    constexpr uint32_t QB = Q8 ? 32 : 16;
+    constexpr uint32_t SB = Q41 ? 4 : 2;
+    constexpr uint32_t QUAD = 4 * QB;  // quant bytes of one quad of blocks
+    constexpr int D = Rows1Depth<TYPE>::value;
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ float pre[1], post[1];
+    __shared__ unsigned int amax_bits;
+
+    const uint32_t nbp = (nb + 3u) & ~3u, nq = nbp / 4;
+    uint4* frag = reinterpret_cast<uint4*>(smem_raw);  // [block][hi, lo][t]
+    float* xsum = reinterpret_cast<float*>(frag + (size_t)nbp * 8);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    constexpr uint32_t rows_per_cta = kRowWarps * 16;
+
+    // Scales of a whole 16-row tile (contiguous in memory) are copied to this warp's shared buffer when
+    // the producer enters the tile; two buffers, because the producer is less than one tile ahead.
+    const uint32_t sc_row_bytes = scp * SB;
+    const uint32_t sc_tile_bytes = 16 * sc_row_bytes;  // a multiple of 256
+    const uint32_t sbuf32 = (uint32_t)__cvta_generic_to_shared(smem_raw + sc_off) + warp * 2 * sc_tile_bytes;
+
+    // ---- producer: the quads of this warp's tiles, in order, D - 1 ahead of the consumer. Each step
+    //      closes one cp.async group: group n holds quad n of the warp's sequence (plus, when quad n is
+    //      the last of its tile, the next tile's scales) ----
+    constexpr uint32_t kStage = Q8 ? 2048 : 1024;  // a, b (, a2, b2): 512 bytes each
+    const uint32_t ring32 = (uint32_t)__cvta_generic_to_shared(smem_raw + ring_off) + warp * D * kStage + lane * 16;
+    uint64_t p_tile = blockIdx.x;
+    uint32_t p_q = 0, p_par = 0, p_slot = 0;
+    const uint8_t *p_pa = qs, *p_pb = qs;
+    auto producer_set_tile = [&]() {
+        if (p_tile * rows_per_cta < N) {
+            const uint32_t r0 = (uint32_t)(p_tile * rows_per_cta) + warp * 16;
+            const uint32_t r = r0 + g;
+            const uint32_t row_a = min(r, N - 1), row_b = min(r + 8, N - 1);
+            p_pa = qs + (size_t)row_a * nbp * QB + 16 * t;
+            p_pb = qs + (size_t)row_b * nbp * QB + 16 * t;
+            if (r0 < N) {
+                const uint32_t bytes = min(16u, N - r0) * sc_row_bytes;
+                const uint8_t* src = sc + (size_t)r0 * sc_row_bytes;
+                const uint32_t dst = sbuf32 + p_par * sc_tile_bytes;
+                for (uint32_t o = lane * 16; o < bytes; o += 32 * 16) cp_async16(dst + o, src + o);
+            }
+            p_par ^= 1u;
+        }
+    };
+    auto producer_step = [&]() {
+        if (p_tile * rows_per_cta < N) {
+            const uint32_t stage = ring32 + p_slot * kStage;
+            cp_async16(stage, p_pa);
+            cp_async16(stage + 512, p_pb);
+            if (Q8) {
+                cp_async16(stage + 1024, p_pa + 64);
+                cp_async16(stage + 1536, p_pb + 64);
+            }
+            p_slot = p_slot + 1 == (uint32_t)D ? 0 : p_slot + 1;
+            if (++p_q == nq) {
+                p_q = 0;
+                p_tile += gridDim.x;
+                producer_set_tile();
+            } else {
+                p_pa += QUAD; p_pb += QUAD;
+            }
+        }
+        cp_async_commit();
+    };
+    producer_set_tile();
+#pragma unroll 1
+    for (int i = 0; i < D - 1; ++i) producer_step();
+    uint32_t c_slot = 0;
+
+    // ---- activations: range prescale, then the fp16 hi / lo fragment image ----
+    if (tid == 0) amax_bits = 0;
+    __syncthreads();
+    {
+        float amax = 0.0f;
+        const float4* xr = reinterpret_cast<const float4*>(x);
+        for (uint32_t i = tid; i < K / 4; i += blockDim.x) {
+            const float4 v = xr[i];
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+        if (lane == 0) atomicMax(&amax_bits, __float_as_uint(amax));
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const float amax = __uint_as_float(amax_bits);
+        int e = 0;
+        if (amax > 0.0f && amax < INFINITY) e = ilogbf(amax) - 13;
+        pre[0] = ldexpf(1.0f, -e);
+        post[0] = ldexpf(1.0f, e);
+    }
+    __syncthreads();
+    stage_activations<!Q8, !Q8>(x, 1, K, nb, nbp, pre, frag, xsum);
+    __syncthreads();
+
+    // This lane feeds MMA column g: part (g & 1) of block (g >> 1) of each quad.
+    const uint32_t myj = g >> 1;
+    const uint32_t frag0 = (uint32_t)__cvta_generic_to_shared(frag + ((size_t)myj * 2 + (g & 1)) * 4 + t);
+    const uint32_t xsum0 = (uint32_t)__cvta_generic_to_shared(xsum + t);
+    const uint32_t pj0 = myj == 0, pj1 = myj == 1, pj2 = myj == 2, pj3 = myj == 3;
+    uint4 bj0 = make_uint4(0, 0, 0, 0), bj1 = bj0, bj2 = bj0, bj3 = bj0;  // stay zero unless this lane's block
+
+    uint64_t c_tile = blockIdx.x;
+    uint32_t c_q = 0, c_par = 0;
+    uint32_t faddr = frag0, xaddr = xsum0;
+    // scales of block 4q + t, rows g and g + 8, in the current tile's buffer
+    const uint32_t sc_lane = g * sc_row_bytes + t * SB;
+    uint32_t saddr = sbuf32 + sc_lane;
+    float acc_a = 0.0f, acc_b = 0.0f, accm_a = 0.0f, accm_b = 0.0f;
+    const float ps = post[0];
+
+    auto consume = [&](const QuadWords<Q8>& d) {
+        lds128_keep(bj0, faddr, pj0);  // one of the four executes: faddr already points at this lane's block
+        lds128_keep(bj1, faddr, pj1);
+        lds128_keep(bj2, faddr, pj2);
+        lds128_keep(bj3, faddr, pj3);
+        float xs = 0.0f;
+        if (!Q8) xs = lds_f32(xaddr);
+        float da, db, ma = 0.0f, mb = 0.0f;
+        if (Q41) {
+            unpack_half2(lds_u32(saddr), da, ma);
+            unpack_half2(lds_u32(saddr + 8 * sc_row_bytes), db, mb);
+        } else {
+            da = __half2float(__ushort_as_half((unsigned short)lds_u16(saddr)));
+            db = __half2float(__ushort_as_half((unsigned short)lds_u16(saddr + 8 * sc_row_bytes)));
+        }
+        float dacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (TYPE == ZQ_TYPE_Q4_0) {
+            // (n - 8) * x summed = sum(n * x) - 8 * sum(x); the MMAs work in units of 2^-24
+            dacc[0] = dacc[2] = xs * (-8.0f / 16777216.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4& bf = j == 0 ? bj0 : j == 1 ? bj1 : j == 2 ? bj2 : bj3;
+            uint32_t a_lo[4], a_hi[4];
+            if (Q8) {
+                unpack_q8(pick(d.a, j), a_lo[0], a_lo[2]);
+                unpack_q8(pick(d.b, j), a_lo[1], a_lo[3]);
+                unpack_q8(pick(d.a2, j), a_hi[0], a_hi[2]);
+                unpack_q8(pick(d.b2, j), a_hi[1], a_hi[3]);
+            } else {
+                unpack_q4(pick(d.a, j), a_lo[0], a_lo[2], a_hi[0], a_hi[2]);
+                unpack_q4(pick(d.b, j), a_lo[1], a_lo[3], a_hi[1], a_hi[3]);
+            }
+            mma_f16(dacc, a_lo, bf.x, bf.y, dacc);
+            mma_f16(dacc, a_hi, bf.z, bf.w, dacc);
+        }
+        if (Q41) {
+            accm_a = fmaf(ma, xs, accm_a);
+            accm_b = fmaf(mb, xs, accm_b);
+        }
+        acc_a = fmaf(dacc[0] + dacc[1], da, acc_a);
+        acc_b = fmaf(dacc[2] + dacc[3], db, acc_b);
+        faddr += 512;  // 4 blocks x (hi, lo) x 4 lanes x 16 bytes
+        xaddr += 16;
+        saddr += 4 * SB;
+        if (++c_q == nq) {
+            // blocks of the row are spread over the 4 lanes of the quad: add them up
+            float va = acc_a, vb = acc_b;
+            if (!Q8) {
+                va *= 16777216.0f;
+                vb *= 16777216.0f;
+            }
+            if (Q41) {
+                va += accm_a;
+                vb += accm_b;
+            }
+            va += __shfl_xor_sync(0xFFFFFFFFu, va, 1);
+            vb += __shfl_xor_sync(0xFFFFFFFFu, vb, 1);
+            va += __shfl_xor_sync(0xFFFFFFFFu, va, 2);
+            vb += __shfl_xor_sync(0xFFFFFFFFu, vb, 2);
+            const uint32_t r0 = (uint32_t)(c_tile * rows_per_cta) + warp * 16 + g;
+            if (t == 0) {
+                if (r0 < N) y[r0] = apply_epilogue(va * ps, ep, r0, r0);
+                if (r0 + 8 < N) y[r0 + 8] = apply_epilogue(vb * ps, ep, r0 + 8, r0 + 8);
+            }
+            c_q = 0;
+            c_tile += gridDim.x;
+            c_par ^= 1u;
+            faddr = frag0;
+            xaddr = xsum0;
+            saddr = sbuf32 + c_par * sc_tile_bytes + sc_lane;
+            acc_a = acc_b = accm_a = accm_b = 0.0f;
+        }
+    };
+
+#pragma unroll 1
+    while (c_tile * rows_per_cta < N) {
+        producer_step();
+        cp_async_wait<D - 1>();  // all but the newest D - 1 groups have landed: this quad (and, at the
+        __syncwarp();            // start of a tile, its scales, copied by all lanes) is in shared memory
+        const uint32_t stage = ring32 + c_slot * kStage;
+        QuadWords<Q8> r;
+        r.a = lds128(stage);
+        r.b = lds128(stage + 512);
+        if (Q8) {
+            r.a2 = lds128(stage + 1024);
+            r.b2 = lds128(stage + 1536);
+        }
+        c_slot = c_slot + 1 == (uint32_t)D ? 0 : c_slot + 1;
+        consume(r);
+    }
+}
+
+template <int TYPE>
+int launch_rows1(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
+    constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
+    constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
+    const uint32_t sms = (uint32_t)sm_count();
+    if (w->nbp / 4 < (uint32_t)Rows1Depth<TYPE>::value) return ZQ_ERR_LIMIT;  // producer must stay within one tile
+    size_t smem = (size_t)w->nbp * 128;
+    if (!Q8) smem += (size_t)w->nbp * sizeof(float);
+    smem = (smem + 127) & ~(size_t)127;
+    const uint32_t sc_off = (uint32_t)smem;
+    smem += (size_t)kRowWarps * 2 * 16 * w->scp * (Q41 ? 4 : 2);
+    smem = (smem + 127) & ~(size_t)127;
+    const uint32_t ring_off = (uint32_t)smem;
+    smem += (size_t)kRowWarps * Rows1Depth<TYPE>::value * (Q8 ? 2048 : 1024);
+    if (smem > 110 * 1024) return ZQ_ERR_LIMIT;  // two CTAs per SM must fit
+    auto kern = gemv_mma1_kernel<TYPE>;
+    if (smem > 48 * 1024)
+        ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const uint32_t cta_tiles = (w->out_dim + kRowWarps * 16 - 1) / (kRowWarps * 16);
+    const uint32_t cap = sms * kCtasPerSm;
+    kern<<<cta_tiles < cap ? cta_tiles : cap, kRowWarps * 32, smem, st>>>(
+        w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim, w->in_dim, w->nb, w->scp, sc_off, ring_off,
+        ep);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
 struct Plan {
     uint32_t WR, KS, grid, ring_off;
     size_t smem;
@@ -649,6 +934,18 @@ int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m
         a.gelu = ep->gelu;
         a.mul = ep->d_mul;
         a.residual = ep->d_residual;
+    }
+    // One activation row and enough 16-row tiles to give every resident warp its own rows: the
+    // block-per-column kernel. Otherwise the general kernel (activation rows in columns, K split).
+    if (m_rows == 1 && (w->out_dim + 15) / 16 >= (uint32_t)sm_count() * kCtasPerSm * kRowWarps) {
+        int rc = ZQ_ERR_UNSUPPORTED;
+        switch (w->type) {
+            case ZQ_TYPE_Q4_0: rc = launch_rows1<ZQ_TYPE_Q4_0>(w, x, y, a, st); break;
+            case ZQ_TYPE_Q4_1: rc = launch_rows1<ZQ_TYPE_Q4_1>(w, x, y, a, st); break;
+            case ZQ_TYPE_Q8_0: rc = launch_rows1<ZQ_TYPE_Q8_0>(w, x, y, a, st); break;
+            default: return ZQ_ERR_UNSUPPORTED;
+        }
+        if (rc != ZQ_ERR_LIMIT) return rc;
     }
     switch (w->type) {
         case ZQ_TYPE_Q4_0: return launch_ns<ZQ_TYPE_Q4_0>(w, x, y, m_rows, a, st);
