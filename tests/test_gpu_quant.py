@@ -107,6 +107,36 @@ def test_matmul_small_batches_f32(zq, oracle, qtype, m):
     assert rel_l2(got, want) <= REL_L2_GUARD
 
 
+REL_L2_GEMM_GUARD = 6e-4  # fp16 operands (weights and activations each rounded once, <= 2^-12 relative)
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("m,n,k", [(64, 520, 768), (128, 256, 1152), (200, 1000, 96), (513, 136, 2048)])
+def test_matmul_many_rows_tensor_core_gemm(zq, oracle, qtype, m, n, k):
+    """More than 48 activation rows take the GEMM: ragged M and N tiles, K that is not a multiple of
+    the 128-wide stage, and the full epilogue."""
+    raw = make_weight(oracle, qtype, n, k)
+    qw = zq.QuantWeight(raw, qtype, n, k)
+    x = make_x(m, k)
+    x[1] *= 1000.0    # rows of very different magnitude: the per-row scale must cope
+    x[2] *= 1e-4
+    x[3] = 0.0
+    rng = np.random.default_rng(9)
+    bias = rng.standard_normal(n).astype(np.float32) * 0.1
+    res = rng.standard_normal((m, n)).astype(np.float32) * 0.1
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_F32).cpu().numpy()
+    want = oracle.linear(qtype, raw, x, n, k, act_mode=0, n_threads=8)
+    assert got.shape == (m, n)
+    for r in (0, 1, 2, m - 1):
+        assert rel_l2(got[r], want[r]) <= REL_L2_BAR
+        assert rel_l2(got[r], want[r]) <= REL_L2_GEMM_GUARD, (r, rel_l2(got[r], want[r]))
+    assert np.all(got[3] == 0.0)
+    assert rel_l2(got, want) <= REL_L2_GEMM_GUARD
+    got2 = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_F32, bias=torch.from_numpy(bias).cuda(),
+                                   residual=torch.from_numpy(res).cuda()).cpu().numpy()
+    assert rel_l2(got2, want + bias + res) <= REL_L2_GEMM_GUARD
+
+
 @pytest.mark.parametrize("qtype", TYPES)
 @pytest.mark.parametrize("n,k", SHAPES)
 def test_gemv_q8_activations_bit_exact(zq, oracle, qtype, n, k):
@@ -183,6 +213,24 @@ def test_vocab_head_full_size(zq, oracle, qtype):
     assert rel_l2(got32, want32) <= REL_L2_GUARD
     assert np.array_equal(gotq8, wantq8)
     assert int(zq.argmax(torch.from_numpy(got32[0]).cuda()).item()) == oracle.argmax(want32[0])
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("k", [1152, 2048])
+def test_single_row_kernel_ragged_tail(zq, oracle, qtype, k):
+    """Enough row tiles for the one-activation-row kernel (whole rows per warp), with a row count that
+    is not a multiple of 16 and a bias + residual epilogue."""
+    n = 148 * 2 * 8 * 16 + 77
+    raw = make_weight(oracle, qtype, n, k)
+    qw = zq.QuantWeight(raw, qtype, n, k)
+    x = make_x(1, k)
+    rng = np.random.default_rng(5)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = rng.standard_normal((1, n)).astype(np.float32)
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_F32, bias=torch.from_numpy(bias).cuda(),
+                                  residual=torch.from_numpy(res).cuda()).cpu().numpy()
+    want = oracle.linear(qtype, raw, x, n, k, act_mode=0, n_threads=8) + bias + res
+    assert rel_l2(got, want) <= REL_L2_GUARD
 
 
 def test_large_k_f32(zq, oracle):

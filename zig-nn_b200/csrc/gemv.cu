@@ -471,6 +471,7 @@ size_t zq_matmul_workspace_bytes(const zq_weight* w, uint32_t m_rows, int act_mo
         const size_t s = ((size_t)m_rows * w->nb * 4 + 255) & ~(size_t)255;
         return q + 2 * s;
     }
+    if (act_mode == ZQ_ACT_F32 && m_rows >= kGemmMinRows) return gemm_f16_workspace_bytes(w, m_rows);
     return 0;
 }
 
@@ -489,6 +490,10 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
     cudaStream_t st = as_stream(stream);
     if (act_mode == ZQ_ACT_F32) {
         if (((uintptr_t)d_x & 15) != 0) return launch_gemv_f32(w, d_x, d_y, m_rows, epilogue, st);
+        // many rows and a workspace for the fp16 activations: the tensor-core GEMM
+        if (m_rows >= kGemmMinRows && d_workspace && ((uintptr_t)d_workspace & 255) == 0 &&
+            workspace_bytes >= gemm_f16_workspace_bytes(w, m_rows))
+            return launch_gemm_f16(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
         // up to 16 activation rows per pass over the weights
         for (uint32_t m0 = 0; m0 < m_rows; m0 += 16) {
             const uint32_t mc = m_rows - m0 < 16 ? m_rows - m0 : 16;

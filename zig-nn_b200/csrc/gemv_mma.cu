@@ -583,9 +583,10 @@ __device__ __forceinline__ void lds128_keep(uint4& v, uint32_t addr, uint32_t pr
 
 constexpr int kRowWarps = 8;  // warps per CTA, one 16-row tile each
 // Quads in flight per lane. They travel through a per-lane cp.async ring in shared memory: register
-// prefetch cannot go this deep (a warp has six load scoreboards), and the stream is latency-bound
-// until roughly 100 KB per SM are in flight.
-template <int TYPE> struct Rows1Depth { static constexpr int value = TYPE == ZQ_TYPE_Q8_0 ? 5 : 8; };
+// prefetch cannot go deep (a warp has six load scoreboards, and later loads share them with earlier
+// ones). Measured on the 1152 -> 262144 head: depths 3..7 are within 2% of each other once the scales
+// no longer travel through the ring; one CTA per SM (8 warps) is 25% slower than two, three are 5% slower.
+constexpr int kRows1Depth = 4;
 
 template <bool Q8>
 struct QuadWords {
@@ -604,8 +605,8 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     return v;
 }
 
-template <int TYPE>
-__global__ void __launch_bounds__(kRowWarps * 32, kCtasPerSm)
+template <int TYPE, int D, int CTAS>
+__global__ void __launch_bounds__(kRowWarps * 32, CTAS)
 gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const float* __restrict__ x,
                  float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t scp, uint32_t sc_off,
                  uint32_t ring_off, EpilogueArgs ep) {
@@ -614,7 +615,6 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     constexpr uint32_t QB = Q8 ? 32 : 16;
     constexpr uint32_t SB = Q41 ? 4 : 2;
     constexpr uint32_t QUAD = 4 * QB;  // quant bytes of one quad of blocks
-    constexpr int D = Rows1Depth<TYPE>::value;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float pre[1], post[1];
@@ -818,12 +818,12 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     }
 }
 
-template <int TYPE>
-int launch_rows1(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
+template <int TYPE, int D, int CTAS>
+int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     const uint32_t sms = (uint32_t)sm_count();
-    if (w->nbp / 4 < (uint32_t)Rows1Depth<TYPE>::value) return ZQ_ERR_LIMIT;  // producer must stay within one tile
+    if (w->nbp / 4 < (uint32_t)D) return ZQ_ERR_LIMIT;  // the producer must stay within one tile of the consumer
     size_t smem = (size_t)w->nbp * 128;
     if (!Q8) smem += (size_t)w->nbp * sizeof(float);
     smem = (smem + 127) & ~(size_t)127;
@@ -831,18 +831,23 @@ int launch_rows1(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, 
     smem += (size_t)kRowWarps * 2 * 16 * w->scp * (Q41 ? 4 : 2);
     smem = (smem + 127) & ~(size_t)127;
     const uint32_t ring_off = (uint32_t)smem;
-    smem += (size_t)kRowWarps * Rows1Depth<TYPE>::value * (Q8 ? 2048 : 1024);
-    if (smem > 110 * 1024) return ZQ_ERR_LIMIT;  // two CTAs per SM must fit
-    auto kern = gemv_mma1_kernel<TYPE>;
+    smem += (size_t)kRowWarps * D * (Q8 ? 2048 : 1024);
+    if (smem > (size_t)(227 * 1024) / CTAS - 1024) return ZQ_ERR_LIMIT;  // CTAS CTAs per SM must fit
+    auto kern = gemv_mma1_kernel<TYPE, D, CTAS>;
     if (smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const uint32_t cta_tiles = (w->out_dim + kRowWarps * 16 - 1) / (kRowWarps * 16);
-    const uint32_t cap = sms * kCtasPerSm;
+    const uint32_t cap = sms * CTAS;
     kern<<<cta_tiles < cap ? cta_tiles : cap, kRowWarps * 32, smem, st>>>(
         w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim, w->in_dim, w->nb, w->scp, sc_off, ring_off,
         ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
+}
+
+template <int TYPE>
+int launch_rows1(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
+    return launch_rows1_cfg<TYPE, kRows1Depth, kCtasPerSm>(w, x, y, ep, st);
 }
 
 struct Plan {
