@@ -347,14 +347,21 @@ size_t gemm_f16_workspace_bytes(const zq_weight* w, uint32_t m_rows) {
     return xb + pb;
 }
 
+int launch_convert_rows_f16(const float* x, __half* x16, float* post, uint32_t m_rows, uint32_t in_dim,
+                            cudaStream_t st) {
+    convert_rows_f16_kernel<<<m_rows, 256, 0, st>>>(x, x16, post, in_dim);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
 int launch_gemm_f16(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
                     void* workspace, cudaStream_t st) {
     if (m_rows > 65535u * BM) return ZQ_ERR_LIMIT;
     const size_t xb = ((size_t)m_rows * w->in_dim * sizeof(__half) + 255) & ~(size_t)255;
     __half* x16 = static_cast<__half*>(workspace);
     float* post = reinterpret_cast<float*>(static_cast<char*>(workspace) + xb);
-    convert_rows_f16_kernel<<<m_rows, 256, 0, st>>>(x, x16, post, w->in_dim);
-    ZQ_LAUNCH_CHECK();
+    int rc0 = launch_convert_rows_f16(x, x16, post, m_rows, w->in_dim, st);
+    if (rc0 != ZQ_OK) return rc0;
     GemmEpilogue a{nullptr, nullptr, nullptr, 0};
     if (ep) {
         a.bias = ep->d_bias;

@@ -1,0 +1,433 @@
+// Batched quantised matmul on the 5th-generation tensor cores (tcgen05 + tensor memory).
+//
+// Same arithmetic as gemm.cu (weights dequantised once to fp16, activations fp16 with a per-row
+// power-of-two scale, f32 accumulation; zig-nn src/gguf/dequant.zig:133-309 is the CPU statement), but
+// the product runs as tcgen05.mma with both operands in shared memory and the accumulator in tensor
+// memory:
+//
+//   A operand  = 128 weight rows x 64 K (fp16, K-major, 128-byte swizzle), written by the dequantising
+//                warps straight from the packed GGUF words;
+//   B operand  = up to 256 activation rows x 64 K (fp16, K-major, same swizzle), copied with cp.async;
+//   D          = 128 lanes x N columns of f32 in tensor memory (one lane per weight row).
+//
+// Roles: warps 0-7 produce stages (dequantise + copy) and later drain the accumulator; one thread of
+// warp 8 issues the MMAs. Stages are handed over through mbarriers: full[s] (256 producer arrivals),
+// empty[s] (tcgen05.commit when the MMAs that read the stage are done), acc (last commit). Every wait
+// is bounded; on a timeout the kernel records it in the library's device-error word, stops using
+// the pipeline, still releases tensor memory and returns (outputs are then undefined; zq_device_error
+// reports it).
+#include "zq_internal.h"
+
+namespace zq {
+namespace {
+
+constexpr int TC_BN = 128;          // weight rows per CTA  (UMMA M)
+constexpr int TC_BM = 256;          // activation rows per CTA, at most (UMMA N)
+constexpr int TC_BK = 64;           // K per stage: one 128-byte swizzle atom of fp16
+constexpr int TC_STAGES = 4;
+constexpr int TC_PRODUCERS = 256;   // threads of warps 0-7
+constexpr int TC_THREADS = TC_PRODUCERS + 32;
+constexpr uint32_t TC_A_BYTES = TC_BN * 128;   // 16 KB
+constexpr uint32_t TC_B_BYTES = TC_BM * 128;   // 32 KB
+constexpr uint32_t TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr uint32_t kSpinLimit = 1u << 24;      // iterations of a try_wait loop before giving up (about a second)
+constexpr unsigned int kErrGemmTimeout = 0x47454D4Du;  // 'GEMM'
+
+struct TcEpilogue {
+    const float* bias;
+    const float* mul;
+    const float* residual;
+    int gelu;
+};
+
+__device__ __forceinline__ float gelu_tanh(float v) {
+    const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
+    const float inner = __fmul_rn(0.7978845608f, __fadd_rn(v, cube));
+    return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, (float)tanh((double)inner)));
+}
+
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
+
+__device__ __forceinline__ uint32_t hsub2_u(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// ---- mbarrier / tcgen05 wrappers -----------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait. Returns false after kSpinLimit polls or when another thread has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned int* err_word) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(err_word, kErrGemmTimeout);
+    return false;
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive columns of f32: register i of lane l = D[lane_base + l][col + i]
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile of rows x 64 fp16, 128-byte swizzle, 8-row groups 1024
+// bytes apart (stride-dimension offset); the leading-dimension offset is unused for this layout.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                          // leading-dimension byte offset (ignored), 16-byte units
+    d |= (uint64_t)(1024u >> 4) << 32;               // stride-dimension byte offset
+    d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                          // swizzle mode: 128 bytes
+    return d;
+}
+// Instruction descriptor, kind::f16: D = f32, A = B = fp16, both K-major, M x N tile.
+__host__ __device__ constexpr uint32_t idesc_f16(uint32_t m, uint32_t n) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ---- weight dequantisation (same mapping as gemm.cu: a thread owns (row, half) of a quad) ---------
+template <int TYPE>
+struct PackedQuad {
+    uint4 w0, w1, w2, w3;  // q4: w0, w1 = words 2*half, 2*half + 1; q8_0: words 4*half .. 4*half + 3 (of blocks 0..3)
+    uint4 s;
+};
+
+template <int TYPE>
+__device__ __forceinline__ void load_packed(PackedQuad<TYPE>& p, const uint8_t* qrow, const uint8_t* srow,
+                                            uint32_t quad, uint32_t half) {
+    if (TYPE == ZQ_TYPE_Q8_0) {
+        const uint4* q = reinterpret_cast<const uint4*>(qrow + (size_t)quad * 128) + half * 4;
+        p.w0 = __ldg(q); p.w1 = __ldg(q + 1); p.w2 = __ldg(q + 2); p.w3 = __ldg(q + 3);
+    } else {
+        const uint4* q = reinterpret_cast<const uint4*>(qrow + (size_t)quad * 64) + half * 2;
+        p.w0 = __ldg(q); p.w1 = __ldg(q + 1);
+    }
+    if (TYPE == ZQ_TYPE_Q4_1) {
+        p.s = __ldg(reinterpret_cast<const uint4*>(srow) + quad);
+    } else {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(srow) + quad);
+        p.s.x = v.x; p.s.y = v.y;
+    }
+}
+
+__device__ __forceinline__ uint32_t pick4(const uint4& v, int j) {
+    return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
+}
+
+template <int TYPE>
+__device__ __forceinline__ void nibbles_to_half(uint32_t nib, uint32_t d2, uint32_t m2, uint32_t& h01,
+                                                uint32_t& h23) {
+    const uint32_t p01 = __byte_perm(nib, 0x64646464u, 0x5140);
+    const uint32_t p23 = __byte_perm(nib, 0x64646464u, 0x5342);
+    if (TYPE == ZQ_TYPE_Q4_0) {
+        constexpr uint32_t k1032 = 0x64086408u;
+        h01 = hmul2_u(hsub2_u(p01, k1032), d2);
+        h23 = hmul2_u(hsub2_u(p23, k1032), d2);
+    } else {
+        constexpr uint32_t k1024 = 0x64006400u;
+        h01 = hfma2_u(hsub2_u(p01, k1024), d2, m2);
+        h23 = hfma2_u(hsub2_u(p23, k1024), d2, m2);
+    }
+}
+__device__ __forceinline__ void bytes_to_half(uint32_t q, uint32_t d2, uint32_t& h01, uint32_t& h23) {
+    const uint32_t u = q ^ 0x80808080u;
+    constexpr uint32_t k1152 = 0x64806480u;
+    h01 = hmul2_u(hsub2_u(__byte_perm(u, 0x64646464u, 0x5140), k1152), d2);
+    h23 = hmul2_u(hsub2_u(__byte_perm(u, 0x64646464u, 0x5342), k1152), d2);
+}
+
+// Blocks JBASE and JBASE + 1 of the quad -> the 64-K A tile of one stage.
+template <int TYPE, int JBASE>
+__device__ __forceinline__ void store_dequant(const PackedQuad<TYPE>& p, uint32_t tile, uint32_t row, uint32_t half) {
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+        const int j = JBASE + jj;
+        uint32_t d2, m2 = 0;
+        if (TYPE == ZQ_TYPE_Q4_1) {
+            const uint32_t dm = pick4(p.s, j);
+            d2 = __byte_perm(dm, dm, 0x1010);
+            m2 = __byte_perm(dm, dm, 0x3232);
+        } else {
+            const uint32_t pair = j < 2 ? p.s.x : p.s.y;
+            d2 = (j & 1) ? __byte_perm(pair, pair, 0x3232) : __byte_perm(pair, pair, 0x1010);
+        }
+        const uint32_t cbase = jj * 4;
+        if (TYPE == ZQ_TYPE_Q8_0) {
+            uint32_t h[8];
+            bytes_to_half(pick4(p.w0, j), d2, h[0], h[1]);
+            bytes_to_half(pick4(p.w1, j), d2, h[2], h[3]);
+            bytes_to_half(pick4(p.w2, j), d2, h[4], h[5]);
+            bytes_to_half(pick4(p.w3, j), d2, h[6], h[7]);
+            sts128(tile + swz(row, cbase + half * 2), h[0], h[1], h[2], h[3]);
+            sts128(tile + swz(row, cbase + half * 2 + 1), h[4], h[5], h[6], h[7]);
+        } else {
+            const uint32_t q0 = pick4(p.w0, j), q1 = pick4(p.w1, j);
+            uint32_t lo[4], hi[4];
+            nibbles_to_half<TYPE>(q0 & 0x0F0F0F0Fu, d2, m2, lo[0], lo[1]);
+            nibbles_to_half<TYPE>(q1 & 0x0F0F0F0Fu, d2, m2, lo[2], lo[3]);
+            nibbles_to_half<TYPE>((q0 >> 4) & 0x0F0F0F0Fu, d2, m2, hi[0], hi[1]);
+            nibbles_to_half<TYPE>((q1 >> 4) & 0x0F0F0F0Fu, d2, m2, hi[2], hi[3]);
+            sts128(tile + swz(row, cbase + half), lo[0], lo[1], lo[2], lo[3]);
+            sts128(tile + swz(row, cbase + 2 + half), hi[0], hi[1], hi[2], hi[3]);
+        }
+    }
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const __half* __restrict__ x16,
+               const float* __restrict__ post, float* __restrict__ y, uint32_t N, uint32_t K, uint32_t M,
+               uint32_t nbp, uint32_t scp, uint32_t n_mma, uint32_t tmem_cols, unsigned int* err_word,
+               TcEpilogue ep) {
+    constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
+    constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
+    constexpr uint32_t QB = Q8 ? 32 : 16;
+    constexpr uint32_t SB = Q41 ? 4 : 2;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long bars[2 * TC_STAGES + 1];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    // operand tiles must start on a 1024-byte boundary (swizzle atoms); the launch adds the slack
+    const uint32_t smem32 = ((uint32_t)__cvta_generic_to_shared(smem) + 1023u) & ~1023u;
+    const uint32_t bar32 = (uint32_t)__cvta_generic_to_shared(bars);
+    auto full_bar = [&](uint32_t s) { return bar32 + s * 8; };
+    auto empty_bar = [&](uint32_t s) { return bar32 + (TC_STAGES + s) * 8; };
+    const uint32_t acc_bar = bar32 + 2 * TC_STAGES * 8;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM;
+    const uint32_t n_stages = nbp / 2;  // 64-K stages (the row padding to whole quads is zero weights)
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < TC_STAGES; ++s) {
+            mbar_init(full_bar(s), TC_PRODUCERS);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {  // the MMA warp owns the tensor-memory allocation
+        const uint32_t slot = (uint32_t)__cvta_generic_to_shared(&tmem_base_slot);
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_p = &abort_flag;
+
+    if (warp < 8) {
+        // ================= producers =================
+        const uint32_t prow = tid >> 1, phalf = tid & 1;
+        const uint32_t wrow = min(n0 + prow, N - 1);
+        const uint8_t* qrow = qs + (size_t)wrow * nbp * QB;
+        const uint8_t* srow = sc + (size_t)wrow * scp * SB;
+        const uint32_t b_chunks = n_mma * 8;  // 16-byte chunks of the activation tile
+        PackedQuad<TYPE> pk;
+        load_packed<TYPE>(pk, qrow, srow, 0, phalf);
+        bool alive = true;
+        for (uint32_t s = 0; s < n_stages && alive; ++s) {
+            const uint32_t slot = s % TC_STAGES, round = s / TC_STAGES;
+            if (round > 0) alive = mbar_wait(empty_bar(slot), (round - 1) & 1u, abort_p, err_word);
+            if (!alive) break;
+            const uint32_t a_tile = smem32 + slot * TC_STAGE_BYTES, b_tile = a_tile + TC_A_BYTES;
+            // activation rows: n_mma x 8 chunks, zero-filled past M and K
+            for (uint32_t idx = tid; idx < b_chunks; idx += TC_PRODUCERS) {
+                const uint32_t r = idx >> 3, c = idx & 7u;
+                const uint32_t m = m0 + r, k = s * TC_BK + c * 8;
+                const bool ok = m < M && k < K;
+                const __half* src = x16 + (size_t)(ok ? m : 0) * K + (ok ? k : 0);
+                cp_async16_zfill(b_tile + swz(r, c), src, ok ? 16u : 0u);
+            }
+            if ((s & 1u) == 0) {
+                store_dequant<TYPE, 0>(pk, a_tile, prow, phalf);
+            } else {
+                store_dequant<TYPE, 2>(pk, a_tile, prow, phalf);
+                if (s + 1 < n_stages) load_packed<TYPE>(pk, qrow, srow, (s + 1) >> 1, phalf);
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            fence_proxy_async();  // generic-proxy writes (st.shared, cp.async) -> visible to the tensor core
+            mbar_arrive(full_bar(slot));
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+
+        // ================= epilogue: drain tensor memory =================
+        if (alive) alive = mbar_wait(acc_bar, 0, abort_p, err_word);
+        tc_fence_after();
+        if (alive) {
+            // warp w reads lanes 32 * (w % 4) ..; warps 0-3 take the low half of the columns, 4-7 the high half
+            const uint32_t lane_base = (warp & 3) * 32;
+            const uint32_t n = n0 + lane_base + lane;
+            const uint32_t col_half = n_mma / 2;  // n_mma is a multiple of 64
+            const uint32_t col0 = (warp >> 2) * col_half;
+            for (uint32_t c = 0; c < col_half; c += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + (lane_base << 16) + col0 + c, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t m = m0 + col0 + c + i;
+                    if (n < N && m < M) {
+                        const size_t o = (size_t)m * N + n;
+                        float v = __uint_as_float(r[i]) * post[m];
+                        if (ep.bias) v = __fadd_rn(v, ep.bias[n]);
+                        if (ep.gelu) v = gelu_tanh(v);
+                        if (ep.mul) v = __fmul_rn(v, ep.mul[o]);
+                        if (ep.residual) v = __fadd_rn(ep.residual[o], v);
+                        y[o] = v;
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    } else {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            const uint32_t idesc = idesc_f16(TC_BN, n_mma);
+            bool alive = true;
+            for (uint32_t s = 0; s < n_stages && alive; ++s) {
+                const uint32_t slot = s % TC_STAGES, round = s / TC_STAGES;
+                alive = mbar_wait(full_bar(slot), round & 1u, abort_p, err_word);
+                if (!alive) break;
+                tc_fence_after();
+                const uint32_t a_tile = smem32 + slot * TC_STAGE_BYTES, b_tile = a_tile + TC_A_BYTES;
+                const uint64_t a_desc = smem_desc_sw128(a_tile), b_desc = smem_desc_sw128(b_tile);
+#pragma unroll
+                for (uint32_t k16 = 0; k16 < TC_BK / 16; ++k16) {
+                    // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
+                    tc_mma_f16(tmem_base, a_desc + 2 * k16, b_desc + 2 * k16, idesc, (s | k16) != 0 ? 1u : 0u);
+                }
+                tc_commit(empty_bar(slot));  // arrives when the MMAs issued so far have read their operands
+            }
+            if (alive) tc_commit(acc_bar);
+            else *abort_p = 1;
+        }
+        __syncwarp();
+    }
+
+    __syncthreads();
+    if (warp == 8) {
+        // If the pipeline was abandoned, MMAs may still be in flight: give the last commit a bounded chance.
+        if (abort_flag && lane == 0) {
+            tc_commit(acc_bar);
+            for (uint32_t i = 0; i < kSpinLimit; ++i)
+                if (mbar_try_wait(acc_bar, 0)) break;
+        }
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+template <int TYPE>
+int launch_tc(const zq_weight* w, const __half* x16, const float* post, float* y, uint32_t M, TcEpilogue ep,
+              cudaStream_t st) {
+    auto kern = gemm_tc_kernel<TYPE>;
+    const size_t smem = (size_t)TC_STAGES * TC_STAGE_BYTES + 1024;  // + alignment slack
+    ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // activation rows per CTA: a multiple of 64 (the epilogue splits the columns in two halves of 32s)
+    uint32_t n_mma = M >= TC_BM ? TC_BM : ((M + 63u) / 64u) * 64u;
+    uint32_t tmem_cols = 64;
+    while (tmem_cols < n_mma) tmem_cols *= 2;
+    const dim3 grid((w->out_dim + TC_BN - 1) / TC_BN, (M + n_mma - 1) / n_mma);
+    if (n_mma != TC_BM && grid.y != 1) return ZQ_ERR_BAD_ARG;  // m0 = blockIdx.y * TC_BM assumes full tiles
+    unsigned int* err_word = nullptr;
+    int rc = device_error_word(&err_word);
+    if (rc != ZQ_OK) return rc;
+    kern<<<grid, TC_THREADS, smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), x16, post, y, w->out_dim,
+                                          w->in_dim, M, w->nbp, w->scp, n_mma, tmem_cols, err_word, ep);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+}  // namespace
+
+// Activation conversion is shared with gemm.cu (launch_convert_rows_f16).
+int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
+                   void* workspace, cudaStream_t st) {
+    if (m_rows > 65535u * TC_BM) return ZQ_ERR_LIMIT;
+    const size_t xb = ((size_t)m_rows * w->in_dim * sizeof(__half) + 255) & ~(size_t)255;
+    __half* x16 = static_cast<__half*>(workspace);
+    float* post = reinterpret_cast<float*>(static_cast<char*>(workspace) + xb);
+    int rc = launch_convert_rows_f16(x, x16, post, m_rows, w->in_dim, st);
+    if (rc != ZQ_OK) return rc;
+    TcEpilogue a{nullptr, nullptr, nullptr, 0};
+    if (ep) {
+        a.bias = ep->d_bias;
+        a.gelu = ep->gelu;
+        a.mul = ep->d_mul;
+        a.residual = ep->d_residual;
+    }
+    switch (w->type) {
+        case ZQ_TYPE_Q4_0: return launch_tc<ZQ_TYPE_Q4_0>(w, x16, post, y, m_rows, a, st);
+        case ZQ_TYPE_Q4_1: return launch_tc<ZQ_TYPE_Q4_1>(w, x16, post, y, m_rows, a, st);
+        case ZQ_TYPE_Q8_0: return launch_tc<ZQ_TYPE_Q8_0>(w, x16, post, y, m_rows, a, st);
+        default: return ZQ_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace zq

@@ -3,6 +3,8 @@
 //   f32  — f32 activations times weights dequantised on the fly (zig-nn src/gguf/dequant.zig:133-309)
 //   q8   — the activation quantiser lives here (quantize_row_q8); the exact int8 GEMV is in
 //          gemv_q8.cu.
+#include <stdlib.h>
+
 #include "zq_internal.h"
 
 namespace zq {
@@ -493,7 +495,12 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
         // many rows and a workspace for the fp16 activations: the tensor-core GEMM
         if (m_rows >= kGemmMinRows && d_workspace && ((uintptr_t)d_workspace & 255) == 0 &&
             workspace_bytes >= gemm_f16_workspace_bytes(w, m_rows))
-            return launch_gemm_f16(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
+        {
+            // ZQ_GEMM=mma selects the mma.sync version of the same product (for comparison)
+            static const bool legacy = getenv("ZQ_GEMM") && getenv("ZQ_GEMM")[0] == 'm';
+            return legacy ? launch_gemm_f16(w, d_x, d_y, m_rows, epilogue, d_workspace, st)
+                          : launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
+        }
         // up to 16 activation rows per pass over the weights
         for (uint32_t m0 = 0; m0 < m_rows; m0 += 16) {
             const uint32_t mc = m_rows - m0 < 16 ? m_rows - m0 : 16;

@@ -10,6 +10,21 @@ thread_local int g_last_cuda_error = 0;
 // Set by a kernel whose bounded device-side wait ran out; read with zq_device_error().
 __device__ unsigned int g_device_error = 0;
 
+// Device address of the error word, for kernels in other translation units (passed as a parameter).
+int device_error_word(unsigned int** out) {
+    static unsigned int* cached[64] = {nullptr};
+    int dev = 0;
+    ZQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return ZQ_ERR_LIMIT;
+    if (!cached[dev]) {
+        void* p = nullptr;
+        ZQ_CUDA(cudaGetSymbolAddress(&p, g_device_error));
+        cached[dev] = static_cast<unsigned int*>(p);
+    }
+    *out = cached[dev];
+    return ZQ_OK;
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;

@@ -98,6 +98,8 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 inline bool is_quant(int t) { return t == ZQ_TYPE_Q4_0 || t == ZQ_TYPE_Q4_1 || t == ZQ_TYPE_Q8_0; }
 
 int sm_count();  // multiprocessors of the current device (cached per device)
+// Device address of the word zq_device_error() reads; kernels with bounded waits record a timeout there.
+int device_error_word(unsigned int** out);
 
 // ---- launchers implemented in gemv.cu and used by the engines -------------------------
 
@@ -119,6 +121,12 @@ constexpr uint32_t kGemmMinRows = 49;  // below this, passes of the 16-row decod
 size_t gemm_f16_workspace_bytes(const zq_weight* w, uint32_t m_rows);
 int launch_gemm_f16(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
                     void* workspace, cudaStream_t st);
+// x16[m][k] = fp16(x[m][k] * 2^-e_m), post[m] = 2^e_m (gemm.cu).
+int launch_convert_rows_f16(const float* x, __half* x16, float* post, uint32_t m_rows, uint32_t in_dim,
+                            cudaStream_t st);
+// The same product with tcgen05.mma and the accumulator in tensor memory (gemm_tc.cu); same workspace.
+int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
+                   void* workspace, cudaStream_t st);
 
 // ---- fused decode-step launchers (ops.cu). `state` is device memory: state[0] = current token,
 // state[1] = its position. Kernels read the position there, so a captured launch sequence can be
