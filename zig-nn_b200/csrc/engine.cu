@@ -217,7 +217,7 @@ int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_strea
     if (!cfg->vocab || !cfg->embed || !cfg->head || !cfg->layer || !cfg->ctx || !cfg->ffn ||
         cfg->embed % cfg->head || cfg->embed % 32 || cfg->ffn % 32)
         return ZQ_ERR_BAD_ARG;
-    if (cfg->ctx > 200 * 1024 / 4) return ZQ_ERR_LIMIT;  // one attention row must fit shared memory
+    if (cfg->ctx > 180 * 1024 / 4) return ZQ_ERR_LIMIT;  // one attention row must fit shared memory
     zq_gpt2* m = new (std::nothrow) zq_gpt2;
     if (!m) return ZQ_ERR_NO_MEM;
     m->c = *cfg;
@@ -508,7 +508,7 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
     uint32_t max_dim = E > F ? E : F;
     if (QD > max_dim) max_dim = QD;
     if (max_dim > 16384) return ZQ_ERR_LIMIT;
-    if (C.ctx > 200 * 1024 / 4) return ZQ_ERR_LIMIT;  // one attention row must fit shared memory
+    if (C.ctx > 180 * 1024 / 4) return ZQ_ERR_LIMIT;  // one attention row must fit shared memory
     zq_gemma3* m = new (std::nothrow) zq_gemma3;
     if (!m) return ZQ_ERR_NO_MEM;
     m->c = C;

@@ -500,8 +500,16 @@ attention_scores_step_kernel(const float* __restrict__ q, const float* __restric
     }
 }
 
-// attention_softmax_v_kernel with the device-side window; QUANT additionally quantises the head's
-// output (head_dim is then a multiple of 32) for the output projection, f32 output optional.
+// Softmax and weighted sum of V for one decode step, device-side window. Same arithmetic as
+// attention_softmax_v_kernel (exponentials added one by one, out[d] += w[p] * v[p][d] for p in order), laid
+// out for long windows: a CTA owns 64 output dimensions of one head (grid = heads x head_dim / 64) and
+// streams V through shared memory in tiles of 64 positions — all 256 threads fetch the next tile
+// (coalesced 256-byte rows, 16 loads in flight each) while 64 threads run the add chain of the current
+// one, so the chain, not the memory latency, sets the time. QUANT additionally quantises the head's output
+// in 32-blocks for the output projection; the f32 output is optional.
+constexpr int kAttnTile = 64;  // positions per V tile
+constexpr int kAttnDims = 64;  // output dimensions per CTA
+
 template <bool QUANT>
 __global__ void __launch_bounds__(256)
 attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* __restrict__ vc,
@@ -509,7 +517,8 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
                                 int32_t* __restrict__ osum, uint32_t n_head, uint32_t n_kv_head,
                                 uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window,
                                 int gpt2_tail) {
-    extern __shared__ __align__(16) float w[];
+    extern __shared__ __align__(16) float w[];  // max window length
+    __shared__ float vt[kAttnTile][kAttnDims];
     __shared__ float red[33];
     __shared__ float bc;
     pdl_launch_dependents();
@@ -519,6 +528,22 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
     const uint32_t h = blockIdx.x;
     const uint32_t kvh = h / (n_head / n_kv_head);
     const uint32_t kv_dim = n_kv_head * head_dim;
+    const uint32_t d0 = blockIdx.y * kAttnDims;
+    const uint32_t pg = threadIdx.x >> 6, dl = threadIdx.x & 63;
+    const bool d_ok = d0 + dl < head_dim;
+    const float* vbase = vc + (size_t)kv_start * kv_dim + (size_t)kvh * head_dim + d0 + dl;
+
+    // rows pg*16 .. pg*16+15 of a tile, one element per row and thread
+    float vreg[16];
+    auto fetch = [&](uint32_t p0) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t p = p0 + pg * 16 + i;
+            vreg[i] = (d_ok && p < kv_len) ? vbase[(size_t)p * kv_dim] : 0.0f;
+        }
+    };
+    fetch(0);  // in flight during the softmax below
+
     const float* sh = scores + (size_t)h * kv_len;
     float mx = -INFINITY;
     for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x) {
@@ -547,22 +572,34 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
     const uint32_t vec_end = gpt2_tail ? (kv_len & ~15u) : kv_len;
     for (uint32_t p = threadIdx.x; p < kv_len; p += blockDim.x)
         w[p] = p < vec_end ? __fmul_rn(w[p], inv) : __fdiv_rn(w[p], sum);
-    __syncthreads();
-    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        const float* vp = vc + (size_t)kv_start * kv_dim + (size_t)kvh * head_dim + d;
-        float acc = 0.0f;
-        uint32_t p = 0;
-        for (; p + 8 <= kv_len; p += 8) {
-            float v[8];
+
+    float acc = 0.0f;
+    for (uint32_t p0 = 0; p0 < kv_len; p0 += kAttnTile) {
+        __syncthreads();  // the previous tile has been consumed (first pass: the weights are complete)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = vp[(size_t)(p + j) * kv_dim];
+        for (int i = 0; i < 16; ++i) vt[pg * 16 + i][dl] = vreg[i];
+        __syncthreads();
+        if (p0 + kAttnTile < kv_len) fetch(p0 + kAttnTile);
+        if (pg == 0) {
+            const uint32_t n = min((uint32_t)kAttnTile, kv_len - p0);
+            uint32_t i = 0;
+            for (; i + 8 <= n; i += 8) {
+                float v[8], ww[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, __fmul_rn(w[p + j], v[j]));
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = vt[i + j][dl];
+                    ww[j] = w[p0 + i + j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, __fmul_rn(ww[j], v[j]));
+            }
+            for (; i < n; ++i) acc = __fadd_rn(acc, __fmul_rn(w[p0 + i], vt[i][dl]));
         }
-        for (; p < kv_len; ++p) acc = __fadd_rn(acc, __fmul_rn(w[p], vp[(size_t)p * kv_dim]));
-        const size_t o = (size_t)h * head_dim + d;
-        if (out) out[o] = acc;
-        if (QUANT) quantize_block_warp(acc, o >> 5, threadIdx.x & 31, oq, oscale, osum);
+    }
+    if (pg == 0) {  // two whole warps: 32-blocks of the output line up with warps
+        const size_t o = (size_t)h * head_dim + d0 + dl;
+        if (d_ok && out) out[o] = acc;
+        if (QUANT && d0 + (dl & ~31u) < head_dim) quantize_block_warp(acc, o >> 5, threadIdx.x & 31, oq, oscale, osum);
     }
 }
 
@@ -623,7 +660,7 @@ int launch_attention_step(const float* q, const float* kc, const float* vc, floa
                           float* oscale, int32_t* osum, float* scores, uint32_t n_head, uint32_t n_kv_head,
                           uint32_t head_dim, const uint32_t* state, uint32_t window, uint32_t max_len,
                           int flags, cudaStream_t st) {
-    if (max_len == 0 || max_len > 200 * 1024 / 4) return ZQ_ERR_LIMIT;
+    if (max_len == 0 || max_len > 180 * 1024 / 4) return ZQ_ERR_LIMIT;
     if (oq && head_dim % 32) return ZQ_ERR_BAD_ARG;
     const size_t smem = (size_t)max_len * sizeof(float);
     const int tail = (flags & ZQ_ATTN_GPT2_SOFTMAX) ? 1 : 0;
@@ -631,16 +668,16 @@ int launch_attention_step(const float* q, const float* kc, const float* vc, floa
                        scores, n_head, n_kv_head, head_dim, state, window));
     if (oq) {
         auto kern = attention_softmax_v_step_kernel<true>;
-        if (smem > 48 * 1024)
+        if (smem > 24 * 1024)  // the kernel also holds a 16 KB static tile
             ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        ZQ_CUDA(launch_pdl(kern, dim3(n_head), dim3(256), smem, st, scores, vc, out, oq, oscale, osum, n_head,
-                           n_kv_head, head_dim, state, window, tail));
+        ZQ_CUDA(launch_pdl(kern, dim3(n_head, (head_dim + kAttnDims - 1) / kAttnDims), dim3(256), smem, st, scores,
+                           vc, out, oq, oscale, osum, n_head, n_kv_head, head_dim, state, window, tail));
     } else {
         auto kern = attention_softmax_v_step_kernel<false>;
-        if (smem > 48 * 1024)
+        if (smem > 24 * 1024)  // the kernel also holds a 16 KB static tile
             ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        ZQ_CUDA(launch_pdl(kern, dim3(n_head), dim3(256), smem, st, scores, vc, out, nullptr, nullptr, nullptr,
-                           n_head, n_kv_head, head_dim, state, window, tail));
+        ZQ_CUDA(launch_pdl(kern, dim3(n_head, (head_dim + kAttnDims - 1) / kAttnDims), dim3(256), smem, st, scores,
+                           vc, out, nullptr, nullptr, nullptr, n_head, n_kv_head, head_dim, state, window, tail));
     }
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
