@@ -316,6 +316,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the sweep / cpu baseline side measurements")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -336,14 +337,41 @@ def main():
     from zignn_b200 import sharding
     # every rank draws the same full-weight stream and keeps its row slice (sharding.row_range)
     raw_full = make_weight_bytes(q, n, k, 42, "cuda")
-    lin = sharding.cuda_sharded_linear(raw_full, ggml.TYPE_IDS[q], n, k, zq.ACT_F32)
+    # N > 1: the slices are exchanged by the library's peer-store kernel; --gather nccl (or a failed
+    # symmetric-memory set-up) uses all_gather_into_tensor instead
+    gather_mode = args.gather if use_dist else "none"
+    lin = None
+    if gather_mode == "peer":
+        try:
+            lin = sharding.cuda_sharded_linear(raw_full, ggml.TYPE_IDS[q], n, k, zq.ACT_F32, gather="peer", m_rows=1)
+        except Exception as e:
+            gather_mode = "nccl (peer set-up failed: %r)" % (e,)
+    if lin is None:
+        lin = sharding.cuda_sharded_linear(raw_full, ggml.TYPE_IDS[q], n, k, zq.ACT_F32)
     del raw_full
     qw, n_local = lin.weight, lin.rows
     x = torch.randn(1, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(43))
     y_local = torch.zeros(1, lin.per, device="cuda")
 
+    # One rank's shard is smaller than L2 (126 MB) from 2 ranks up. Consecutive steps therefore use
+    # different copies of the shard, enough of them to exceed L2, so every step streams from HBM.
+    local_weight_bytes = max(1, n_local * (k // 32) * BPB[q])
+    copies = 1
+    if use_dist:
+        copies = max(2, int(-(-170e6 // local_weight_bytes)))
+        copies += copies % 2  # the peer exchange alternates two buffers: keep sequences even
+    weights = [qw]
+    for _ in range(copies - 1):
+        weights.append(zq.QuantWeight(qw.raw_bytes(), ggml.TYPE_IDS[q], n_local, k) if n_local else None)
+    counter = [0]
+
     def step():
-        lin.forward_local(x, out=y_local)
+        w = weights[counter[0] % copies]
+        counter[0] += 1
+        if gather_mode == "peer":
+            return lin.forward(x, weight=w)  # GEMV with the exchange fused in (or GEMV + exchange kernel)
+        if w is not None:
+            zq.quant_matmul_no_grad(x, w, zq.ACT_F32, out=y_local)
         return lin.gather(y_local) if use_dist else y_local
 
     def sync():
@@ -351,29 +379,39 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    # one rank's shard is smaller than L2 (126 MB) from 2 ranks up: evict it between timed steps
-    local_weight_bytes = n_local * (k // 32) * BPB[q]
-    flush = None
-    if local_weight_bytes < 160e6:
-        flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-        flush = lambda: flush_buf.fill_(1)
-    for _ in range(max(3, args.warmup)):
-        step()
-    timed_step = step
-    if not use_dist:
-        # one step = one replay of a captured launch (the host-side call overhead of the Python binding
-        # would otherwise be part of a 35 us step); the end-to-end leg below uses plain calls
+    for _ in range(max(3, args.warmup) + (copies - max(3, args.warmup) % copies) % copies):
+        step()  # a whole number of passes over the copies: the next step uses copy 0 again
+    # Steps are replayed from a captured launch sequence (one pass over the copies): the host-side call
+    # overhead of the Python binding would otherwise be a large part of a 10-35 us step. NCCL's collective
+    # stays outside capture; the end-to-end leg below always uses plain calls.
+    seq_len = copies
+    graph = None
+    if gather_mode in ("none", "peer"):
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
+            for _ in range(seq_len):
+                step()
+        graph.replay()  # one untimed replay
+    sync()
+
+    def timed_region():
+        """Exactly args.steps steps: whole replays of the captured sequence, then the rest as plain calls."""
+        if graph is None:
+            for _ in range(args.steps):
+                step()
+            return
+        for _ in range(args.steps // seq_len):
+            graph.replay()
+        for _ in range(args.steps % seq_len):
             step()
-        timed_step = graph.replay
-        for _ in range(3):
-            timed_step()
+
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    total_ms = time_region(torch, timed_step, args.steps, sync, flush)
+    total_ms = time_region(torch, timed_region, 1, sync)
+    if gather_mode == "peer" and (args.steps % seq_len) % 2:
+        step()  # untimed: back to an even number of exchanges
     clocks = sampler.stop() if sampler else None
     if use_dist:
         tmax = torch.tensor([total_ms], device="cuda")
@@ -394,7 +432,7 @@ def main():
 
     for _ in range(3):
         e2e_step()
-    e2e_ms = time_region(torch, e2e_step, args.steps, sync, flush)
+    e2e_ms = time_region(torch, e2e_step, args.steps, sync)
     if use_dist:
         tmax = torch.tensor([e2e_ms], device="cuda")
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -405,8 +443,14 @@ def main():
         peak, peak_kind = measured_peak()
         kernel_ms = ms
         if use_dist:  # the GEMV alone, for the roofline of the dominant kernel
-            kernel_ms = time_region(torch, lambda: lin.forward_local(x, out=y_local), args.steps,
-                                    torch.cuda.synchronize, flush) / args.steps
+            kc = [0]
+
+            def kernel_only():
+                w = weights[kc[0] % copies]
+                kc[0] += 1
+                if w is not None:
+                    zq.quant_matmul_no_grad(x, w, zq.ACT_F32, out=y_local)
+            kernel_ms = graph_time_us(torch, [kernel_only] * copies) * 1e-3
         local_bytes = algorithmic_bytes(q, n_local, k)
         achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
         line = {
@@ -414,15 +458,19 @@ def main():
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": dict(workload="configs[1]: Q4_0 GEMV 1152->262144, M=1, f32 activations",
-                           weights="N(0,0.02) seed 42 quantised q4_0", l2=("weights (170 MB) larger than L2 (126 MB)" if flush is None else
-                               "256 MB write between timed steps evicts L2 (per-step event pairs)"),
-                           sharding="rows split over %d rank(s)%s" % (world, ", NCCL all-gather of outputs" if use_dist else ""),
-                           launch="CUDA graph replay per step" if not use_dist else "plain calls"),
+                           weights="N(0,0.02) seed 42 quantised q4_0", l2=("weights (170 MB) larger than L2 (126 MB)" if copies == 1 else
+                               "%d copies of the %.0f MB shard used in turn (together larger than L2)"
+                               % (copies, local_weight_bytes / 1e6)),
+                           sharding="rows split over %d rank(s)%s" % (
+                               world, ", all-gather of outputs: " + gather_mode +
+                               (" stores fused into the GEMV epilogue" if getattr(lin, "fused", False) else "")
+                               if use_dist else ""),
+                           launch="CUDA graph replay" if graph is not None else "plain calls"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES, "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": local_bytes, "kernel": "gemv_mma_kernel<q4_0>"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k, "d2h_bytes_per_step": hy.numel() * 4},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * (1 if gather_mode != "peer" or getattr(lin, "fused", False) else 3),
             "clocks": clocks,
         }
         if not args.no_extra and world == 1:

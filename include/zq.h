@@ -172,6 +172,46 @@ int zq_matvec_f32(const float* d_w, const float* d_x, float* d_y, uint32_t out_d
 /* argmax with first-maximum-wins ties (src/models/gpt2.zig:980-990). Result in d_index[0]. */
 int zq_argmax(const float* d_logits, uint32_t n, int32_t* d_index, zq_stream stream);
 
+/* ------------------------------------------------ row sharding over GPUs */
+
+/* All-gather of the output slices of a row-sharded linear over NVLink peer memory. The reference
+ * splits a matmul's rows over CPU threads that share one output buffer
+ * (ThreadPool.matmul, src/gguf/thread_pool.zig:96-181); across GPUs every rank has its own copy of the
+ * output, so after computing y[slice_offset .. slice_offset + slice_len) into its own buffer a rank
+ * calls this to copy that range into the same place of every peer's buffer (plain peer stores) and to
+ * wait until every peer has done the same for the current round.
+ *   h_y_peers[r]    device pointer, valid on this GPU, to rank r's result buffer (entry `rank` = own)
+ *   h_flag_peers[r] device pointer, valid on this GPU, to rank r's counters: `world` uint32, zeroed once
+ *   round           1, 2, 3, ... — the same value on every rank for the same call, growing by one per call
+ * The caller alternates two result buffers between rounds (a peer may run one round ahead). Ranks
+ * must reach the call within about a second of each other: the wait is bounded and records a timeout
+ * in the word zq_device_error() reads instead of hanging. The two host arrays are read before return. */
+int zq_peer_gather(float* const* h_y_peers, uint32_t* const* h_flag_peers, uint32_t world, uint32_t rank,
+                   size_t slice_offset, size_t slice_len, uint32_t round, zq_stream stream);
+
+/* The same exchange with the round number kept in device memory (*d_round, zeroed once by the caller,
+ * incremented by this call on the stream) and the two alternating result buffers passed together: odd
+ * rounds use h_y_peers_odd, even rounds h_y_peers_even. Nothing in the launch depends on host state
+ * that changes between calls, so a stream capture that contains an even number of these calls can be
+ * replayed. The caller writes its slice into its own odd / even buffer accordingly. */
+int zq_peer_gather_step(float* const* h_y_peers_odd, float* const* h_y_peers_even,
+                        uint32_t* const* h_flag_peers, uint32_t world, uint32_t rank, size_t slice_offset,
+                        size_t slice_len, uint32_t* d_round, zq_stream stream);
+
+/* One activation row times a row-sharded weight with the exchange inside the GEMV kernel: every output
+ * row is stored into this rank's result buffer and, in the same epilogue, into every peer's (plain peer
+ * stores), so the all-gather overlaps the weight stream; the grid's last CTA then publishes a counter on
+ * every peer and waits (bounded, as above) for theirs. f32 activations.
+ *   w            this rank's rows [row_offset, row_offset + out_dim) of the whole matrix
+ *   h_y_peers_*  as for zq_peer_gather_step: whole result rows, odd / even rounds
+ *   h_flag_peers counters used by this entry point only (`world` uint32 per rank, zeroed once)
+ *   d_sync       two uint32 on this GPU, zeroed once: completed rounds, CTA arrivals
+ * Returns ZQ_ERR_UNSUPPORTED when the shard has too few rows for this kernel; the caller then uses
+ * zq_matmul followed by zq_peer_gather_step. */
+int zq_matmul_gather(const zq_weight* w, const float* d_x, const zq_epilogue* epilogue,
+                     float* const* h_y_peers_odd, float* const* h_y_peers_even, uint32_t* const* h_flag_peers,
+                     uint32_t world, uint32_t rank, uint32_t row_offset, uint32_t* d_sync, zq_stream stream);
+
 /* --------------------------------------------------- small ops (inference) */
 
 /* rms_norm_rows (src/models/gemma3.zig:906-946; MetalContext.dispatch_rms_norm,

@@ -42,6 +42,9 @@ SIGNATURES = {
     "zq_quantize_rows_q8": (i, [vp, u32, u32, vp, vp, vp, vp]),
     "zq_matvec_f32": (i, [vp, vp, vp, u32, u32, vp]),
     "zq_argmax": (i, [vp, u32, vp, vp]),
+    "zq_peer_gather": (i, [vp, vp, u32, u32, C.c_size_t, C.c_size_t, u32, vp]),
+    "zq_peer_gather_step": (i, [vp, vp, vp, u32, u32, C.c_size_t, C.c_size_t, vp, vp]),
+    "zq_matmul_gather": (i, [vp, vp, vp, vp, vp, vp, u32, u32, u32, vp, vp]),
     "zq_rms_norm": (i, [vp, vp, vp, u32, u32, f, vp]),
     "zq_rms_norm_residual": (i, [vp, vp, vp, u32, u32, f, vp]),
     "zq_rms_norm_in_place": (i, [vp, vp, u32, u32, f, vp]),

@@ -535,6 +535,14 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
     return ZQ_ERR_BAD_ARG;
 }
 
+int zq_matmul_gather(const zq_weight* w, const float* d_x, const zq_epilogue* epilogue,
+                     float* const* h_y_peers_odd, float* const* h_y_peers_even, uint32_t* const* h_flag_peers,
+                     uint32_t world, uint32_t rank, uint32_t row_offset, uint32_t* d_sync, zq_stream stream) {
+    if (!w || !d_x || !h_y_peers_odd || !h_y_peers_even || !h_flag_peers || !d_sync) return ZQ_ERR_BAD_ARG;
+    return launch_gemv_gather_f32(w, d_x, epilogue, h_y_peers_odd, h_y_peers_even, h_flag_peers, world, rank,
+                                  row_offset, d_sync, as_stream(stream));
+}
+
 int zq_matvec_f32(const float* d_w, const float* d_x, float* d_y, uint32_t out_dim, uint32_t in_dim,
                   zq_stream stream) {
     if (!d_w || !d_x || !d_y || out_dim == 0 || in_dim == 0) return ZQ_ERR_BAD_ARG;

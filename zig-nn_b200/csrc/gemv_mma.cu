@@ -582,6 +582,28 @@ __device__ __forceinline__ void lds128_keep(uint4& v, uint32_t addr, uint32_t pr
 }
 
 constexpr int kRowWarps = 8;  // warps per CTA, one 16-row tile each
+
+// Row-sharded use: besides its own result buffer the kernel stores every output row into the same
+// place of each peer's buffer (plain stores to peer-mapped memory over NVLink), so the all-gather of the
+// slices happens while the weights are still streaming. When the last CTA of the grid is done it adds 1
+// to this rank's counter on every peer and waits — bounded — until every peer's counter here has
+// reached the round number. world <= 1: an ordinary GEMV into `y`.
+constexpr int kPeerMax = 8;
+constexpr uint32_t kPeerSpinLimit = 1u << 20;               // polls before giving up (about a second)
+constexpr unsigned int kErrFusedGatherTimeout = 0x46474154u;  // 'FGAT'
+struct PeerArgs {
+    float* y[2][kPeerMax];       // [round parity][rank]: result buffers, entry `rank` is this GPU's own
+    uint32_t* flags[kPeerMax];   // [rank]: that rank's counters, one uint32 per source rank
+    uint32_t* sync;              // this GPU: [0] completed rounds, [1] CTAs that have finished the current one
+    unsigned int* err;           // the library's device-error word
+    uint32_t world, rank, row_off;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 // Quads in flight per lane. They travel through a per-lane cp.async ring in shared memory: register
 // prefetch cannot go deep (a warp has six load scoreboards, and later loads share them with earlier
 // ones). Measured on the 1152 -> 262144 head: depths 3..7 are within 2% of each other once the scales
@@ -609,7 +631,7 @@ template <int TYPE, int D, int CTAS>
 __global__ void __launch_bounds__(kRowWarps * 32, CTAS)
 gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const float* __restrict__ x,
                  float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t scp, uint32_t sc_off,
-                 uint32_t ring_off, EpilogueArgs ep) {
+                 uint32_t ring_off, EpilogueArgs ep, PeerArgs pa) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QB = Q8 ? 32 : 16;
@@ -627,6 +649,12 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     constexpr uint32_t rows_per_cta = kRowWarps * 16;
+
+    // sharded: every CTA reads the round before any CTA can finish it (the counter moves only when all
+    // CTAs have arrived at the end of the kernel)
+    const bool sharded = pa.world > 1;
+    const uint32_t round = sharded ? pa.sync[0] + 1 : 0;
+    if (sharded) y = pa.y[round & 1u][pa.rank] + pa.row_off;
 
     // Scales of a whole 16-row tile (contiguous in memory) are copied to this warp's shared buffer when
     // the producer enters the tile; two buffers, because the producer is less than one tile ahead.
@@ -787,8 +815,20 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
             vb += __shfl_xor_sync(0xFFFFFFFFu, vb, 2);
             const uint32_t r0 = (uint32_t)(c_tile * rows_per_cta) + warp * 16 + g;
             if (t == 0) {
-                if (r0 < N) y[r0] = apply_epilogue(va * ps, ep, r0, r0);
-                if (r0 + 8 < N) y[r0 + 8] = apply_epilogue(vb * ps, ep, r0 + 8, r0 + 8);
+                if (r0 < N) {
+                    const float o = apply_epilogue(va * ps, ep, r0, r0);
+                    y[r0] = o;
+                    if (sharded)
+                        for (uint32_t p = 0; p < pa.world; ++p)
+                            if (p != pa.rank) pa.y[round & 1u][p][pa.row_off + r0] = o;
+                }
+                if (r0 + 8 < N) {
+                    const float o = apply_epilogue(vb * ps, ep, r0 + 8, r0 + 8);
+                    y[r0 + 8] = o;
+                    if (sharded)
+                        for (uint32_t p = 0; p < pa.world; ++p)
+                            if (p != pa.rank) pa.y[round & 1u][p][pa.row_off + r0 + 8] = o;
+                }
             }
             c_q = 0;
             c_tile += gridDim.x;
@@ -816,10 +856,39 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
         c_slot = c_slot + 1 == (uint32_t)D ? 0 : c_slot + 1;
         consume(r);
     }
+
+    if (sharded) {
+        __threadfence_system();  // this thread's peer stores are visible system-wide ...
+        __syncthreads();         // ... for every thread of the CTA, before the CTA counts itself done
+        if (tid == 0) {
+            const uint32_t ticket = atomicAdd(pa.sync + 1, 1u);
+            if (ticket == gridDim.x - 1) {  // every CTA has stored, fenced and arrived
+                __threadfence_system();
+                for (uint32_t p = 0; p < pa.world; ++p)
+                    if (p != pa.rank) atomicAdd_system(pa.flags[p] + pa.rank, 1u);
+                for (uint32_t p = 0; p < pa.world; ++p) {
+                    if (p == pa.rank) continue;
+                    bool ok = false;
+                    for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
+                        if ((int32_t)(ld_acquire_sys_u32(pa.flags[pa.rank] + p) - round) >= 0) {
+                            ok = true;
+                            break;
+                        }
+                        __nanosleep(32);
+                    }
+                    if (!ok) atomicExch(pa.err, kErrFusedGatherTimeout);
+                }
+                pa.sync[1] = 0;
+                __threadfence();
+                pa.sync[0] = round;  // later kernels on this stream see the completed round
+            }
+        }
+    }
 }
 
 template <int TYPE, int D, int CTAS>
-int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
+int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
+                     cudaStream_t st) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     const uint32_t sms = (uint32_t)sm_count();
@@ -840,14 +909,25 @@ int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs 
     const uint32_t cap = sms * CTAS;
     kern<<<cta_tiles < cap ? cta_tiles : cap, kRowWarps * 32, smem, st>>>(
         w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim, w->in_dim, w->nb, w->scp, sc_off, ring_off,
-        ep);
+        ep, pa);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
 
 template <int TYPE>
-int launch_rows1(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, cudaStream_t st) {
-    return launch_rows1_cfg<TYPE, kRows1Depth, kCtasPerSm>(w, x, y, ep, st);
+int launch_rows1(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
+                 cudaStream_t st) {
+    return launch_rows1_cfg<TYPE, kRows1Depth, kCtasPerSm>(w, x, y, ep, pa, st);
+}
+
+int launch_rows1_any(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
+                     cudaStream_t st) {
+    switch (w->type) {
+        case ZQ_TYPE_Q4_0: return launch_rows1<ZQ_TYPE_Q4_0>(w, x, y, ep, pa, st);
+        case ZQ_TYPE_Q4_1: return launch_rows1<ZQ_TYPE_Q4_1>(w, x, y, ep, pa, st);
+        case ZQ_TYPE_Q8_0: return launch_rows1<ZQ_TYPE_Q8_0>(w, x, y, ep, pa, st);
+        default: return ZQ_ERR_UNSUPPORTED;
+    }
 }
 
 struct Plan {
@@ -943,13 +1023,8 @@ int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m
     // One activation row and enough 16-row tiles to give every resident warp its own rows: the
     // block-per-column kernel. Otherwise the general kernel (activation rows in columns, K split).
     if (m_rows == 1 && (w->out_dim + 15) / 16 >= (uint32_t)sm_count() * kCtasPerSm * kRowWarps) {
-        int rc = ZQ_ERR_UNSUPPORTED;
-        switch (w->type) {
-            case ZQ_TYPE_Q4_0: rc = launch_rows1<ZQ_TYPE_Q4_0>(w, x, y, a, st); break;
-            case ZQ_TYPE_Q4_1: rc = launch_rows1<ZQ_TYPE_Q4_1>(w, x, y, a, st); break;
-            case ZQ_TYPE_Q8_0: rc = launch_rows1<ZQ_TYPE_Q8_0>(w, x, y, a, st); break;
-            default: return ZQ_ERR_UNSUPPORTED;
-        }
+        PeerArgs none{};
+        const int rc = launch_rows1_any(w, x, y, a, none, st);
         if (rc != ZQ_ERR_LIMIT) return rc;
     }
     switch (w->type) {
@@ -958,6 +1033,40 @@ int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m
         case ZQ_TYPE_Q8_0: return launch_ns<ZQ_TYPE_Q8_0>(w, x, y, m_rows, a, st);
         default: return ZQ_ERR_UNSUPPORTED;
     }
+}
+
+
+// One activation row, row-sharded weight: GEMV with the all-gather of the output slices in its epilogue.
+// ZQ_ERR_UNSUPPORTED when the shard is too small for the whole-rows kernel (the caller then runs the
+// plain GEMV followed by the separate exchange).
+int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue* ep, float* const* y_odd,
+                           float* const* y_even, uint32_t* const* flags, uint32_t world, uint32_t rank,
+                           uint32_t row_off, uint32_t* d_sync, cudaStream_t st) {
+    if (world < 2 || world > (uint32_t)kPeerMax || rank >= world) return ZQ_ERR_BAD_ARG;
+    if (((uintptr_t)x & 15) != 0) return ZQ_ERR_BAD_ARG;
+    if ((w->out_dim + 15) / 16 < (uint32_t)sm_count() * kRowWarps) return ZQ_ERR_UNSUPPORTED;
+    EpilogueArgs a{nullptr, nullptr, nullptr, 0};
+    if (ep) {
+        a.bias = ep->d_bias;
+        a.gelu = ep->gelu;
+        a.mul = ep->d_mul;
+        a.residual = ep->d_residual;
+    }
+    PeerArgs pa{};
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!y_odd[r] || !y_even[r] || !flags[r]) return ZQ_ERR_BAD_ARG;
+        pa.y[1][r] = y_odd[r];
+        pa.y[0][r] = y_even[r];
+        pa.flags[r] = flags[r];
+    }
+    pa.sync = d_sync;
+    int rc = device_error_word(&pa.err);
+    if (rc != ZQ_OK) return rc;
+    pa.world = world;
+    pa.rank = rank;
+    pa.row_off = row_off;
+    rc = launch_rows1_any(w, x, nullptr, a, pa, st);
+    return rc == ZQ_ERR_LIMIT ? ZQ_ERR_UNSUPPORTED : rc;
 }
 
 }  // namespace zq

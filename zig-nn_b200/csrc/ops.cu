@@ -366,7 +366,9 @@ __device__ __forceinline__ void quantize_block_warp(float v, size_t blk, int lan
 // RES = true:   res += rms_norm(src, w1);  h = rms_norm(res, w2)     -> quantised
 // (gemma3.zig:662-666, 725-737, 768-773: post-norm + residual, then the next block's pre-norm.)
 // One CTA; dim is a multiple of 32.
-template <bool RES>
+// PER > 0: dim <= 256 * PER and every global operand is fetched into registers up front, so the
+// kernel pays one memory round trip instead of one per phase; PER = 0 is the general form.
+template <bool RES, int PER>
 __global__ void __launch_bounds__(256)
 norm_quant_kernel(const float* __restrict__ src, const float* __restrict__ w1, float* __restrict__ res,
                   const float* __restrict__ w2, uint32_t dim, float eps, int8_t* __restrict__ q,
@@ -374,31 +376,77 @@ norm_quant_kernel(const float* __restrict__ src, const float* __restrict__ w1, f
     extern __shared__ __align__(16) float xs[];
     __shared__ float part[16];
     __shared__ float bc;
+    constexpr int P = PER > 0 ? PER : 1;
+    float rw1[P], rw2[P], rres[P];
     pdl_launch_dependents();
-    for (uint32_t i = threadIdx.x * 32; i < dim; i += blockDim.x * 32) {  // norm weights: one line per thread
-        prefetch_l2_line(w1 + i);
-        if (RES) prefetch_l2_line(w2 + i);
+    if (PER > 0) {
+#pragma unroll
+        for (int u = 0; u < P; ++u) {
+            const uint32_t i = threadIdx.x + u * 256;
+            rw1[u] = i < dim ? w1[i] : 0.0f;
+            rw2[u] = (RES && i < dim) ? w2[i] : 0.0f;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x * 32; i < dim; i += blockDim.x * 32) {  // norm weights: one line per thread
+            prefetch_l2_line(w1 + i);
+            if (RES) prefetch_l2_line(w2 + i);
+        }
     }
     pdl_wait();
-    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) xs[i] = src[i];
+    if (PER > 0) {
+        float rs[P];
+#pragma unroll
+        for (int u = 0; u < P; ++u) {
+            const uint32_t i = threadIdx.x + u * 256;
+            rs[u] = i < dim ? src[i] : 0.0f;
+            rres[u] = (RES && i < dim) ? res[i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < P; ++u) {
+            const uint32_t i = threadIdx.x + u * 256;
+            if (i < dim) xs[i] = rs[u];
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) xs[i] = src[i];
+    }
     __syncthreads();
     float ss = sumsq_lanes16(xs, dim, part, &bc);
     float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
-    const float* wq = w1;
     if (RES) {
-        for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
-            const float r = __fadd_rn(res[i], __fmul_rn(__fmul_rn(xs[i], inv), w1[i]));
-            res[i] = r;
-            xs[i] = r;
+        if (PER > 0) {
+#pragma unroll
+            for (int u = 0; u < P; ++u) {
+                const uint32_t i = threadIdx.x + u * 256;
+                if (i < dim) {
+                    const float r = __fadd_rn(rres[u], __fmul_rn(__fmul_rn(xs[i], inv), rw1[u]));
+                    res[i] = r;
+                    xs[i] = r;
+                }
+            }
+        } else {
+            for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
+                const float r = __fadd_rn(res[i], __fmul_rn(__fmul_rn(xs[i], inv), w1[i]));
+                res[i] = r;
+                xs[i] = r;
+            }
         }
         __syncthreads();
         ss = sumsq_lanes16(xs, dim, part, &bc);
         inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
-        wq = w2;
     }
     const int lane = threadIdx.x & 31;
-    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x)
-        quantize_block_warp(__fmul_rn(__fmul_rn(xs[i], inv), wq[i]), i >> 5, lane, q, scale, sum);
+    if (PER > 0) {
+#pragma unroll
+        for (int u = 0; u < P; ++u) {
+            const uint32_t i = threadIdx.x + u * 256;
+            if (i < dim)  // dim is a multiple of 32: whole warps
+                quantize_block_warp(__fmul_rn(__fmul_rn(xs[i], inv), RES ? rw2[u] : rw1[u]), i >> 5, lane, q, scale, sum);
+        }
+    } else {
+        const float* wq = RES ? w2 : w1;
+        for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x)
+            quantize_block_warp(__fmul_rn(__fmul_rn(xs[i], inv), wq[i]), i >> 5, lane, q, scale, sum);
+    }
 }
 
 // Per-head work between the QKV projection and attention (gemma3.zig:689-716): q and k heads get
@@ -630,12 +678,20 @@ inline unsigned grid1d(size_t n, unsigned threads) { return (unsigned)((n + thre
 int launch_norm_quant(const float* src, const float* w1, float* res, const float* w2, uint32_t dim, float eps,
                       int8_t* q, float* scale, int32_t* sum, cudaStream_t st) {
     if (dim == 0 || dim % 32 || dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
-    if (res)
-        ZQ_CUDA(launch_pdl(norm_quant_kernel<true>, dim3(1), dim3(256), dim * sizeof(float), st, src, w1, res, w2,
-                           dim, eps, q, scale, sum));
-    else
-        ZQ_CUDA(launch_pdl(norm_quant_kernel<false>, dim3(1), dim3(256), dim * sizeof(float), st, src, w1,
-                           nullptr, nullptr, dim, eps, q, scale, sum));
+    const size_t smem = dim * sizeof(float);
+    cudaError_t e;
+    if (dim <= 256 * 5) {
+        e = res ? launch_pdl(norm_quant_kernel<true, 5>, dim3(1), dim3(256), smem, st, src, w1, res, w2, dim, eps, q,
+                             scale, sum)
+                : launch_pdl(norm_quant_kernel<false, 5>, dim3(1), dim3(256), smem, st, src, w1, nullptr, nullptr, dim,
+                             eps, q, scale, sum);
+    } else {
+        e = res ? launch_pdl(norm_quant_kernel<true, 0>, dim3(1), dim3(256), smem, st, src, w1, res, w2, dim, eps, q,
+                             scale, sum)
+                : launch_pdl(norm_quant_kernel<false, 0>, dim3(1), dim3(256), smem, st, src, w1, nullptr, nullptr, dim,
+                             eps, q, scale, sum);
+    }
+    ZQ_CUDA(e);
     return ZQ_OK;
 }
 

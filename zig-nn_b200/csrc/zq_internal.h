@@ -111,6 +111,10 @@ int launch_gemv_f32(const zq_weight* w, const float* x, float* y, uint32_t m_row
 // Tensor-core f32-activation GEMV for m_rows <= 16 (gemv_mma.cu); x must be 16-byte aligned.
 int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
                         const zq_epilogue* ep, cudaStream_t st);
+// f32-activation GEMV for one row with the all-gather of row-sharded outputs fused in (gemv_mma.cu).
+int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue* ep, float* const* y_odd,
+                           float* const* y_even, uint32_t* const* flags, uint32_t world, uint32_t rank,
+                           uint32_t row_off, uint32_t* d_sync, cudaStream_t st);
 int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum,
                    float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
 int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, int8_t* q,

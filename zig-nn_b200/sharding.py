@@ -96,8 +96,128 @@ class ShardedQuantLinear:
         return self.gather(self.forward_local(x))
 
 
-def cuda_sharded_linear(raw, quant_type, out_dim, in_dim, act_mode=0, group=None):
-    """ShardedQuantLinear whose per-rank product is the CUDA kernel (raw: uint8 tensor on the device)."""
+class PeerGather:
+    """The all-gather as peer stores over NVLink (csrc/peer_gather.cu) instead of a library collective.
+
+    Result buffers and counters live in symmetric memory (torch.distributed._symmetric_memory supplies
+    the allocation and the exchange of peer-mapped pointers; the copy and the flag protocol are the
+    library's own kernel). Two result buffers alternate between rounds. Layout of a buffer:
+    [world][m][per] f32, rank r's slice at r * m * per, the same layout all_gather_into_tensor produces.
+    """
+
+    def __init__(self, world, rank, m, per, device, group=None):
+        import os
+        import ctypes as C
+        import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings are all we use
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        self._lib, self._C = _lib, C
+        self.world, self.rank, self.m, self.per = world, rank, m, per
+        grp = group if group is not None else dist.group.WORLD
+        n = world * m * per
+        self.bufs, self._yptrs = [], []
+        for _ in range(2):
+            t = symm_mem.empty(n, dtype=torch.float32, device=device)
+            t.zero_()
+            h = symm_mem.rendezvous(t, grp)
+            self.bufs.append(t)
+            self._yptrs.append((C.c_void_p * world)(*[int(p) for p in h.buffer_ptrs]))
+        self.flags = symm_mem.empty(world, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        hf = symm_mem.rendezvous(self.flags, grp)
+        self._fptrs = (C.c_void_p * world)(*[int(p) for p in hf.buffer_ptrs])
+        self._handles = (h, hf)
+        self.round = 0                                                     # host copy of the round number
+        self.d_round = torch.zeros(1, dtype=torch.int32, device=device)    # the kernel's own copy
+        # the fused GEMV + exchange keeps its own counters
+        self.fflags = symm_mem.empty(world, dtype=torch.int32, device=device)
+        self.fflags.zero_()
+        hff = symm_mem.rendezvous(self.fflags, grp)
+        self._ffptrs = (C.c_void_p * world)(*[int(p) for p in hff.buffer_ptrs])
+        self._handles = self._handles + (hff,)
+        self.d_sync = torch.zeros(2, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)  # every rank's counters are zero before anybody adds to them
+
+    def next_buffer(self):
+        """The buffer this round's local slice goes into: [world][m][per], write row-block `rank`."""
+        return self.bufs[(self.round + 1) & 1].view(self.world, self.m, self.per)
+
+    def gather(self):
+        """Publish this rank's slice of next_buffer() to all peers and wait for theirs; returns the buffer.
+        The round number is kept on the device too, so a captured sequence with an even number of
+        forward() calls can be replayed (call note_replayed() after each replay)."""
+        self.round += 1
+        which = self.round & 1
+        C = self._C
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        n = self.m * self.per
+        rc = self._lib.load().zq_peer_gather_step(self._yptrs[1], self._yptrs[0], self._fptrs, self.world, self.rank,
+                                                  self.rank * n, n, C.c_void_p(self.d_round.data_ptr()), stream)
+        self._lib.check(rc, "zq_peer_gather_step")
+        return self.bufs[which].view(self.world, self.m, self.per)
+
+    def fused_matmul(self, x, weight):
+        """x [1][in_dim] times this rank's weight rows with the exchange inside the GEMV kernel.
+        Returns the gathered buffer, or None when the shard is too small for that kernel (nothing ran)."""
+        C = self._C
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rc = self._lib.load().zq_matmul_gather(weight.handle, C.c_void_p(x.data_ptr()), None, self._yptrs[1],
+                                               self._yptrs[0], self._ffptrs, self.world, self.rank,
+                                               self.rank * self.per, C.c_void_p(self.d_sync.data_ptr()), stream)
+        if rc == 2:  # ZQ_ERR_UNSUPPORTED
+            return None
+        self._lib.check(rc, "zq_matmul_gather")
+        self.round += 1
+        return self.bufs[self.round & 1].view(self.world, self.m, self.per)
+
+    def note_replayed(self, n_calls):
+        """A captured sequence containing `n_calls` (even) gather() calls has been replayed once."""
+        if n_calls % 2:
+            raise ValueError("a replayable sequence holds an even number of rounds")
+        self.round += n_calls
+
+
+class PeerShardedLinear(ShardedQuantLinear):
+    """ShardedQuantLinear whose slices are exchanged by PeerGather: the local product is written straight
+    into this rank's row-block of the symmetric result buffer, then pushed to the peers."""
+
+    def __init__(self, *args, m_rows=1, device=None, **kw):
+        super().__init__(*args, **kw)
+        self.m_rows = m_rows
+        self.fused = None  # None: not tried yet; True / False: the fused kernel does / does not take this shard
+        self.peer = PeerGather(self.world, self.rank, m_rows, self.per, device, group=self.group)
+
+    def forward(self, x, weight=None):
+        """weight: another device copy of this rank's rows to use instead of the one built at construction."""
+        m = x.shape[0]
+        if m != self.m_rows:
+            raise ValueError("built for %d activation rows, got %d" % (self.m_rows, m))
+        w = weight if weight is not None else self.weight
+        even = self.out_dim == self.world * self.per  # every rank owns `per` rows: all ranks take the same branch
+        if m == 1 and self.fused is not False and even:
+            g = self.peer.fused_matmul(x, w)
+            self.fused = g is not None
+            if g is not None:
+                return g.reshape(1, self.world * self.per)[:, :self.out_dim]
+        buf = self.peer.next_buffer()
+        if self.rows:
+            if self.rows == self.per:
+                self.compute(x, w, buf[self.rank])
+            else:
+                tmp = torch.empty(m, self.rows, dtype=torch.float32, device=x.device)
+                self.compute(x, w, tmp)
+                buf[self.rank][:, :self.rows] = tmp
+        g = self.peer.gather()
+        if m == 1:
+            return g.reshape(1, self.world * self.per)[:, :self.out_dim]
+        return g.permute(1, 0, 2).reshape(m, self.world * self.per)[:, :self.out_dim]
+
+
+def cuda_sharded_linear(raw, quant_type, out_dim, in_dim, act_mode=0, group=None, gather="nccl", m_rows=1):
+    """ShardedQuantLinear whose per-rank product is the CUDA kernel (raw: uint8 tensor on the device).
+    gather: "nccl" (all_gather_into_tensor) or "peer" (the library's peer-store kernel)."""
     from . import api
 
     def make_weight(part, qt, rows, k):
@@ -106,4 +226,7 @@ def cuda_sharded_linear(raw, quant_type, out_dim, in_dim, act_mode=0, group=None
     def compute(x, w, out):
         api.quant_matmul_no_grad(x, w, act_mode, out=out)
 
+    if gather == "peer":
+        return PeerShardedLinear(raw, quant_type, out_dim, in_dim, make_weight, compute, group=group,
+                                 m_rows=m_rows, device=raw.device)
     return ShardedQuantLinear(raw, quant_type, out_dim, in_dim, make_weight, compute, group=group)
