@@ -304,6 +304,36 @@ def decode_extra(torch, zq, ggml):
     return out
 
 
+def run_case(args):
+    """One quantised matmul, --steps timed calls on fresh weight copies (HBM-cold), one JSON line."""
+    import torch
+    import zignn_b200
+    from zignn_b200 import api as zq
+    from zignn_b200 import ggml
+    parts = args.case.split(",")
+    qname, k, n, m = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
+    mode = zq.ACT_Q8 if len(parts) > 4 and parts[4] == "q8" else zq.ACT_F32
+    raw = make_weight_bytes(qname, n, k, 42, "cuda")
+    wbytes = n * (k // 32) * BPB[qname]
+    copies = max(2, min(16, int(300e6 // wbytes) + 1))
+    ws = [zq.QuantWeight(raw, ggml.TYPE_IDS[qname], n, k) for _ in range(copies)]
+    x = torch.randn(m, k, device="cuda")
+    y = torch.empty(m, n, device="cuda")
+    wsb = torch.empty(max(_lib_ws(zq, ws[0], m, mode), 256), dtype=torch.uint8, device="cuda")
+    for i in range(max(1, args.warmup)):
+        zq.quant_matmul_no_grad(x, ws[i % copies], mode, out=y, workspace=wsb)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        zq.quant_matmul_no_grad(x, ws[i % copies], mode, out=y, workspace=wsb)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    print(json.dumps({"case": args.case, "us_per_call": us, "tflops": 2.0 * m * n * k / us / 1e6,
+                      "gbs": algorithmic_bytes(qname, n, k, m) / us / 1e3, "steps": args.steps}), flush=True)
+
+
 def _lib_ws(zq, w, m, mode):
     from zignn_b200 import _lib
     return _lib.load().zq_matmul_workspace_bytes(w.handle, m, mode)
@@ -317,9 +347,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the sweep / cpu baseline side measurements")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
+    ap.add_argument("--case", default=None, metavar="TYPE,K,N,M[,ACT]",
+                    help="time one quantised matmul (e.g. q4_0,4096,14336,512 or q8_0,1152,6912,1,q8) and exit; "
+                         "for profiling a kernel other than the headline one")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.case:
+        return run_case(args)
 
     import torch
     import zignn_b200

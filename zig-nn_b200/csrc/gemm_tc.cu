@@ -7,7 +7,10 @@
 //
 //   A operand  = 128 weight rows x 64 K (fp16, K-major, 128-byte swizzle), written by the dequantising
 //                warps straight from the packed GGUF words;
-//   B operand  = up to 256 activation rows x 64 K (fp16, K-major, same swizzle), copied with cp.async;
+//   B operand  = up to 256 activation rows x 64 K (fp16, K-major, same swizzle). The conversion kernel
+//                writes the fp16 activations segment-major ([K / 64][rows][64], chunks already swizzled,
+//                rows padded with zeros to whole tiles), so a stage's tile is one contiguous block that a
+//                single bulk copy (cp.async.bulk, completion counted on the stage's mbarrier) brings in;
 //   D          = 128 lanes x N columns of f32 in tensor memory (one lane per weight row).
 //
 // Roles: warps 0-7 produce stages (dequantise + copy) and later drain the accumulator; one thread of
@@ -66,9 +69,6 @@ __device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) 
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
 
 // ---- mbarrier / tcgen05 wrappers -----------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -76,6 +76,16 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// global -> shared bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned); the bytes are
+// counted on `bar` as they land
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -143,6 +153,42 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
 // Instruction descriptor, kind::f16: D = f32, A = B = fp16, both K-major, M x N tile.
 __host__ __device__ constexpr uint32_t idesc_f16(uint32_t m, uint32_t n) {
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ---- activations: f32 rows -> fp16, segment-major and pre-swizzled -------------------------------
+// xt[(seg * m_pad + m) * 64 + ((c ^ (m & 7)) * 8) + e] = fp16(x[m][seg * 64 + c * 8 + e] * 2^-e_m), zero for
+// m >= M or k >= K; post[m] = 2^e_m. One CTA per padded row.
+__global__ void __launch_bounds__(256)
+convert_rows_tiled_kernel(const float* __restrict__ x, __half* __restrict__ xt, float* __restrict__ post,
+                          uint32_t M, uint32_t K, uint32_t m_pad, uint32_t n_seg) {
+    __shared__ float red[8];
+    __shared__ float s_pre;
+    const uint32_t m = blockIdx.x;
+    const bool real = m < M;
+    const float* row = x + (size_t)(real ? m : 0) * K;
+    float amax = 0.0f;
+    if (real)
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = red[0];
+        for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
+        int e = 0;
+        if (a > 0.0f && a < INFINITY) e = ilogbf(a) - 13;
+        s_pre = ldexpf(1.0f, -e);
+        if (real) post[m] = ldexpf(1.0f, e);
+    }
+    __syncthreads();
+    const float pre = s_pre;
+    const uint32_t kp = n_seg * 64;  // padded K
+    for (uint32_t k = threadIdx.x; k < kp; k += blockDim.x) {
+        const uint32_t seg = k >> 6, c = (k >> 3) & 7u, e = k & 7u;
+        const float v = (real && k < K) ? row[k] * pre : 0.0f;
+        xt[((size_t)seg * m_pad + m) * 64 + ((c ^ (m & 7u)) << 3) + e] = __float2half_rn(v);
+    }
 }
 
 // ---- weight dequantisation (same mapping as gemm.cu: a thread owns (row, half) of a quad) ---------
@@ -235,10 +281,10 @@ __device__ __forceinline__ void store_dequant(const PackedQuad<TYPE>& p, uint32_
 
 template <int TYPE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const __half* __restrict__ x16,
+gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const __half* __restrict__ xt,
                const float* __restrict__ post, float* __restrict__ y, uint32_t N, uint32_t K, uint32_t M,
-               uint32_t nbp, uint32_t scp, uint32_t n_mma, uint32_t tmem_cols, unsigned int* err_word,
-               TcEpilogue ep) {
+               uint32_t m_pad, uint32_t nbp, uint32_t scp, uint32_t n_mma, uint32_t tmem_cols,
+               unsigned int* err_word, TcEpilogue ep) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QB = Q8 ? 32 : 16;
@@ -256,7 +302,7 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     const uint32_t acc_bar = bar32 + 2 * TC_STAGES * 8;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM;
+    const uint32_t n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * n_mma;
     const uint32_t n_stages = nbp / 2;  // 64-K stages (the row padding to whole quads is zero weights)
 
     if (tid == 0) {
@@ -286,34 +332,34 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
         const uint32_t wrow = min(n0 + prow, N - 1);
         const uint8_t* qrow = qs + (size_t)wrow * nbp * QB;
         const uint8_t* srow = sc + (size_t)wrow * scp * SB;
-        const uint32_t b_chunks = n_mma * 8;  // 16-byte chunks of the activation tile
-        PackedQuad<TYPE> pk;
+        // packed words of the current quad and of the next one (loaded a whole quad ahead of their use)
+        PackedQuad<TYPE> pk, pk_next;
+        const uint32_t n_quads = nbp / 4;
         load_packed<TYPE>(pk, qrow, srow, 0, phalf);
+        if (n_quads > 1) load_packed<TYPE>(pk_next, qrow, srow, 1, phalf);
         bool alive = true;
         for (uint32_t s = 0; s < n_stages && alive; ++s) {
             const uint32_t slot = s % TC_STAGES, round = s / TC_STAGES;
             if (round > 0) alive = mbar_wait(empty_bar(slot), (round - 1) & 1u, abort_p, err_word);
             if (!alive) break;
             const uint32_t a_tile = smem32 + slot * TC_STAGE_BYTES, b_tile = a_tile + TC_A_BYTES;
-            // activation rows: n_mma x 8 chunks, zero-filled past M and K
-            for (uint32_t idx = tid; idx < b_chunks; idx += TC_PRODUCERS) {
-                const uint32_t r = idx >> 3, c = idx & 7u;
-                const uint32_t m = m0 + r, k = s * TC_BK + c * 8;
-                const bool ok = m < M && k < K;
-                const __half* src = x16 + (size_t)(ok ? m : 0) * K + (ok ? k : 0);
-                cp_async16_zfill(b_tile + swz(r, c), src, ok ? 16u : 0u);
+            if (tid == 0) {
+                // the stage's activation tile: n_mma rows x 128 bytes, contiguous in the converted image
+                const uint32_t bytes = n_mma * 128u;
+                mbar_expect_tx(full_bar(slot), bytes);
+                bulk_copy_g2s(b_tile, xt + ((size_t)s * m_pad + m0) * 64, bytes, full_bar(slot));
             }
             if ((s & 1u) == 0) {
                 store_dequant<TYPE, 0>(pk, a_tile, prow, phalf);
             } else {
                 store_dequant<TYPE, 2>(pk, a_tile, prow, phalf);
-                if (s + 1 < n_stages) load_packed<TYPE>(pk, qrow, srow, (s + 1) >> 1, phalf);
+                pk = pk_next;
+                const uint32_t q_ahead = ((s + 1) >> 1) + 1;
+                if (q_ahead < n_quads) load_packed<TYPE>(pk_next, qrow, srow, q_ahead, phalf);
             }
-            asm volatile("cp.async.wait_all;" ::: "memory");
-            fence_proxy_async();  // generic-proxy writes (st.shared, cp.async) -> visible to the tensor core
+            fence_proxy_async();  // generic-proxy writes (st.shared) -> visible to the tensor core
             mbar_arrive(full_bar(slot));
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
 
         // ================= epilogue: drain tensor memory =================
         if (alive) alive = mbar_wait(acc_bar, 0, abort_p, err_word);
@@ -383,38 +429,54 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     }
 }
 
+// rows per CTA tile and padded row count for m_rows activation rows
+inline void tc_tiling(uint32_t m_rows, uint32_t* n_mma, uint32_t* m_pad) {
+    *n_mma = m_rows >= (uint32_t)TC_BM ? (uint32_t)TC_BM : ((m_rows + 63u) / 64u) * 64u;
+    *m_pad = ((m_rows + *n_mma - 1) / *n_mma) * *n_mma;
+}
+
 template <int TYPE>
-int launch_tc(const zq_weight* w, const __half* x16, const float* post, float* y, uint32_t M, TcEpilogue ep,
+int launch_tc(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
               cudaStream_t st) {
     auto kern = gemm_tc_kernel<TYPE>;
     const size_t smem = (size_t)TC_STAGES * TC_STAGE_BYTES + 1024;  // + alignment slack
     ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // activation rows per CTA: a multiple of 64 (the epilogue splits the columns in two halves of 32s)
-    uint32_t n_mma = M >= TC_BM ? TC_BM : ((M + 63u) / 64u) * 64u;
+    uint32_t n_mma, m_pad;
+    tc_tiling(M, &n_mma, &m_pad);
     uint32_t tmem_cols = 64;
     while (tmem_cols < n_mma) tmem_cols *= 2;
-    const dim3 grid((w->out_dim + TC_BN - 1) / TC_BN, (M + n_mma - 1) / n_mma);
-    if (n_mma != TC_BM && grid.y != 1) return ZQ_ERR_BAD_ARG;  // m0 = blockIdx.y * TC_BM assumes full tiles
+    const dim3 grid((w->out_dim + TC_BN - 1) / TC_BN, m_pad / n_mma);
     unsigned int* err_word = nullptr;
     int rc = device_error_word(&err_word);
     if (rc != ZQ_OK) return rc;
-    kern<<<grid, TC_THREADS, smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), x16, post, y, w->out_dim,
-                                          w->in_dim, M, w->nbp, w->scp, n_mma, tmem_cols, err_word, ep);
+    kern<<<grid, TC_THREADS, smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), xt, post, y, w->out_dim,
+                                          w->in_dim, M, m_pad, w->nbp, w->scp, n_mma, tmem_cols, err_word, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
 
 }  // namespace
 
-// Activation conversion is shared with gemm.cu (launch_convert_rows_f16).
+size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows) {
+    uint32_t n_mma, m_pad;
+    tc_tiling(m_rows, &n_mma, &m_pad);
+    const size_t xb = ((size_t)(w->nbp / 2) * m_pad * 64 * sizeof(__half) + 255) & ~(size_t)255;
+    const size_t pb = ((size_t)m_rows * sizeof(float) + 255) & ~(size_t)255;
+    return xb + pb;
+}
+
 int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
                    void* workspace, cudaStream_t st) {
     if (m_rows > 65535u * TC_BM) return ZQ_ERR_LIMIT;
-    const size_t xb = ((size_t)m_rows * w->in_dim * sizeof(__half) + 255) & ~(size_t)255;
-    __half* x16 = static_cast<__half*>(workspace);
+    uint32_t n_mma, m_pad;
+    tc_tiling(m_rows, &n_mma, &m_pad);
+    const uint32_t n_seg = w->nbp / 2;
+    const size_t xb = ((size_t)n_seg * m_pad * 64 * sizeof(__half) + 255) & ~(size_t)255;
+    __half* xt = static_cast<__half*>(workspace);
     float* post = reinterpret_cast<float*>(static_cast<char*>(workspace) + xb);
-    int rc = launch_convert_rows_f16(x, x16, post, m_rows, w->in_dim, st);
-    if (rc != ZQ_OK) return rc;
+    convert_rows_tiled_kernel<<<m_pad, 256, 0, st>>>(x, xt, post, m_rows, w->in_dim, m_pad, n_seg);
+    ZQ_LAUNCH_CHECK();
     TcEpilogue a{nullptr, nullptr, nullptr, 0};
     if (ep) {
         a.bias = ep->d_bias;
@@ -423,9 +485,9 @@ int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows
         a.residual = ep->d_residual;
     }
     switch (w->type) {
-        case ZQ_TYPE_Q4_0: return launch_tc<ZQ_TYPE_Q4_0>(w, x16, post, y, m_rows, a, st);
-        case ZQ_TYPE_Q4_1: return launch_tc<ZQ_TYPE_Q4_1>(w, x16, post, y, m_rows, a, st);
-        case ZQ_TYPE_Q8_0: return launch_tc<ZQ_TYPE_Q8_0>(w, x16, post, y, m_rows, a, st);
+        case ZQ_TYPE_Q4_0: return launch_tc<ZQ_TYPE_Q4_0>(w, xt, post, y, m_rows, a, st);
+        case ZQ_TYPE_Q4_1: return launch_tc<ZQ_TYPE_Q4_1>(w, xt, post, y, m_rows, a, st);
+        case ZQ_TYPE_Q8_0: return launch_tc<ZQ_TYPE_Q8_0>(w, xt, post, y, m_rows, a, st);
         default: return ZQ_ERR_UNSUPPORTED;
     }
 }

@@ -473,7 +473,10 @@ size_t zq_matmul_workspace_bytes(const zq_weight* w, uint32_t m_rows, int act_mo
         const size_t s = ((size_t)m_rows * w->nb * 4 + 255) & ~(size_t)255;
         return q + 2 * s;
     }
-    if (act_mode == ZQ_ACT_F32 && m_rows >= kGemmMinRows) return gemm_f16_workspace_bytes(w, m_rows);
+    if (act_mode == ZQ_ACT_F32 && m_rows >= kGemmMinRows) {  // either GEMM kernel can use it
+        const size_t a = gemm_f16_workspace_bytes(w, m_rows), b = gemm_tc_workspace_bytes(w, m_rows);
+        return a > b ? a : b;
+    }
     return 0;
 }
 
@@ -494,7 +497,7 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
         if (((uintptr_t)d_x & 15) != 0) return launch_gemv_f32(w, d_x, d_y, m_rows, epilogue, st);
         // many rows and a workspace for the fp16 activations: the tensor-core GEMM
         if (m_rows >= kGemmMinRows && d_workspace && ((uintptr_t)d_workspace & 255) == 0 &&
-            workspace_bytes >= gemm_f16_workspace_bytes(w, m_rows))
+            workspace_bytes >= zq_matmul_workspace_bytes(w, m_rows, act_mode))
         {
             // ZQ_GEMM=mma selects the mma.sync version of the same product (for comparison)
             static const bool legacy = getenv("ZQ_GEMM") && getenv("ZQ_GEMM")[0] == 'm';

@@ -131,6 +131,7 @@ int launch_convert_rows_f16(const float* x, __half* x16, float* post, uint32_t m
 // The same product with tcgen05.mma and the accumulator in tensor memory (gemm_tc.cu); same workspace.
 int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
                    void* workspace, cudaStream_t st);
+size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows);
 
 // ---- fused decode-step launchers (ops.cu). `state` is device memory: state[0] = current token,
 // state[1] = its position. Kernels read the position there, so a captured launch sequence can be
