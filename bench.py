@@ -310,6 +310,25 @@ def run_case(args):
     import zignn_b200
     from zignn_b200 import api as zq
     from zignn_b200 import ggml
+    if args.case.startswith("decode:"):
+        # decode:<gpt2_small_q4_0|gemma3_1b_q8_0>,<prompt tokens>,<greedy steps>
+        import numpy as np
+        from zignn_b200 import hostmodel
+        name, n_prompt, n_steps = args.case[7:].split(",")
+        if name.startswith("gemma"):
+            host = hostmodel.Gemma3Host.synthetic(hostmodel.GEMMA3_1B, qtype=ggml.Q8_0, seed=42, device="cuda")
+            eng, vocab = zq.Gemma3(host), hostmodel.GEMMA3_1B["vocab"]
+        else:
+            host = hostmodel.Gpt2Host.synthetic(hostmodel.GPT2_SMALL, qtype=ggml.Q4_0, seed=42, device="cuda")
+            eng, vocab = zq.Gpt2(host), hostmodel.GPT2_SMALL["vocab"]
+        prompt = np.random.default_rng(44).integers(0, vocab, size=int(n_prompt))
+        first = int(eng.prefill(prompt).argmax().item())
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        toks = eng.decode_greedy(first, int(n_steps))
+        dt = time.perf_counter() - t0
+        print(json.dumps({"case": args.case, "tok_s": int(n_steps) / dt, "last_token": int(toks[-1])}), flush=True)
+        return
     parts = args.case.split(",")
     qname, k, n, m = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
     mode = zq.ACT_Q8 if len(parts) > 4 and parts[4] == "q8" else zq.ACT_F32
@@ -348,8 +367,9 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the sweep / cpu baseline side measurements")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
     ap.add_argument("--case", default=None, metavar="TYPE,K,N,M[,ACT]",
-                    help="time one quantised matmul (e.g. q4_0,4096,14336,512 or q8_0,1152,6912,1,q8) and exit; "
-                         "for profiling a kernel other than the headline one")
+                    help="time one quantised matmul (e.g. q4_0,4096,14336,512 or q8_0,1152,6912,1,q8), or one "
+                         "engine run (decode:gemma3_1b_q8_0,300,3 = prompt tokens, greedy steps), and exit; for "
+                         "profiling kernels other than the headline one")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
