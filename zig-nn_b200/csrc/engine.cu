@@ -157,23 +157,30 @@ struct zq_gpt2 {
     }
 };
 
-static int gpt2_linear(const Linear& L, const float* x, float* y, const float* bias, int gelu,
-                       const float* residual, cudaStream_t st) {
+// y = W . (ln ? LayerNorm(x) : x) + bias [gelu] [+ residual]. Quantised weights take the norm in the GEMV
+// prologue; f32 weights (the .f32 branch of linear_forward_q, gpt2.zig:652-671) use separate launches.
+static int gpt2_linear(zq_gpt2* m, const Linear& L, const float* x, float* y, const float* bias, int gelu,
+                       const float* residual, const float* ln_w, const float* ln_b, cudaStream_t st) {
     zq_epilogue ep{bias, gelu, nullptr, residual};
+    int rc;
     if (L.qw) {
-        int rc = launch_gemv_mma_f32(L.qw, x, y, 1, &ep, st);
-        if (rc == ZQ_ERR_LIMIT) rc = launch_gemv_f32(L.qw, x, y, 1, &ep, st);
-        return rc;
+        rc = launch_gemv_mma_ln_f32(L.qw, x, y, 1, &ep, ln_w, ln_b, 1e-5f, st);
+        if (rc != ZQ_ERR_LIMIT) return rc;
     }
-    // f32 weight: matvec, then the same epilogue as separate launches
-    int rc = zq_matvec_f32(L.f32w, x, y, L.out_dim, L.in_dim, st);
+    if (ln_w) {
+        if ((rc = zq_layer_norm(m->ln, x, ln_w, ln_b, 1, L.in_dim, 1e-5f, st))) return rc;
+        x = m->ln;
+    }
+    if (L.qw) return launch_gemv_f32(L.qw, x, y, 1, &ep, st);
+    rc = zq_matvec_f32(L.f32w, x, y, L.out_dim, L.in_dim, st);
     if (rc == ZQ_OK && bias) rc = zq_add_broadcast(y, y, bias, L.out_dim, L.out_dim, st);
     if (rc == ZQ_OK && gelu) rc = zq_gelu(y, y, L.out_dim, st);
     if (rc == ZQ_OK && residual) rc = zq_add_broadcast(y, y, residual, L.out_dim, L.out_dim, st);
     return rc;
 }
 
-// One decode step for the token and position held in m->d_state (gpt2.zig:423-509).
+// One decode step for the token and position held in m->d_state (gpt2.zig:423-509), six launches per
+// layer: [ln1 + qkv] | cache write + scores | softmax.V | proj + residual | [ln2 + fc + gelu] | mproj + residual.
 static int gpt2_step(zq_gpt2* m, int variant, cudaStream_t st) {
     const zq_gpt2_config& C = m->c;
     const uint32_t E = C.embed, hd = E / C.head;
@@ -181,20 +188,17 @@ static int gpt2_step(zq_gpt2* m, int variant, cudaStream_t st) {
     if ((rc = launch_gpt2_embed_step(m->x, m->wte, m->wpe, m->d_state, E, st))) return rc;
     for (uint32_t l = 0; l < C.layer; ++l) {
         const zq_gpt2::Block& b = m->blocks[l];
-        if ((rc = zq_layer_norm(m->ln, m->x, b.ln1_w, b.ln1_b, 1, E, 1e-5f, st))) return rc;
-        if ((rc = gpt2_linear(b.qkv, m->ln, m->qkv, b.qkv_b, 0, nullptr, st))) return rc;
-        if ((rc = launch_write_kv_step(m->qkv + E, m->qkv + 2 * E, m->k[l], m->v[l], m->d_state, E, st))) return rc;
-        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], m->att, nullptr, nullptr, nullptr, m->scores,
-                                        C.head, C.head, hd, m->d_state, 0, C.ctx, ZQ_ATTN_GPT2_SOFTMAX, st)))
+        if ((rc = gpt2_linear(m, b.qkv, m->x, m->qkv, b.qkv_b, 0, nullptr, b.ln1_w, b.ln1_b, st))) return rc;
+        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], m->qkv + E, m->qkv + 2 * E, m->att, nullptr, nullptr,
+                                        nullptr, m->scores, C.head, C.head, hd, m->d_state, 0, C.ctx,
+                                        ZQ_ATTN_GPT2_SOFTMAX, st)))
             return rc;
-        if ((rc = gpt2_linear(b.proj, m->att, m->x, b.proj_b, 0, m->x, st))) return rc;
-        if ((rc = zq_layer_norm(m->ln, m->x, b.ln2_w, b.ln2_b, 1, E, 1e-5f, st))) return rc;
-        if ((rc = gpt2_linear(b.fc, m->ln, m->hid, b.fc_b, 1, nullptr, st))) return rc;
-        if ((rc = gpt2_linear(b.mproj, m->hid, m->x, b.mproj_b, 0, m->x, st))) return rc;
+        if ((rc = gpt2_linear(m, b.proj, m->att, m->x, b.proj_b, 0, m->x, nullptr, nullptr, st))) return rc;
+        if ((rc = gpt2_linear(m, b.fc, m->x, m->hid, b.fc_b, 1, nullptr, b.ln2_w, b.ln2_b, st))) return rc;
+        if ((rc = gpt2_linear(m, b.mproj, m->hid, m->x, b.mproj_b, 0, m->x, nullptr, nullptr, st))) return rc;
     }
     if (variant != STEP_CACHE_ONLY) {
-        if ((rc = zq_layer_norm(m->ln, m->x, m->ln_f_w, m->ln_f_b, 1, E, 1e-5f, st))) return rc;
-        if ((rc = zq_matvec_f32(m->wte, m->ln, m->logits, C.vocab, E, st))) return rc;
+        if ((rc = launch_matvec_ln_f32(m->wte, m->x, m->logits, C.vocab, E, m->ln_f_w, m->ln_f_b, 1e-5f, st))) return rc;
     }
     if (variant == STEP_GREEDY) {
         if ((rc = zq_argmax(m->logits, C.vocab, m->d_arg, st))) return rc;
@@ -427,8 +431,8 @@ static int gemma3_step(zq_gemma3* m, int variant, cudaStream_t st) {
         const bool global = (l % C.global_every) == C.global_every - 1;
         const uint32_t window = global ? 0u : C.sliding_window;
         const uint32_t max_len = (window && window < C.ctx) ? window : C.ctx;
-        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], nullptr, m->xq, m->xscale, m->xsum, m->scores,
-                                        C.head, C.head_kv, D, m->d_state, window, max_len, 0, st)))
+        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], nullptr, nullptr, nullptr, m->xq, m->xscale, m->xsum,
+                                        m->scores, C.head, C.head_kv, D, m->d_state, window, max_len, 0, st)))
             return rc;
         if ((rc = gemma_gemv(m, b.o, m->proj, st))) return rc;
         if ((rc = launch_norm_quant(m->proj, b.post_attn_norm_w, m->x, b.ffn_norm_w, E, C.rms_eps, m->xq,

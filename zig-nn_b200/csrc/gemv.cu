@@ -256,21 +256,75 @@ __global__ void quantize_q8_kernel(const float* __restrict__ x, int8_t* __restri
 
 __global__ void __launch_bounds__(256)
 matvec_f32_kernel(const float* __restrict__ w, const float* __restrict__ x, float* __restrict__ y,
-                  uint32_t N, uint32_t K) {
+                  uint32_t N, uint32_t K, const float* __restrict__ ln_gamma, const float* __restrict__ ln_beta,
+                  float ln_eps) {
     extern __shared__ __align__(16) float xs[];
-    for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) xs[i] = x[i];
-    __syncthreads();
-    const int lane = threadIdx.x & 31;
+    __shared__ float red[10];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t warps = blockDim.x >> 5;
+    if (ln_gamma != nullptr) {
+        // LayerNorm of the row in the prologue (two-pass mean / variance, gpt2.zig:541-596)
+        float sum = 0.0f;
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) sum += x[i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+        if (lane == 0) red[warp] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+            for (uint32_t i = 0; i < warps; ++i) t += red[i];
+            red[8] = t / (float)K;
+        }
+        __syncthreads();
+        const float mean = red[8];
+        float var = 0.0f;
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
+            const float d = x[i] - mean;
+            var = fmaf(d, d, var);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) var += __shfl_xor_sync(0xFFFFFFFFu, var, off);
+        __syncthreads();
+        if (lane == 0) red[warp] = var;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+            for (uint32_t i = 0; i < warps; ++i) t += red[i];
+            red[9] = 1.0f / sqrtf(t / (float)K + ln_eps);
+        }
+        __syncthreads();
+        const float inv_std = red[9];
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x)
+            xs[i] = __fadd_rn(__fmul_rn(__fmul_rn(x[i] - mean, inv_std), ln_gamma[i]), ln_beta[i]);
+    } else {
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) xs[i] = x[i];
+    }
+    __syncthreads();
     const bool vec = (K % 4 == 0);
-    for (uint64_t row = (uint64_t)blockIdx.x * warps + (threadIdx.x >> 5); row < N;
-         row += (uint64_t)gridDim.x * warps) {
+    for (uint64_t row = (uint64_t)blockIdx.x * warps + warp; row < N; row += (uint64_t)gridDim.x * warps) {
         const float* wr = w + row * K;
         float acc = 0.0f;
         if (vec) {
             const float4* w4 = reinterpret_cast<const float4*>(wr);
             const float4* x4 = reinterpret_cast<const float4*>(xs);
-            for (uint32_t i = lane; i < K / 4; i += 32) {
+            const uint32_t n4 = K / 4;
+            uint32_t i = lane;
+            for (; i + 96 < n4; i += 128) {  // four independent 128-bit loads in flight per lane
+                float4 a[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) a[u] = __ldg(w4 + i + 32 * u);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float4 b = x4[i + 32 * u];
+                    acc = fmaf(a[u].x, b.x, acc);
+                    acc = fmaf(a[u].y, b.y, acc);
+                    acc = fmaf(a[u].z, b.z, acc);
+                    acc = fmaf(a[u].w, b.w, acc);
+                }
+            }
+            for (; i < n4; i += 32) {
                 const float4 a = __ldg(w4 + i), b = x4[i];
                 acc = fmaf(a.x, b.x, acc);
                 acc = fmaf(a.y, b.y, acc);
@@ -459,6 +513,18 @@ int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, in
     return ZQ_OK;
 }
 
+int launch_matvec_ln_f32(const float* w, const float* x, float* y, uint32_t out_dim, uint32_t in_dim,
+                         const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st) {
+    const size_t smem = (size_t)in_dim * sizeof(float);
+    int rc = set_smem(matvec_f32_kernel, smem);
+    if (rc != ZQ_OK) return rc;
+    const uint64_t tiles = ((uint64_t)out_dim + 7) / 8;
+    const uint64_t cap = (uint64_t)sm_count() * 8;
+    ZQ_CUDA(launch_pdl(matvec_f32_kernel, dim3((unsigned)(tiles < cap ? tiles : cap)), dim3(256), smem, st, w, x, y,
+                       out_dim, in_dim, ln_gamma, ln_beta, ln_eps));
+    return ZQ_OK;
+}
+
 }  // namespace zq
 
 using namespace zq;
@@ -549,15 +615,7 @@ int zq_matmul_gather(const zq_weight* w, const float* d_x, const zq_epilogue* ep
 int zq_matvec_f32(const float* d_w, const float* d_x, float* d_y, uint32_t out_dim, uint32_t in_dim,
                   zq_stream stream) {
     if (!d_w || !d_x || !d_y || out_dim == 0 || in_dim == 0) return ZQ_ERR_BAD_ARG;
-    const size_t smem = (size_t)in_dim * sizeof(float);
-    int rc = set_smem(matvec_f32_kernel, smem);
-    if (rc != ZQ_OK) return rc;
-    const uint64_t tiles = ((uint64_t)out_dim + 7) / 8;
-    const uint64_t cap = (uint64_t)sm_count() * 8;
-    matvec_f32_kernel<<<(unsigned)(tiles < cap ? tiles : cap), 256, smem, as_stream(stream)>>>(
-        d_w, d_x, d_y, out_dim, in_dim);
-    ZQ_LAUNCH_CHECK();
-    return ZQ_OK;
+    return launch_matvec_ln_f32(d_w, d_x, d_y, out_dim, in_dim, nullptr, nullptr, 0.0f, as_stream(stream));
 }
 
 int zq_argmax(const float* d_logits, uint32_t n, int32_t* d_index, zq_stream stream) {

@@ -25,11 +25,16 @@ namespace {
 
 constexpr int kMaxCols = 4;  // column sets of 8 MMA columns = 4 activation rows (hi, lo) each
 
+// Per-call options: the output epilogue and, for one activation row, an optional LayerNorm applied to
+// the row before the product (ln_gamma != nullptr; two-pass mean / variance as gpt2.zig:541-596).
 struct EpilogueArgs {
     const float* bias;
     const float* mul;
     const float* residual;
     int gelu;
+    const float* ln_gamma;
+    const float* ln_beta;
+    float ln_eps;
 };
 
 __device__ __forceinline__ float gelu_tanh(float v) {
@@ -376,6 +381,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     // per-warp cp.async ring, 128-byte aligned, behind everything else (offset passed by the host)
     unsigned char* ring = smem_raw + ring_off;
 
+    pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t wr = warp % WR, ks = warp / WR;
@@ -430,6 +436,50 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
 #pragma unroll 1
     for (int i = 0; i < (USE_RING ? D - 1 : 1); ++i) producer_step();
     uint32_t c_slot = 0;
+
+    // Everything above touched only the weights. The activations may come from the kernel before this one.
+    pdl_wait();
+
+    // ---- optional LayerNorm of the (single) activation row into shared memory ----
+    if (ep.ln_gamma != nullptr) {
+        __shared__ float lnred[34];
+        float* xln = reinterpret_cast<float*>(smem_raw + ring_off) - ((K + 31u) & ~31u);  // just below the ring
+        const int nw = blockDim.x >> 5;
+        float sum = 0.0f;
+        for (uint32_t i = tid; i < K; i += blockDim.x) sum += x[i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+        if (lane == 0) lnred[warp] = sum;
+        __syncthreads();
+        if (tid == 0) {
+            float t2 = 0.0f;
+            for (int w2 = 0; w2 < nw; ++w2) t2 += lnred[w2];
+            lnred[32] = t2 / (float)K;
+        }
+        __syncthreads();
+        const float mean = lnred[32];
+        float var = 0.0f;
+        for (uint32_t i = tid; i < K; i += blockDim.x) {
+            const float d = x[i] - mean;
+            var = fmaf(d, d, var);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) var += __shfl_xor_sync(0xFFFFFFFFu, var, off);
+        __syncthreads();
+        if (lane == 0) lnred[warp] = var;
+        __syncthreads();
+        if (tid == 0) {
+            float t2 = 0.0f;
+            for (int w2 = 0; w2 < nw; ++w2) t2 += lnred[w2];
+            lnred[33] = 1.0f / sqrtf(t2 / (float)K + ep.ln_eps);
+        }
+        __syncthreads();
+        const float inv_std = lnred[33];
+        for (uint32_t i = tid; i < K; i += blockDim.x)
+            xln[i] = __fadd_rn(__fmul_rn(__fmul_rn(x[i] - mean, inv_std), ep.ln_gamma[i]), ep.ln_beta[i]);
+        __syncthreads();
+        x = xln;
+    }
 
     // ---- activations: range prescale, then the fp16 hi/lo fragment image ----
     if (tid < 16) amax_bits[tid] = 0;
@@ -581,7 +631,6 @@ __device__ __forceinline__ void lds128_keep(uint4& v, uint32_t addr, uint32_t pr
         : "r"(addr), "r"(pred));
 }
 
-constexpr int kRowWarps = 8;  // warps per CTA, one 16-row tile each
 
 // Row-sharded use: besides its own result buffer the kernel stores every output row into the same
 // place of each peer's buffer (plain stores to peer-mapped memory over NVLink), so the all-gather of the
@@ -627,8 +676,8 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     return v;
 }
 
-template <int TYPE, int D, int CTAS>
-__global__ void __launch_bounds__(kRowWarps * 32, CTAS)
+template <int TYPE, int D, int CTAS, int W>
+__global__ void __launch_bounds__(W * 32, CTAS)
 gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const float* __restrict__ x,
                  float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t scp, uint32_t sc_off,
                  uint32_t ring_off, EpilogueArgs ep, PeerArgs pa) {
@@ -648,7 +697,7 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    constexpr uint32_t rows_per_cta = kRowWarps * 16;
+    constexpr uint32_t rows_per_cta = W * 16;
 
     // sharded: every CTA reads the round before any CTA can finish it (the counter moves only when all
     // CTAs have arrived at the end of the kernel)
@@ -890,7 +939,7 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     }
 }
 
-template <int TYPE, int D, int CTAS>
+template <int TYPE, int D, int CTAS, int W>
 int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
                      cudaStream_t st) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
@@ -901,27 +950,35 @@ int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs 
     if (!Q8) smem += (size_t)w->nbp * sizeof(float);
     smem = (smem + 127) & ~(size_t)127;
     const uint32_t sc_off = (uint32_t)smem;
-    smem += (size_t)kRowWarps * 2 * 16 * w->scp * (Q41 ? 4 : 2);
+    smem += (size_t)W * 2 * 16 * w->scp * (Q41 ? 4 : 2);
     smem = (smem + 127) & ~(size_t)127;
     const uint32_t ring_off = (uint32_t)smem;
-    smem += (size_t)kRowWarps * D * (Q8 ? 2048 : 1024);
+    smem += (size_t)W * D * (Q8 ? 2048 : 1024);
     if (smem > (size_t)(227 * 1024) / CTAS - 1024) return ZQ_ERR_LIMIT;  // CTAS CTAs per SM must fit
-    auto kern = gemv_mma1_kernel<TYPE, D, CTAS>;
+    auto kern = gemv_mma1_kernel<TYPE, D, CTAS, W>;
     if (smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const uint32_t cta_tiles = (w->out_dim + kRowWarps * 16 - 1) / (kRowWarps * 16);
+    const uint32_t cta_tiles = (w->out_dim + W * 16 - 1) / (W * 16);
     const uint32_t cap = sms * CTAS;
-    kern<<<cta_tiles < cap ? cta_tiles : cap, kRowWarps * 32, smem, st>>>(
+    kern<<<cta_tiles < cap ? cta_tiles : cap, W * 32, smem, st>>>(
         w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim, w->in_dim, w->nb, w->scp, sc_off, ring_off,
         ep, pa);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
 
+// Whole rows per warp need enough row tiles to occupy the GPU. With fewer tiles the CTAs get smaller (so
+// that every SM still has several) and the ring deeper (fewer warps must keep as many bytes in flight).
 template <int TYPE>
 int launch_rows1(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
                  cudaStream_t st) {
-    return launch_rows1_cfg<TYPE, kRows1Depth, kCtasPerSm>(w, x, y, ep, pa, st);
+    const uint32_t tiles = (w->out_dim + 15) / 16, sms = (uint32_t)sm_count();
+    constexpr int S = TYPE == ZQ_TYPE_Q8_0 ? 2 : 1;  // q8_0 stages are twice as large
+    int rc = ZQ_ERR_LIMIT;
+    if (tiles >= sms * 2 * 8) rc = launch_rows1_cfg<TYPE, kRows1Depth, kCtasPerSm, 8>(w, x, y, ep, pa, st);
+    if (rc == ZQ_ERR_LIMIT && tiles >= sms * 2 * 4) rc = launch_rows1_cfg<TYPE, 8 / S, 4, 4>(w, x, y, ep, pa, st);
+    if (rc == ZQ_ERR_LIMIT && tiles >= sms * 4) rc = launch_rows1_cfg<TYPE, 16 / S, 4, 2>(w, x, y, ep, pa, st);
+    return rc;
 }
 
 int launch_rows1_any(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
@@ -942,7 +999,7 @@ struct Plan {
 
 // CTA shape: enough warps in flight on every SM; K is split across warps only when there are too
 // few row tiles to do that with one warp per tile.
-Plan make_plan(const zq_weight* w, uint32_t M, int ns, bool use_ring) {
+Plan make_plan(const zq_weight* w, uint32_t M, int ns, bool use_ring, bool with_ln) {
     Plan p{};
     const bool q41 = w->type == ZQ_TYPE_Q4_1;
     const uint32_t tiles = (w->out_dim + 15) / 16;
@@ -958,6 +1015,7 @@ Plan make_plan(const zq_weight* w, uint32_t M, int ns, bool use_ring) {
     if (w->type != ZQ_TYPE_Q8_0) smem += (size_t)w->nbp * M * sizeof(float);
     if (ks > 1) smem += (size_t)p.WR * ks * ns * 2 * 32 * sizeof(float);
     smem = (smem + 127) & ~(size_t)127;
+    if (with_ln) smem += (size_t)((w->in_dim + 31u) & ~31u) * sizeof(float);  // the normalised row, just below the ring
     p.ring_off = (uint32_t)smem;
     const bool q8 = w->type == ZQ_TYPE_Q8_0;
     const size_t stage = q8 ? Ring<true, false>::kStage : q41 ? Ring<false, true>::kStage : Ring<false, false>::kStage;
@@ -976,14 +1034,14 @@ Plan make_plan(const zq_weight* w, uint32_t M, int ns, bool use_ring) {
 
 template <int TYPE, int NS, bool USE_RING>
 int launch_kernel(const zq_weight* w, const float* x, float* y, uint32_t M, EpilogueArgs ep, cudaStream_t st) {
-    const Plan p = make_plan(w, M, NS, USE_RING);
+    const Plan p = make_plan(w, M, NS, USE_RING, ep.ln_gamma != nullptr);
     if (!p.fits) return ZQ_ERR_LIMIT;
     auto kern = gemv_mma_kernel<TYPE, NS, USE_RING>;
     if (p.smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
-    kern<<<p.grid, p.WR * p.KS * 32, p.smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim,
-                                                    w->in_dim, w->nb, w->scp, M, p.WR, p.KS, p.ring_off, ep);
-    ZQ_LAUNCH_CHECK();
+    ZQ_CUDA(launch_pdl(kern, dim3(p.grid), dim3(p.WR * p.KS * 32), p.smem, st, w->qs,
+                       static_cast<const uint8_t*>(w->sc), x, y, w->out_dim, w->in_dim, w->nb, w->scp, M, p.WR, p.KS,
+                       p.ring_off, ep));
     return ZQ_OK;
 }
 
@@ -1014,10 +1072,17 @@ int launch_ns(const zq_weight* w, const float* x, float* y, uint32_t M, Epilogue
 // Returns ZQ_ERR_LIMIT when the activation image does not fit in shared memory.
 int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
                         const zq_epilogue* ep, cudaStream_t st) {
+    return launch_gemv_mma_ln_f32(w, x, y, m_rows, ep, nullptr, nullptr, 0.0f, st);
+}
+
+// ln_gamma != nullptr (one activation row only): y = W . LayerNorm(x), the norm computed in the prologue.
+int launch_gemv_mma_ln_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
+                           const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st) {
     if (m_rows == 0) return ZQ_OK;
     if (m_rows > 16) return ZQ_ERR_BAD_ARG;
+    if (ln_gamma && (m_rows != 1 || !ln_beta)) return ZQ_ERR_BAD_ARG;
     if (((uintptr_t)x & 15) != 0) return ZQ_ERR_BAD_ARG;  // activation rows are read as float4
-    EpilogueArgs a{nullptr, nullptr, nullptr, 0};
+    EpilogueArgs a{nullptr, nullptr, nullptr, 0, ln_gamma, ln_beta, ln_eps};
     if (ep) {
         a.bias = ep->d_bias;
         a.gelu = ep->gelu;
@@ -1026,7 +1091,7 @@ int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m
     }
     // One activation row and enough 16-row tiles to give every resident warp its own rows: the
     // block-per-column kernel. Otherwise the general kernel (activation rows in columns, K split).
-    if (m_rows == 1 && (w->out_dim + 15) / 16 >= (uint32_t)sm_count() * kCtasPerSm * kRowWarps) {
+    if (m_rows == 1 && !ln_gamma && (w->out_dim + 15) / 16 >= (uint32_t)sm_count() * 4) {
         PeerArgs none{};
         const int rc = launch_rows1_any(w, x, y, a, none, st);
         if (rc != ZQ_ERR_LIMIT) return rc;
@@ -1048,8 +1113,8 @@ int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue
                            uint32_t row_off, uint32_t* d_sync, cudaStream_t st) {
     if (world < 2 || world > (uint32_t)kPeerMax || rank >= world) return ZQ_ERR_BAD_ARG;
     if (((uintptr_t)x & 15) != 0) return ZQ_ERR_BAD_ARG;
-    if ((w->out_dim + 15) / 16 < (uint32_t)sm_count() * kRowWarps) return ZQ_ERR_UNSUPPORTED;
-    EpilogueArgs a{nullptr, nullptr, nullptr, 0};
+    if ((w->out_dim + 15) / 16 < (uint32_t)sm_count() * 4) return ZQ_ERR_UNSUPPORTED;
+    EpilogueArgs a{nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0.0f};
     if (ep) {
         a.bias = ep->d_bias;
         a.gelu = ep->gelu;

@@ -517,7 +517,8 @@ __device__ __forceinline__ void step_window(const uint32_t* state, uint32_t wind
 // attention_scores_kernel with the window taken from the device-side position. The grid covers the
 // largest possible window; CTAs past the current one leave at once.
 __global__ void __launch_bounds__(256)
-attention_scores_step_kernel(const float* __restrict__ q, const float* __restrict__ kc,
+attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc, float* __restrict__ vc,
+                             const float* __restrict__ k_new, const float* __restrict__ v_new,
                              float* __restrict__ scores, uint32_t n_head, uint32_t n_kv_head,
                              uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window) {
     __shared__ float part[16][17];
@@ -525,15 +526,27 @@ attention_scores_step_kernel(const float* __restrict__ q, const float* __restric
     pdl_wait();
     uint32_t kv_start, kv_len;
     step_window(state, window, &kv_start, &kv_len);
-    if (blockIdx.x * 16 >= kv_len) return;
     const uint32_t h = blockIdx.y;
     const uint32_t kvh = h / (n_head / n_kv_head);
     const uint32_t kv_dim = n_kv_head * head_dim;
+    // k_new / v_new: this step's key and value rows are not in the caches yet. The first CTA of each kv
+    // head stores them (gpt2.zig:812-816); the score of the current position reads k_new directly.
+    const uint32_t pos = kv_start + kv_len - 1;
+    if (k_new != nullptr && blockIdx.x == 0 && h % (n_head / n_kv_head) == 0) {
+        for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) {
+            kc[(size_t)pos * kv_dim + (size_t)kvh * head_dim + i] = k_new[(size_t)kvh * head_dim + i];
+            vc[(size_t)pos * kv_dim + (size_t)kvh * head_dim + i] = v_new[(size_t)kvh * head_dim + i];
+        }
+    }
+    if (blockIdx.x * 16 >= kv_len) return;
     const uint32_t pp = threadIdx.x >> 4, l = threadIdx.x & 15;
     const uint32_t p = blockIdx.x * 16 + pp;
     const uint32_t dim16 = head_dim & ~15u;
     const float* qh = q + (size_t)h * head_dim;
-    const float* kr = kc + (size_t)(kv_start + min(p, kv_len - 1)) * kv_dim + (size_t)kvh * head_dim;
+    const uint32_t pc = min(p, kv_len - 1);
+    const float* kr = (k_new != nullptr && pc == kv_len - 1)
+                          ? k_new + (size_t)kvh * head_dim
+                          : kc + (size_t)(kv_start + pc) * kv_dim + (size_t)kvh * head_dim;
     float acc = 0.0f;
     for (uint32_t d = l; d < dim16; d += 16) acc = __fadd_rn(acc, __fmul_rn(qh[d], kr[d]));
     part[pp][l] = acc;
@@ -712,28 +725,30 @@ int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t
     return ZQ_OK;
 }
 
-int launch_attention_step(const float* q, const float* kc, const float* vc, float* out, int8_t* oq,
-                          float* oscale, int32_t* osum, float* scores, uint32_t n_head, uint32_t n_kv_head,
-                          uint32_t head_dim, const uint32_t* state, uint32_t window, uint32_t max_len,
-                          int flags, cudaStream_t st) {
+int launch_attention_step(const float* q, float* kc, float* vc, const float* k_new, const float* v_new,
+                          float* out, int8_t* oq, float* oscale, int32_t* osum, float* scores, uint32_t n_head,
+                          uint32_t n_kv_head, uint32_t head_dim, const uint32_t* state, uint32_t window,
+                          uint32_t max_len, int flags, cudaStream_t st) {
     if (max_len == 0 || max_len > 180 * 1024 / 4) return ZQ_ERR_LIMIT;
     if (oq && head_dim % 32) return ZQ_ERR_BAD_ARG;
     const size_t smem = (size_t)max_len * sizeof(float);
     const int tail = (flags & ZQ_ATTN_GPT2_SOFTMAX) ? 1 : 0;
-    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head), dim3(256), 0, st, q, kc,
-                       scores, n_head, n_kv_head, head_dim, state, window));
+    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head), dim3(256), 0, st, q, kc, vc,
+                       k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window));
     if (oq) {
         auto kern = attention_softmax_v_step_kernel<true>;
         if (smem > 24 * 1024)  // the kernel also holds a 16 KB static tile
             ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         ZQ_CUDA(launch_pdl(kern, dim3(n_head, (head_dim + kAttnDims - 1) / kAttnDims), dim3(256), smem, st, scores,
-                           vc, out, oq, oscale, osum, n_head, n_kv_head, head_dim, state, window, tail));
+                           static_cast<const float*>(vc), out, oq, oscale, osum, n_head, n_kv_head, head_dim, state,
+                           window, tail));
     } else {
         auto kern = attention_softmax_v_step_kernel<false>;
         if (smem > 24 * 1024)  // the kernel also holds a 16 KB static tile
             ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         ZQ_CUDA(launch_pdl(kern, dim3(n_head, (head_dim + kAttnDims - 1) / kAttnDims), dim3(256), smem, st, scores,
-                           vc, out, nullptr, nullptr, nullptr, n_head, n_kv_head, head_dim, state, window, tail));
+                           static_cast<const float*>(vc), out, nullptr, nullptr, nullptr, n_head, n_kv_head, head_dim,
+                           state, window, tail));
     }
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;

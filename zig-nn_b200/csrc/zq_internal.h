@@ -111,6 +111,9 @@ int launch_gemv_f32(const zq_weight* w, const float* x, float* y, uint32_t m_row
 // Tensor-core f32-activation GEMV for m_rows <= 16 (gemv_mma.cu); x must be 16-byte aligned.
 int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
                         const zq_epilogue* ep, cudaStream_t st);
+// The same with LayerNorm(x) computed in the kernel's prologue (one activation row; gpt2.zig:541-596).
+int launch_gemv_mma_ln_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
+                           const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st);
 // f32-activation GEMV for one row with the all-gather of row-sharded outputs fused in (gemv_mma.cu).
 int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue* ep, float* const* y_odd,
                            float* const* y_even, uint32_t* const* flags, uint32_t world, uint32_t rank,
@@ -148,11 +151,15 @@ int launch_qk_norm_rope_kv(float* qkv, const float* q_norm_w, const float* k_nor
 int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t* q, float* scale,
                           int32_t* sum, cudaStream_t st);
 // Single-query attention over positions [max(0, pos + 1 - window), pos] (window 0 = all); max_len is the
-// largest window any step can have. `out` (f32) and `oq/oscale/osum` (quantised) are each optional.
-int launch_attention_step(const float* q, const float* kc, const float* vc, float* out, int8_t* oq,
-                          float* oscale, int32_t* osum, float* scores, uint32_t n_head, uint32_t n_kv_head,
-                          uint32_t head_dim, const uint32_t* state, uint32_t window, uint32_t max_len,
-                          int flags, cudaStream_t st);
+// largest window any step can have. k_new / v_new (optional): this step's key / value rows, stored into
+// row `pos` of the caches by the same launch. `out` (f32) and `oq/oscale/osum` (quantised) are each optional.
+int launch_attention_step(const float* q, float* kc, float* vc, const float* k_new, const float* v_new,
+                          float* out, int8_t* oq, float* oscale, int32_t* osum, float* scores, uint32_t n_head,
+                          uint32_t n_kv_head, uint32_t head_dim, const uint32_t* state, uint32_t window,
+                          uint32_t max_len, int flags, cudaStream_t st);
+// f32 matvec (GPT-2 vocabulary head) with an optional LayerNorm of x in the prologue (gemv.cu).
+int launch_matvec_ln_f32(const float* w, const float* x, float* y, uint32_t out_dim, uint32_t in_dim,
+                         const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st);
 int launch_gpt2_embed_step(float* x, const float* wte, const float* wpe, const uint32_t* state, uint32_t embed,
                            cudaStream_t st);
 int launch_write_kv_step(const float* k, const float* v, float* kc, float* vc, const uint32_t* state,
