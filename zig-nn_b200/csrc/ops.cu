@@ -226,6 +226,8 @@ __global__ void __launch_bounds__(256)
 layer_norm_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ gamma,
                   const float* __restrict__ beta, uint32_t cols, float eps) {
     __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = x + (size_t)blockIdx.x * cols;
     float* o = out + (size_t)blockIdx.x * cols;
     float s = 0.0f;
@@ -876,8 +878,8 @@ int zq_layer_norm(float* d_out, const float* d_x, const float* d_gamma, const fl
                   uint32_t rows, uint32_t cols, float eps, zq_stream stream) {
     if (!d_out || !d_x || !d_gamma || !d_beta || cols == 0) return ZQ_ERR_BAD_ARG;
     if (rows == 0) return ZQ_OK;
-    layer_norm_kernel<<<rows, 256, 0, as_stream(stream)>>>(d_out, d_x, d_gamma, d_beta, cols, eps);
-    ZQ_LAUNCH_CHECK();
+    ZQ_CUDA(launch_pdl(layer_norm_kernel, dim3(rows), dim3(256), 0, as_stream(stream), d_out, d_x, d_gamma, d_beta, cols,
+                       eps));
     return ZQ_OK;
 }
 
