@@ -13,8 +13,8 @@
 //                single bulk copy (cp.async.bulk, completion counted on the stage's mbarrier) brings in;
 //   D          = 128 lanes x N columns of f32 in tensor memory (one lane per weight row).
 //
-// Roles: warps 0-7 produce stages (dequantise + copy) and later drain the accumulator; one thread of
-// warp 8 issues the MMAs. Stages are handed over through mbarriers: full[s] (256 producer arrivals),
+// Roles: warps 0-15 produce stages (dequantise) and later drain the accumulator; one thread of
+// warp 16 issues the MMAs. Stages are handed over through mbarriers: full[s] (256 producer arrivals),
 // empty[s] (tcgen05.commit when the MMAs that read the stage are done), acc (last commit). Every wait
 // is bounded; on a timeout the kernel records it in the library's device-error word, stops using
 // the pipeline, still releases tensor memory and returns (outputs are then undefined; zq_device_error
@@ -28,7 +28,7 @@ constexpr int TC_BN = 128;          // weight rows per CTA  (UMMA M)
 constexpr int TC_BM = 256;          // activation rows per CTA, at most (UMMA N)
 constexpr int TC_BK = 64;           // K per stage: one 128-byte swizzle atom of fp16
 constexpr int TC_STAGES = 4;
-constexpr int TC_PRODUCERS = 256;   // threads of warps 0-7
+constexpr int TC_PRODUCERS = 512;   // threads of warps 0-15
 constexpr int TC_THREADS = TC_PRODUCERS + 32;
 constexpr uint32_t TC_A_BYTES = TC_BN * 128;   // 16 KB
 constexpr uint32_t TC_B_BYTES = TC_BM * 128;   // 32 KB
@@ -242,40 +242,42 @@ __device__ __forceinline__ void bytes_to_half(uint32_t q, uint32_t d2, uint32_t&
     h23 = hmul2_u(hsub2_u(__byte_perm(u, 0x64646464u, 0x5342), k1152), d2);
 }
 
-// Blocks JBASE and JBASE + 1 of the quad -> the 64-K A tile of one stage.
+// Block j of the quad (j = JBASE + jj: the stage holds blocks JBASE and JBASE + 1) -> its 32 K-columns of the
+// 64-K A tile. A thread owns (row, half, jj).
 template <int TYPE, int JBASE>
-__device__ __forceinline__ void store_dequant(const PackedQuad<TYPE>& p, uint32_t tile, uint32_t row, uint32_t half) {
-#pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
-        const int j = JBASE + jj;
-        uint32_t d2, m2 = 0;
-        if (TYPE == ZQ_TYPE_Q4_1) {
-            const uint32_t dm = pick4(p.s, j);
-            d2 = __byte_perm(dm, dm, 0x1010);
-            m2 = __byte_perm(dm, dm, 0x3232);
-        } else {
-            const uint32_t pair = j < 2 ? p.s.x : p.s.y;
-            d2 = (j & 1) ? __byte_perm(pair, pair, 0x3232) : __byte_perm(pair, pair, 0x1010);
-        }
-        const uint32_t cbase = jj * 4;
-        if (TYPE == ZQ_TYPE_Q8_0) {
-            uint32_t h[8];
-            bytes_to_half(pick4(p.w0, j), d2, h[0], h[1]);
-            bytes_to_half(pick4(p.w1, j), d2, h[2], h[3]);
-            bytes_to_half(pick4(p.w2, j), d2, h[4], h[5]);
-            bytes_to_half(pick4(p.w3, j), d2, h[6], h[7]);
-            sts128(tile + swz(row, cbase + half * 2), h[0], h[1], h[2], h[3]);
-            sts128(tile + swz(row, cbase + half * 2 + 1), h[4], h[5], h[6], h[7]);
-        } else {
-            const uint32_t q0 = pick4(p.w0, j), q1 = pick4(p.w1, j);
-            uint32_t lo[4], hi[4];
-            nibbles_to_half<TYPE>(q0 & 0x0F0F0F0Fu, d2, m2, lo[0], lo[1]);
-            nibbles_to_half<TYPE>(q1 & 0x0F0F0F0Fu, d2, m2, lo[2], lo[3]);
-            nibbles_to_half<TYPE>((q0 >> 4) & 0x0F0F0F0Fu, d2, m2, hi[0], hi[1]);
-            nibbles_to_half<TYPE>((q1 >> 4) & 0x0F0F0F0Fu, d2, m2, hi[2], hi[3]);
-            sts128(tile + swz(row, cbase + half), lo[0], lo[1], lo[2], lo[3]);
-            sts128(tile + swz(row, cbase + 2 + half), hi[0], hi[1], hi[2], hi[3]);
-        }
+__device__ __forceinline__ void store_dequant(const PackedQuad<TYPE>& p, uint32_t tile, uint32_t row, uint32_t half,
+                                              uint32_t jj) {
+    // select block j's words and scale without dynamic register indexing
+    const uint32_t q0 = jj ? pick4(p.w0, JBASE + 1) : pick4(p.w0, JBASE);
+    const uint32_t q1 = jj ? pick4(p.w1, JBASE + 1) : pick4(p.w1, JBASE);
+    uint32_t d2, m2 = 0;
+    if (TYPE == ZQ_TYPE_Q4_1) {
+        const uint32_t dm = jj ? pick4(p.s, JBASE + 1) : pick4(p.s, JBASE);
+        d2 = __byte_perm(dm, dm, 0x1010);
+        m2 = __byte_perm(dm, dm, 0x3232);
+    } else {
+        const uint32_t pair = JBASE < 2 ? p.s.x : p.s.y;  // blocks (0, 1) or (2, 3)
+        d2 = jj ? __byte_perm(pair, pair, 0x3232) : __byte_perm(pair, pair, 0x1010);
+    }
+    const uint32_t cbase = jj * 4;
+    if (TYPE == ZQ_TYPE_Q8_0) {
+        const uint32_t q2 = jj ? pick4(p.w2, JBASE + 1) : pick4(p.w2, JBASE);
+        const uint32_t q3 = jj ? pick4(p.w3, JBASE + 1) : pick4(p.w3, JBASE);
+        uint32_t h[8];
+        bytes_to_half(q0, d2, h[0], h[1]);
+        bytes_to_half(q1, d2, h[2], h[3]);
+        bytes_to_half(q2, d2, h[4], h[5]);
+        bytes_to_half(q3, d2, h[6], h[7]);
+        sts128(tile + swz(row, cbase + half * 2), h[0], h[1], h[2], h[3]);
+        sts128(tile + swz(row, cbase + half * 2 + 1), h[4], h[5], h[6], h[7]);
+    } else {
+        uint32_t lo[4], hi[4];
+        nibbles_to_half<TYPE>(q0 & 0x0F0F0F0Fu, d2, m2, lo[0], lo[1]);
+        nibbles_to_half<TYPE>(q1 & 0x0F0F0F0Fu, d2, m2, lo[2], lo[3]);
+        nibbles_to_half<TYPE>((q0 >> 4) & 0x0F0F0F0Fu, d2, m2, hi[0], hi[1]);
+        nibbles_to_half<TYPE>((q1 >> 4) & 0x0F0F0F0Fu, d2, m2, hi[2], hi[3]);
+        sts128(tile + swz(row, cbase + half), lo[0], lo[1], lo[2], lo[3]);
+        sts128(tile + swz(row, cbase + 2 + half), hi[0], hi[1], hi[2], hi[3]);
     }
 }
 
@@ -314,7 +316,7 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {  // the MMA warp owns the tensor-memory allocation
+    if (warp == TC_PRODUCERS / 32) {  // the MMA warp owns the tensor-memory allocation
         const uint32_t slot = (uint32_t)__cvta_generic_to_shared(&tmem_base_slot);
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(tmem_cols)
                      : "memory");
@@ -326,9 +328,9 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_p = &abort_flag;
 
-    if (warp < 8) {
+    if (warp < TC_PRODUCERS / 32) {
         // ================= producers =================
-        const uint32_t prow = tid >> 1, phalf = tid & 1;
+        const uint32_t prow = tid >> 2, phalf = (tid >> 1) & 1, pjj = tid & 1;
         const uint32_t wrow = min(n0 + prow, N - 1);
         const uint8_t* qrow = qs + (size_t)wrow * nbp * QB;
         const uint8_t* srow = sc + (size_t)wrow * scp * SB;
@@ -350,9 +352,9 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
                 bulk_copy_g2s(b_tile, xt + ((size_t)s * m_pad + m0) * 64, bytes, full_bar(slot));
             }
             if ((s & 1u) == 0) {
-                store_dequant<TYPE, 0>(pk, a_tile, prow, phalf);
+                store_dequant<TYPE, 0>(pk, a_tile, prow, phalf, pjj);
             } else {
-                store_dequant<TYPE, 2>(pk, a_tile, prow, phalf);
+                store_dequant<TYPE, 2>(pk, a_tile, prow, phalf, pjj);
                 pk = pk_next;
                 const uint32_t q_ahead = ((s + 1) >> 1) + 1;
                 if (q_ahead < n_quads) load_packed<TYPE>(pk_next, qrow, srow, q_ahead, phalf);
@@ -365,18 +367,16 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
         if (alive) alive = mbar_wait(acc_bar, 0, abort_p, err_word);
         tc_fence_after();
         if (alive) {
-            // warp w reads lanes 32 * (w % 4) ..; warps 0-3 take the low half of the columns, 4-7 the high half
+            // warp w reads lanes 32 * (w % 4) ..; the column chunks of 32 go round the four warp groups
             const uint32_t lane_base = (warp & 3) * 32;
             const uint32_t n = n0 + lane_base + lane;
-            const uint32_t col_half = n_mma / 2;  // n_mma is a multiple of 64
-            const uint32_t col0 = (warp >> 2) * col_half;
-            for (uint32_t c = 0; c < col_half; c += 32) {
+            for (uint32_t c = (warp >> 2) * 32; c < n_mma; c += (TC_PRODUCERS / 128) * 32) {
                 uint32_t r[32];
-                tc_ld32(tmem_base + (lane_base << 16) + col0 + c, r);
+                tc_ld32(tmem_base + (lane_base << 16) + c, r);
                 tc_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const uint32_t m = m0 + col0 + c + i;
+                    const uint32_t m = m0 + c + i;
                     if (n < N && m < M) {
                         const size_t o = (size_t)m * N + n;
                         float v = __uint_as_float(r[i]) * post[m];
@@ -416,7 +416,7 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     }
 
     __syncthreads();
-    if (warp == 8) {
+    if (warp == TC_PRODUCERS / 32) {
         // If the pipeline was abandoned, MMAs may still be in flight: give the last commit a bounded chance.
         if (abort_flag && lane == 0) {
             tc_commit(acc_bar);
