@@ -138,6 +138,20 @@ def test_matmul_many_rows_tensor_core_gemm(zq, oracle, qtype, m, n, k):
 
 
 @pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("m", [1, 5, 33])
+def test_f16_activation_mode_any_row_count(zq, oracle, qtype, m):
+    """ZQ_ACT_F16 sends any number of rows through the tensor-core GEMM (fp16 operands)."""
+    n, k = 300, 1152
+    raw = make_weight(oracle, qtype, n, k)
+    qw = zq.QuantWeight(raw, qtype, n, k)
+    x = make_x(m, k)
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_F16).cpu().numpy()
+    want = oracle.linear(qtype, raw, x, n, k, act_mode=0, n_threads=4)
+    assert got.shape == (m, n)
+    assert rel_l2(got, want) <= REL_L2_GEMM_GUARD
+
+
+@pytest.mark.parametrize("qtype", TYPES)
 @pytest.mark.parametrize("n,k", SHAPES)
 def test_gemv_q8_activations_bit_exact(zq, oracle, qtype, n, k):
     raw = make_weight(oracle, qtype, n, k)
@@ -157,6 +171,28 @@ def test_matmul_small_batches_q8_bit_exact(zq, oracle, m):
     got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_Q8).cpu().numpy()
     want = oracle.linear(ggml.Q4_1, raw, x, n, k, act_mode=1, n_threads=4)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("m,n,k", [(17, 300, 1152), (64, 520, 768), (100, 129, 96), (200, 1000, 6912)])
+def test_matmul_many_rows_q8_bit_exact(zq, oracle, qtype, m, n, k):
+    """More than 16 Q8-quantised activation rows take the exact int8 tensor-core GEMM; every output must
+    equal the CPU path bit for bit (ragged M / N tiles, K not a multiple of 128, full epilogue)."""
+    raw = make_weight(oracle, qtype, n, k)
+    qw = zq.QuantWeight(raw, qtype, n, k)
+    x = make_x(m, k)
+    x[1] *= 100.0
+    x[2, :64] = 0.0
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_Q8).cpu().numpy()
+    want = oracle.linear(qtype, raw, x, n, k, act_mode=1, n_threads=8)
+    assert got.shape == (m, n)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), rel_l2(got, want)
+    rng = np.random.default_rng(3)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    got2 = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_Q8, bias=torch.from_numpy(bias).cuda(),
+                                   residual=torch.from_numpy(res).cuda()).cpu().numpy()
+    assert np.array_equal(got2, res + (want + bias))
 
 
 def test_quantize_rows_q8_bit_exact(zq, oracle):

@@ -1,0 +1,264 @@
+// Exact integer GEMM for Q8-quantised activations and many activation rows (batched decode, prefill).
+//
+// Same arithmetic as the decode kernel in gemv_q8.cu and as zig-nn's CPU path
+// (ThreadPool.matmul, src/gguf/thread_pool.zig:96-181 -> src/gguf/simd_dot.zig:71-152): per 32-block an
+// exact int8 x int8 -> int32 dot, turned into the f32 term (d * s) * float(idot) [+ (m * s) * float(qsum)],
+// and the terms of a row added in block order. Here the block dots of 16 weight rows x 8 activation rows
+// come from one mma.sync.m16n8k32 (s8 x s8 -> s32, exact), the weights are read once per 64 activation
+// rows instead of once per row, and each (weight row, activation row) pair keeps its running f32 sum in
+// a register, so the result is bit-identical to running the decode kernel row by row.
+//
+// Tile: 128 weight rows (8 warps x 16) x 64 activation rows per CTA; K advances by one quad of blocks
+// (128 values). The quantised activations of a quad (64 rows x 128 bytes, their scales and sums) are
+// staged in shared memory with cp.async, double-buffered; 16-byte halves of a (row, block) entry are
+// swapped for rows with bit 2 set so that the fragment loads are free of bank conflicts.
+#include "zq_internal.h"
+
+namespace zq {
+namespace {
+
+// CTA shape: W warps x 16 weight rows, NT x 8 activation rows. The large shape (8 warps, 64 rows) reads
+// the weights once per 64 activation rows; matrices with few rows take smaller CTAs so that the grid
+// still covers the GPU.
+
+struct QgEpilogue {
+    const float* bias;
+    const float* mul;
+    const float* residual;
+    int gelu;
+};
+
+__device__ __forceinline__ float gelu_tanh(float v) {
+    const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
+    const float inner = __fmul_rn(0.7978845608f, __fadd_rn(v, cube));
+    return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, (float)tanh((double)inner)));
+}
+
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%10,%10,%10,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ uint32_t pick4(const uint4& v, int j) {
+    return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
+}
+
+template <int TYPE, int W, int NT>
+__global__ void __launch_bounds__(W * 32)
+gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const int8_t* __restrict__ xq,
+               const float* __restrict__ xscale, const int32_t* __restrict__ xqsum, float* __restrict__ y,
+               uint32_t N, uint32_t K, uint32_t M, uint32_t nb, uint32_t scp, QgEpilogue ep) {
+    constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
+    constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
+    constexpr uint32_t QB = Q8 ? 32 : 16;
+    constexpr uint32_t QUAD = 4 * QB;
+    constexpr int QG_BN = W * 16, QG_BM = NT * 8, QG_NT = NT;
+    constexpr uint32_t QG_XQ_BYTES = 4 * QG_BM * 32;  // 4 blocks x BM rows x 32 int8
+    constexpr uint32_t QG_SC_BYTES = 4 * QG_BM * 4;   // 4 blocks x BM rows x f32 (and the same for the sums)
+    constexpr uint32_t QG_STAGE = QG_XQ_BYTES + 2 * QG_SC_BYTES;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t smem32 = (uint32_t)__cvta_generic_to_shared(smem);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t nbp = (nb + 3u) & ~3u, nq = nbp / 4;
+    const uint32_t n0 = blockIdx.x * QG_BN + warp * 16, m0 = blockIdx.y * QG_BM;
+
+    // activations of quad q -> stage: xq entries [blk][row][32 bytes] (16-byte halves swapped when row & 4),
+    // scales [blk][row], sums [blk][row]. Rows >= M and blocks >= nb are zero-filled (never used for output).
+    auto issue = [&](uint32_t stage, uint32_t q) {
+        const uint32_t base = smem32 + stage * QG_STAGE;
+        for (uint32_t idx = tid; idx < 8u * QG_BM; idx += W * 32) {  // (blk, row, half)
+            const uint32_t b = idx / (2u * QG_BM), r = (idx >> 1) % QG_BM, h = idx & 1u;
+            const uint32_t blk = q * 4 + b, m = m0 + r;
+            const bool ok = m < M && blk < nb;
+            const int8_t* src = xq + (size_t)(ok ? m : 0) * K + (size_t)(ok ? blk : 0) * 32 + h * 16;
+            cp_async16_zfill(base + ((b * QG_BM + r) * 2 + (h ^ ((r >> 2) & 1u))) * 16, src, ok ? 16u : 0u);
+        }
+        for (uint32_t idx = tid; idx < 4u * QG_BM; idx += W * 32) {  // (blk, row)
+            const uint32_t b = idx / QG_BM, r = idx % QG_BM;
+            const uint32_t blk = q * 4 + b, m = m0 + r;
+            const bool ok = m < M && blk < nb;
+            const size_t o = (size_t)(ok ? m : 0) * nb + (ok ? blk : 0);
+            cp_async4_zfill(base + QG_XQ_BYTES + (b * QG_BM + r) * 4, xscale + o, ok ? 4u : 0u);
+            cp_async4_zfill(base + QG_XQ_BYTES + QG_SC_BYTES + (b * QG_BM + r) * 4, xqsum + o, ok ? 4u : 0u);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    const uint32_t row_a = min(n0 + g, N - 1), row_b = min(n0 + g + 8, N - 1);
+    const uint8_t* pa = qs + (size_t)row_a * nbp * QB + 16 * t;
+    const uint8_t* pb = qs + (size_t)row_b * nbp * QB + 16 * t;
+    const uint8_t* sa = sc + (size_t)row_a * scp * (Q41 ? 4 : 2);
+    const uint8_t* sb = sc + (size_t)row_b * scp * (Q41 ? 4 : 2);
+
+    float run[QG_NT][4];
+#pragma unroll
+    for (int j = 0; j < QG_NT; ++j) run[j][0] = run[j][1] = run[j][2] = run[j][3] = 0.0f;
+
+    // fragment addressing inside a stage: entry (blk, row = 8j + g), word t (and 4 + t), halves swapped by row bit 2
+    const uint32_t swap = ((uint32_t)g >> 2) & 1u;
+    const uint32_t frag_lo = ((uint32_t)g * 2 + (0u ^ swap)) * 16 + t * 4;   // word t
+    const uint32_t frag_hi = ((uint32_t)g * 2 + (1u ^ swap)) * 16 + t * 4;   // word 4 + t
+
+    issue(0, 0);
+    for (uint32_t q = 0; q < nq; ++q) {
+        const uint32_t stage = q & 1u;
+        if (q + 1 < nq) issue(stage ^ 1u, q + 1);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        // this quad's weights
+        const uint4 wa = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD));
+        const uint4 wb = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD));
+        uint4 wa2 = wa, wb2 = wb;
+        if (Q8) {
+            wa2 = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD + 64));
+            wb2 = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD + 64));
+        }
+        float da[4], db[4], ma[4], mb[4];
+        if (Q41) {
+            const uint4 va = __ldg(reinterpret_cast<const uint4*>(sa) + q);
+            const uint4 vb = __ldg(reinterpret_cast<const uint4*>(sb) + q);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&reinterpret_cast<const uint32_t*>(&va)[b]));
+                const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&reinterpret_cast<const uint32_t*>(&vb)[b]));
+                da[b] = fa.x; ma[b] = fa.y;
+                db[b] = fb.x; mb[b] = fb.y;
+            }
+        } else {
+            const uint2 va = __ldg(reinterpret_cast<const uint2*>(sa) + q);
+            const uint2 vb = __ldg(reinterpret_cast<const uint2*>(sb) + q);
+            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&va.x));
+            const float2 a23 = __half22float2(*reinterpret_cast<const __half2*>(&va.y));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&vb.x));
+            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&vb.y));
+            da[0] = a01.x; da[1] = a01.y; da[2] = a23.x; da[3] = a23.y;
+            db[0] = b01.x; db[1] = b01.y; db[2] = b23.x; db[3] = b23.y;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) ma[b] = mb[b] = 0.0f;
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // stage q has landed (q + 1 may still be in flight)
+        __syncthreads();
+
+        const uint32_t base = smem32 + stage * QG_STAGE;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            if (q * 4 + b >= nb) break;  // row padding: no term is added for blocks that do not exist
+            uint32_t a0, a1, a2, a3;
+            if (Q8) {
+                a0 = pick4(wa, b); a1 = pick4(wb, b); a2 = pick4(wa2, b); a3 = pick4(wb2, b);
+            } else {
+                const uint32_t ua = pick4(wa, b), ub = pick4(wb, b);
+                a0 = ua & 0x0F0F0F0Fu; a1 = ub & 0x0F0F0F0Fu;
+                a2 = (ua >> 4) & 0x0F0F0F0Fu; a3 = (ub >> 4) & 0x0F0F0F0Fu;
+            }
+            const uint32_t xb = base + b * (QG_BM * 32), sbase = base + QG_XQ_BYTES + b * (QG_BM * 4);
+#pragma unroll
+            for (int j = 0; j < QG_NT; ++j) {
+                const uint32_t b0 = lds32(xb + j * 256 + frag_lo), b1 = lds32(xb + j * 256 + frag_hi);
+                int d[4];
+                mma_s8(d, a0, a1, a2, a3, b0, b1);
+                // columns of this lane: activation rows 8j + 2t and 8j + 2t + 1
+                const uint32_t so = sbase + (j * 8 + 2 * t) * 4;
+                float s0, s1;
+                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(s0), "=f"(s1) : "r"(so));
+                int qs0 = 0, qs1 = 0;
+                if (!Q8) asm volatile("ld.shared.v2.s32 {%0,%1}, [%2];" : "=r"(qs0), "=r"(qs1) : "r"(so + QG_SC_BYTES));
+                if (TYPE == ZQ_TYPE_Q4_0) {  // sum((n - 8) * q) = sum(n * q) - 8 * sum(q), exact
+                    d[0] -= 8 * qs0; d[1] -= 8 * qs1; d[2] -= 8 * qs0; d[3] -= 8 * qs1;
+                }
+                float t0 = __fmul_rn(__fmul_rn(da[b], s0), (float)d[0]);
+                float t1 = __fmul_rn(__fmul_rn(da[b], s1), (float)d[1]);
+                float t2 = __fmul_rn(__fmul_rn(db[b], s0), (float)d[2]);
+                float t3 = __fmul_rn(__fmul_rn(db[b], s1), (float)d[3]);
+                if (Q41) {
+                    t0 = __fadd_rn(t0, __fmul_rn(__fmul_rn(ma[b], s0), (float)qs0));
+                    t1 = __fadd_rn(t1, __fmul_rn(__fmul_rn(ma[b], s1), (float)qs1));
+                    t2 = __fadd_rn(t2, __fmul_rn(__fmul_rn(mb[b], s0), (float)qs0));
+                    t3 = __fadd_rn(t3, __fmul_rn(__fmul_rn(mb[b], s1), (float)qs1));
+                }
+                run[j][0] = __fadd_rn(run[j][0], t0);
+                run[j][1] = __fadd_rn(run[j][1], t1);
+                run[j][2] = __fadd_rn(run[j][2], t2);
+                run[j][3] = __fadd_rn(run[j][3], t3);
+            }
+        }
+        __syncthreads();  // the stage is overwritten by the copies issued in the next iteration
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+
+#pragma unroll
+    for (int j = 0; j < QG_NT; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t n = n0 + g + (e >> 1) * 8;
+            const uint32_t m = m0 + j * 8 + 2 * t + (e & 1);
+            if (n < N && m < M) {
+                const size_t o = (size_t)m * N + n;
+                float v = run[j][e];
+                if (ep.bias) v = __fadd_rn(v, ep.bias[n]);
+                if (ep.gelu) v = gelu_tanh(v);
+                if (ep.mul) v = __fmul_rn(v, ep.mul[o]);
+                if (ep.residual) v = __fadd_rn(ep.residual[o], v);
+                y[o] = v;
+            }
+        }
+    }
+}
+
+template <int TYPE, int W, int NT>
+int launch_cfg(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum, float* y, uint32_t M,
+               QgEpilogue ep, cudaStream_t st) {
+    const dim3 grid((w->out_dim + W * 16 - 1) / (W * 16), (M + NT * 8 - 1) / (NT * 8));
+    if (grid.y > 65535u) return ZQ_ERR_LIMIT;
+    const size_t smem = 2 * (size_t)(4 * NT * 8 * 32 + 2 * 4 * NT * 8 * 4);
+    gemm_q8_kernel<TYPE, W, NT><<<grid, W * 32, smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), xq, xs, xsum,
+                                                            y, w->out_dim, w->in_dim, M, w->nb, w->scp, ep);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+template <int TYPE>
+int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum, float* y, uint32_t M,
+               QgEpilogue ep, cudaStream_t st) {
+    const uint64_t sms = (uint64_t)sm_count();
+    const uint64_t big = (uint64_t)((w->out_dim + 127) / 128) * ((M + 63) / 64);
+    if (big >= sms) return launch_cfg<TYPE, 8, 8>(w, xq, xs, xsum, y, M, ep, st);
+    const uint64_t mid = (uint64_t)((w->out_dim + 31) / 32) * ((M + 63) / 64);
+    if (mid >= sms) return launch_cfg<TYPE, 2, 8>(w, xq, xs, xsum, y, M, ep, st);
+    return launch_cfg<TYPE, 2, 2>(w, xq, xs, xsum, y, M, ep, st);
+}
+
+}  // namespace
+
+int launch_gemm_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum, float* y,
+                   uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st) {
+    QgEpilogue a{nullptr, nullptr, nullptr, 0};
+    if (ep) {
+        a.bias = ep->d_bias;
+        a.gelu = ep->gelu;
+        a.mul = ep->d_mul;
+        a.residual = ep->d_residual;
+    }
+    switch (w->type) {
+        case ZQ_TYPE_Q4_0: return launch_one<ZQ_TYPE_Q4_0>(w, xq, xscale, xsum, y, m_rows, a, st);
+        case ZQ_TYPE_Q4_1: return launch_one<ZQ_TYPE_Q4_1>(w, xq, xscale, xsum, y, m_rows, a, st);
+        case ZQ_TYPE_Q8_0: return launch_one<ZQ_TYPE_Q8_0>(w, xq, xscale, xsum, y, m_rows, a, st);
+        default: return ZQ_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace zq

@@ -539,7 +539,8 @@ size_t zq_matmul_workspace_bytes(const zq_weight* w, uint32_t m_rows, int act_mo
         const size_t s = ((size_t)m_rows * w->nb * 4 + 255) & ~(size_t)255;
         return q + 2 * s;
     }
-    if (act_mode == ZQ_ACT_F32 && m_rows >= kGemmMinRows) {  // either GEMM kernel can use it
+    if ((act_mode == ZQ_ACT_F32 && m_rows >= kGemmMinRows) || (act_mode == ZQ_ACT_F16 && m_rows > 0)) {
+        // either GEMM kernel can use it
         const size_t a = gemm_f16_workspace_bytes(w, m_rows), b = gemm_tc_workspace_bytes(w, m_rows);
         return a > b ? a : b;
     }
@@ -588,6 +589,15 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
         }
         return ZQ_OK;
     }
+    if (act_mode == ZQ_ACT_F16) {  // the tensor-core GEMM whatever the row count
+        if (((uintptr_t)d_x & 3) != 0) return ZQ_ERR_BAD_ARG;
+        if (!d_workspace || ((uintptr_t)d_workspace & 255) ||
+            workspace_bytes < zq_matmul_workspace_bytes(w, m_rows, act_mode))
+            return ZQ_ERR_BAD_ARG;
+        static const bool legacy = getenv("ZQ_GEMM") && getenv("ZQ_GEMM")[0] == 'm';
+        return legacy ? launch_gemm_f16(w, d_x, d_y, m_rows, epilogue, d_workspace, st)
+                      : launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
+    }
     if (act_mode == ZQ_ACT_Q8) {
         if (w->in_dim > 16384) return ZQ_ERR_LIMIT;
         const size_t need = zq_matmul_workspace_bytes(w, m_rows, act_mode);
@@ -599,6 +609,8 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
         int32_t* sm = reinterpret_cast<int32_t*>(static_cast<char*>(d_workspace) + qbytes + sbytes);
         int rc = launch_quantize_rows_q8(d_x, m_rows, w->in_dim, q, sc, sm, st);
         if (rc != ZQ_OK) return rc;
+        // from a handful of rows on, the exact int8 GEMM (weights read once per 64 rows) beats a GEMV per row
+        if (m_rows >= 5) return launch_gemm_q8(w, q, sc, sm, d_y, m_rows, epilogue, st);
         return launch_gemv_q8(w, q, sc, sm, d_y, m_rows, epilogue, st);
     }
     return ZQ_ERR_BAD_ARG;

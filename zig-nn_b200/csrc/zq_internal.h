@@ -122,6 +122,9 @@ int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, co
                    float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
 int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, int8_t* q,
                             float* scale, int32_t* sum, cudaStream_t st);
+// Exact int8 tensor-core GEMM for many Q8-quantised activation rows; bit-identical to launch_gemv_q8 (gemm_q8.cu).
+int launch_gemm_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum, float* y,
+                   uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
 // Tensor-core GEMM for many activation rows (gemm.cu): fp16 operands, f32 accumulation. `workspace`
 // holds gemm_f16_workspace_bytes() bytes, 256-byte aligned.
 constexpr uint32_t kGemmMinRows = 49;  // below this, passes of the 16-row decode kernel are faster
