@@ -192,7 +192,7 @@ static int gpt2_step(zq_gpt2* m, int variant, cudaStream_t st) {
         if ((rc = gpt2_linear(m, b.qkv, m->x, m->qkv, b.qkv_b, 0, nullptr, b.ln1_w, b.ln1_b, st))) return rc;
         if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], m->qkv + E, m->qkv + 2 * E, m->att, nullptr, nullptr,
                                         nullptr, m->scores, C.head, C.head, hd, m->d_state, 0, C.ctx,
-                                        ZQ_ATTN_GPT2_SOFTMAX, st)))
+                                        ZQ_ATTN_GPT2_SOFTMAX, 1, 3 * E, st)))
             return rc;
         if ((rc = gpt2_linear(m, b.proj, m->att, m->x, b.proj_b, 0, m->x, nullptr, nullptr, st))) return rc;
         if ((rc = gpt2_linear(m, b.fc, m->x, m->hid, b.fc_b, 1, nullptr, b.ln2_w, b.ln2_b, st))) return rc;
@@ -380,6 +380,8 @@ struct zq_gemma3 {
     float* xscale = nullptr;
     int32_t* xsum = nullptr;
     uint32_t* d_state = nullptr;
+    int32_t* d_tokens = nullptr;  // token ids of a prefill chunk
+    uint32_t max_rows = 1;        // rows the activation buffers hold (prefill chunk size)
     int32_t* d_arg = nullptr;
     uint32_t* d_record = nullptr;
     uint32_t seq_len = 0;
@@ -399,68 +401,83 @@ struct zq_gemma3 {
     }
 };
 
-// The activation row is quantised once (thread_pool.zig:111-114); any number of weights consume it.
-static int gemma_gemv(zq_gemma3* m, const zq_weight* w, float* y, cudaStream_t st) {
-    return launch_gemv_q8(w, m->xq, m->xscale, m->xsum, y, 1, nullptr, st);
+// Activation rows are quantised once (thread_pool.zig:111-114); any number of weights consume them.
+// T rows: one exact GEMV per row, or from five rows up the exact int8 GEMM (identical results).
+static int gemma_linear(zq_gemma3* m, const zq_weight* w, float* y, uint32_t y_stride, uint32_t T, cudaStream_t st) {
+    if (T >= 5 && y_stride == w->out_dim) return launch_gemm_q8(w, m->xq, m->xscale, m->xsum, y, T, nullptr, st);
+    for (uint32_t r = 0; r < T; ++r) {
+        int rc = launch_gemv_q8(w, m->xq + (size_t)r * w->in_dim, m->xscale + (size_t)r * w->nb,
+                                m->xsum + (size_t)r * w->nb, y + (size_t)r * y_stride, 1, nullptr, st);
+        if (rc != ZQ_OK) return rc;
+    }
+    return ZQ_OK;
 }
 
-// One decode step for the token and position held in m->d_state (gemma3.zig:551-846), about ten
-// launches per layer: [norm+quantise] qkv | qk-norm+rope+cache | scores | softmax.V+quantise | o |
+// Forward pass over T consecutive tokens starting at position m->d_state[1] (gemma3.zig:551-846).
+// T == 1 is a decode step (token in m->d_state[0]); T > 1 is a batched prefill chunk (tokens in
+// m->d_tokens), every row computed with exactly the arithmetic of a decode step. About ten launches per
+// layer: [norm+quantise] qkv | qk-norm+rope+cache | scores | softmax.V+quantise | o |
 // post-norm+residual+pre-norm+quantise | gate,up | gelu.mul+quantise | down | post-norm+residual+...
-static int gemma3_step(zq_gemma3* m, int variant, cudaStream_t st) {
+// Logits (and the argmax of a greedy step) are those of the last row.
+static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st) {
     const zq_gemma3_config& C = m->c;
     const uint32_t E = C.embed, D = C.head_dim, QD = C.head * D, KD = C.head_kv * D, F = C.ffn;
+    const uint32_t QKV = QD + 2 * KD;
+    if (T == 0 || T > m->max_rows) return ZQ_ERR_BAD_ARG;
     int rc;
-    if ((rc = zq_dequant_rows_scaled(m->token_embd, reinterpret_cast<const int32_t*>(m->d_state), 1,
-                                     sqrtf((float)E), m->x, st)))
-        return rc;
+    const int32_t* ids = T == 1 ? reinterpret_cast<const int32_t*>(m->d_state) : m->d_tokens;
+    if ((rc = zq_dequant_rows_scaled(m->token_embd, ids, T, sqrtf((float)E), m->x, st))) return rc;
     if ((rc = launch_norm_quant(m->x, m->blocks[0].attn_norm_w, nullptr, nullptr, E, C.rms_eps, m->xq,
-                                m->xscale, m->xsum, st)))
+                                m->xscale, m->xsum, T, E, st)))
         return rc;
     for (uint32_t l = 0; l < C.layer; ++l) {
         const zq_gemma3::Block& b = m->blocks[l];
         // attention block (gemma3.zig:662-731)
         if (b.qkv) {
-            if ((rc = gemma_gemv(m, b.qkv, m->qkv, st))) return rc;
+            if ((rc = gemma_linear(m, b.qkv, m->qkv, QKV, T, st))) return rc;
         } else {
-            if ((rc = gemma_gemv(m, b.q, m->qkv, st))) return rc;
-            if ((rc = gemma_gemv(m, b.k, m->qkv + QD, st))) return rc;
-            if ((rc = gemma_gemv(m, b.v, m->qkv + QD + KD, st))) return rc;
+            if ((rc = gemma_linear(m, b.q, m->qkv, QKV, T, st))) return rc;
+            if ((rc = gemma_linear(m, b.k, m->qkv + QD, QKV, T, st))) return rc;
+            if ((rc = gemma_linear(m, b.v, m->qkv + QD + KD, QKV, T, st))) return rc;
         }
         if ((rc = launch_qk_norm_rope_kv(m->qkv, b.q_norm_w, b.k_norm_w, m->freqs, m->k[l], m->v[l], m->d_state,
-                                         C.head, C.head_kv, D, C.rms_eps, st)))
+                                         C.head, C.head_kv, D, C.rms_eps, T, QKV, st)))
             return rc;
         const bool global = (l % C.global_every) == C.global_every - 1;
         const uint32_t window = global ? 0u : C.sliding_window;
         const uint32_t max_len = (window && window < C.ctx) ? window : C.ctx;
         if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], nullptr, nullptr, nullptr, m->xq, m->xscale, m->xsum,
-                                        m->scores, C.head, C.head_kv, D, m->d_state, window, max_len, 0, st)))
+                                        m->scores, C.head, C.head_kv, D, m->d_state, window, max_len, 0, T, QKV, st)))
             return rc;
-        if ((rc = gemma_gemv(m, b.o, m->proj, st))) return rc;
+        if ((rc = gemma_linear(m, b.o, m->proj, E, T, st))) return rc;
         if ((rc = launch_norm_quant(m->proj, b.post_attn_norm_w, m->x, b.ffn_norm_w, E, C.rms_eps, m->xq,
-                                    m->xscale, m->xsum, st)))
+                                    m->xscale, m->xsum, T, E, st)))
             return rc;
         // FFN block (gemma3.zig:734-773)
         if (b.gate_up) {
-            if ((rc = gemma_gemv(m, b.gate_up, m->gu, st))) return rc;
+            if ((rc = gemma_linear(m, b.gate_up, m->gu, 2 * F, T, st))) return rc;
         } else {
-            if ((rc = gemma_gemv(m, b.gate, m->gu, st))) return rc;
-            if ((rc = gemma_gemv(m, b.up, m->gu + F, st))) return rc;
+            if ((rc = gemma_linear(m, b.gate, m->gu, 2 * F, T, st))) return rc;
+            if ((rc = gemma_linear(m, b.up, m->gu + F, 2 * F, T, st))) return rc;
         }
-        if ((rc = launch_gelu_mul_quant(m->gu, m->gu + F, F, m->xq, m->xscale, m->xsum, st))) return rc;
-        if ((rc = gemma_gemv(m, b.down, m->ffn, st))) return rc;
+        if ((rc = launch_gelu_mul_quant(m->gu, m->gu + F, F, m->xq, m->xscale, m->xsum, T, 2 * F, st))) return rc;
+        if ((rc = gemma_linear(m, b.down, m->ffn, E, T, st))) return rc;
         const float* next_norm = l + 1 < C.layer ? m->blocks[l + 1].attn_norm_w
                                  : (variant != STEP_CACHE_ONLY ? m->output_norm_w : nullptr);
         if (next_norm) {
             if ((rc = launch_norm_quant(m->ffn, b.post_ffw_norm_w, m->x, next_norm, E, C.rms_eps, m->xq, m->xscale,
-                                        m->xsum, st)))
+                                        m->xsum, T, E, st)))
                 return rc;
-        } else if ((rc = zq_rms_norm_residual(m->ffn, b.post_ffw_norm_w, m->x, E, 1, C.rms_eps, st))) {
+        } else if ((rc = zq_rms_norm_residual(m->ffn, b.post_ffw_norm_w, m->x, E, T, C.rms_eps, st))) {
             return rc;
         }
     }
-    if (variant != STEP_CACHE_ONLY) {
-        if ((rc = gemma_gemv(m, m->token_embd, m->logits, st))) return rc;
+    if (variant != STEP_CACHE_ONLY) {  // the last row's logits
+        const zq_weight* w = m->token_embd;
+        const size_t r = T - 1;
+        if ((rc = launch_gemv_q8(w, m->xq + r * w->in_dim, m->xscale + r * w->nb, m->xsum + r * w->nb, m->logits, 1,
+                                 nullptr, st)))
+            return rc;
     }
     if (variant == STEP_GREEDY) {
         if ((rc = zq_argmax(m->logits, C.vocab, m->d_arg, st))) return rc;
@@ -471,7 +488,7 @@ static int gemma3_step(zq_gemma3* m, int variant, cudaStream_t st) {
 }
 
 static int gemma3_run(zq_gemma3* m, int variant, cudaStream_t st) {
-    return m->graphs.run(variant, st, [&](cudaStream_t s) { return gemma3_step(m, variant, s); });
+    return m->graphs.run(variant, st, [&](cudaStream_t s) { return gemma3_forward(m, 1, variant, s); });
 }
 
 // Upload several GGUF matrices with the same in_dim and type as one matrix of stacked rows.
@@ -590,16 +607,20 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
             return cuda_fail(e);
         }
     }
-    TRY(m->arena.alloc_n(&m->x, E));
-    TRY(m->arena.alloc_n(&m->qkv, (size_t)QD + 2 * KD));
-    TRY(m->arena.alloc_n(&m->proj, E));
-    TRY(m->arena.alloc_n(&m->gu, 2 * (size_t)F));
-    TRY(m->arena.alloc_n(&m->ffn, E));
+    // activation buffers hold a prefill chunk of up to 128 tokens (a decode step uses row 0)
+    m->max_rows = C.ctx < 128 ? C.ctx : 128;
+    const size_t R = m->max_rows;
+    TRY(m->arena.alloc_n(&m->x, R * E));
+    TRY(m->arena.alloc_n(&m->qkv, R * ((size_t)QD + 2 * KD)));
+    TRY(m->arena.alloc_n(&m->proj, R * E));
+    TRY(m->arena.alloc_n(&m->gu, R * 2 * (size_t)F));
+    TRY(m->arena.alloc_n(&m->ffn, R * E));
     TRY(m->arena.alloc_n(&m->logits, C.vocab));
-    TRY(m->arena.alloc_n(&m->scores, (size_t)C.head * C.ctx));
-    TRY(m->arena.alloc_n(&m->xq, max_dim));
-    TRY(m->arena.alloc_n(&m->xscale, max_dim / 32));
-    TRY(m->arena.alloc_n(&m->xsum, max_dim / 32));
+    TRY(m->arena.alloc_n(&m->scores, R * C.head * C.ctx));
+    TRY(m->arena.alloc_n(&m->xq, R * max_dim));
+    TRY(m->arena.alloc_n(&m->xscale, R * (max_dim / 32)));
+    TRY(m->arena.alloc_n(&m->xsum, R * (max_dim / 32)));
+    TRY(m->arena.alloc_n(&m->d_tokens, R));
     TRY(m->arena.alloc_n(&m->d_state, 4));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, C.ctx));
@@ -638,10 +659,20 @@ int zq_gemma3_prefill(zq_gemma3* m, const uint32_t* h_tokens, uint32_t n, zq_str
         if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
     m->seq_len = 0;
-    for (uint32_t t = 0; t < n; ++t) {
-        set_state_kernel<<<1, 1, 0, st>>>(m->d_state, h_tokens[t], t, 0);
+    // chunks of up to max_rows tokens, each a batched forward pass (every row = the arithmetic of a decode step)
+    for (uint32_t t0 = 0; t0 < n; t0 += m->max_rows) {
+        const uint32_t T = n - t0 < m->max_rows ? n - t0 : m->max_rows;
+        const bool last = t0 + T == n;
+        set_state_kernel<<<1, 1, 0, st>>>(m->d_state, h_tokens[t0], t0, 0);
         ZQ_LAUNCH_CHECK();
-        int rc = gemma3_run(m, t + 1 == n ? STEP_LOGITS : STEP_CACHE_ONLY, st);
+        int rc;
+        if (T == 1) {
+            rc = gemma3_run(m, last ? STEP_LOGITS : STEP_CACHE_ONLY, st);
+        } else {
+            ZQ_CUDA(cudaMemcpyAsync(m->d_tokens, h_tokens + t0, T * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
+            rc = gemma3_forward(m, T, last ? STEP_LOGITS : STEP_CACHE_ONLY, st);
+            ZQ_CUDA(cudaStreamSynchronize(st));  // h_tokens is the caller's memory
+        }
         if (rc != ZQ_OK) return rc;
     }
     m->seq_len = n;

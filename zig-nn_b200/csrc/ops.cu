@@ -374,12 +374,20 @@ template <bool RES, int PER>
 __global__ void __launch_bounds__(256)
 norm_quant_kernel(const float* __restrict__ src, const float* __restrict__ w1, float* __restrict__ res,
                   const float* __restrict__ w2, uint32_t dim, float eps, int8_t* __restrict__ q,
-                  float* __restrict__ scale, int32_t* __restrict__ sum) {
+                  float* __restrict__ scale, int32_t* __restrict__ sum, uint32_t src_stride) {
     extern __shared__ __align__(16) float xs[];
     __shared__ float part[16];
     __shared__ float bc;
     constexpr int P = PER > 0 ? PER : 1;
     float rw1[P], rw2[P], rres[P];
+    {   // one CTA per row (decode: one row; batched prefill: one per token)
+        const size_t row = blockIdx.x;
+        src += row * src_stride;
+        if (RES) res += row * dim;
+        q += row * dim;
+        scale += row * (dim >> 5);
+        sum += row * (dim >> 5);
+    }
     pdl_launch_dependents();
     if (PER > 0) {
 #pragma unroll
@@ -458,12 +466,13 @@ __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_kernel(float* __restrict__ qkv, const float* __restrict__ q_norm_w,
                        const float* __restrict__ k_norm_w, const float* __restrict__ freqs,
                        float* __restrict__ kc, float* __restrict__ vc, const uint32_t* __restrict__ state,
-                       uint32_t n_head, uint32_t n_kv_head, uint32_t head_dim, float eps) {
+                       uint32_t n_head, uint32_t n_kv_head, uint32_t head_dim, float eps, uint32_t qkv_stride) {
     extern __shared__ __align__(16) float xs[];
     __shared__ float bc;
     pdl_launch_dependents();
     pdl_wait();
-    const uint32_t pos = state[1];
+    const uint32_t pos = state[1] + blockIdx.y;  // blockIdx.y: token of a batched prefill (0 when decoding)
+    qkv += (size_t)blockIdx.y * qkv_stride;
     const uint32_t b = blockIdx.x, kv_dim = n_kv_head * head_dim;
     if (b >= n_head + n_kv_head) {  // v head: copy
         const uint32_t hv = b - n_head - n_kv_head;
@@ -497,20 +506,22 @@ qk_norm_rope_kv_kernel(float* __restrict__ qkv, const float* __restrict__ q_norm
 // projection). One warp per 32-block.
 __global__ void __launch_bounds__(256)
 gelu_mul_quant_kernel(const float* __restrict__ gate, const float* __restrict__ up, uint32_t n_blocks,
-                      int8_t* __restrict__ q, float* __restrict__ scale, int32_t* __restrict__ sum) {
+                      int8_t* __restrict__ q, float* __restrict__ scale, int32_t* __restrict__ sum,
+                      uint32_t blocks_per_row, uint32_t in_stride) {
     const uint32_t blk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait();
     if (blk >= n_blocks) return;
-    const size_t i = (size_t)blk * 32 + lane;
+    // rows of gate / up are in_stride floats apart; the quantised output is dense
+    const size_t i = (size_t)(blk / blocks_per_row) * in_stride + (size_t)(blk % blocks_per_row) * 32 + lane;
     quantize_block_warp(__fmul_rn(gelu_tanh(gate[i]), up[i]), blk, lane, q, scale, sum);
 }
 
 // The window a decode step attends to: positions [kv_start, pos]; `window` = 0 means all of them.
 __device__ __forceinline__ void step_window(const uint32_t* state, uint32_t window, uint32_t* kv_start,
-                                            uint32_t* kv_len) {
-    const uint32_t end = state[1] + 1;
+                                            uint32_t* kv_len, uint32_t token = 0) {
+    const uint32_t end = state[1] + token + 1;
     const uint32_t len = (window && end > window) ? window : end;
     *kv_start = end - len;
     *kv_len = len;
@@ -522,12 +533,15 @@ __global__ void __launch_bounds__(256)
 attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc, float* __restrict__ vc,
                              const float* __restrict__ k_new, const float* __restrict__ v_new,
                              float* __restrict__ scores, uint32_t n_head, uint32_t n_kv_head,
-                             uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window) {
+                             uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window,
+                             uint32_t q_stride, uint32_t scores_stride) {
     __shared__ float part[16][17];
     pdl_launch_dependents();
     pdl_wait();
     uint32_t kv_start, kv_len;
-    step_window(state, window, &kv_start, &kv_len);
+    step_window(state, window, &kv_start, &kv_len, blockIdx.z);  // blockIdx.z: token of a batched prefill
+    q += (size_t)blockIdx.z * q_stride;
+    scores += (size_t)blockIdx.z * scores_stride;
     const uint32_t h = blockIdx.y;
     const uint32_t kvh = h / (n_head / n_kv_head);
     const uint32_t kv_dim = n_kv_head * head_dim;
@@ -579,7 +593,7 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
                                 float* __restrict__ out, int8_t* __restrict__ oq, float* __restrict__ oscale,
                                 int32_t* __restrict__ osum, uint32_t n_head, uint32_t n_kv_head,
                                 uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window,
-                                int gpt2_tail) {
+                                int gpt2_tail, uint32_t scores_stride) {
     extern __shared__ __align__(16) float w[];  // max window length
     __shared__ float vt[kAttnTile][kAttnDims];
     __shared__ float red[33];
@@ -587,7 +601,9 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
     pdl_launch_dependents();
     pdl_wait();
     uint32_t kv_start, kv_len;
-    step_window(state, window, &kv_start, &kv_len);
+    step_window(state, window, &kv_start, &kv_len, blockIdx.z);  // blockIdx.z: token of a batched prefill
+    scores += (size_t)blockIdx.z * scores_stride;
+    const size_t out_row = (size_t)blockIdx.z * n_head * head_dim;
     const uint32_t h = blockIdx.x;
     const uint32_t kvh = h / (n_head / n_kv_head);
     const uint32_t kv_dim = n_kv_head * head_dim;
@@ -660,7 +676,7 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
         }
     }
     if (pg == 0) {  // two whole warps: 32-blocks of the output line up with warps
-        const size_t o = (size_t)h * head_dim + d0 + dl;
+        const size_t o = out_row + (size_t)h * head_dim + d0 + dl;
         if (d_ok && out) out[o] = acc;
         if (QUANT && d0 + (dl & ~31u) < head_dim) quantize_block_warp(acc, o >> 5, threadIdx.x & 31, oq, oscale, osum);
     }
@@ -691,20 +707,21 @@ inline unsigned grid1d(size_t n, unsigned threads) { return (unsigned)((n + thre
 // ---- launchers used by the engines (declared in zq_internal.h) ----------------------------
 
 int launch_norm_quant(const float* src, const float* w1, float* res, const float* w2, uint32_t dim, float eps,
-                      int8_t* q, float* scale, int32_t* sum, cudaStream_t st) {
+                      int8_t* q, float* scale, int32_t* sum, uint32_t rows, uint32_t src_stride, cudaStream_t st) {
     if (dim == 0 || dim % 32 || dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
+    if (rows == 0) return ZQ_OK;
     const size_t smem = dim * sizeof(float);
     cudaError_t e;
     if (dim <= 256 * 5) {
-        e = res ? launch_pdl(norm_quant_kernel<true, 5>, dim3(1), dim3(256), smem, st, src, w1, res, w2, dim, eps, q,
-                             scale, sum)
-                : launch_pdl(norm_quant_kernel<false, 5>, dim3(1), dim3(256), smem, st, src, w1, nullptr, nullptr, dim,
-                             eps, q, scale, sum);
+        e = res ? launch_pdl(norm_quant_kernel<true, 5>, dim3(rows), dim3(256), smem, st, src, w1, res, w2, dim, eps, q,
+                             scale, sum, src_stride)
+                : launch_pdl(norm_quant_kernel<false, 5>, dim3(rows), dim3(256), smem, st, src, w1, nullptr, nullptr,
+                             dim, eps, q, scale, sum, src_stride);
     } else {
-        e = res ? launch_pdl(norm_quant_kernel<true, 0>, dim3(1), dim3(256), smem, st, src, w1, res, w2, dim, eps, q,
-                             scale, sum)
-                : launch_pdl(norm_quant_kernel<false, 0>, dim3(1), dim3(256), smem, st, src, w1, nullptr, nullptr, dim,
-                             eps, q, scale, sum);
+        e = res ? launch_pdl(norm_quant_kernel<true, 0>, dim3(rows), dim3(256), smem, st, src, w1, res, w2, dim, eps, q,
+                             scale, sum, src_stride)
+                : launch_pdl(norm_quant_kernel<false, 0>, dim3(rows), dim3(256), smem, st, src, w1, nullptr, nullptr,
+                             dim, eps, q, scale, sum, src_stride);
     }
     ZQ_CUDA(e);
     return ZQ_OK;
@@ -712,47 +729,54 @@ int launch_norm_quant(const float* src, const float* w1, float* res, const float
 
 int launch_qk_norm_rope_kv(float* qkv, const float* q_norm_w, const float* k_norm_w, const float* freqs,
                            float* kc, float* vc, const uint32_t* state, uint32_t n_head, uint32_t n_kv_head,
-                           uint32_t head_dim, float eps, cudaStream_t st) {
+                           uint32_t head_dim, float eps, uint32_t rows, uint32_t qkv_stride, cudaStream_t st) {
     if (head_dim % 2 || head_dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
-    ZQ_CUDA(launch_pdl(qk_norm_rope_kv_kernel, dim3(n_head + 2 * n_kv_head), dim3(128), head_dim * sizeof(float),
-                       st, qkv, q_norm_w, k_norm_w, freqs, kc, vc, state, n_head, n_kv_head, head_dim, eps));
+    if (rows == 0) return ZQ_OK;
+    ZQ_CUDA(launch_pdl(qk_norm_rope_kv_kernel, dim3(n_head + 2 * n_kv_head, rows), dim3(128), head_dim * sizeof(float),
+                       st, qkv, q_norm_w, k_norm_w, freqs, kc, vc, state, n_head, n_kv_head, head_dim, eps,
+                       qkv_stride));
     return ZQ_OK;
 }
 
 int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t* q, float* scale,
-                          int32_t* sum, cudaStream_t st) {
+                          int32_t* sum, uint32_t rows, uint32_t in_stride, cudaStream_t st) {
     if (n % 32) return ZQ_ERR_BAD_ARG;
-    ZQ_CUDA(launch_pdl(gelu_mul_quant_kernel, dim3(grid1d(n, 256)), dim3(256), 0, st, gate, up, n / 32, q, scale,
-                       sum));
+    if (rows == 0) return ZQ_OK;
+    const size_t total = (size_t)rows * n;
+    ZQ_CUDA(launch_pdl(gelu_mul_quant_kernel, dim3(grid1d(total, 256)), dim3(256), 0, st, gate, up,
+                       (uint32_t)(total / 32), q, scale, sum, n / 32, in_stride));
     return ZQ_OK;
 }
 
 int launch_attention_step(const float* q, float* kc, float* vc, const float* k_new, const float* v_new,
                           float* out, int8_t* oq, float* oscale, int32_t* osum, float* scores, uint32_t n_head,
                           uint32_t n_kv_head, uint32_t head_dim, const uint32_t* state, uint32_t window,
-                          uint32_t max_len, int flags, cudaStream_t st) {
+                          uint32_t max_len, int flags, uint32_t rows, uint32_t q_stride, cudaStream_t st) {
     if (max_len == 0 || max_len > 180 * 1024 / 4) return ZQ_ERR_LIMIT;
     if (oq && head_dim % 32) return ZQ_ERR_BAD_ARG;
+    if (rows == 0) return ZQ_OK;
+    if (rows > 65535u || (rows > 1 && k_new)) return ZQ_ERR_BAD_ARG;
     const size_t smem = (size_t)max_len * sizeof(float);
     const int tail = (flags & ZQ_ATTN_GPT2_SOFTMAX) ? 1 : 0;
-    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head), dim3(256), 0, st, q, kc, vc,
-                       k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window));
+    const uint32_t scores_stride = n_head * max_len;
+    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head, rows), dim3(256), 0, st, q, kc,
+                       vc, k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window, q_stride, scores_stride));
+    const dim3 grid(n_head, (head_dim + kAttnDims - 1) / kAttnDims, rows);
     if (oq) {
         auto kern = attention_softmax_v_step_kernel<true>;
         if (smem > 24 * 1024)  // the kernel also holds a 16 KB static tile
             ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        ZQ_CUDA(launch_pdl(kern, dim3(n_head, (head_dim + kAttnDims - 1) / kAttnDims), dim3(256), smem, st, scores,
+        ZQ_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, static_cast<const float*>(scores),
                            static_cast<const float*>(vc), out, oq, oscale, osum, n_head, n_kv_head, head_dim, state,
-                           window, tail));
+                           window, tail, scores_stride));
     } else {
         auto kern = attention_softmax_v_step_kernel<false>;
-        if (smem > 24 * 1024)  // the kernel also holds a 16 KB static tile
+        if (smem > 24 * 1024)
             ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        ZQ_CUDA(launch_pdl(kern, dim3(n_head, (head_dim + kAttnDims - 1) / kAttnDims), dim3(256), smem, st, scores,
+        ZQ_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, static_cast<const float*>(scores),
                            static_cast<const float*>(vc), out, nullptr, nullptr, nullptr, n_head, n_kv_head, head_dim,
-                           state, window, tail));
+                           state, window, tail, scores_stride));
     }
-    ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
 
