@@ -144,6 +144,8 @@ struct zq_gpt2 {
     float *x = nullptr, *ln = nullptr, *qkv = nullptr, *att = nullptr, *hid = nullptr, *logits = nullptr;
     float* scores = nullptr;  // [head][ctx] attention scratch
     uint32_t* d_state = nullptr;
+    int32_t* d_tokens = nullptr;   // token ids of a prefill chunk
+    uint32_t max_rows = 1;         // rows the activation buffers hold (prefill chunk size)
     int32_t* d_arg = nullptr;
     uint32_t* d_record = nullptr;  // ctx entries for greedy decoding
     uint32_t seq_len = 0;
@@ -157,49 +159,72 @@ struct zq_gpt2 {
     }
 };
 
-// y = W . (ln ? LayerNorm(x) : x) + bias [gelu] [+ residual]. f32 weights (the .f32 branch of
-// linear_forward_q, gpt2.zig:652-671) take their epilogue as separate launches.
+// y[T][out] = W . (ln ? LayerNorm(x) : x)[T][in] + bias [gelu] [+ residual[T][out]]. Quantised weights run
+// in passes of up to 16 rows through the decode kernel (every row keeps the arithmetic of a decode step);
+// f32 weights (the .f32 branch of linear_forward_q, gpt2.zig:652-671) row by row with a separate epilogue.
+// The norm runs as its own small launch: folded into the GEMV prologue every CTA repeats its two
+// block-wide reductions before it can start, which measured 12% slower per step.
 static int gpt2_linear(zq_gpt2* m, const Linear& L, const float* x, float* y, const float* bias, int gelu,
-                       const float* residual, const float* ln_w, const float* ln_b, cudaStream_t st) {
-    zq_epilogue ep{bias, gelu, nullptr, residual};
+                       const float* residual, const float* ln_w, const float* ln_b, uint32_t T, cudaStream_t st) {
     int rc;
-    // The norm runs as its own small launch: folded into the GEMV prologue (launch_gemv_mma_ln_f32) every
-    // CTA repeats its two block-wide reductions before it can start, which measured 12% slower per step.
     if (ln_w) {
-        if ((rc = zq_layer_norm(m->ln, x, ln_w, ln_b, 1, L.in_dim, 1e-5f, st))) return rc;
+        if ((rc = zq_layer_norm(m->ln, x, ln_w, ln_b, T, L.in_dim, 1e-5f, st))) return rc;
         x = m->ln;
     }
-    if (L.qw) {
-        rc = launch_gemv_mma_f32(L.qw, x, y, 1, &ep, st);
-        return rc == ZQ_ERR_LIMIT ? launch_gemv_f32(L.qw, x, y, 1, &ep, st) : rc;
+    for (uint32_t r0 = 0; r0 < T; r0 += 16) {
+        const uint32_t mc = T - r0 < 16 ? T - r0 : 16;
+        const float* xr = x + (size_t)r0 * L.in_dim;
+        float* yr = y + (size_t)r0 * L.out_dim;
+        const float* rr = residual ? residual + (size_t)r0 * L.out_dim : nullptr;
+        zq_epilogue ep{bias, gelu, nullptr, rr};
+        if (L.qw) {
+            rc = launch_gemv_mma_f32(L.qw, xr, yr, mc, &ep, st);
+            if (rc == ZQ_ERR_LIMIT) rc = launch_gemv_f32(L.qw, xr, yr, mc, &ep, st);
+            if (rc != ZQ_OK) return rc;
+            continue;
+        }
+        for (uint32_t r = 0; r < mc; ++r) {
+            float* y1 = yr + (size_t)r * L.out_dim;
+            rc = zq_matvec_f32(L.f32w, xr + (size_t)r * L.in_dim, y1, L.out_dim, L.in_dim, st);
+            if (rc == ZQ_OK && bias) rc = zq_add_broadcast(y1, y1, bias, L.out_dim, L.out_dim, st);
+            if (rc == ZQ_OK && gelu) rc = zq_gelu(y1, y1, L.out_dim, st);
+            if (rc == ZQ_OK && rr) rc = zq_add_broadcast(y1, y1, rr + (size_t)r * L.out_dim, L.out_dim, L.out_dim, st);
+            if (rc != ZQ_OK) return rc;
+        }
     }
-    rc = zq_matvec_f32(L.f32w, x, y, L.out_dim, L.in_dim, st);
-    if (rc == ZQ_OK && bias) rc = zq_add_broadcast(y, y, bias, L.out_dim, L.out_dim, st);
-    if (rc == ZQ_OK && gelu) rc = zq_gelu(y, y, L.out_dim, st);
-    if (rc == ZQ_OK && residual) rc = zq_add_broadcast(y, y, residual, L.out_dim, L.out_dim, st);
-    return rc;
+    return ZQ_OK;
 }
 
-// One decode step for the token and position held in m->d_state (gpt2.zig:423-509), eight launches per
-// layer: ln1 | qkv | cache write + scores | softmax.V | proj + residual | ln2 | fc + gelu | mproj + residual.
-static int gpt2_step(zq_gpt2* m, int variant, cudaStream_t st) {
+// Forward pass over T consecutive tokens starting at position m->d_state[1] (gpt2.zig:423-509). T == 1 is a
+// decode step (token in m->d_state[0]); T > 1 a batched prefill chunk (tokens in m->d_tokens). Eight
+// launches per layer when decoding: ln1 | qkv | cache write + scores | softmax.V | proj + residual | ln2 |
+// fc + gelu | mproj + residual. Logits are those of the last row.
+static int gpt2_forward(zq_gpt2* m, uint32_t T, int variant, cudaStream_t st) {
     const zq_gpt2_config& C = m->c;
     const uint32_t E = C.embed, hd = E / C.head;
+    if (T == 0 || T > m->max_rows) return ZQ_ERR_BAD_ARG;
     int rc;
-    if ((rc = launch_gpt2_embed_step(m->x, m->wte, m->wpe, m->d_state, E, st))) return rc;
+    if ((rc = launch_gpt2_embed_step(m->x, m->wte, m->wpe, m->d_state, T == 1 ? nullptr : m->d_tokens, E, T, st)))
+        return rc;
     for (uint32_t l = 0; l < C.layer; ++l) {
         const zq_gpt2::Block& b = m->blocks[l];
-        if ((rc = gpt2_linear(m, b.qkv, m->x, m->qkv, b.qkv_b, 0, nullptr, b.ln1_w, b.ln1_b, st))) return rc;
-        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], m->qkv + E, m->qkv + 2 * E, m->att, nullptr, nullptr,
-                                        nullptr, m->scores, C.head, C.head, hd, m->d_state, 0, C.ctx,
-                                        ZQ_ATTN_GPT2_SOFTMAX, 1, 3 * E, st)))
+        if ((rc = gpt2_linear(m, b.qkv, m->x, m->qkv, b.qkv_b, 0, nullptr, b.ln1_w, b.ln1_b, T, st))) return rc;
+        const float *k_new = m->qkv + E, *v_new = m->qkv + 2 * E;
+        if (T > 1) {  // the decode step writes its cache row inside the scores kernel
+            if ((rc = launch_write_kv_step(k_new, v_new, m->k[l], m->v[l], m->d_state, E, T, 3 * E, st))) return rc;
+            k_new = v_new = nullptr;
+        }
+        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], k_new, v_new, m->att, nullptr, nullptr, nullptr,
+                                        m->scores, C.head, C.head, hd, m->d_state, 0, C.ctx, ZQ_ATTN_GPT2_SOFTMAX, T,
+                                        3 * E, st)))
             return rc;
-        if ((rc = gpt2_linear(m, b.proj, m->att, m->x, b.proj_b, 0, m->x, nullptr, nullptr, st))) return rc;
-        if ((rc = gpt2_linear(m, b.fc, m->x, m->hid, b.fc_b, 1, nullptr, b.ln2_w, b.ln2_b, st))) return rc;
-        if ((rc = gpt2_linear(m, b.mproj, m->hid, m->x, b.mproj_b, 0, m->x, nullptr, nullptr, st))) return rc;
+        if ((rc = gpt2_linear(m, b.proj, m->att, m->x, b.proj_b, 0, m->x, nullptr, nullptr, T, st))) return rc;
+        if ((rc = gpt2_linear(m, b.fc, m->x, m->hid, b.fc_b, 1, nullptr, b.ln2_w, b.ln2_b, T, st))) return rc;
+        if ((rc = gpt2_linear(m, b.mproj, m->hid, m->x, b.mproj_b, 0, m->x, nullptr, nullptr, T, st))) return rc;
     }
     if (variant != STEP_CACHE_ONLY) {
-        if ((rc = zq_layer_norm(m->ln, m->x, m->ln_f_w, m->ln_f_b, 1, E, 1e-5f, st))) return rc;
+        const float* last = m->x + (size_t)(T - 1) * E;
+        if ((rc = zq_layer_norm(m->ln, last, m->ln_f_w, m->ln_f_b, 1, E, 1e-5f, st))) return rc;
         if ((rc = launch_matvec_ln_f32(m->wte, m->ln, m->logits, C.vocab, E, nullptr, nullptr, 0.0f, st))) return rc;
     }
     if (variant == STEP_GREEDY) {
@@ -211,7 +236,7 @@ static int gpt2_step(zq_gpt2* m, int variant, cudaStream_t st) {
 }
 
 static int gpt2_run(zq_gpt2* m, int variant, cudaStream_t st) {
-    return m->graphs.run(variant, st, [&](cudaStream_t s) { return gpt2_step(m, variant, s); });
+    return m->graphs.run(variant, st, [&](cudaStream_t s) { return gpt2_forward(m, 1, variant, s); });
 }
 
 extern "C" {
@@ -265,13 +290,17 @@ int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_strea
         cudaMemsetAsync(m->k[l], 0, (size_t)cfg->ctx * E * sizeof(float), st);
         cudaMemsetAsync(m->v[l], 0, (size_t)cfg->ctx * E * sizeof(float), st);
     }
-    TRY(m->arena.alloc_n(&m->x, E));
-    TRY(m->arena.alloc_n(&m->ln, E));
-    TRY(m->arena.alloc_n(&m->qkv, 3 * (size_t)E));
-    TRY(m->arena.alloc_n(&m->att, E));
-    TRY(m->arena.alloc_n(&m->hid, F));
+    // activation buffers hold a prefill chunk of up to 128 tokens (a decode step uses row 0)
+    m->max_rows = cfg->ctx < 128 ? cfg->ctx : 128;
+    const size_t R = m->max_rows;
+    TRY(m->arena.alloc_n(&m->x, R * E));
+    TRY(m->arena.alloc_n(&m->ln, R * (E > F ? E : F)));
+    TRY(m->arena.alloc_n(&m->qkv, R * 3 * (size_t)E));
+    TRY(m->arena.alloc_n(&m->att, R * E));
+    TRY(m->arena.alloc_n(&m->hid, R * F));
     TRY(m->arena.alloc_n(&m->logits, cfg->vocab));
-    TRY(m->arena.alloc_n(&m->scores, (size_t)cfg->head * cfg->ctx));
+    TRY(m->arena.alloc_n(&m->scores, R * cfg->head * cfg->ctx));
+    TRY(m->arena.alloc_n(&m->d_tokens, R));
     TRY(m->arena.alloc_n(&m->d_state, 4));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, cfg->ctx));
@@ -310,10 +339,19 @@ int zq_gpt2_prefill(zq_gpt2* m, const uint32_t* h_tokens, uint32_t n, zq_stream 
         if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
     m->seq_len = 0;
-    for (uint32_t t = 0; t < n; ++t) {
-        set_state_kernel<<<1, 1, 0, st>>>(m->d_state, h_tokens[t], t, 0);
+    for (uint32_t t0 = 0; t0 < n; t0 += m->max_rows) {  // chunks of up to max_rows tokens
+        const uint32_t T = n - t0 < m->max_rows ? n - t0 : m->max_rows;
+        const bool last = t0 + T == n;
+        set_state_kernel<<<1, 1, 0, st>>>(m->d_state, h_tokens[t0], t0, 0);
         ZQ_LAUNCH_CHECK();
-        int rc = gpt2_run(m, t + 1 == n ? STEP_LOGITS : STEP_CACHE_ONLY, st);
+        int rc;
+        if (T == 1) {
+            rc = gpt2_run(m, last ? STEP_LOGITS : STEP_CACHE_ONLY, st);
+        } else {
+            ZQ_CUDA(cudaMemcpyAsync(m->d_tokens, h_tokens + t0, T * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
+            rc = gpt2_forward(m, T, last ? STEP_LOGITS : STEP_CACHE_ONLY, st);
+            ZQ_CUDA(cudaStreamSynchronize(st));  // h_tokens is the caller's memory
+        }
         if (rc != ZQ_OK) return rc;
     }
     m->seq_len = n;

@@ -683,20 +683,23 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
 }
 
 // GPT-2 embedding and cache write at the device-side position (gpt2.zig:449-453, 812-816).
+// blockIdx.y: token of a batched prefill (ids in `tokens`); decoding uses the token in state[0].
 __global__ void gpt2_embed_step_kernel(float* __restrict__ x, const float* __restrict__ wte,
                                        const float* __restrict__ wpe, const uint32_t* __restrict__ state,
-                                       uint32_t embed) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < embed) x[i] = wte[(size_t)state[0] * embed + i] + wpe[(size_t)state[1] * embed + i];
+                                       const int32_t* __restrict__ tokens, uint32_t embed) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    const uint32_t tok = tokens ? (uint32_t)tokens[r] : state[0];
+    if (i < embed) x[(size_t)r * embed + i] = wte[(size_t)tok * embed + i] + wpe[(size_t)(state[1] + r) * embed + i];
 }
+// k / v rows of the batch (in_stride floats apart) -> cache rows state[1] + r
 __global__ void write_kv_step_kernel(const float* __restrict__ k, const float* __restrict__ v,
                                      float* __restrict__ kc, float* __restrict__ vc,
-                                     const uint32_t* __restrict__ state, uint32_t kv_dim) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t pos = state[1];
+                                     const uint32_t* __restrict__ state, uint32_t kv_dim, uint32_t in_stride) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    const uint32_t pos = state[1] + r;
     if (i < kv_dim) {
-        kc[(size_t)pos * kv_dim + i] = k[i];
-        vc[(size_t)pos * kv_dim + i] = v[i];
+        kc[(size_t)pos * kv_dim + i] = k[(size_t)r * in_stride + i];
+        vc[(size_t)pos * kv_dim + i] = v[(size_t)r * in_stride + i];
     }
 }
 
@@ -780,16 +783,18 @@ int launch_attention_step(const float* q, float* kc, float* vc, const float* k_n
     return ZQ_OK;
 }
 
-int launch_gpt2_embed_step(float* x, const float* wte, const float* wpe, const uint32_t* state, uint32_t embed,
-                           cudaStream_t st) {
-    gpt2_embed_step_kernel<<<grid1d(embed, 256), 256, 0, st>>>(x, wte, wpe, state, embed);
+int launch_gpt2_embed_step(float* x, const float* wte, const float* wpe, const uint32_t* state,
+                           const int32_t* tokens, uint32_t embed, uint32_t rows, cudaStream_t st) {
+    if (rows == 0) return ZQ_OK;
+    gpt2_embed_step_kernel<<<dim3(grid1d(embed, 256), rows), 256, 0, st>>>(x, wte, wpe, state, tokens, embed);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
 
 int launch_write_kv_step(const float* k, const float* v, float* kc, float* vc, const uint32_t* state,
-                         uint32_t kv_dim, cudaStream_t st) {
-    write_kv_step_kernel<<<grid1d(kv_dim, 256), 256, 0, st>>>(k, v, kc, vc, state, kv_dim);
+                         uint32_t kv_dim, uint32_t rows, uint32_t in_stride, cudaStream_t st) {
+    if (rows == 0) return ZQ_OK;
+    write_kv_step_kernel<<<dim3(grid1d(kv_dim, 256), rows), 256, 0, st>>>(k, v, kc, vc, state, kv_dim, in_stride);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }

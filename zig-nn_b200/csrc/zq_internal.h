@@ -166,9 +166,9 @@ int launch_attention_step(const float* q, float* kc, float* vc, const float* k_n
 // f32 matvec (GPT-2 vocabulary head) with an optional LayerNorm of x in the prologue (gemv.cu).
 int launch_matvec_ln_f32(const float* w, const float* x, float* y, uint32_t out_dim, uint32_t in_dim,
                          const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st);
-int launch_gpt2_embed_step(float* x, const float* wte, const float* wpe, const uint32_t* state, uint32_t embed,
-                           cudaStream_t st);
+int launch_gpt2_embed_step(float* x, const float* wte, const float* wpe, const uint32_t* state,
+                           const int32_t* tokens, uint32_t embed, uint32_t rows, cudaStream_t st);
 int launch_write_kv_step(const float* k, const float* v, float* kc, float* vc, const uint32_t* state,
-                         uint32_t kv_dim, cudaStream_t st);
+                         uint32_t kv_dim, uint32_t rows, uint32_t in_stride, cudaStream_t st);
 
 }  // namespace zq
