@@ -387,6 +387,23 @@ int zq_gemma3_decode_next(zq_gemma3* m, uint32_t token, zq_stream stream,
 int zq_gemma3_decode_greedy(zq_gemma3* m, uint32_t first_token, uint32_t n_steps,
                             zq_stream stream, uint32_t* h_tokens_out);
 
+/* Several independent sequences in one engine (batched decode). The reference decodes one sequence at a
+ * time (gemma3.zig:789-827); here n_seq sequences share the weights, each with its own KV-cache slot and
+ * position, and one call advances all of them: the linears run as exact int8 GEMMs over the n_seq rows
+ * (weights read once per step instead of once per sequence), every row with the arithmetic of a
+ * single-sequence decode step, so each sequence's logits are bit-identical to decoding it alone.
+ *   zq_gemma3_create_batch      n_seq cache slots (1 <= n_seq <= 1024); n_seq == 1 is zq_gemma3_create
+ *   zq_gemma3_prefill_seq       prefill of sequence `seq`; *d_logits = its last token's logits [vocab]
+ *   zq_gemma3_decode_next_batch h_tokens[n_seq] = next token of every sequence; *d_logits = [n_seq][vocab]
+ *   zq_gemma3_seq_len_of        tokens held by sequence `seq`
+ * zq_gemma3_decode_next / _decode_greedy need n_seq == 1. */
+int zq_gemma3_create_batch(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, uint32_t n_seq,
+                           zq_stream stream, zq_gemma3** out);
+int zq_gemma3_prefill_seq(zq_gemma3* m, uint32_t seq, const uint32_t* h_tokens, uint32_t n, zq_stream stream,
+                          const float** d_logits);
+int zq_gemma3_decode_next_batch(zq_gemma3* m, const uint32_t* h_tokens, zq_stream stream, const float** d_logits);
+int zq_gemma3_seq_len_of(const zq_gemma3* m, uint32_t seq, uint32_t* seq_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,6 +75,10 @@ SIGNATURES = {
     "zq_gemma3_prefill": (i, [vp, vp, u32, vp, P(vp)]),
     "zq_gemma3_decode_next": (i, [vp, u32, vp, P(vp)]),
     "zq_gemma3_decode_greedy": (i, [vp, u32, u32, vp, vp]),
+    "zq_gemma3_create_batch": (i, [P(S.Gemma3Config), P(S.Gemma3Weights), u32, vp, P(vp)]),
+    "zq_gemma3_prefill_seq": (i, [vp, u32, vp, u32, vp, P(vp)]),
+    "zq_gemma3_decode_next_batch": (i, [vp, vp, vp, P(vp)]),
+    "zq_gemma3_seq_len_of": (i, [vp, u32, P(u32)]),
 }
 
 

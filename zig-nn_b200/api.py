@@ -358,3 +358,53 @@ class Gpt2(_Engine):
 class Gemma3(_Engine):
     """gemma3(C): init / prefill / decode_next (src/models/gemma3.zig:283,551,789)."""
     _prefix = "zq_gemma3"
+
+
+class Gemma3Batch:
+    """Several independent sequences in one engine: prefill each, then advance all of them per call
+    (the linears run as exact int8 GEMMs over the sequences)."""
+
+    def __init__(self, host_model, n_seq):
+        lib = _lib.load()
+        self._cfg = host_model.config_struct()
+        self._w = host_model.weights_struct()
+        self.vocab, self.n_seq = self._cfg.vocab, int(n_seq)
+        h = C.c_void_p()
+        _lib.check(lib.zq_gemma3_create_batch(C.byref(self._cfg), C.byref(self._w), self.n_seq, _stream(), C.byref(h)),
+                   "zq_gemma3_create_batch")
+        self._h = h
+
+    def prefill(self, seq, tokens):
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        ptr = C.c_void_p()
+        rc = _lib.load().zq_gemma3_prefill_seq(self._h, int(seq), toks.ctypes.data_as(C.c_void_p), toks.size, _stream(),
+                                               C.byref(ptr))
+        _lib.check(rc, "zq_gemma3_prefill_seq")
+        return torch.as_tensor(_DevicePtrView(ptr.value, self.vocab), device="cuda").clone()
+
+    def decode_next(self, tokens):
+        """tokens: one per sequence -> logits [n_seq][vocab] (a copy)."""
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        if toks.size != self.n_seq:
+            raise ValueError("need %d tokens, got %d" % (self.n_seq, toks.size))
+        ptr = C.c_void_p()
+        rc = _lib.load().zq_gemma3_decode_next_batch(self._h, toks.ctypes.data_as(C.c_void_p), _stream(), C.byref(ptr))
+        _lib.check(rc, "zq_gemma3_decode_next_batch")
+        view = torch.as_tensor(_DevicePtrView(ptr.value, self.n_seq * self.vocab), device="cuda")
+        return view.clone().view(self.n_seq, self.vocab)
+
+    def seq_len(self, seq):
+        n = C.c_uint32()
+        _lib.check(_lib.load().zq_gemma3_seq_len_of(self._h, int(seq), C.byref(n)))
+        return n.value
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _lib.load().zq_gemma3_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -216,7 +216,7 @@ static int gpt2_forward(zq_gpt2* m, uint32_t T, int variant, cudaStream_t st) {
         }
         if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], k_new, v_new, m->att, nullptr, nullptr, nullptr,
                                         m->scores, C.head, C.head, hd, m->d_state, 0, C.ctx, ZQ_ATTN_GPT2_SOFTMAX, T,
-                                        3 * E, st)))
+                                        3 * E, nullptr, 0, st)))
             return rc;
         if ((rc = gpt2_linear(m, b.proj, m->att, m->x, b.proj_b, 0, m->x, nullptr, nullptr, T, st))) return rc;
         if ((rc = gpt2_linear(m, b.fc, m->x, m->hid, b.fc_b, 1, nullptr, b.ln2_w, b.ln2_b, T, st))) return rc;
@@ -418,11 +418,16 @@ struct zq_gemma3 {
     float* xscale = nullptr;
     int32_t* xsum = nullptr;
     uint32_t* d_state = nullptr;
-    int32_t* d_tokens = nullptr;  // token ids of a prefill chunk
-    uint32_t max_rows = 1;        // rows the activation buffers hold (prefill chunk size)
+    int32_t* d_tokens = nullptr;  // token ids of a prefill chunk / of a batched decode step
+    uint32_t max_rows = 1;        // rows the activation buffers hold (prefill chunk size, >= n_seq)
     int32_t* d_arg = nullptr;
     uint32_t* d_record = nullptr;
     uint32_t seq_len = 0;
+    // several independent sequences (batched decode): each has its own cache slot and position
+    uint32_t n_seq = 1;
+    uint32_t* d_pos = nullptr;            // [n_seq] positions of a batched decode step
+    std::vector<uint32_t> seq_lens;       // host copy, [n_seq]
+    float* logits_batch = nullptr;        // [n_seq][vocab]
     ~zq_gemma3() {
         zq_weight_free(token_embd);
         for (auto& b : blocks) {
@@ -457,13 +462,19 @@ static int gemma_linear(zq_gemma3* m, const zq_weight* w, float* y, uint32_t y_s
 // layer: [norm+quantise] qkv | qk-norm+rope+cache | scores | softmax.V+quantise | o |
 // post-norm+residual+pre-norm+quantise | gate,up | gelu.mul+quantise | down | post-norm+residual+...
 // Logits (and the argmax of a greedy step) are those of the last row.
-static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st) {
+// batch == false: the T rows are consecutive tokens of sequence `seq` (its cache slot). batch == true: row r
+// is the next token of sequence r, at position m->d_pos[r], and every row's logits go to m->logits_batch.
+static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st, uint32_t seq = 0,
+                          bool batch = false) {
     const zq_gemma3_config& C = m->c;
     const uint32_t E = C.embed, D = C.head_dim, QD = C.head * D, KD = C.head_kv * D, F = C.ffn;
     const uint32_t QKV = QD + 2 * KD;
-    if (T == 0 || T > m->max_rows) return ZQ_ERR_BAD_ARG;
+    if (T == 0 || T > m->max_rows || seq >= m->n_seq) return ZQ_ERR_BAD_ARG;
+    const size_t cache_stride = (size_t)C.ctx * KD;
+    const uint32_t* row_pos = batch ? m->d_pos : nullptr;
+    const size_t slot = batch ? 0 : seq * cache_stride;
     int rc;
-    const int32_t* ids = T == 1 ? reinterpret_cast<const int32_t*>(m->d_state) : m->d_tokens;
+    const int32_t* ids = (T == 1 && !batch) ? reinterpret_cast<const int32_t*>(m->d_state) : m->d_tokens;
     if ((rc = zq_dequant_rows_scaled(m->token_embd, ids, T, sqrtf((float)E), m->x, st))) return rc;
     if ((rc = launch_norm_quant(m->x, m->blocks[0].attn_norm_w, nullptr, nullptr, E, C.rms_eps, m->xq,
                                 m->xscale, m->xsum, T, E, st)))
@@ -478,14 +489,16 @@ static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st
             if ((rc = gemma_linear(m, b.k, m->qkv + QD, QKV, T, st))) return rc;
             if ((rc = gemma_linear(m, b.v, m->qkv + QD + KD, QKV, T, st))) return rc;
         }
-        if ((rc = launch_qk_norm_rope_kv(m->qkv, b.q_norm_w, b.k_norm_w, m->freqs, m->k[l], m->v[l], m->d_state,
-                                         C.head, C.head_kv, D, C.rms_eps, T, QKV, st)))
+        if ((rc = launch_qk_norm_rope_kv(m->qkv, b.q_norm_w, b.k_norm_w, m->freqs, m->k[l] + slot, m->v[l] + slot,
+                                         m->d_state, C.head, C.head_kv, D, C.rms_eps, T, QKV, row_pos, cache_stride,
+                                         st)))
             return rc;
         const bool global = (l % C.global_every) == C.global_every - 1;
         const uint32_t window = global ? 0u : C.sliding_window;
         const uint32_t max_len = (window && window < C.ctx) ? window : C.ctx;
-        if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], nullptr, nullptr, nullptr, m->xq, m->xscale, m->xsum,
-                                        m->scores, C.head, C.head_kv, D, m->d_state, window, max_len, 0, T, QKV, st)))
+        if ((rc = launch_attention_step(m->qkv, m->k[l] + slot, m->v[l] + slot, nullptr, nullptr, nullptr, m->xq,
+                                        m->xscale, m->xsum, m->scores, C.head, C.head_kv, D, m->d_state, window, max_len,
+                                        0, T, QKV, row_pos, cache_stride, st)))
             return rc;
         if ((rc = gemma_linear(m, b.o, m->proj, E, T, st))) return rc;
         if ((rc = launch_norm_quant(m->proj, b.post_attn_norm_w, m->x, b.ffn_norm_w, E, C.rms_eps, m->xq,
@@ -510,7 +523,9 @@ static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st
             return rc;
         }
     }
-    if (variant != STEP_CACHE_ONLY) {  // the last row's logits
+    if (variant != STEP_CACHE_ONLY && batch) {  // every sequence's logits
+        if ((rc = gemma_linear(m, m->token_embd, m->logits_batch, C.vocab, T, st))) return rc;
+    } else if (variant != STEP_CACHE_ONLY) {  // the last row's logits
         const zq_weight* w = m->token_embd;
         const size_t r = T - 1;
         if ((rc = launch_gemv_q8(w, m->xq + r * w->in_dim, m->xscale + r * w->nb, m->xsum + r * w->nb, m->logits, 1,
@@ -559,7 +574,12 @@ extern "C" {
 
 int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq_stream stream,
                      zq_gemma3** out) {
-    if (!cfg || !w || !out || !w->blocks) return ZQ_ERR_BAD_ARG;
+    return zq_gemma3_create_batch(cfg, w, 1, stream, out);
+}
+
+int zq_gemma3_create_batch(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, uint32_t n_seq,
+                           zq_stream stream, zq_gemma3** out) {
+    if (!cfg || !w || !out || !w->blocks || n_seq == 0 || n_seq > 1024) return ZQ_ERR_BAD_ARG;
     *out = nullptr;
     const zq_gemma3_config& C = *cfg;
     if (!C.vocab || !C.embed || !C.head || !C.head_kv || !C.head_dim || !C.layer || !C.ctx || !C.ffn ||
@@ -573,6 +593,8 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
     zq_gemma3* m = new (std::nothrow) zq_gemma3;
     if (!m) return ZQ_ERR_NO_MEM;
     m->c = C;
+    m->n_seq = n_seq;
+    m->seq_lens.assign(n_seq, 0);
     m->graphs.disabled = getenv("ZQ_NO_GRAPH") != nullptr;
     cudaStream_t st = as_stream(stream);
     int rc = ZQ_OK;
@@ -628,10 +650,10 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
             TRY(up_q(&b.up, s.ffn_up_weight, F, E));
         }
         TRY(up_q(&b.down, s.ffn_down_weight, E, F));
-        TRY(m->arena.alloc_n(&m->k[l], (size_t)C.ctx * KD));
-        TRY(m->arena.alloc_n(&m->v[l], (size_t)C.ctx * KD));
-        cudaMemsetAsync(m->k[l], 0, (size_t)C.ctx * KD * sizeof(float), st);
-        cudaMemsetAsync(m->v[l], 0, (size_t)C.ctx * KD * sizeof(float), st);
+        TRY(m->arena.alloc_n(&m->k[l], (size_t)n_seq * C.ctx * KD));  // one cache slot per sequence
+        TRY(m->arena.alloc_n(&m->v[l], (size_t)n_seq * C.ctx * KD));
+        cudaMemsetAsync(m->k[l], 0, (size_t)n_seq * C.ctx * KD * sizeof(float), st);
+        cudaMemsetAsync(m->v[l], 0, (size_t)n_seq * C.ctx * KD * sizeof(float), st);
     }
     {
         std::vector<float> hf(D / 2);
@@ -647,7 +669,10 @@ int zq_gemma3_create(const zq_gemma3_config* cfg, const zq_gemma3_weights* w, zq
     }
     // activation buffers hold a prefill chunk of up to 128 tokens (a decode step uses row 0)
     m->max_rows = C.ctx < 128 ? C.ctx : 128;
+    if (m->max_rows < n_seq) m->max_rows = n_seq;
     const size_t R = m->max_rows;
+    TRY(m->arena.alloc_n(&m->d_pos, n_seq));
+    if (n_seq > 1) TRY(m->arena.alloc_n(&m->logits_batch, (size_t)n_seq * C.vocab));
     TRY(m->arena.alloc_n(&m->x, R * E));
     TRY(m->arena.alloc_n(&m->qkv, R * ((size_t)QD + 2 * KD)));
     TRY(m->arena.alloc_n(&m->proj, R * E));
@@ -691,35 +716,71 @@ int zq_gemma3_seq_len(const zq_gemma3* m, uint32_t* seq_len) {
 
 int zq_gemma3_prefill(zq_gemma3* m, const uint32_t* h_tokens, uint32_t n, zq_stream stream,
                       const float** d_logits) {
-    if (!m || !h_tokens || !d_logits) return ZQ_ERR_BAD_ARG;
+    return zq_gemma3_prefill_seq(m, 0, h_tokens, n, stream, d_logits);
+}
+
+int zq_gemma3_prefill_seq(zq_gemma3* m, uint32_t seq, const uint32_t* h_tokens, uint32_t n, zq_stream stream,
+                          const float** d_logits) {
+    if (!m || !h_tokens || !d_logits || seq >= m->n_seq) return ZQ_ERR_BAD_ARG;
     if (n == 0 || n > m->c.ctx) return ZQ_ERR_SEQUENCE;
     for (uint32_t t = 0; t < n; ++t)
         if (h_tokens[t] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
-    m->seq_len = 0;
+    m->seq_lens[seq] = 0;
+    if (seq == 0) m->seq_len = 0;
     // chunks of up to max_rows tokens, each a batched forward pass (every row = the arithmetic of a decode step)
-    for (uint32_t t0 = 0; t0 < n; t0 += m->max_rows) {
-        const uint32_t T = n - t0 < m->max_rows ? n - t0 : m->max_rows;
+    const uint32_t chunk = m->c.ctx < 128 ? m->c.ctx : 128;
+    for (uint32_t t0 = 0; t0 < n; t0 += chunk) {
+        const uint32_t T = n - t0 < chunk ? n - t0 : chunk;
         const bool last = t0 + T == n;
         set_state_kernel<<<1, 1, 0, st>>>(m->d_state, h_tokens[t0], t0, 0);
         ZQ_LAUNCH_CHECK();
         int rc;
-        if (T == 1) {
+        if (T == 1 && m->n_seq == 1) {
             rc = gemma3_run(m, last ? STEP_LOGITS : STEP_CACHE_ONLY, st);
+        } else if (T == 1) {
+            rc = gemma3_forward(m, 1, last ? STEP_LOGITS : STEP_CACHE_ONLY, st, seq);
         } else {
             ZQ_CUDA(cudaMemcpyAsync(m->d_tokens, h_tokens + t0, T * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
-            rc = gemma3_forward(m, T, last ? STEP_LOGITS : STEP_CACHE_ONLY, st);
+            rc = gemma3_forward(m, T, last ? STEP_LOGITS : STEP_CACHE_ONLY, st, seq);
             ZQ_CUDA(cudaStreamSynchronize(st));  // h_tokens is the caller's memory
         }
         if (rc != ZQ_OK) return rc;
     }
-    m->seq_len = n;
+    m->seq_lens[seq] = n;
+    if (seq == 0) m->seq_len = n;
     *d_logits = m->logits;
     return ZQ_OK;
 }
 
+int zq_gemma3_seq_len_of(const zq_gemma3* m, uint32_t seq, uint32_t* seq_len) {
+    if (!m || !seq_len || seq >= m->n_seq) return ZQ_ERR_BAD_ARG;
+    *seq_len = m->seq_lens[seq];
+    return ZQ_OK;
+}
+
+// One decode step for every sequence at once: row r = sequence r, its next token h_tokens[r] at its own
+// position; the linears run as exact int8 GEMMs over the n_seq rows. Logits: [n_seq][vocab].
+int zq_gemma3_decode_next_batch(zq_gemma3* m, const uint32_t* h_tokens, zq_stream stream, const float** d_logits) {
+    if (!m || !h_tokens || !d_logits || m->n_seq < 2) return ZQ_ERR_BAD_ARG;
+    for (uint32_t r = 0; r < m->n_seq; ++r) {
+        if (h_tokens[r] >= m->c.vocab) return ZQ_ERR_BAD_ARG;
+        if (m->seq_lens[r] >= m->c.ctx) return ZQ_ERR_SEQUENCE;
+    }
+    cudaStream_t st = as_stream(stream);
+    ZQ_CUDA(cudaMemcpyAsync(m->d_tokens, h_tokens, m->n_seq * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
+    ZQ_CUDA(cudaMemcpyAsync(m->d_pos, m->seq_lens.data(), m->n_seq * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
+    ZQ_CUDA(cudaStreamSynchronize(st));  // both sources are host memory that changes below / belongs to the caller
+    int rc = gemma3_forward(m, m->n_seq, STEP_LOGITS, st, 0, true);
+    if (rc != ZQ_OK) return rc;
+    for (uint32_t r = 0; r < m->n_seq; ++r) m->seq_lens[r] += 1;
+    m->seq_len = m->seq_lens[0];
+    *d_logits = m->logits_batch;
+    return ZQ_OK;
+}
+
 int zq_gemma3_decode_next(zq_gemma3* m, uint32_t token, zq_stream stream, const float** d_logits) {
-    if (!m || !d_logits) return ZQ_ERR_BAD_ARG;
+    if (!m || !d_logits || m->n_seq != 1) return ZQ_ERR_BAD_ARG;
     if (m->seq_len >= m->c.ctx) return ZQ_ERR_SEQUENCE;
     if (token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
@@ -734,7 +795,7 @@ int zq_gemma3_decode_next(zq_gemma3* m, uint32_t token, zq_stream stream, const 
 
 int zq_gemma3_decode_greedy(zq_gemma3* m, uint32_t first_token, uint32_t n_steps, zq_stream stream,
                             uint32_t* h_tokens_out) {
-    if (!m || !h_tokens_out) return ZQ_ERR_BAD_ARG;
+    if (!m || !h_tokens_out || m->n_seq != 1) return ZQ_ERR_BAD_ARG;
     if (n_steps == 0) return ZQ_OK;
     if ((uint64_t)m->seq_len + n_steps > m->c.ctx) return ZQ_ERR_SEQUENCE;
     if (first_token >= m->c.vocab) return ZQ_ERR_BAD_ARG;

@@ -466,13 +466,20 @@ __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_kernel(float* __restrict__ qkv, const float* __restrict__ q_norm_w,
                        const float* __restrict__ k_norm_w, const float* __restrict__ freqs,
                        float* __restrict__ kc, float* __restrict__ vc, const uint32_t* __restrict__ state,
-                       uint32_t n_head, uint32_t n_kv_head, uint32_t head_dim, float eps, uint32_t qkv_stride) {
+                       uint32_t n_head, uint32_t n_kv_head, uint32_t head_dim, float eps, uint32_t qkv_stride,
+                       const uint32_t* __restrict__ row_pos, size_t cache_stride) {
     extern __shared__ __align__(16) float xs[];
     __shared__ float bc;
     pdl_launch_dependents();
     pdl_wait();
-    const uint32_t pos = state[1] + blockIdx.y;  // blockIdx.y: token of a batched prefill (0 when decoding)
+    // blockIdx.y: a token of a batched prefill (position state[1] + row, one cache), or — row_pos given —
+    // one of several independent sequences (own position, own cache cache_stride floats further)
+    const uint32_t pos = row_pos ? row_pos[blockIdx.y] : state[1] + blockIdx.y;
     qkv += (size_t)blockIdx.y * qkv_stride;
+    if (row_pos) {
+        kc += (size_t)blockIdx.y * cache_stride;
+        vc += (size_t)blockIdx.y * cache_stride;
+    }
     const uint32_t b = blockIdx.x, kv_dim = n_kv_head * head_dim;
     if (b >= n_head + n_kv_head) {  // v head: copy
         const uint32_t hv = b - n_head - n_kv_head;
@@ -520,8 +527,8 @@ gelu_mul_quant_kernel(const float* __restrict__ gate, const float* __restrict__ 
 
 // The window a decode step attends to: positions [kv_start, pos]; `window` = 0 means all of them.
 __device__ __forceinline__ void step_window(const uint32_t* state, uint32_t window, uint32_t* kv_start,
-                                            uint32_t* kv_len, uint32_t token = 0) {
-    const uint32_t end = state[1] + token + 1;
+                                            uint32_t* kv_len, uint32_t token = 0, const uint32_t* row_pos = nullptr) {
+    const uint32_t end = (row_pos ? row_pos[token] : state[1] + token) + 1;
     const uint32_t len = (window && end > window) ? window : end;
     *kv_start = end - len;
     *kv_len = len;
@@ -534,14 +541,19 @@ attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc
                              const float* __restrict__ k_new, const float* __restrict__ v_new,
                              float* __restrict__ scores, uint32_t n_head, uint32_t n_kv_head,
                              uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window,
-                             uint32_t q_stride, uint32_t scores_stride) {
+                             uint32_t q_stride, uint32_t scores_stride, const uint32_t* __restrict__ row_pos,
+                             size_t cache_stride) {
     __shared__ float part[16][17];
     pdl_launch_dependents();
     pdl_wait();
     uint32_t kv_start, kv_len;
-    step_window(state, window, &kv_start, &kv_len, blockIdx.z);  // blockIdx.z: token of a batched prefill
+    step_window(state, window, &kv_start, &kv_len, blockIdx.z, row_pos);  // blockIdx.z: token or sequence
     q += (size_t)blockIdx.z * q_stride;
     scores += (size_t)blockIdx.z * scores_stride;
+    if (row_pos) {
+        kc += (size_t)blockIdx.z * cache_stride;
+        vc += (size_t)blockIdx.z * cache_stride;
+    }
     const uint32_t h = blockIdx.y;
     const uint32_t kvh = h / (n_head / n_kv_head);
     const uint32_t kv_dim = n_kv_head * head_dim;
@@ -593,7 +605,8 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
                                 float* __restrict__ out, int8_t* __restrict__ oq, float* __restrict__ oscale,
                                 int32_t* __restrict__ osum, uint32_t n_head, uint32_t n_kv_head,
                                 uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window,
-                                int gpt2_tail, uint32_t scores_stride) {
+                                int gpt2_tail, uint32_t scores_stride, const uint32_t* __restrict__ row_pos,
+                                size_t cache_stride) {
     extern __shared__ __align__(16) float w[];  // max window length
     __shared__ float vt[kAttnTile][kAttnDims];
     __shared__ float red[33];
@@ -601,8 +614,9 @@ attention_softmax_v_step_kernel(const float* __restrict__ scores, const float* _
     pdl_launch_dependents();
     pdl_wait();
     uint32_t kv_start, kv_len;
-    step_window(state, window, &kv_start, &kv_len, blockIdx.z);  // blockIdx.z: token of a batched prefill
+    step_window(state, window, &kv_start, &kv_len, blockIdx.z, row_pos);  // blockIdx.z: token or sequence
     scores += (size_t)blockIdx.z * scores_stride;
+    if (row_pos) vc += (size_t)blockIdx.z * cache_stride;
     const size_t out_row = (size_t)blockIdx.z * n_head * head_dim;
     const uint32_t h = blockIdx.x;
     const uint32_t kvh = h / (n_head / n_kv_head);
@@ -732,12 +746,13 @@ int launch_norm_quant(const float* src, const float* w1, float* res, const float
 
 int launch_qk_norm_rope_kv(float* qkv, const float* q_norm_w, const float* k_norm_w, const float* freqs,
                            float* kc, float* vc, const uint32_t* state, uint32_t n_head, uint32_t n_kv_head,
-                           uint32_t head_dim, float eps, uint32_t rows, uint32_t qkv_stride, cudaStream_t st) {
+                           uint32_t head_dim, float eps, uint32_t rows, uint32_t qkv_stride, const uint32_t* row_pos,
+                           size_t cache_stride, cudaStream_t st) {
     if (head_dim % 2 || head_dim > 48 * 1024 / 4) return ZQ_ERR_LIMIT;
     if (rows == 0) return ZQ_OK;
     ZQ_CUDA(launch_pdl(qk_norm_rope_kv_kernel, dim3(n_head + 2 * n_kv_head, rows), dim3(128), head_dim * sizeof(float),
                        st, qkv, q_norm_w, k_norm_w, freqs, kc, vc, state, n_head, n_kv_head, head_dim, eps,
-                       qkv_stride));
+                       qkv_stride, row_pos, cache_stride));
     return ZQ_OK;
 }
 
@@ -754,7 +769,8 @@ int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t
 int launch_attention_step(const float* q, float* kc, float* vc, const float* k_new, const float* v_new,
                           float* out, int8_t* oq, float* oscale, int32_t* osum, float* scores, uint32_t n_head,
                           uint32_t n_kv_head, uint32_t head_dim, const uint32_t* state, uint32_t window,
-                          uint32_t max_len, int flags, uint32_t rows, uint32_t q_stride, cudaStream_t st) {
+                          uint32_t max_len, int flags, uint32_t rows, uint32_t q_stride, const uint32_t* row_pos,
+                          size_t cache_stride, cudaStream_t st) {
     if (max_len == 0 || max_len > 180 * 1024 / 4) return ZQ_ERR_LIMIT;
     if (oq && head_dim % 32) return ZQ_ERR_BAD_ARG;
     if (rows == 0) return ZQ_OK;
@@ -763,7 +779,8 @@ int launch_attention_step(const float* q, float* kc, float* vc, const float* k_n
     const int tail = (flags & ZQ_ATTN_GPT2_SOFTMAX) ? 1 : 0;
     const uint32_t scores_stride = n_head * max_len;
     ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head, rows), dim3(256), 0, st, q, kc,
-                       vc, k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window, q_stride, scores_stride));
+                       vc, k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window, q_stride, scores_stride,
+                       row_pos, cache_stride));
     const dim3 grid(n_head, (head_dim + kAttnDims - 1) / kAttnDims, rows);
     if (oq) {
         auto kern = attention_softmax_v_step_kernel<true>;
@@ -771,14 +788,14 @@ int launch_attention_step(const float* q, float* kc, float* vc, const float* k_n
             ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         ZQ_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, static_cast<const float*>(scores),
                            static_cast<const float*>(vc), out, oq, oscale, osum, n_head, n_kv_head, head_dim, state,
-                           window, tail, scores_stride));
+                           window, tail, scores_stride, row_pos, cache_stride));
     } else {
         auto kern = attention_softmax_v_step_kernel<false>;
         if (smem > 24 * 1024)
             ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         ZQ_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, static_cast<const float*>(scores),
                            static_cast<const float*>(vc), out, nullptr, nullptr, nullptr, n_head, n_kv_head, head_dim,
-                           state, window, tail, scores_stride));
+                           state, window, tail, scores_stride, row_pos, cache_stride));
     }
     return ZQ_OK;
 }

@@ -143,8 +143,9 @@ size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows);
 // state[1] = its position. Kernels read the position there, so a captured launch sequence can be
 // replayed for every step.
 
-// `rows` > 1 (batched prefill): row r is token r of the batch at position state[1] + r; inputs of row r
-// start r * <stride> floats further, quantised outputs are dense [rows][dim].
+// `rows` > 1: row r is token r of a prefill chunk at position state[1] + r, or — row_pos != nullptr — one
+// of several independent sequences at position row_pos[r] with its own cache cache_stride floats
+// further. Inputs of row r start r * <stride> floats further, quantised outputs are dense [rows][dim].
 // res == nullptr: quantise rms_norm(src, w1).  Otherwise res += rms_norm(src, w1) and quantise
 // rms_norm(res, w2).
 int launch_norm_quant(const float* src, const float* w1, float* res, const float* w2, uint32_t dim, float eps,
@@ -152,7 +153,8 @@ int launch_norm_quant(const float* src, const float* w1, float* res, const float
 // qkv = [q heads | k heads | v heads]; q is normalised and rotated in place, k and v go to the caches.
 int launch_qk_norm_rope_kv(float* qkv, const float* q_norm_w, const float* k_norm_w, const float* freqs,
                            float* kc, float* vc, const uint32_t* state, uint32_t n_head, uint32_t n_kv_head,
-                           uint32_t head_dim, float eps, uint32_t rows, uint32_t qkv_stride, cudaStream_t st);
+                           uint32_t head_dim, float eps, uint32_t rows, uint32_t qkv_stride, const uint32_t* row_pos,
+                           size_t cache_stride, cudaStream_t st);
 int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t* q, float* scale,
                           int32_t* sum, uint32_t rows, uint32_t in_stride, cudaStream_t st);
 // Single-query attention over positions [max(0, pos + 1 - window), pos] (window 0 = all); max_len is the
@@ -162,7 +164,8 @@ int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t
 int launch_attention_step(const float* q, float* kc, float* vc, const float* k_new, const float* v_new,
                           float* out, int8_t* oq, float* oscale, int32_t* osum, float* scores, uint32_t n_head,
                           uint32_t n_kv_head, uint32_t head_dim, const uint32_t* state, uint32_t window,
-                          uint32_t max_len, int flags, uint32_t rows, uint32_t q_stride, cudaStream_t st);
+                          uint32_t max_len, int flags, uint32_t rows, uint32_t q_stride, const uint32_t* row_pos,
+                          size_t cache_stride, cudaStream_t st);
 // f32 matvec (GPT-2 vocabulary head) with an optional LayerNorm of x in the prologue (gemv.cu).
 int launch_matvec_ln_f32(const float* w, const float* x, float* y, uint32_t out_dim, uint32_t in_dim,
                          const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st);
