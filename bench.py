@@ -310,6 +310,32 @@ def run_case(args):
     import zignn_b200
     from zignn_b200 import api as zq
     from zignn_b200 import ggml
+    if args.case.startswith("batch:"):
+        # batch:<gemma3_1b_q4_1|gemma3_1b_q8_0>,<sequences>,<prompt tokens>,<decode steps>
+        import numpy as np
+        from zignn_b200 import hostmodel
+        name, n_seq, n_prompt, n_steps = args.case[6:].split(",")
+        n_seq, n_prompt, n_steps = int(n_seq), int(n_prompt), int(n_steps)
+        qt = ggml.Q4_1 if name.endswith("q4_1") else ggml.Q8_0
+        host = hostmodel.Gemma3Host.synthetic(hostmodel.GEMMA3_1B, qtype=qt, seed=42, device="cuda")
+        eng = zq.Gemma3Batch(host, n_seq)
+        rng = np.random.default_rng(44)
+        toks = []
+        t0 = time.perf_counter()
+        for i in range(n_seq):
+            toks.append(int(eng.prefill(i, rng.integers(0, hostmodel.GEMMA3_1B["vocab"], size=n_prompt)).argmax().item()))
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        toks = eng.decode_next(toks).argmax(dim=1).cpu().numpy()  # first call: one-time set-up
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        for _ in range(n_steps):
+            toks = eng.decode_next(toks).argmax(dim=1).cpu().numpy()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t2
+        print(json.dumps({"case": args.case, "tok_s_all_sequences": n_seq * n_steps / dt, "ms_per_step": dt / n_steps * 1e3,
+                          "prefill_ms_per_sequence": (t1 - t0) / n_seq * 1e3}), flush=True)
+        return
     if args.case.startswith("decode:"):
         # decode:<gpt2_small_q4_0|gemma3_1b_q8_0>,<prompt tokens>,<greedy steps>
         import numpy as np

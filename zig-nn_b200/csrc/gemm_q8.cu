@@ -114,37 +114,56 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     const uint32_t frag_lo = ((uint32_t)g * 2 + (0u ^ swap)) * 16 + t * 4;   // word t
     const uint32_t frag_hi = ((uint32_t)g * 2 + (1u ^ swap)) * 16 + t * 4;   // word 4 + t
 
+    // this lane's packed words and raw scales of one quad; the next quad's are loaded while the current one
+    // is being multiplied
+    struct QuadW {
+        uint4 wa, wb, wa2, wb2, sa4, sb4;
+    };
+    auto load_quad = [&](QuadW& d, uint32_t q) {
+        d.wa = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD));
+        d.wb = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD));
+        if (Q8) {
+            d.wa2 = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD + 64));
+            d.wb2 = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD + 64));
+        }
+        if (Q41) {
+            d.sa4 = __ldg(reinterpret_cast<const uint4*>(sa) + q);
+            d.sb4 = __ldg(reinterpret_cast<const uint4*>(sb) + q);
+        } else {
+            const uint2 va = __ldg(reinterpret_cast<const uint2*>(sa) + q);
+            const uint2 vb = __ldg(reinterpret_cast<const uint2*>(sb) + q);
+            d.sa4.x = va.x; d.sa4.y = va.y;
+            d.sb4.x = vb.x; d.sb4.y = vb.y;
+        }
+    };
+    QuadW cur, nxt;
+    load_quad(cur, 0);
     issue(0, 0);
     for (uint32_t q = 0; q < nq; ++q) {
         const uint32_t stage = q & 1u;
-        if (q + 1 < nq) issue(stage ^ 1u, q + 1);
-        else asm volatile("cp.async.commit_group;" ::: "memory");
-        // this quad's weights
-        const uint4 wa = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD));
-        const uint4 wb = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD));
-        uint4 wa2 = wa, wb2 = wb;
-        if (Q8) {
-            wa2 = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD + 64));
-            wb2 = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD + 64));
+        if (q + 1 < nq) {
+            issue(stage ^ 1u, q + 1);
+            load_quad(nxt, q + 1);
+        } else {
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
+        const uint4 wa = cur.wa, wb = cur.wb;
+        const uint4 wa2 = Q8 ? cur.wa2 : cur.wa, wb2 = Q8 ? cur.wb2 : cur.wb;
         float da[4], db[4], ma[4], mb[4];
         if (Q41) {
-            const uint4 va = __ldg(reinterpret_cast<const uint4*>(sa) + q);
-            const uint4 vb = __ldg(reinterpret_cast<const uint4*>(sb) + q);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&reinterpret_cast<const uint32_t*>(&va)[b]));
-                const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&reinterpret_cast<const uint32_t*>(&vb)[b]));
+                const uint32_t ua = pick4(cur.sa4, b), ub = pick4(cur.sb4, b);
+                const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&ua));
+                const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&ub));
                 da[b] = fa.x; ma[b] = fa.y;
                 db[b] = fb.x; mb[b] = fb.y;
             }
         } else {
-            const uint2 va = __ldg(reinterpret_cast<const uint2*>(sa) + q);
-            const uint2 vb = __ldg(reinterpret_cast<const uint2*>(sb) + q);
-            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&va.x));
-            const float2 a23 = __half22float2(*reinterpret_cast<const __half2*>(&va.y));
-            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&vb.x));
-            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&vb.y));
+            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&cur.sa4.x));
+            const float2 a23 = __half22float2(*reinterpret_cast<const __half2*>(&cur.sa4.y));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&cur.sb4.x));
+            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&cur.sb4.y));
             da[0] = a01.x; da[1] = a01.y; da[2] = a23.x; da[3] = a23.y;
             db[0] = b01.x; db[1] = b01.y; db[2] = b23.x; db[3] = b23.y;
 #pragma unroll
@@ -197,6 +216,7 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
             }
         }
         __syncthreads();  // the stage is overwritten by the copies issued in the next iteration
+        cur = nxt;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
 
@@ -239,7 +259,11 @@ int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int3
     if (big >= sms) return launch_cfg<TYPE, 8, 8>(w, xq, xs, xsum, y, M, ep, st);
     const uint64_t mid = (uint64_t)((w->out_dim + 31) / 32) * ((M + 63) / 64);
     if (mid >= sms) return launch_cfg<TYPE, 2, 8>(w, xq, xs, xsum, y, M, ep, st);
-    return launch_cfg<TYPE, 2, 2>(w, xq, xs, xsum, y, M, ep, st);
+    // few weight rows: the running sums are a serial chain over K per output, so only more (smaller) warps
+    // tiles shorten the launch
+    const uint64_t small = (uint64_t)((w->out_dim + 31) / 32) * ((M + 15) / 16);
+    if (small >= 2 * sms) return launch_cfg<TYPE, 2, 2>(w, xq, xs, xsum, y, M, ep, st);
+    return launch_cfg<TYPE, 1, 1>(w, xq, xs, xsum, y, M, ep, st);
 }
 
 }  // namespace
