@@ -82,11 +82,11 @@ __global__ void greedy_feed_kernel(uint32_t* state, const int32_t* arg, uint32_t
 // attributes get set and launch errors surface outside capture); the second captures on the
 // engine's own stream (the caller's may be the legacy default stream, which cannot capture); every
 // use from then on is one graph launch on the caller's stream.
-enum StepVariant { STEP_CACHE_ONLY = 0, STEP_LOGITS = 1, STEP_GREEDY = 2, STEP_VARIANTS = 3 };
+enum StepVariant { STEP_CACHE_ONLY = 0, STEP_LOGITS = 1, STEP_GREEDY = 2, STEP_BATCH = 3, STEP_VARIANTS = 4 };
 
 struct StepGraphs {
-    cudaGraphExec_t exec[STEP_VARIANTS] = {nullptr, nullptr, nullptr};
-    bool warmed[STEP_VARIANTS] = {false, false, false};
+    cudaGraphExec_t exec[STEP_VARIANTS] = {nullptr, nullptr, nullptr, nullptr};
+    bool warmed[STEP_VARIANTS] = {false, false, false, false};
     cudaStream_t capture_stream = nullptr;
     bool disabled = false;
     ~StepGraphs() {
@@ -771,7 +771,8 @@ int zq_gemma3_decode_next_batch(zq_gemma3* m, const uint32_t* h_tokens, zq_strea
     ZQ_CUDA(cudaMemcpyAsync(m->d_tokens, h_tokens, m->n_seq * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
     ZQ_CUDA(cudaMemcpyAsync(m->d_pos, m->seq_lens.data(), m->n_seq * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
     ZQ_CUDA(cudaStreamSynchronize(st));  // both sources are host memory that changes below / belongs to the caller
-    int rc = gemma3_forward(m, m->n_seq, STEP_LOGITS, st, 0, true);
+    // tokens and positions live in device memory: the launch sequence is the same every step and is replayed
+    int rc = m->graphs.run(STEP_BATCH, st, [&](cudaStream_t s2) { return gemma3_forward(m, m->n_seq, STEP_LOGITS, s2, 0, true); });
     if (rc != ZQ_OK) return rc;
     for (uint32_t r = 0; r < m->n_seq; ++r) m->seq_lens[r] += 1;
     m->seq_len = m->seq_lens[0];
