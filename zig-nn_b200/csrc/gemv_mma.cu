@@ -23,8 +23,6 @@
 namespace zq {
 namespace {
 
-constexpr int kMaxCols = 4;  // column sets of 8 MMA columns = 4 activation rows (hi, lo) each
-
 // Per-call options: the output epilogue and, for one activation row, an optional LayerNorm applied to
 // the row before the product (ln_gamma != nullptr; two-pass mean / variance as gpt2.zig:541-596).
 struct EpilogueArgs {
@@ -60,11 +58,6 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
           "f"(c[3]));
 }
 
-__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
 __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -285,12 +278,6 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
 
 __device__ __forceinline__ uint32_t pick(const uint4& v, int j) {
     return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
-}
-__device__ __forceinline__ float half_lo(uint32_t v) {
-    return __half2float(__ushort_as_half((unsigned short)(v & 0xFFFFu)));
-}
-__device__ __forceinline__ float half_hi(uint32_t v) {
-    return __half2float(__ushort_as_half((unsigned short)(v >> 16)));
 }
 
 __device__ __forceinline__ void unpack_half2(uint32_t v, float& lo, float& hi) {
