@@ -345,11 +345,14 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
             if (round > 0) alive = mbar_wait(empty_bar(slot), (round - 1) & 1u, abort_p, err_word);
             if (!alive) break;
             const uint32_t a_tile = smem32 + slot * TC_STAGE_BYTES, b_tile = a_tile + TC_A_BYTES;
-            if (tid == 0) {
-                // the stage's activation tile: n_mma rows x 128 bytes, contiguous in the converted image
-                const uint32_t bytes = n_mma * 128u;
+            if ((tid & 31) == 0 && warp < 8) {
+                // the stage's activation tile: n_mma rows x 128 bytes, contiguous in the converted image; eight
+                // threads (one per warp) copy an eighth each so that several transfers are in flight
+                const uint32_t bytes = n_mma * 16u;  // n_mma is a multiple of 64: a multiple of 1024 bytes
+                const uint32_t off = warp * bytes;
                 mbar_expect_tx(full_bar(slot), bytes);
-                bulk_copy_g2s(b_tile, xt + ((size_t)s * m_pad + m0) * 64, bytes, full_bar(slot));
+                bulk_copy_g2s(b_tile + off, reinterpret_cast<const unsigned char*>(xt + ((size_t)s * m_pad + m0) * 64) + off,
+                              bytes, full_bar(slot));
             }
             if ((s & 1u) == 0) {
                 store_dequant<TYPE, 0>(pk, a_tile, prow, phalf, pjj);
