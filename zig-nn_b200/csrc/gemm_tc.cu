@@ -14,7 +14,7 @@
 //   D          = 128 lanes x N columns of f32 in tensor memory (one lane per weight row).
 //
 // Roles: warps 0-15 produce stages (dequantise) and later drain the accumulator; one thread of
-// warp 16 issues the MMAs. Stages are handed over through mbarriers: full[s] (256 producer arrivals),
+// warp 16 issues the MMAs. Stages are handed over through mbarriers: full[s] (one arrival per producer warp),
 // empty[s] (tcgen05.commit when the MMAs that read the stage are done), acc (last commit). Every wait
 // is bounded; on a timeout the kernel records it in the library's device-error word, stops using
 // the pipeline, still releases tensor memory and returns (outputs are then undefined; zq_device_error
@@ -309,7 +309,7 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
 
     if (tid == 0) {
         for (uint32_t s = 0; s < TC_STAGES; ++s) {
-            mbar_init(full_bar(s), TC_PRODUCERS);
+            mbar_init(full_bar(s), TC_PRODUCERS / 32);  // one arrival per producer warp
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(acc_bar, 1);
@@ -363,7 +363,8 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
                 if (q_ahead < n_quads) load_packed<TYPE>(pk_next, qrow, srow, q_ahead, phalf);
             }
             fence_proxy_async();  // generic-proxy writes (st.shared) -> visible to the tensor core
-            mbar_arrive(full_bar(slot));
+            __syncwarp();         // every lane's stores and fence precede the warp's single arrival
+            if (lane == 0) mbar_arrive(full_bar(slot));  // 16 arrivals per stage instead of 512 serialised ones
         }
 
         // ================= epilogue: drain tensor memory =================
