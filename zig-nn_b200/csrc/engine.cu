@@ -216,7 +216,7 @@ static int gpt2_forward(zq_gpt2* m, uint32_t T, int variant, cudaStream_t st) {
         }
         if ((rc = launch_attention_step(m->qkv, m->k[l], m->v[l], k_new, v_new, m->att, nullptr, nullptr, nullptr,
                                         m->scores, C.head, C.head, hd, m->d_state, 0, C.ctx, ZQ_ATTN_GPT2_SOFTMAX, T,
-                                        3 * E, nullptr, 0, st)))
+                                        3 * E, nullptr, 0, nullptr, nullptr, nullptr, 0.0f, st)))
             return rc;
         if ((rc = gpt2_linear(m, b.proj, m->att, m->x, b.proj_b, 0, m->x, nullptr, nullptr, T, st))) return rc;
         if ((rc = gpt2_linear(m, b.fc, m->x, m->hid, b.fc_b, 1, nullptr, b.ln2_w, b.ln2_b, T, st))) return rc;
@@ -489,16 +489,24 @@ static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st
             if ((rc = gemma_linear(m, b.k, m->qkv + QD, QKV, T, st))) return rc;
             if ((rc = gemma_linear(m, b.v, m->qkv + QD + KD, QKV, T, st))) return rc;
         }
-        if ((rc = launch_qk_norm_rope_kv(m->qkv, b.q_norm_w, b.k_norm_w, m->freqs, m->k[l] + slot, m->v[l] + slot,
-                                         m->d_state, C.head, C.head_kv, D, C.rms_eps, T, QKV, row_pos, cache_stride,
-                                         st)))
-            return rc;
         const bool global = (l % C.global_every) == C.global_every - 1;
         const uint32_t window = global ? 0u : C.sliding_window;
         const uint32_t max_len = (window && window < C.ctx) ? window : C.ctx;
-        if ((rc = launch_attention_step(m->qkv, m->k[l] + slot, m->v[l] + slot, nullptr, nullptr, nullptr, m->xq,
-                                        m->xscale, m->xsum, m->scores, C.head, C.head_kv, D, m->d_state, window, max_len,
-                                        0, T, QKV, row_pos, cache_stride, st)))
+        // A prefill chunk needs every token's key in the cache before any score: separate launch. A decode
+        // step (one row, or one row per independent sequence) normalises / rotates q and its own new key
+        // inside the scores kernel, which also stores the cache row.
+        const bool fused_qk = T == 1 || batch;
+        if (!fused_qk) {
+            if ((rc = launch_qk_norm_rope_kv(m->qkv, b.q_norm_w, b.k_norm_w, m->freqs, m->k[l] + slot, m->v[l] + slot,
+                                             m->d_state, C.head, C.head_kv, D, C.rms_eps, T, QKV, row_pos,
+                                             cache_stride, st)))
+                return rc;
+        }
+        if ((rc = launch_attention_step(m->qkv, m->k[l] + slot, m->v[l] + slot, fused_qk ? m->qkv + QD : nullptr,
+                                        fused_qk ? m->qkv + QD + KD : nullptr, nullptr, m->xq, m->xscale, m->xsum,
+                                        m->scores, C.head, C.head_kv, D, m->d_state, window, max_len, 0, T, QKV, row_pos,
+                                        cache_stride, fused_qk ? b.q_norm_w : nullptr, b.k_norm_w, m->freqs, C.rms_eps,
+                                        st)))
             return rc;
         if ((rc = gemma_linear(m, b.o, m->proj, E, T, st))) return rc;
         if ((rc = launch_norm_quant(m->proj, b.post_attn_norm_w, m->x, b.ffn_norm_w, E, C.rms_eps, m->xq,

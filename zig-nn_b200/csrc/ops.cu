@@ -534,6 +534,17 @@ __device__ __forceinline__ void step_window(const uint32_t* state, uint32_t wind
     *kv_len = len;
 }
 
+// Optional per-head RMSNorm + RoPE of q and of this step's k inside the scores kernel (decode only): the
+// raw projection outputs come in, every CTA normalises and rotates the query head it needs (and the new
+// key, if it scores the current position or stores the cache row) with the arithmetic of
+// qk_norm_rope_kv_kernel, so that kernel's launch disappears from the step.
+struct QkNormRope {
+    const float* q_norm_w;  // nullptr: q and k_new are used as they are
+    const float* k_norm_w;
+    const float* freqs;
+    float eps;
+};
+
 // attention_scores_kernel with the window taken from the device-side position. The grid covers the
 // largest possible window; CTAs past the current one leave at once.
 __global__ void __launch_bounds__(256)
@@ -542,38 +553,84 @@ attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc
                              float* __restrict__ scores, uint32_t n_head, uint32_t n_kv_head,
                              uint32_t head_dim, const uint32_t* __restrict__ state, uint32_t window,
                              uint32_t q_stride, uint32_t scores_stride, const uint32_t* __restrict__ row_pos,
-                             size_t cache_stride) {
+                             size_t cache_stride, QkNormRope nr) {
     __shared__ float part[16][17];
+    __shared__ float inv2[2];
+    extern __shared__ __align__(16) float qk[];  // nr: normalised + rotated q head, then k head
     pdl_launch_dependents();
     pdl_wait();
     uint32_t kv_start, kv_len;
     step_window(state, window, &kv_start, &kv_len, blockIdx.z, row_pos);  // blockIdx.z: token or sequence
     q += (size_t)blockIdx.z * q_stride;
+    if (k_new) {
+        k_new += (size_t)blockIdx.z * q_stride;
+        v_new += (size_t)blockIdx.z * q_stride;
+    }
     scores += (size_t)blockIdx.z * scores_stride;
     if (row_pos) {
         kc += (size_t)blockIdx.z * cache_stride;
         vc += (size_t)blockIdx.z * cache_stride;
     }
     const uint32_t h = blockIdx.y;
-    const uint32_t kvh = h / (n_head / n_kv_head);
+    const uint32_t group = n_head / n_kv_head;
+    const uint32_t kvh = h / group;
     const uint32_t kv_dim = n_kv_head * head_dim;
     // k_new / v_new: this step's key and value rows are not in the caches yet. The first CTA of each kv
-    // head stores them (gpt2.zig:812-816); the score of the current position reads k_new directly.
+    // head stores them (gpt2.zig:812-816); the score of the current position reads the new key directly.
     const uint32_t pos = kv_start + kv_len - 1;
-    if (k_new != nullptr && blockIdx.x == 0 && h % (n_head / n_kv_head) == 0) {
+    const bool writer = k_new != nullptr && blockIdx.x == 0 && h % group == 0;
+    const bool in_window = blockIdx.x * 16 < kv_len;
+    if (!in_window && !writer) return;
+    const float* qh = q + (size_t)h * head_dim;
+    const float* knew = k_new ? k_new + (size_t)kvh * head_dim : nullptr;
+    if (nr.q_norm_w != nullptr) {
+        const bool need_k = writer || (in_window && blockIdx.x * 16 + 16 > kv_len - 1);
+        float* qn = qk;
+        float* kn = qk + head_dim;
         for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) {
-            kc[(size_t)pos * kv_dim + (size_t)kvh * head_dim + i] = k_new[(size_t)kvh * head_dim + i];
-            vc[(size_t)pos * kv_dim + (size_t)kvh * head_dim + i] = v_new[(size_t)kvh * head_dim + i];
+            qn[i] = qh[i];
+            if (need_k) kn[i] = knew[i];
+        }
+        __syncthreads();
+        // squares added one by one in index order (rms_norm_in_place), q by thread 0, k by thread 32
+        if (threadIdx.x == 0)
+            inv2[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq_sequential(qn, head_dim), (float)head_dim), nr.eps)));
+        if (threadIdx.x == 32 && need_k)
+            inv2[1] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq_sequential(kn, head_dim), (float)head_dim), nr.eps)));
+        __syncthreads();
+        const float fpos = (float)pos;
+        for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) {  // i < head_dim / 2: q pair; above: k pair
+            const bool is_k = i >= head_dim / 2;
+            if (is_k && !need_k) continue;
+            const uint32_t j = is_k ? i - head_dim / 2 : i;
+            float* v = is_k ? kn : qn;
+            const float* wn = is_k ? nr.k_norm_w : nr.q_norm_w;
+            const float inv = inv2[is_k ? 1 : 0];
+            const float x0 = __fmul_rn(__fmul_rn(v[2 * j], inv), wn[2 * j]);
+            const float x1 = __fmul_rn(__fmul_rn(v[2 * j + 1], inv), wn[2 * j + 1]);
+            const float theta = __fmul_rn(fpos, nr.freqs[j]);
+            const float c = (float)cos((double)theta), sn = (float)sin((double)theta);
+            v[2 * j] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+            v[2 * j + 1] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+        }
+        __syncthreads();
+        qh = qn;
+        knew = kn;
+    }
+    if (writer) {
+        const float* vsrc = v_new + (size_t)kvh * head_dim;
+        for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) {
+            kc[(size_t)pos * kv_dim + (size_t)kvh * head_dim + i] = knew[i];
+            vc[(size_t)pos * kv_dim + (size_t)kvh * head_dim + i] = vsrc[i];
         }
     }
-    if (blockIdx.x * 16 >= kv_len) return;
+    if (!in_window) return;
     const uint32_t pp = threadIdx.x >> 4, l = threadIdx.x & 15;
     const uint32_t p = blockIdx.x * 16 + pp;
     const uint32_t dim16 = head_dim & ~15u;
-    const float* qh = q + (size_t)h * head_dim;
     const uint32_t pc = min(p, kv_len - 1);
     const float* kr = (k_new != nullptr && pc == kv_len - 1)
-                          ? k_new + (size_t)kvh * head_dim
+                          ? knew
                           : kc + (size_t)(kv_start + pc) * kv_dim + (size_t)kvh * head_dim;
     float acc = 0.0f;
     for (uint32_t d = l; d < dim16; d += 16) acc = __fadd_rn(acc, __fmul_rn(qh[d], kr[d]));
@@ -770,17 +827,24 @@ int launch_attention_step(const float* q, float* kc, float* vc, const float* k_n
                           float* out, int8_t* oq, float* oscale, int32_t* osum, float* scores, uint32_t n_head,
                           uint32_t n_kv_head, uint32_t head_dim, const uint32_t* state, uint32_t window,
                           uint32_t max_len, int flags, uint32_t rows, uint32_t q_stride, const uint32_t* row_pos,
-                          size_t cache_stride, cudaStream_t st) {
+                          size_t cache_stride, const float* q_norm_w, const float* k_norm_w, const float* freqs,
+                          float norm_eps, cudaStream_t st) {
     if (max_len == 0 || max_len > 180 * 1024 / 4) return ZQ_ERR_LIMIT;
     if (oq && head_dim % 32) return ZQ_ERR_BAD_ARG;
     if (rows == 0) return ZQ_OK;
-    if (rows > 65535u || (rows > 1 && k_new)) return ZQ_ERR_BAD_ARG;
+    // new keys are taken from the caller's rows only when no row needs another row's key: one row, or
+    // independent sequences
+    if (rows > 65535u || (rows > 1 && k_new && !row_pos)) return ZQ_ERR_BAD_ARG;
+    if (q_norm_w && (!k_new || !k_norm_w || !freqs || head_dim % 2)) return ZQ_ERR_BAD_ARG;
+    const QkNormRope nr{q_norm_w, k_norm_w, freqs, norm_eps};
+    const size_t smem_scores = q_norm_w ? 2 * (size_t)head_dim * sizeof(float) : 0;
+    if (smem_scores > 40 * 1024) return ZQ_ERR_LIMIT;
     const size_t smem = (size_t)max_len * sizeof(float);
     const int tail = (flags & ZQ_ATTN_GPT2_SOFTMAX) ? 1 : 0;
     const uint32_t scores_stride = n_head * max_len;
-    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head, rows), dim3(256), 0, st, q, kc,
-                       vc, k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window, q_stride, scores_stride,
-                       row_pos, cache_stride));
+    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head, rows), dim3(256), smem_scores,
+                       st, q, kc, vc, k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window, q_stride,
+                       scores_stride, row_pos, cache_stride, nr));
     const dim3 grid(n_head, (head_dim + kAttnDims - 1) / kAttnDims, rows);
     if (oq) {
         auto kern = attention_softmax_v_step_kernel<true>;

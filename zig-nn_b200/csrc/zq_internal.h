@@ -160,12 +160,14 @@ int launch_gelu_mul_quant(const float* gate, const float* up, uint32_t n, int8_t
 // Single-query attention over positions [max(0, pos + 1 - window), pos] (window 0 = all); max_len is the
 // largest window any step can have. k_new / v_new (optional, rows == 1): this step's key / value rows,
 // stored into row `pos` of the caches by the same launch. `out` (f32) and `oq/oscale/osum` (quantised)
-// are each optional. scores holds rows * n_head * max_len floats.
+// are each optional. scores holds rows * n_head * max_len floats. q_norm_w != nullptr: q and k_new are raw
+// projection outputs; per-head RMSNorm + RoPE (gemma3.zig:689-716) is applied inside the scores kernel.
 int launch_attention_step(const float* q, float* kc, float* vc, const float* k_new, const float* v_new,
                           float* out, int8_t* oq, float* oscale, int32_t* osum, float* scores, uint32_t n_head,
                           uint32_t n_kv_head, uint32_t head_dim, const uint32_t* state, uint32_t window,
                           uint32_t max_len, int flags, uint32_t rows, uint32_t q_stride, const uint32_t* row_pos,
-                          size_t cache_stride, cudaStream_t st);
+                          size_t cache_stride, const float* q_norm_w, const float* k_norm_w, const float* freqs,
+                          float norm_eps, cudaStream_t st);
 // f32 matvec (GPT-2 vocabulary head) with an optional LayerNorm of x in the prologue (gemv.cu).
 int launch_matvec_ln_f32(const float* w, const float* x, float* y, uint32_t out_dim, uint32_t in_dim,
                          const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st);
