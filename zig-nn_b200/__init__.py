@@ -2,12 +2,12 @@
 ops between them, as hand-written sm_100a CUDA kernels behind a C ABI (include/zq.h).
 
 The directory is named ``zig-nn_b200``; import it as ``zignn_b200`` (see zignn_b200.py at the
-repository root). ``ggml``, ``structs``, ``hostmodel`` and ``sharding`` are host-only; everything in ``api``
+repository root). ``ggml``, ``gguf``, ``structs``, ``hostmodel`` and ``sharding`` are host-only; everything in ``api``
 needs libzq.so and a GPU and raises if either is missing.
 """
-from . import ggml, hostmodel, sharding, structs  # noqa: F401
+from . import ggml, gguf, hostmodel, sharding, structs  # noqa: F401
 
-__all__ = ["ggml", "hostmodel", "sharding", "structs", "api", "_lib"]
+__all__ = ["ggml", "gguf", "hostmodel", "sharding", "structs", "api", "_lib"]
 
 
 def __getattr__(name):

@@ -1,5 +1,6 @@
-"""Host-side model containers: the tensors a GGUF loader would hand over, plus seeded
-synthetic generators for GPT-2 and Gemma-3 shaped models.
+"""Host-side model containers: the tensors a GGUF loader hands over, seeded synthetic generators
+for GPT-2 and Gemma-3 shaped models, and their GGUF form (`to_gguf` / `from_gguf`) under the tensor
+names zig-nn's loaders use (src/models/gpt2.zig:70-181, src/models/gemma3.zig:129-226).
 
 A container keeps every numpy array alive and builds the C structs of include/zq.h
 (zq_gpt2_weights / zq_gemma3_weights) that point into them.
@@ -10,6 +11,7 @@ import numpy as np
 import torch
 
 from . import ggml
+from . import gguf
 from . import structs as S
 
 GPT2_SMALL = dict(vocab=50257, embed=768, head=12, layer=12, ctx=1024, ffn=3072)
@@ -110,6 +112,75 @@ class Gpt2Host:
     def quant_bytes(self):
         return sum(v.raw.size for b in self.blocks for v in b.values() if isinstance(v, QuantTensor))
 
+    # field of a block -> tensor name suffix (gpt2.zig:134-181)
+    _BLOCK_NAMES = dict(
+        ln1_weight="attn_norm.weight", ln1_bias="attn_norm.bias",
+        attn_qkv_weight="attn_qkv.weight", attn_qkv_bias="attn_qkv.bias",
+        attn_proj_weight="attn_output.weight", attn_proj_bias="attn_output.bias",
+        ln2_weight="ffn_norm.weight", ln2_bias="ffn_norm.bias",
+        mlp_fc_weight="ffn_up.weight", mlp_fc_bias="ffn_up.bias",
+        mlp_proj_weight="ffn_down.weight", mlp_proj_bias="ffn_down.bias")
+
+    def to_gguf(self, path):
+        """GGUF v3 file that zig-nn's gpt2_weights.load_from_gguf reads (gpt2.zig:70-90)."""
+        c = self.cfg
+        meta = [("general.architecture", gguf.T_STRING, "gpt2"),
+                ("general.name", gguf.T_STRING, "synthetic gpt2"),
+                ("gpt2.context_length", gguf.T_UINT32, c["ctx"]),
+                ("gpt2.embedding_length", gguf.T_UINT32, c["embed"]),
+                ("gpt2.block_count", gguf.T_UINT32, c["layer"]),
+                ("gpt2.feed_forward_length", gguf.T_UINT32, c["ffn"]),
+                ("gpt2.attention.head_count", gguf.T_UINT32, c["head"]),
+                ("gpt2.attention.layer_norm_epsilon", gguf.T_FLOAT32, 1e-5)]
+        tensors = [_f32_tensor("token_embd.weight", self.wte), _f32_tensor("position_embd.weight", self.wpe),
+                   _f32_tensor("output_norm.weight", self.ln_f_weight),
+                   _f32_tensor("output_norm.bias", self.ln_f_bias)]
+        for i, b in enumerate(self.blocks):
+            for field, suffix in self._BLOCK_NAMES.items():
+                tensors.append(_any_tensor("blk.%d.%s" % (i, suffix), b[field]))
+        gguf.write(path, meta, tensors)
+
+    @classmethod
+    def from_gguf(cls, path_or_file):
+        """Model geometry from the tensor shapes (zig-nn fixes it at compile time), head count from metadata."""
+        f = path_or_file if isinstance(path_or_file, gguf.GGUFFile) else gguf.parse(path_or_file)
+        wte, wpe = f.get_tensor_raw_bytes("token_embd.weight"), f.get_tensor_raw_bytes("position_embd.weight")
+        layer = 0
+        while f.get_tensor_info("blk.%d.attn_qkv.weight" % layer) is not None:
+            layer += 1
+        embed = wte.in_dim
+        head = f.get_metadata_u32("gpt2.attention.head_count") or max(1, embed // 64)
+        ffn = f.get_tensor_raw_bytes("blk.0.ffn_up.weight").out_dim
+        m = cls(dict(vocab=wte.out_dim, embed=embed, head=head, layer=layer, ctx=wpe.out_dim, ffn=ffn))
+        m._gguf = f  # quantised tensors are views into the mapped file
+        m.wte = f.load_tensor_f32("token_embd.weight")
+        m.wpe = f.load_tensor_f32("position_embd.weight")
+        m.ln_f_weight = f.load_tensor_f32("output_norm.weight")
+        m.ln_f_bias = f.load_tensor_f32("output_norm.bias")
+        for i in range(layer):
+            m.blocks.append({field: _load_field(f, "blk.%d.%s" % (i, suffix), quant=field.endswith("_weight")
+                                                and not field.startswith("ln"))
+                             for field, suffix in cls._BLOCK_NAMES.items()})
+        return m
+
+
+def _f32_tensor(name, a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return (name, tuple(reversed(a.shape)), ggml.F32, a)
+
+
+def _any_tensor(name, v):
+    if isinstance(v, QuantTensor):
+        return (name, (v.in_dim, v.out_dim), v.qtype, v.raw)  # GGUF order: innermost dimension first
+    return _f32_tensor(name, v)
+
+
+def _load_field(f, name, quant):
+    if not quant:
+        return f.load_tensor_f32(name)
+    r = f.get_tensor_raw_bytes(name)
+    return QuantTensor(r.data, r.type_, r.out_dim, r.in_dim)
+
 
 class Gemma3Host:
     def __init__(self, cfg):
@@ -172,3 +243,67 @@ class Gemma3Host:
     def quant_bytes(self):
         n = self.token_embd.raw.size
         return n + sum(v.raw.size for b in self.blocks for v in b.values() if isinstance(v, QuantTensor))
+
+    # field of a block -> tensor name suffix (gemma3.zig:174-226)
+    _BLOCK_NAMES = dict(
+        attn_norm_weight="attn_norm.weight", post_attention_norm_weight="post_attention_norm.weight",
+        attn_q_weight="attn_q.weight", attn_k_weight="attn_k.weight", attn_v_weight="attn_v.weight",
+        attn_output_weight="attn_output.weight", attn_q_norm_weight="attn_q_norm.weight",
+        attn_k_norm_weight="attn_k_norm.weight", ffn_norm_weight="ffn_norm.weight",
+        post_ffw_norm_weight="post_ffw_norm.weight", ffn_gate_weight="ffn_gate.weight",
+        ffn_up_weight="ffn_up.weight", ffn_down_weight="ffn_down.weight")
+    _QUANT_FIELDS = ("attn_q_weight", "attn_k_weight", "attn_v_weight", "attn_output_weight", "ffn_gate_weight",
+                     "ffn_up_weight", "ffn_down_weight")
+
+    def to_gguf(self, path):
+        """GGUF v3 file that zig-nn's gemma3_weights.load_from_gguf reads (gemma3.zig:129-143)."""
+        c = self.cfg
+        meta = [("general.architecture", gguf.T_STRING, "gemma3"),
+                ("general.name", gguf.T_STRING, "synthetic gemma3"),
+                ("gemma3.context_length", gguf.T_UINT32, c["ctx"]),
+                ("gemma3.embedding_length", gguf.T_UINT32, c["embed"]),
+                ("gemma3.block_count", gguf.T_UINT32, c["layer"]),
+                ("gemma3.feed_forward_length", gguf.T_UINT32, c["ffn"]),
+                ("gemma3.attention.head_count", gguf.T_UINT32, c["head"]),
+                ("gemma3.attention.head_count_kv", gguf.T_UINT32, c["head_kv"]),
+                ("gemma3.attention.key_length", gguf.T_UINT32, c["head_dim"]),
+                ("gemma3.attention.value_length", gguf.T_UINT32, c["head_dim"]),
+                ("gemma3.attention.layer_norm_rms_epsilon", gguf.T_FLOAT32, c["rms_eps"]),
+                ("gemma3.attention.sliding_window", gguf.T_UINT32, c["sliding_window"]),
+                ("gemma3.attention.sliding_window_pattern", gguf.T_UINT32, c["global_every"]),
+                ("gemma3.rope.freq_base", gguf.T_FLOAT32, c["rope_base"])]
+        tensors = [_any_tensor("token_embd.weight", self.token_embd),
+                   _f32_tensor("output_norm.weight", self.output_norm_weight)]
+        for i, b in enumerate(self.blocks):
+            for field, suffix in self._BLOCK_NAMES.items():
+                tensors.append(_any_tensor("blk.%d.%s" % (i, suffix), b[field]))
+        gguf.write(path, meta, tensors)
+
+    @classmethod
+    def from_gguf(cls, path_or_file, ctx=None):
+        """Geometry from tensor shapes and metadata; what a file does not say falls back to the constants
+        zig-nn compiles in (gemma3.zig:15-29)."""
+        f = path_or_file if isinstance(path_or_file, gguf.GGUFFile) else gguf.parse(path_or_file)
+        embd = f.get_tensor_raw_bytes("token_embd.weight")
+        layer = 0
+        while f.get_tensor_info("blk.%d.attn_q.weight" % layer) is not None:
+            layer += 1
+        u32, f32 = f.get_metadata_u32, f.get_metadata_f32
+        head_dim = f.get_tensor_raw_bytes("blk.0.attn_q_norm.weight").n_elem
+        q, k = f.get_tensor_raw_bytes("blk.0.attn_q.weight"), f.get_tensor_raw_bytes("blk.0.attn_k.weight")
+        cfg = dict(GEMMA3_1B)
+        cfg.update(vocab=embd.out_dim, embed=embd.in_dim, head=q.out_dim // head_dim, head_kv=k.out_dim // head_dim,
+                   head_dim=head_dim, layer=layer, ffn=f.get_tensor_raw_bytes("blk.0.ffn_gate.weight").out_dim)
+        cfg["ctx"] = ctx or u32("gemma3.context_length") or cfg["ctx"]
+        cfg["rope_base"] = f32("gemma3.rope.freq_base") or cfg["rope_base"]
+        cfg["sliding_window"] = u32("gemma3.attention.sliding_window") or cfg["sliding_window"]
+        cfg["rms_eps"] = f32("gemma3.attention.layer_norm_rms_epsilon") or cfg["rms_eps"]
+        cfg["global_every"] = u32("gemma3.attention.sliding_window_pattern") or cfg["global_every"]
+        m = cls(cfg)
+        m._gguf = f  # quantised tensors are views into the mapped file
+        m.token_embd = _load_field(f, "token_embd.weight", quant=True)
+        m.output_norm_weight = f.load_tensor_f32("output_norm.weight")
+        for i in range(layer):
+            m.blocks.append({field: _load_field(f, "blk.%d.%s" % (i, suffix), quant=field in cls._QUANT_FIELDS)
+                             for field, suffix in cls._BLOCK_NAMES.items()})
+        return m
