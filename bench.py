@@ -357,6 +357,29 @@ def run_case(args):
         dt = time.perf_counter() - t0
         print(json.dumps({"case": args.case, "tok_s": int(n_steps) / dt, "last_token": int(toks[-1])}), flush=True)
         return
+    if args.case.startswith("trans:"):
+        # trans:<type>,<in_dim K>,<out_dim N>,<rows M>: grad_x[M][K] = grad_out[M][N] . W[N][K]
+        qname, k, n, m = args.case[6:].split(",")
+        k, n, m = int(k), int(n), int(m)
+        raw = make_weight_bytes(qname, n, k, 42, "cuda")
+        w = zq.QuantWeight(raw, ggml.TYPE_IDS[qname], n, k)
+        go = torch.randn(m, n, device="cuda") * 1e-3
+        gx = torch.empty(m, k, device="cuda")
+        from zignn_b200 import _lib
+        wsb = torch.empty(_lib.load().zq_matmul_transposed_workspace_bytes(w.handle, m), dtype=torch.uint8, device="cuda")
+        for _ in range(max(1, args.warmup)):
+            zq.quant_matmul_transposed(go, w, grad_x=gx, workspace=wsb)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            zq.quant_matmul_transposed(go, w, grad_x=gx, workspace=wsb)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps
+        print(json.dumps({"case": args.case, "us_per_call": us, "tflops": 2.0 * m * n * k / us / 1e6,
+                          "steps": args.steps}), flush=True)
+        return
     parts = args.case.split(",")
     qname, k, n, m = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
     mode = zq.ACT_Q8 if len(parts) > 4 and parts[4] == "q8" else zq.ACT_F32
@@ -508,7 +531,14 @@ def main():
     hx = torch.randn(1, k).pin_memory()
     hy = torch.empty(tuple(step().shape), dtype=torch.float32).pin_memory()  # the full logits row on every rank
 
+    host_call = zq.HostLinear(qw, 1, zq.ACT_F32) if not use_dist else None
+
     def e2e_step():
+        if host_call is not None:
+            # the host-buffer call of the public API: x staged to the device, the kernel writes the logits
+            # straight into the pinned result buffer (PCIe traffic: 4K bytes in, 4N bytes out per step)
+            host_call(hx, hy)
+            return
         x.copy_(hx, non_blocking=True)
         hy.copy_(step(), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads hy

@@ -137,7 +137,11 @@ size_t zq_matmul_workspace_bytes(const zq_weight* w, uint32_t m_rows, int act_mo
  * ThreadPool.matmul (src/gguf/thread_pool.zig:96-160), MetalContext.dispatch_matmul and
  * dispatch_matmul_batched (src/backend/metal.zig:729-846).
  * m_rows <= 16 runs the bandwidth-bound decode kernels; larger m_rows the tiled kernels.
- * d_workspace: zq_matmul_workspace_bytes() bytes, 256-byte aligned, or NULL when that is 0. */
+ * d_workspace: zq_matmul_workspace_bytes() bytes, 256-byte aligned, or NULL when that is 0.
+ * d_y may also be page-locked host memory that the device can address (cudaHostAlloc, cudaHostRegister):
+ * the kernels only write y (unless an epilogue pointer aliases it), so a caller that wants the result on
+ * the host — the reference's matmuls return into host slices — saves the device-to-host copy; the rows
+ * leave over PCIe while the weights are still streaming. */
 int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows, int act_mode,
               const zq_epilogue* epilogue, void* d_workspace, size_t workspace_bytes,
               zq_stream stream);
@@ -158,6 +162,24 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
  *   Calls no cudaMalloc / cudaFree or other allocating routine. */
 int zq_matmul_q8_static(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
                         const zq_epilogue* epilogue, zq_stream stream);
+
+/* Scratch needed by zq_matmul_transposed for (w, m_rows): the fp16 copy of grad_out and its row scales. */
+size_t zq_matmul_transposed_workspace_bytes(const zq_weight* w, uint32_t m_rows);
+
+/* grad_x[m][k] (+)= sum_j grad_out[m][j] * W[j][k]: the backward of zq_matmul with respect to its
+ * activations, weights decoded on the fly. Replaces matmul_q4_0_trans_batched / matmul_q4_1_trans_batched /
+ * matmul_q8_0_trans_batched (src/backend/shaders/nn_training_kernels.metal:1149-1242) behind
+ * MetalContext.dispatch_quant_trans_batched, which backward_quant_matmul calls
+ * (src/diff/mps_runtime.zig:1212-1230).
+ * d_grad_out: [m_rows][out_dim] f32; d_grad_x: [m_rows][in_dim] f32, 8-byte aligned.
+ * accumulate != 0 adds to d_grad_x (what the reference's kernels do); 0 overwrites it.
+ * out_dim must be a multiple of 8 (ZQ_ERR_UNSUPPORTED otherwise).
+ * d_workspace: zq_matmul_transposed_workspace_bytes() bytes, 256-byte aligned.
+ * Tensor-core product of fp16 copies (one rounding each for weights and gradients), f32 accumulation:
+ * about 3e-4 relative L2 against the f32 statement; sums over the weight rows may be split over CTAs and
+ * meet through atomic adds, so the last bits depend on the schedule. */
+int zq_matmul_transposed(const zq_weight* w, const float* d_grad_out, float* d_grad_x, uint32_t m_rows,
+                         int accumulate, void* d_workspace, size_t workspace_bytes, zq_stream stream);
 
 /* quantize_row_q8 (src/gguf/simd_dot.zig:25-64) for m_rows rows of in_dim floats.
  * d_q: int8 [m_rows][in_dim]; d_scale: f32 [m_rows][in_dim/32]; d_sum: int32 [m_rows][in_dim/32]. */

@@ -58,6 +58,7 @@ def _load(path=None):
         "zqo_dot_q8": (f, [i, vp, vp, sz]),
         "zqo_matmul_q8": (i, [i, vp, vp, vp, sz, sz, i, i]),
         "zqo_linear": (i, [i, vp, vp, vp, sz, sz, sz, i, i]),
+        "zqo_matmul_transposed": (i, [i, vp, vp, vp, sz, sz, sz, i, i]),
         "zqo_layer_norm_rows": (None, [vp, vp, vp, vp, sz, sz]),
         "zqo_layer_norm_forward": (None, [vp, vp, vp, vp, sz, sz, f]),
         "zqo_rms_norm_rows": (None, [vp, vp, vp, sz, sz, f]),
@@ -185,6 +186,18 @@ def linear(t, w, x, out_dim, in_dim, act_mode=0, n_threads=1):
     if rc:
         raise ValueError("zqo_linear failed: %d" % rc)
     return y
+
+
+def matmul_transposed(t, w, grad_out, out_dim, in_dim, grad_x=None, n_threads=1):
+    """grad_x [m, in_dim] (+)= grad_out [m, out_dim] . W; grad_x given = accumulate into a copy of it."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    g = _f32(grad_out).reshape(-1, out_dim)
+    acc = grad_x is not None
+    o = _f32(grad_x).reshape(-1, in_dim).copy() if acc else np.empty((g.shape[0], in_dim), dtype=np.float32)
+    rc = lib().zqo_matmul_transposed(t, _p(w), _p(g), _p(o), g.shape[0], out_dim, in_dim, int(acc), n_threads)
+    if rc:
+        raise ValueError("UnsupportedQuantType")
+    return o
 
 
 def layer_norm_rows(x, w, b):

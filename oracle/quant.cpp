@@ -404,4 +404,33 @@ int zqo_linear(int type, const uint8_t* w, const float* x, float* y, size_t m_ro
     return 0;
 }
 
+
+// ------------------------------------------------- transposed matmul (backward w.r.t. activations)
+
+// grad_x[m][k] (+)= sum_j grad_out[m][j] * W[j][k], j ascending, f32: the statement of
+// matmul_q4_0_trans_batched / _q4_1_ / _q8_0_ (src/backend/shaders/nn_training_kernels.metal:1149-1242):
+// each weight is decoded as there (d * (q - 8), d * q + m, d * q) and `acc += g * w` runs over the weight
+// rows in order; the finished sum is added to grad_x (the shader accumulates; accumulate == 0 stores).
+int zqo_matmul_transposed(int type, const uint8_t* w, const float* grad_out, float* grad_x, size_t m_rows,
+                          size_t out_dim, size_t in_dim, int accumulate, int n_threads) {
+    if (type != ZQ_TYPE_Q4_0 && type != ZQ_TYPE_Q4_1 && type != ZQ_TYPE_Q8_0) return 1;
+    const size_t row_bytes = zqo_tensor_bytes(type, in_dim);
+#pragma omp parallel num_threads(n_threads > 0 ? n_threads : 1)
+    {
+        std::vector<float> wrow(in_dim), acc(in_dim);
+#pragma omp for schedule(static)
+        for (long m = 0; m < (long)m_rows; ++m) {
+            std::fill(acc.begin(), acc.end(), 0.0f);
+            for (size_t j = 0; j < out_dim; ++j) {
+                zqo_dequantize(type, w + j * row_bytes, wrow.data(), in_dim);
+                const float g = grad_out[(size_t)m * out_dim + j];
+                for (size_t k = 0; k < in_dim; ++k) acc[k] += g * wrow[k];
+            }
+            float* o = grad_x + (size_t)m * in_dim;
+            for (size_t k = 0; k < in_dim; ++k) o[k] = accumulate ? o[k] + acc[k] : acc[k];
+        }
+    }
+    return 0;
+}
+
 }  // extern "C"

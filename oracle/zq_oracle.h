@@ -78,6 +78,9 @@ int zqo_matmul_q8(int type, const uint8_t* w, const float* x, float* y, size_t o
 
 /* Batched rows: y[m] = matmul(x[m]) for m in 0..m_rows, the way linear_forward_q loops
  * (src/models/gpt2.zig:640-686, src/models/gemma3.zig:889-901). act_mode: 0 f32, 1 q8. */
+/* grad_x[m][k] (+)= sum_j grad_out[m][j] * W[j][k] (nn_training_kernels.metal:1149-1242) */
+int zqo_matmul_transposed(int type, const uint8_t* w, const float* grad_out, float* grad_x, size_t m_rows,
+                          size_t out_dim, size_t in_dim, int accumulate, int n_threads);
 int zqo_linear(int type, const uint8_t* w, const float* x, float* y, size_t m_rows,
                size_t out_dim, size_t in_dim, int act_mode, int n_threads);
 

@@ -137,3 +137,37 @@ def test_gemma3_1b_full_size_greedy_64(zq, oracle):
     print("gemma3 full-size logits rel-L2: max %.2e median %.2e" % (max(errs), float(np.median(errs))))
     assert gt == ct, (len(gt), gt[-1], ct[-1])
     assert max(errs) <= 1e-3, max(errs)
+
+
+def test_engines_from_gguf_files_match_engines_from_memory(zq, oracle, tmp_path):
+    """Write the synthetic models as GGUF files under zig-nn's tensor names, map them back, and run the
+    engines straight from the mapped bytes: logits are the bits of the in-memory model."""
+    from zignn_b200 import gguf
+    g_host = hostmodel.Gpt2Host.synthetic(GPT2_TINY, seed=42, std=0.08).randomize_small_params()
+    g_path = str(tmp_path / "gpt2.gguf")
+    g_host.to_gguf(g_path)
+    prompt = np.random.default_rng(44).integers(0, GPT2_TINY["vocab"], size=20)
+    a = zq.Gpt2(g_host).prefill(prompt).cpu().numpy()
+    b = zq.Gpt2(hostmodel.Gpt2Host.from_gguf(g_path)).prefill(prompt).cpu().numpy()
+    assert np.array_equal(a, b)
+
+    m_host = hostmodel.Gemma3Host.synthetic(GEMMA_TINY, qtype=ggml.Q4_0, embd_qtype=ggml.Q8_0, down_qtype=ggml.Q4_1,
+                                            seed=42, std=0.08).randomize_small_params()
+    m_path = str(tmp_path / "gemma3.gguf")
+    m_host.to_gguf(m_path)
+    from_file = hostmodel.Gemma3Host.from_gguf(m_path)
+    prompt = np.random.default_rng(45).integers(0, GEMMA_TINY["vocab"], size=24)
+    eng = zq.Gemma3(from_file)
+    ref = oracle.Gemma3(m_host, 4)
+    lg, lc = eng.prefill(prompt).cpu().numpy(), ref.prefill(prompt)
+    assert np.array_equal(lg, lc)
+    for _ in range(8):
+        t = int(np.argmax(lc))
+        lg, lc = eng.decode_next(t).cpu().numpy(), ref.decode_next(t)
+        assert np.array_equal(lg, lc)
+
+    # a quantised tensor asked for as f32 is decoded by the CUDA decoder: the oracle's bits
+    f = gguf.parse(m_path)
+    r = f.get_tensor_raw_bytes("blk.0.ffn_down.weight")
+    want = oracle.dequantize(r.type_, np.asarray(r.data), r.n_elem)
+    assert np.array_equal(f.load_tensor_f32("blk.0.ffn_down.weight"), want)

@@ -320,3 +320,95 @@ def test_matvec_f32_and_argmax(zq, oracle):
     big = np.zeros(300000, np.float32)
     big[[250000, 123456]] = 3.0
     assert int(zq.argmax(torch.from_numpy(big).cuda()).item()) == 123456
+
+
+# ---- transposed product (backward with respect to the activations) ----------------------------------
+
+REL_L2_TRANS = 6e-4  # fp16 copies of weights and gradients, f32 accumulation: about 3e-4
+
+
+@pytest.mark.parametrize("qtype", [ggml.Q4_0, ggml.Q4_1, ggml.Q8_0])
+@pytest.mark.parametrize("shape", [(256, 128, 130), (72, 96, 5), (1152, 6912, 64), (6912, 1152, 300)])
+def test_matmul_transposed_against_oracle(zq, oracle, qtype, shape):
+    """grad_x = grad_out . W for ragged row counts, weight-row counts that are not a multiple of the 128-row
+    stage, in_dim below one 128-column tile, and shapes whose weight rows are split over several CTAs."""
+    out_dim, in_dim, m = shape
+    g = torch.Generator().manual_seed(out_dim + m)
+    w = torch.randn(out_dim, in_dim, generator=g) * 0.02
+    raw = ggml.quantize(qtype, w).numpy()
+    go = torch.randn(m, out_dim, generator=g) * 1e-3  # gradient-sized values: the row scale matters
+    go[0] = 0.0
+    qw = zq.QuantWeight(raw, qtype, out_dim, in_dim)
+    got = zq.quant_matmul_transposed(go.cuda(), qw).cpu().numpy()
+    want = oracle.matmul_transposed(qtype, raw, go.numpy(), out_dim, in_dim, n_threads=8)
+    assert rel_l2(got, want) <= REL_L2_TRANS, rel_l2(got, want)
+    assert np.all(got[0] == 0.0)
+
+
+def test_matmul_transposed_accumulates_like_the_reference_kernels(zq, oracle):
+    out_dim, in_dim, m = 4096, 256, 40  # 32 stages: split over CTAs, partial sums meet by atomic adds
+    g = torch.Generator().manual_seed(3)
+    raw = ggml.quantize(ggml.Q4_0, torch.randn(out_dim, in_dim, generator=g) * 0.02).numpy()
+    go = torch.randn(m, out_dim, generator=g)
+    base = torch.randn(m, in_dim, generator=g)
+    qw = zq.QuantWeight(raw, ggml.Q4_0, out_dim, in_dim)
+    gx = base.clone().cuda()
+    out = zq.quant_matmul_transposed(go.cuda(), qw, grad_x=gx, accumulate=True)
+    assert out.data_ptr() == gx.data_ptr()
+    want = oracle.matmul_transposed(ggml.Q4_0, raw, go.numpy(), out_dim, in_dim, grad_x=base.numpy(), n_threads=8)
+    assert rel_l2(gx.cpu().numpy(), want) <= REL_L2_TRANS
+    # overwrite mode ignores what grad_x held
+    gx2 = torch.full((m, in_dim), 7.0, device="cuda")
+    zq.quant_matmul_transposed(go.cuda(), qw, grad_x=gx2)
+    want2 = oracle.matmul_transposed(ggml.Q4_0, raw, go.numpy(), out_dim, in_dim, n_threads=8)
+    assert rel_l2(gx2.cpu().numpy(), want2) <= REL_L2_TRANS
+
+
+def test_quant_matmul_backward_to_activations(zq, oracle):
+    """quant_matmul_no_grad on an input that requires grad carries the backward to x (the weight stays
+    frozen): d/dx sum(y * c) = c . W."""
+    out_dim, in_dim = 384, 160
+    g = torch.Generator().manual_seed(11)
+    raw = ggml.quantize(ggml.Q8_0, torch.randn(out_dim, in_dim, generator=g) * 0.05).numpy()
+    qw = zq.QuantWeight(raw, ggml.Q8_0, out_dim, in_dim)
+    x = torch.randn(3, 7, in_dim, generator=g).cuda().requires_grad_(True)
+    c = torch.randn(3, 7, out_dim, generator=g).cuda()
+    y = zq.quant_matmul_no_grad(x, qw)
+    assert y.requires_grad and y.shape == (3, 7, out_dim)
+    (y * c).sum().backward()
+    want = oracle.matmul_transposed(ggml.Q8_0, raw, c.cpu().numpy().reshape(-1, out_dim), out_dim, in_dim)
+    assert rel_l2(x.grad.cpu().numpy().reshape(-1, in_dim), want) <= REL_L2_TRANS
+    with torch.no_grad():
+        assert not zq.quant_matmul_no_grad(x, qw).requires_grad
+
+
+def test_matmul_transposed_rejects_bad_arguments(zq):
+    raw = ggml.quantize(ggml.Q4_0, torch.zeros(12, 32)).numpy()  # 12 weight rows: not a multiple of 8
+    qw = zq.QuantWeight(raw, ggml.Q4_0, 12, 32)
+    with pytest.raises(RuntimeError, match="UNSUPPORTED"):
+        zq.quant_matmul_transposed(torch.zeros(2, 12, device="cuda"), qw)
+    with pytest.raises(ValueError):
+        zq.quant_matmul_transposed(torch.zeros(2, 16, device="cuda"), qw)
+
+
+@pytest.mark.parametrize("qtype,mode", [(ggml.Q4_0, 0), (ggml.Q8_0, 1)])
+def test_host_buffer_call_writes_the_same_bits_into_pinned_memory(zq, qtype, mode):
+    """HostLinear: x from a pinned host buffer, y written by the kernel directly into pinned host memory
+    (first call plain, later calls replayed), and the pageable route — all equal to the device-buffer call."""
+    out_dim, in_dim = 40000, 1152  # enough row tiles for the whole-rows kernels
+    g = torch.Generator().manual_seed(9)
+    raw = ggml.quantize(qtype, torch.randn(out_dim, in_dim, generator=g) * 0.02).numpy()
+    qw = zq.QuantWeight(raw, qtype, out_dim, in_dim)
+    lin = zq.HostLinear(qw, 1, mode)
+    hx, hy = torch.empty(1, in_dim).pin_memory(), torch.empty(1, out_dim).pin_memory()
+    for seed in (1, 2, 3):
+        hx.copy_(torch.randn(1, in_dim, generator=g))
+        hy.fill_(float("nan"))
+        lin(hx, hy)
+        want = zq.quant_matmul_no_grad(hx.cuda(), qw, mode).cpu()
+        assert torch.equal(hy, want)
+    pageable = torch.empty(1, out_dim)
+    lin(hx.clone(), pageable)
+    assert torch.equal(pageable, want)
+    with pytest.raises(ValueError):
+        lin(hx, torch.empty(1, out_dim + 1).pin_memory())

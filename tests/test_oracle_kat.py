@@ -266,3 +266,24 @@ def test_quant_matmul_q8_0_forward(oracle):  # "quantMatmulNoGrad Q8_0 forward":
     x = (np.float32(0.05) * (np.arange(M * IN, dtype=np.float32) - np.float32(15.0))).reshape(M, IN)
     y = oracle.linear(Q8_0, raw, x, OUT, IN, act_mode=0)
     np.testing.assert_allclose(y, x @ wd.T, atol=1e-3)
+
+
+@pytest.mark.parametrize("qtype", [2, 3, 8])
+def test_transposed_product_is_the_decoded_matrix_times_the_gradient(oracle, qtype):
+    """nn_training_kernels.metal:1149-1242 decodes W[j][k] and sums grad_out[m][j] * W[j][k] over j; with
+    one weight row the sum has one term, and with many rows it stays within f32 rounding of the f64 product."""
+    rng = np.random.default_rng(qtype)
+    w = (rng.standard_normal((40, 64)) * 0.05).astype(np.float32)
+    raw = oracle.quantize(qtype, w.reshape(-1))
+    dec = oracle.dequantize(qtype, raw, w.size).reshape(40, 64)
+    g = rng.standard_normal((3, 40)).astype(np.float32)
+    got = oracle.matmul_transposed(qtype, raw, g, 40, 64)
+    ref = g.astype(np.float64) @ dec.astype(np.float64)
+    assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
+    row_bytes = raw.size // 40
+    one = oracle.matmul_transposed(qtype, raw[:row_bytes], g[:, :1], 1, 64)
+    assert np.array_equal(one, g[:, :1] * dec[:1])  # a single f32 product per element, added to zero
+    acc = oracle.matmul_transposed(qtype, raw, g, 40, 64, grad_x=np.full((3, 64), 2.0, np.float32))
+    assert np.array_equal(acc, np.float32(2.0) + got)
+    with pytest.raises(ValueError):
+        oracle.matmul_transposed(0, raw, g, 40, 64)

@@ -39,6 +39,8 @@ SIGNATURES = {
     "zq_matmul_workspace_bytes": (sz, [vp, u32, i]),
     "zq_matmul": (i, [vp, vp, vp, u32, i, P(S.Epilogue), vp, sz, vp]),
     "zq_matmul_q8_static": (i, [vp, vp, vp, u32, P(S.Epilogue), vp]),
+    "zq_matmul_transposed_workspace_bytes": (sz, [vp, u32]),
+    "zq_matmul_transposed": (i, [vp, vp, vp, u32, i, vp, sz, vp]),
     "zq_quantize_rows_q8": (i, [vp, u32, u32, vp, vp, vp, vp]),
     "zq_matvec_f32": (i, [vp, vp, vp, u32, u32, vp]),
     "zq_argmax": (i, [vp, u32, vp, vp]),

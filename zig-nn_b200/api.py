@@ -94,9 +94,7 @@ class QuantWeight:
             pass
 
 
-def quant_matmul_no_grad(x, qw, act_mode=ACT_F32, bias=None, gelu=False, mul=None, residual=None,
-                         out=None, workspace=None):
-    """x [..., in_dim] f32 CUDA -> [..., out_dim]; quantised weight times activations."""
+def _quant_matmul(x, qw, act_mode, bias, gelu, mul, residual, out, workspace):
     lib = _lib.load()
     x = _dev_f32(x)
     if x.shape[-1] != qw.in_dim:
@@ -112,6 +110,113 @@ def quant_matmul_no_grad(x, qw, act_mode=ACT_F32, bias=None, gelu=False, mul=Non
                        need, _stream())
     _lib.check(rc, "zq_matmul")
     return y
+
+
+class _QuantMatmulFn(torch.autograd.Function):
+    """The node quant_matmul_no_grad builds when x requires grad: backward_quant_matmul
+    (src/diff/mps_runtime.zig:1212-1230) is the transposed product."""
+
+    @staticmethod
+    def forward(ctx, x, qw, act_mode):
+        ctx.qw = qw
+        return _quant_matmul(x.detach(), qw, act_mode, None, False, None, None, None, None)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        return quant_matmul_transposed(grad_out.contiguous(), ctx.qw), None, None
+
+
+def quant_matmul_no_grad(x, qw, act_mode=ACT_F32, bias=None, gelu=False, mul=None, residual=None,
+                         out=None, workspace=None):
+    """x [..., in_dim] f32 CUDA -> [..., out_dim]; quantised weight times activations
+    (DiffMpsRuntime.quant_matmul_no_grad, src/diff/mps_runtime.zig:1171-1205). "no_grad" refers to the
+    frozen weight: when x requires grad the result carries the backward to x, as in the reference."""
+    if torch.is_grad_enabled() and isinstance(x, torch.Tensor) and x.requires_grad:
+        if bias is not None or gelu or mul is not None or residual is not None or out is not None:
+            raise ValueError("the differentiable form takes no epilogue and no out=")
+        return _QuantMatmulFn.apply(x, qw, act_mode)
+    return _quant_matmul(x, qw, act_mode, bias, gelu, mul, residual, out, workspace)
+
+
+def quant_matmul_transposed(grad_out, qw, grad_x=None, accumulate=False, workspace=None):
+    """grad_x [..., in_dim] (+)= grad_out [..., out_dim] . W — dispatch_quant_trans_batched of the
+    reference's Metal runtime (src/diff/mps_runtime.zig:1217-1227). accumulate=True adds into grad_x."""
+    lib = _lib.load()
+    g = _dev_f32(grad_out)
+    if g.shape[-1] != qw.out_dim:
+        raise ValueError("last dim %d != out_dim %d" % (g.shape[-1], qw.out_dim))
+    m = g.numel() // qw.out_dim
+    if grad_x is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs grad_x")
+        grad_x = torch.empty(*g.shape[:-1], qw.in_dim, dtype=torch.float32, device=g.device)
+    elif grad_x.numel() != m * qw.in_dim or grad_x.dtype != torch.float32 or not grad_x.is_contiguous():
+        raise ValueError("grad_x must be a contiguous f32 tensor of %d x %d" % (m, qw.in_dim))
+    need = lib.zq_matmul_transposed_workspace_bytes(qw.handle, m)
+    ws = workspace
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=g.device)
+    rc = lib.zq_matmul_transposed(qw.handle, _ptr(g), _ptr(grad_x), m, int(bool(accumulate)), _ptr(ws), need,
+                                  _stream())
+    _lib.check(rc, "zq_matmul_transposed")
+    return grad_x
+
+
+class HostLinear:
+    """y = x . W^T with HOST buffers, the call shape of zig-nn's CPU path (matmul_q4_0_f32(weight, input,
+    output, ...) on slices in host memory, src/gguf/dequant.zig:170-182; ThreadPool.matmul,
+    src/gguf/thread_pool.zig:96-160).
+
+    x and y are page-locked host tensors. x is copied into a device buffer; y is not copied at all: page-locked
+    memory is addressable from the device, the kernels only ever write y, so the GEMV stores its rows straight
+    into the caller's buffer over PCIe while the weights are still streaming. The copy and the launch are
+    recorded once per (x, y) buffer pair and replayed afterwards. Pageable buffers take the plain route
+    (device result, then a copy)."""
+
+    def __init__(self, qw, m_rows=1, act_mode=ACT_F32, use_graph=True):
+        self.qw, self.m, self.act_mode, self.use_graph = qw, int(m_rows), act_mode, use_graph
+        self._x = torch.empty(self.m, qw.in_dim, dtype=torch.float32, device="cuda")
+        need = _lib.load().zq_matmul_workspace_bytes(qw.handle, self.m, act_mode)
+        self._ws = torch.empty(max(need, 256), dtype=torch.uint8, device="cuda")
+        self._need = need
+        self._graphs = {}
+
+    def _launch(self, hx, y_ptr):
+        self._x.copy_(hx.reshape(self.m, self.qw.in_dim), non_blocking=True)
+        ep = S.Epilogue(None, 0, None, None)
+        rc = _lib.load().zq_matmul(self.qw.handle, _ptr(self._x), y_ptr, self.m, self.act_mode, C.byref(ep),
+                                   _ptr(self._ws) if self._need else None, self._need, _stream())
+        _lib.check(rc, "zq_matmul")
+
+    def __call__(self, hx, hy):
+        """hx: [m_rows, in_dim] f32 host; hy: [m_rows, out_dim] f32 host, overwritten. Returns hy; the result is
+        complete when the call returns."""
+        for t, n in ((hx, self.m * self.qw.in_dim), (hy, self.m * self.qw.out_dim)):
+            if t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
+                raise ValueError("expected contiguous float32 host tensors of %d x in_dim / out_dim" % self.m)
+        if not (hx.is_pinned() and hy.is_pinned()):
+            y = torch.empty(self.m, self.qw.out_dim, dtype=torch.float32, device="cuda")
+            self._launch(hx, C.c_void_p(y.data_ptr()))
+            hy.copy_(y.reshape(hy.shape))  # synchronises
+            return hy
+        key = (hx.data_ptr(), hy.data_ptr())
+        g = self._graphs.get(key)
+        if g is None and self.use_graph:
+            self._launch(hx, C.c_void_p(hy.data_ptr()))  # plain first call: one-time set-up stays out of the capture
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._launch(hx, C.c_void_p(hy.data_ptr()))
+            if len(self._graphs) >= 8:
+                self._graphs.clear()
+            self._graphs[key] = (g, hx, hy)  # keeps the buffers alive as long as the recording
+            g = self._graphs[key]
+        if g is not None:
+            g[0].replay()
+        else:
+            self._launch(hx, C.c_void_p(hy.data_ptr()))
+        torch.cuda.current_stream().synchronize()
+        return hy
 
 
 def quant_matmul_q8_static(x, qw, bias=None, gelu=False, mul=None, residual=None, out=None):

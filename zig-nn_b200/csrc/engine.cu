@@ -171,26 +171,20 @@ static int gpt2_linear(zq_gpt2* m, const Linear& L, const float* x, float* y, co
         if ((rc = zq_layer_norm(m->ln, x, ln_w, ln_b, T, L.in_dim, 1e-5f, st))) return rc;
         x = m->ln;
     }
-    for (uint32_t r0 = 0; r0 < T; r0 += 16) {
-        const uint32_t mc = T - r0 < 16 ? T - r0 : 16;
-        const float* xr = x + (size_t)r0 * L.in_dim;
-        float* yr = y + (size_t)r0 * L.out_dim;
-        const float* rr = residual ? residual + (size_t)r0 * L.out_dim : nullptr;
-        zq_epilogue ep{bias, gelu, nullptr, rr};
-        if (L.qw) {
-            rc = launch_gemv_mma_f32(L.qw, xr, yr, mc, &ep, st);
-            if (rc == ZQ_ERR_LIMIT) rc = launch_gemv_f32(L.qw, xr, yr, mc, &ep, st);
-            if (rc != ZQ_OK) return rc;
-            continue;
-        }
-        for (uint32_t r = 0; r < mc; ++r) {
-            float* y1 = yr + (size_t)r * L.out_dim;
-            rc = zq_matvec_f32(L.f32w, xr + (size_t)r * L.in_dim, y1, L.out_dim, L.in_dim, st);
-            if (rc == ZQ_OK && bias) rc = zq_add_broadcast(y1, y1, bias, L.out_dim, L.out_dim, st);
-            if (rc == ZQ_OK && gelu) rc = zq_gelu(y1, y1, L.out_dim, st);
-            if (rc == ZQ_OK && rr) rc = zq_add_broadcast(y1, y1, rr + (size_t)r * L.out_dim, L.out_dim, L.out_dim, st);
-            if (rc != ZQ_OK) return rc;
-        }
+    zq_epilogue ep{bias, gelu, nullptr, residual};
+    if (L.qw) {
+        rc = launch_gemv_mma_passes_f32(L.qw, x, y, T, &ep, st);
+        if (rc == ZQ_ERR_LIMIT) rc = launch_gemv_f32(L.qw, x, y, T, &ep, st);
+        return rc;
+    }
+    for (uint32_t r = 0; r < T; ++r) {
+        float* y1 = y + (size_t)r * L.out_dim;
+        rc = zq_matvec_f32(L.f32w, x + (size_t)r * L.in_dim, y1, L.out_dim, L.in_dim, st);
+        if (rc == ZQ_OK && bias) rc = zq_add_broadcast(y1, y1, bias, L.out_dim, L.out_dim, st);
+        if (rc == ZQ_OK && gelu) rc = zq_gelu(y1, y1, L.out_dim, st);
+        if (rc == ZQ_OK && residual)
+            rc = zq_add_broadcast(y1, y1, residual + (size_t)r * L.out_dim, L.out_dim, L.out_dim, st);
+        if (rc != ZQ_OK) return rc;
     }
     return ZQ_OK;
 }

@@ -571,23 +571,11 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
             return legacy ? launch_gemm_f16(w, d_x, d_y, m_rows, epilogue, d_workspace, st)
                           : launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
         }
-        // up to 16 activation rows per pass over the weights
-        for (uint32_t m0 = 0; m0 < m_rows; m0 += 16) {
-            const uint32_t mc = m_rows - m0 < 16 ? m_rows - m0 : 16;
-            zq_epilogue ep{nullptr, 0, nullptr, nullptr};
-            if (epilogue) {
-                ep = *epilogue;
-                if (ep.d_mul) ep.d_mul += (size_t)m0 * w->out_dim;
-                if (ep.d_residual) ep.d_residual += (size_t)m0 * w->out_dim;
-            }
-            int rc = launch_gemv_mma_f32(w, d_x + (size_t)m0 * w->in_dim, d_y + (size_t)m0 * w->out_dim, mc,
-                                         epilogue ? &ep : nullptr, st);
-            if (rc == ZQ_ERR_LIMIT)  // activation image too large for shared memory: row-at-a-time kernel
-                rc = launch_gemv_f32(w, d_x + (size_t)m0 * w->in_dim, d_y + (size_t)m0 * w->out_dim, mc,
-                                     epilogue ? &ep : nullptr, st);
-            if (rc != ZQ_OK) return rc;
-        }
-        return ZQ_OK;
+        // passes of up to 16 activation rows over the weights
+        int rc = launch_gemv_mma_passes_f32(w, d_x, d_y, m_rows, epilogue, st);
+        if (rc == ZQ_ERR_LIMIT)  // activation image too large for shared memory: row-at-a-time kernel
+            rc = launch_gemv_f32(w, d_x, d_y, m_rows, epilogue, st);
+        return rc;
     }
     if (act_mode == ZQ_ACT_F16) {  // the tensor-core GEMM whatever the row count
         if (((uintptr_t)d_x & 3) != 0) return ZQ_ERR_BAD_ARG;
@@ -609,8 +597,12 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
         int32_t* sm = reinterpret_cast<int32_t*>(static_cast<char*>(d_workspace) + qbytes + sbytes);
         int rc = launch_quantize_rows_q8(d_x, m_rows, w->in_dim, q, sc, sm, st);
         if (rc != ZQ_OK) return rc;
-        // from a handful of rows on, the exact int8 GEMM (weights read once per 64 rows) beats a GEMV per row
-        if (m_rows >= 5) return launch_gemm_q8(w, q, sc, sm, d_y, m_rows, epilogue, st);
+        // From a handful of rows on, the exact int8 GEMM (weights read once per 64 rows) beats a GEMV per row:
+        // from 2 rows for matrices that sit in L2 and have short rows (measured 1.1-1.6x at 2-4 rows), from 5
+        // rows otherwise (long rows with few of them leave the GEMM too few CTAs; the 170-320 MB vocabulary
+        // head streams faster through the whole-rows GEMV up to 4 rows). Both give the same bits.
+        const uint32_t q8_gemm_min = (w->bytes <= ((size_t)32 << 20) && w->in_dim <= 4096) ? 2u : 5u;
+        if (m_rows >= q8_gemm_min) return launch_gemm_q8(w, q, sc, sm, d_y, m_rows, epilogue, st);
         return launch_gemv_q8(w, q, sc, sm, d_y, m_rows, epilogue, st);
     }
     return ZQ_ERR_BAD_ARG;

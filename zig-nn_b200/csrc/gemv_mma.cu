@@ -105,43 +105,57 @@ __device__ void stage_activations(const float* __restrict__ x, uint32_t M, uint3
     const uint32_t ncols = 2 * M;
     const uint32_t total = nbp * ncols * 4;
     const uint32_t total_up = (total + 31u) & ~31u;  // whole warps run the shuffles below
-    for (uint32_t i = threadIdx.x; i < total_up; i += blockDim.x) {
-        const bool active = i < total;
-        const uint32_t ii = active ? i : 0;
-        const uint32_t t = ii & 3u, col = (ii >> 2) % ncols, blk = (ii >> 2) / ncols;
-        const uint32_t m = col >> 1;
-        const bool lo_part = col & 1u;
-        float v[8];
-        if (blk < nb) {
-            const float* p = x + (size_t)m * K + (size_t)blk * 32u;
-            const float4 a = *reinterpret_cast<const float4*>(p + 4u * t);
-            const float4 b = *reinterpret_cast<const float4*>(p + 16u + 4u * t);
-            const float s = pre[m];
-            v[0] = a.x * s; v[1] = a.y * s; v[2] = a.z * s; v[3] = a.w * s;
-            v[4] = b.x * s; v[5] = b.y * s; v[6] = b.z * s; v[7] = b.w * s;
-        } else {
+    constexpr int U = 4;  // entries per thread and round: their loads are all issued before any is used
+    for (uint32_t i0 = threadIdx.x; i0 < total_up; i0 += blockDim.x * U) {
+        float4 a[U], b[U];
+        float s[U];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+        for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * blockDim.x;
+            const uint32_t ii = i < total ? i : 0;
+            const uint32_t t = ii & 3u, col = (ii >> 2) % ncols, blk = (ii >> 2) / ncols;
+            const uint32_t m = col >> 1;
+            a[u] = b[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            s[u] = 0.0f;
+            if (i < total_up && blk < nb) {
+                const float* p = x + (size_t)m * K + (size_t)blk * 32u;
+                a[u] = *reinterpret_cast<const float4*>(p + 4u * t);
+                b[u] = *reinterpret_cast<const float4*>(p + 16u + 4u * t);
+                s[u] = pre[m];
+            }
         }
-        if (WITH_SUM) {
-            float s8 = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-            s8 += __shfl_xor_sync(0xFFFFFFFFu, s8, 1);
-            s8 += __shfl_xor_sync(0xFFFFFFFFu, s8, 2);
-            if (active && !lo_part && t == 0) xsum[blk * M + m] = s8;
-        }
-        float w[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float hi = __half2float(__float2half_rn(v[j]));
-            w[j] = lo_part ? (v[j] - hi) : hi;  // x - hi is exact in f32
-        }
-        if (HI_DIV16) {  // exact: a power of two (tiny parts may round in the subnormal range)
+        for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * blockDim.x;
+            if (i >= total_up) break;  // uniform per warp: blockDim.x and total_up are multiples of 32
+            const bool active = i < total;
+            const uint32_t ii = active ? i : 0;
+            const uint32_t t = ii & 3u, col = (ii >> 2) % ncols, blk = (ii >> 2) / ncols;
+            const uint32_t m = col >> 1;
+            const bool lo_part = col & 1u;
+            float v[8];
+            v[0] = a[u].x * s[u]; v[1] = a[u].y * s[u]; v[2] = a[u].z * s[u]; v[3] = a[u].w * s[u];
+            v[4] = b[u].x * s[u]; v[5] = b[u].y * s[u]; v[6] = b[u].z * s[u]; v[7] = b[u].w * s[u];
+            if (WITH_SUM) {
+                float s8 = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+                s8 += __shfl_xor_sync(0xFFFFFFFFu, s8, 1);
+                s8 += __shfl_xor_sync(0xFFFFFFFFu, s8, 2);
+                if (active && !lo_part && t == 0) xsum[blk * M + m] = s8;
+            }
+            float w[8];
 #pragma unroll
-            for (int j = 4; j < 8; ++j) w[j] *= 0.0625f;
+            for (int j = 0; j < 8; ++j) {
+                const float hi = __half2float(__float2half_rn(v[j]));
+                w[j] = lo_part ? (v[j] - hi) : hi;  // x - hi is exact in f32
+            }
+            if (HI_DIV16) {  // exact: a power of two (tiny parts may round in the subnormal range)
+#pragma unroll
+                for (int j = 4; j < 8; ++j) w[j] *= 0.0625f;
+            }
+            if (active)
+                frag[i] = make_uint4(pack_half2(w[0], w[2]), pack_half2(w[1], w[3]), pack_half2(w[4], w[6]),
+                                     pack_half2(w[5], w[7]));
         }
-        if (active)
-            frag[i] = make_uint4(pack_half2(w[0], w[2]), pack_half2(w[1], w[3]), pack_half2(w[4], w[6]),
-                                 pack_half2(w[5], w[7]));
     }
 }
 
@@ -372,6 +386,9 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t wr = warp % WR, ks = warp / WR;
+    // Warps past WR * KS only help to build the activation image; they own no quads (q_lo == q_hi below)
+    // and no output, but keep every barrier of the tile loop.
+    const bool helper = (uint32_t)warp >= WR * KS;
 
     const uint32_t nq = nbp / 4;
     const uint32_t per = (nq + KS - 1) / KS;
@@ -469,18 +486,23 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     }
 
     // ---- activations: range prescale, then the fp16 hi/lo fragment image ----
-    if (tid < 16) amax_bits[tid] = 0;
-    __syncthreads();
-    for (uint32_t m = 0; m < M; ++m) {
+    // one warp per activation row, eight 128-bit loads in flight per lane
+    for (uint32_t m = warp; m < M; m += blockDim.x >> 5) {
         float amax = 0.0f;
         const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
-        for (uint32_t i = tid; i < K / 4; i += blockDim.x) {
-            const float4 v = xr[i];
-            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        const uint32_t n4 = K / 4;
+        for (uint32_t i0 = lane; i0 < n4; i0 += 32 * 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = i0 + 32 * u < n4 ? xr[i0 + 32 * u] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v[u].x), fabsf(v[u].y))), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-        if (lane == 0) atomicMax(&amax_bits[m], __float_as_uint(amax));  // non-negative floats order as ints
+        if (lane == 0) amax_bits[m] = __float_as_uint(amax);
     }
     __syncthreads();
     if (tid < (int)M) {
@@ -560,11 +582,13 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
             }
         }
         if (KS > 1) {
-            float* mine = red + ((size_t)(wr * KS + ks) * NS * 2) * 32;
+            if (!helper) {
+                float* mine = red + ((size_t)(wr * KS + ks) * NS * 2) * 32;
 #pragma unroll
-            for (int c = 0; c < NS; ++c) {
-                mine[(c * 2 + 0) * 32 + lane] = out_a[c];
-                mine[(c * 2 + 1) * 32 + lane] = out_b[c];
+                for (int c = 0; c < NS; ++c) {
+                    mine[(c * 2 + 0) * 32 + lane] = out_a[c];
+                    mine[(c * 2 + 1) * 32 + lane] = out_b[c];
+                }
             }
             __syncthreads();
             if (ks == 0) {
@@ -979,7 +1003,7 @@ int launch_rows1_any(const zq_weight* w, const float* x, float* y, EpilogueArgs 
 }
 
 struct Plan {
-    uint32_t WR, KS, grid, ring_off;
+    uint32_t WR, KS, grid, ring_off, warps;
     size_t smem;
     bool fits;
 };
@@ -998,6 +1022,12 @@ Plan make_plan(const zq_weight* w, uint32_t M, int ns, bool use_ring, bool with_
     while (warps > ks && (tiles + warps / ks - 1) / (warps / ks) < sms) warps /= 2;
     p.WR = warps / ks ? warps / ks : 1;
     p.KS = ks;
+    // The activation image has nbp * 2M * 4 entries of 16 bytes; with several activation rows and few
+    // computing warps, extra warps share the work of building it (about four entries per thread).
+    const uint32_t entries = w->nbp * 2 * M * 4;
+    uint32_t total_warps = (entries + 127) / 128;
+    if (total_warps > 8) total_warps = 8;
+    p.warps = total_warps > p.WR * ks ? total_warps : p.WR * ks;
     size_t smem = (size_t)w->nbp * 2 * M * 64 + 16;  // activation image + zero slot
     if (w->type != ZQ_TYPE_Q8_0) smem += (size_t)w->nbp * M * sizeof(float);
     if (ks > 1) smem += (size_t)p.WR * ks * ns * 2 * 32 * sizeof(float);
@@ -1026,7 +1056,7 @@ int launch_kernel(const zq_weight* w, const float* x, float* y, uint32_t M, Epil
     auto kern = gemv_mma_kernel<TYPE, NS, USE_RING>;
     if (p.smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
-    ZQ_CUDA(launch_pdl(kern, dim3(p.grid), dim3(p.WR * p.KS * 32), p.smem, st, w->qs,
+    ZQ_CUDA(launch_pdl(kern, dim3(p.grid), dim3(p.warps * 32), p.smem, st, w->qs,
                        static_cast<const uint8_t*>(w->sc), x, y, w->out_dim, w->in_dim, w->nb, w->scp, M, p.WR, p.KS,
                        p.ring_off, ep));
     return ZQ_OK;
@@ -1091,6 +1121,30 @@ int launch_gemv_mma_ln_f32(const zq_weight* w, const float* x, float* y, uint32_
     }
 }
 
+
+// Any number of activation rows: passes of up to 16 rows over the weights, the pass height halved until
+// the activation image of a pass fits in shared memory. ZQ_ERR_LIMIT when not even one row fits.
+int launch_gemv_mma_passes_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
+                               const zq_epilogue* epilogue, cudaStream_t st) {
+    uint32_t pass = 16;
+    while (pass > 1 && pass / 2 >= m_rows) pass /= 2;
+    const bool ring = w->type != ZQ_TYPE_Q4_1 && (size_t)w->out_dim * w->nbp * w->qb >= ((size_t)64 << 20);
+    while (pass >= 1 && !make_plan(w, pass, (int)((pass + 3) / 4), ring, false).fits) pass /= 2;
+    if (pass == 0) return ZQ_ERR_LIMIT;
+    for (uint32_t m0 = 0; m0 < m_rows; m0 += pass) {
+        const uint32_t mc = m_rows - m0 < pass ? m_rows - m0 : pass;
+        zq_epilogue ep{nullptr, 0, nullptr, nullptr};
+        if (epilogue) {
+            ep = *epilogue;
+            if (ep.d_mul) ep.d_mul += (size_t)m0 * w->out_dim;
+            if (ep.d_residual) ep.d_residual += (size_t)m0 * w->out_dim;
+        }
+        const int rc = launch_gemv_mma_f32(w, x + (size_t)m0 * w->in_dim, y + (size_t)m0 * w->out_dim, mc,
+                                           epilogue ? &ep : nullptr, st);
+        if (rc != ZQ_OK) return rc;
+    }
+    return ZQ_OK;
+}
 
 // One activation row, row-sharded weight: GEMV with the all-gather of the output slices in its epilogue.
 // ZQ_ERR_UNSUPPORTED when the shard is too small for the whole-rows kernel (the caller then runs the

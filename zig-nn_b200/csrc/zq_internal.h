@@ -111,6 +111,9 @@ int launch_gemv_f32(const zq_weight* w, const float* x, float* y, uint32_t m_row
 // Tensor-core f32-activation GEMV for m_rows <= 16 (gemv_mma.cu); x must be 16-byte aligned.
 int launch_gemv_mma_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
                         const zq_epilogue* ep, cudaStream_t st);
+// Any row count: passes of up to 16 rows, the pass height chosen so that its activation image fits.
+int launch_gemv_mma_passes_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows,
+                               const zq_epilogue* ep, cudaStream_t st);
 // The same with LayerNorm(x) computed in the kernel's prologue (one activation row; gpt2.zig:541-596).
 int launch_gemv_mma_ln_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
                            const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st);
