@@ -323,6 +323,9 @@ def run_case(args):
         toks = []
         t0 = time.perf_counter()
         for i in range(n_seq):
+            if n_prompt == 0:  # no prefill: every sequence starts from an empty cache with a random token
+                toks.append(int(rng.integers(0, hostmodel.GEMMA3_1B["vocab"])))
+                continue
             toks.append(int(eng.prefill(i, rng.integers(0, hostmodel.GEMMA3_1B["vocab"], size=n_prompt)).argmax().item()))
         torch.cuda.synchronize()
         t1 = time.perf_counter()
@@ -490,7 +493,9 @@ def main():
     # Steps are replayed from a captured launch sequence (one pass over the copies): the host-side call
     # overhead of the Python binding would otherwise be a large part of a 10-35 us step. NCCL's collective
     # stays outside capture; the end-to-end leg below always uses plain calls.
-    seq_len = copies
+    # (one rank: the 170 MB matrix is HBM-cold by size; ten steps per recording, so that consecutive steps
+    # follow each other on the device as the kernels of a decode step do)
+    seq_len = copies if use_dist else 10
     graph = None
     if gather_mode in ("none", "peer"):
         torch.cuda.synchronize()
@@ -578,7 +583,7 @@ def main():
                                world, ", all-gather of outputs: " + gather_mode +
                                (" stores fused into the GEMV epilogue" if getattr(lin, "fused", False) else "")
                                if use_dist else ""),
-                           launch="CUDA graph replay" if graph is not None else "plain calls"),
+                           launch=("CUDA graph replay, %d steps per recording" % seq_len) if graph is not None else "plain calls"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES, "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": local_bytes, "kernel": "gemv_mma1_kernel<q4_0>"},

@@ -699,8 +699,6 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     constexpr uint32_t QUAD = 4 * QB;  // quant bytes of one quad of blocks
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ float pre[1], post[1];
-    __shared__ unsigned int amax_bits;
 
     const uint32_t nbp = (nb + 3u) & ~3u, nq = nbp / 4;
     uint4* frag = reinterpret_cast<uint4*>(smem_raw);  // [block][hi, lo][t]
@@ -710,11 +708,10 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     const int g = lane >> 2, t = lane & 3;
     constexpr uint32_t rows_per_cta = W * 16;
 
-    // sharded: every CTA reads the round before any CTA can finish it (the counter moves only when all
-    // CTAs have arrived at the end of the kernel)
+    // Let the next kernel on the stream be scheduled as CTAs of this one retire: its weight stream can
+    // start while this kernel's last tiles drain. Everything up to the wait below touches only weights.
+    pdl_launch_dependents();
     const bool sharded = pa.world > 1;
-    const uint32_t round = sharded ? pa.sync[0] + 1 : 0;
-    if (sharded) y = pa.y[round & 1u][pa.rank] + pa.row_off;
 
     // Scales of a whole 16-row tile (contiguous in memory) are copied to this warp's shared buffer when
     // the producer enters the tile; two buffers, because the producer is less than one tile ahead.
@@ -771,30 +768,37 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     for (int i = 0; i < D - 1; ++i) producer_step();
     uint32_t c_slot = 0;
 
-    // ---- activations: range prescale, then the fp16 hi / lo fragment image ----
-    if (tid == 0) amax_bits = 0;
-    __syncthreads();
+    // The activations, the result buffer and (sharded) the round counter may belong to the kernel before
+    // this one: wait for it to complete. Sharded: every CTA then reads the round before any CTA can finish
+    // it (the counter moves only when all CTAs have arrived at the end of the kernel).
+    pdl_wait();
+    const uint32_t round = sharded ? pa.sync[0] + 1 : 0;
+    if (sharded) y = pa.y[round & 1u][pa.rank] + pa.row_off;
+
+    // ---- activations: range prescale, then the fp16 hi / lo fragment image. Every warp finds the row's
+    //      largest magnitude by itself (the row is a few KB and stays in L1): no block-wide exchange ----
+    float pre_l[1], ps;
     {
         float amax = 0.0f;
         const float4* xr = reinterpret_cast<const float4*>(x);
-        for (uint32_t i = tid; i < K / 4; i += blockDim.x) {
-            const float4 v = xr[i];
-            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        const uint32_t n4 = K / 4;
+        for (uint32_t i0 = lane; i0 < n4; i0 += 32 * 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = i0 + 32 * u < n4 ? xr[i0 + 32 * u] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v[u].x), fabsf(v[u].y))), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-        if (lane == 0) atomicMax(&amax_bits, __float_as_uint(amax));
-    }
-    __syncthreads();
-    if (tid == 0) {
-        const float amax = __uint_as_float(amax_bits);
         int e = 0;
         if (amax > 0.0f && amax < INFINITY) e = ilogbf(amax) - 13;
-        pre[0] = ldexpf(1.0f, -e);
-        post[0] = ldexpf(1.0f, e);
+        pre_l[0] = ldexpf(1.0f, -e);
+        ps = ldexpf(1.0f, e);
     }
-    __syncthreads();
-    stage_activations<!Q8, !Q8>(x, 1, K, nb, nbp, pre, frag, xsum);
+    stage_activations<!Q8, !Q8>(x, 1, K, nb, nbp, pre_l, frag, xsum);
     __syncthreads();
 
     // This lane feeds MMA column g: part (g & 1) of block (g >> 1) of each quad.
@@ -811,7 +815,6 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     const uint32_t sc_lane = g * sc_row_bytes + t * SB;
     uint32_t saddr = sbuf32 + sc_lane;
     float acc_a = 0.0f, acc_b = 0.0f, accm_a = 0.0f, accm_b = 0.0f;
-    const float ps = post[0];
 
     auto consume = [&](const QuadWords<Q8>& d) {
         lds128_keep(bj0, faddr, pj0);  // one of the four executes: faddr already points at this lane's block
@@ -873,22 +876,15 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
             vb += __shfl_xor_sync(0xFFFFFFFFu, vb, 1);
             va += __shfl_xor_sync(0xFFFFFFFFu, va, 2);
             vb += __shfl_xor_sync(0xFFFFFFFFu, vb, 2);
-            const uint32_t r0 = (uint32_t)(c_tile * rows_per_cta) + warp * 16 + g;
-            if (t == 0) {
-                if (r0 < N) {
-                    const float o = apply_epilogue(va * ps, ep, r0, r0);
-                    y[r0] = o;
-                    if (sharded)
-                        for (uint32_t p = 0; p < pa.world; ++p)
-                            if (p != pa.rank) pa.y[round & 1u][p][pa.row_off + r0] = o;
-                }
-                if (r0 + 8 < N) {
-                    const float o = apply_epilogue(vb * ps, ep, r0 + 8, r0 + 8);
-                    y[r0 + 8] = o;
-                    if (sharded)
-                        for (uint32_t p = 0; p < pa.world; ++p)
-                            if (p != pa.rank) pa.y[round & 1u][p][pa.row_off + r0 + 8] = o;
-                }
+            // all four lanes of a quad hold both sums: lane t = 0 stores row g, lane t = 1 row g + 8, so one
+            // store instruction writes the tile's 16 outputs as 64 contiguous bytes
+            const uint32_t row = (uint32_t)(c_tile * rows_per_cta) + warp * 16 + g + (t == 1 ? 8u : 0u);
+            if (t < 2 && row < N) {
+                const float o = apply_epilogue((t == 1 ? vb : va) * ps, ep, row, row);
+                y[row] = o;
+                if (sharded)
+                    for (uint32_t p = 0; p < pa.world; ++p)
+                        if (p != pa.rank) pa.y[round & 1u][p][pa.row_off + row] = o;
             }
             c_q = 0;
             c_tile += gridDim.x;
@@ -971,10 +967,9 @@ int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs 
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const uint32_t cta_tiles = (w->out_dim + W * 16 - 1) / (W * 16);
     const uint32_t cap = sms * CTAS;
-    kern<<<cta_tiles < cap ? cta_tiles : cap, W * 32, smem, st>>>(
-        w->qs, static_cast<const uint8_t*>(w->sc), x, y, w->out_dim, w->in_dim, w->nb, w->scp, sc_off, ring_off,
-        ep, pa);
-    ZQ_LAUNCH_CHECK();
+    ZQ_CUDA(launch_pdl(kern, dim3(cta_tiles < cap ? cta_tiles : cap), dim3(W * 32), smem, st, w->qs,
+                       static_cast<const uint8_t*>(w->sc), x, y, w->out_dim, w->in_dim, w->nb, w->scp, sc_off,
+                       ring_off, ep, pa));
     return ZQ_OK;
 }
 
