@@ -297,6 +297,11 @@ int zq_gather(float* d_out, const float* d_table, const int32_t* d_idx, uint32_t
               uint32_t embed_dim, zq_stream stream);
 /* dispatch_scale (cuda_ops.zig:236): out[i] = x[i] * s. */
 int zq_scale(float* d_out, const float* d_x, float s, size_t n, zq_stream stream);
+/* d_dst[i] = src[i], n floats, as a kernel. `src` may be page-locked host memory that the device can
+ * address: staging a host activation row this way (instead of a copy-engine transfer) lets the matmul
+ * that follows on the stream start streaming its weights while the row is still on its way. No
+ * counterpart in the reference, whose CUDA path uploads with cuMemcpyHtoD (src/backend/cuda_context.zig:176). */
+int zq_copy_f32(float* d_dst, const float* src, size_t n, zq_stream stream);
 
 /* ------------------------------------------------------------- models */
 

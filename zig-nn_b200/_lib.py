@@ -63,6 +63,7 @@ SIGNATURES = {
     "zq_mul_broadcast": (i, [vp, vp, vp, sz, sz, vp]),
     "zq_gather": (i, [vp, vp, vp, u32, u32, vp]),
     "zq_scale": (i, [vp, vp, f, sz, vp]),
+    "zq_copy_f32": (i, [vp, vp, sz, vp]),
     "zq_gpt2_create": (i, [P(S.Gpt2Config), P(S.Gpt2Weights), vp, P(vp)]),
     "zq_gpt2_free": (i, [vp]),
     "zq_gpt2_reset_cache": (i, [vp]),

@@ -182,7 +182,11 @@ class HostLinear:
         self._graphs = {}
 
     def _launch(self, hx, y_ptr):
-        self._x.copy_(hx.reshape(self.m, self.qw.in_dim), non_blocking=True)
+        if hx.is_pinned():  # a kernel copy: the matmul behind it starts on its weights meanwhile
+            _lib.check(_lib.load().zq_copy_f32(_ptr(self._x), C.c_void_p(hx.data_ptr()), hx.numel(), _stream()),
+                       "zq_copy_f32")
+        else:
+            self._x.copy_(hx.reshape(self.m, self.qw.in_dim), non_blocking=True)
         ep = S.Epilogue(None, 0, None, None)
         rc = _lib.load().zq_matmul(self.qw.handle, _ptr(self._x), y_ptr, self.m, self.act_mode, C.byref(ep),
                                    _ptr(self._ws) if self._need else None, self._need, _stream())

@@ -187,6 +187,16 @@ __global__ void gather_kernel(float* __restrict__ out, const float* __restrict__
     const size_t r = i / dim, c = i - r * dim;
     out[i] = table[(size_t)idx[r] * dim + c];
 }
+// Plain copy as a kernel: unlike a copy-engine transfer it chains with the next kernel by programmatic
+// dependent launch, and its source may be page-locked host memory that the device can address.
+__global__ void __launch_bounds__(256)
+copy_f32_kernel(float* __restrict__ dst, const float* __restrict__ src, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = src[i];
+}
+
 __global__ void scale_kernel(float* __restrict__ out, const float* __restrict__ x, float s, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = x[i] * s;
@@ -1028,6 +1038,14 @@ int zq_gather(float* d_out, const float* d_table, const int32_t* d_idx, uint32_t
     gather_kernel<<<grid1d((size_t)num_indices * embed_dim, 256), 256, 0, as_stream(stream)>>>(
         d_out, d_table, d_idx, num_indices, embed_dim);
     ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+int zq_copy_f32(float* d_dst, const float* src, size_t n, zq_stream stream) {
+    if (!d_dst || !src) return ZQ_ERR_BAD_ARG;
+    if (n == 0) return ZQ_OK;
+    const unsigned grid = grid1d(n, 256) < 64u ? grid1d(n, 256) : 64u;
+    ZQ_CUDA(launch_pdl(copy_f32_kernel, dim3(grid), dim3(256), 0, as_stream(stream), d_dst, src, n));
     return ZQ_OK;
 }
 
