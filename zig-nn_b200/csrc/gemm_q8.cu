@@ -9,9 +9,12 @@
 // a register, so the result is bit-identical to running the decode kernel row by row.
 //
 // Tile: 128 weight rows (8 warps x 16) x 64 activation rows per CTA; K advances by one quad of blocks
-// (128 values). The quantised activations of a quad (64 rows x 128 bytes, their scales and sums) are
-// staged in shared memory with cp.async, double-buffered; 16-byte halves of a (row, block) entry are
-// swapped for rows with bit 2 set so that the fragment loads are free of bank conflicts.
+// (128 values). Everything a quad needs travels through a ring of D shared-memory stages filled with
+// cp.async, D - 1 quads ahead of the multiplications: the quantised activations (64 rows x 128 bytes, their
+// scales and sums; 16-byte halves of a (row, block) entry are swapped for rows with bit 2 set so that the
+// fragment loads are free of bank conflicts) and, per lane, the packed weight words and scales of its two
+// rows. The small CTA shapes used for matrices with few rows have only a few warps per SM, so the depth of
+// this ring — not occupancy — is what hides the memory latency there.
 #include "zq_internal.h"
 
 namespace zq {
@@ -56,7 +59,37 @@ __device__ __forceinline__ uint32_t pick4(const uint4& v, int j) {
     return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// Bytes of one ring stage: activations of the CTA, then per warp the packed words (512 bytes per array:
+// rows g, rows g + 8, and for q8_0 their second halves) and the scales (rows g, rows g + 8).
 template <int TYPE, int W, int NT>
+struct QgStage {
+    static constexpr uint32_t kXq = 4 * NT * 8 * 32;   // 4 blocks x BM rows x 32 int8
+    static constexpr uint32_t kSc = 4 * NT * 8 * 4;    // 4 blocks x BM rows x f32 (and the same for the sums)
+    static constexpr uint32_t kAct = kXq + 2 * kSc;
+    static constexpr uint32_t kWq = TYPE == ZQ_TYPE_Q8_0 ? 2048 : 1024;
+    static constexpr uint32_t kWsHalf = TYPE == ZQ_TYPE_Q4_1 ? 512 : 256;
+    static constexpr uint32_t kWarp = kWq + 2 * kWsHalf;
+    static constexpr uint32_t kBytes = (kAct + W * kWarp + 127u) & ~127u;
+};
+
+template <int TYPE, int W, int NT, int D>
 __global__ void __launch_bounds__(W * 32)
 gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const int8_t* __restrict__ xq,
                const float* __restrict__ xscale, const int32_t* __restrict__ xqsum, float* __restrict__ y,
@@ -65,10 +98,9 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QB = Q8 ? 32 : 16;
     constexpr uint32_t QUAD = 4 * QB;
+    using S = QgStage<TYPE, W, NT>;
     constexpr int QG_BN = W * 16, QG_BM = NT * 8, QG_NT = NT;
-    constexpr uint32_t QG_XQ_BYTES = 4 * QG_BM * 32;  // 4 blocks x BM rows x 32 int8
-    constexpr uint32_t QG_SC_BYTES = 4 * QG_BM * 4;   // 4 blocks x BM rows x f32 (and the same for the sums)
-    constexpr uint32_t QG_STAGE = QG_XQ_BYTES + 2 * QG_SC_BYTES;
+    constexpr uint32_t QG_XQ_BYTES = S::kXq, QG_SC_BYTES = S::kSc, QG_STAGE = S::kBytes;
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t smem32 = (uint32_t)__cvta_generic_to_shared(smem);
 
@@ -77,8 +109,17 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     const uint32_t nbp = (nb + 3u) & ~3u, nq = nbp / 4;
     const uint32_t n0 = blockIdx.x * QG_BN + warp * 16, m0 = blockIdx.y * QG_BM;
 
-    // activations of quad q -> stage: xq entries [blk][row][32 bytes] (16-byte halves swapped when row & 4),
-    // scales [blk][row], sums [blk][row]. Rows >= M and blocks >= nb are zero-filled (never used for output).
+    const uint32_t row_a = min(n0 + g, N - 1), row_b = min(n0 + g + 8, N - 1);
+    const uint8_t* pa = qs + (size_t)row_a * nbp * QB + 16 * t;
+    const uint8_t* pb = qs + (size_t)row_b * nbp * QB + 16 * t;
+    const uint8_t* sa = sc + (size_t)row_a * scp * (Q41 ? 4 : 2);
+    const uint8_t* sb = sc + (size_t)row_b * scp * (Q41 ? 4 : 2);
+    const uint32_t wring = smem32 + S::kAct + warp * S::kWarp;  // this warp's part of stage 0
+
+    // Quad q -> stage. Activations: xq entries [blk][row][32 bytes] (16-byte halves swapped when row & 4),
+    // scales [blk][row], sums [blk][row]; rows >= M and blocks >= nb are zero-filled (never used for output).
+    // Weights: every lane copies the 16-byte pieces and the scales of its own two rows and reads the same
+    // slots back later, so they need no synchronisation beyond cp.async.wait_group.
     auto issue = [&](uint32_t stage, uint32_t q) {
         const uint32_t base = smem32 + stage * QG_STAGE;
         for (uint32_t idx = tid; idx < 8u * QG_BM; idx += W * 32) {  // (blk, row, half)
@@ -96,14 +137,21 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
             cp_async4_zfill(base + QG_XQ_BYTES + (b * QG_BM + r) * 4, xscale + o, ok ? 4u : 0u);
             cp_async4_zfill(base + QG_XQ_BYTES + QG_SC_BYTES + (b * QG_BM + r) * 4, xqsum + o, ok ? 4u : 0u);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        const uint32_t wb = wring + stage * QG_STAGE;
+        cp_async16(wb + lane * 16, pa + (size_t)q * QUAD);
+        cp_async16(wb + 512 + lane * 16, pb + (size_t)q * QUAD);
+        if (Q8) {
+            cp_async16(wb + 1024 + lane * 16, pa + (size_t)q * QUAD + 64);
+            cp_async16(wb + 1536 + lane * 16, pb + (size_t)q * QUAD + 64);
+        }
+        if (Q41) {
+            cp_async16(wb + S::kWq + lane * 16, reinterpret_cast<const uint4*>(sa) + q);
+            cp_async16(wb + S::kWq + S::kWsHalf + lane * 16, reinterpret_cast<const uint4*>(sb) + q);
+        } else {
+            cp_async8(wb + S::kWq + lane * 8, reinterpret_cast<const uint2*>(sa) + q);
+            cp_async8(wb + S::kWq + S::kWsHalf + lane * 8, reinterpret_cast<const uint2*>(sb) + q);
+        }
     };
-
-    const uint32_t row_a = min(n0 + g, N - 1), row_b = min(n0 + g + 8, N - 1);
-    const uint8_t* pa = qs + (size_t)row_a * nbp * QB + 16 * t;
-    const uint8_t* pb = qs + (size_t)row_b * nbp * QB + 16 * t;
-    const uint8_t* sa = sc + (size_t)row_a * scp * (Q41 ? 4 : 2);
-    const uint8_t* sb = sc + (size_t)row_b * scp * (Q41 ? 4 : 2);
 
     float run[QG_NT][4];
 #pragma unroll
@@ -114,73 +162,59 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     const uint32_t frag_lo = ((uint32_t)g * 2 + (0u ^ swap)) * 16 + t * 4;   // word t
     const uint32_t frag_hi = ((uint32_t)g * 2 + (1u ^ swap)) * 16 + t * 4;   // word 4 + t
 
-    // this lane's packed words and raw scales of one quad; the next quad's are loaded while the current one
-    // is being multiplied
-    struct QuadW {
-        uint4 wa, wb, wa2, wb2, sa4, sb4;
-    };
-    auto load_quad = [&](QuadW& d, uint32_t q) {
-        d.wa = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD));
-        d.wb = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD));
-        if (Q8) {
-            d.wa2 = __ldg(reinterpret_cast<const uint4*>(pa + (size_t)q * QUAD + 64));
-            d.wb2 = __ldg(reinterpret_cast<const uint4*>(pb + (size_t)q * QUAD + 64));
-        }
-        if (Q41) {
-            d.sa4 = __ldg(reinterpret_cast<const uint4*>(sa) + q);
-            d.sb4 = __ldg(reinterpret_cast<const uint4*>(sb) + q);
-        } else {
-            const uint2 va = __ldg(reinterpret_cast<const uint2*>(sa) + q);
-            const uint2 vb = __ldg(reinterpret_cast<const uint2*>(sb) + q);
-            d.sa4.x = va.x; d.sa4.y = va.y;
-            d.sb4.x = vb.x; d.sb4.y = vb.y;
-        }
-    };
-    QuadW cur, nxt;
-    load_quad(cur, 0);
-    issue(0, 0);
+    // group number n holds quad n (an empty group when the row has no such quad)
+#pragma unroll 1
+    for (uint32_t i = 0; i + 1 < (uint32_t)D; ++i) {
+        if (i < nq) issue(i, i);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    uint32_t stage = 0, p_stage = D - 1;
+#pragma unroll 1
     for (uint32_t q = 0; q < nq; ++q) {
-        const uint32_t stage = q & 1u;
-        if (q + 1 < nq) {
-            issue(stage ^ 1u, q + 1);
-            load_quad(nxt, q + 1);
-        } else {
-            asm volatile("cp.async.commit_group;" ::: "memory");
+        if (q + D - 1 < nq) issue(p_stage, q + D - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        p_stage = p_stage + 1 == (uint32_t)D ? 0 : p_stage + 1;
+        asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");  // quad q has landed
+        __syncthreads();
+
+        const uint32_t base = smem32 + stage * QG_STAGE;
+        const uint32_t wb = wring + stage * QG_STAGE;
+        const uint4 wa = lds128(wb + lane * 16), wbv = lds128(wb + 512 + lane * 16);
+        uint4 wa2 = wa, wb2 = wbv;
+        if (Q8) {
+            wa2 = lds128(wb + 1024 + lane * 16);
+            wb2 = lds128(wb + 1536 + lane * 16);
         }
-        const uint4 wa = cur.wa, wb = cur.wb;
-        const uint4 wa2 = Q8 ? cur.wa2 : cur.wa, wb2 = Q8 ? cur.wb2 : cur.wb;
         float da[4], db[4], ma[4], mb[4];
         if (Q41) {
+            const uint4 sa4 = lds128(wb + S::kWq + lane * 16), sb4 = lds128(wb + S::kWq + S::kWsHalf + lane * 16);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const uint32_t ua = pick4(cur.sa4, b), ub = pick4(cur.sb4, b);
+                const uint32_t ua = pick4(sa4, b), ub = pick4(sb4, b);
                 const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&ua));
                 const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&ub));
                 da[b] = fa.x; ma[b] = fa.y;
                 db[b] = fb.x; mb[b] = fb.y;
             }
         } else {
-            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&cur.sa4.x));
-            const float2 a23 = __half22float2(*reinterpret_cast<const __half2*>(&cur.sa4.y));
-            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&cur.sb4.x));
-            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&cur.sb4.y));
+            const uint2 sa2 = lds64(wb + S::kWq + lane * 8), sb2 = lds64(wb + S::kWq + S::kWsHalf + lane * 8);
+            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&sa2.x));
+            const float2 a23 = __half22float2(*reinterpret_cast<const __half2*>(&sa2.y));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&sb2.x));
+            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&sb2.y));
             da[0] = a01.x; da[1] = a01.y; da[2] = a23.x; da[3] = a23.y;
             db[0] = b01.x; db[1] = b01.y; db[2] = b23.x; db[3] = b23.y;
 #pragma unroll
             for (int b = 0; b < 4; ++b) ma[b] = mb[b] = 0.0f;
         }
-        asm volatile("cp.async.wait_group 1;" ::: "memory");  // stage q has landed (q + 1 may still be in flight)
-        __syncthreads();
-
-        const uint32_t base = smem32 + stage * QG_STAGE;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             if (q * 4 + b >= nb) break;  // row padding: no term is added for blocks that do not exist
             uint32_t a0, a1, a2, a3;
             if (Q8) {
-                a0 = pick4(wa, b); a1 = pick4(wb, b); a2 = pick4(wa2, b); a3 = pick4(wb2, b);
+                a0 = pick4(wa, b); a1 = pick4(wbv, b); a2 = pick4(wa2, b); a3 = pick4(wb2, b);
             } else {
-                const uint32_t ua = pick4(wa, b), ub = pick4(wb, b);
+                const uint32_t ua = pick4(wa, b), ub = pick4(wbv, b);
                 a0 = ua & 0x0F0F0F0Fu; a1 = ub & 0x0F0F0F0Fu;
                 a2 = (ua >> 4) & 0x0F0F0F0Fu; a3 = (ub >> 4) & 0x0F0F0F0Fu;
             }
@@ -215,8 +249,8 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
                 run[j][3] = __fadd_rn(run[j][3], t3);
             }
         }
-        __syncthreads();  // the stage is overwritten by the copies issued in the next iteration
-        cur = nxt;
+        __syncthreads();  // this stage is overwritten by the copies issued in the next iteration
+        stage = stage + 1 == (uint32_t)D ? 0 : stage + 1;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
 
@@ -239,14 +273,17 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     }
 }
 
-template <int TYPE, int W, int NT>
+template <int TYPE, int W, int NT, int D>
 int launch_cfg(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum, float* y, uint32_t M,
                QgEpilogue ep, cudaStream_t st) {
     const dim3 grid((w->out_dim + W * 16 - 1) / (W * 16), (M + NT * 8 - 1) / (NT * 8));
     if (grid.y > 65535u) return ZQ_ERR_LIMIT;
-    const size_t smem = 2 * (size_t)(4 * NT * 8 * 32 + 2 * 4 * NT * 8 * 4);
-    gemm_q8_kernel<TYPE, W, NT><<<grid, W * 32, smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), xq, xs, xsum,
-                                                            y, w->out_dim, w->in_dim, M, w->nb, w->scp, ep);
+    const size_t smem = (size_t)D * QgStage<TYPE, W, NT>::kBytes;
+    auto kern = gemm_q8_kernel<TYPE, W, NT, D>;
+    if (smem > 48 * 1024)
+        ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, W * 32, smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), xq, xs, xsum, y, w->out_dim,
+                                     w->in_dim, M, w->nb, w->scp, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -256,14 +293,14 @@ int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int3
                QgEpilogue ep, cudaStream_t st) {
     const uint64_t sms = (uint64_t)sm_count();
     const uint64_t big = (uint64_t)((w->out_dim + 127) / 128) * ((M + 63) / 64);
-    if (big >= sms) return launch_cfg<TYPE, 8, 8>(w, xq, xs, xsum, y, M, ep, st);
+    if (big >= sms) return launch_cfg<TYPE, 8, 8, 3>(w, xq, xs, xsum, y, M, ep, st);
     const uint64_t mid = (uint64_t)((w->out_dim + 31) / 32) * ((M + 63) / 64);
-    if (mid >= sms) return launch_cfg<TYPE, 2, 8>(w, xq, xs, xsum, y, M, ep, st);
+    if (mid >= sms) return launch_cfg<TYPE, 2, 8, 4>(w, xq, xs, xsum, y, M, ep, st);
     // few weight rows: the running sums are a serial chain over K per output, so only more (smaller) warps
     // tiles shorten the launch
     const uint64_t small = (uint64_t)((w->out_dim + 31) / 32) * ((M + 15) / 16);
-    if (small >= 2 * sms) return launch_cfg<TYPE, 2, 2>(w, xq, xs, xsum, y, M, ep, st);
-    return launch_cfg<TYPE, 1, 1>(w, xq, xs, xsum, y, M, ep, st);
+    if (small >= 2 * sms) return launch_cfg<TYPE, 2, 2, 6>(w, xq, xs, xsum, y, M, ep, st);
+    return launch_cfg<TYPE, 1, 1, 8>(w, xq, xs, xsum, y, M, ep, st);
 }
 
 }  // namespace
