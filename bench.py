@@ -585,7 +585,9 @@ def main():
                                if use_dist else ""),
                            launch=("CUDA graph replay, %d steps per recording" % seq_len) if graph is not None else "plain calls"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES, "peak_kind": peak_kind,
+                         # ncu capture of the full matrix; a shard's launch is scaled by its rows
+                         "traffic": int(NCU_TRAFFIC_BYTES * local_bytes / algorithmic_bytes(q, n, k)),
+                         "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": local_bytes, "kernel": "gemv_mma1_kernel<q4_0>"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k, "d2h_bytes_per_step": hy.numel() * 4},
             "gpu_launches": args.steps * (1 if gather_mode != "peer" or getattr(lin, "fused", False) else 3),

@@ -162,6 +162,10 @@ gemm_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     const uint32_t frag_lo = ((uint32_t)g * 2 + (0u ^ swap)) * 16 + t * 4;   // word t
     const uint32_t frag_hi = ((uint32_t)g * 2 + (1u ^ swap)) * 16 + t * 4;   // word 4 + t
 
+    // the quantised activations come from the kernel before this one
+    pdl_launch_dependents();
+    pdl_wait();
+
     // group number n holds quad n (an empty group when the row has no such quad)
 #pragma unroll 1
     for (uint32_t i = 0; i + 1 < (uint32_t)D; ++i) {
@@ -282,9 +286,8 @@ int launch_cfg(const zq_weight* w, const int8_t* xq, const float* xs, const int3
     auto kern = gemm_q8_kernel<TYPE, W, NT, D>;
     if (smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, W * 32, smem, st>>>(w->qs, static_cast<const uint8_t*>(w->sc), xq, xs, xsum, y, w->out_dim,
-                                     w->in_dim, M, w->nb, w->scp, ep);
-    ZQ_LAUNCH_CHECK();
+    ZQ_CUDA(launch_pdl(kern, grid, dim3(W * 32), smem, st, w->qs, static_cast<const uint8_t*>(w->sc), xq, xs, xsum,
+                       y, w->out_dim, w->in_dim, M, w->nb, w->scp, ep));
     return ZQ_OK;
 }
 

@@ -588,13 +588,15 @@ attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc
     // k_new / v_new: this step's key and value rows are not in the caches yet. The first CTA of each kv
     // head stores them (gpt2.zig:812-816); the score of the current position reads the new key directly.
     const uint32_t pos = kv_start + kv_len - 1;
+    // A CTA takes the 16-key tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the window.
     const bool writer = k_new != nullptr && blockIdx.x == 0 && h % group == 0;
     const bool in_window = blockIdx.x * 16 < kv_len;
     if (!in_window && !writer) return;
     const float* qh = q + (size_t)h * head_dim;
     const float* knew = k_new ? k_new + (size_t)kvh * head_dim : nullptr;
     if (nr.q_norm_w != nullptr) {
-        const bool need_k = writer || (in_window && blockIdx.x * 16 + 16 > kv_len - 1);
+        // the new key is needed by the writer and by the CTA whose tiles include the last position
+        const bool need_k = writer || (in_window && ((kv_len - 1) / 16) % gridDim.x == blockIdx.x);
         float* qn = qk;
         float* kn = qk + head_dim;
         for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) {
@@ -636,23 +638,26 @@ attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc
     }
     if (!in_window) return;
     const uint32_t pp = threadIdx.x >> 4, l = threadIdx.x & 15;
-    const uint32_t p = blockIdx.x * 16 + pp;
     const uint32_t dim16 = head_dim & ~15u;
-    const uint32_t pc = min(p, kv_len - 1);
-    const float* kr = (k_new != nullptr && pc == kv_len - 1)
-                          ? knew
-                          : kc + (size_t)(kv_start + pc) * kv_dim + (size_t)kvh * head_dim;
-    float acc = 0.0f;
-    for (uint32_t d = l; d < dim16; d += 16) acc = __fadd_rn(acc, __fmul_rn(qh[d], kr[d]));
-    part[pp][l] = acc;
-    __syncthreads();
-    if (l == 0 && p < kv_len) {
-        float s = part[pp][0];
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)head_dim));
+    for (uint32_t p0 = blockIdx.x * 16; p0 < kv_len; p0 += gridDim.x * 16) {
+        const uint32_t p = p0 + pp;
+        const uint32_t pc = min(p, kv_len - 1);
+        const float* kr = (k_new != nullptr && pc == kv_len - 1)
+                              ? knew
+                              : kc + (size_t)(kv_start + pc) * kv_dim + (size_t)kvh * head_dim;
+        float acc = 0.0f;
+        for (uint32_t d = l; d < dim16; d += 16) acc = __fadd_rn(acc, __fmul_rn(qh[d], kr[d]));
+        part[pp][l] = acc;
+        __syncthreads();
+        if (l == 0 && p < kv_len) {
+            float s = part[pp][0];
 #pragma unroll
-        for (int j = 1; j < 16; ++j) s = __fadd_rn(s, part[pp][j]);
-        for (uint32_t d = dim16; d < head_dim; ++d) s = __fadd_rn(s, __fmul_rn(qh[d], kr[d]));
-        const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)head_dim));
-        scores[(size_t)h * kv_len + p] = __fmul_rn(s, scale);
+            for (int j = 1; j < 16; ++j) s = __fadd_rn(s, part[pp][j]);
+            for (uint32_t d = dim16; d < head_dim; ++d) s = __fadd_rn(s, __fmul_rn(qh[d], kr[d]));
+            scores[(size_t)h * kv_len + p] = __fmul_rn(s, scale);
+        }
+        __syncthreads();  // `part` is rewritten by the next tile
     }
 }
 
@@ -852,7 +857,13 @@ int launch_attention_step(const float* q, float* kc, float* vc, const float* k_n
     const size_t smem = (size_t)max_len * sizeof(float);
     const int tail = (flags & ZQ_ATTN_GPT2_SOFTMAX) ? 1 : 0;
     const uint32_t scores_stride = n_head * max_len;
-    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3((max_len + 15) / 16, n_head, rows), dim3(256), smem_scores,
+    // One CTA per 16-key tile when few rows are in flight (a decode step: parallelism comes from the tiles);
+    // with many rows (batched sequences, prefill chunks) a CTA walks over several tiles, which saves
+    // launching thousands of CTAs that find their tile outside the row's window and repeats the per-CTA
+    // q / k preparation less often.
+    uint32_t tiles_x = (max_len + 15) / 16;
+    if (rows >= 16 && tiles_x > 8) tiles_x = 8;
+    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3(tiles_x, n_head, rows), dim3(256), smem_scores,
                        st, q, kc, vc, k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window, q_stride,
                        scores_stride, row_pos, cache_stride, nr));
     const dim3 grid(n_head, (head_dim + kAttnDims - 1) / kAttnDims, rows);
