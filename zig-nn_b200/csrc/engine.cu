@@ -420,7 +420,6 @@ struct zq_gemma3 {
     // several independent sequences (batched decode): each has its own cache slot and position
     uint32_t n_seq = 1;
     uint32_t* d_pos = nullptr;            // [n_seq] positions of a batched decode step
-    unsigned int* d_tail = nullptr;       // arrival counter of the GEMVs that end with a norm (0 between launches)
     std::vector<uint32_t> seq_lens;       // host copy, [n_seq]
     float* logits_batch = nullptr;        // [n_seq][vocab]
     ~zq_gemma3() {
@@ -503,18 +502,10 @@ static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st
                                         cache_stride, fused_qk ? b.q_norm_w : nullptr, b.k_norm_w, m->freqs, C.rms_eps,
                                         st)))
             return rc;
-        // A decode step lets the last CTA of the projection run the norms that follow it (one launch less);
-        // matrices that the tail kernel does not take fall back to the two launches.
-        const bool tail = T == 1 && !batch;
-        rc = tail ? launch_gemv_q8_norm_tail(b.o, m->xq, m->xscale, m->xsum, m->proj, m->d_tail, b.post_attn_norm_w,
-                                             m->x, b.ffn_norm_w, C.rms_eps, m->xq, m->xscale, m->xsum, st)
-                  : ZQ_ERR_UNSUPPORTED;
-        if (rc == ZQ_ERR_UNSUPPORTED) {
-            if ((rc = gemma_linear(m, b.o, m->proj, E, T, st))) return rc;
-            rc = launch_norm_quant(m->proj, b.post_attn_norm_w, m->x, b.ffn_norm_w, E, C.rms_eps, m->xq, m->xscale,
-                                   m->xsum, T, E, st);
-        }
-        if (rc) return rc;
+        if ((rc = gemma_linear(m, b.o, m->proj, E, T, st))) return rc;
+        if ((rc = launch_norm_quant(m->proj, b.post_attn_norm_w, m->x, b.ffn_norm_w, E, C.rms_eps, m->xq,
+                                    m->xscale, m->xsum, T, E, st)))
+            return rc;
         // FFN block (gemma3.zig:734-773)
         if (b.gate_up) {
             if ((rc = gemma_linear(m, b.gate_up, m->gu, 2 * F, T, st))) return rc;
@@ -523,21 +514,16 @@ static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st
             if ((rc = gemma_linear(m, b.up, m->gu + F, 2 * F, T, st))) return rc;
         }
         if ((rc = launch_gelu_mul_quant(m->gu, m->gu + F, F, m->xq, m->xscale, m->xsum, T, 2 * F, st))) return rc;
+        if ((rc = gemma_linear(m, b.down, m->ffn, E, T, st))) return rc;
         const float* next_norm = l + 1 < C.layer ? m->blocks[l + 1].attn_norm_w
                                  : (variant != STEP_CACHE_ONLY ? m->output_norm_w : nullptr);
-        rc = (tail && next_norm)
-                 ? launch_gemv_q8_norm_tail(b.down, m->xq, m->xscale, m->xsum, m->ffn, m->d_tail, b.post_ffw_norm_w,
-                                            m->x, next_norm, C.rms_eps, m->xq, m->xscale, m->xsum, st)
-                 : ZQ_ERR_UNSUPPORTED;
-        if (rc == ZQ_ERR_UNSUPPORTED) {
-            if ((rc = gemma_linear(m, b.down, m->ffn, E, T, st))) return rc;
-            if (next_norm)
-                rc = launch_norm_quant(m->ffn, b.post_ffw_norm_w, m->x, next_norm, E, C.rms_eps, m->xq, m->xscale,
-                                       m->xsum, T, E, st);
-            else
-                rc = zq_rms_norm_residual(m->ffn, b.post_ffw_norm_w, m->x, E, T, C.rms_eps, st);
+        if (next_norm) {
+            if ((rc = launch_norm_quant(m->ffn, b.post_ffw_norm_w, m->x, next_norm, E, C.rms_eps, m->xq, m->xscale,
+                                        m->xsum, T, E, st)))
+                return rc;
+        } else if ((rc = zq_rms_norm_residual(m->ffn, b.post_ffw_norm_w, m->x, E, T, C.rms_eps, st))) {
+            return rc;
         }
-        if (rc) return rc;
     }
     if (variant != STEP_CACHE_ONLY && batch) {  // every sequence's logits
         if ((rc = gemma_linear(m, m->token_embd, m->logits_batch, C.vocab, T, st))) return rc;
@@ -703,8 +689,6 @@ int zq_gemma3_create_batch(const zq_gemma3_config* cfg, const zq_gemma3_weights*
     TRY(m->arena.alloc_n(&m->d_state, 4));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, C.ctx));
-    TRY(m->arena.alloc_n(&m->d_tail, 1));
-    cudaMemsetAsync(m->d_tail, 0, sizeof(unsigned int), st);
 #undef TRY
     cudaError_t e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) {

@@ -10,34 +10,16 @@
 // block 4q + t in lane t. That lane applies the block's scales and stores the f32 term to shared
 // memory. When every block of a row has its term, one lane adds them in block order. Because only
 // the terms (not partial sums) cross warps, K can be split over warps without changing a single bit.
-#include "step_common.cuh"
 #include "zq_internal.h"
 
 namespace zq {
 namespace {
-
-using namespace step_common;
 
 struct EpilogueArgs {
     const float* bias;
     const float* mul;
     const float* residual;
     int gelu;
-};
-
-// Optional work of the CTA that finishes last (Gemma decode step, gemma3.zig:725-737, 768-773): once
-// the whole output row y[N] exists,  res += rms_norm(y, w1);  h = rms_norm(res, w2);  h quantised
-// (quantize_row_q8) into q / scale / sum — the arithmetic of norm_quant_kernel<true> in ops.cu, which this
-// replaces as a separate launch. `counter` is a device word that is 0 between launches.
-struct NormTail {
-    unsigned int* counter;  // nullptr: no tail
-    const float* w1;
-    float* res;
-    const float* w2;
-    float eps;
-    int8_t* q;
-    float* scale;
-    int32_t* sum;
 };
 
 __device__ __forceinline__ float gelu_tanh(float v) {
@@ -77,8 +59,7 @@ template <int TYPE>
 __global__ void __launch_bounds__(512)
 gemv_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const int8_t* __restrict__ xq,
                const float* __restrict__ xscale, const int32_t* __restrict__ xqsum, float* __restrict__ y,
-               uint32_t N, uint32_t nb, uint32_t scp, uint32_t WR, uint32_t KS, int prefetch, EpilogueArgs ep,
-               NormTail nt) {
+               uint32_t N, uint32_t nb, uint32_t scp, uint32_t WR, uint32_t KS, int prefetch, EpilogueArgs ep) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QB = Q8 ? 32 : 16;
@@ -218,37 +199,6 @@ gemv_q8_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
             if (row < N) y[row] = apply_epilogue(run, ep, row);
         }
         if (KS > 1) __syncthreads(); else __syncwarp();  // terms are rewritten by the next tile
-    }
-
-    if (nt.counter != nullptr) {
-        __shared__ unsigned int s_last;
-        __shared__ float part[16];
-        __shared__ float bc;
-        __syncthreads();  // this CTA's rows of y are stored
-        if (tid == 0) {
-            __threadfence();
-            s_last = atomicAdd(nt.counter, 1u) == gridDim.x - 1 ? 1u : 0u;
-        }
-        __syncthreads();
-        if (s_last) {  // every CTA has stored its rows and fenced: y is complete
-            __threadfence();
-            float* row = reinterpret_cast<float*>(smem_raw);  // the GEMV's buffers are no longer needed
-            for (uint32_t i = tid; i < N; i += blockDim.x) row[i] = __ldcg(y + i);
-            __syncthreads();
-            float ss = sumsq_lanes16(row, N, part, &bc);
-            float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)N), nt.eps)));
-            for (uint32_t i = tid; i < N; i += blockDim.x) {
-                const float r = __fadd_rn(nt.res[i], __fmul_rn(__fmul_rn(row[i], inv), nt.w1[i]));
-                nt.res[i] = r;
-                row[i] = r;
-            }
-            __syncthreads();
-            ss = sumsq_lanes16(row, N, part, &bc);
-            inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)N), nt.eps)));
-            for (uint32_t i = tid; i < N; i += blockDim.x)  // N is a multiple of 32: whole warps
-                quantize_block_warp(__fmul_rn(__fmul_rn(row[i], inv), nt.w2[i]), i >> 5, lane, nt.q, nt.scale, nt.sum);
-            if (tid == 0) *nt.counter = 0;
-        }
     }
 }
 
@@ -499,12 +449,11 @@ int launch_rows(const zq_weight* w, const int8_t* xq, const float* xs, const int
 
 template <int TYPE>
 int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum, float* y,
-               EpilogueArgs ep, NormTail nt, cudaStream_t st) {
+               EpilogueArgs ep, cudaStream_t st) {
     const uint32_t tiles = (w->out_dim + 15) / 16;
     const uint32_t sms = (uint32_t)sm_count();
     const uint32_t nq = w->nbp / 4;
     if (tiles >= sms * 2 * kRowsWarps) {  // enough row tiles for whole rows per warp: the ring kernel
-        if (nt.counter) return ZQ_ERR_UNSUPPORTED;  // the tail lives in the K-split kernel only
         const int rc = launch_rows<TYPE>(w, xq, xs, xsum, y, ep, st);
         if (rc != ZQ_ERR_LIMIT) return rc;
     }
@@ -518,11 +467,7 @@ int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int3
     const size_t fixed = (size_t)nq * 4 * 16 * 2 + (size_t)w->nbp * 8;
     auto smem_for = [&](uint32_t r) { return fixed + (size_t)r * 16 * (w->nbp + 1) * sizeof(float); };
     while (wr > 1 && smem_for(wr) > 96 * 1024) wr /= 2;
-    size_t smem = smem_for(wr);
-    if (nt.counter) {  // the last CTA keeps the output row (out_dim floats) where the GEMV's buffers were
-        if (w->out_dim % 32) return ZQ_ERR_UNSUPPORTED;
-        if (smem < (size_t)w->out_dim * sizeof(float)) smem = (size_t)w->out_dim * sizeof(float);
-    }
+    const size_t smem = smem_for(wr);
     if (smem > 200 * 1024) return ZQ_ERR_LIMIT;
     auto kern = gemv_q8_kernel<TYPE>;
     if (smem > 48 * 1024)
@@ -536,7 +481,7 @@ int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int3
     const int prefetch = w->bytes <= (size_t)48 << 20;
     ZQ_CUDA(launch_pdl(kern, dim3(cta_tiles < cap ? cta_tiles : cap), dim3(wr * ks * 32), smem, st, w->qs,
                        static_cast<const uint8_t*>(w->sc), xq, xs, xsum, y, w->out_dim, w->nb, w->scp, wr, ks,
-                       prefetch, ep, nt));
+                       prefetch, ep));
     return ZQ_OK;
 }
 
@@ -554,35 +499,16 @@ int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, co
             a.residual = ep->d_residual ? ep->d_residual + yo : nullptr;
         }
         const int8_t* q = xq + (size_t)m * w->in_dim;
-        const NormTail none{};
         int rc;
         switch (w->type) {
-            case ZQ_TYPE_Q4_0: rc = launch_one<ZQ_TYPE_Q4_0>(w, q, xscale + bo, xsum + bo, y + yo, a, none, st); break;
-            case ZQ_TYPE_Q4_1: rc = launch_one<ZQ_TYPE_Q4_1>(w, q, xscale + bo, xsum + bo, y + yo, a, none, st); break;
-            case ZQ_TYPE_Q8_0: rc = launch_one<ZQ_TYPE_Q8_0>(w, q, xscale + bo, xsum + bo, y + yo, a, none, st); break;
+            case ZQ_TYPE_Q4_0: rc = launch_one<ZQ_TYPE_Q4_0>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
+            case ZQ_TYPE_Q4_1: rc = launch_one<ZQ_TYPE_Q4_1>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
+            case ZQ_TYPE_Q8_0: rc = launch_one<ZQ_TYPE_Q8_0>(w, q, xscale + bo, xsum + bo, y + yo, a, st); break;
             default: return ZQ_ERR_UNSUPPORTED;
         }
         if (rc != ZQ_OK) return rc;
     }
     return ZQ_OK;
-}
-
-// One activation row; when the output row is complete the last CTA runs
-//   res += rms_norm(y, w1);  quantise(rms_norm(res, w2)) -> q / scale / sum
-// (q / scale / sum may be the buffers the activations came from: every CTA has read them by then).
-// ZQ_ERR_UNSUPPORTED when the matrix is of the many-row-tiles kind or out_dim is not a multiple of 32.
-int launch_gemv_q8_norm_tail(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum,
-                             float* y, unsigned int* counter, const float* w1, float* res, const float* w2,
-                             float eps, int8_t* q, float* scale, int32_t* sum, cudaStream_t st) {
-    if (!counter || !w1 || !res || !w2 || !q || !scale || !sum) return ZQ_ERR_BAD_ARG;
-    const EpilogueArgs a{nullptr, nullptr, nullptr, 0};
-    const NormTail nt{counter, w1, res, w2, eps, q, scale, sum};
-    switch (w->type) {
-        case ZQ_TYPE_Q4_0: return launch_one<ZQ_TYPE_Q4_0>(w, xq, xscale, xsum, y, a, nt, st);
-        case ZQ_TYPE_Q4_1: return launch_one<ZQ_TYPE_Q4_1>(w, xq, xscale, xsum, y, a, nt, st);
-        case ZQ_TYPE_Q8_0: return launch_one<ZQ_TYPE_Q8_0>(w, xq, xscale, xsum, y, a, nt, st);
-        default: return ZQ_ERR_UNSUPPORTED;
-    }
 }
 
 }  // namespace zq

@@ -125,11 +125,6 @@ int launch_gemv_q8(const zq_weight* w, const int8_t* xq, const float* xscale, co
                    float* y, uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
 int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, int8_t* q,
                             float* scale, int32_t* sum, cudaStream_t st);
-// launch_gemv_q8 for one row with the Gemma step's post-norm + residual + pre-norm + quantise run by the last
-// CTA (gemv_q8.cu); ZQ_ERR_UNSUPPORTED when this matrix does not go through the kernel that has the tail.
-int launch_gemv_q8_norm_tail(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum,
-                             float* y, unsigned int* counter, const float* w1, float* res, const float* w2,
-                             float eps, int8_t* q, float* scale, int32_t* sum, cudaStream_t st);
 // Exact int8 tensor-core GEMM for many Q8-quantised activation rows; bit-identical to launch_gemv_q8 (gemm_q8.cu).
 int launch_gemm_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum, float* y,
                    uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
