@@ -557,6 +557,7 @@ struct QkNormRope {
 
 // attention_scores_kernel with the window taken from the device-side position. The grid covers the
 // largest possible window; CTAs past the current one leave at once.
+template <bool LOOP>  // LOOP: a CTA walks over several key tiles (many rows in flight); else one tile per CTA
 __global__ void __launch_bounds__(256)
 attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc, float* __restrict__ vc,
                              const float* __restrict__ k_new, const float* __restrict__ v_new,
@@ -596,7 +597,8 @@ attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc
     const float* knew = k_new ? k_new + (size_t)kvh * head_dim : nullptr;
     if (nr.q_norm_w != nullptr) {
         // the new key is needed by the writer and by the CTA whose tiles include the last position
-        const bool need_k = writer || (in_window && ((kv_len - 1) / 16) % gridDim.x == blockIdx.x);
+        const bool need_k = writer || (in_window && (LOOP ? ((kv_len - 1) / 16) % gridDim.x == blockIdx.x
+                                                           : blockIdx.x * 16 + 16 > kv_len - 1));
         float* qn = qk;
         float* kn = qk + head_dim;
         for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) {
@@ -657,6 +659,7 @@ attention_scores_step_kernel(const float* __restrict__ q, float* __restrict__ kc
             for (uint32_t d = dim16; d < head_dim; ++d) s = __fadd_rn(s, __fmul_rn(qh[d], kr[d]));
             scores[(size_t)h * kv_len + p] = __fmul_rn(s, scale);
         }
+        if (!LOOP) break;
         __syncthreads();  // `part` is rewritten by the next tile
     }
 }
@@ -862,10 +865,11 @@ int launch_attention_step(const float* q, float* kc, float* vc, const float* k_n
     // launching thousands of CTAs that find their tile outside the row's window and repeats the per-CTA
     // q / k preparation less often.
     uint32_t tiles_x = (max_len + 15) / 16;
-    if (rows >= 16 && tiles_x > 8) tiles_x = 8;
-    ZQ_CUDA(launch_pdl(attention_scores_step_kernel, dim3(tiles_x, n_head, rows), dim3(256), smem_scores,
-                       st, q, kc, vc, k_new, v_new, scores, n_head, n_kv_head, head_dim, state, window, q_stride,
-                       scores_stride, row_pos, cache_stride, nr));
+    const bool loop = rows >= 16 && tiles_x > 8;
+    if (loop) tiles_x = 8;
+    ZQ_CUDA(launch_pdl(loop ? attention_scores_step_kernel<true> : attention_scores_step_kernel<false>,
+                       dim3(tiles_x, n_head, rows), dim3(256), smem_scores, st, q, kc, vc, k_new, v_new, scores, n_head,
+                       n_kv_head, head_dim, state, window, q_stride, scores_stride, row_pos, cache_stride, nr));
     const dim3 grid(n_head, (head_dim + kAttnDims - 1) / kAttnDims, rows);
     if (oq) {
         auto kern = attention_softmax_v_step_kernel<true>;
