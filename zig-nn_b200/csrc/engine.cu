@@ -441,7 +441,7 @@ struct zq_gemma3 {
 // Activation rows are quantised once (thread_pool.zig:111-114); any number of weights consume them.
 // T rows: one exact GEMV per row, or from five rows up the exact int8 GEMM (identical results).
 static int gemma_linear(zq_gemma3* m, const zq_weight* w, float* y, uint32_t y_stride, uint32_t T, cudaStream_t st) {
-    if (T >= 5 && y_stride == w->out_dim) return launch_gemm_q8(w, m->xq, m->xscale, m->xsum, y, T, nullptr, st);
+    if (T >= 2 && y_stride == w->out_dim) return launch_gemm_q8(w, m->xq, m->xscale, m->xsum, y, T, nullptr, st);
     for (uint32_t r = 0; r < T; ++r) {
         int rc = launch_gemv_q8(w, m->xq + (size_t)r * w->in_dim, m->xscale + (size_t)r * w->nb,
                                 m->xsum + (size_t)r * w->nb, y + (size_t)r * y_stride, 1, nullptr, st);

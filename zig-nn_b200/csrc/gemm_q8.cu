@@ -291,19 +291,32 @@ int launch_cfg(const zq_weight* w, const int8_t* xq, const float* xs, const int3
     return ZQ_OK;
 }
 
+// CTA shape by measurement on the Gemma-3 layer shapes (64 and 128 activation rows): a warp owns 16 weight
+// rows x NT column tiles of 8 activation rows. Few column tiles per warp mean more warps (the running sums
+// are a serial chain over K per output, so only more, smaller warp tiles shorten a launch that cannot fill
+// the GPU) but also more passes over the weights through L2; so: the largest NT that still gives about
+// 1000 warps, never so small that a weight is read more than 8 times, and the smallest such NT when no
+// choice reaches 1000 warps. (6912->1152 at 128 rows: 35 us with NT = 2, 41 us with NT = 1, 60 us with
+// one-warp CTAs; 1152->13824 at 64 rows: 21 us with NT = 4, 25 us with NT = 8.)
 template <int TYPE>
 int launch_one(const zq_weight* w, const int8_t* xq, const float* xs, const int32_t* xsum, float* y, uint32_t M,
                QgEpilogue ep, cudaStream_t st) {
-    const uint64_t sms = (uint64_t)sm_count();
-    const uint64_t big = (uint64_t)((w->out_dim + 127) / 128) * ((M + 63) / 64);
-    if (big >= sms) return launch_cfg<TYPE, 8, 8, 3>(w, xq, xs, xsum, y, M, ep, st);
-    const uint64_t mid = (uint64_t)((w->out_dim + 31) / 32) * ((M + 63) / 64);
-    if (mid >= sms) return launch_cfg<TYPE, 2, 8, 4>(w, xq, xs, xsum, y, M, ep, st);
-    // few weight rows: the running sums are a serial chain over K per output, so only more (smaller) warps
-    // tiles shorten the launch
-    const uint64_t small = (uint64_t)((w->out_dim + 31) / 32) * ((M + 15) / 16);
-    if (small >= 2 * sms) return launch_cfg<TYPE, 2, 2, 6>(w, xq, xs, xsum, y, M, ep, st);
-    return launch_cfg<TYPE, 1, 1, 8>(w, xq, xs, xsum, y, M, ep, st);
+    const uint64_t rt = (w->out_dim + 15) / 16, mt8 = (M + 7) / 8;
+    uint32_t nt_cap = 1, nt_min = 1;
+    while (nt_cap < 8 && nt_cap < mt8) nt_cap *= 2;
+    while (nt_min < nt_cap && (mt8 + nt_min - 1) / nt_min > 8) nt_min *= 2;
+    uint32_t nt = nt_min;
+    for (uint32_t c = nt_cap; c >= nt_min; c /= 2)
+        if (rt * ((mt8 + c - 1) / c) >= 1000) {
+            nt = c;
+            break;
+        }
+    switch (nt) {
+        case 8: return launch_cfg<TYPE, 8, 8, 3>(w, xq, xs, xsum, y, M, ep, st);
+        case 4: return launch_cfg<TYPE, 4, 4, 4>(w, xq, xs, xsum, y, M, ep, st);
+        case 2: return launch_cfg<TYPE, 4, 2, 6>(w, xq, xs, xsum, y, M, ep, st);
+        default: return launch_cfg<TYPE, 4, 1, 8>(w, xq, xs, xsum, y, M, ep, st);
+    }
 }
 
 }  // namespace

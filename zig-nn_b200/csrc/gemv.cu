@@ -597,11 +597,10 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
         int32_t* sm = reinterpret_cast<int32_t*>(static_cast<char*>(d_workspace) + qbytes + sbytes);
         int rc = launch_quantize_rows_q8(d_x, m_rows, w->in_dim, q, sc, sm, st);
         if (rc != ZQ_OK) return rc;
-        // From a handful of rows on, the exact int8 GEMM (weights read once per 64 rows) beats a GEMV per row:
-        // from 2 rows for matrices that sit in L2 and have short rows (measured 1.1-1.6x at 2-4 rows), from 5
-        // rows otherwise (long rows with few of them leave the GEMM too few CTAs; the 170-320 MB vocabulary
-        // head streams faster through the whole-rows GEMV up to 4 rows). Both give the same bits.
-        const uint32_t q8_gemm_min = (w->bytes <= ((size_t)32 << 20) && w->in_dim <= 4096) ? 2u : 5u;
+        // From two rows on, the exact int8 GEMM (weights read once for up to 64 rows) beats a GEMV per row:
+        // measured 1.1-1.6x at 2-4 rows on the small matrices and 1.5-2.3x on the 170-320 MB vocabulary
+        // head (4 rows: 71-89 us against 130-206 us). Both give the same bits.
+        const uint32_t q8_gemm_min = 2;
         if (m_rows >= q8_gemm_min) return launch_gemm_q8(w, q, sc, sm, d_y, m_rows, epilogue, st);
         return launch_gemv_q8(w, q, sc, sm, d_y, m_rows, epilogue, st);
     }
