@@ -62,5 +62,7 @@ extern "C" int zq_matmul_q8_static(const zq_weight* w, const float* d_x, float* 
     cudaStream_t st = zq::as_stream(stream);
     rc = zq::launch_quantize_rows_q8(d_x, m_rows, w->in_dim, q, scale, sum, st);
     if (rc != ZQ_OK) return rc;
+    // same kernels as zq_matmul in ZQ_ACT_Q8 mode (neither allocates): the exact int8 GEMM from two rows on
+    if (m_rows >= 2) return zq::launch_gemm_q8(w, q, scale, sum, d_y, m_rows, epilogue, st);
     return zq::launch_gemv_q8(w, q, scale, sum, d_y, m_rows, epilogue, st);
 }
