@@ -13,6 +13,8 @@
 //                single bulk copy (cp.async.bulk, completion counted on the stage's mbarrier) brings in;
 //   D          = 128 lanes x N columns of f32 in tensor memory (one lane per weight row).
 //
+// A CTA owns one or two tiles of 128 weight rows (two accumulators side by side in tensor memory, the
+// activation tile of a stage shared by both; chosen per call, see launch_tc).
 // Roles: warps 0-15 produce stages (dequantise) and later drain the accumulator; one thread of
 // warp 16 issues the MMAs. Stages are handed over through mbarriers: full[s] (one arrival per producer warp),
 // empty[s] (tcgen05.commit when the MMAs that read the stage are done), acc (last commit). Every wait
@@ -27,12 +29,18 @@ namespace {
 constexpr int TC_BN = 128;          // weight rows per CTA  (UMMA M)
 constexpr int TC_BM = 256;          // activation rows per CTA, at most (UMMA N)
 constexpr int TC_BK = 64;           // K per stage: one 128-byte swizzle atom of fp16
-constexpr int TC_STAGES = 4;
+constexpr int TC_MAX_STAGES = 4;
 constexpr int TC_PRODUCERS = 512;   // threads of warps 0-15
 constexpr int TC_THREADS = TC_PRODUCERS + 32;
-constexpr uint32_t TC_A_BYTES = TC_BN * 128;   // 16 KB
+constexpr uint32_t TC_A_BYTES = TC_BN * 128;   // 16 KB per tile of 128 weight rows
 constexpr uint32_t TC_B_BYTES = TC_BM * 128;   // 32 KB
-constexpr uint32_t TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+// RT tiles of 128 weight rows share one activation tile per stage (RT accumulators in tensor memory):
+// RT = 1: 48 KB stages, 4 of them; RT = 2: 64 KB stages, 3 of them, twice the MMA work per hand-over.
+template <int RT>
+struct TcShape {
+    static constexpr uint32_t kStageBytes = RT * TC_A_BYTES + TC_B_BYTES;
+    static constexpr int kStages = RT == 1 ? 4 : 3;
+};
 constexpr uint32_t kSpinLimit = 1u << 24;      // iterations of a try_wait loop before giving up (about a second)
 constexpr unsigned int kErrGemmTimeout = 0x47454D4Du;  // 'GEMM'
 
@@ -281,7 +289,7 @@ __device__ __forceinline__ void store_dequant(const PackedQuad<TYPE>& p, uint32_
     }
 }
 
-template <int TYPE>
+template <int TYPE, int RT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const __half* __restrict__ xt,
                const float* __restrict__ post, float* __restrict__ y, uint32_t N, uint32_t K, uint32_t M,
@@ -291,8 +299,10 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QB = Q8 ? 32 : 16;
     constexpr uint32_t SB = Q41 ? 4 : 2;
+    constexpr uint32_t TC_STAGES = TcShape<RT>::kStages, TC_STAGE_BYTES = TcShape<RT>::kStageBytes;
+    const uint32_t acc_cols = tmem_cols / RT;  // columns of one accumulator (a power of two >= n_mma)
     extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long bars[2 * TC_STAGES + 1];
+    __shared__ __align__(8) unsigned long long bars[2 * TC_MAX_STAGES + 1];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -304,7 +314,7 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     const uint32_t acc_bar = bar32 + 2 * TC_STAGES * 8;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * n_mma;
+    const uint32_t n0 = blockIdx.x * (RT * TC_BN), m0 = blockIdx.y * n_mma;
     const uint32_t n_stages = nbp / 2;  // 64-K stages (the row padding to whole quads is zero weights)
 
     if (tid == 0) {
@@ -331,20 +341,28 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     if (warp < TC_PRODUCERS / 32) {
         // ================= producers =================
         const uint32_t prow = tid >> 2, phalf = (tid >> 1) & 1, pjj = tid & 1;
-        const uint32_t wrow = min(n0 + prow, N - 1);
-        const uint8_t* qrow = qs + (size_t)wrow * nbp * QB;
-        const uint8_t* srow = sc + (size_t)wrow * scp * SB;
+        const uint8_t* qrow[RT];
+        const uint8_t* srow[RT];
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+            const uint32_t wrow = min(n0 + r * TC_BN + prow, N - 1);
+            qrow[r] = qs + (size_t)wrow * nbp * QB;
+            srow[r] = sc + (size_t)wrow * scp * SB;
+        }
         // packed words of the current quad and of the next one (loaded a whole quad ahead of their use)
-        PackedQuad<TYPE> pk, pk_next;
+        PackedQuad<TYPE> pk[RT], pk_next[RT];
         const uint32_t n_quads = nbp / 4;
-        load_packed<TYPE>(pk, qrow, srow, 0, phalf);
-        if (n_quads > 1) load_packed<TYPE>(pk_next, qrow, srow, 1, phalf);
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+            load_packed<TYPE>(pk[r], qrow[r], srow[r], 0, phalf);
+            if (n_quads > 1) load_packed<TYPE>(pk_next[r], qrow[r], srow[r], 1, phalf);
+        }
         bool alive = true;
         for (uint32_t s = 0; s < n_stages && alive; ++s) {
             const uint32_t slot = s % TC_STAGES, round = s / TC_STAGES;
             if (round > 0) alive = mbar_wait(empty_bar(slot), (round - 1) & 1u, abort_p, err_word);
             if (!alive) break;
-            const uint32_t a_tile = smem32 + slot * TC_STAGE_BYTES, b_tile = a_tile + TC_A_BYTES;
+            const uint32_t a_tile = smem32 + slot * TC_STAGE_BYTES, b_tile = a_tile + RT * TC_A_BYTES;
             if ((tid & 31) == 0 && warp < 8) {
                 // the stage's activation tile: n_mma rows x 128 bytes, contiguous in the converted image; eight
                 // threads (one per warp) copy an eighth each so that several transfers are in flight
@@ -354,13 +372,16 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
                 bulk_copy_g2s(b_tile + off, reinterpret_cast<const unsigned char*>(xt + ((size_t)s * m_pad + m0) * 64) + off,
                               bytes, full_bar(slot));
             }
-            if ((s & 1u) == 0) {
-                store_dequant<TYPE, 0>(pk, a_tile, prow, phalf, pjj);
-            } else {
-                store_dequant<TYPE, 2>(pk, a_tile, prow, phalf, pjj);
-                pk = pk_next;
-                const uint32_t q_ahead = ((s + 1) >> 1) + 1;
-                if (q_ahead < n_quads) load_packed<TYPE>(pk_next, qrow, srow, q_ahead, phalf);
+#pragma unroll
+            for (int r = 0; r < RT; ++r) {
+                if ((s & 1u) == 0) {
+                    store_dequant<TYPE, 0>(pk[r], a_tile + r * TC_A_BYTES, prow, phalf, pjj);
+                } else {
+                    store_dequant<TYPE, 2>(pk[r], a_tile + r * TC_A_BYTES, prow, phalf, pjj);
+                    pk[r] = pk_next[r];
+                    const uint32_t q_ahead = ((s + 1) >> 1) + 1;
+                    if (q_ahead < n_quads) load_packed<TYPE>(pk_next[r], qrow[r], srow[r], q_ahead, phalf);
+                }
             }
             fence_proxy_async();  // generic-proxy writes (st.shared) -> visible to the tensor core
             __syncwarp();         // every lane's stores and fence precede the warp's single arrival
@@ -373,22 +394,25 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
         if (alive) {
             // warp w reads lanes 32 * (w % 4) ..; the column chunks of 32 go round the four warp groups
             const uint32_t lane_base = (warp & 3) * 32;
-            const uint32_t n = n0 + lane_base + lane;
-            for (uint32_t c = (warp >> 2) * 32; c < n_mma; c += (TC_PRODUCERS / 128) * 32) {
-                uint32_t r[32];
-                tc_ld32(tmem_base + (lane_base << 16) + c, r);
-                tc_wait_ld();
+#pragma unroll 1
+            for (int r = 0; r < RT; ++r) {
+                const uint32_t n = n0 + r * TC_BN + lane_base + lane;
+                for (uint32_t c = (warp >> 2) * 32; c < n_mma; c += (TC_PRODUCERS / 128) * 32) {
+                    uint32_t v32[32];
+                    tc_ld32(tmem_base + (lane_base << 16) + r * acc_cols + c, v32);
+                    tc_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const uint32_t m = m0 + c + i;
-                    if (n < N && m < M) {
-                        const size_t o = (size_t)m * N + n;
-                        float v = __uint_as_float(r[i]) * post[m];
-                        if (ep.bias) v = __fadd_rn(v, ep.bias[n]);
-                        if (ep.gelu) v = gelu_tanh(v);
-                        if (ep.mul) v = __fmul_rn(v, ep.mul[o]);
-                        if (ep.residual) v = __fadd_rn(ep.residual[o], v);
-                        y[o] = v;
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t m = m0 + c + i;
+                        if (n < N && m < M) {
+                            const size_t o = (size_t)m * N + n;
+                            float v = __uint_as_float(v32[i]) * post[m];
+                            if (ep.bias) v = __fadd_rn(v, ep.bias[n]);
+                            if (ep.gelu) v = gelu_tanh(v);
+                            if (ep.mul) v = __fmul_rn(v, ep.mul[o]);
+                            if (ep.residual) v = __fadd_rn(ep.residual[o], v);
+                            y[o] = v;
+                        }
                     }
                 }
             }
@@ -404,12 +428,15 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
                 alive = mbar_wait(full_bar(slot), round & 1u, abort_p, err_word);
                 if (!alive) break;
                 tc_fence_after();
-                const uint32_t a_tile = smem32 + slot * TC_STAGE_BYTES, b_tile = a_tile + TC_A_BYTES;
-                const uint64_t a_desc = smem_desc_sw128(a_tile), b_desc = smem_desc_sw128(b_tile);
+                const uint32_t a_tile = smem32 + slot * TC_STAGE_BYTES, b_tile = a_tile + RT * TC_A_BYTES;
+                const uint64_t b_desc = smem_desc_sw128(b_tile);
 #pragma unroll
                 for (uint32_t k16 = 0; k16 < TC_BK / 16; ++k16) {
                     // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
-                    tc_mma_f16(tmem_base, a_desc + 2 * k16, b_desc + 2 * k16, idesc, (s | k16) != 0 ? 1u : 0u);
+#pragma unroll
+                    for (int r = 0; r < RT; ++r)
+                        tc_mma_f16(tmem_base + r * acc_cols, smem_desc_sw128(a_tile + r * TC_A_BYTES) + 2 * k16,
+                                   b_desc + 2 * k16, idesc, (s | k16) != 0 ? 1u : 0u);
                 }
                 tc_commit(empty_bar(slot));  // arrives when the MMAs issued so far have read their operands
             }
@@ -439,18 +466,19 @@ inline void tc_tiling(uint32_t m_rows, uint32_t* n_mma, uint32_t* m_pad) {
     *m_pad = ((m_rows + *n_mma - 1) / *n_mma) * *n_mma;
 }
 
-template <int TYPE>
-int launch_tc(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
-              cudaStream_t st) {
-    auto kern = gemm_tc_kernel<TYPE>;
-    const size_t smem = (size_t)TC_STAGES * TC_STAGE_BYTES + 1024;  // + alignment slack
+template <int TYPE, int RT>
+int launch_tc_rt(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
+                 cudaStream_t st) {
+    auto kern = gemm_tc_kernel<TYPE, RT>;
+    const size_t smem = (size_t)TcShape<RT>::kStages * TcShape<RT>::kStageBytes + 1024;  // + alignment slack
     ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // activation rows per CTA: a multiple of 64 (the epilogue splits the columns in two halves of 32s)
     uint32_t n_mma, m_pad;
     tc_tiling(M, &n_mma, &m_pad);
-    uint32_t tmem_cols = 64;
-    while (tmem_cols < n_mma) tmem_cols *= 2;
-    const dim3 grid((w->out_dim + TC_BN - 1) / TC_BN, m_pad / n_mma);
+    uint32_t acc_cols = 64;
+    while (acc_cols < n_mma) acc_cols *= 2;
+    const uint32_t tmem_cols = acc_cols * RT;  // RT accumulators side by side
+    const dim3 grid((w->out_dim + RT * TC_BN - 1) / (RT * TC_BN), m_pad / n_mma);
     unsigned int* err_word = nullptr;
     int rc = device_error_word(&err_word);
     if (rc != ZQ_OK) return rc;
@@ -458,6 +486,20 @@ int launch_tc(const zq_weight* w, const __half* xt, const float* post, float* y,
                                           w->in_dim, M, m_pad, w->nbp, w->scp, n_mma, tmem_cols, err_word, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
+}
+
+template <int TYPE>
+int launch_tc(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
+              cudaStream_t st) {
+    // Two 128-row tiles per CTA double the MMA work per stage hand-over (the loop that bounds this kernel);
+    // they pay off when the paired tiles still cover about two thirds of the SMs (measured at 2048 rows:
+    // 4096->14336 691 -> 738, 14336->4096 659 -> 776, head 518 -> 625 TFLOP/s; with 54-56 paired tiles the
+    // single-tile form is 1.4x faster).
+    uint32_t n_mma, m_pad;
+    tc_tiling(M, &n_mma, &m_pad);
+    const uint64_t paired = (uint64_t)((w->out_dim + 2 * TC_BN - 1) / (2 * TC_BN)) * (m_pad / n_mma);
+    if (paired >= 100) return launch_tc_rt<TYPE, 2>(w, xt, post, y, M, ep, st);
+    return launch_tc_rt<TYPE, 1>(w, xt, post, y, M, ep, st);
 }
 
 }  // namespace
