@@ -111,10 +111,12 @@ REL_L2_GEMM_GUARD = 6e-4  # fp16 operands (weights and activations each rounded 
 
 
 @pytest.mark.parametrize("qtype", TYPES)
-@pytest.mark.parametrize("m,n,k", [(64, 520, 768), (128, 256, 1152), (200, 1000, 96), (513, 136, 2048)])
+@pytest.mark.parametrize("m,n,k", [(64, 520, 768), (128, 256, 1152), (200, 1000, 96), (513, 136, 2048),
+                                   (1030, 6420, 96)])
 def test_matmul_many_rows_tensor_core_gemm(zq, oracle, qtype, m, n, k):
     """More than 48 activation rows take the GEMM: ragged M and N tiles, K that is not a multiple of
-    the 128-wide stage, and the full epilogue."""
+    the 128-wide stage, and the full epilogue. The last shape has enough tiles for the form with two
+    128-row weight tiles per CTA (ragged in both directions: the last pair holds 20 rows)."""
     raw = make_weight(oracle, qtype, n, k)
     qw = zq.QuantWeight(raw, qtype, n, k)
     x = make_x(m, k)
