@@ -139,6 +139,75 @@ def test_gemma3_1b_full_size_greedy_64(zq, oracle):
     assert max(errs) <= 1e-3, max(errs)
 
 
+def test_gemma3_1b_full_size_prefill_across_the_sliding_window(zq, oracle):
+    """Gemma-3-1B shape, Q8_0: a 520-token prefill (five chunks through the exact int8 GEMM, the last rows
+    beyond the 512-token window of the local layers) and eight greedy steps; logits are the CPU path's bits."""
+    import os
+    host = hostmodel.Gemma3Host.synthetic(hostmodel.GEMMA3_1B, qtype=ggml.Q8_0, seed=42, std=0.02, device="cuda")
+    prompt = np.random.default_rng(45).integers(0, 262144, size=520)
+    eng, ref = zq.Gemma3(host), oracle.Gemma3(host, os.cpu_count() or 8)
+    lg, lc = eng.prefill(prompt).cpu().numpy(), ref.prefill(prompt)
+    assert np.array_equal(lg, lc), rel_l2(lg, lc)
+    for step in range(8):
+        t = int(np.argmax(lc))
+        assert int(np.argmax(lg)) == t
+        lg, lc = eng.decode_next(t).cpu().numpy(), ref.decode_next(t)
+        assert np.array_equal(lg, lc), (step, rel_l2(lg, lc))
+    assert eng.seq_len == 528
+
+
+def test_gemma3_1b_q4_1_batched_sequences_full_size(zq, oracle):
+    """Gemma-3-1B shape with Q4_1 weights, four independent sequences of different lengths (one beyond the
+    sliding window) advanced together: each sequence's logits are the bits of decoding it alone on the CPU."""
+    import os
+    host = hostmodel.Gemma3Host.synthetic(hostmodel.GEMMA3_1B, qtype=ggml.Q4_1, seed=42, std=0.02, device="cuda")
+    rng = np.random.default_rng(46)
+    prompts = [rng.integers(0, 262144, size=n) for n in (3, 40, 130, 530)]
+    eng = zq.Gemma3Batch(host, len(prompts))
+    refs = [oracle.Gemma3(host, os.cpu_count() or 8) for _ in prompts]
+    toks = []
+    for i, p in enumerate(prompts):
+        lg, lc = eng.prefill(i, p).cpu().numpy(), refs[i].prefill(p)
+        assert np.array_equal(lg, lc), ("prefill", i, rel_l2(lg, lc))
+        toks.append(int(np.argmax(lc)))
+    for step in range(4):
+        lg = eng.decode_next(toks).cpu().numpy()
+        for i in range(len(prompts)):
+            lc = refs[i].decode_next(toks[i])
+            assert np.array_equal(lg[i], lc), (step, i, rel_l2(lg[i], lc))
+            toks[i] = int(np.argmax(lc))
+
+
+def test_reset_cache_restarts_every_sequence_of_a_batch_engine(zq):
+    """reset_cache, then the same prefills and steps again: positions restart at zero for every sequence and
+    the logits repeat bit for bit; the one-sequence engine keeps its per-sequence length in step."""
+    host = hostmodel.Gemma3Host.synthetic(GEMMA_TINY, qtype=ggml.Q8_0, seed=9, std=0.08).randomize_small_params()
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, GEMMA_TINY["vocab"], size=n) for n in (5, 19, 30)]
+    eng = zq.Gemma3Batch(host, 3)
+
+    def run():
+        out = [eng.prefill(i, p).cpu() for i, p in enumerate(prompts)]
+        toks = [int(o.argmax()) for o in out]
+        for _ in range(6):
+            lg = eng.decode_next(toks).cpu()
+            out.append(lg)
+            toks = [int(r.argmax()) for r in lg]
+        return out
+
+    first = run()
+    assert [eng.seq_len(i) for i in range(3)] == [len(p) + 6 for p in prompts]
+    eng.reset_cache()
+    assert [eng.seq_len(i) for i in range(3)] == [0, 0, 0]
+    second = run()
+    assert all(torch.equal(a, b) for a, b in zip(first, second))
+    one = zq.Gemma3(host)
+    t = int(one.prefill(prompts[0]).argmax())
+    one.decode_next(t)
+    one.decode_greedy(t, 3)
+    assert one.seq_len == len(prompts[0]) + 4 == one.seq_len_of(0)
+
+
 def test_engines_from_gguf_files_match_engines_from_memory(zq, oracle, tmp_path):
     """Write the synthetic models as GGUF files under zig-nn's tensor names, map them back, and run the
     engines straight from the mapped bytes: logits are the bits of the in-memory model."""

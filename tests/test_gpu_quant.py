@@ -414,3 +414,78 @@ def test_host_buffer_call_writes_the_same_bits_into_pinned_memory(zq, qtype, mod
     assert torch.equal(pageable, want)
     with pytest.raises(ValueError):
         lin(hx, torch.empty(1, out_dim + 1).pin_memory())
+
+
+# ---- the many-row products at the shapes of the sweep and of the sharded configuration ------------------
+
+
+def _sampled_rows(n, count=64, seed=17):
+    """Weight rows to compare: both ends, a row on each side of every 128-row tile boundary near the ends,
+    and a seeded sample of the middle."""
+    rng = np.random.default_rng(seed)
+    fixed = [0, 1, 127, 128, 129, 255, 256, n - 257, n - 129, n - 128, n - 2, n - 1]
+    rest = rng.choice(n, size=count - len(fixed), replace=False)
+    return np.unique(np.clip(np.concatenate([fixed, rest]), 0, n - 1))
+
+
+@pytest.mark.parametrize("k,n,m", [(4096, 14336, 64), (4096, 14336, 2048), (14336, 4096, 64), (14336, 4096, 2048),
+                                   (1152, 6912, 512), (6912, 1152, 512), (1152, 262144, 128)])
+def test_tensor_core_gemm_at_full_shapes_sampled_rows(zq, oracle, k, n, m):
+    """The tcgen05 GEMM at the real shapes (Q4_0; up to 224 K-stages, the paired-tile form, the 262144-row
+    vocabulary head). The CPU side computes a sample of the weight rows: a subset of the raw row bytes is a
+    smaller weight whose outputs are exactly those columns of the full product."""
+    g = torch.Generator(device="cuda").manual_seed(1000 + k + m)
+    raw_d = ggml.quantize(ggml.Q4_0, torch.randn(n, k, generator=g, device="cuda") * 0.02)
+    qw = zq.QuantWeight(raw_d, ggml.Q4_0, n, k)
+    x = torch.randn(m, k, generator=g, device="cuda")
+    got = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32)
+    rows = _sampled_rows(n)
+    row_bytes = k // 32 * 18
+    sub = raw_d.view(n, row_bytes)[torch.from_numpy(rows).cuda()].cpu().numpy().reshape(-1)
+    want = oracle.linear(ggml.Q4_0, sub, x.cpu().numpy(), len(rows), k, act_mode=0, n_threads=16)
+    got_s = got[:, torch.from_numpy(rows).cuda()].cpu().numpy()
+    err = rel_l2(got_s, want)
+    assert err <= REL_L2_BAR
+    assert err <= REL_L2_GEMM_GUARD, err
+    worst = max(rel_l2(got_s[r], want[r]) for r in range(0, m, max(1, m // 16)))
+    assert worst <= REL_L2_BAR, worst
+    # A size-independent check that touches every output: the sum of an output row equals x . (column sums of
+    # W). Independent rounding errors of 3e-4 per output add up to about 3e-4 of the row's 2-norm; a wrong
+    # 128-column tile would move the sum by about ten times the bound.
+    colsum_w = qw.dequantize().sum(dim=0, dtype=torch.float64)
+    want_sum = x.double() @ colsum_w
+    got_sum = got.sum(dim=1, dtype=torch.float64)
+    bound = 2e-3 * got.double().norm(dim=1)
+    assert bool(((got_sum - want_sum).abs() <= bound).all()), float(((got_sum - want_sum).abs() / bound).max())
+
+
+@pytest.mark.parametrize("m", [64, 512])
+def test_exact_int8_gemm_at_vocab_head_sampled_rows(zq, oracle, m):
+    """The exact int8 GEMM on the 1152 -> 262144 head in Q4_1 (the batched engine's logits): sampled weight
+    rows, every activation row, bit-identical to the CPU path."""
+    n, k = 262144, 1152
+    g = torch.Generator(device="cuda").manual_seed(77 + m)
+    raw_d = ggml.quantize(ggml.Q4_1, torch.randn(n, k, generator=g, device="cuda") * 0.02)
+    qw = zq.QuantWeight(raw_d, ggml.Q4_1, n, k)
+    x = torch.randn(m, k, generator=g, device="cuda")
+    got = zq.quant_matmul_no_grad(x, qw, zq.ACT_Q8)
+    rows = _sampled_rows(n)
+    sub = raw_d.view(n, k // 32 * 20)[torch.from_numpy(rows).cuda()].cpu().numpy().reshape(-1)
+    want = oracle.linear(ggml.Q4_1, sub, x.cpu().numpy(), len(rows), k, act_mode=1, n_threads=16)
+    assert np.array_equal(got[:, torch.from_numpy(rows).cuda()].cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("out_dim,in_dim,m", [(14336, 4096, 2048), (4096, 14336, 64)])
+def test_matmul_transposed_at_full_shapes_sampled_columns(zq, oracle, out_dim, in_dim, m):
+    """grad_x = grad_out . W at the sharded-GEMM shapes; the CPU side computes a sample of the rows of
+    grad_out (each output row depends on its own grad_out row only)."""
+    g = torch.Generator(device="cuda").manual_seed(out_dim + m)
+    raw_d = ggml.quantize(ggml.Q4_0, torch.randn(out_dim, in_dim, generator=g, device="cuda") * 0.02)
+    qw = zq.QuantWeight(raw_d, ggml.Q4_0, out_dim, in_dim)
+    go = torch.randn(m, out_dim, generator=g, device="cuda") * 1e-3
+    got = zq.quant_matmul_transposed(go, qw)
+    rows = np.unique(np.concatenate([[0, 1, m - 1], np.random.default_rng(3).choice(m, size=5, replace=False)]))
+    want = oracle.matmul_transposed(ggml.Q4_0, raw_d.cpu().numpy(), go[torch.from_numpy(rows).cuda()].cpu().numpy(),
+                                    out_dim, in_dim, n_threads=16)
+    err = rel_l2(got[torch.from_numpy(rows).cuda()].cpu().numpy(), want)
+    assert err <= REL_L2_TRANS, err

@@ -468,6 +468,11 @@ class Gemma3(_Engine):
     """gemma3(C): init / prefill / decode_next (src/models/gemma3.zig:283,551,789)."""
     _prefix = "zq_gemma3"
 
+    def seq_len_of(self, seq):
+        n = C.c_uint32()
+        _lib.check(_lib.load().zq_gemma3_seq_len_of(self._h, int(seq), C.byref(n)))
+        return n.value
+
 
 class Gemma3Batch:
     """Several independent sequences in one engine: prefill each, then advance all of them per call
@@ -506,6 +511,10 @@ class Gemma3Batch:
         n = C.c_uint32()
         _lib.check(_lib.load().zq_gemma3_seq_len_of(self._h, int(seq), C.byref(n)))
         return n.value
+
+    def reset_cache(self):
+        """Every sequence restarts at position 0 (its cache rows are overwritten by the next prefill)."""
+        _lib.check(_lib.load().zq_gemma3_reset_cache(self._h))
 
     def close(self):
         if getattr(self, "_h", None):

@@ -6,6 +6,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <new>
 #include <vector>
 
@@ -707,6 +708,7 @@ int zq_gemma3_free(zq_gemma3* m) {
 int zq_gemma3_reset_cache(zq_gemma3* m) {
     if (!m) return ZQ_ERR_BAD_ARG;
     m->seq_len = 0;
+    std::fill(m->seq_lens.begin(), m->seq_lens.end(), 0u);  // every sequence of a batch engine restarts
     return ZQ_OK;
 }
 
@@ -792,6 +794,7 @@ int zq_gemma3_decode_next(zq_gemma3* m, uint32_t token, zq_stream stream, const 
     int rc = gemma3_run(m, STEP_LOGITS, st);
     if (rc != ZQ_OK) return rc;
     m->seq_len += 1;
+    m->seq_lens[0] = m->seq_len;
     *d_logits = m->logits;
     return ZQ_OK;
 }
@@ -809,6 +812,7 @@ int zq_gemma3_decode_greedy(zq_gemma3* m, uint32_t first_token, uint32_t n_steps
         int rc = gemma3_run(m, STEP_GREEDY, st);
         if (rc != ZQ_OK) return rc;
         m->seq_len += 1;
+        m->seq_lens[0] = m->seq_len;
     }
     ZQ_CUDA(cudaMemcpyAsync(h_tokens_out, m->d_record, n_steps * sizeof(uint32_t),
                             cudaMemcpyDeviceToHost, st));
