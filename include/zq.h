@@ -431,6 +431,33 @@ int zq_gemma3_prefill_seq(zq_gemma3* m, uint32_t seq, const uint32_t* h_tokens, 
 int zq_gemma3_decode_next_batch(zq_gemma3* m, const uint32_t* h_tokens, zq_stream stream, const float** d_logits);
 int zq_gemma3_seq_len_of(const zq_gemma3* m, uint32_t seq, uint32_t* seq_len);
 
+/* How a one-sequence decode step runs on the device. The reference's Metal engine encodes a whole token
+ * into one command buffer (gemma3_metal.zig:189-260); the counterpart here is ONE persistent cooperative
+ * kernel per token (or per run of greedy tokens), its phases separated by grid barriers, weights streamed
+ * ahead of the phases by bulk copies. Results are bit-identical in both modes.
+ *   ZQ_DECODE_AUTO             the persistent kernel when the model fits its plan, else the launch sequence
+ *   ZQ_DECODE_LAUNCH_SEQUENCE  always the captured sequence of about ten launches per layer
+ *   ZQ_DECODE_PERSISTENT       the persistent kernel; ZQ_ERR_UNSUPPORTED when the model does not fit it
+ *                              (mixed types inside q|k|v or gate|up, a weight row above a ring slot,
+ *                              batched engines)
+ * zq_gemma3_decode_mode reports the mode the next decode step will use (never AUTO). Prefill chunks and
+ * batched steps always use the launch sequence. */
+#define ZQ_DECODE_AUTO 0
+#define ZQ_DECODE_LAUNCH_SEQUENCE 1
+#define ZQ_DECODE_PERSISTENT 2
+int zq_gemma3_set_decode_mode(zq_gemma3* m, int mode);
+int zq_gemma3_decode_mode(const zq_gemma3* m, int* mode);
+/* Per-phase timing of one decode step, the device-side counterpart of gemma3.ProfileStats
+ * (gemma3.zig:35-92, filled at :417-491): the persistent kernel runs one step (like decode_next) and every
+ * CTA records its SM cycle counter at each phase boundary. h_cycles[n_ctas][capacity] receives the stamps of
+ * CTA c at h_cycles[c * capacity ...], in program order: token start; per layer 16 stamps (qkv prologue done,
+ * qkv done, barrier passed, scores done, barrier, softmax.V done, barrier, o prologue done, o done, barrier,
+ * ffn prologue done, gate/up done, barrier, down prologue done, down done, barrier); head prologue done, head
+ * done. Unused entries are 0. capacity >= 3 + 16 * layers holds all of them. ZQ_ERR_UNSUPPORTED without the
+ * persistent kernel. */
+int zq_gemma3_profile_step(zq_gemma3* m, uint32_t token, zq_stream stream, long long* h_cycles, uint32_t capacity,
+                           uint32_t* n_ctas);
+
 #ifdef __cplusplus
 }
 #endif

@@ -208,6 +208,52 @@ def test_reset_cache_restarts_every_sequence_of_a_batch_engine(zq):
     assert one.seq_len == len(prompts[0]) + 4 == one.seq_len_of(0)
 
 
+@pytest.mark.parametrize("qtypes", [(ggml.Q8_0, ggml.Q8_0, ggml.Q8_0), (ggml.Q4_0, ggml.Q8_0, ggml.Q4_1),
+                                    (ggml.Q4_1, ggml.Q4_1, ggml.Q4_1)])
+def test_persistent_decode_kernel_equals_the_launch_sequence(zq, qtypes):
+    """One cooperative kernel per token against the captured launch sequence: same logits bit for bit, step
+    by step and through the on-device greedy loop (window 16 crossed, global layer included)."""
+    q, embd, down = qtypes
+    host = hostmodel.Gemma3Host.synthetic(GEMMA_TINY, qtype=q, embd_qtype=embd, down_qtype=down, seed=11,
+                                          std=0.08).randomize_small_params()
+    prompt = np.random.default_rng(3).integers(0, GEMMA_TINY["vocab"], size=13)
+    a, b = zq.Gemma3(host), zq.Gemma3(host)
+    assert a.decode_mode == zq.DECODE_PERSISTENT
+    b.set_decode_mode(zq.DECODE_LAUNCH_SEQUENCE)
+    assert b.decode_mode == zq.DECODE_LAUNCH_SEQUENCE
+    la, lb = a.prefill(prompt), b.prefill(prompt)
+    assert torch.equal(la, lb)
+    tok = int(la.argmax())
+    for step in range(30):
+        la, lb = a.decode_next(tok), b.decode_next(tok)
+        assert torch.equal(la, lb), step
+        tok = int(la.argmax())
+    ta, tb = a.decode_greedy(tok, 25), b.decode_greedy(tok, 25)
+    assert list(ta) == list(tb)
+    assert a.seq_len == b.seq_len == 13 + 30 + 25
+    # a single-token prefill and a cache-only step go through the kernel too
+    a.reset_cache(), b.reset_cache()
+    assert torch.equal(a.prefill([5]), b.prefill([5]))
+    assert torch.equal(a.decode_next(7), b.decode_next(7))
+    from zignn_b200 import _lib
+    assert _lib.device_error(clear=False) == 0
+
+
+def test_persistent_decode_kernel_full_size_greedy_against_launch_sequence(zq):
+    """Gemma-3-1B shape, Q8_0, 600-token context (beyond the window): 48 greedy tokens from the on-device loop
+    of the persistent kernel equal those of the launch sequence, and so do the logits of the step after."""
+    host = hostmodel.Gemma3Host.synthetic(hostmodel.GEMMA3_1B, qtype=ggml.Q8_0, seed=42, std=0.02, device="cuda")
+    prompt = np.random.default_rng(47).integers(0, 262144, size=600)
+    a, b = zq.Gemma3(host), zq.Gemma3(host)
+    b.set_decode_mode(zq.DECODE_LAUNCH_SEQUENCE)
+    la, lb = a.prefill(prompt), b.prefill(prompt)
+    assert torch.equal(la, lb)
+    tok = int(la.argmax())
+    ta, tb = a.decode_greedy(tok, 48), b.decode_greedy(tok, 48)
+    assert list(ta) == list(tb)
+    assert torch.equal(a.decode_next(int(ta[-1])), b.decode_next(int(tb[-1])))
+
+
 def test_engines_from_gguf_files_match_engines_from_memory(zq, oracle, tmp_path):
     """Write the synthetic models as GGUF files under zig-nn's tensor names, map them back, and run the
     engines straight from the mapped bytes: logits are the bits of the in-memory model."""

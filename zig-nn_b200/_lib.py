@@ -82,6 +82,9 @@ SIGNATURES = {
     "zq_gemma3_prefill_seq": (i, [vp, u32, vp, u32, vp, P(vp)]),
     "zq_gemma3_decode_next_batch": (i, [vp, vp, vp, P(vp)]),
     "zq_gemma3_seq_len_of": (i, [vp, u32, P(u32)]),
+    "zq_gemma3_set_decode_mode": (i, [vp, i]),
+    "zq_gemma3_decode_mode": (i, [vp, P(i)]),
+    "zq_gemma3_profile_step": (i, [vp, u32, vp, vp, u32, P(u32)]),
 }
 
 
@@ -120,3 +123,12 @@ def load():
 def check(status, where=""):
     if status != 0:
         raise ZqError(status, where)
+
+
+def device_error(clear=True):
+    """The code a kernel's bounded device-side wait left behind when it ran out (0 = none): the four
+    characters of a tag such as 'GATH' (peer gather), 'GBAR' (grid barrier of the persistent decode
+    kernel) packed into an integer. clear=True resets the word."""
+    v = C.c_uint()
+    check(load().zq_device_error(C.byref(v), int(bool(clear))), "zq_device_error")
+    return v.value

@@ -13,6 +13,7 @@ from . import _lib, ggml
 from . import structs as S
 
 ACT_F32, ACT_Q8, ACT_F16 = 0, 1, 2
+DECODE_AUTO, DECODE_LAUNCH_SEQUENCE, DECODE_PERSISTENT = 0, 1, 2
 
 
 def _stream():
@@ -472,6 +473,28 @@ class Gemma3(_Engine):
         n = C.c_uint32()
         _lib.check(_lib.load().zq_gemma3_seq_len_of(self._h, int(seq), C.byref(n)))
         return n.value
+
+    def set_decode_mode(self, mode):
+        """DECODE_AUTO / DECODE_LAUNCH_SEQUENCE / DECODE_PERSISTENT (one cooperative kernel per token)."""
+        _lib.check(_lib.load().zq_gemma3_set_decode_mode(self._h, int(mode)), "zq_gemma3_set_decode_mode")
+
+    def profile_step(self, token):
+        """One decode step with per-phase cycle stamps (the device-side counterpart of gemma3.ProfileStats,
+        src/models/gemma3.zig:35-92). Returns an int64 array [n_ctas][3 + 16 * layers] of SM cycle counts at the
+        phase boundaries (layout: include/zq.h, zq_gemma3_profile_step)."""
+        cap = 3 + 16 * self._cfg.layer
+        buf = np.zeros(4096 * cap, dtype=np.int64)
+        n = C.c_uint32()
+        rc = _lib.load().zq_gemma3_profile_step(self._h, int(token), _stream(), buf.ctypes.data_as(C.c_void_p), cap,
+                                                C.byref(n))
+        _lib.check(rc, "zq_gemma3_profile_step")
+        return buf[:n.value * cap].reshape(n.value, cap)
+
+    @property
+    def decode_mode(self):
+        mode = C.c_int()
+        _lib.check(_lib.load().zq_gemma3_decode_mode(self._h, C.byref(mode)))
+        return mode.value
 
 
 class Gemma3Batch:

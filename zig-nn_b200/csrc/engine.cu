@@ -10,6 +10,7 @@
 #include <new>
 #include <vector>
 
+#include "decode_gemma.h"
 #include "zq_internal.h"
 
 namespace zq {
@@ -423,7 +424,13 @@ struct zq_gemma3 {
     uint32_t* d_pos = nullptr;            // [n_seq] positions of a batched decode step
     std::vector<uint32_t> seq_lens;       // host copy, [n_seq]
     float* logits_batch = nullptr;        // [n_seq][vocab]
+    // One-sequence decode steps run as one persistent cooperative kernel when the model fits its plan
+    // (decode_gemma.cu); otherwise, and for prefill chunks and batched sequences, as the launch sequence.
+    GemmaDecoder* decoder = nullptr;
+    int decode_mode = ZQ_DECODE_AUTO;
+    float *att = nullptr, *geglu = nullptr;  // attention output [head*head_dim], gelu(gate)*up [ffn]
     ~zq_gemma3() {
+        gemma_decoder_free(decoder);
         zq_weight_free(token_embd);
         for (auto& b : blocks) {
             zq_weight_free(b.qkv);
@@ -543,8 +550,63 @@ static int gemma3_forward(zq_gemma3* m, uint32_t T, int variant, cudaStream_t st
     return ZQ_OK;
 }
 
+static bool gemma3_persistent(const zq_gemma3* m) {
+    return m->decoder != nullptr && m->decode_mode != ZQ_DECODE_LAUNCH_SEQUENCE;
+}
+
 static int gemma3_run(zq_gemma3* m, int variant, cudaStream_t st) {
+    if (gemma3_persistent(m)) return gemma_decoder_run(m->decoder, 1, variant, st);
     return m->graphs.run(variant, st, [&](cudaStream_t s) { return gemma3_forward(m, 1, variant, s); });
+}
+
+// The persistent decode kernel's view of the engine: built once, after every buffer exists.
+static int gemma3_make_decoder(zq_gemma3* m) {
+    const zq_gemma3_config& C = m->c;
+    if (m->n_seq != 1) return ZQ_OK;
+    for (const auto& b : m->blocks)
+        if (!b.qkv || !b.gate_up) return ZQ_OK;  // mixed types inside q|k|v or gate|up: launch sequence only
+    GemmaDecoderDesc d;
+    d.embed = C.embed;
+    d.head_dim = C.head_dim;
+    d.n_head = C.head;
+    d.n_kv = C.head_kv;
+    d.ffn = C.ffn;
+    d.ctx = C.ctx;
+    d.eps = C.rms_eps;
+    d.embed_scale = sqrtf((float)C.embed);
+    d.token_embd = m->token_embd;
+    d.output_norm_w = m->output_norm_w;
+    d.freqs = m->freqs;
+    for (uint32_t l = 0; l < C.layer; ++l) {
+        const zq_gemma3::Block& b = m->blocks[l];
+        GemmaDecoderLayer L;
+        L.qkv = b.qkv;
+        L.o = b.o;
+        L.gate_up = b.gate_up;
+        L.down = b.down;
+        L.attn_norm_w = b.attn_norm_w;
+        L.post_attn_norm_w = b.post_attn_norm_w;
+        L.q_norm_w = b.q_norm_w;
+        L.k_norm_w = b.k_norm_w;
+        L.ffn_norm_w = b.ffn_norm_w;
+        L.post_ffw_norm_w = b.post_ffw_norm_w;
+        L.kc = m->k[l];
+        L.vc = m->v[l];
+        const bool global = (l % C.global_every) == C.global_every - 1;
+        L.window = (global || C.sliding_window >= C.ctx) ? 0u : C.sliding_window;
+        d.layers.push_back(L);
+    }
+    d.qkv = m->qkv;
+    d.scores = m->scores;
+    d.att = m->att;
+    d.proj = m->proj;
+    d.g = m->geglu;
+    d.ffn_out = m->ffn;
+    d.logits = m->logits;
+    d.state = m->d_state;
+    d.record = m->d_record;
+    const int rc = gemma_decoder_create(d, &m->decoder);
+    return rc == ZQ_ERR_UNSUPPORTED ? ZQ_OK : rc;
 }
 
 // Upload several GGUF matrices with the same in_dim and type as one matrix of stacked rows.
@@ -690,6 +752,9 @@ int zq_gemma3_create_batch(const zq_gemma3_config* cfg, const zq_gemma3_weights*
     TRY(m->arena.alloc_n(&m->d_state, 4));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, C.ctx));
+    TRY(m->arena.alloc_n(&m->att, QD));
+    TRY(m->arena.alloc_n(&m->geglu, F));
+    TRY(gemma3_make_decoder(m));
 #undef TRY
     cudaError_t e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) {
@@ -697,6 +762,35 @@ int zq_gemma3_create_batch(const zq_gemma3_config* cfg, const zq_gemma3_weights*
         return cuda_fail(e);
     }
     *out = m;
+    return ZQ_OK;
+}
+
+int zq_gemma3_set_decode_mode(zq_gemma3* m, int mode) {
+    if (!m || mode < ZQ_DECODE_AUTO || mode > ZQ_DECODE_PERSISTENT) return ZQ_ERR_BAD_ARG;
+    if (mode == ZQ_DECODE_PERSISTENT && !m->decoder) return ZQ_ERR_UNSUPPORTED;
+    m->decode_mode = mode;
+    return ZQ_OK;
+}
+
+int zq_gemma3_decode_mode(const zq_gemma3* m, int* mode) {
+    if (!m || !mode) return ZQ_ERR_BAD_ARG;
+    *mode = gemma3_persistent(m) ? ZQ_DECODE_PERSISTENT : ZQ_DECODE_LAUNCH_SEQUENCE;
+    return ZQ_OK;
+}
+
+int zq_gemma3_profile_step(zq_gemma3* m, uint32_t token, zq_stream stream, long long* h_cycles, uint32_t capacity,
+                           uint32_t* n_ctas) {
+    if (!m || !h_cycles || !n_ctas || m->n_seq != 1) return ZQ_ERR_BAD_ARG;
+    if (!m->decoder) return ZQ_ERR_UNSUPPORTED;
+    if (m->seq_len >= m->c.ctx) return ZQ_ERR_SEQUENCE;
+    if (token >= m->c.vocab) return ZQ_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    set_state_kernel<<<1, 1, 0, st>>>(m->d_state, token, m->seq_len, 0);
+    ZQ_LAUNCH_CHECK();
+    int rc = gemma_decoder_profile(m->decoder, DECODE_LOGITS, st, h_cycles, capacity, n_ctas);
+    if (rc != ZQ_OK) return rc;
+    m->seq_len += 1;
+    m->seq_lens[0] = m->seq_len;
     return ZQ_OK;
 }
 
@@ -808,11 +902,18 @@ int zq_gemma3_decode_greedy(zq_gemma3* m, uint32_t first_token, uint32_t n_steps
     cudaStream_t st = as_stream(stream);
     set_state_kernel<<<1, 1, 0, st>>>(m->d_state, first_token, m->seq_len, 0);
     ZQ_LAUNCH_CHECK();
-    for (uint32_t s = 0; s < n_steps; ++s) {
-        int rc = gemma3_run(m, STEP_GREEDY, st);
+    if (gemma3_persistent(m)) {  // every step inside one launch: the argmax feeds the next token on the device
+        int rc = gemma_decoder_run(m->decoder, n_steps, DECODE_GREEDY, st);
         if (rc != ZQ_OK) return rc;
-        m->seq_len += 1;
+        m->seq_len += n_steps;
         m->seq_lens[0] = m->seq_len;
+    } else {
+        for (uint32_t s = 0; s < n_steps; ++s) {
+            int rc = gemma3_run(m, STEP_GREEDY, st);
+            if (rc != ZQ_OK) return rc;
+            m->seq_len += 1;
+            m->seq_lens[0] = m->seq_len;
+        }
     }
     ZQ_CUDA(cudaMemcpyAsync(h_tokens_out, m->d_record, n_steps * sizeof(uint32_t),
                             cudaMemcpyDeviceToHost, st));
