@@ -26,9 +26,15 @@ sys.path.insert(0, REPO)
 
 WORKLOAD = dict(qtype="q4_0", out_dim=262144, in_dim=1152, m_rows=1)
 BPB = {"q4_0": 18, "q4_1": 20, "q8_0": 34}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, from the ncu capture
-# summarised in profiles/gemv_mma1_q4_0_vocab_head_1152x262144.md (172 002 304 read + 4 768 000 written).
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from an ncu capture of
+# this workload (172 002 304 bytes read + 4 768 000 written); a shard's launch is scaled by its rows.
 NCU_TRAFFIC_BYTES = 176257536
+WORKLOAD_NAME = "configs[1]: Q4_0 GEMV 1152->262144, M=1, f32 activations"
+
+
+def config_dict(weights, l2, sharding, launch):
+    """The `config` object of both arms: same keys, so the two lines can be compared field by field."""
+    return dict(workload=WORKLOAD_NAME, weights=weights, l2=l2, sharding=sharding, launch=launch)
 
 
 def algorithmic_bytes(qtype, n, k, m=1):
@@ -132,29 +138,62 @@ def make_weight_bytes(qtype_name, n, k, seed, device):
     return torch.cat(chunks)
 
 
-def cpu_baseline(qtype_name, n, k, target_seconds=12.0):
-    """Times the oracle's f32-activation matmul (zig-nn dequant.zig:170-309) with all host threads on the
-    same [n, k] weight; bounded to about `target_seconds` of CPU work."""
+def _time_calls(fn, target_seconds, max_calls=5000):
+    fn()  # warm
+    calls, t0 = 0, time.perf_counter()
+    while True:
+        fn()
+        calls += 1
+        el = time.perf_counter() - t0
+        if el > target_seconds or calls >= max_calls:
+            return calls, el
+
+
+def openblas_leg(oracle, t, raw, x, n, k, qtype_name, target_seconds=4.0):
+    """zig-nn's dense CPU path for the same product (src/backend/cpu.zig:148-209: cblas_sgemm): the weight is
+    dequantised to f32 once, untimed, then y = x . W^T through the BLAS that numpy is linked against."""
     import numpy as np
-    import torch
+    info = "unknown"
+    try:
+        cfg = np.show_config(mode="dicts")
+        b = cfg.get("Build Dependencies", {}).get("blas", {})
+        info = "%s %s" % (b.get("name", "?"), b.get("version", "?"))
+    except Exception:
+        pass
+    w = oracle.dequantize(t, raw, n * k).reshape(n, k)
+    y = np.empty(n, np.float32)
+    calls, el = _time_calls(lambda: np.dot(w, x, out=y), target_seconds, 200)
+    threads = int(os.environ.get("OPENBLAS_NUM_THREADS", 0)) or host_threads()
+    return {"value": algorithmic_bytes(qtype_name, n, k) * calls / el / 1e9, "unit": "GB/s", "cores": threads,
+            "ms_per_call": el / calls * 1e3, "f32_gbs": (4.0 * n * k + 4 * k + 4 * n) * calls / el / 1e9,
+            "blas": info, "sample": "%d sgemv calls on the dequantised f32 weight in %.1f s" % (calls, el)}
+
+
+def cpu_baseline(qtype_name, n, k, target_seconds=10.0):
+    """Times the oracle's f32-activation matmul (zig-nn dequant.zig:170-309) on the same [n, k] weight: with
+    all host threads (`value`), on one thread — the way gpt2.zig:632-686 calls it — and zig-nn's dense BLAS
+    path on the dequantised weight. Bounded to about 20 s of CPU work."""
+    import numpy as np
     from zignn_b200 import ggml
     oracle, build = load_oracle()
     threads = host_threads()
     raw = make_weight_bytes(qtype_name, n, k, 42, "cpu").numpy()
     x = np.random.default_rng(43).standard_normal(k).astype(np.float32)
     t = ggml.TYPE_IDS[qtype_name]
-    oracle.matmul_f32(t, raw, x, n, k, threads)  # warm
-    calls, t0 = 0, time.perf_counter()
-    while True:
-        oracle.matmul_f32(t, raw, x, n, k, threads)
-        calls += 1
-        el = time.perf_counter() - t0
-        if el > target_seconds or calls >= 5000:
-            break
-    gbs = algorithmic_bytes(qtype_name, n, k) * calls / el / 1e9
-    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": "%d GEMV calls of %s [%d,%d] x f32[1,%d] in %.1f s (oracle build: %s)"
-                      % (calls, qtype_name, n, k, k, el, build)}
+    nbytes = algorithmic_bytes(qtype_name, n, k)
+    calls, el = _time_calls(lambda: oracle.matmul_f32(t, raw, x, n, k, threads), target_seconds)
+    c1, e1 = _time_calls(lambda: oracle.matmul_f32(t, raw, x, n, k, 1), 3.0)
+    out = {"value": nbytes * calls / el / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+           "sample": "%d GEMV calls of %s [%d,%d] x f32[1,%d] in %.1f s (oracle build: %s)"
+                     % (calls, qtype_name, n, k, k, el, build),
+           "reference_threads": {"value": nbytes * c1 / e1 / 1e9, "unit": "GB/s", "cores": 1,
+                                 "note": "linear_forward_q of gpt2.zig:632-686 runs matmul_q4_0_f32 on the calling thread",
+                                 "sample": "%d calls in %.1f s" % (c1, e1)}}
+    try:
+        out["openblas_sgemm"] = openblas_leg(oracle, t, raw, x, n, k, qtype_name)
+    except Exception as e:
+        out["openblas_sgemm"] = {"value": None, "error": repr(e)}
+    return out
 
 
 def run_reference(args):
@@ -181,8 +220,11 @@ def run_reference(args):
         "impl": "reference", "metric": "q4_0_gemv_algorithmic_gbs", "value": gbs, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": dict(workload="configs[1]: Q4_0 GEMV 1152->262144, M=1, f32 activations",
-                       note="CPU restatement of zig-nn matmul_q4_0_f32 (dequant.zig:170-182), row-split over host threads"),
+        "config": config_dict(weights="N(0,0.02) seed 42 quantised q4_0",
+                              l2="host memory (the 170 MB matrix exceeds the host caches)",
+                              sharding="rows split over %d host thread(s): CPU restatement of zig-nn matmul_q4_0_f32 "
+                                       "(dequant.zig:170-182)" % threads,
+                              launch="plain calls"),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": "%d timed GEMV calls (oracle build: %s)" % (args.steps, build)},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -261,46 +303,95 @@ def sweep_extra(torch, zq, ggml, m_list=(1,)):
     return out
 
 
+def decode_bytes_per_token(name, cfg, ctx_mid):
+    """Algorithmic HBM bytes of one decoded token: every quantised block once (plus GPT-2's f32 embedding
+    matrix as the logits head) and the key / value rows the attention reads at context `ctx_mid`."""
+    if name.startswith("gpt2"):
+        E, F, L, V = cfg["embed"], cfg["ffn"], cfg["layer"], cfg["vocab"]
+        weights = L * (3 * E * E + E * E + 2 * E * F)
+        return weights // 32 * BPB["q4_0"] + 4 * V * E + L * 2 * ctx_mid * E * 4
+    E, F, L, V, D = cfg["embed"], cfg["ffn"], cfg["layer"], cfg["vocab"], cfg["head_dim"]
+    qd, kd = cfg["head"] * D, cfg["head_kv"] * D
+    weights = L * ((qd + 2 * kd) * E + E * qd + 3 * E * F) + V * E
+    n_global = L // cfg["global_every"]
+    kv_rows = (L - n_global) * min(ctx_mid, cfg["sliding_window"]) + n_global * ctx_mid
+    return weights // 32 * BPB["q8_0"] + kv_rows * 2 * kd * 4
+
+
 def decode_extra(torch, zq, ggml):
-    """Batch-1 greedy decode rates of the two model shapes (configs[0] and configs[2]) through the
-    engines, next to the CPU checker on the same synthetic weights with all host threads. The CPU leg
-    is a bounded sample: a 4-token prefill and 6 decode steps."""
+    """Batch-1 greedy decode rates of the two model shapes (configs[0] and configs[2]) through the engines,
+    as a rate and as a fraction of the HBM roofline, next to the CPU checker on the same synthetic weights at
+    the same context: with the thread count zig-nn itself uses (GPT-2: the calling thread, gpt2.zig:632-686;
+    Gemma-3: min(cores, 8), gemma3.zig:285-286) and, from a short context, with all host threads. The CPU legs
+    are bounded samples: one prefill of the prompt and 6 decode steps."""
     import numpy as np
     from zignn_b200 import hostmodel
     oracle, build = load_oracle()
     threads = host_threads()
+    peak, peak_kind = measured_peak()
     out = []
-    cases = (("gpt2_small_q4_0", hostmodel.Gpt2Host, hostmodel.GPT2_SMALL, ggml.Q4_0, zq.Gpt2, oracle.Gpt2, 32, 128),
-             ("gemma3_1b_q8_0", hostmodel.Gemma3Host, hostmodel.GEMMA3_1B, ggml.Q8_0, zq.Gemma3, oracle.Gemma3, 512, 256))
-    for name, Host, cfg, qt, Eng, Ora, n_prompt, n_decode in cases:
+    cases = (("gpt2_small_q4_0", hostmodel.Gpt2Host, hostmodel.GPT2_SMALL, ggml.Q4_0, zq.Gpt2, oracle.Gpt2, 32, 128, 1),
+             ("gemma3_1b_q8_0", hostmodel.Gemma3Host, hostmodel.GEMMA3_1B, ggml.Q8_0, zq.Gemma3, oracle.Gemma3, 512, 256,
+              min(threads, 8)))
+    for name, Host, cfg, qt, Eng, Ora, n_prompt, n_decode, ref_threads in cases:
         host = Host.synthetic(cfg, qtype=qt, seed=42, device="cuda")
-        eng = Eng(host)
         prompt = np.random.default_rng(44).integers(0, cfg["vocab"], size=n_prompt)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        logits = eng.prefill(prompt)
-        first = int(logits.argmax().item())
-        t1 = time.perf_counter()
-        eng.decode_greedy(first, 8)  # the first steps set up the replayed launch sequence
-        t2 = time.perf_counter()
-        toks = eng.decode_greedy(first, n_decode)  # returns after the tokens are on the host
-        t3 = time.perf_counter()
-        eng.close()
-        ref = Ora(host, threads)
+        rates = {}
+        modes = [("persistent_kernel", zq.DECODE_AUTO), ("launch_sequence", zq.DECODE_LAUNCH_SEQUENCE)] \
+            if name.startswith("gemma") else [("launch_sequence", None)]
+        for label, mode in modes:
+            eng = Eng(host)
+            if mode is not None:
+                eng.set_decode_mode(mode)
+                if mode == zq.DECODE_AUTO and eng.decode_mode != zq.DECODE_PERSISTENT:
+                    eng.close()
+                    continue
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            first = int(eng.prefill(prompt).argmax().item())
+            t1 = time.perf_counter()
+            eng.decode_greedy(first, 8)  # the first steps set up the replayed launch sequence
+            eng.reset_cache()
+            first = int(eng.prefill(prompt).argmax().item())
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+            toks = eng.decode_greedy(first, n_decode)  # returns after the tokens are on the host
+            t3 = time.perf_counter()
+            rates[label] = dict(tok_s=n_decode / (t3 - t2), prefill_ms=(t1 - t0) * 1e3, last_token=int(toks[-1]))
+            eng.close()
+        best = max(rates, key=lambda k: rates[k]["tok_s"])
+        gpu_tps = rates[best]["tok_s"]
+        ref = Ora(host, ref_threads)
         c0 = time.perf_counter()
-        lc = ref.prefill(prompt[:4])
-        tok = int(np.argmax(lc))
+        tok = int(np.argmax(ref.prefill(prompt)))
         c1 = time.perf_counter()
         n_cpu = 6
         for _ in range(n_cpu):
             tok = int(np.argmax(ref.decode_next(tok)))
         c2 = time.perf_counter()
-        gpu_tps, cpu_tps = n_decode / (t3 - t2), n_cpu / (c2 - c1)
+        cpu_tps = n_cpu / (c2 - c1)
+        del ref
+        allt = Ora(host, threads)
+        tok = int(np.argmax(allt.prefill(prompt[:4])))
+        a1 = time.perf_counter()
+        for _ in range(n_cpu):
+            tok = int(np.argmax(allt.decode_next(tok)))
+        a2 = time.perf_counter()
+        del allt
+        nbytes = decode_bytes_per_token(name, cfg, n_prompt + n_decode // 2)
         out.append({"model": name, "prompt": n_prompt, "decode_steps": n_decode,
-                    "gpu_decode_tok_s": round(gpu_tps, 1), "gpu_prefill_ms": round((t1 - t0) * 1e3, 1),
-                    "cpu_decode_tok_s": round(cpu_tps, 2), "cpu_threads": threads, "cpu_build": build,
-                    "gpu_over_cpu": round(gpu_tps / cpu_tps, 1), "last_token": int(toks[-1])})
-        del eng, ref, host
+                    "gpu_decode_tok_s": round(gpu_tps, 1), "gpu_path": best,
+                    "gpu_paths": {k: round(v["tok_s"], 1) for k, v in rates.items()},
+                    "gpu_prefill_ms": round(rates[best]["prefill_ms"], 1),
+                    "bytes_per_token": nbytes, "achieved_gbs": round(nbytes * gpu_tps / 1e9, 1),
+                    "frac_of_hbm_peak": round(nbytes * gpu_tps / 1e9 / peak, 4), "peak_kind": peak_kind,
+                    "cpu_decode_tok_s": round(cpu_tps, 2), "cpu_threads": ref_threads,
+                    "cpu_prefill_tok_s": round(n_prompt / (c1 - c0), 2),
+                    "cpu_note": "thread count of the reference; same prompt and context as the GPU leg",
+                    "cpu_all_threads_short_context_tok_s": round(n_cpu / (a2 - a1), 2), "cpu_all_threads": threads,
+                    "cpu_build": build, "gpu_over_cpu": round(gpu_tps / cpu_tps, 1),
+                    "last_token": rates[best]["last_token"]})
+        del host
     return out
 
 
@@ -457,10 +548,46 @@ def main():
             gather_mode = "nccl (peer set-up failed: %r)" % (e,)
     if lin is None:
         lin = sharding.cuda_sharded_linear(raw_full, ggml.TYPE_IDS[q], n, k, zq.ACT_F32)
-    del raw_full
     qw, n_local = lin.weight, lin.rows
     x = torch.randn(1, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(43))
     y_local = torch.zeros(1, lin.per, device="cuda")
+
+    # Correctness of what is about to be timed (N > 1): the gathered row against the unsharded product on this
+    # rank's GPU, and against the CPU checker on 256 sampled rows. A mismatch ends the run with a non-zero status.
+    parity = None
+    if use_dist:
+        full = zq.QuantWeight(raw_full, ggml.TYPE_IDS[q], n, k)
+        want = zq.quant_matmul_no_grad(x, full, zq.ACT_F32)
+        if gather_mode == "peer":
+            got = lin.forward(x).clone()
+            lin.forward(x)  # an even number of exchanges: the two result buffers alternate
+        else:
+            zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, out=y_local)
+            got = lin.gather(y_local).clone()
+        torch.cuda.synchronize()
+        diff = float((got.double() - want.double()).norm() / want.double().norm())
+        parity = {"gathered_vs_unsharded_rel_l2": diff, "bit_equal": bool(torch.equal(got, want)), "tolerance": 2e-6}
+        if rank == 0:
+            import numpy as np
+            oracle, _ = load_oracle()
+            rows = np.sort(np.random.default_rng(5).choice(n, size=256, replace=False))
+            row_bytes = k // 32 * BPB[q]
+            sub = raw_full.view(n, row_bytes)[torch.from_numpy(rows).cuda()].cpu().numpy().reshape(-1)
+            ref = oracle.matmul_f32(ggml.TYPE_IDS[q], sub, x.cpu().numpy().reshape(-1), len(rows), k, 4)
+            g = got[0, torch.from_numpy(rows).cuda()].cpu().numpy()
+            parity["vs_cpu_oracle_rel_l2_256_rows"] = float(np.linalg.norm(g - ref) / np.linalg.norm(ref))
+            parity["ok"] = diff <= 2e-6 and parity["vs_cpu_oracle_rel_l2_256_rows"] <= 2e-6
+        else:
+            parity["ok"] = diff <= 2e-6
+        flag = torch.tensor([0 if parity["ok"] else 1], device="cuda")
+        dist.all_reduce(flag)
+        if int(flag.item()):
+            if rank == 0:
+                print(json.dumps({"error": "sharded result differs from the unsharded product", "parity": parity}), flush=True)
+            dist.destroy_process_group()
+            sys.exit(3)
+        del full, want, got
+    del raw_full
 
     # One rank's shard is smaller than L2 (126 MB) from 2 ranks up. Consecutive steps therefore use
     # different copies of the shard, enough of them to exceed L2, so every step streams from HBM.
@@ -537,6 +664,32 @@ def main():
     hy = torch.empty(tuple(step().shape), dtype=torch.float32).pin_memory()  # the full logits row on every rank
 
     host_call = zq.HostLinear(qw, 1, zq.ACT_F32) if not use_dist else None
+    from zignn_b200 import _lib as zlib
+    import ctypes as C
+
+    def copy_f32(dst_ptr, src_ptr, count):
+        zlib.check(zlib.load().zq_copy_f32(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), count,
+                                           C.c_void_p(torch.cuda.current_stream().cuda_stream)), "zq_copy_f32")
+
+    def e2e_device_part():
+        # pinned x -> device by a copy kernel, the sharded product with its exchange, the full row -> pinned y
+        copy_f32(x.data_ptr(), hx.data_ptr(), k)
+        y = step()
+        copy_f32(hy.data_ptr(), y.data_ptr(), hy.numel())
+
+    # N > 1: one recording per weight copy (an even number: the exchange alternates two result buffers, and a
+    # recording's copy-out reads the buffer of its own round), replayed in turn; one replay = one call.
+    e2e_graphs = []
+    if use_dist and gather_mode == "peer":
+        for _ in range(copies):
+            e2e_device_part()
+        torch.cuda.synchronize()
+        for _ in range(copies):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                e2e_device_part()
+            e2e_graphs.append(g)
+    e2e_calls = [0]
 
     def e2e_step():
         if host_call is not None:
@@ -544,13 +697,19 @@ def main():
             # straight into the pinned result buffer (PCIe traffic: 4K bytes in, 4N bytes out per step)
             host_call(hx, hy)
             return
-        x.copy_(hx, non_blocking=True)
-        hy.copy_(step(), non_blocking=True)
+        if e2e_graphs:
+            e2e_graphs[e2e_calls[0] % copies].replay()
+            e2e_calls[0] += 1
+        else:
+            x.copy_(hx, non_blocking=True)
+            hy.copy_(step(), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads hy
 
-    for _ in range(3):
+    for _ in range(copies if e2e_graphs else 3):
         e2e_step()
     e2e_ms = time_region(torch, e2e_step, args.steps, sync)
+    if e2e_graphs and e2e_calls[0] % 2:
+        e2e_step()  # untimed: back to an even number of exchanges
     if use_dist:
         tmax = torch.tensor([e2e_ms], device="cuda")
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -575,15 +734,16 @@ def main():
             "metric": "q4_0_gemv_algorithmic_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": dict(workload="configs[1]: Q4_0 GEMV 1152->262144, M=1, f32 activations",
-                           weights="N(0,0.02) seed 42 quantised q4_0", l2=("weights (170 MB) larger than L2 (126 MB)" if copies == 1 else
-                               "%d copies of the %.0f MB shard used in turn (together larger than L2)"
-                               % (copies, local_weight_bytes / 1e6)),
-                           sharding="rows split over %d rank(s)%s" % (
-                               world, ", all-gather of outputs: " + gather_mode +
-                               (" stores fused into the GEMV epilogue" if getattr(lin, "fused", False) else "")
-                               if use_dist else ""),
-                           launch=("CUDA graph replay, %d steps per recording" % seq_len) if graph is not None else "plain calls"),
+            "config": config_dict(
+                weights="N(0,0.02) seed 42 quantised q4_0",
+                l2=("weights (170 MB) larger than L2 (126 MB)" if copies == 1 else
+                    "%d copies of the %.0f MB shard used in turn (together larger than L2)"
+                    % (copies, local_weight_bytes / 1e6)),
+                sharding="rows split over %d rank(s)%s" % (
+                    world, ", all-gather of outputs: " + gather_mode +
+                    (" stores fused into the GEMV epilogue" if getattr(lin, "fused", False) else "")
+                    if use_dist else ""),
+                launch=("CUDA graph replay, %d steps per recording" % seq_len) if graph is not None else "plain calls"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          # ncu capture of the full matrix; a shard's launch is scaled by its rows
                          "traffic": int(NCU_TRAFFIC_BYTES * local_bytes / algorithmic_bytes(q, n, k)),
@@ -593,19 +753,25 @@ def main():
             "gpu_launches": args.steps * (1 if gather_mode != "peer" or getattr(lin, "fused", False) else 3),
             "clocks": clocks,
         }
+        if parity is not None:
+            line["parity"] = parity
         if not args.no_extra and world == 1:
             try:
                 line["cpu_baseline"] = cpu_baseline(q, n, k)
             except Exception as e:  # the baseline is informational; never lose the GPU line
                 line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": host_threads(), "kind": "port",
                                         "sample": "failed: %r" % (e,)}
+            # the second half of the metric: decode tok/s of the two model shapes, with their HBM roofline
+            try:
+                line["roofline"]["decode"] = decode_extra(torch, zq, ggml)
+            except Exception as e:
+                line["roofline"]["decode"] = {"error": repr(e)}
+            line["decode"] = line["roofline"]["decode"]
             line["extra"] = {}
-            for key, fn in (("sweep_hbm_cold", lambda: sweep_extra(torch, zq, ggml, m_list=(1, 4, 16))),
-                            ("decode", lambda: decode_extra(torch, zq, ggml))):
-                try:
-                    line["extra"][key] = fn()
-                except Exception as e:
-                    line["extra"][key] = {"error": repr(e)}
+            try:
+                line["extra"]["sweep_hbm_cold"] = sweep_extra(torch, zq, ggml, m_list=(1, 4, 16))
+            except Exception as e:
+                line["extra"]["sweep_hbm_cold"] = {"error": repr(e)}
         print(json.dumps(line), flush=True)
     if use_dist:
         dist.barrier()

@@ -450,10 +450,10 @@ int zq_gemma3_decode_mode(const zq_gemma3* m, int* mode);
 /* Per-phase timing of one decode step, the device-side counterpart of gemma3.ProfileStats
  * (gemma3.zig:35-92, filled at :417-491): the persistent kernel runs one step (like decode_next) and every
  * CTA records its SM cycle counter at each phase boundary. h_cycles[n_ctas][capacity] receives the stamps of
- * CTA c at h_cycles[c * capacity ...], in program order: token start; per layer 16 stamps (qkv prologue done,
- * qkv done, barrier passed, scores done, barrier, softmax.V done, barrier, o prologue done, o done, barrier,
- * ffn prologue done, gate/up done, barrier, down prologue done, down done, barrier); head prologue done, head
- * done. Unused entries are 0. capacity >= 3 + 16 * layers holds all of them. ZQ_ERR_UNSUPPORTED without the
+ * CTA c at h_cycles[c * capacity ...], in program order: token start; per layer 10 stamps (qkv prologue done,
+ * qkv done, scores done, softmax.V done, o prologue done, o done, ffn prologue done, gate/up done, down prologue
+ * done, down done); head prologue done, head done. A prologue includes the wait for the vector it consumes.
+ * Unused entries are 0. capacity >= 3 + 10 * layers holds all of them. ZQ_ERR_UNSUPPORTED without the
  * persistent kernel. */
 int zq_gemma3_profile_step(zq_gemma3* m, uint32_t token, zq_stream stream, long long* h_cycles, uint32_t capacity,
                            uint32_t* n_ctas);

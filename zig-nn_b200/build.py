@@ -1,4 +1,7 @@
-"""Builds libzq.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
+"""Builds libzq.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a, and the module image of the f32
+forward kernels that zig-nn's CUDA backend loads by name (cuda_kernels.fatbin / cuda_kernels.cubin: what
+`nvcc -ptx -arch=sm_90 ... cuda_kernels.cu` produces by hand in the reference, src/backend/cuda_kernels.cu:2,
+here as a build step and for sm_100a; cuModuleLoadData takes either file's bytes).
 
     python zig-nn_b200/build.py [--force] [--verbose]
 """
@@ -13,6 +16,9 @@ REPO = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libzq.so")
+MODULE_SRC = os.path.join(CSRC, "module", "cuda_kernels.cu")
+MODULE_FATBIN = os.path.join(HERE, "cuda_kernels.fatbin")
+MODULE_CUBIN = os.path.join(HERE, "cuda_kernels.cubin")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -53,8 +59,21 @@ def _compile(src, verbose):
     return obj, r.stderr
 
 
+def build_module_image(force=False):
+    """cuda_kernels.fatbin and cuda_kernels.cubin: the sm_100a image of csrc/module/cuda_kernels.cu."""
+    for out, flag in ((MODULE_FATBIN, "-fatbin"), (MODULE_CUBIN, "-cubin")):
+        if not force and os.path.exists(out) and os.path.getmtime(out) >= os.path.getmtime(MODULE_SRC):
+            continue
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", flag, "-o", out, MODULE_SRC]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed for the module image:\n%s\n%s" % (r.stdout, r.stderr))
+    return MODULE_FATBIN
+
+
 def build(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
+    build_module_image(force)
     if force:
         for f in os.listdir(OBJ):
             os.remove(os.path.join(OBJ, f))

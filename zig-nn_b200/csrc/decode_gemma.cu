@@ -1,7 +1,7 @@
 // One persistent cooperative kernel per Gemma-3 decode step (or per run of greedy steps): the whole
 // token — embedding, 26 x (norm, qkv, attention, o, norm, gate/up, GeGLU, down), final norm, logits,
-// argmax — runs as phases of ONE grid of one CTA per SM, separated by grid barriers, instead of about
-// 270 dependent kernel launches (gemma3.zig:662-846; the one-encoder form of gemma3_metal.zig:189-260).
+// argmax — runs as phases of ONE grid of one CTA per SM instead of about 270 dependent kernel launches
+// (gemma3.zig:662-846; the one-encoder form of gemma3_metal.zig:189-260).
 //
 // Arithmetic. Every phase performs the roundings of the launch-sequence engine (ops.cu, gemv_q8.cu) in
 // the same order — exact int8 block dots, block terms (d*s)*float(idot) added in block order, 16-lane
@@ -12,17 +12,22 @@
 //   * The producer walks the static schedule of weight "units" (a few whole rows of a matrix with their
 //     scales) that this CTA will need, in order, and streams them into a ring of shared-memory slots
 //     with cp.async.bulk + mbarrier. Weights do not depend on activations, so the producer runs ahead
-//     of the consumers across phase and token boundaries: HBM keeps streaming while the consumers sit
-//     in a grid barrier, a norm or the attention's serial chains.
+//     of the consumers across phase and token boundaries: HBM keeps streaming while the consumers wait
+//     for an exchange, run a norm or the attention's serial chains.
 //   * Small vectors (the residual stream, norms, the quantised activation image) are recomputed by every
-//     CTA in its own shared memory rather than exchanged: that removes the grid barrier a separate
-//     norm phase would need.
-//   * Cross-CTA data (qkv, scores, attention output, projections) goes through global memory (L2).
+//     CTA in its own shared memory rather than exchanged.
+//   * Vectors that cross CTAs (qkv, scores, attention output, projections) are exchanged through global
+//     memory as 64-bit words {value, epoch}: the consumer's load of a word is at the same time the test
+//     whether its producer has written it, so an exchange costs one store and one load round trip and no
+//     grid-wide barrier exists. Each exchange of a run has its own epoch number; buffers alternate with
+//     the layer's parity and every CTA signs a per-layer presence word, so a buffer is rewritten only after
+//     every CTA has finished the layer that read it.
 //
-// Every wait is bounded: a grid barrier or slot wait that runs out records a code in the device error
-// word, raises the abort flag, and every CTA drains its copies in flight and returns.
+// Every wait is bounded: a poll or slot wait that runs out records a code in the device error word,
+// raises the abort flag (tagged with the launch), and every CTA drains its copies in flight and returns.
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <new>
 #include <vector>
@@ -36,29 +41,40 @@ namespace {
 constexpr int kConsumerWarps = 16;
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 32;
-constexpr unsigned int kErrGridBarrier = 0x47424152u;  // 'GBAR'
-constexpr unsigned int kErrUnitWait = 0x554E4954u;     // 'UNIT'
-constexpr uint32_t kGridSpinLimit = 1u << 22;
+constexpr unsigned int kErrExchange = 0x58434847u;  // 'XCHG'
+constexpr unsigned int kErrUnitWait = 0x554E4954u;  // 'UNIT'
+constexpr uint32_t kPollLimit = 1u << 21;
 constexpr uint32_t kSlotSpinLimit = 1u << 22;
-constexpr uint32_t kVTile = 512;  // positions per V tile of the attention phase
+constexpr uint32_t kVTile = 256;   // positions per V tile of the attention phase
 
-enum { EP_STORE = 0, EP_GEGLU = 1, EP_LOGITS = 2 };
+enum { EP_VECTOR = 0, EP_GEGLU = 1, EP_LOGITS = 2 };
 
-// A quantised matrix as the kernel walks it: units of `rows_per_unit` whole rows.
+// A quantised matrix as the kernel walks it. Rows are taken in tiles of `rows_per_tile` (at most 8: one
+// weight row per lane group of an int8 tensor-core tile); a tile whose rows do not fit a ring slot is cut
+// along K into `chunks` pieces of `chunk_quads` quads (4 blocks each). One unit = one piece of one tile.
 struct DMat {
     const uint8_t* qs;
     const uint8_t* sc;
     uint32_t type, n_rows, nb, nbp;
     uint32_t row_q_bytes, row_s_bytes;
-    uint32_t rows_per_unit, n_units;
-    uint32_t split;  // 1: a unit holds rows_per_unit/2 rows of the first half and the matching rows of the second
+    uint32_t rows_per_tile, n_tiles;
+    uint32_t split;       // 1: a tile holds rows_per_tile/2 rows of the first half and the matching rows of the second
+    uint32_t chunks;      // pieces per tile along K (1: whole rows, one bulk copy of quants and one of scales)
+    uint32_t chunk_quads; // quads per piece (the last piece of a row may be shorter)
+    uint32_t pad_;
 };
 
-struct DLayer {
+struct alignas(16) DLayer {
     DMat qkv, o, gate_up, down;
     const float *attn_norm_w, *post_attn_norm_w, *q_norm_w, *k_norm_w, *ffn_norm_w, *post_ffw_norm_w;
     float *kc, *vc;
     uint32_t window;  // 0: every position (global layer)
+};
+
+// Exchange buffers, two of each (layer parity). A word is (epoch << 32) | float bits.
+struct Exchange {
+    unsigned long long *qkv, *scores, *att, *proj, *g, *ffn, *best;
+    uint32_t qkv_n, scores_n, att_n, proj_n, g_n, ffn_n, best_n;  // words per parity
 };
 
 struct DParams {
@@ -66,27 +82,28 @@ struct DParams {
     DMat head;  // token_embd: embedding rows and the tied logits head
     const float* output_norm_w;
     const float* freqs;
-    float *qkv, *scores, *att, *proj, *g, *ffn, *logits;
+    float* logits;
     uint32_t* state;   // [0] token, [1] position, [2] next slot of the greedy record
     uint32_t* record;
-    uint32_t* sync;    // [0], [1]: barrier counters used by alternate launches; [2]: abort flag
-    float* part_val;   // per-CTA argmax candidates
-    uint32_t* part_idx;
+    uint32_t* abort_word;  // holds the id of a launch that gave up
     unsigned int* err;
     long long* prof;   // optional: per-CTA cycle stamps of one step (prof_cap per CTA); nullptr = off
+    Exchange ex;
     uint32_t prof_cap;
     uint32_t n_layer, E, D, n_head, n_kv, F, ctx, max_len;
     float eps, embed_scale;
     // shared-memory carve-up (bytes from the start of dynamic shared memory)
-    uint32_t n_slots, slot_bytes, off_ring, off_xres, off_xs, off_rope, off_scratch, terms_per_warp, nbp_max;
+    uint32_t n_slots, slot_bytes, off_ring, off_layers, off_xres, off_xs, off_rope, off_vnew, off_scratch;
+    uint32_t terms_per_warp, nbp_max;
+    uint32_t terms_bytes;  // bytes behind the activation image: block terms, staging of the prologues
 };
 
 // ---- small device helpers --------------------------------------------------------------------
 
 __device__ __forceinline__ void cbar() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
 
-__device__ __forceinline__ float exp_f32(float x) { return (float)exp((double)x); }
-__device__ __forceinline__ float gelu_tanh(float v) {
+__device__ __noinline__ float exp_f32(float x) { return (float)exp((double)x); }
+__device__ __noinline__ float gelu_tanh(float v) {
     const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
     const float inner = __fmul_rn(0.7978845608f, __fadd_rn(v, cube));
     return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, (float)tanh((double)inner)));
@@ -130,6 +147,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
+// The same with a suspend-time hint (nanoseconds): the thread may sleep in hardware until the phase completes
+// or the time has passed, instead of occupying the shared-memory pipeline with polls.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok;
+}
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
@@ -138,71 +168,130 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+__device__ __forceinline__ uint32_t ld_relaxed_gpu_u32(const uint32_t* p) {
     uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
-    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// One exchange word: a naturally aligned 64-bit store / load is a single memory operation.
+__device__ __forceinline__ void xstore(unsigned long long* p, float v, uint32_t epoch) {
+    const unsigned long long w = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ void xstore_u32(unsigned long long* p, uint32_t v, uint32_t epoch) {
+    const unsigned long long w = ((unsigned long long)epoch << 32) | (unsigned long long)v;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long xload(const unsigned long long* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
 }
 
-// Shared state of one CTA.
+// Head of the dynamic shared memory: the launch parameters (copied once, so that device functions read them
+// with shared-memory loads instead of through the parameter space), the ring's barriers and small exchange cells.
+struct Shared {
+    DParams p;
+    unsigned long long full[64];
+    unsigned long long empty[64];
+    uint32_t released[64];  // per ring slot: uses consumed so far
+    int abort;
+    uint32_t launch_id;     // the abort word holds the id of the launch that gave up
+    float part[16];         // 16 lane sums
+    float bc;               // broadcast cell
+    float red[32];          // per-warp partials
+    float bval[kConsumerWarps];
+    uint32_t bidx[kConsumerWarps];
+};
+constexpr uint32_t kSharedHead = (sizeof(Shared) + 127u) & ~127u;
+
+__device__ __forceinline__ unsigned char* smem_base() {
+    extern __shared__ __align__(128) unsigned char zq_decode_smem[];
+    return zq_decode_smem;
+}
+__device__ __forceinline__ Shared& sh() { return *reinterpret_cast<Shared*>(smem_base()); }
+
+// Per-thread view of the CTA's shared state; built (a few address computations) at the top of every device
+// function rather than passed by reference, which would put it into local memory.
 struct Cta {
     unsigned char* smem;
     uint32_t smem32;
     uint32_t full0, empty0;  // shared addresses of the mbarrier arrays
     volatile int* s_abort;
-    int* s_ok;
-    float* part;   // 16 lane sums
-    float* bc;     // broadcast cell
-    float* red;    // 16 per-warp partials + spare
+    float* part;
+    float* bc;
+    float* red;
+    volatile uint32_t* released;
     int tid, lane, warp;
-    uint32_t epoch;   // grid barriers passed (thread 0 only uses it)
-    uint32_t launch_id;  // the abort word holds the id of the launch that gave up
-    volatile uint32_t* released;  // per ring slot: uses consumed so far
+    uint32_t launch_id;
 };
-
-// Bounded wait for a ring slot. On a timeout the CTA-wide abort flag is raised; the caller skips its work
-// and the CTA leaves together at the next grid barrier.
-__device__ __forceinline__ bool slot_wait(const Cta& c, uint32_t bar, uint32_t parity, unsigned int* err) {
-    for (uint32_t i = 0; i < kSlotSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *c.s_abort) return false;
-    }
-    *c.s_abort = 1;
-    atomicExch(err, kErrUnitWait);
-    return false;
+__device__ __forceinline__ Cta make_cta() {
+    Shared& S = sh();
+    Cta c;
+    c.smem = smem_base();
+    c.smem32 = (uint32_t)__cvta_generic_to_shared(c.smem);
+    c.full0 = (uint32_t)__cvta_generic_to_shared(S.full);
+    c.empty0 = (uint32_t)__cvta_generic_to_shared(S.empty);
+    c.s_abort = &S.abort;
+    c.part = S.part;
+    c.bc = &S.bc;
+    c.red = S.red;
+    c.released = S.released;
+    c.tid = threadIdx.x;
+    c.lane = threadIdx.x & 31;
+    c.warp = threadIdx.x >> 5;
+    c.launch_id = S.launch_id;
+    return c;
 }
 
-// Grid barrier over the consumer threads of every CTA. Returns false (to every consumer thread of the CTA)
-// when this CTA has raised its abort flag, another CTA has, or the wait ran out.
-__device__ __forceinline__ bool grid_barrier(Cta& c, const DParams& p, uint32_t* counter) {
-    cbar();
-    if (c.tid == 0) {
-        bool ok = !*c.s_abort;
-        if (ok) {
-            c.epoch += 1;
-            const uint32_t target = c.epoch * gridDim.x;
-            red_release_gpu_add(counter, 1u);
-            ok = false;
-            for (uint32_t i = 0; i < kGridSpinLimit; ++i) {
-                if ((int32_t)(ld_acquire_gpu(counter) - target) >= 0) {
-                    ok = true;
-                    break;
+__device__ __forceinline__ void raise_abort(const Cta& c, const DParams& p, unsigned int code) {
+    *c.s_abort = 1;
+    if (ld_relaxed_gpu_u32(p.abort_word) != c.launch_id) atomicExch(p.err, code);
+    atomicExch(p.abort_word, c.launch_id);
+}
+
+// Up to N words of an exchange buffer per thread — words first, first + stride, ... (valid below n) — with all
+// loads in flight at once; words whose producer has not written yet are polled again, a bounded number of times.
+template <int N>
+__device__ __forceinline__ void xload_batch(const Cta& c, const DParams& p, const unsigned long long* buf,
+                                            uint32_t first, uint32_t stride, uint32_t n, uint32_t epoch, float (&out)[N]) {
+    unsigned long long w[N];
+#pragma unroll
+    for (int u = 0; u < N; ++u) w[u] = first + u * stride < n ? xload(buf + first + u * stride) : 0ull;
+    bool missing = false;
+#pragma unroll
+    for (int u = 0; u < N; ++u)
+        if (first + u * stride < n && (uint32_t)(w[u] >> 32) != epoch) missing = true;
+    if (missing) {
+        for (uint32_t spin = 0; missing && spin < kPollLimit; ++spin) {
+            missing = false;
+#pragma unroll
+            for (int u = 0; u < N; ++u) {
+                if (first + u * stride < n && (uint32_t)(w[u] >> 32) != epoch) {
+                    w[u] = xload(buf + first + u * stride);
+                    if ((uint32_t)(w[u] >> 32) != epoch) missing = true;
                 }
-                if ((i & 63u) == 63u && ld_acquire_gpu(p.sync + 2) == c.launch_id) break;
             }
-            if (!ok && ld_acquire_gpu(p.sync + 2) != c.launch_id) atomicExch(p.err, kErrGridBarrier);
+            if (missing && (spin & 63u) == 63u && (*c.s_abort || ld_relaxed_gpu_u32(p.abort_word) == c.launch_id)) break;
         }
-        if (!ok) {
-            atomicExch(p.sync + 2, c.launch_id);
-            *c.s_abort = 1;
-        }
-        *c.s_ok = ok ? 1 : 0;
+        if (missing) raise_abort(c, p, kErrExchange);
     }
-    cbar();
-    return *c.s_ok != 0;
+#pragma unroll
+    for (int u = 0; u < N; ++u) out[u] = __uint_as_float((uint32_t)w[u]);
+}
+
+// Bounded wait for a ring slot. On a timeout the abort flag is raised; the caller skips its work and the
+// CTA leaves at its next uniform check.
+__device__ __forceinline__ bool slot_wait(const Cta& c, const DParams& p, uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    // Not there yet: wait without flooding the shared-memory pipeline that the working warps' loads, shuffles
+    // and barrier operations go through. About a second in all.
+    for (uint32_t i = 0; i < (1u << 19); ++i) {
+        if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+        if ((i & 15u) == 15u && *c.s_abort) return false;
+    }
+    raise_abort(c, p, kErrUnitWait);
+    return false;
 }
 
 // Sum of squares in the CPU loop's order (gemma3.zig:920-930): 16 lane accumulators, lanes added 0..15,
@@ -212,15 +301,25 @@ __device__ __forceinline__ float sumsq_lanes16(const Cta& c, const float* xs, ui
     if (c.tid < 16) {
         float acc = 0.0f;
         uint32_t i = c.tid;
-        for (; i + 16 * 7 < dim16; i += 16 * 8) {
+        if (i + 16 * 7 < dim16) {  // loads and squares of the next eight elements run under the adds of these
             float v[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) v[u] = xs[i + 16 * u];
+            i += 16 * 8;
+#pragma unroll 1
+            for (; i + 16 * 7 < dim16; i += 16 * 8) {
+                float n[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __fmul_rn(v[u], v[u]);
+                for (int u = 0; u < 8; ++u) n[u] = xs[i + 16 * u];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, v[u]);
+                for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, __fmul_rn(v[u], v[u]));
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = n[u];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, __fmul_rn(v[u], v[u]));
         }
+#pragma unroll 1
         for (; i < dim16; i += 16) acc = __fadd_rn(acc, __fmul_rn(xs[i], xs[i]));
         c.part[c.tid] = acc;
     }
@@ -229,25 +328,35 @@ __device__ __forceinline__ float sumsq_lanes16(const Cta& c, const float* xs, ui
         float ss = c.part[0];
 #pragma unroll
         for (int l = 1; l < 16; ++l) ss = __fadd_rn(ss, c.part[l]);
+#pragma unroll 1
         for (uint32_t i = dim16; i < dim; ++i) ss = __fadd_rn(ss, __fmul_rn(xs[i], xs[i]));
         *c.bc = ss;
     }
     cbar();
     return *c.bc;
 }
-// Squares added one by one (rms_norm_in_place, gemma3.zig:949-959).
+// Squares added one by one (rms_norm_in_place, gemma3.zig:949-959); the next eight loads run under the adds.
 __device__ __forceinline__ float sumsq_sequential(const float* xs, uint32_t dim) {
     float ss = 0.0f;
     uint32_t i = 0;
-    for (; i + 8 <= dim; i += 8) {
-        float v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = xs[i + u];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = __fmul_rn(v[u], v[u]);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) ss = __fadd_rn(ss, v[u]);
+    if (dim >= 8) {
+        float4 a = *reinterpret_cast<const float4*>(xs), b = *reinterpret_cast<const float4*>(xs + 4);
+#pragma unroll 1
+        for (i = 8; i + 8 <= dim; i += 8) {
+            const float4 na = *reinterpret_cast<const float4*>(xs + i), nb = *reinterpret_cast<const float4*>(xs + i + 4);
+            ss = __fadd_rn(ss, __fmul_rn(a.x, a.x)); ss = __fadd_rn(ss, __fmul_rn(a.y, a.y));
+            ss = __fadd_rn(ss, __fmul_rn(a.z, a.z)); ss = __fadd_rn(ss, __fmul_rn(a.w, a.w));
+            ss = __fadd_rn(ss, __fmul_rn(b.x, b.x)); ss = __fadd_rn(ss, __fmul_rn(b.y, b.y));
+            ss = __fadd_rn(ss, __fmul_rn(b.z, b.z)); ss = __fadd_rn(ss, __fmul_rn(b.w, b.w));
+            a = na;
+            b = nb;
+        }
+        ss = __fadd_rn(ss, __fmul_rn(a.x, a.x)); ss = __fadd_rn(ss, __fmul_rn(a.y, a.y));
+        ss = __fadd_rn(ss, __fmul_rn(a.z, a.z)); ss = __fadd_rn(ss, __fmul_rn(a.w, a.w));
+        ss = __fadd_rn(ss, __fmul_rn(b.x, b.x)); ss = __fadd_rn(ss, __fmul_rn(b.y, b.y));
+        ss = __fadd_rn(ss, __fmul_rn(b.z, b.z)); ss = __fadd_rn(ss, __fmul_rn(b.w, b.w));
     }
+#pragma unroll 1
     for (; i < dim; ++i) ss = __fadd_rn(ss, __fmul_rn(xs[i], xs[i]));
     return ss;
 }
@@ -271,17 +380,14 @@ __device__ __forceinline__ XImage ximage(unsigned char* scratch, uint32_t nbp_ma
 
 // quantize_row_q8 (simd_dot.zig:25-64) of the 32 values held one per lane, written into the image.
 __device__ __forceinline__ void quant_block_to_image(float v, uint32_t b, int lane, const XImage& x) {
-    float amax = fabsf(v);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    // |v| as an unsigned integer orders like the float: one warp-wide integer maximum gives max(abs(v))
+    const float amax = __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(v))));
     const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
     const float inv = __fdiv_rn(1.0f, s);
     float r = roundf(__fmul_rn(v, inv));
     r = fminf(127.0f, fmaxf(-127.0f, r));
     const int qi = (int)r;
-    int acc = qi;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+    const int acc = __reduce_add_sync(0xFFFFFFFFu, qi);
     const uint32_t w = (uint32_t)lane >> 2;
     unsigned char* dst = reinterpret_cast<unsigned char*>(w < 4 ? x.xl : x.xh);
     dst[((((b >> 2) * 4 + (w & 3u)) * 4 + (b & 3u)) << 2) + ((uint32_t)lane & 3u)] = (unsigned char)(signed char)qi;
@@ -292,96 +398,159 @@ __device__ __forceinline__ void quant_block_to_image(float v, uint32_t b, int la
 }
 // Blocks [nb, nbp) of the image (row padding): zero quants, scale 1.
 __device__ __forceinline__ void image_padding(const Cta& c, const XImage& x, uint32_t nb, uint32_t nbp) {
+#pragma unroll 1
     for (uint32_t i = nb * 8 + c.tid; i < nbp * 8; i += kConsumers) {
         const uint32_t b = i >> 3, w = i & 7u;
         uint32_t* dst = reinterpret_cast<uint32_t*>(w < 4 ? x.xl : x.xh);
         dst[((b >> 2) * 4 + (w & 3u)) * 4 + (b & 3u)] = 0u;
     }
+#pragma unroll 1
     for (uint32_t b = nb + c.tid; b < nbp; b += kConsumers) {
         x.xsc[b] = 1.0f;
         x.xsum[b] = 0;
     }
 }
-// Quantise a dense f32 vector from global memory into the image.
-__device__ __forceinline__ void quantise_global(const Cta& c, const float* src, uint32_t dim, const XImage& x) {
-    for (uint32_t i = c.tid; i < dim; i += kConsumers) quant_block_to_image(__ldcg(src + i), i >> 5, c.lane, x);
+
+// An exchanged f32 vector (dim % 32 == 0), quantised into the image. 16 words per thread and pass, all in
+// flight at once: one round trip for up to 8192 elements. The values are parked in `stage` (16 * 512 floats,
+// each thread reads back only what it wrote) so that the quantiser exists once, in a rolled loop: the kernel
+// runs every phase once per layer, and code size, not arithmetic, is what instruction fetch pays for.
+__device__ __noinline__ void quantise_exchanged(const unsigned long long* buf,
+                                                uint32_t dim, uint32_t epoch, float* stage) {
+    const Cta c = make_cta();
+    const DParams& p = sh().p;
+    const XImage x = ximage(c.smem + p.off_scratch, p.nbp_max);
+    for (uint32_t base = 0; base < dim; base += kConsumers * 16) {
+        {
+            float v[16];
+            xload_batch<16>(c, p, buf, base + c.tid, kConsumers, dim, epoch, v);
+#pragma unroll
+            for (int u = 0; u < 16; ++u) stage[u * kConsumers + c.tid] = v[u];
+        }
+#pragma unroll 1
+        for (uint32_t u = 0; u < 16; ++u) {
+            const uint32_t i = base + u * kConsumers + c.tid;
+            if (i - c.lane >= dim) break;  // whole warps
+            quant_block_to_image(stage[u * kConsumers + c.tid], i >> 5, c.lane, x);
+        }
+    }
     image_padding(c, x, dim >> 5, (dim / 32 + 3u) & ~3u);
 }
 
 // xres (+)= rms_norm(src, w1) when src != nullptr; then h = rms_norm(xres, w2) quantised into the image
-// (gemma3.zig:662-666, 725-737, 768-773 followed by the row quantiser of the next linear).
-__device__ __forceinline__ void norm_quant(const Cta& c, const float* src, const float* w1, const float* w2,
-                                           float* xres, float* xs, uint32_t dim, float eps, const XImage& x) {
+// (gemma3.zig:662-666, 725-737, 768-773 followed by the row quantiser of the next linear). The norm weights
+// are requested (asynchronous copies into `wstage`, 2 * dim floats) together with the exchanged vector, so the
+// prologue pays one memory round trip.
+__device__ __noinline__ void norm_quant(const unsigned long long* src, uint32_t epoch,
+                                        const float* w1, const float* w2, float* xres, float* xs, uint32_t dim,
+                                        float eps, float* wstage) {
+    const Cta c = make_cta();
+    const DParams& p = sh().p;
+    const XImage x = ximage(c.smem + p.off_scratch, p.nbp_max);
+    float* w1s = wstage;
+    float* w2s = wstage + dim;
+    {
+        const uint32_t ws32 = c.smem32 + (uint32_t)(reinterpret_cast<unsigned char*>(wstage) - c.smem);
+        for (uint32_t i = c.tid * 4; i < dim; i += kConsumers * 4) {
+            if (src) cp_async16(ws32 + i * 4, w1 + i);
+            cp_async16(ws32 + (dim + i) * 4, w2 + i);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     if (src) {
-        for (uint32_t i = c.tid; i < dim; i += kConsumers) xs[i] = __ldcg(src + i);
+#pragma unroll 1
+        for (uint32_t base = 0; base < dim; base += kConsumers * 4) {
+            float v[4];
+            xload_batch<4>(c, p, src, base + c.tid, kConsumers, dim, epoch, v);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = base + u * kConsumers + c.tid;
+                if (i < dim) xs[i] = v[u];
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (src) {
         cbar();
         const float ss = sumsq_lanes16(c, xs, dim);
         const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+#pragma unroll 1
         for (uint32_t i = c.tid; i < dim; i += kConsumers)
-            xres[i] = __fadd_rn(xres[i], __fmul_rn(__fmul_rn(xs[i], inv), __ldg(w1 + i)));
+            xres[i] = __fadd_rn(xres[i], __fmul_rn(__fmul_rn(xs[i], inv), w1s[i]));
     }
     cbar();
     const float ss = sumsq_lanes16(c, xres, dim);
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+#pragma unroll 1
     for (uint32_t i = c.tid; i < dim; i += kConsumers)
-        quant_block_to_image(__fmul_rn(__fmul_rn(xres[i], inv), __ldg(w2 + i)), i >> 5, c.lane, x);
+        quant_block_to_image(__fmul_rn(__fmul_rn(xres[i], inv), w2s[i]), i >> 5, c.lane, x);
     image_padding(c, x, dim >> 5, (dim / 32 + 3u) & ~3u);
 }
 
-// Block terms of one unit (`rows` whole rows in shared memory): lane (pair, t) handles (row, quad) pairs,
-// 8 per warp pass; after the 4-lane transpose-reduce lane t holds the exact dot of block 4*quad + t.
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    // rows 8..15 of the 16-row tile are not used: their fragments (a1, a3) are zero
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%6,%5,%6}, {%7,%8}, "
+                 "{%6,%6,%6,%6};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a2), "r"(0), "r"(b0), "r"(b1));
+}
+
+// Block terms of one unit: up to 8 rows x `nqc` quads of weights in shared memory against quads
+// [q_first, q_first + nqc) of the activation image. The exact int32 dot of a block comes from ONE int8
+// tensor-core instruction (mma.sync m16n8k32: A = the 32 weights of that block for the eight rows, one row
+// per lane group; B = the block's 32 activations, the same in every column), so that every lane (g, t) holds
+// the dots of row g for all four blocks of the quad and keeps block t's. No shuffles, a fifth of the
+// instructions of the dp4a form. Terms land at terms[row * pitch + 4 * (q_term + quad_in_piece) + t].
 template <int TYPE>
-__device__ __forceinline__ void unit_terms(const unsigned char* slab_q, const unsigned char* slab_s, uint32_t rows,
-                                           uint32_t nq, uint32_t row_q_bytes, uint32_t row_s_bytes, const XImage& x,
-                                           float* terms, uint32_t pitch, int lane) {
+__device__ __forceinline__ void unit_terms(const unsigned char* slab_q, uint32_t q_pitch, const unsigned char* slab_s,
+                                           uint32_t s_pitch, uint32_t rows, uint32_t nqc, uint32_t q_first, uint32_t q_begin,
+                                           uint32_t q_step, uint32_t q_term, const XImage& x, float* terms, uint32_t pitch,
+                                           int lane) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QUAD = Q8 ? 128 : 64;
     const int t = lane & 3;
-    const uint32_t total = rows * nq;
-    uint32_t r = ((uint32_t)lane >> 2) / nq, q = ((uint32_t)lane >> 2) - r * nq;
-    const uint32_t passes = (total + 7) / 8;
-#pragma unroll 2
-    for (uint32_t it = 0; it < passes; ++it) {
-        const bool valid = r < rows;
-        const uint32_t rr = valid ? r : 0u, qq = valid ? q : 0u;
-        const unsigned char* pw = slab_q + (size_t)rr * row_q_bytes + qq * QUAD + 16 * t;
-        const uint4 wa = *reinterpret_cast<const uint4*>(pw);
-        uint4 wa2 = wa;
-        if (Q8) wa2 = *reinterpret_cast<const uint4*>(pw + 64);
-        const uint32_t blk = qq * 4 + t;
+    const uint32_t g = (uint32_t)lane >> 2;
+    const uint32_t gr = g < rows ? g : 0u;  // lane groups beyond the unit's rows repeat row 0 (their terms are not read)
+    const unsigned char* wrow = slab_q + (size_t)gr * q_pitch + 16 * t;
+    const unsigned char* srow = slab_s + (size_t)gr * s_pitch;
+    float* trow = terms + g * pitch;
+#pragma unroll 4
+    for (uint32_t q = q_begin; q < nqc; q += q_step) {  // quads q_begin, q_begin + q_step, ... of the piece
+        const uint4 wa = *reinterpret_cast<const uint4*>(wrow + q * QUAD);
+        uint4 wb = wa;
+        if (Q8) wb = *reinterpret_cast<const uint4*>(wrow + q * QUAD + 64);
+        const uint4 xlo = x.xl[(q_first + q) * 4 + t], xhi = x.xh[(q_first + q) * 4 + t];
+        int acc[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t a0, a2;
+            if (Q8) {
+                a0 = pick(wa, j);
+                a2 = pick(wb, j);
+            } else {
+                const uint32_t u = pick(wa, j);
+                a0 = u & 0x0F0F0F0Fu;
+                a2 = (u >> 4) & 0x0F0F0F0Fu;
+            }
+            mma_s8(acc[j], a0, a2, pick(xlo, j), pick(xhi, j));
+        }
+        int idot = t == 0 ? acc[0][0] : t == 1 ? acc[1][0] : t == 2 ? acc[2][0] : acc[3][0];
+        const uint32_t bl = q * 4 + t, blk = (q_first + q) * 4 + t;
         float d, m = 0.0f;
         if (Q41) {
-            const __half2 h = *reinterpret_cast<const __half2*>(slab_s + (size_t)rr * row_s_bytes + blk * 4);
+            const __half2 h = *reinterpret_cast<const __half2*>(srow + bl * 4);
             d = __low2float(h);
             m = __high2float(h);
         } else {
-            d = __half2float(*reinterpret_cast<const __half*>(slab_s + (size_t)rr * row_s_bytes + blk * 2));
+            d = __half2float(*reinterpret_cast<const __half*>(srow + bl * 2));
         }
-        const uint4 xlo = x.xl[qq * 4 + t], xhi = x.xh[qq * 4 + t];
-        int p4[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int x0 = (int)pick(xlo, j), x1 = (int)pick(xhi, j);
-            if (Q8) {
-                p4[j] = __dp4a((int)pick(wa2, j), x1, __dp4a((int)pick(wa, j), x0, 0));
-            } else {
-                const uint32_t u = pick(wa, j);
-                p4[j] = __dp4a((int)((u >> 4) & 0x0F0F0F0Fu), x1, __dp4a((int)(u & 0x0F0F0F0Fu), x0, 0));
-            }
-        }
-        int idot = quad_transpose_reduce(p4, t);
         const float s = x.xsc[blk];
         const int qsum = x.xsum[blk];
         if (TYPE == ZQ_TYPE_Q4_0) idot -= 8 * qsum;
         float term = __fmul_rn(__fmul_rn(d, s), (float)idot);
         if (Q41) term = __fadd_rn(term, __fmul_rn(__fmul_rn(m, s), (float)qsum));
-        if (valid) terms[rr * pitch + blk] = term;
-        q += 8;
-        while (q >= nq) {
-            q -= nq;
-            ++r;
-        }
+        trow[(q_term + q) * 4 + t] = term;
     }
 }
 
@@ -396,115 +565,265 @@ __device__ __forceinline__ void best_update(Best& b, float v, uint32_t i) {
     }
 }
 
-// One matrix-vector phase: this CTA's units of `m`, taken by the consumer warps in turn from the ring.
-// The activation image is complete (cbar) before the call. Returns with *unit_base advanced.
-__device__ __forceinline__ void gemv_phase(const Cta& c, const DParams& p, const DMat& m, uint32_t* unit_base,
-                                           const XImage& x, float* terms_all, int ep, float* out, Best* best) {
+// Geometry of one unit (piece `ch` of tile `tile`) as both sides of the ring compute it.
+struct UnitGeom {
+    uint32_t rows;      // rows in the slab (both halves of a split tile together)
+    uint32_t row0;      // first row (of the first half when split)
+    uint32_t q_first;   // first quad of the piece
+    uint32_t nqc;       // quads in the piece
+    uint32_t q_pitch;   // bytes between rows of quants in the slab
+    uint32_t s_pitch;   // bytes between rows of scales in the slab
+    uint32_t s_off;     // byte offset of the slab's scale rows
+    uint32_t s_delta;   // bytes to skip at the start of a scale row (its source was aligned down to 16)
+};
+__device__ __forceinline__ UnitGeom unit_geom(const DMat& m, uint32_t tile, uint32_t ch) {
+    UnitGeom u;
+    const uint32_t R = m.rows_per_tile, nq = m.nbp >> 2;
+    const uint32_t QUAD = m.type == ZQ_TYPE_Q8_0 ? 128u : 64u, SB = m.type == ZQ_TYPE_Q4_1 ? 4u : 2u;
+    if (m.split) {
+        const uint32_t half = R >> 1, n_half = m.n_rows >> 1;
+        u.row0 = tile * half;
+        u.rows = 2 * min(half, n_half - u.row0);
+    } else {
+        u.row0 = tile * R;
+        u.rows = min(R, m.n_rows - u.row0);
+    }
+    u.q_first = ch * m.chunk_quads;
+    u.nqc = min(m.chunk_quads, nq - u.q_first);
+    if (m.chunks == 1) {
+        u.q_pitch = m.row_q_bytes;
+        u.s_pitch = m.row_s_bytes;
+        u.s_off = u.rows * m.row_q_bytes;
+        u.s_delta = 0;
+    } else {
+        u.q_pitch = m.chunk_quads * QUAD;
+        const uint32_t so = u.q_first * 4 * SB;
+        u.s_delta = so & 15u;
+        u.s_pitch = ((m.chunk_quads * 4 * SB + 15u) & ~15u) + 16u;
+        u.s_off = R * u.q_pitch;
+    }
+    return u;
+}
+
+__device__ __forceinline__ bool unit_acquire(const Cta& c, const DParams& p, uint32_t slot, uint32_t use) {
+    // The slot's previous use must have been consumed before its barrier is read: a parity wait alone cannot
+    // tell fill `use` from fill `use - 2`.
+    bool ready = true;
+    if (use > 0) {
+        uint32_t spins = 0;
+        while (c.released[slot] < use && ++spins < kSlotSpinLimit) __nanosleep(64);
+        ready = c.released[slot] >= use;
+        if (!ready) raise_abort(c, p, kErrUnitWait);
+    }
+    ready = ready && slot_wait(c, p, c.full0 + slot * 8, use & 1u);
+    return __all_sync(0xFFFFFFFFu, ready);  // the whole warp decides together
+}
+// `count` of the 16 arrivals that free a slot: a warp that consumed a unit alone signs for all of them.
+__device__ __forceinline__ void unit_release(const Cta& c, uint32_t slot, uint32_t use, uint32_t count) {
+    __syncwarp();
+    if (c.lane == 0) {
+        c.released[slot] = use + 1;
+        __threadfence_block();
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(c.empty0 + slot * 8), "r"(count) : "memory");
+    }
+}
+template <typename... A>
+__device__ __forceinline__ void unit_terms_any(uint32_t type, A... a) {
+    if (type == ZQ_TYPE_Q8_0) unit_terms<ZQ_TYPE_Q8_0>(a...);
+    else if (type == ZQ_TYPE_Q4_0) unit_terms<ZQ_TYPE_Q4_0>(a...);
+    else unit_terms<ZQ_TYPE_Q4_1>(a...);
+}
+// Sum of `n` terms in order, added onto `run`; the next four terms are loaded while these four are added.
+__device__ __forceinline__ float ordered_sum(float run, const float* tr, uint32_t n) {
+    uint32_t b = 0;
+    if (n >= 4) {
+        float4 a = *reinterpret_cast<const float4*>(tr);
+#pragma unroll 1
+        for (b = 4; b + 4 <= n; b += 4) {
+            const float4 n4 = *reinterpret_cast<const float4*>(tr + b);
+            run = __fadd_rn(run, a.x);
+            run = __fadd_rn(run, a.y);
+            run = __fadd_rn(run, a.z);
+            run = __fadd_rn(run, a.w);
+            a = n4;
+        }
+        run = __fadd_rn(run, a.x);
+        run = __fadd_rn(run, a.y);
+        run = __fadd_rn(run, a.z);
+        run = __fadd_rn(run, a.w);
+    }
+#pragma unroll 1
+    for (; b < n; ++b) run = __fadd_rn(run, tr[b]);
+    return run;
+}
+
+// One matrix-vector phase: this CTA's tiles of `m` (tile = cta, cta + grid, ...). The activation image is
+// complete (cbar) before the call. Outputs leave as exchange words (EP_VECTOR, EP_GEGLU) or as plain f32 logits
+// (EP_LOGITS). Block terms are added onto a row's sum in block order, as the CPU loop does. Two forms:
+//   * few tiles per CTA (the layer matrices): all 16 warps share every unit — the quads of the CTA's units are
+//     dealt round the warps, so a warp runs one or a few tensor-core steps instead of a whole row's worth —
+//     the terms meet in a CTA-wide buffer, and after a barrier one thread per row adds them up;
+//   * many tiles (the vocabulary head): one warp per tile, pieces and sums warp-private, no barrier.
+// Returns the advanced unit counter.
+__device__ __noinline__ uint32_t gemv_phase(const DMat& m, uint32_t unit_base, int ep, unsigned long long* xout,
+                                            uint32_t epoch, float* out, Best* best) {
+    const Cta c = make_cta();
+    const DParams& p = sh().p;
+    const XImage x = ximage(c.smem + p.off_scratch, p.nbp_max);
+    float* terms_all = reinterpret_cast<float*>(x.xsum + p.nbp_max);
     const uint32_t G = gridDim.x, cta = blockIdx.x;
-    const uint32_t n_units = m.n_units;
-    const uint32_t mine = n_units > cta ? (n_units - cta - 1) / G + 1 : 0;
-    const uint32_t base = *unit_base;
-    *unit_base = base + mine;
-    if (c.warp >= kConsumerWarps) return;
-    const uint32_t type = m.type, nb = m.nb, nq = m.nbp >> 2, pitch = m.nbp + 1;
-    const uint32_t rqb = m.row_q_bytes, rsb = m.row_s_bytes, R = m.rows_per_unit, N = m.n_rows;
+    const uint32_t n_tiles = m.n_tiles, C = m.chunks;
+    const uint32_t mine = n_tiles > cta ? (n_tiles - cta - 1) / G + 1 : 0;
+    const uint32_t base = unit_base;
+    const uint32_t type = m.type;
+    const uint32_t row_pitch = m.nbp + 4;  // terms of a whole row
+    // Sharing a unit costs every warp its wait / release bookkeeping: worth it only for a handful of units.
+    if (mine * C <= 8 && mine * 8 * row_pitch * 4 <= p.terms_bytes) {
+        // ---- all warps on every unit
+        uint32_t dealt = 0;  // quads dealt so far: quad j of the phase goes to warp j % 16
+        bool live = true;
+#pragma unroll 1
+        for (uint32_t n = 0; live && n < mine * C; ++n) {
+            const uint32_t i = n / C, ch = n - i * C;
+            const uint32_t gi = base + n, slot = gi % p.n_slots, use = gi / p.n_slots;
+            const UnitGeom u = unit_geom(m, cta + i * G, ch);
+            const uint32_t first = ((uint32_t)c.warp + kConsumerWarps - (dealt % kConsumerWarps)) % kConsumerWarps;
+            // Every warp waits for the unit, also one without a quad in it: its arrival below must not reach the
+            // slot's barrier before the arrivals of the slot's previous use are complete.
+            if (!unit_acquire(c, p, slot, use)) {
+                live = false;
+                break;
+            }
+            if (first < u.nqc) {
+                const unsigned char* slab_q = c.smem + p.off_ring + (size_t)slot * p.slot_bytes;
+                unit_terms_any(type, slab_q, u.q_pitch, slab_q + u.s_off + u.s_delta, u.s_pitch, u.rows, u.nqc, u.q_first,
+                               first, (uint32_t)kConsumerWarps, u.q_first, x, terms_all + (size_t)i * 8 * row_pitch, row_pitch,
+                               c.lane);
+            }
+            unit_release(c, slot, use, 1);
+            dealt += u.nqc;
+        }
+        cbar();  // every term of the phase is in the buffer
+        const uint32_t nb = m.nb;
+#pragma unroll 1
+        for (uint32_t r = c.tid; r < mine * 8; r += kConsumers) {
+            const uint32_t i = r >> 3, g = r & 7u;
+            const UnitGeom u = unit_geom(m, cta + i * G, 0);
+            const float* tr = terms_all + (size_t)r * row_pitch;
+            if (ep == EP_GEGLU) {
+                const uint32_t half = u.rows >> 1;
+                if (g < half) {
+                    const float gate = ordered_sum(0.0f, tr, nb);
+                    const float up = ordered_sum(0.0f, tr + (size_t)half * row_pitch, nb);
+                    xstore(xout + u.row0 + g, __fmul_rn(gelu_tanh(gate), up), epoch);
+                }
+            } else if (g < u.rows) {
+                const float v = ordered_sum(0.0f, tr, nb);
+                if (ep == EP_LOGITS) {
+                    out[u.row0 + g] = v;
+                    if (best) best_update(*best, v, u.row0 + g);
+                } else {
+                    xstore(xout + u.row0 + g, v, epoch);
+                }
+            }
+        }
+        return base + mine * C;
+    }
+    // ---- one warp per tile
+    const uint32_t pitch = m.chunk_quads * 4 + 4;
     float* terms = terms_all + (size_t)c.warp * p.terms_per_warp;
-    for (uint32_t i = c.warp; i < mine; i += kConsumerWarps) {
-        const uint32_t gi = base + i, slot = gi % p.n_slots, use = gi / p.n_slots;
-        const uint32_t u = cta + i * G;
-        uint32_t rows, row0;
-        if (m.split) {
-            const uint32_t half = R >> 1, n_half = N >> 1;
-            row0 = u * half;
-            rows = 2 * min(half, n_half - row0);
-        } else {
-            row0 = u * R;
-            rows = min(R, N - row0);
-        }
-        // The slot's previous use must have been consumed before its barrier is read: a parity wait alone
-        // cannot tell fill `use` from fill `use - 2`.
-        bool ready = true;
-        if (use > 0) {
-            uint32_t spins = 0;
-            while (c.released[slot] < use && ++spins < kSlotSpinLimit) {
-            }
-            ready = c.released[slot] >= use;
-            if (!ready) {
-                *c.s_abort = 1;
-                atomicExch(p.err, kErrUnitWait);
-            }
-        }
-        ready = ready && slot_wait(c, c.full0 + slot * 8, use & 1u, p.err);
-        if (!__all_sync(0xFFFFFFFFu, ready)) break;  // the whole warp leaves together
-        const unsigned char* slab_q = c.smem + p.off_ring + (size_t)slot * p.slot_bytes;
-        const unsigned char* slab_s = slab_q + (size_t)rows * rqb;
-        if (type == ZQ_TYPE_Q8_0)
-            unit_terms<ZQ_TYPE_Q8_0>(slab_q, slab_s, rows, nq, rqb, rsb, x, terms, pitch, c.lane);
-        else if (type == ZQ_TYPE_Q4_0)
-            unit_terms<ZQ_TYPE_Q4_0>(slab_q, slab_s, rows, nq, rqb, rsb, x, terms, pitch, c.lane);
-        else
-            unit_terms<ZQ_TYPE_Q4_1>(slab_q, slab_s, rows, nq, rqb, rsb, x, terms, pitch, c.lane);
-        __syncwarp();
-        if (c.lane == 0) {  // the slot's bytes have been read
-            c.released[slot] = use + 1;
-            __threadfence_block();
-            mbar_arrive(c.empty0 + slot * 8);
-        }
-        // one lane per row adds the row's terms in block order, as the CPU loop does
+    bool live = true;
+#pragma unroll 1
+    for (uint32_t i = c.warp; live && i < mine; i += kConsumerWarps) {
+        const uint32_t tile = cta + i * G;
         float run = 0.0f;
-        if ((uint32_t)c.lane < rows) {
-            const float* tr = terms + c.lane * pitch;
-            uint32_t b = 0;
-            for (; b + 4 <= nb; b += 4) {
-                const float t0 = tr[b], t1 = tr[b + 1], t2 = tr[b + 2], t3 = tr[b + 3];
-                run = __fadd_rn(run, t0);
-                run = __fadd_rn(run, t1);
-                run = __fadd_rn(run, t2);
-                run = __fadd_rn(run, t3);
+        uint32_t rows = 0, row0 = 0;
+#pragma unroll 1
+        for (uint32_t ch = 0; ch < C; ++ch) {
+            const uint32_t gi = base + i * C + ch, slot = gi % p.n_slots, use = gi / p.n_slots;
+            const UnitGeom u = unit_geom(m, tile, ch);
+            rows = u.rows;
+            row0 = u.row0;
+            if (!unit_acquire(c, p, slot, use)) {
+                live = false;
+                break;
             }
-            for (; b < nb; ++b) run = __fadd_rn(run, tr[b]);
+            const unsigned char* slab_q = c.smem + p.off_ring + (size_t)slot * p.slot_bytes;
+            unit_terms_any(type, slab_q, u.q_pitch, slab_q + u.s_off + u.s_delta, u.s_pitch, rows, u.nqc, u.q_first, 0u, 1u,
+                           0u, x, terms, pitch, c.lane);
+            unit_release(c, slot, use, (uint32_t)kConsumerWarps);
+            if ((uint32_t)c.lane < rows)
+                run = ordered_sum(run, terms + c.lane * pitch, min(u.nqc * 4, m.nb - u.q_first * 4));
+            __syncwarp();  // the terms are rewritten by the next piece
         }
+        if (!live) break;
         if (ep == EP_GEGLU) {
             const uint32_t half = rows >> 1;
             const float up = __shfl_down_sync(0xFFFFFFFFu, run, half);
-            if ((uint32_t)c.lane < half) out[row0 + c.lane] = __fmul_rn(gelu_tanh(run), up);
+            if ((uint32_t)c.lane < half) xstore(xout + row0 + c.lane, __fmul_rn(gelu_tanh(run), up), epoch);
         } else if ((uint32_t)c.lane < rows) {
-            out[row0 + c.lane] = run;
-            if (ep == EP_LOGITS && best) best_update(*best, run, row0 + c.lane);
+            if (ep == EP_LOGITS) {
+                out[row0 + c.lane] = run;
+                if (best) best_update(*best, run, row0 + c.lane);
+            } else {
+                xstore(xout + row0 + c.lane, run, epoch);
+            }
         }
-        __syncwarp();  // the terms are rewritten by the warp's next unit
     }
+    return base + mine * C;
 }
 
 // The producer's side of gemv_phase: issue this CTA's units of `m` into the ring, in the same order.
-__device__ __forceinline__ bool produce_phase(const Cta& c, const DParams& p, const DMat& m, uint32_t* unit_base,
-                                              uint32_t* issued) {
+__device__ __noinline__ bool produce_phase(const DMat& m, uint32_t* unit_base,
+                                           uint32_t* issued) {
+    const Cta c = make_cta();
+    const DParams& p = sh().p;
+    (void)p;
     const uint32_t G = gridDim.x, cta = blockIdx.x;
-    const uint32_t mine = m.n_units > cta ? (m.n_units - cta - 1) / G + 1 : 0;
+    const uint32_t C = m.chunks;
+    const uint32_t mine = m.n_tiles > cta ? (m.n_tiles - cta - 1) / G + 1 : 0;
     const uint32_t base = *unit_base;
-    *unit_base = base + mine;
-    const uint32_t rqb = m.row_q_bytes, rsb = m.row_s_bytes, R = m.rows_per_unit, N = m.n_rows;
-    for (uint32_t i = 0; i < mine; ++i) {
-        const uint32_t gi = base + i, slot = gi % p.n_slots, use = gi / p.n_slots;
-        const uint32_t u = cta + i * G;
-        if (use > 0 && !slot_wait(c, c.empty0 + slot * 8, (use - 1) & 1u, p.err)) return false;
+    *unit_base = base + mine * C;
+    const uint32_t rqb = m.row_q_bytes, rsb = m.row_s_bytes, N = m.n_rows;
+    const uint32_t QUAD = m.type == ZQ_TYPE_Q8_0 ? 128u : 64u, SB = m.type == ZQ_TYPE_Q4_1 ? 4u : 2u;
+    const uint8_t* qs = m.qs;
+    const uint8_t* sc = m.sc;
+#pragma unroll 1
+    for (uint32_t n = 0; n < mine * C; ++n) {
+        const uint32_t i = n / C, ch = n - i * C;
+        const uint32_t gi = base + n, slot = gi % p.n_slots, use = gi / p.n_slots;
+        const uint32_t tile = cta + i * G;
+        if (use > 0 && !slot_wait(c, p, c.empty0 + slot * 8, (use - 1) & 1u)) return false;
         const uint32_t dst = c.smem32 + p.off_ring + slot * p.slot_bytes;
         const uint32_t bar = c.full0 + slot * 8;
-        if (m.split) {
-            const uint32_t half = R >> 1, n_half = N >> 1;
-            const uint32_t row0 = u * half, h = min(half, n_half - row0);
-            const uint32_t qb = h * rqb, sb = h * rsb;
-            mbar_arrive_expect_tx(bar, 2 * (qb + sb));
-            bulk_copy_g2s(dst, m.qs + (size_t)row0 * rqb, qb, bar);
-            bulk_copy_g2s(dst + qb, m.qs + (size_t)(n_half + row0) * rqb, qb, bar);
-            bulk_copy_g2s(dst + 2 * qb, m.sc + (size_t)row0 * rsb, sb, bar);
-            bulk_copy_g2s(dst + 2 * qb + sb, m.sc + (size_t)(n_half + row0) * rsb, sb, bar);
+        const UnitGeom u = unit_geom(m, tile, ch);
+        if (C == 1) {
+            if (m.split) {
+                const uint32_t h = u.rows >> 1, n_half = N >> 1;
+                const uint32_t qb = h * rqb, sb = h * rsb;
+                mbar_arrive_expect_tx(bar, 2 * (qb + sb));
+                bulk_copy_g2s(dst, qs + (size_t)u.row0 * rqb, qb, bar);
+                bulk_copy_g2s(dst + qb, qs + (size_t)(n_half + u.row0) * rqb, qb, bar);
+                bulk_copy_g2s(dst + 2 * qb, sc + (size_t)u.row0 * rsb, sb, bar);
+                bulk_copy_g2s(dst + 2 * qb + sb, sc + (size_t)(n_half + u.row0) * rsb, sb, bar);
+            } else {
+                const uint32_t qb = u.rows * rqb, sb = u.rows * rsb;
+                mbar_arrive_expect_tx(bar, qb + sb);
+                bulk_copy_g2s(dst, qs + (size_t)u.row0 * rqb, qb, bar);
+                bulk_copy_g2s(dst + qb, sc + (size_t)u.row0 * rsb, sb, bar);
+            }
         } else {
-            const uint32_t row0 = u * R, rows = min(R, N - row0);
-            const uint32_t qb = rows * rqb, sb = rows * rsb;
-            mbar_arrive_expect_tx(bar, qb + sb);
-            bulk_copy_g2s(dst, m.qs + (size_t)row0 * rqb, qb, bar);
-            bulk_copy_g2s(dst + qb, m.sc + (size_t)row0 * rsb, sb, bar);
+            // a piece of a long row: one copy of quants and one of scales (from a 16-byte boundary) per row
+            const uint32_t qbytes = u.nqc * QUAD;
+            const uint32_t so = u.q_first * 4 * SB, sa = so & ~15u;
+            const uint32_t sbytes = ((u.s_delta + u.nqc * 4 * SB + 15u) & ~15u);
+            mbar_arrive_expect_tx(bar, u.rows * (qbytes + sbytes));
+            for (uint32_t r = 0; r < u.rows; ++r) {
+                const uint32_t half = u.rows >> 1;
+                const size_t row = m.split ? (r < half ? u.row0 + r : (N >> 1) + u.row0 + (r - half)) : u.row0 + r;
+                bulk_copy_g2s(dst + r * u.q_pitch, qs + row * rqb + (size_t)u.q_first * QUAD, qbytes, bar);
+                bulk_copy_g2s(dst + u.s_off + r * u.s_pitch, sc + row * rsb + sa, sbytes, bar);
+            }
         }
         *issued = gi + 1;
     }
@@ -512,10 +831,14 @@ __device__ __forceinline__ bool produce_phase(const Cta& c, const DParams& p, co
 }
 
 // Embedding row of `tok`, dequantised and scaled (gemma3.zig:800-803, 855-871): q*d, then *scale.
-__device__ __forceinline__ void embed_row(const Cta& c, const DMat& m, uint32_t tok, float scale, float* xres,
+__device__ __noinline__ void embed_row(const DMat& m, uint32_t tok, float scale, float* xres,
                                           uint32_t dim) {
+    const Cta c = make_cta();
+    const DParams& p = sh().p;
+    (void)p;
     const unsigned char* qrow = m.qs + (size_t)tok * m.row_q_bytes;
     const unsigned char* srow = m.sc + (size_t)tok * m.row_s_bytes;
+#pragma unroll 1
     for (uint32_t k = c.tid; k < dim; k += kConsumers) {
         const uint32_t blk = k >> 5, j = k & 31u;
         float v;
@@ -538,41 +861,79 @@ __device__ __forceinline__ void embed_row(const Cta& c, const DMat& m, uint32_t 
     }
 }
 
-// Attention, first half (gemma3.zig:689-716, 1062-1090): every CTA normalises and rotates the query heads
-// and this step's key heads in its own shared memory; CTA 0 stores the key / value rows of position `pos`;
-// the scores of the window are spread over the CTAs in tiles of 32 (position, head) pairs.
-__device__ __forceinline__ void scores_phase(const Cta& c, const DParams& p, const DLayer& L, uint32_t pos,
-                                             uint32_t kv_start, uint32_t kv_len, const float* rope, float* qn) {
+// Attention, first half (gemma3.zig:689-716, 1062-1090): every CTA takes the exchanged q|k|v row, normalises
+// and rotates the query heads and this step's key heads in its own shared memory and keeps this step's value
+// heads (`vnew`); the last CTA stores the key / value rows of position `pos`; the scores of the window are
+// spread over the CTAs in tiles of 32 (position, head) pairs and leave as exchange words.
+// Returns false (to every thread) when the CTA has to leave.
+__device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
+                                             uint32_t kv_start, uint32_t kv_len, const float* rope, float* qn,
+                                             float* vnew, const unsigned long long* qkv_in, uint32_t ep_in,
+                                             unsigned long long* scores_out, uint32_t ep_out) {
+    const Cta c = make_cta();
+    const DParams& p = sh().p;
+    (void)p;
     const uint32_t D = p.D, nh = p.n_head, nkv = p.n_kv, group = nh / nkv, kv_dim = nkv * D;
-    const uint32_t nvec = nh + nkv;
-    for (uint32_t i = c.tid; i < nvec * D; i += kConsumers) qn[i] = __ldcg(p.qkv + i);
+    const uint32_t nvec = nh + nkv, nqk = nvec * D, nall = nqk + kv_dim;
+    // norm weights of the pairs this thread rotates: requested before the exchange is polled
+    const uint32_t half = D / 2, pairs = nvec * half;
+    float2 nw[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const uint32_t i = c.tid + u * kConsumers;
+        if (i < pairs) {
+            const uint32_t v = i / half, j = i - v * half;
+            nw[u] = __ldg(reinterpret_cast<const float2*>(v < nh ? L.q_norm_w : L.k_norm_w) + j);
+        } else {
+            nw[u] = make_float2(0.0f, 0.0f);
+        }
+    }
+#pragma unroll 1
+    for (uint32_t base = 0; base < nall; base += kConsumers * 4) {
+        float v[4];
+        xload_batch<4>(c, p, qkv_in, base + c.tid, kConsumers, nall, ep_in, v);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t i = base + u * kConsumers + c.tid;
+            if (i < nqk) qn[i] = v[u];
+            else if (i < nall) vnew[i - nqk] = v[u];
+        }
+    }
     cbar();
+    const bool leave = *c.s_abort != 0;  // uniform: read between two barriers that every thread passes
+#pragma unroll 1
     for (uint32_t v = c.warp; v < nvec; v += kConsumerWarps)  // one chain per vector, one warp each
         if (c.lane == 0)
             c.red[v & 31u] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq_sequential(qn + v * D, D), (float)D), p.eps)));
     cbar();
-    for (uint32_t i = c.tid; i < nvec * (D / 2); i += kConsumers) {
-        const uint32_t v = i / (D / 2), j = i - v * (D / 2);
-        const float* wn = v < nh ? L.q_norm_w : L.k_norm_w;
+    if (leave) return false;
+#pragma unroll 1
+    for (uint32_t i = c.tid, u = 0; i < pairs; i += kConsumers, ++u) {
+        const uint32_t v = i / half, j = i - v * half;
+        float2 w;
+        if (u < 2) w = u == 0 ? nw[0] : nw[1];
+        else w = __ldg(reinterpret_cast<const float2*>(v < nh ? L.q_norm_w : L.k_norm_w) + j);
         float* vec = qn + v * D;
         const float inv = c.red[v & 31u];
-        const float x0 = __fmul_rn(__fmul_rn(vec[2 * j], inv), __ldg(wn + 2 * j));
-        const float x1 = __fmul_rn(__fmul_rn(vec[2 * j + 1], inv), __ldg(wn + 2 * j + 1));
+        const float x0 = __fmul_rn(__fmul_rn(vec[2 * j], inv), w.x);
+        const float x1 = __fmul_rn(__fmul_rn(vec[2 * j + 1], inv), w.y);
         const float cs = rope[2 * j], sn = rope[2 * j + 1];
         vec[2 * j] = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
         vec[2 * j + 1] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
     }
     cbar();
-    if (blockIdx.x == 0) {
+    if (blockIdx.x == gridDim.x - 1) {  // cache rows of this position, for the steps to come
+#pragma unroll 1
         for (uint32_t i = c.tid; i < kv_dim; i += kConsumers) {
             L.kc[(size_t)pos * kv_dim + i] = qn[nh * D + i];
-            L.vc[(size_t)pos * kv_dim + i] = __ldcg(p.qkv + (nh + nkv) * D + i);
+            L.vc[(size_t)pos * kv_dim + i] = vnew[i];
         }
     }
     const uint32_t jobs = kv_len * nh, tiles = (jobs + 31) / 32;
     const uint32_t l = c.tid & 15u, js = c.tid >> 4;
     const uint32_t dim16 = D & ~15u;
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)D));
+#pragma unroll 1
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const uint32_t job = tile * 32 + js;
         const bool live = job < jobs;
@@ -582,15 +943,16 @@ __device__ __forceinline__ void scores_phase(const Cta& c, const DParams& p, con
         const bool from_smem = pi == kv_len - 1;
         const float* kr = from_smem ? qn + (nh + kvh) * D : L.kc + (size_t)(kv_start + pi) * kv_dim + (size_t)kvh * D;
         float acc = 0.0f;
-        for (uint32_t d0 = l; d0 < dim16; d0 += 16 * 8) {
-            float kv[8];
+#pragma unroll 1
+        for (uint32_t d0 = l; d0 < dim16; d0 += 16 * 16) {
+            float kv[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 const uint32_t d = d0 + 16 * u;
                 kv[u] = d < dim16 ? (from_smem ? kr[d] : __ldcg(kr + d)) : 0.0f;
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 const uint32_t d = d0 + 16 * u;
                 if (d < dim16) acc = __fadd_rn(acc, __fmul_rn(qh[d], kv[u]));
             }
@@ -600,72 +962,113 @@ __device__ __forceinline__ void scores_phase(const Cta& c, const DParams& p, con
 #pragma unroll
         for (int j = 1; j < 16; ++j) s = __fadd_rn(s, __shfl_sync(0xFFFFFFFFu, acc, j, 16));
         if (l == 0 && live) {
+#pragma unroll 1
             for (uint32_t d = dim16; d < D; ++d) s = __fadd_rn(s, __fmul_rn(qh[d], from_smem ? kr[d] : __ldcg(kr + d)));
-            p.scores[(size_t)h * p.max_len + pi] = __fmul_rn(s, scale);
+            xstore(scores_out + (size_t)h * p.max_len + pi, __fmul_rn(s, scale), ep_out);
         }
     }
+    return true;
 }
 
 // Attention, second half (gemma3.zig:1092-1120): a job owns 8 output dimensions of one kv head for all the
 // query heads that share it. Softmax per head (maximum, exp, the exponentials added one by one, times
-// 1/sum), then out[d] += w[p] * v[p][d] position by position; V streams through shared memory in tiles.
-__device__ __forceinline__ void softmax_v_phase(const Cta& c, const DParams& p, const DLayer& L, uint32_t kv_start,
-                                                uint32_t kv_len, unsigned char* scratch) {
+// 1/sum), then out[d] += w[p] * v[p][d] position by position; V streams through shared memory in tiles, the
+// row of the current position comes from `vnew`. Returns false when the CTA has to leave.
+__device__ __noinline__ bool softmax_v_phase(const DLayer& L, uint32_t kv_start,
+                                                uint32_t kv_len, unsigned char* scratch, const float* vnew,
+                                                const unsigned long long* scores_in, uint32_t ep_in,
+                                                unsigned long long* att_out, uint32_t ep_out) {
+    const Cta c = make_cta();
+    const DParams& p = sh().p;
+    (void)p;
     const uint32_t D = p.D, nh = p.n_head, nkv = p.n_kv, group = nh / nkv, kv_dim = nkv * D;
     const uint32_t chunks = D / 8, jobs = nkv * chunks;
     float* w = reinterpret_cast<float*>(scratch);                      // [group][max_len]
     float* vt = w + (size_t)group * p.max_len;                         // [2][kVTile][8]
     const uint32_t vt32 = c.smem32 + (uint32_t)(reinterpret_cast<unsigned char*>(vt) - c.smem);
     const uint32_t wph = kConsumerWarps / group;                       // warps per head
-    for (uint32_t job = blockIdx.x; job < jobs; job += gridDim.x) {
+    bool ok = true;
+#pragma unroll 1
+    for (uint32_t job = blockIdx.x; ok && job < jobs; job += gridDim.x) {
         const uint32_t kvh = job / chunks, dc = job - kvh * chunks;
         const float* vbase = L.vc + (size_t)kv_start * kv_dim + (size_t)kvh * D + dc * 8;
         auto fetch_tile = [&](uint32_t tile) {
             const uint32_t p0 = tile * kVTile, n = min(kVTile, kv_len - p0);
             const uint32_t dst = vt32 + (tile & 1u) * kVTile * 32;
-            for (uint32_t i = c.tid; i < n * 2; i += kConsumers)
-                cp_async16(dst + i * 16, vbase + (size_t)(p0 + (i >> 1)) * kv_dim + (i & 1u) * 4);
+#pragma unroll 1
+            for (uint32_t i = c.tid; i < n * 2; i += kConsumers) {
+                const uint32_t q = p0 + (i >> 1);
+                if (q + 1 < kv_len) {
+                    cp_async16(dst + i * 16, vbase + (size_t)q * kv_dim + (i & 1u) * 4);
+                } else {  // the current position's row: this step's value heads
+                    const float* vs = vnew + kvh * D + dc * 8 + (i & 1u) * 4;
+                    float* vd = vt + (size_t)(tile & 1u) * kVTile * 8 + (size_t)i * 4;
+                    vd[0] = vs[0]; vd[1] = vs[1]; vd[2] = vs[2]; vd[3] = vs[3];
+                }
+            }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
         fetch_tile(0);  // in flight during the softmax
         {
             const uint32_t hg = c.warp / wph, tl = c.tid - hg * wph * 32, nt = wph * 32;
-            const float* sh = p.scores + (size_t)(kvh * group + hg) * p.max_len;
+            const unsigned long long* sh = scores_in + (size_t)(kvh * group + hg) * p.max_len;
             float* wh = w + (size_t)hg * p.max_len;
             float mx = -INFINITY;
-            for (uint32_t q = tl; q < kv_len; q += nt) {
-                const float v = __ldcg(sh + q);
-                wh[q] = v;
-                mx = fmaxf(mx, v);
+#pragma unroll 1
+            for (uint32_t base = 0; base < kv_len; base += nt * 8) {
+                float v[8];
+                xload_batch<8>(c, p, sh, base + tl, nt, kv_len, ep_in, v);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const uint32_t i = base + u * nt + tl;
+                    if (i < kv_len) {
+                        wh[i] = v[u];
+                        mx = fmaxf(mx, v[u]);
+                    }
+                }
             }
             mx = warp_max(mx);
             if (c.lane == 0) c.red[c.warp] = mx;
             cbar();
+            if (*c.s_abort) ok = false;  // uniform: read between two barriers that every thread passes
             mx = c.red[hg * wph];
+#pragma unroll 1
             for (uint32_t k = 1; k < wph; ++k) mx = fmaxf(mx, c.red[hg * wph + k]);
+#pragma unroll 1
             for (uint32_t q = tl; q < kv_len; q += nt) wh[q] = exp_f32(__fsub_rn(wh[q], mx));
             cbar();
-            if ((uint32_t)c.tid < group) {  // one serial sum per head
+            if ((uint32_t)c.tid < group) {  // one serial sum per head; the next eight are loaded under the adds
                 const float* wq = w + (size_t)c.tid * p.max_len;
                 float s = 0.0f;
                 uint32_t q = 0;
-                for (; q + 8 <= kv_len; q += 8) {
-                    const float4 a = *reinterpret_cast<const float4*>(wq + q);
-                    const float4 b = *reinterpret_cast<const float4*>(wq + q + 4);
+                if (kv_len >= 8) {
+                    float4 a = *reinterpret_cast<const float4*>(wq), b = *reinterpret_cast<const float4*>(wq + 4);
+#pragma unroll 1
+                    for (q = 8; q + 8 <= kv_len; q += 8) {
+                        const float4 na = *reinterpret_cast<const float4*>(wq + q);
+                        const float4 nb = *reinterpret_cast<const float4*>(wq + q + 4);
+                        s = __fadd_rn(s, a.x); s = __fadd_rn(s, a.y); s = __fadd_rn(s, a.z); s = __fadd_rn(s, a.w);
+                        s = __fadd_rn(s, b.x); s = __fadd_rn(s, b.y); s = __fadd_rn(s, b.z); s = __fadd_rn(s, b.w);
+                        a = na;
+                        b = nb;
+                    }
                     s = __fadd_rn(s, a.x); s = __fadd_rn(s, a.y); s = __fadd_rn(s, a.z); s = __fadd_rn(s, a.w);
                     s = __fadd_rn(s, b.x); s = __fadd_rn(s, b.y); s = __fadd_rn(s, b.z); s = __fadd_rn(s, b.w);
                 }
+#pragma unroll 1
                 for (; q < kv_len; ++q) s = __fadd_rn(s, wq[q]);
                 c.part[c.tid] = __fdiv_rn(1.0f, s);
             }
             cbar();
             const float inv = c.part[hg];
+#pragma unroll 1
             for (uint32_t q = tl; q < kv_len; q += nt) wh[q] = __fmul_rn(wh[q], inv);
         }
         const uint32_t n_tiles = (kv_len + kVTile - 1) / kVTile;
         const bool chain = (uint32_t)c.tid < group * 8;  // thread (hg, d): one accumulation chain
         const uint32_t hg = (uint32_t)c.tid >> 3, d = (uint32_t)c.tid & 7u;
         float acc = 0.0f;
+#pragma unroll 1
         for (uint32_t tile = 0; tile < n_tiles; ++tile) {
             if (tile + 1 < n_tiles) {
                 fetch_tile(tile + 1);
@@ -676,69 +1079,76 @@ __device__ __forceinline__ void softmax_v_phase(const Cta& c, const DParams& p, 
             cbar();  // the tile (and, first pass, the weights) are complete for every thread
             if (chain) {
                 const uint32_t p0 = tile * kVTile, n = min(kVTile, kv_len - p0);
-                const float* vtile = vt + (size_t)(tile & 1u) * kVTile * 8;
+                const float* vtile = vt + (size_t)(tile & 1u) * kVTile * 8 + d;
                 const float* wq = w + (size_t)hg * p.max_len + p0;
                 uint32_t i = 0;
-                for (; i + 8 <= n; i += 8) {
-                    float vv[8], ww[8];
+                if (n >= 8) {  // products of the next eight positions are formed under the adds of these eight
+                    float pr[8];
+                    {
+                        const float4 wa = *reinterpret_cast<const float4*>(wq), wb = *reinterpret_cast<const float4*>(wq + 4);
+                        pr[0] = __fmul_rn(wa.x, vtile[0]);  pr[1] = __fmul_rn(wa.y, vtile[8]);
+                        pr[2] = __fmul_rn(wa.z, vtile[16]); pr[3] = __fmul_rn(wa.w, vtile[24]);
+                        pr[4] = __fmul_rn(wb.x, vtile[32]); pr[5] = __fmul_rn(wb.y, vtile[40]);
+                        pr[6] = __fmul_rn(wb.z, vtile[48]); pr[7] = __fmul_rn(wb.w, vtile[56]);
+                    }
+#pragma unroll 1
+                    for (i = 8; i + 8 <= n; i += 8) {
+                        const float4 wa = *reinterpret_cast<const float4*>(wq + i);
+                        const float4 wb = *reinterpret_cast<const float4*>(wq + i + 4);
+                        const float* vp = vtile + (size_t)i * 8;
+                        float nx[8];
+                        nx[0] = __fmul_rn(wa.x, vp[0]);  nx[1] = __fmul_rn(wa.y, vp[8]);
+                        nx[2] = __fmul_rn(wa.z, vp[16]); nx[3] = __fmul_rn(wa.w, vp[24]);
+                        nx[4] = __fmul_rn(wb.x, vp[32]); nx[5] = __fmul_rn(wb.y, vp[40]);
+                        nx[6] = __fmul_rn(wb.z, vp[48]); nx[7] = __fmul_rn(wb.w, vp[56]);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        vv[j] = vtile[(i + j) * 8 + d];
-                        ww[j] = wq[i + j];
+                        for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, pr[j]);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) pr[j] = nx[j];
                     }
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, __fmul_rn(ww[j], vv[j]));
+                    for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, pr[j]);
                 }
-                for (; i < n; ++i) acc = __fadd_rn(acc, __fmul_rn(wq[i], vtile[i * 8 + d]));
+#pragma unroll 1
+                for (; i < n; ++i) acc = __fadd_rn(acc, __fmul_rn(wq[i], vtile[(size_t)i * 8]));
             }
             cbar();  // the buffer the next fetch overwrites has been consumed
         }
-        if (chain) p.att[(size_t)(kvh * group + hg) * D + dc * 8 + d] = acc;
+        if (chain && ok) xstore(att_out + (size_t)(kvh * group + hg) * D + dc * 8 + d, acc, ep_out);
     }
+    return ok;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-gemma3_decode_kernel(const __grid_constant__ DParams p, uint32_t n_steps, int variant, uint32_t launch_id) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_bars[2 * 64];
-    __shared__ int s_abort, s_ok;
-    __shared__ uint32_t s_released[64];
-    __shared__ float s_part[16], s_bc, s_red[32];
-    __shared__ float s_bval[kConsumerWarps];
-    __shared__ uint32_t s_bidx[kConsumerWarps];
-
-    Cta c;
-    c.smem = smem;
-    c.smem32 = (uint32_t)__cvta_generic_to_shared(smem);
-    c.full0 = (uint32_t)__cvta_generic_to_shared(s_bars);
-    c.empty0 = c.full0 + 64 * 8;
-    c.s_abort = &s_abort;
-    c.s_ok = &s_ok;
-    c.part = s_part;
-    c.bc = &s_bc;
-    c.red = s_red;
-    c.tid = threadIdx.x;
-    c.lane = threadIdx.x & 31;
-    c.warp = threadIdx.x >> 5;
-    c.epoch = 0;
-    c.released = s_released;
-
+gemma3_decode_kernel(const __grid_constant__ DParams p_in, uint32_t n_steps, int variant, uint32_t launch_id,
+                     uint32_t epoch_base) {
+    unsigned char* smem = smem_base();
+    Shared& S = sh();
+    {   // the launch parameters, word by word (DParams is a multiple of 4 bytes)
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(&p_in);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&S.p);
+        for (uint32_t i = threadIdx.x; i < sizeof(DParams) / 4; i += kThreads) dst[i] = src[i];
+    }
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < p.n_slots; ++s) {
-            mbar_init(c.full0 + s * 8, 1);
-            mbar_init(c.empty0 + s * 8, 1);
-            s_released[s] = 0;
+        for (uint32_t s = 0; s < p_in.n_slots; ++s) {
+            mbar_init((uint32_t)__cvta_generic_to_shared(&S.full[s]), 1);
+            mbar_init((uint32_t)__cvta_generic_to_shared(&S.empty[s]), kConsumerWarps);
+            S.released[s] = 0;
         }
-
-        s_abort = 0;
-        s_ok = 1;
+        S.abort = 0;
+        S.launch_id = launch_id;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // the counter of the next launch: nobody touches it during this one
-        if (blockIdx.x == 0) p.sync[(launch_id ^ 1u) & 1u] = 0u;
+    }
+    const DParams& p = S.p;
+    // the layer table, once per launch: descriptors are read at every phase and must not cost a memory round trip
+    DLayer* layers = reinterpret_cast<DLayer*>(smem + p_in.off_layers);
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(p_in.layers);
+        uint4* dst = reinterpret_cast<uint4*>(layers);
+        for (uint32_t i = threadIdx.x; i < p_in.n_layer * (uint32_t)(sizeof(DLayer) / 16); i += kThreads) dst[i] = __ldg(src + i);
     }
     __syncthreads();
-    uint32_t* counter = p.sync + (launch_id & 1u);
-    c.launch_id = launch_id;
+    const Cta c = make_cta();
     const bool want_logits = variant != DECODE_CACHE_ONLY;
     uint32_t unit_base = 0;
 
@@ -749,12 +1159,12 @@ gemma3_decode_kernel(const __grid_constant__ DParams p, uint32_t n_steps, int va
             uint32_t issued = 0;
             for (uint32_t step = 0; ok && step < n_steps; ++step) {
                 for (uint32_t l = 0; ok && l < p.n_layer; ++l) {
-                    const DLayer& L = p.layers[l];
-                    ok = produce_phase(c, p, L.qkv, &unit_base, &issued) && produce_phase(c, p, L.o, &unit_base, &issued) &&
-                         produce_phase(c, p, L.gate_up, &unit_base, &issued) &&
-                         produce_phase(c, p, L.down, &unit_base, &issued);
+                    const DLayer& L = layers[l];
+                    ok = produce_phase(L.qkv, &unit_base, &issued) && produce_phase(L.o, &unit_base, &issued) &&
+                         produce_phase(L.gate_up, &unit_base, &issued) &&
+                         produce_phase(L.down, &unit_base, &issued);
                 }
-                if (ok && want_logits) ok = produce_phase(c, p, p.head, &unit_base, &issued);
+                if (ok && want_logits) ok = produce_phase(p.head, &unit_base, &issued);
             }
             if (!ok) {
                 // Stopped early: copies already issued still land in this CTA's shared memory. Wait (bounded)
@@ -774,80 +1184,108 @@ gemma3_decode_kernel(const __grid_constant__ DParams p, uint32_t n_steps, int va
     float* xres = reinterpret_cast<float*>(smem + p.off_xres);
     float* xs = reinterpret_cast<float*>(smem + p.off_xs);
     float* rope = reinterpret_cast<float*>(smem + p.off_rope);
+    float* vnew = reinterpret_cast<float*>(smem + p.off_vnew);
     unsigned char* scratch = smem + p.off_scratch;
-    const XImage x = ximage(scratch, p.nbp_max);
-    float* terms_all = reinterpret_cast<float*>(x.xsum + p.nbp_max);
+    float* terms_all = reinterpret_cast<float*>(ximage(scratch, p.nbp_max).xsum + p.nbp_max);
     const uint32_t E = p.E, D = p.D;
+    const Exchange& ex = p.ex;
     uint32_t tok = __ldcg(p.state + 0), pos = __ldcg(p.state + 1), rec = __ldcg(p.state + 2);
+    uint32_t epoch = epoch_base;  // the next exchange's number; every CTA counts alike
+    uint32_t lc = 0;              // layers run so far in this launch: picks the buffer parity
     uint32_t n_stamp = 0;
     // cycle stamp of this CTA at a phase boundary (thread 0; profiling runs only)
 #define ZQ_STAMP()                                                                              \
     do {                                                                                        \
         if (p.prof && c.tid == 0 && n_stamp < p.prof_cap) p.prof[(size_t)blockIdx.x * p.prof_cap + n_stamp++] = clock64(); \
     } while (0)
+    // uniform exit: s_abort is read between two barriers that every consumer thread passes
+#define ZQ_CHECK_ABORT()         \
+    do {                         \
+        cbar();                  \
+        const int a__ = S.abort; \
+        cbar();                  \
+        if (a__) return;         \
+    } while (0)
 
     for (uint32_t step = 0; step < n_steps; ++step) {
         ZQ_STAMP();
-        embed_row(c, p.head, tok, p.embed_scale, xres, E);
+        __threadfence();  // cache rows that the last CTA stored during earlier steps are read below
+        embed_row(p.head, tok, p.embed_scale, xres, E);
         for (uint32_t j = c.tid; j < D / 2; j += kConsumers) {  // RoPE angles of this position, every layer
             const float theta = __fmul_rn((float)pos, __ldg(p.freqs + j));
             rope[2 * j] = (float)cos((double)theta);
             rope[2 * j + 1] = (float)sin((double)theta);
         }
-        for (uint32_t l = 0; l < p.n_layer; ++l) {
-            const DLayer& L = p.layers[l];
+        for (uint32_t l = 0; l < p.n_layer; ++l, ++lc) {
+            const DLayer& L = layers[l];
+            const uint32_t par = lc & 1u, prev = par ^ 1u;
+            const uint32_t e_ffn_prev = epoch - 1;  // the previous layer's last exchange (unused for l == 0)
+            const uint32_t e_qkv = epoch, e_scores = epoch + 1, e_att = epoch + 2, e_proj = epoch + 3, e_g = epoch + 4,
+                           e_ffn = epoch + 5;
+            epoch += 6;
             // --- attention block
-            norm_quant(c, l ? p.ffn : nullptr, l ? p.layers[l - 1].post_ffw_norm_w : nullptr, L.attn_norm_w, xres, xs, E,
-                       p.eps, x);
-            cbar();
+            norm_quant(l ? ex.ffn + (size_t)prev * ex.ffn_n : nullptr, e_ffn_prev,
+                       l ? layers[l - 1].post_ffw_norm_w : nullptr, L.attn_norm_w, xres, xs, E, p.eps, terms_all);
+            if (l) {  // every CTA has finished the previous layer: its buffers of this parity may be rewritten
+                for (uint32_t base = 0; base < gridDim.x; base += kConsumers) {
+                    float v[1];
+                    xload_batch<1>(c, p, ex.ffn + (size_t)prev * ex.ffn_n, E + base + (uint32_t)c.tid, 1u, E + gridDim.x,
+                                   e_ffn_prev, v);
+                }
+            }
+            ZQ_CHECK_ABORT();
             ZQ_STAMP();
-            gemv_phase(c, p, L.qkv, &unit_base, x, terms_all, EP_STORE, p.qkv, nullptr);
+            unit_base = gemv_phase(L.qkv, unit_base, EP_VECTOR, ex.qkv + (size_t)par * ex.qkv_n, e_qkv, nullptr, nullptr);
             ZQ_STAMP();
-            if (!grid_barrier(c, p, counter)) return;
-            ZQ_STAMP();
+            cbar();  // the image region becomes attention scratch
             const uint32_t end = pos + 1;
             const uint32_t kv_len = (L.window && end > L.window) ? L.window : end;
             const uint32_t kv_start = end - kv_len;
-            scores_phase(c, p, L, pos, kv_start, kv_len, rope, reinterpret_cast<float*>(scratch));
+            if (!scores_phase(L, pos, kv_start, kv_len, rope, reinterpret_cast<float*>(scratch), vnew,
+                              ex.qkv + (size_t)par * ex.qkv_n, e_qkv, ex.scores + (size_t)par * ex.scores_n, e_scores))
+                return;
             ZQ_STAMP();
-            if (!grid_barrier(c, p, counter)) return;
+            cbar();  // qn is overwritten by the softmax weights
+            if (!softmax_v_phase(L, kv_start, kv_len, scratch, vnew, ex.scores + (size_t)par * ex.scores_n, e_scores,
+                                 ex.att + (size_t)par * ex.att_n, e_att))
+                return;
             ZQ_STAMP();
-            softmax_v_phase(c, p, L, kv_start, kv_len, scratch);
-            ZQ_STAMP();
-            if (!grid_barrier(c, p, counter)) return;
-            ZQ_STAMP();
-            quantise_global(c, p.att, p.n_head * D, x);
             cbar();
+            quantise_exchanged(ex.att + (size_t)par * ex.att_n, p.n_head * D, e_att, terms_all);
+            ZQ_CHECK_ABORT();
             ZQ_STAMP();
-            gemv_phase(c, p, L.o, &unit_base, x, terms_all, EP_STORE, p.proj, nullptr);
+            unit_base = gemv_phase(L.o, unit_base, EP_VECTOR, ex.proj + (size_t)par * ex.proj_n, e_proj, nullptr, nullptr);
             ZQ_STAMP();
-            if (!grid_barrier(c, p, counter)) return;
-            ZQ_STAMP();
+            cbar();
             // --- FFN block
-            norm_quant(c, p.proj, L.post_attn_norm_w, L.ffn_norm_w, xres, xs, E, p.eps, x);
+            norm_quant(ex.proj + (size_t)par * ex.proj_n, e_proj, L.post_attn_norm_w, L.ffn_norm_w, xres, xs, E, p.eps, terms_all);
+            ZQ_CHECK_ABORT();
+            ZQ_STAMP();
+            unit_base = gemv_phase(L.gate_up, unit_base, EP_GEGLU, ex.g + (size_t)par * ex.g_n, e_g, nullptr, nullptr);
+            ZQ_STAMP();
             cbar();
+            quantise_exchanged(ex.g + (size_t)par * ex.g_n, p.F, e_g, terms_all);
+            ZQ_CHECK_ABORT();
             ZQ_STAMP();
-            gemv_phase(c, p, L.gate_up, &unit_base, x, terms_all, EP_GEGLU, p.g, nullptr);
-            ZQ_STAMP();
-            if (!grid_barrier(c, p, counter)) return;
-            ZQ_STAMP();
-            quantise_global(c, p.g, p.F, x);
-            cbar();
-            ZQ_STAMP();
-            gemv_phase(c, p, L.down, &unit_base, x, terms_all, EP_STORE, p.ffn, nullptr);
-            ZQ_STAMP();
-            if (!grid_barrier(c, p, counter)) return;
+            unit_base = gemv_phase(L.down, unit_base, EP_VECTOR, ex.ffn + (size_t)par * ex.ffn_n, e_ffn, nullptr, nullptr);
+            cbar();  // every warp of this CTA is through the layer: sign the presence word
+            if (c.tid == 0) xstore(ex.ffn + (size_t)par * ex.ffn_n + E + blockIdx.x, 0.0f, e_ffn);
             ZQ_STAMP();
         }
         if (want_logits) {
-            norm_quant(c, p.ffn, p.layers[p.n_layer - 1].post_ffw_norm_w, p.output_norm_w, xres, xs, E, p.eps, x);
-            cbar();
+            const uint32_t last = (lc - 1) & 1u;
+            norm_quant(ex.ffn + (size_t)last * ex.ffn_n, epoch - 1, layers[p.n_layer - 1].post_ffw_norm_w,
+                       p.output_norm_w, xres, xs, E, p.eps, terms_all);
+            ZQ_CHECK_ABORT();
             ZQ_STAMP();
             Best best{-INFINITY, 0xFFFFFFFFu};
-            gemv_phase(c, p, p.head, &unit_base, x, terms_all, EP_LOGITS, p.logits, variant == DECODE_GREEDY ? &best : nullptr);
+            unit_base = gemv_phase(p.head, unit_base, EP_LOGITS, nullptr, 0, p.logits,
+                       variant == DECODE_GREEDY ? &best : nullptr);
             ZQ_STAMP();
             if (variant == DECODE_GREEDY) {
                 // first maximum wins (gpt2.zig:980-990): lanes, warps, CTAs, always preferring the lower index
+                const uint32_t e_best = epoch++;
+                unsigned long long* bx = ex.best + (size_t)(step & 1u) * ex.best_n;
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) {
                     Best o;
@@ -856,19 +1294,24 @@ gemma3_decode_kernel(const __grid_constant__ DParams p, uint32_t n_steps, int va
                     best_update(best, o.v, o.i);
                 }
                 if (c.lane == 0) {
-                    s_bval[c.warp] = best.v;
-                    s_bidx[c.warp] = best.i;
+                    S.bval[c.warp] = best.v;
+                    S.bidx[c.warp] = best.i;
                 }
                 cbar();
                 if (c.tid == 0) {
-                    Best b{s_bval[0], s_bidx[0]};
-                    for (int wv = 1; wv < kConsumerWarps; ++wv) best_update(b, s_bval[wv], s_bidx[wv]);
-                    p.part_val[blockIdx.x] = b.v;
-                    p.part_idx[blockIdx.x] = b.i;
+                    Best b{S.bval[0], S.bidx[0]};
+                    for (int wv = 1; wv < kConsumerWarps; ++wv) best_update(b, S.bval[wv], S.bidx[wv]);
+                    xstore(bx + 2 * blockIdx.x, b.v, e_best);
+                    xstore_u32(bx + 2 * blockIdx.x + 1, b.i, e_best);
                 }
-                if (!grid_barrier(c, p, counter)) return;
+                // every CTA reads every candidate: the next token is known everywhere without another exchange
                 Best b{-INFINITY, 0xFFFFFFFFu};
-                for (uint32_t k = c.lane; k < gridDim.x; k += 32) best_update(b, __ldcg(p.part_val + k), __ldcg(p.part_idx + k));
+                for (uint32_t base = 0; base < gridDim.x; base += 32) {
+                    const uint32_t k = base + c.lane;
+                    float v[2];
+                    xload_batch<2>(c, p, bx, 2 * k, 1u, 2 * gridDim.x, e_best, v);
+                    if (k < gridDim.x) best_update(b, v[0], __float_as_uint(v[1]));
+                }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) {
                     Best o;
@@ -876,6 +1319,7 @@ gemma3_decode_kernel(const __grid_constant__ DParams p, uint32_t n_steps, int va
                     o.i = __shfl_xor_sync(0xFFFFFFFFu, b.i, off);
                     best_update(b, o.v, o.i);
                 }
+                ZQ_CHECK_ABORT();
                 tok = b.i;
                 if (blockIdx.x == 0 && c.tid == 0) p.record[rec] = tok;
                 rec += 1;
@@ -884,6 +1328,7 @@ gemma3_decode_kernel(const __grid_constant__ DParams p, uint32_t n_steps, int va
         pos += 1;
     }
 #undef ZQ_STAMP
+#undef ZQ_CHECK_ABORT
     if (blockIdx.x == 0 && c.tid == 0) {
         p.state[0] = tok;
         p.state[1] = pos;
@@ -893,7 +1338,9 @@ gemma3_decode_kernel(const __grid_constant__ DParams p, uint32_t n_steps, int va
 
 // ---- host side --------------------------------------------------------------------------------
 
-bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split) {
+// Tiles of up to 8 rows (one per lane group of the tensor-core tile). A small matrix gets smaller tiles so
+// that at least half of the CTAs have one; rows that do not fit a ring slot are cut along K.
+bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split, uint32_t grid) {
     d->qs = w->qs;
     d->sc = static_cast<const uint8_t*>(w->sc);
     d->type = (uint32_t)w->type;
@@ -902,19 +1349,26 @@ bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split) {
     d->nbp = w->nbp;
     d->row_q_bytes = w->nbp * w->qb;
     d->row_s_bytes = w->scp * (w->type == ZQ_TYPE_Q4_1 ? 4u : 2u);
-    uint32_t r = slot_bytes / (d->row_q_bytes + d->row_s_bytes);
-    if (r > 8) r = 8;
+    d->pad_ = 0;
     d->split = split ? 1u : 0u;
-    if (split) {
-        r &= ~1u;
-        if (r < 2 || (w->out_dim & 1u)) return false;
-        const uint32_t half = r / 2, n_half = w->out_dim / 2;
-        d->n_units = (n_half + half - 1) / half;
+    if (split && (w->out_dim & 1u)) return false;
+    const uint32_t n = split ? w->out_dim / 2 : w->out_dim;  // rows to hand out (pairs of rows when split)
+    auto tiles = [&](uint32_t rows) { const uint32_t per = split ? rows / 2 : rows; return (n + per - 1) / per; };
+    uint32_t r = 8;
+    while (r > (split ? 2u : 1u) && tiles(r) < grid / 2) r /= 2;
+    d->rows_per_tile = r;
+    d->n_tiles = tiles(r);
+    const uint32_t QUAD = w->qb * 4, SB = w->type == ZQ_TYPE_Q4_1 ? 4u : 2u, nq = w->nbp / 4;
+    if (r * (d->row_q_bytes + d->row_s_bytes) <= slot_bytes) {
+        d->chunks = 1;
+        d->chunk_quads = nq;
     } else {
-        if (r < 1) return false;
-        d->n_units = (w->out_dim + r - 1) / r;
+        uint32_t cq = nq;
+        while (cq > 1 && r * (cq * QUAD + ((cq * 4 * SB + 15u) & ~15u) + 16u) > slot_bytes) --cq;
+        if (r * (cq * QUAD + ((cq * 4 * SB + 15u) & ~15u) + 16u) > slot_bytes) return false;
+        d->chunk_quads = cq;
+        d->chunks = (nq + cq - 1) / cq;
     }
-    d->rows_per_unit = r;
     return true;
 }
 
@@ -923,10 +1377,13 @@ bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split) {
 struct GemmaDecoder {
     DParams p;
     DLayer* d_layers = nullptr;
-    void* d_misc = nullptr;  // sync words, argmax partials
+    void* d_misc = nullptr;  // abort word and the exchange buffers
     size_t smem = 0;
     uint32_t grid = 0;
     uint32_t launches = 0;
+    uint32_t epoch = 1;      // first exchange number of the next launch (0 is what a fresh buffer holds)
+    uint32_t exchanges_per_step = 0;
+    size_t misc_bytes = 0;
     long long* d_prof = nullptr;
     ~GemmaDecoder() {
         cudaFree(d_layers);
@@ -951,7 +1408,7 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
     ZQ_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
     if (!coop) return ZQ_ERR_UNSUPPORTED;
 
-    // slot size: the largest single row (quants + scales) any matrix has, at least 4 KB
+    // slot size: eight q8_0 rows of 1152 weights with their scales (9.75 KB) unless the caller asks otherwise
     uint32_t max_row = 0, nbp_max = 0;
     auto row_bytes = [&](const zq_weight* w) {
         const uint32_t b = w->nbp * w->qb + w->scp * (w->type == ZQ_TYPE_Q4_1 ? 4u : 2u);
@@ -965,27 +1422,28 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
         row_bytes(L.gate_up);
         row_bytes(L.down);
     }
-    uint32_t slot_bytes = desc.slot_bytes ? desc.slot_bytes : (max_row < 7680u ? 7680u : max_row);
+    uint32_t slot_bytes = desc.slot_bytes ? desc.slot_bytes : 9984u;
     slot_bytes = (slot_bytes + 255u) & ~255u;
-    if (slot_bytes < max_row) return ZQ_ERR_UNSUPPORTED;
 
     GemmaDecoder* d = new (std::nothrow) GemmaDecoder;
     if (!d) return ZQ_ERR_NO_MEM;
     DParams& p = d->p;
     memset(&p, 0, sizeof(p));
     std::vector<DLayer> layers(desc.layers.size());
-    bool ok = describe(&p.head, desc.token_embd, slot_bytes, false);
+    memset(static_cast<void*>(layers.data()), 0, layers.size() * sizeof(DLayer));
+    const uint32_t grid = (uint32_t)sm_count();
+    bool ok = describe(&p.head, desc.token_embd, slot_bytes, false, grid);
     uint32_t terms = 0;
     auto note_terms = [&](const DMat& m) {
-        const uint32_t t = m.rows_per_unit * (m.nbp + 1);
+        const uint32_t t = 8 * (m.chunk_quads * 4 + 4);
         if (t > terms) terms = t;
     };
     note_terms(p.head);
     for (size_t l = 0; ok && l < layers.size(); ++l) {
         const GemmaDecoderLayer& s = desc.layers[l];
         DLayer& L = layers[l];
-        ok = describe(&L.qkv, s.qkv, slot_bytes, false) && describe(&L.o, s.o, slot_bytes, false) &&
-             describe(&L.gate_up, s.gate_up, slot_bytes, true) && describe(&L.down, s.down, slot_bytes, false);
+        ok = describe(&L.qkv, s.qkv, slot_bytes, false, grid) && describe(&L.o, s.o, slot_bytes, false, grid) &&
+             describe(&L.gate_up, s.gate_up, slot_bytes, true, grid) && describe(&L.down, s.down, slot_bytes, false, grid);
         note_terms(L.qkv);
         note_terms(L.o);
         note_terms(L.gate_up);
@@ -1006,12 +1464,6 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
     }
     p.output_norm_w = desc.output_norm_w;
     p.freqs = desc.freqs;
-    p.qkv = desc.qkv;
-    p.scores = desc.scores;
-    p.att = desc.att;
-    p.proj = desc.proj;
-    p.g = desc.g;
-    p.ffn = desc.ffn_out;
     p.logits = desc.logits;
     p.state = desc.state;
     p.record = desc.record;
@@ -1030,34 +1482,42 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
 
     // shared-memory carve-up
     auto up = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
-    const size_t gemv_scratch = (size_t)nbp_max * (32 + 8) + (size_t)kConsumerWarps * p.terms_per_warp * 4;
+    size_t after_image = (size_t)kConsumerWarps * p.terms_per_warp * 4;      // block terms of the dot phases
+    if (after_image < (size_t)16 * kConsumers * 4) after_image = (size_t)16 * kConsumers * 4;  // staging of the quantiser
+    if (after_image < (size_t)2 * E * 4) after_image = (size_t)2 * E * 4;      // norm weights
+    p.terms_bytes = (uint32_t)after_image;
+    const size_t gemv_scratch = (size_t)nbp_max * (32 + 8) + after_image;
     const size_t att_a = (size_t)(nh + nkv) * D * 4;
     const size_t att_b = (size_t)group * desc.ctx * 4 + 2 * (size_t)kVTile * 32;
     size_t scratch = gemv_scratch > att_a ? gemv_scratch : att_a;
     if (att_b > scratch) scratch = att_b;
-    size_t off = 0;
+    size_t off = kSharedHead;
+    p.off_layers = (uint32_t)off;
+    off = up(off + layers.size() * sizeof(DLayer), 128);
     p.off_xres = (uint32_t)off;
     off = up(off + (size_t)E * 4, 128);
     p.off_xs = (uint32_t)off;
     off = up(off + (size_t)E * 4, 128);
     p.off_rope = (uint32_t)off;
     off = up(off + (size_t)D * 4, 128);
+    p.off_vnew = (uint32_t)off;
+    off = up(off + (size_t)nkv * D * 4, 128);
     p.off_scratch = (uint32_t)off;
     off = up(off + scratch, 128);
     p.off_ring = (uint32_t)off;
-    const size_t budget = (size_t)max_smem - 2048;  // static shared memory of the kernel
-    if (off + 16 * (size_t)slot_bytes > budget) {
+    const size_t budget = (size_t)max_smem - 256;  // a little static shared memory of called functions
+    if (off + 8 * (size_t)slot_bytes > budget) {
         delete d;
         return ZQ_ERR_UNSUPPORTED;
     }
     uint32_t n_slots = (uint32_t)((budget - off) / slot_bytes);
     if (n_slots > 64) n_slots = 64;
-    if (desc.n_slots && desc.n_slots >= 16 && desc.n_slots <= n_slots) n_slots = desc.n_slots;
+    if (desc.n_slots && desc.n_slots >= 8 && desc.n_slots <= n_slots) n_slots = desc.n_slots;
     p.n_slots = n_slots;
     p.slot_bytes = slot_bytes;
     d->smem = off + (size_t)n_slots * slot_bytes;
 
-    d->grid = (uint32_t)sm_count();
+    d->grid = grid;
     cudaError_t e = cudaFuncSetAttribute(gemma3_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->smem);
     int per_sm = 0;
     if (e == cudaSuccess)
@@ -1067,22 +1527,45 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
         if (e != cudaSuccess) return cuda_fail(e);
         return ZQ_ERR_UNSUPPORTED;
     }
-    const size_t misc = 64 + (size_t)d->grid * 8;
+    // exchange buffers (two of each) behind the abort word
+    Exchange& ex = p.ex;
+    ex.qkv_n = (nh + 2 * nkv) * D;
+    ex.scores_n = nh * desc.ctx;
+    ex.att_n = nh * D;
+    ex.proj_n = E;
+    ex.g_n = F;
+    ex.ffn_n = E + d->grid;
+    ex.best_n = 2 * d->grid;
+    const size_t words = 2 * ((size_t)ex.qkv_n + ex.scores_n + ex.att_n + ex.proj_n + ex.g_n + ex.ffn_n + ex.best_n);
+    d->misc_bytes = 256 + words * 8;
     if (cudaMalloc(&d->d_layers, layers.size() * sizeof(DLayer)) != cudaSuccess ||
-        cudaMalloc(&d->d_misc, misc) != cudaSuccess) {
+        cudaMalloc(&d->d_misc, d->misc_bytes) != cudaSuccess) {
         delete d;
         return ZQ_ERR_NO_MEM;
     }
     e = cudaMemcpy(d->d_layers, layers.data(), layers.size() * sizeof(DLayer), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemset(d->d_misc, 0, misc);
+    if (e == cudaSuccess) e = cudaMemset(d->d_misc, 0, d->misc_bytes);
     if (e != cudaSuccess) {
         delete d;
         return cuda_fail(e);
     }
     p.layers = d->d_layers;
-    p.sync = static_cast<uint32_t*>(d->d_misc);
-    p.part_val = reinterpret_cast<float*>(static_cast<unsigned char*>(d->d_misc) + 64);
-    p.part_idx = reinterpret_cast<uint32_t*>(p.part_val + d->grid);
+    p.abort_word = static_cast<uint32_t*>(d->d_misc);
+    unsigned long long* w = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(d->d_misc) + 256);
+    ex.qkv = w;
+    w += 2 * (size_t)ex.qkv_n;
+    ex.scores = w;
+    w += 2 * (size_t)ex.scores_n;
+    ex.att = w;
+    w += 2 * (size_t)ex.att_n;
+    ex.proj = w;
+    w += 2 * (size_t)ex.proj_n;
+    ex.g = w;
+    w += 2 * (size_t)ex.g_n;
+    ex.ffn = w;
+    w += 2 * (size_t)ex.ffn_n;
+    ex.best = w;
+    d->exchanges_per_step = 6 * p.n_layer + 1;
     int rc = device_error_word(&p.err);
     if (rc != ZQ_OK) {
         delete d;
@@ -1094,20 +1577,29 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
 
 int gemma_decoder_run(GemmaDecoder* d, uint32_t n_steps, int variant, cudaStream_t st) {
     if (n_steps == 0) return ZQ_OK;
-    // ids 1, 2, 3, ...: the low bit picks the barrier counter, the value marks this launch's abort word
+    // launch ids 1, 2, 3, ... mark this launch's abort word
     uint32_t launch_id = d->launches + 1u;
-    if (launch_id == 0u) launch_id = 2u;
-    void* args[] = {&d->p, &n_steps, &variant, &launch_id};
+    if (launch_id == 0u) launch_id = 1u;
+    // Exchange numbers never repeat while a buffer may still hold an old one: when the 32-bit counter would wrap,
+    // the buffers are cleared (stream-ordered) and numbering restarts.
+    const uint64_t need = (uint64_t)n_steps * d->exchanges_per_step + 2;
+    if ((uint64_t)d->epoch + need >= 0xFFFFFFF0ull) {
+        ZQ_CUDA(cudaMemsetAsync(static_cast<unsigned char*>(d->d_misc) + 256, 0, d->misc_bytes - 256, st));
+        d->epoch = 1;
+    }
+    uint32_t epoch_base = d->epoch;
+    void* args[] = {&d->p, &n_steps, &variant, &launch_id, &epoch_base};
     ZQ_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(gemma3_decode_kernel), dim3(d->grid), dim3(kThreads),
                                         args, d->smem, st));
     d->launches = launch_id;
+    d->epoch += (uint32_t)need;
     return ZQ_OK;
 }
 
-// One step with cycle stamps: per CTA, thread 0's clock64() at every phase boundary, in program order:
-// token start; per layer 16 stamps (qkv prologue done, qkv done, barrier passed, scores done, barrier,
-// softmax.V done, barrier, o prologue done, o done, barrier, ffn prologue done, gate/up done, barrier, down
-// prologue done, down done, barrier); then head prologue done, head done. h_out[cta][cap].
+// One step with cycle stamps: per CTA, thread 0's clock64() at the phase boundaries, in program order:
+// token start; per layer 10 stamps (qkv prologue done, qkv done, scores done, softmax.V done, o prologue done,
+// o done, ffn prologue done, gate/up done, down prologue done, down done); then head prologue done, head done.
+// h_out[cta][cap].
 int gemma_decoder_profile(GemmaDecoder* d, int variant, cudaStream_t st, long long* h_out, uint32_t cap,
                           uint32_t* n_ctas) {
     if (!h_out || cap == 0) return ZQ_ERR_BAD_ARG;

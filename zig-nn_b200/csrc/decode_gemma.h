@@ -23,9 +23,8 @@ struct GemmaDecoderDesc {
     const float* output_norm_w;
     const float* freqs;
     std::vector<GemmaDecoderLayer> layers;
-    // engine-owned device buffers: qkv [q|k|v], scores [n_head][ctx], att [n_head*head_dim], proj [embed],
-    // g [ffn], ffn_out [embed], logits [vocab]; state [3], record [ctx]
-    float *qkv, *scores, *att, *proj, *g, *ffn_out, *logits;
+    // engine-owned device buffers: logits [vocab]; state [3] = token, position, record index; record [ctx]
+    float* logits;
     uint32_t *state, *record;
     uint32_t slot_bytes = 0, n_slots = 0;  // 0: chosen by the decoder
 };
@@ -39,7 +38,8 @@ void gemma_decoder_free(GemmaDecoder* d);
 // n_steps tokens in one launch. The token, its position and the record index are read from state[0..2];
 // DECODE_GREEDY feeds each argmax back as the next token and appends it to the record.
 int gemma_decoder_run(GemmaDecoder* d, uint32_t n_steps, int variant, cudaStream_t st);
-// One step with per-CTA cycle stamps at the phase boundaries; h_out[grid][cap], *n_ctas = grid.
+// One step with per-CTA cycle stamps at the phase boundaries (token start; ten per layer; two for the head);
+// h_out[grid][cap], *n_ctas = grid.
 int gemma_decoder_profile(GemmaDecoder* d, int variant, cudaStream_t st, long long* h_out, uint32_t cap,
                           uint32_t* n_ctas);
 uint32_t gemma_decoder_grid(const GemmaDecoder* d);

@@ -428,7 +428,6 @@ struct zq_gemma3 {
     // (decode_gemma.cu); otherwise, and for prefill chunks and batched sequences, as the launch sequence.
     GemmaDecoder* decoder = nullptr;
     int decode_mode = ZQ_DECODE_AUTO;
-    float *att = nullptr, *geglu = nullptr;  // attention output [head*head_dim], gelu(gate)*up [ffn]
     ~zq_gemma3() {
         gemma_decoder_free(decoder);
         zq_weight_free(token_embd);
@@ -596,12 +595,6 @@ static int gemma3_make_decoder(zq_gemma3* m) {
         L.window = (global || C.sliding_window >= C.ctx) ? 0u : C.sliding_window;
         d.layers.push_back(L);
     }
-    d.qkv = m->qkv;
-    d.scores = m->scores;
-    d.att = m->att;
-    d.proj = m->proj;
-    d.g = m->geglu;
-    d.ffn_out = m->ffn;
     d.logits = m->logits;
     d.state = m->d_state;
     d.record = m->d_record;
@@ -752,8 +745,6 @@ int zq_gemma3_create_batch(const zq_gemma3_config* cfg, const zq_gemma3_weights*
     TRY(m->arena.alloc_n(&m->d_state, 4));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, C.ctx));
-    TRY(m->arena.alloc_n(&m->att, QD));
-    TRY(m->arena.alloc_n(&m->geglu, F));
     TRY(gemma3_make_decoder(m));
 #undef TRY
     cudaError_t e = cudaStreamSynchronize(st);
