@@ -482,7 +482,7 @@ class Gemma3(_Engine):
         """One decode step with per-phase cycle stamps (the device-side counterpart of gemma3.ProfileStats,
         src/models/gemma3.zig:35-92). Returns an int64 array [n_ctas][3 + 10 * layers] of SM cycle counts at the
         phase boundaries (layout: include/zq.h, zq_gemma3_profile_step)."""
-        cap = max(400, 3 + 10 * self._cfg.layer)
+        cap = 3 + 10 * self._cfg.layer
         buf = np.zeros(4096 * cap, dtype=np.int64)
         n = C.c_uint32()
         rc = _lib.load().zq_gemma3_profile_step(self._h, int(token), _stream(), buf.ctypes.data_as(C.c_void_p), cap,

@@ -1034,8 +1034,18 @@ __device__ __noinline__ bool softmax_v_phase(const DLayer& L, uint32_t kv_start,
             mx = c.red[hg * wph];
 #pragma unroll 1
             for (uint32_t k = 1; k < wph; ++k) mx = fmaxf(mx, c.red[hg * wph + k]);
+            // four exponentials per pass, inlined: the double-precision chains of the four overlap
 #pragma unroll 1
-            for (uint32_t q = tl; q < kv_len; q += nt) wh[q] = exp_f32(__fsub_rn(wh[q], mx));
+            for (uint32_t q = tl; q < kv_len; q += 4 * nt) {
+                float e[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) e[u] = q + u * nt < kv_len ? wh[q + u * nt] : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) e[u] = (float)exp((double)__fsub_rn(e[u], mx));
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (q + u * nt < kv_len) wh[q + u * nt] = e[u];
+            }
             cbar();
             if ((uint32_t)c.tid < group) {  // one serial sum per head; the next eight are loaded under the adds
                 const float* wq = w + (size_t)c.tid * p.max_len;
