@@ -32,9 +32,10 @@ NCU_TRAFFIC_BYTES = 176257536
 WORKLOAD_NAME = "configs[1]: Q4_0 GEMV 1152->262144, M=1, f32 activations"
 
 
-def config_dict(weights, l2, sharding, launch):
-    """The `config` object of both arms: same keys, so the two lines can be compared field by field."""
-    return dict(workload=WORKLOAD_NAME, weights=weights, l2=l2, sharding=sharding, launch=launch)
+def config_dict():
+    """The `config` object: identical in both arms (ours and --impl reference), field by field."""
+    return dict(workload=WORKLOAD_NAME, qtype=WORKLOAD["qtype"], out_dim=WORKLOAD["out_dim"], in_dim=WORKLOAD["in_dim"],
+                m_rows=WORKLOAD["m_rows"], weights="N(0,0.02) seed 42 quantised q4_0", activations="f32 N(0,1) seed 43")
 
 
 def algorithmic_bytes(qtype, n, k, m=1):
@@ -220,11 +221,11 @@ def run_reference(args):
         "impl": "reference", "metric": "q4_0_gemv_algorithmic_gbs", "value": gbs, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": config_dict(weights="N(0,0.02) seed 42 quantised q4_0",
-                              l2="host memory (the 170 MB matrix exceeds the host caches)",
-                              sharding="rows split over %d host thread(s): CPU restatement of zig-nn matmul_q4_0_f32 "
-                                       "(dequant.zig:170-182)" % threads,
-                              launch="plain calls"),
+        "config": config_dict(),
+        "run": dict(l2="host memory (the 170 MB matrix exceeds the host caches)",
+                    sharding="rows split over %d host thread(s): CPU restatement of zig-nn matmul_q4_0_f32 "
+                             "(dequant.zig:170-182)" % threads,
+                    launch="plain calls"),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": "%d timed GEMV calls (oracle build: %s)" % (args.steps, build)},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -734,8 +735,8 @@ def main():
             "metric": "q4_0_gemv_algorithmic_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config_dict(
-                weights="N(0,0.02) seed 42 quantised q4_0",
+            "config": config_dict(),
+            "run": dict(
                 l2=("weights (170 MB) larger than L2 (126 MB)" if copies == 1 else
                     "%d copies of the %.0f MB shard used in turn (together larger than L2)"
                     % (copies, local_weight_bytes / 1e6)),

@@ -40,7 +40,7 @@ typedef enum zq_status {
                                 (error.EmptySequence / SequenceTooLong / ContextFull,
                                 src/models/gpt2.zig:425-426,445) */
     ZQ_ERR_TIMEOUT = 7,      /* a bounded device-side wait gave up */
-    ZQ_ERR_PEER = 8          /* peer (multi-GPU) set-up failed */
+    ZQ_ERR_PEER = 8          /* peer (multi-GPU) set-up failed: a peer's buffer or flag pointer is missing */
 } zq_status;
 
 const char* zq_status_string(int status);
@@ -52,6 +52,14 @@ int zq_abi_version(void);
  * memory instead of hanging. *out receives the flag (0 = never happened); clear != 0 resets it.
  * Synchronises the device. */
 int zq_device_error(unsigned int* out, int clear);
+/* The same as a status: ZQ_ERR_TIMEOUT when a bounded device-side wait has run out since the word was last
+ * cleared (the result buffers of that call then hold stale data), ZQ_OK otherwise. Synchronises the device.
+ * Callers of the peer exchanges check it at their own synchronisation points. */
+int zq_device_check(int clear);
+/* Number of polls a device-side wait on a PEER's flag makes before it gives up (zq_peer_gather*,
+ * zq_matmul_gather); 0 restores the kernels' own defaults (about a second). Process-wide; takes effect with the
+ * next launch. Lets a host fail fast, and lets a test make a wait run out without hanging anything. */
+int zq_set_wait_limit(unsigned int polls);
 
 /* GGML tensor type ids — src/gguf/dequant.zig:9-20. */
 typedef enum zq_type {
@@ -65,6 +73,12 @@ typedef enum zq_type {
 /* How the activation row is treated before the dot products.
  *   ZQ_ACT_F32: f32 activations times weights dequantised on the fly — the GPT-2
  *               path (src/models/gpt2.zig:632-686 -> src/gguf/dequant.zig:133-309).
+ *               Up to 48 rows per call the activations keep 22 mantissa bits (results agree
+ *               with the f32 CPU path to about 1e-7 relative L2). From 49 rows on the call is a
+ *               tensor-core GEMM with fp16 operands, as ZQ_ACT_F16: about 3e-4 relative L2
+ *               (inside the path's 1e-3 bar), and it NEEDS the workspace of
+ *               zq_matmul_workspace_bytes(); without one the call returns ZQ_ERR_BAD_ARG (it is
+ *               not served by the slower small-batch kernel behind the caller's back).
  *   ZQ_ACT_Q8 : each activation row is first quantised to 32-wide int8 blocks and
  *               the dots are exact int8 x int8 -> int32 — the Gemma-3 path
  *               (src/gguf/thread_pool.zig:96-160 -> src/gguf/simd_dot.zig:25-152).

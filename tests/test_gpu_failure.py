@@ -1,0 +1,125 @@
+"""Failure paths that must end with a status, not with a hang: a device-side wait that runs out, a missing
+peer pointer, a many-row call without its workspace. Every wait here is bounded by a small poll count set
+through zq_set_wait_limit; nothing faults, traps or spins for long."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from zignn_b200 import ggml
+
+pytestmark = pytest.mark.gpu
+
+GATH = int.from_bytes(b"GATH", "big")
+FGAT = int.from_bytes(b"FGAT", "big")
+
+
+def ptr_array(tensors):
+    return (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def test_peer_gather_wait_runs_out_and_the_library_stays_usable(zq):
+    """world = 2 on ONE GPU: the 'peer' is a second local buffer whose owner never shows up, so the flag this
+    rank waits for is never advanced. With a limit of 1024 polls the kernel returns, the device error word reads
+    'GATH', zq_device_check reports ZQ_ERR_TIMEOUT once, and later calls work."""
+    from zignn_b200 import _lib
+    lib = _lib.load()
+    assert _lib.device_error(clear=True) in (0, GATH, FGAT)
+    n = 4096
+    y = [torch.zeros(2 * n, device="cuda") for _ in range(2)]       # result buffers of rank 0 and of the absent rank 1
+    flags = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
+    y[0][:n] = 1.0
+    lib.zq_set_wait_limit(1024)
+    try:
+        rc = lib.zq_peer_gather(ptr_array(y), ptr_array(flags), 2, 0, 0, n, 1, stream())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.all(y[1][:n] == 1.0)               # the slice was pushed to the peer's buffer
+        assert int(flags[1][0].item()) == 8             # and published there (8 CTAs per peer)
+        assert _lib.device_error(clear=False) == GATH   # the wait for the peer's slice gave up
+        assert lib.zq_device_check(1) == 7              # ZQ_ERR_TIMEOUT, cleared by the call
+        assert lib.zq_device_check(0) == 0
+        # the same exchange with the peer's arrival supplied by hand completes without an error
+        flags[0][1] = 16
+        rc = lib.zq_peer_gather(ptr_array(y), ptr_array(flags), 2, 0, 0, n, 2, stream())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert lib.zq_device_check(1) == 0
+    finally:
+        lib.zq_set_wait_limit(0)
+    # a missing peer pointer is a set-up error, reported before anything is launched
+    bad = (C.c_void_p * 2)(y[0].data_ptr(), None)
+    assert lib.zq_peer_gather(bad, ptr_array(flags), 2, 0, 0, n, 3, stream()) == 8  # ZQ_ERR_PEER
+
+
+def test_fused_gather_wait_runs_out(zq, oracle):
+    """The exchange fused into the GEMV epilogue, same set-up: the result rows are correct in this rank's own
+    buffer and in the 'peer' buffer, the wait for the absent peer ends after the poll limit with 'FGAT'."""
+    from zignn_b200 import _lib
+    lib = _lib.load()
+    _lib.device_error(clear=True)
+    n, k = 148 * 2 * 8 * 16, 1152  # enough row tiles for the whole-rows kernel
+    rng = np.random.default_rng(1)
+    raw = oracle.quantize(ggml.Q4_0, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    qw = zq.QuantWeight(raw, ggml.Q4_0, n, k)
+    x = torch.from_numpy(rng.standard_normal((1, k)).astype(np.float32)).cuda()
+    want = zq.quant_matmul_no_grad(x, qw).reshape(-1)
+    odd = [torch.zeros(2 * n, device="cuda") for _ in range(2)]
+    even = [torch.zeros(2 * n, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
+    sync = torch.zeros(2, dtype=torch.int32, device="cuda")
+    lib.zq_set_wait_limit(1024)
+    try:
+        rc = lib.zq_matmul_gather(qw.handle, C.c_void_p(x.data_ptr()), None, ptr_array(odd), ptr_array(even),
+                                  ptr_array(flags), 2, 0, 0, C.c_void_p(sync.data_ptr()), stream())
+        assert rc == 0
+        torch.cuda.synchronize()
+        for buf in (odd[0], odd[1]):  # round 1 uses the odd buffers: this rank's own and the peer's
+            assert torch.allclose(buf[:n], want, rtol=1e-5, atol=1e-7)
+        assert _lib.device_error(clear=False) == FGAT
+        assert lib.zq_device_check(1) == 7
+    finally:
+        lib.zq_set_wait_limit(0)
+    assert torch.equal(zq.quant_matmul_no_grad(x, qw).reshape(-1), want)  # the library still works
+
+
+def test_many_rows_without_workspace_is_refused(zq, oracle):
+    from zignn_b200 import _lib
+    import zignn_b200.structs as S
+    lib = _lib.load()
+    raw = oracle.quantize(ggml.Q4_0, np.zeros((64, 64), np.float32))
+    qw = zq.QuantWeight(raw, ggml.Q4_0, 64, 64)
+    x, y = torch.zeros(64, 64, device="cuda"), torch.zeros(64, 64, device="cuda")
+    ep = S.Epilogue(None, 0, None, None)
+    rc = lib.zq_matmul(qw.handle, C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), 64, zq.ACT_F32, C.byref(ep), None, 0,
+                       stream())
+    assert rc == 1  # ZQ_ERR_BAD_ARG: 49 rows or more need the workspace
+    rc = lib.zq_matmul(qw.handle, C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), 48, zq.ACT_F32, C.byref(ep), None, 0,
+                       stream())
+    assert rc == 0
+
+
+@pytest.mark.parametrize("m", [1, 64])
+def test_rows_of_vanishing_magnitude_give_finite_results(zq, oracle, m):
+    """A row whose largest magnitude is 1e-38 (a vanished gradient): the power-of-two row scale must not
+    overflow; outputs are finite and zero at the accuracy of the path."""
+    n, k = 128, 256
+    raw = oracle.quantize(ggml.Q8_0, (np.random.default_rng(2).standard_normal((n, k)) * 0.02).astype(np.float32))
+    qw = zq.QuantWeight(raw, ggml.Q8_0, n, k)
+    x = np.random.default_rng(3).standard_normal((m, k)).astype(np.float32)
+    x[0] = 1e-38
+    got = zq.quant_matmul_no_grad(torch.from_numpy(x).cuda(), qw, zq.ACT_F32).cpu().numpy()
+    assert np.all(np.isfinite(got))
+    assert np.max(np.abs(got[0])) <= 1e-30
+    if m > 1:
+        want = oracle.linear(ggml.Q8_0, raw, x, n, k, act_mode=0, n_threads=2)
+        err = np.linalg.norm(got[1:] - want[1:]) / np.linalg.norm(want[1:])
+        assert err <= 6e-4
+    go = torch.from_numpy(np.full((2, n), 1e-38, np.float32)).cuda()
+    gx = zq.quant_matmul_transposed(go, qw).cpu().numpy()
+    assert np.all(np.isfinite(gx)) and np.max(np.abs(gx)) <= 1e-30

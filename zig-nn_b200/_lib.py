@@ -25,6 +25,8 @@ SIGNATURES = {
     "zq_last_cuda_error": (i, []),
     "zq_abi_version": (i, []),
     "zq_device_error": (i, [P(u32), i]),
+    "zq_device_check": (i, [i]),
+    "zq_set_wait_limit": (i, [u32]),
     "zq_block_size": (sz, [i]),
     "zq_bytes_per_block": (sz, [i]),
     "zq_tensor_bytes": (sz, [i, sz]),

@@ -248,7 +248,6 @@ int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_strea
     zq_gpt2* m = new (std::nothrow) zq_gpt2;
     if (!m) return ZQ_ERR_NO_MEM;
     m->c = *cfg;
-    m->graphs.disabled = getenv("ZQ_NO_GRAPH") != nullptr;
     cudaStream_t st = as_stream(stream);
     const uint32_t E = cfg->embed, F = cfg->ffn;
     int rc = ZQ_OK;
@@ -653,7 +652,6 @@ int zq_gemma3_create_batch(const zq_gemma3_config* cfg, const zq_gemma3_weights*
     m->c = C;
     m->n_seq = n_seq;
     m->seq_lens.assign(n_seq, 0);
-    m->graphs.disabled = getenv("ZQ_NO_GRAPH") != nullptr;
     cudaStream_t st = as_stream(stream);
     int rc = ZQ_OK;
 #define TRY(expr)                  \

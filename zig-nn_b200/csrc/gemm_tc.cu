@@ -184,8 +184,7 @@ convert_rows_tiled_kernel(const float* __restrict__ x, __half* __restrict__ xt, 
     if (threadIdx.x == 0) {
         float a = red[0];
         for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
-        int e = 0;
-        if (a > 0.0f && a < INFINITY) e = ilogbf(a) - 13;
+        const int e = row_scale_exponent(a);
         s_pre = ldexpf(1.0f, -e);
         if (real) post[m] = ldexpf(1.0f, e);
     }

@@ -540,9 +540,7 @@ size_t zq_matmul_workspace_bytes(const zq_weight* w, uint32_t m_rows, int act_mo
         return q + 2 * s;
     }
     if ((act_mode == ZQ_ACT_F32 && m_rows >= kGemmMinRows) || (act_mode == ZQ_ACT_F16 && m_rows > 0)) {
-        // either GEMM kernel can use it
-        const size_t a = gemm_f16_workspace_bytes(w, m_rows), b = gemm_tc_workspace_bytes(w, m_rows);
-        return a > b ? a : b;
+        return gemm_tc_workspace_bytes(w, m_rows);
     }
     return 0;
 }
@@ -559,17 +557,17 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
     if (!w) return ZQ_ERR_BAD_ARG;
     if (m_rows == 0) return ZQ_OK;
     if (!d_x || !d_y) return ZQ_ERR_BAD_ARG;
+    if (check_weight_device(w) != ZQ_OK) return ZQ_ERR_BAD_ARG;  // the weight lives on another device
     cudaStream_t st = as_stream(stream);
     if (act_mode == ZQ_ACT_F32) {
         if (((uintptr_t)d_x & 15) != 0) return launch_gemv_f32(w, d_x, d_y, m_rows, epilogue, st);
-        // many rows and a workspace for the fp16 activations: the tensor-core GEMM
-        if (m_rows >= kGemmMinRows && d_workspace && ((uintptr_t)d_workspace & 255) == 0 &&
-            workspace_bytes >= zq_matmul_workspace_bytes(w, m_rows, act_mode))
-        {
-            // ZQ_GEMM=mma selects the mma.sync version of the same product (for comparison)
-            static const bool legacy = getenv("ZQ_GEMM") && getenv("ZQ_GEMM")[0] == 'm';
-            return legacy ? launch_gemm_f16(w, d_x, d_y, m_rows, epilogue, d_workspace, st)
-                          : launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
+        // many rows: the tensor-core GEMM, which needs the workspace for its fp16 activation image. A call
+        // without one is refused rather than served by 16-row passes that are several times slower.
+        if (m_rows >= kGemmMinRows) {
+            if (!d_workspace || ((uintptr_t)d_workspace & 255) != 0 ||
+                workspace_bytes < zq_matmul_workspace_bytes(w, m_rows, act_mode))
+                return ZQ_ERR_BAD_ARG;
+            return launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
         }
         // passes of up to 16 activation rows over the weights
         int rc = launch_gemv_mma_passes_f32(w, d_x, d_y, m_rows, epilogue, st);
@@ -582,9 +580,7 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
         if (!d_workspace || ((uintptr_t)d_workspace & 255) ||
             workspace_bytes < zq_matmul_workspace_bytes(w, m_rows, act_mode))
             return ZQ_ERR_BAD_ARG;
-        static const bool legacy = getenv("ZQ_GEMM") && getenv("ZQ_GEMM")[0] == 'm';
-        return legacy ? launch_gemm_f16(w, d_x, d_y, m_rows, epilogue, d_workspace, st)
-                      : launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
+        return launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
     }
     if (act_mode == ZQ_ACT_Q8) {
         if (w->in_dim > 16384) return ZQ_ERR_LIMIT;

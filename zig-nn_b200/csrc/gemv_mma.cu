@@ -507,8 +507,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, 
     __syncthreads();
     if (tid < (int)M) {
         const float amax = __uint_as_float(amax_bits[tid]);
-        int e = 0;  // |x| * 2^-e < 2^14: both fp16 parts, and the parts divided by 16, stay normal
-        if (amax > 0.0f && amax < INFINITY) e = ilogbf(amax) - 13;
+        const int e = row_scale_exponent(amax);
         pre[tid] = ldexpf(1.0f, -e);
         post[tid] = ldexpf(1.0f, e);
     }
@@ -657,6 +656,7 @@ struct PeerArgs {
     uint32_t* sync;              // this GPU: [0] completed rounds, [1] CTAs that have finished the current one
     unsigned int* err;           // the library's device-error word
     uint32_t world, rank, row_off;
+    uint32_t spin_limit;         // polls of a local flag before giving up
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
@@ -793,8 +793,7 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-        int e = 0;
-        if (amax > 0.0f && amax < INFINITY) e = ilogbf(amax) - 13;
+        const int e = row_scale_exponent(amax);
         pre_l[0] = ldexpf(1.0f, -e);
         ps = ldexpf(1.0f, e);
     }
@@ -930,7 +929,7 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
                 for (uint32_t p = 0; p < pa.world; ++p) {
                     if (p == pa.rank) continue;
                     bool ok = false;
-                    for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
+                    for (uint32_t i = 0; i < pa.spin_limit; ++i) {
                         if ((int32_t)(ld_acquire_sys_u32(pa.flags[pa.rank] + p) - round) >= 0) {
                             ok = true;
                             break;
@@ -1159,7 +1158,7 @@ int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue
     }
     PeerArgs pa{};
     for (uint32_t r = 0; r < world; ++r) {
-        if (!y_odd[r] || !y_even[r] || !flags[r]) return ZQ_ERR_BAD_ARG;
+        if (!y_odd[r] || !y_even[r] || !flags[r]) return ZQ_ERR_PEER;  // a peer's buffer was never mapped
         pa.y[1][r] = y_odd[r];
         pa.y[0][r] = y_even[r];
         pa.flags[r] = flags[r];
@@ -1170,6 +1169,7 @@ int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue
     pa.world = world;
     pa.rank = rank;
     pa.row_off = row_off;
+    pa.spin_limit = wait_limit() ? wait_limit() : kPeerSpinLimit;
     rc = launch_rows1_any(w, x, nullptr, a, pa, st);
     return rc == ZQ_ERR_LIMIT ? ZQ_ERR_UNSUPPORTED : rc;
 }

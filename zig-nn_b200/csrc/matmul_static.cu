@@ -51,6 +51,8 @@ extern "C" int zq_matmul_q8_static(const zq_weight* w, const float* d_x, float* 
     if (m_rows == 0) return ZQ_OK;
     if (!d_x || !d_y) return ZQ_ERR_BAD_ARG;
     if (m_rows > kMaxRows || w->in_dim > kMaxInDim) return ZQ_ERR_LIMIT;  // beyond the built-in scratch
+    // the scratch of the CURRENT device is used: the weight has to live there too
+    if (zq::check_weight_device(w) != ZQ_OK) return ZQ_ERR_BAD_ARG;
     void* base = nullptr;
     int rc = static_scratch(&base);
     if (rc != ZQ_OK) return rc;

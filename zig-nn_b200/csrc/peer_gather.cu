@@ -37,7 +37,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 
 __global__ void __launch_bounds__(256)
 peer_gather_kernel(PeerTable tab, uint32_t world, uint32_t rank, size_t slice_off, size_t slice_len,
-                   uint32_t round_arg, const uint32_t* __restrict__ round_ctr, unsigned int* err_word) {
+                   uint32_t round_arg, const uint32_t* __restrict__ round_ctr, unsigned int* err_word,
+                   uint32_t spin_limit) {
     const uint32_t round = round_ctr ? *round_ctr : round_arg;
     const uint32_t pi = blockIdx.x / kCtasPerPeer, chunk = blockIdx.x % kCtasPerPeer;
     const uint32_t peer = pi < rank ? pi : pi + 1;  // the peers in rank order, skipping this rank
@@ -67,7 +68,7 @@ peer_gather_kernel(PeerTable tab, uint32_t world, uint32_t rank, size_t slice_of
             const uint32_t want = round * kCtasPerPeer;
             const uint32_t* f = tab.flags[rank] + peer;
             bool ok = false;
-            for (uint32_t i = 0; i < kSpinLimit; ++i) {
+            for (uint32_t i = 0; i < spin_limit; ++i) {
                 if ((int32_t)(ld_acquire_sys(f) - want) >= 0) {
                     ok = true;
                     break;
@@ -89,7 +90,7 @@ static int peer_gather_launch(float* const* y_odd, float* const* y_even, uint32_
                               uint32_t* d_round, cudaStream_t st) {
     PeerTable tab{};
     for (uint32_t r = 0; r < world; ++r) {
-        if (!y_odd[r] || !y_even[r] || !h_flag_peers[r]) return ZQ_ERR_BAD_ARG;
+        if (!y_odd[r] || !y_even[r] || !h_flag_peers[r]) return ZQ_ERR_PEER;  // a peer's buffer was never mapped
         tab.y[1][r] = y_odd[r];
         tab.y[0][r] = y_even[r];
         tab.flags[r] = h_flag_peers[r];
@@ -102,7 +103,7 @@ static int peer_gather_launch(float* const* y_odd, float* const* y_even, uint32_
         ZQ_LAUNCH_CHECK();
     }
     peer_gather_kernel<<<(world - 1) * kCtasPerPeer, 256, 0, st>>>(tab, world, rank, slice_offset, slice_len, round,
-                                                                    d_round, err_word);
+                                                                    d_round, err_word, wait_limit() ? wait_limit() : kSpinLimit);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }

@@ -1,6 +1,9 @@
 // Weight handles: upload + re-layout of GGUF quant blocks, bit-exact dequantisation.
 #include <new>
 
+#include <atomic>
+#include <mutex>
+
 #include "zq_internal.h"
 
 namespace zq {
@@ -11,11 +14,22 @@ thread_local int g_last_cuda_error = 0;
 __device__ unsigned int g_device_error = 0;
 
 // Device address of the error word, for kernels in other translation units (passed as a parameter).
+static std::atomic<uint32_t> g_wait_limit{0};
+uint32_t wait_limit() { return g_wait_limit.load(std::memory_order_relaxed); }
+
+int check_weight_device(const zq_weight* w) {
+    int dev = -1;
+    ZQ_CUDA(cudaGetDevice(&dev));
+    return w && w->device == dev ? ZQ_OK : ZQ_ERR_BAD_ARG;
+}
+
 int device_error_word(unsigned int** out) {
     static unsigned int* cached[64] = {nullptr};
+    static std::mutex mu;
     int dev = 0;
     ZQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return ZQ_ERR_LIMIT;
+    std::lock_guard<std::mutex> lock(mu);
     if (!cached[dev]) {
         void* p = nullptr;
         ZQ_CUDA(cudaGetSymbolAddress(&p, g_device_error));
@@ -147,6 +161,8 @@ int make_weight(int type, uint32_t out_dim, uint32_t in_dim, zq_weight** out) {
     }
     w->qs = static_cast<uint8_t*>(w->base);
     w->sc = w->qs + qs_pad;
+    w->device = 0;
+    cudaGetDevice(&w->device);
     *out = w;
     return ZQ_OK;
 }
@@ -184,6 +200,16 @@ int zq_device_error(unsigned int* out, int clear) {
         const unsigned int z = 0;
         ZQ_CUDA(cudaMemcpyToSymbol(zq::g_device_error, &z, sizeof(z)));
     }
+    return ZQ_OK;
+}
+int zq_device_check(int clear) {
+    unsigned int v = 0;
+    const int rc = zq_device_error(&v, clear);
+    if (rc != ZQ_OK) return rc;
+    return v ? ZQ_ERR_TIMEOUT : ZQ_OK;
+}
+int zq_set_wait_limit(unsigned int polls) {
+    zq::g_wait_limit.store(polls, std::memory_order_relaxed);
     return ZQ_OK;
 }
 int zq_abi_version(void) { return 1; }

@@ -3,6 +3,7 @@
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 
 #include "zq.h"
@@ -31,6 +32,7 @@ struct zq_weight {
     void* sc;          // device
     void* base;        // the single allocation holding qs and sc
     size_t bytes;      // size of that allocation
+    int device;        // ordinal of the device that holds it
 };
 
 namespace zq {
@@ -95,11 +97,23 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 #endif
 
+// Exponent e of the power-of-two row scale 2^-e that brings a row's largest magnitude `amax` just under 2^14
+// (fp16 operands keep full precision, no overflow). Rows that are zero, not finite, or so small that 2^-e
+// would overflow f32 (amax below 2^-100: vanishing gradients) are left unscaled.
+__host__ __device__ inline int row_scale_exponent(float amax) {
+    if (!(amax > 7.8886090522101181e-31f) || !(amax < INFINITY)) return 0;
+    return ilogbf(amax) - 13;
+}
+
 inline bool is_quant(int t) { return t == ZQ_TYPE_Q4_0 || t == ZQ_TYPE_Q4_1 || t == ZQ_TYPE_Q8_0; }
 
 int sm_count();  // multiprocessors of the current device (cached per device)
+// Polls a device-side wait on a peer's flag makes before it gives up (zq_set_wait_limit; 0 = the kernel's default).
+uint32_t wait_limit();
 // Device address of the word zq_device_error() reads; kernels with bounded waits record a timeout there.
 int device_error_word(unsigned int** out);
+// ZQ_OK when the weight lives on the current device, ZQ_ERR_BAD_ARG otherwise.
+int check_weight_device(const zq_weight* w);
 
 // ---- launchers implemented in gemv.cu and used by the engines -------------------------
 
@@ -128,16 +142,12 @@ int launch_quantize_rows_q8(const float* x, uint32_t m_rows, uint32_t in_dim, in
 // Exact int8 tensor-core GEMM for many Q8-quantised activation rows; bit-identical to launch_gemv_q8 (gemm_q8.cu).
 int launch_gemm_q8(const zq_weight* w, const int8_t* xq, const float* xscale, const int32_t* xsum, float* y,
                    uint32_t m_rows, const zq_epilogue* ep, cudaStream_t st);
-// Tensor-core GEMM for many activation rows (gemm.cu): fp16 operands, f32 accumulation. `workspace`
-// holds gemm_f16_workspace_bytes() bytes, 256-byte aligned.
 constexpr uint32_t kGemmMinRows = 49;  // below this, passes of the 16-row decode kernel are faster
-size_t gemm_f16_workspace_bytes(const zq_weight* w, uint32_t m_rows);
-int launch_gemm_f16(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
-                    void* workspace, cudaStream_t st);
 // x16[m][k] = fp16(x[m][k] * 2^-e_m), post[m] = 2^e_m (gemm.cu).
 int launch_convert_rows_f16(const float* x, __half* x16, float* post, uint32_t m_rows, uint32_t in_dim,
                             cudaStream_t st);
-// The same product with tcgen05.mma and the accumulator in tensor memory (gemm_tc.cu); same workspace.
+// Tensor-core GEMM for many activation rows: tcgen05.mma, fp16 operands, accumulator in tensor memory
+// (gemm_tc.cu). `workspace` holds gemm_tc_workspace_bytes() bytes, 256-byte aligned.
 int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
                    void* workspace, cudaStream_t st);
 size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows);

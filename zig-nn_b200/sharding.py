@@ -172,6 +172,12 @@ class PeerGather:
         self.round += 1
         return self.bufs[self.round & 1].view(self.world, self.m, self.per)
 
+    def check(self, clear=True):
+        """Raises when a bounded device-side wait of an exchange ran out since the last check (a peer reached
+        its call more than the wait limit later, or never): the buffers returned since then hold stale data.
+        Synchronises the device; call it at the points where the host synchronises anyway."""
+        self._lib.check(self._lib.load().zq_device_check(int(bool(clear))), "peer exchange")
+
     def note_replayed(self, n_calls):
         """A captured sequence containing `n_calls` (even) gather() calls has been replayed once."""
         if n_calls % 2:
