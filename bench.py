@@ -577,7 +577,8 @@ def main():
             ref = oracle.matmul_f32(ggml.TYPE_IDS[q], sub, x.cpu().numpy().reshape(-1), len(rows), k, 4)
             g = got[0, torch.from_numpy(rows).cuda()].cpu().numpy()
             parity["vs_cpu_oracle_rel_l2_256_rows"] = float(np.linalg.norm(g - ref) / np.linalg.norm(ref))
-            parity["ok"] = diff <= 2e-6 and parity["vs_cpu_oracle_rel_l2_256_rows"] <= 2e-6
+            parity["cpu_tolerance"] = 1e-5  # the path's bar is 1e-3; f32 summation orders differ by about 1e-6
+            parity["ok"] = diff <= 2e-6 and parity["vs_cpu_oracle_rel_l2_256_rows"] <= 1e-5
         else:
             parity["ok"] = diff <= 2e-6
         flag = torch.tensor([0 if parity["ok"] else 1], device="cuda")
