@@ -60,8 +60,10 @@ struct DMat {
     uint32_t rows_per_tile, n_tiles;
     uint32_t split;       // 1: a tile holds rows_per_tile/2 rows of the first half and the matching rows of the second
     uint32_t chunks;      // pieces per tile along K (1: whole rows, one bulk copy of quants and one of scales)
-    uint32_t chunk_quads; // quads per piece (the last piece of a row may be shorter)
-    uint32_t pad_;
+    uint32_t chunk_quads; // quads per piece (the last piece of a row may be shorter); at most 16
+    uint32_t tiles_div, tiles_rem;  // n_tiles / grid and n_tiles % grid: CTA c owns tiles_div + (c < tiles_rem) tiles
+    uint32_t chunk_q_pitch;         // bytes between the rows of a piece in a ring slot (chunks > 1)
+    uint32_t pad_[2];
 };
 
 struct alignas(16) DLayer {
@@ -93,9 +95,11 @@ struct DParams {
     uint32_t n_layer, E, D, n_head, n_kv, F, ctx, max_len;
     float eps, embed_scale;
     // shared-memory carve-up (bytes from the start of dynamic shared memory)
-    uint32_t n_slots, slot_bytes, off_ring, off_layers, off_xres, off_xs, off_rope, off_vnew, off_scratch;
+    uint32_t n_slots, slot_magic, slot_bytes, off_ring, off_layers, off_xres, off_xs, off_rope, off_vnew, off_scratch;
     uint32_t terms_per_warp, nbp_max;
     uint32_t terms_bytes;  // bytes behind the activation image: block terms, staging of the prologues
+    uint32_t deal_limit;   // a phase with at most this many units per CTA shares every unit among all warps
+    uint32_t xh_off;       // second half of the activation image, in 16-byte words from the first
 };
 
 // ---- small device helpers --------------------------------------------------------------------
@@ -115,6 +119,16 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 __device__ __forceinline__ uint32_t pick(const uint4& v, int j) {
     return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
+}
+// n / d and n % d with magic = floor(2^32 / d) (0xFFFFFFFF for d = 1) from the host: the product's high word is
+// the quotient or one less; a 32-bit division instruction sequence costs 65-95 cycles on this part.
+__device__ __forceinline__ void fast_divmod(uint32_t n, uint32_t d, uint32_t magic, uint32_t& q, uint32_t& r) {
+    q = __umulhi(n, magic);
+    r = n - q * d;
+    if (r >= d) {
+        r -= d;
+        q += 1;
+    }
 }
 __device__ __forceinline__ int quad_transpose_reduce(const int (&p)[4], int t) {
     const bool upper = t & 2;
@@ -369,11 +383,13 @@ struct XImage {
     float* xsc;
     int32_t* xsum;
 };
+// The second half starts an odd multiple of 64 bytes behind the first (xh_off): lane groups that read the
+// halves in opposite order (unit_terms) then touch different banks.
 __device__ __forceinline__ XImage ximage(unsigned char* scratch, uint32_t nbp_max) {
     XImage x;
     x.xl = reinterpret_cast<uint4*>(scratch);
-    x.xh = x.xl + nbp_max;
-    x.xsc = reinterpret_cast<float*>(x.xh + nbp_max);
+    x.xh = x.xl + sh().p.xh_off;
+    x.xsc = reinterpret_cast<float*>(x.xl + 2 * nbp_max + 8);
     x.xsum = reinterpret_cast<int32_t*>(x.xsc + nbp_max);
     return x;
 }
@@ -487,55 +503,48 @@ __device__ __noinline__ void norm_quant(const unsigned long long* src, uint32_t 
     image_padding(c, x, dim >> 5, (dim / 32 + 3u) & ~3u);
 }
 
-__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    // rows 8..15 of the 16-row tile are not used: their fragments (a1, a3) are zero
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%6,%5,%6}, {%7,%8}, "
-                 "{%6,%6,%6,%6};"
-                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-                 : "r"(a0), "r"(a2), "r"(0), "r"(b0), "r"(b1));
-}
-
-// Block terms of one unit: up to 8 rows x `nqc` quads of weights in shared memory against quads
-// [q_first, q_first + nqc) of the activation image. The exact int32 dot of a block comes from ONE int8
-// tensor-core instruction (mma.sync m16n8k32: A = the 32 weights of that block for the eight rows, one row
-// per lane group; B = the block's 32 activations, the same in every column), so that every lane (g, t) holds
-// the dots of row g for all four blocks of the quad and keeps block t's. No shuffles, a fifth of the
-// instructions of the dp4a form. Terms land at terms[row * pitch + 4 * (q_term + quad_in_piece) + t].
+// Block terms of one unit: up to 8 rows of weights in shared memory against the activation image, for quads
+// [q_lo, q_hi) of the piece (the piece starts at quad q_first of the row). Lane (g, t) holds word t (and, for
+// q8_0, word 4 + t) of the four blocks of a quad of row g: one 128-bit load each; its dp4a partial dots of the
+// four blocks meet the other three lanes' in a 4 x 4 transpose-and-add (three shuffles), after which lane t
+// holds the exact int32 dot of block t. (The int8 mma.sync form of the same step was measured 1.5 x slower on
+// this part: 56 cycles per instruction.) The eight rows of a q8_0 unit lie a multiple of 128 bytes apart, so
+// odd row groups read their two halves in the opposite order (and the activation halves with them): the row
+// segments of one load then cover all 32 banks. Terms land at terms[row * pitch + 4 * (q_term + q) + t].
 template <int TYPE>
 __device__ __forceinline__ void unit_terms(const unsigned char* slab_q, uint32_t q_pitch, const unsigned char* slab_s,
-                                           uint32_t s_pitch, uint32_t rows, uint32_t nqc, uint32_t q_first, uint32_t q_begin,
-                                           uint32_t q_step, uint32_t q_term, const XImage& x, float* terms, uint32_t pitch,
-                                           int lane) {
+                                           uint32_t s_pitch, uint32_t rows, uint32_t q_lo, uint32_t q_hi, uint32_t q_first,
+                                           uint32_t q_term, const XImage& x, float* terms, uint32_t pitch, int lane) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr bool Q41 = TYPE == ZQ_TYPE_Q4_1;
     constexpr uint32_t QUAD = Q8 ? 128 : 64;
     const int t = lane & 3;
     const uint32_t g = (uint32_t)lane >> 2;
     const uint32_t gr = g < rows ? g : 0u;  // lane groups beyond the unit's rows repeat row 0 (their terms are not read)
+    const uint32_t sw = Q8 ? (g & 1u) * 64u : 0u;
     const unsigned char* wrow = slab_q + (size_t)gr * q_pitch + 16 * t;
     const unsigned char* srow = slab_s + (size_t)gr * s_pitch;
+    const uint4* xa = (Q8 && (g & 1u)) ? x.xh : x.xl;
+    const uint4* xb = (Q8 && (g & 1u)) ? x.xl : x.xh;
     float* trow = terms + g * pitch;
-#pragma unroll 4
-    for (uint32_t q = q_begin; q < nqc; q += q_step) {  // quads q_begin, q_begin + q_step, ... of the piece
-        const uint4 wa = *reinterpret_cast<const uint4*>(wrow + q * QUAD);
+#pragma unroll 2
+    for (uint32_t q = q_lo; q < q_hi; ++q) {
+        const uint4 wa = *reinterpret_cast<const uint4*>(wrow + q * QUAD + sw);
         uint4 wb = wa;
-        if (Q8) wb = *reinterpret_cast<const uint4*>(wrow + q * QUAD + 64);
-        const uint4 xlo = x.xl[(q_first + q) * 4 + t], xhi = x.xh[(q_first + q) * 4 + t];
-        int acc[4][4];
+        if (Q8) wb = *reinterpret_cast<const uint4*>(wrow + q * QUAD + 64 - sw);
+        const uint4 x0 = xa[(q_first + q) * 4 + t], x1 = xb[(q_first + q) * 4 + t];
+        int part[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            uint32_t a0, a2;
             if (Q8) {
-                a0 = pick(wa, j);
-                a2 = pick(wb, j);
+                part[j] = __dp4a((int)pick(wa, j), (int)pick(x0, j), __dp4a((int)pick(wb, j), (int)pick(x1, j), 0));
             } else {
                 const uint32_t u = pick(wa, j);
-                a0 = u & 0x0F0F0F0Fu;
-                a2 = (u >> 4) & 0x0F0F0F0Fu;
+                part[j] = __dp4a((int)(u & 0x0F0F0F0Fu), (int)pick(x0, j),
+                                 __dp4a((int)((u >> 4) & 0x0F0F0F0Fu), (int)pick(x1, j), 0));
             }
-            mma_s8(acc[j], a0, a2, pick(xlo, j), pick(xhi, j));
         }
-        int idot = t == 0 ? acc[0][0] : t == 1 ? acc[1][0] : t == 2 ? acc[2][0] : acc[3][0];
+        int idot = quad_transpose_reduce(part, t);
         const uint32_t bl = q * 4 + t, blk = (q_first + q) * 4 + t;
         float d, m = 0.0f;
         if (Q41) {
@@ -579,7 +588,7 @@ struct UnitGeom {
 __device__ __forceinline__ UnitGeom unit_geom(const DMat& m, uint32_t tile, uint32_t ch) {
     UnitGeom u;
     const uint32_t R = m.rows_per_tile, nq = m.nbp >> 2;
-    const uint32_t QUAD = m.type == ZQ_TYPE_Q8_0 ? 128u : 64u, SB = m.type == ZQ_TYPE_Q4_1 ? 4u : 2u;
+    const uint32_t SB = m.type == ZQ_TYPE_Q4_1 ? 4u : 2u;
     if (m.split) {
         const uint32_t half = R >> 1, n_half = m.n_rows >> 1;
         u.row0 = tile * half;
@@ -596,7 +605,7 @@ __device__ __forceinline__ UnitGeom unit_geom(const DMat& m, uint32_t tile, uint
         u.s_off = u.rows * m.row_q_bytes;
         u.s_delta = 0;
     } else {
-        u.q_pitch = m.chunk_quads * QUAD;
+        u.q_pitch = m.chunk_q_pitch;
         const uint32_t so = u.q_first * 4 * SB;
         u.s_delta = so & 15u;
         u.s_pitch = ((m.chunk_quads * 4 * SB + 15u) & ~15u) + 16u;
@@ -633,25 +642,51 @@ __device__ __forceinline__ void unit_terms_any(uint32_t type, A... a) {
     else if (type == ZQ_TYPE_Q4_0) unit_terms<ZQ_TYPE_Q4_0>(a...);
     else unit_terms<ZQ_TYPE_Q4_1>(a...);
 }
-// Sum of `n` terms in order, added onto `run`; the next four terms are loaded while these four are added.
+// Sum of `n` terms in order, added onto `run` (tr 16-byte aligned). A dependent add takes four cycles and a
+// shared-memory load about thirty: sixteen terms are added while the next sixteen are on their way.
 __device__ __forceinline__ float ordered_sum(float run, const float* tr, uint32_t n) {
+    const float4* t4 = reinterpret_cast<const float4*>(tr);
     uint32_t b = 0;
-    if (n >= 4) {
-        float4 a = *reinterpret_cast<const float4*>(tr);
+#define ZQ_ADD4(v)                  \
+    run = __fadd_rn(run, (v).x);    \
+    run = __fadd_rn(run, (v).y);    \
+    run = __fadd_rn(run, (v).z);    \
+    run = __fadd_rn(run, (v).w)
+    if (n >= 16) {
+        float4 a0 = t4[0], a1 = t4[1], a2 = t4[2], a3 = t4[3];
 #pragma unroll 1
-        for (b = 4; b + 4 <= n; b += 4) {
-            const float4 n4 = *reinterpret_cast<const float4*>(tr + b);
-            run = __fadd_rn(run, a.x);
-            run = __fadd_rn(run, a.y);
-            run = __fadd_rn(run, a.z);
-            run = __fadd_rn(run, a.w);
-            a = n4;
+        for (b = 16; b + 16 <= n; b += 16) {
+            const float4 n0 = t4[(b >> 2)], n1 = t4[(b >> 2) + 1], n2 = t4[(b >> 2) + 2], n3 = t4[(b >> 2) + 3];
+            ZQ_ADD4(a0);
+            ZQ_ADD4(a1);
+            ZQ_ADD4(a2);
+            ZQ_ADD4(a3);
+            a0 = n0;
+            a1 = n1;
+            a2 = n2;
+            a3 = n3;
         }
-        run = __fadd_rn(run, a.x);
-        run = __fadd_rn(run, a.y);
-        run = __fadd_rn(run, a.z);
-        run = __fadd_rn(run, a.w);
+        // the tail's loads (up to three vectors and three scalars) go out before the last sixteen adds
+        const uint32_t rest = n - b;
+        float4 r0 = make_float4(0.f, 0.f, 0.f, 0.f), r1 = r0, r2 = r0;
+        if (rest >= 4) r0 = t4[(b >> 2)];
+        if (rest >= 8) r1 = t4[(b >> 2) + 1];
+        if (rest >= 12) r2 = t4[(b >> 2) + 2];
+        ZQ_ADD4(a0);
+        ZQ_ADD4(a1);
+        ZQ_ADD4(a2);
+        ZQ_ADD4(a3);
+        if (rest >= 4) { ZQ_ADD4(r0); b += 4; }
+        if (rest >= 8) { ZQ_ADD4(r1); b += 4; }
+        if (rest >= 12) { ZQ_ADD4(r2); b += 4; }
+    } else {
+#pragma unroll 1
+        for (; b + 4 <= n; b += 4) {
+            const float4 a = t4[b >> 2];
+            ZQ_ADD4(a);
+        }
     }
+#undef ZQ_ADD4
 #pragma unroll 1
     for (; b < n; ++b) run = __fadd_rn(run, tr[b]);
     return run;
@@ -660,10 +695,14 @@ __device__ __forceinline__ float ordered_sum(float run, const float* tr, uint32_
 // One matrix-vector phase: this CTA's tiles of `m` (tile = cta, cta + grid, ...). The activation image is
 // complete (cbar) before the call. Outputs leave as exchange words (EP_VECTOR, EP_GEGLU) or as plain f32 logits
 // (EP_LOGITS). Block terms are added onto a row's sum in block order, as the CPU loop does. Two forms:
-//   * few tiles per CTA (the layer matrices): all 16 warps share every unit — the quads of the CTA's units are
-//     dealt round the warps, so a warp runs one or a few tensor-core steps instead of a whole row's worth —
-//     the terms meet in a CTA-wide buffer, and after a barrier one thread per row adds them up;
+//   * few units per CTA (the layer matrices): the quads of all the CTA's units, taken as one sequence, are cut
+//     into 16 equal runs, one per warp; a warp touches only the one or two units its run lies in, the terms meet
+//     in a CTA-wide buffer, and after a barrier one thread per row adds them up. A unit's 16 slot-release
+//     arrivals are shared out among the warps that read it: a warp whose run covers quads [lo, hi) of a unit of
+//     n quads (n <= 16) arrives with f(hi) - f(lo), f(x) = x below n and 16 at n, which adds up to 16 whatever
+//     the cut;
 //   * many tiles (the vocabulary head): one warp per tile, pieces and sums warp-private, no barrier.
+// Loop counters instead of divisions throughout: a 32-bit division costs 65-95 cycles on this part.
 // Returns the advanced unit counter.
 __device__ __noinline__ uint32_t gemv_phase(const DMat& m, uint32_t unit_base, int ep, unsigned long long* xout,
                                             uint32_t epoch, float* out, Best* best) {
@@ -672,43 +711,51 @@ __device__ __noinline__ uint32_t gemv_phase(const DMat& m, uint32_t unit_base, i
     const XImage x = ximage(c.smem + p.off_scratch, p.nbp_max);
     float* terms_all = reinterpret_cast<float*>(x.xsum + p.nbp_max);
     const uint32_t G = gridDim.x, cta = blockIdx.x;
-    const uint32_t n_tiles = m.n_tiles, C = m.chunks;
-    const uint32_t mine = n_tiles > cta ? (n_tiles - cta - 1) / G + 1 : 0;
+    const uint32_t C = m.chunks;
+    const uint32_t mine = m.tiles_div + (cta < m.tiles_rem ? 1u : 0u);
     const uint32_t base = unit_base;
     const uint32_t type = m.type;
+    const uint32_t n_slots = p.n_slots, slot_magic = p.slot_magic;
     const uint32_t row_pitch = m.nbp + 4;  // terms of a whole row
-    // Sharing a unit costs every warp its wait / release bookkeeping: worth it only for a handful of units.
-    if (mine * C <= 8 && mine * 8 * row_pitch * 4 <= p.terms_bytes) {
-        // ---- all warps on every unit
-        uint32_t dealt = 0;  // quads dealt so far: quad j of the phase goes to warp j % 16
+    const uint32_t nq = m.nbp >> 2, cq = m.chunk_quads;
+    if (mine * C <= p.deal_limit && mine * 8 * row_pitch * 4 <= p.terms_bytes) {
+        // ---- all warps share the phase's quads
+        const uint32_t total = mine * nq;
+        const uint32_t run_lo = ((uint32_t)c.warp * total) >> 4, run_hi = (((uint32_t)c.warp + 1u) * total) >> 4;
+        uint32_t i = 0, ch = 0, us = 0;  // tile, piece, first quad of the unit in the phase's sequence
         bool live = true;
 #pragma unroll 1
-        for (uint32_t n = 0; live && n < mine * C; ++n) {
-            const uint32_t i = n / C, ch = n - i * C;
-            const uint32_t gi = base + n, slot = gi % p.n_slots, use = gi / p.n_slots;
-            const UnitGeom u = unit_geom(m, cta + i * G, ch);
-            const uint32_t first = ((uint32_t)c.warp + kConsumerWarps - (dealt % kConsumerWarps)) % kConsumerWarps;
-            // Every warp waits for the unit, also one without a quad in it: its arrival below must not reach the
-            // slot's barrier before the arrivals of the slot's previous use are complete.
-            if (!unit_acquire(c, p, slot, use)) {
-                live = false;
-                break;
-            }
-            if (first < u.nqc) {
+        for (uint32_t n = 0; n < mine * C; ++n) {
+            const uint32_t q_first = ch * cq;
+            const uint32_t nqc = min(cq, nq - q_first);
+            const uint32_t ue = us + nqc;
+            if (run_lo < ue && run_hi > us) {
+                const uint32_t lo = max(run_lo, us) - us, hi = min(run_hi, ue) - us;
+                uint32_t slot, use;
+                fast_divmod(base + n, n_slots, slot_magic, use, slot);
+                const UnitGeom u = unit_geom(m, cta + i * G, ch);
+                if (!unit_acquire(c, p, slot, use)) {
+                    live = false;
+                    break;
+                }
                 const unsigned char* slab_q = c.smem + p.off_ring + (size_t)slot * p.slot_bytes;
-                unit_terms_any(type, slab_q, u.q_pitch, slab_q + u.s_off + u.s_delta, u.s_pitch, u.rows, u.nqc, u.q_first,
-                               first, (uint32_t)kConsumerWarps, u.q_first, x, terms_all + (size_t)i * 8 * row_pitch, row_pitch,
-                               c.lane);
+                unit_terms_any(type, slab_q, u.q_pitch, slab_q + u.s_off + u.s_delta, u.s_pitch, u.rows, lo, hi, q_first,
+                               q_first, x, terms_all + (size_t)i * 8 * row_pitch, row_pitch, c.lane);
+                unit_release(c, slot, use, (hi == nqc ? (uint32_t)kConsumerWarps : hi) - lo);
             }
-            unit_release(c, slot, use, 1);
-            dealt += u.nqc;
+            us = ue;
+            if (++ch == C) {
+                ch = 0;
+                ++i;
+            }
         }
+        (void)live;
         cbar();  // every term of the phase is in the buffer
         const uint32_t nb = m.nb;
 #pragma unroll 1
         for (uint32_t r = c.tid; r < mine * 8; r += kConsumers) {
-            const uint32_t i = r >> 3, g = r & 7u;
-            const UnitGeom u = unit_geom(m, cta + i * G, 0);
+            const uint32_t ti = r >> 3, g = r & 7u;
+            const UnitGeom u = unit_geom(m, cta + ti * G, 0);
             const float* tr = terms_all + (size_t)r * row_pitch;
             if (ep == EP_GEGLU) {
                 const uint32_t half = u.rows >> 1;
@@ -730,7 +777,7 @@ __device__ __noinline__ uint32_t gemv_phase(const DMat& m, uint32_t unit_base, i
         return base + mine * C;
     }
     // ---- one warp per tile
-    const uint32_t pitch = m.chunk_quads * 4 + 4;
+    const uint32_t pitch = cq * 4 + 4;
     float* terms = terms_all + (size_t)c.warp * p.terms_per_warp;
     bool live = true;
 #pragma unroll 1
@@ -740,7 +787,8 @@ __device__ __noinline__ uint32_t gemv_phase(const DMat& m, uint32_t unit_base, i
         uint32_t rows = 0, row0 = 0;
 #pragma unroll 1
         for (uint32_t ch = 0; ch < C; ++ch) {
-            const uint32_t gi = base + i * C + ch, slot = gi % p.n_slots, use = gi / p.n_slots;
+            uint32_t slot, use;
+            fast_divmod(base + i * C + ch, n_slots, slot_magic, use, slot);
             const UnitGeom u = unit_geom(m, tile, ch);
             rows = u.rows;
             row0 = u.row0;
@@ -749,8 +797,8 @@ __device__ __noinline__ uint32_t gemv_phase(const DMat& m, uint32_t unit_base, i
                 break;
             }
             const unsigned char* slab_q = c.smem + p.off_ring + (size_t)slot * p.slot_bytes;
-            unit_terms_any(type, slab_q, u.q_pitch, slab_q + u.s_off + u.s_delta, u.s_pitch, rows, u.nqc, u.q_first, 0u, 1u,
-                           0u, x, terms, pitch, c.lane);
+            unit_terms_any(type, slab_q, u.q_pitch, slab_q + u.s_off + u.s_delta, u.s_pitch, rows, 0u, u.nqc, u.q_first, 0u, x,
+                           terms, pitch, c.lane);
             unit_release(c, slot, use, (uint32_t)kConsumerWarps);
             if ((uint32_t)c.lane < rows)
                 run = ordered_sum(run, terms + c.lane * pitch, min(u.nqc * 4, m.nb - u.q_first * 4));
@@ -778,20 +826,22 @@ __device__ __noinline__ bool produce_phase(const DMat& m, uint32_t* unit_base,
                                            uint32_t* issued) {
     const Cta c = make_cta();
     const DParams& p = sh().p;
-    (void)p;
     const uint32_t G = gridDim.x, cta = blockIdx.x;
     const uint32_t C = m.chunks;
-    const uint32_t mine = m.n_tiles > cta ? (m.n_tiles - cta - 1) / G + 1 : 0;
+    const uint32_t mine = m.tiles_div + (cta < m.tiles_rem ? 1u : 0u);
     const uint32_t base = *unit_base;
     *unit_base = base + mine * C;
     const uint32_t rqb = m.row_q_bytes, rsb = m.row_s_bytes, N = m.n_rows;
     const uint32_t QUAD = m.type == ZQ_TYPE_Q8_0 ? 128u : 64u, SB = m.type == ZQ_TYPE_Q4_1 ? 4u : 2u;
+    const uint32_t n_slots = p.n_slots, slot_magic = p.slot_magic;
     const uint8_t* qs = m.qs;
     const uint8_t* sc = m.sc;
+    uint32_t i = 0, ch = 0;
 #pragma unroll 1
     for (uint32_t n = 0; n < mine * C; ++n) {
-        const uint32_t i = n / C, ch = n - i * C;
-        const uint32_t gi = base + n, slot = gi % p.n_slots, use = gi / p.n_slots;
+        const uint32_t gi = base + n;
+        uint32_t slot, use;
+        fast_divmod(gi, n_slots, slot_magic, use, slot);
         const uint32_t tile = cta + i * G;
         if (use > 0 && !slot_wait(c, p, c.empty0 + slot * 8, (use - 1) & 1u)) return false;
         const uint32_t dst = c.smem32 + p.off_ring + slot * p.slot_bytes;
@@ -818,14 +868,19 @@ __device__ __noinline__ bool produce_phase(const DMat& m, uint32_t* unit_base,
             const uint32_t so = u.q_first * 4 * SB, sa = so & ~15u;
             const uint32_t sbytes = ((u.s_delta + u.nqc * 4 * SB + 15u) & ~15u);
             mbar_arrive_expect_tx(bar, u.rows * (qbytes + sbytes));
+            const uint32_t half = u.rows >> 1;
+#pragma unroll 1
             for (uint32_t r = 0; r < u.rows; ++r) {
-                const uint32_t half = u.rows >> 1;
                 const size_t row = m.split ? (r < half ? u.row0 + r : (N >> 1) + u.row0 + (r - half)) : u.row0 + r;
                 bulk_copy_g2s(dst + r * u.q_pitch, qs + row * rqb + (size_t)u.q_first * QUAD, qbytes, bar);
                 bulk_copy_g2s(dst + u.s_off + r * u.s_pitch, sc + row * rsb + sa, sbytes, bar);
             }
         }
         *issued = gi + 1;
+        if (++ch == C) {
+            ch = 0;
+            ++i;
+        }
     }
     return true;
 }
@@ -1359,7 +1414,7 @@ bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split, uint
     d->nbp = w->nbp;
     d->row_q_bytes = w->nbp * w->qb;
     d->row_s_bytes = w->scp * (w->type == ZQ_TYPE_Q4_1 ? 4u : 2u);
-    d->pad_ = 0;
+    d->pad_[0] = d->pad_[1] = 0;
     d->split = split ? 1u : 0u;
     if (split && (w->out_dim & 1u)) return false;
     const uint32_t n = split ? w->out_dim / 2 : w->out_dim;  // rows to hand out (pairs of rows when split)
@@ -1368,16 +1423,24 @@ bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split, uint
     while (r > (split ? 2u : 1u) && tiles(r) < grid / 2) r /= 2;
     d->rows_per_tile = r;
     d->n_tiles = tiles(r);
+    d->tiles_div = d->n_tiles / grid;
+    d->tiles_rem = d->n_tiles % grid;
     const uint32_t QUAD = w->qb * 4, SB = w->type == ZQ_TYPE_Q4_1 ? 4u : 2u, nq = w->nbp / 4;
-    if (r * (d->row_q_bytes + d->row_s_bytes) <= slot_bytes) {
+    // A piece has at most 16 quads (the shared slot release of gemv_phase counts on it). Rows of a piece of a
+    // 4-bit matrix lie an odd multiple of 64 bytes apart, so that the eight row segments of one load cover all banks.
+    auto q_pitch = [&](uint32_t cq) { return cq * QUAD + ((QUAD == 64 && !(cq & 1u)) ? 64u : 0u); };
+    auto piece_bytes = [&](uint32_t cq) { return r * (q_pitch(cq) + ((cq * 4 * SB + 15u) & ~15u) + 16u); };
+    if (nq <= 16 && r * (d->row_q_bytes + d->row_s_bytes) <= slot_bytes) {
         d->chunks = 1;
         d->chunk_quads = nq;
+        d->chunk_q_pitch = d->row_q_bytes;
     } else {
-        uint32_t cq = nq;
-        while (cq > 1 && r * (cq * QUAD + ((cq * 4 * SB + 15u) & ~15u) + 16u) > slot_bytes) --cq;
-        if (r * (cq * QUAD + ((cq * 4 * SB + 15u) & ~15u) + 16u) > slot_bytes) return false;
+        uint32_t cq = nq < 16 ? nq : 16;
+        while (cq > 1 && piece_bytes(cq) > slot_bytes) --cq;
+        if (piece_bytes(cq) > slot_bytes) return false;
         d->chunk_quads = cq;
         d->chunks = (nq + cq - 1) / cq;
+        d->chunk_q_pitch = q_pitch(cq);
     }
     return true;
 }
@@ -1432,8 +1495,8 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
         row_bytes(L.gate_up);
         row_bytes(L.down);
     }
-    uint32_t slot_bytes = desc.slot_bytes ? desc.slot_bytes : 9984u;
-    slot_bytes = (slot_bytes + 255u) & ~255u;
+    uint32_t slot_bytes = desc.slot_bytes ? desc.slot_bytes : 9856u;
+    slot_bytes = (slot_bytes + 127u) & ~127u;
 
     GemmaDecoder* d = new (std::nothrow) GemmaDecoder;
     if (!d) return ZQ_ERR_NO_MEM;
@@ -1496,7 +1559,9 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
     if (after_image < (size_t)16 * kConsumers * 4) after_image = (size_t)16 * kConsumers * 4;  // staging of the quantiser
     if (after_image < (size_t)2 * E * 4) after_image = (size_t)2 * E * 4;      // norm weights
     p.terms_bytes = (uint32_t)after_image;
-    const size_t gemv_scratch = (size_t)nbp_max * (32 + 8) + after_image;
+    const size_t gemv_scratch = (size_t)nbp_max * (32 + 8) + 128 + after_image;
+    p.xh_off = nbp_max + (((nbp_max * 16u) & 127u) == 64u ? 0u : 4u);
+    p.deal_limit = desc.deal_limit ? desc.deal_limit : 8u;
     const size_t att_a = (size_t)(nh + nkv) * D * 4;
     const size_t att_b = (size_t)group * desc.ctx * 4 + 2 * (size_t)kVTile * 32;
     size_t scratch = gemv_scratch > att_a ? gemv_scratch : att_a;
@@ -1524,6 +1589,7 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
     if (n_slots > 64) n_slots = 64;
     if (desc.n_slots && desc.n_slots >= 8 && desc.n_slots <= n_slots) n_slots = desc.n_slots;
     p.n_slots = n_slots;
+    p.slot_magic = (uint32_t)(0x100000000ull / n_slots);
     p.slot_bytes = slot_bytes;
     d->smem = off + (size_t)n_slots * slot_bytes;
 

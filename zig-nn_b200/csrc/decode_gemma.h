@@ -27,6 +27,7 @@ struct GemmaDecoderDesc {
     float* logits;
     uint32_t *state, *record;
     uint32_t slot_bytes = 0, n_slots = 0;  // 0: chosen by the decoder
+    uint32_t deal_limit = 0;               // units per CTA and phase up to which all warps share every unit (0: default)
 };
 
 struct GemmaDecoder;
