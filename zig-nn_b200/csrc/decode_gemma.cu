@@ -46,6 +46,10 @@ constexpr unsigned int kErrUnitWait = 0x554E4954u;  // 'UNIT'
 constexpr uint32_t kPollLimit = 1u << 21;
 constexpr uint32_t kSlotSpinLimit = 1u << 22;
 constexpr uint32_t kVTile = 256;   // positions per V tile of the attention phase
+// Serial chains (ordered sums) run on warp 1, not warp 0: the producer warp (16) shares warp 0's scheduler, and
+// its polling takes issue slots that a chain of dependent adds feels one for one.
+constexpr int kChainWarp = 1;
+constexpr int kChainTid = kChainWarp * 32;
 
 enum { EP_VECTOR = 0, EP_GEGLU = 1, EP_LOGITS = 2 };
 
@@ -100,6 +104,8 @@ struct DParams {
     uint32_t terms_bytes;  // bytes behind the activation image: block terms, staging of the prologues
     uint32_t deal_limit;   // a phase with at most this many units per CTA shares every unit among all warps
     uint32_t xh_off;       // second half of the activation image, in 16-byte words from the first
+    uint32_t group, half_d;  // query heads per kv head; D / 2
+    uint32_t magic_chunks, magic_group, magic_half, magic_nh;  // floor(2^32 / x) for fast_divmod: D / 8, group, D / 2, n_head
 };
 
 // ---- small device helpers --------------------------------------------------------------------
@@ -312,39 +318,40 @@ __device__ __forceinline__ bool slot_wait(const Cta& c, const DParams& p, uint32
 // then the tail. `xs` complete before the call (a cbar lies between its writes and this call).
 __device__ __forceinline__ float sumsq_lanes16(const Cta& c, const float* xs, uint32_t dim) {
     const uint32_t dim16 = dim & ~15u;
-    if (c.tid < 16) {
+    if (c.warp == kChainWarp) {
         float acc = 0.0f;
-        uint32_t i = c.tid;
-        if (i + 16 * 7 < dim16) {  // loads and squares of the next eight elements run under the adds of these
-            float v[8];
+        uint32_t i = c.lane;
+        if (c.lane < 16) {
+            if (i + 16 * 7 < dim16) {  // loads and squares of the next eight elements run under the adds of these
+                float v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = xs[i + 16 * u];
-            i += 16 * 8;
+                for (int u = 0; u < 8; ++u) v[u] = xs[i + 16 * u];
+                i += 16 * 8;
 #pragma unroll 1
-            for (; i + 16 * 7 < dim16; i += 16 * 8) {
-                float n[8];
+                for (; i + 16 * 7 < dim16; i += 16 * 8) {
+                    float n[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) n[u] = xs[i + 16 * u];
+                    for (int u = 0; u < 8; ++u) n[u] = xs[i + 16 * u];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, __fmul_rn(v[u], v[u]));
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) v[u] = n[u];
+                }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, __fmul_rn(v[u], v[u]));
-#pragma unroll
-                for (int u = 0; u < 8; ++u) v[u] = n[u];
             }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, __fmul_rn(v[u], v[u]));
+#pragma unroll 1
+            for (; i < dim16; i += 16) acc = __fadd_rn(acc, __fmul_rn(xs[i], xs[i]));
         }
-#pragma unroll 1
-        for (; i < dim16; i += 16) acc = __fadd_rn(acc, __fmul_rn(xs[i], xs[i]));
-        c.part[c.tid] = acc;
-    }
-    cbar();
-    if (c.tid == 0) {
-        float ss = c.part[0];
+        // the 16 lane sums in lane order (every lane of the warp forms the same total), then the tail
+        float ss = __shfl_sync(0xFFFFFFFFu, acc, 0);
 #pragma unroll
-        for (int l = 1; l < 16; ++l) ss = __fadd_rn(ss, c.part[l]);
+        for (int l = 1; l < 16; ++l) ss = __fadd_rn(ss, __shfl_sync(0xFFFFFFFFu, acc, l));
+        if (c.lane == 0) {
 #pragma unroll 1
-        for (uint32_t i = dim16; i < dim; ++i) ss = __fadd_rn(ss, __fmul_rn(xs[i], xs[i]));
-        *c.bc = ss;
+            for (uint32_t k = dim16; k < dim; ++k) ss = __fadd_rn(ss, __fmul_rn(xs[k], xs[k]));
+            *c.bc = ss;
+        }
     }
     cbar();
     return *c.bc;
@@ -643,7 +650,8 @@ __device__ __forceinline__ void unit_terms_any(uint32_t type, A... a) {
     else unit_terms<ZQ_TYPE_Q4_1>(a...);
 }
 // Sum of `n` terms in order, added onto `run` (tr 16-byte aligned). A dependent add takes four cycles and a
-// shared-memory load about thirty: sixteen terms are added while the next sixteen are on their way.
+// shared-memory load about thirty: sixteen terms are added while the next sixteen are on their way, in two
+// register sets that take turns (no copies between them).
 __device__ __forceinline__ float ordered_sum(float run, const float* tr, uint32_t n) {
     const float4* t4 = reinterpret_cast<const float4*>(tr);
     uint32_t b = 0;
@@ -653,20 +661,38 @@ __device__ __forceinline__ float ordered_sum(float run, const float* tr, uint32_
     run = __fadd_rn(run, (v).z);    \
     run = __fadd_rn(run, (v).w)
     if (n >= 16) {
-        float4 a0 = t4[0], a1 = t4[1], a2 = t4[2], a3 = t4[3];
+        float4 a0 = t4[0], a1 = t4[1], a2 = t4[2], a3 = t4[3];  // terms [b - 16, b): loaded, not yet added
+        b = 16;
 #pragma unroll 1
-        for (b = 16; b + 16 <= n; b += 16) {
-            const float4 n0 = t4[(b >> 2)], n1 = t4[(b >> 2) + 1], n2 = t4[(b >> 2) + 2], n3 = t4[(b >> 2) + 3];
+        while (b + 32 <= n) {
+            const float4 c0 = t4[(b >> 2)], c1 = t4[(b >> 2) + 1], c2 = t4[(b >> 2) + 2], c3 = t4[(b >> 2) + 3];
             ZQ_ADD4(a0);
             ZQ_ADD4(a1);
             ZQ_ADD4(a2);
             ZQ_ADD4(a3);
-            a0 = n0;
-            a1 = n1;
-            a2 = n2;
-            a3 = n3;
+            a0 = t4[(b >> 2) + 4];
+            a1 = t4[(b >> 2) + 5];
+            a2 = t4[(b >> 2) + 6];
+            a3 = t4[(b >> 2) + 7];
+            ZQ_ADD4(c0);
+            ZQ_ADD4(c1);
+            ZQ_ADD4(c2);
+            ZQ_ADD4(c3);
+            b += 32;
         }
-        // the tail's loads (up to three vectors and three scalars) go out before the last sixteen adds
+        if (b + 16 <= n) {
+            const float4 c0 = t4[(b >> 2)], c1 = t4[(b >> 2) + 1], c2 = t4[(b >> 2) + 2], c3 = t4[(b >> 2) + 3];
+            ZQ_ADD4(a0);
+            ZQ_ADD4(a1);
+            ZQ_ADD4(a2);
+            ZQ_ADD4(a3);
+            a0 = c0;
+            a1 = c1;
+            a2 = c2;
+            a3 = c3;
+            b += 16;
+        }
+        // the tail's loads (up to three vectors) go out before the last sixteen adds
         const uint32_t rest = n - b;
         float4 r0 = make_float4(0.f, 0.f, 0.f, 0.f), r1 = r0, r2 = r0;
         if (rest >= 4) r0 = t4[(b >> 2)];
@@ -753,7 +779,8 @@ __device__ __noinline__ uint32_t gemv_phase(const DMat& m, uint32_t unit_base, i
         cbar();  // every term of the phase is in the buffer
         const uint32_t nb = m.nb;
 #pragma unroll 1
-        for (uint32_t r = c.tid; r < mine * 8; r += kConsumers) {
+        for (uint32_t r = (uint32_t)(c.tid >= kChainTid ? c.tid - kChainTid : c.tid + kConsumers - kChainTid); r < mine * 8;
+             r += kConsumers) {  // rows start on warp 1 (kChainWarp)
             const uint32_t ti = r >> 3, g = r & 7u;
             const UnitGeom u = unit_geom(m, cta + ti * G, 0);
             const float* tr = terms_all + (size_t)r * row_pitch;
@@ -928,16 +955,17 @@ __device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
     const Cta c = make_cta();
     const DParams& p = sh().p;
     (void)p;
-    const uint32_t D = p.D, nh = p.n_head, nkv = p.n_kv, group = nh / nkv, kv_dim = nkv * D;
+    const uint32_t D = p.D, nh = p.n_head, nkv = p.n_kv, group = p.group, kv_dim = nkv * D;
     const uint32_t nvec = nh + nkv, nqk = nvec * D, nall = nqk + kv_dim;
     // norm weights of the pairs this thread rotates: requested before the exchange is polled
-    const uint32_t half = D / 2, pairs = nvec * half;
+    const uint32_t half = p.half_d, pairs = nvec * half;
     float2 nw[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
         const uint32_t i = c.tid + u * kConsumers;
         if (i < pairs) {
-            const uint32_t v = i / half, j = i - v * half;
+            uint32_t v, j;
+            fast_divmod(i, half, p.magic_half, v, j);
             nw[u] = __ldg(reinterpret_cast<const float2*>(v < nh ? L.q_norm_w : L.k_norm_w) + j);
         } else {
             nw[u] = make_float2(0.0f, 0.0f);
@@ -957,14 +985,16 @@ __device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
     cbar();
     const bool leave = *c.s_abort != 0;  // uniform: read between two barriers that every thread passes
 #pragma unroll 1
-    for (uint32_t v = c.warp; v < nvec; v += kConsumerWarps)  // one chain per vector, one warp each
-        if (c.lane == 0)
+    // one chain per vector, one warp each; warps 1, 2, 3, 5, 6, 7, ... first (not on the producer's scheduler)
+    for (uint32_t v = 0; v < nvec; ++v)
+        if (c.lane == 0 && (uint32_t)c.warp == (v < 12 ? v + 1 + v / 3 : (v & 3u) * 4))
             c.red[v & 31u] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq_sequential(qn + v * D, D), (float)D), p.eps)));
     cbar();
     if (leave) return false;
 #pragma unroll 1
     for (uint32_t i = c.tid, u = 0; i < pairs; i += kConsumers, ++u) {
-        const uint32_t v = i / half, j = i - v * half;
+        uint32_t v, j;
+        fast_divmod(i, half, p.magic_half, v, j);
         float2 w;
         if (u < 2) w = u == 0 ? nw[0] : nw[1];
         else w = __ldg(reinterpret_cast<const float2*>(v < nh ? L.q_norm_w : L.k_norm_w) + j);
@@ -984,7 +1014,7 @@ __device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
             L.vc[(size_t)pos * kv_dim + i] = vnew[i];
         }
     }
-    const uint32_t jobs = kv_len * nh, tiles = (jobs + 31) / 32;
+    const uint32_t jobs = kv_len * nh, tiles = (jobs + 31) >> 5;
     const uint32_t l = c.tid & 15u, js = c.tid >> 4;
     const uint32_t dim16 = D & ~15u;
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)D));
@@ -993,7 +1023,9 @@ __device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
         const uint32_t job = tile * 32 + js;
         const bool live = job < jobs;
         const uint32_t jc = live ? job : jobs - 1;
-        const uint32_t pi = jc / nh, h = jc - pi * nh, kvh = h / group;
+        uint32_t pi, h, kvh, hrem;
+        fast_divmod(jc, nh, p.magic_nh, pi, h);
+        fast_divmod(h, group, p.magic_group, kvh, hrem);
         const float* qh = qn + h * D;
         const bool from_smem = pi == kv_len - 1;
         const float* kr = from_smem ? qn + (nh + kvh) * D : L.kc + (size_t)(kv_start + pi) * kv_dim + (size_t)kvh * D;
@@ -1025,59 +1057,62 @@ __device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
     return true;
 }
 
-// Attention, second half (gemma3.zig:1092-1120): a job owns 8 output dimensions of one kv head for all the
-// query heads that share it. Softmax per head (maximum, exp, the exponentials added one by one, times
-// 1/sum), then out[d] += w[p] * v[p][d] position by position; V streams through shared memory in tiles, the
-// row of the current position comes from `vnew`. Returns false when the CTA has to leave.
+// Attention, second half (gemma3.zig:1092-1120): a job owns 8 output dimensions of one query head. Softmax of
+// the head (maximum, exp, the exponentials added one by one, times 1/sum), then out[d] += w[p] * v[p][d]
+// position by position. Both are serial chains of one add (4 cycles) per position; everything else is taken
+// off them: the products w[p] * v[p][d] of a tile of positions are formed by warps 1-15 (V rows straight from
+// the cache, the current position's row from `vnew`) into prod[d][p], while eight threads of warp 0 add the
+// previous tile's products in order. Returns false when the CTA has to leave.
 __device__ __noinline__ bool softmax_v_phase(const DLayer& L, uint32_t kv_start,
                                                 uint32_t kv_len, unsigned char* scratch, const float* vnew,
                                                 const unsigned long long* scores_in, uint32_t ep_in,
                                                 unsigned long long* att_out, uint32_t ep_out) {
     const Cta c = make_cta();
     const DParams& p = sh().p;
-    (void)p;
-    const uint32_t D = p.D, nh = p.n_head, nkv = p.n_kv, group = nh / nkv, kv_dim = nkv * D;
-    const uint32_t chunks = D / 8, jobs = nkv * chunks;
-    float* w = reinterpret_cast<float*>(scratch);                      // [group][max_len]
-    float* vt = w + (size_t)group * p.max_len;                         // [2][kVTile][8]
-    const uint32_t vt32 = c.smem32 + (uint32_t)(reinterpret_cast<unsigned char*>(vt) - c.smem);
-    const uint32_t wph = kConsumerWarps / group;                       // warps per head
+    const uint32_t D = p.D, nh = p.n_head, nkv = p.n_kv, kv_dim = nkv * D;
+    const uint32_t chunks = D / 8, jobs = nh * chunks;
+    constexpr uint32_t PITCH = kVTile + 4;                             // 4 mod 32 banks: stores and chain loads conflict-free
+    float* w = reinterpret_cast<float*>(scratch);                      // [max_len]
+    float* prod = w + (((size_t)p.max_len + 3u) & ~(size_t)3u);        // [2][8][PITCH]
     bool ok = true;
 #pragma unroll 1
     for (uint32_t job = blockIdx.x; ok && job < jobs; job += gridDim.x) {
-        const uint32_t kvh = job / chunks, dc = job - kvh * chunks;
+        uint32_t h, dc, kvh, hrem;
+        fast_divmod(job, chunks, p.magic_chunks, h, dc);
+        fast_divmod(h, p.group, p.magic_group, kvh, hrem);
         const float* vbase = L.vc + (size_t)kv_start * kv_dim + (size_t)kvh * D + dc * 8;
-        auto fetch_tile = [&](uint32_t tile) {
+        const float* vcur = vnew + kvh * D + dc * 8;
+        // products of tile `tile` by threads first, first + step, ...: (position, dimension) pairs, dimension fastest
+        auto make_products = [&](uint32_t tile, uint32_t first, uint32_t step) {
             const uint32_t p0 = tile * kVTile, n = min(kVTile, kv_len - p0);
-            const uint32_t dst = vt32 + (tile & 1u) * kVTile * 32;
+            float* dst = prod + (size_t)(tile & 1u) * 8 * PITCH;
 #pragma unroll 1
-            for (uint32_t i = c.tid; i < n * 2; i += kConsumers) {
-                const uint32_t q = p0 + (i >> 1);
-                if (q + 1 < kv_len) {
-                    cp_async16(dst + i * 16, vbase + (size_t)q * kv_dim + (i & 1u) * 4);
-                } else {  // the current position's row: this step's value heads
-                    const float* vs = vnew + kvh * D + dc * 8 + (i & 1u) * 4;
-                    float* vd = vt + (size_t)(tile & 1u) * kVTile * 8 + (size_t)i * 4;
-                    vd[0] = vs[0]; vd[1] = vs[1]; vd[2] = vs[2]; vd[3] = vs[3];
+            for (uint32_t i = first; i < n * 8; i += 4 * step) {
+                float v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t k = i + u * step, q = p0 + (k >> 3), d = k & 7u;
+                    v[u] = k < n * 8 ? (q + 1 < kv_len ? __ldcg(vbase + (size_t)q * kv_dim + d) : vcur[d]) : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t k = i + u * step, pi = k >> 3, d = k & 7u;
+                    if (k < n * 8) dst[d * PITCH + pi] = __fmul_rn(w[p0 + pi], v[u]);
                 }
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        fetch_tile(0);  // in flight during the softmax
         {
-            const uint32_t hg = c.warp / wph, tl = c.tid - hg * wph * 32, nt = wph * 32;
-            const unsigned long long* sh = scores_in + (size_t)(kvh * group + hg) * p.max_len;
-            float* wh = w + (size_t)hg * p.max_len;
+            const unsigned long long* sh_ = scores_in + (size_t)h * p.max_len;
             float mx = -INFINITY;
 #pragma unroll 1
-            for (uint32_t base = 0; base < kv_len; base += nt * 8) {
-                float v[8];
-                xload_batch<8>(c, p, sh, base + tl, nt, kv_len, ep_in, v);
+            for (uint32_t base = 0; base < kv_len; base += kConsumers * 4) {
+                float v[4];
+                xload_batch<4>(c, p, sh_, base + c.tid, kConsumers, kv_len, ep_in, v);
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const uint32_t i = base + u * nt + tl;
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t i = base + u * kConsumers + c.tid;
                     if (i < kv_len) {
-                        wh[i] = v[u];
+                        w[i] = v[u];
                         mx = fmaxf(mx, v[u]);
                     }
                 }
@@ -1086,100 +1121,47 @@ __device__ __noinline__ bool softmax_v_phase(const DLayer& L, uint32_t kv_start,
             if (c.lane == 0) c.red[c.warp] = mx;
             cbar();
             if (*c.s_abort) ok = false;  // uniform: read between two barriers that every thread passes
-            mx = c.red[hg * wph];
+            mx = c.red[0];
+#pragma unroll
+            for (int k = 1; k < kConsumerWarps; ++k) mx = fmaxf(mx, c.red[k]);
+            // up to two exponentials per pass, inlined: their double-precision chains overlap
 #pragma unroll 1
-            for (uint32_t k = 1; k < wph; ++k) mx = fmaxf(mx, c.red[hg * wph + k]);
-            // four exponentials per pass, inlined: the double-precision chains of the four overlap
-#pragma unroll 1
-            for (uint32_t q = tl; q < kv_len; q += 4 * nt) {
-                float e[4];
+            for (uint32_t q = c.tid; q < kv_len; q += 2 * kConsumers) {
+                float e[2];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) e[u] = q + u * nt < kv_len ? wh[q + u * nt] : 0.0f;
+                for (int u = 0; u < 2; ++u) e[u] = q + u * kConsumers < kv_len ? w[q + u * kConsumers] : 0.0f;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) e[u] = (float)exp((double)__fsub_rn(e[u], mx));
+                for (int u = 0; u < 2; ++u) e[u] = (float)exp((double)__fsub_rn(e[u], mx));
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (q + u * nt < kv_len) wh[q + u * nt] = e[u];
+                for (int u = 0; u < 2; ++u)
+                    if (q + u * kConsumers < kv_len) w[q + u * kConsumers] = e[u];
             }
             cbar();
-            if ((uint32_t)c.tid < group) {  // one serial sum per head; the next eight are loaded under the adds
-                const float* wq = w + (size_t)c.tid * p.max_len;
-                float s = 0.0f;
-                uint32_t q = 0;
-                if (kv_len >= 8) {
-                    float4 a = *reinterpret_cast<const float4*>(wq), b = *reinterpret_cast<const float4*>(wq + 4);
-#pragma unroll 1
-                    for (q = 8; q + 8 <= kv_len; q += 8) {
-                        const float4 na = *reinterpret_cast<const float4*>(wq + q);
-                        const float4 nb = *reinterpret_cast<const float4*>(wq + q + 4);
-                        s = __fadd_rn(s, a.x); s = __fadd_rn(s, a.y); s = __fadd_rn(s, a.z); s = __fadd_rn(s, a.w);
-                        s = __fadd_rn(s, b.x); s = __fadd_rn(s, b.y); s = __fadd_rn(s, b.z); s = __fadd_rn(s, b.w);
-                        a = na;
-                        b = nb;
-                    }
-                    s = __fadd_rn(s, a.x); s = __fadd_rn(s, a.y); s = __fadd_rn(s, a.z); s = __fadd_rn(s, a.w);
-                    s = __fadd_rn(s, b.x); s = __fadd_rn(s, b.y); s = __fadd_rn(s, b.z); s = __fadd_rn(s, b.w);
-                }
-#pragma unroll 1
-                for (; q < kv_len; ++q) s = __fadd_rn(s, wq[q]);
-                c.part[c.tid] = __fdiv_rn(1.0f, s);
-            }
+            if (c.tid == kChainTid) c.part[0] = __fdiv_rn(1.0f, ordered_sum(0.0f, w, kv_len));  // the serial sum of the head
             cbar();
-            const float inv = c.part[hg];
+            const float inv = c.part[0];
 #pragma unroll 1
-            for (uint32_t q = tl; q < kv_len; q += nt) wh[q] = __fmul_rn(wh[q], inv);
+            for (uint32_t q = c.tid; q < kv_len; q += kConsumers) w[q] = __fmul_rn(w[q], inv);
+            cbar();
         }
         const uint32_t n_tiles = (kv_len + kVTile - 1) / kVTile;
-        const bool chain = (uint32_t)c.tid < group * 8;  // thread (hg, d): one accumulation chain
-        const uint32_t hg = (uint32_t)c.tid >> 3, d = (uint32_t)c.tid & 7u;
+        make_products(0, (uint32_t)c.tid, (uint32_t)kConsumers);
+        cbar();
         float acc = 0.0f;
 #pragma unroll 1
         for (uint32_t tile = 0; tile < n_tiles; ++tile) {
-            if (tile + 1 < n_tiles) {
-                fetch_tile(tile + 1);
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-            } else {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-            }
-            cbar();  // the tile (and, first pass, the weights) are complete for every thread
-            if (chain) {
-                const uint32_t p0 = tile * kVTile, n = min(kVTile, kv_len - p0);
-                const float* vtile = vt + (size_t)(tile & 1u) * kVTile * 8 + d;
-                const float* wq = w + (size_t)hg * p.max_len + p0;
-                uint32_t i = 0;
-                if (n >= 8) {  // products of the next eight positions are formed under the adds of these eight
-                    float pr[8];
-                    {
-                        const float4 wa = *reinterpret_cast<const float4*>(wq), wb = *reinterpret_cast<const float4*>(wq + 4);
-                        pr[0] = __fmul_rn(wa.x, vtile[0]);  pr[1] = __fmul_rn(wa.y, vtile[8]);
-                        pr[2] = __fmul_rn(wa.z, vtile[16]); pr[3] = __fmul_rn(wa.w, vtile[24]);
-                        pr[4] = __fmul_rn(wb.x, vtile[32]); pr[5] = __fmul_rn(wb.y, vtile[40]);
-                        pr[6] = __fmul_rn(wb.z, vtile[48]); pr[7] = __fmul_rn(wb.w, vtile[56]);
-                    }
-#pragma unroll 1
-                    for (i = 8; i + 8 <= n; i += 8) {
-                        const float4 wa = *reinterpret_cast<const float4*>(wq + i);
-                        const float4 wb = *reinterpret_cast<const float4*>(wq + i + 4);
-                        const float* vp = vtile + (size_t)i * 8;
-                        float nx[8];
-                        nx[0] = __fmul_rn(wa.x, vp[0]);  nx[1] = __fmul_rn(wa.y, vp[8]);
-                        nx[2] = __fmul_rn(wa.z, vp[16]); nx[3] = __fmul_rn(wa.w, vp[24]);
-                        nx[4] = __fmul_rn(wb.x, vp[32]); nx[5] = __fmul_rn(wb.y, vp[40]);
-                        nx[6] = __fmul_rn(wb.z, vp[48]); nx[7] = __fmul_rn(wb.w, vp[56]);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, pr[j]);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) pr[j] = nx[j];
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, pr[j]);
+            if ((c.warp & 3) == kChainWarp) {  // the chain has its scheduler to itself
+                if (c.warp == kChainWarp && c.lane < 8) {
+                    const uint32_t n = min(kVTile, kv_len - tile * kVTile);
+                    acc = ordered_sum(acc, prod + (size_t)(tile & 1u) * 8 * PITCH + (size_t)c.lane * PITCH, n);
                 }
-#pragma unroll 1
-                for (; i < n; ++i) acc = __fadd_rn(acc, __fmul_rn(wq[i], vtile[(size_t)i * 8]));
+            } else if (tile + 1 < n_tiles) {
+                const uint32_t helper = (uint32_t)(c.warp - (c.warp >> 2) - (c.warp & 3 ? 1 : 0)) * 32u + (uint32_t)c.lane;
+                make_products(tile + 1, helper, 12u * 32u);
             }
-            cbar();  // the buffer the next fetch overwrites has been consumed
+            cbar();  // the next tile's products are complete, this tile's have been added
         }
-        if (chain && ok) xstore(att_out + (size_t)(kvh * group + hg) * D + dc * 8 + d, acc, ep_out);
+        if (c.warp == kChainWarp && c.lane < 8 && ok) xstore(att_out + (size_t)h * D + dc * 8 + c.lane, acc, ep_out);
     }
     return ok;
 }
@@ -1562,8 +1544,15 @@ int gemma_decoder_create(const GemmaDecoderDesc& desc, GemmaDecoder** out) {
     const size_t gemv_scratch = (size_t)nbp_max * (32 + 8) + 128 + after_image;
     p.xh_off = nbp_max + (((nbp_max * 16u) & 127u) == 64u ? 0u : 4u);
     p.deal_limit = desc.deal_limit ? desc.deal_limit : 8u;
+    auto magic = [](uint32_t d) { return d <= 1 ? 0xFFFFFFFFu : (uint32_t)(0x100000000ull / d); };
+    p.group = group;
+    p.half_d = D / 2;
+    p.magic_chunks = magic(D / 8);
+    p.magic_group = magic(group);
+    p.magic_half = magic(D / 2);
+    p.magic_nh = magic(nh);
     const size_t att_a = (size_t)(nh + nkv) * D * 4;
-    const size_t att_b = (size_t)group * desc.ctx * 4 + 2 * (size_t)kVTile * 32;
+    const size_t att_b = (((size_t)desc.ctx + 3) & ~(size_t)3) * 4 + 2 * 8 * (size_t)(kVTile + 4) * 4;
     size_t scratch = gemv_scratch > att_a ? gemv_scratch : att_a;
     if (att_b > scratch) scratch = att_b;
     size_t off = kSharedHead;
