@@ -266,6 +266,67 @@ def argmax(logits):
     return out
 
 
+SAMPLE_MAX_K = 256  # gpt2.zig:865
+
+
+def _exp_f32(x):
+    """exp of f32 values, evaluated in double and rounded once (the convention of every exponential on this path)."""
+    return np.exp(np.asarray(x, dtype=np.float64)).astype(np.float32)
+
+
+def sample_top_k(logits, top_k, temperature, rng):
+    """Temperature + top-k sampling on the host, the way gpt2.sample_top_k does it (src/models/gpt2.zig:866-977).
+
+    `logits`: 1-D f32 (torch tensor on any device or numpy array; a copy is taken, the caller's row is left alone).
+    `rng`: a numpy.random.Generator; one f32 uniform is drawn per call, as the reference draws `rng.float(f32)`.
+    top_k == 0 or top_k >= n samples from the softmax of all logits (sample_full_softmax). Otherwise the (at most
+    256) largest scaled logits are kept in the reference's min-buffer ORDER — the first k in index order, every
+    later larger value overwriting the slot of the current minimum — because the cumulative distribution is walked
+    in that order, and the token returned for a given uniform depends on it."""
+    if isinstance(logits, torch.Tensor):
+        logits = logits.detach().float().cpu().numpy()
+    v = np.array(logits, dtype=np.float32).reshape(-1)
+    n = v.size
+    k = top_k if 0 < top_k < n else n
+    inv_temp = np.float32(1.0) / np.float32(temperature) if (temperature > 0 and temperature != 1.0) else np.float32(1.0)
+    if k >= n:
+        if inv_temp != 1.0:
+            v = v * inv_temp
+        e = _exp_f32(v - v.max())
+        probs = e * (np.float32(1.0) / np.cumsum(e, dtype=np.float32)[-1])
+        r = np.float32(rng.random(dtype=np.float32))
+        hit = np.nonzero(np.cumsum(probs, dtype=np.float32) >= r)[0]
+        return int(hit[0]) if hit.size else n - 1
+    k = min(k, SAMPLE_MAX_K)
+    v = v * inv_temp
+    vals = v[:k].copy()
+    idxs = np.arange(k, dtype=np.int64)
+    pos = int(np.argmin(vals))  # first minimum, as the reference's strict `<` scan finds it
+    mn = vals[pos]
+    BLOCK = 4096
+    for b0 in range(k, n, BLOCK):
+        blk = v[b0:b0 + BLOCK]
+        for j in np.nonzero(blk > mn)[0]:  # the minimum only rises: a value that fails now fails later too
+            x = blk[j]
+            if x > mn:
+                vals[pos] = x
+                idxs[pos] = b0 + j
+                pos = int(np.argmin(vals))
+                mn = vals[pos]
+    e = _exp_f32(vals - vals.max())
+    total = np.float32(0.0)
+    for x in e:
+        total = np.float32(total + x)
+    probs = e * (np.float32(1.0) / total)
+    r = np.float32(rng.random(dtype=np.float32))
+    c = np.float32(0.0)
+    for j in range(k):
+        c = np.float32(c + probs[j])
+        if c >= r:
+            return int(idxs[j])
+    return int(idxs[k - 1])
+
+
 def rms_norm(x, w, eps):
     x = _dev_f32(x)
     out = torch.empty_like(x)
