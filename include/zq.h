@@ -73,12 +73,16 @@ typedef enum zq_type {
 /* How the activation row is treated before the dot products.
  *   ZQ_ACT_F32: f32 activations times weights dequantised on the fly — the GPT-2
  *               path (src/models/gpt2.zig:632-686 -> src/gguf/dequant.zig:133-309).
- *               Up to 48 rows per call the activations keep 22 mantissa bits (results agree
+ *               Up to 16 rows per call the activations keep 22 mantissa bits (results agree
  *               with the f32 CPU path to about 1e-7 relative L2). From 49 rows on the call is a
  *               tensor-core GEMM with fp16 operands, as ZQ_ACT_F16: about 3e-4 relative L2
  *               (inside the path's 1e-3 bar), and it NEEDS the workspace of
  *               zq_matmul_workspace_bytes(); without one the call returns ZQ_ERR_BAD_ARG (it is
  *               not served by the slower small-batch kernel behind the caller's back).
+ *               17 to 48 rows: zq_matmul_workspace_bytes() is non-zero for matrices of 12 288 rows
+ *               and more, and a call that brings that workspace runs the weight-streaming
+ *               tensor-core form (fp16 operands, 3e-4, 2-3 x faster); a call without workspace,
+ *               or on a smaller matrix, runs passes of the 16-row kernel (1e-7).
  *   ZQ_ACT_Q8 : each activation row is first quantised to 32-wide int8 blocks and
  *               the dots are exact int8 x int8 -> int32 — the Gemma-3 path
  *               (src/gguf/thread_pool.zig:96-160 -> src/gguf/simd_dot.zig:25-152).

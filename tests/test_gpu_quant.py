@@ -489,3 +489,75 @@ def test_matmul_transposed_at_full_shapes_sampled_columns(zq, oracle, out_dim, i
                                     out_dim, in_dim, n_threads=16)
     err = rel_l2(got[torch.from_numpy(rows).cuda()].cpu().numpy(), want)
     assert err <= REL_L2_TRANS, err
+
+
+# ---- the weight-streaming tensor-core form (17-128 activation rows, matrices of 12 288 rows and more) ----
+
+
+STREAM_TYPES = [(ggml.Q4_0, 18), (ggml.Q4_1, 20), (ggml.Q8_0, 34)]
+
+
+@pytest.mark.parametrize("qt,block_bytes", STREAM_TYPES)
+@pytest.mark.parametrize("k,n", [(1152, 37888 + 24), (1024, 12416), (4096, 14336)])
+@pytest.mark.parametrize("m", [17, 32, 33, 64, 100, 128])
+def test_streaming_gemm_sampled_rows(zq, oracle, qt, block_bytes, k, n, m):
+    """Few activation rows against many weight rows: f32-activation calls of 17-128 rows that bring the workspace
+    zq_matmul_workspace_bytes asks for run the persistent weight-streaming kernel (weights as the N operand of
+    tcgen05.mma, packed quants by tensor copies). Covers both tile heights (256 rows from 37 888 weight rows on,
+    128 below), a last tile that is cut off (n not a multiple of the tile), a K whose last chunk is short (1152 =
+    9 quads), up to 32 rows spread over the lane quarters and more in natural order. Sampled weight rows against
+    the CPU path (dequant.zig:170-309), every output against the dequantised product."""
+    g = torch.Generator(device="cuda").manual_seed(31 * m + k + int(qt))
+    raw_d = ggml.quantize(qt, torch.randn(n, k, generator=g, device="cuda") * 0.02)
+    qw = zq.QuantWeight(raw_d, qt, n, k)
+    x = torch.randn(m, k, generator=g, device="cuda")
+    from zignn_b200 import _lib
+    assert _lib.load().zq_matmul_workspace_bytes(qw.handle, m, zq.ACT_F32) > 0  # the streaming form is on offer
+    got = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32)
+    assert bool(torch.isfinite(got).all())
+    rows = _sampled_rows(n)
+    sub = raw_d.view(n, k // 32 * block_bytes)[torch.from_numpy(rows).cuda()].cpu().numpy().reshape(-1)
+    want = oracle.linear(qt, sub, x.cpu().numpy(), len(rows), k, act_mode=0, n_threads=16)
+    got_s = got[:, torch.from_numpy(rows).cuda()].cpu().numpy()
+    err = rel_l2(got_s, want)
+    assert err <= REL_L2_BAR
+    assert err <= REL_L2_GEMM_GUARD, err
+    worst = max(rel_l2(got_s[r], want[r]) for r in range(m))
+    assert worst <= REL_L2_BAR, worst
+    full = x @ qw.dequantize().t()
+    assert float((got - full).norm() / full.norm()) <= REL_L2_GEMM_GUARD
+    # no output is left unwritten or written twice with different values: element-wise closeness everywhere
+    assert bool(((got - full).abs() <= 4e-3 * full.abs().max()).all())
+    assert _lib.device_error() == 0
+
+
+def test_streaming_gemm_epilogue_and_row_counts(zq):
+    """bias, GELU, multiplier and residual in the streaming form's epilogue, for row counts on both sides of the
+    interleaved / natural placement (32 | 33) and a count that leaves lane quarters empty (65)."""
+    k, n = 1152, 12800
+    g = torch.Generator(device="cuda").manual_seed(5)
+    raw_d = ggml.quantize(ggml.Q4_0, torch.randn(n, k, generator=g, device="cuda") * 0.02)
+    qw = zq.QuantWeight(raw_d, ggml.Q4_0, n, k)
+    wd = qw.dequantize()
+    for m in (17, 31, 32, 33, 65, 128):
+        x = torch.randn(m, k, generator=g, device="cuda")
+        bias = torch.randn(n, generator=g, device="cuda")
+        mul = torch.randn(m, n, generator=g, device="cuda")
+        res = torch.randn(m, n, generator=g, device="cuda")
+        base = x @ wd.t()
+        got = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, bias=bias)
+        assert torch.allclose(got, base + bias, rtol=0, atol=4e-3 * float(base.abs().max()))
+        got = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, bias=bias, gelu=True, mul=mul, residual=res)
+        want = res + torch.nn.functional.gelu(base + bias, approximate="tanh") * mul
+        assert torch.allclose(got, want, rtol=0, atol=6e-3 * float(want.abs().max()))
+    # a call without workspace keeps the exact small-batch kernel (passes of 16 rows)
+    x = torch.randn(20, k, generator=g, device="cuda")
+    from zignn_b200 import _lib
+    from zignn_b200 import structs as S
+    import ctypes as C
+    y = torch.empty(20, n, device="cuda")
+    ep = S.Epilogue(None, 0, None, None)
+    rc = _lib.load().zq_matmul(qw.handle, x.data_ptr(), y.data_ptr(), 20, zq.ACT_F32, C.byref(ep), None, 0,
+                               torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert rel_l2(y.cpu().numpy(), (x.double() @ wd.double().t()).float().cpu().numpy()) <= REL_L2_GUARD

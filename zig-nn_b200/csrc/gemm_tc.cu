@@ -21,6 +21,8 @@
 // is bounded; on a timeout the kernel records it in the library's device-error word, stops using
 // the pipeline, still releases tensor memory and returns (outputs are then undefined; zq_device_error
 // reports it).
+#include <cuda.h>  // CUtensorMap and the enums of cuTensorMapEncodeTiled (the entry point is looked up at run time)
+
 #include "zq_internal.h"
 
 namespace zq {
@@ -168,10 +170,15 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t m, uint32_t n) {
 // m >= M or k >= K; post[m] = 2^e_m. One CTA per padded row.
 __global__ void __launch_bounds__(256)
 convert_rows_tiled_kernel(const float* __restrict__ x, __half* __restrict__ xt, float* __restrict__ post,
-                          uint32_t M, uint32_t K, uint32_t m_pad, uint32_t n_seg) {
+                          uint32_t M, uint32_t K, uint32_t m_pad, uint32_t n_seg, uint32_t quarter_rows) {
     __shared__ float red[8];
     __shared__ float s_pre;
-    const uint32_t m = blockIdx.x;
+    // quarter_rows = 0: row m of x sits at place m of a segment. Otherwise (few rows, streaming form) the places are
+    // four quarters of quarter_rows each and row m sits at place m / 4 of quarter m % 4, so that the rows spread
+    // over the four lane quarters of tensor memory and all four draining warps have work.
+    const uint32_t place = blockIdx.x;
+    const uint32_t m = quarter_rows ? (place % quarter_rows) * 4u + place / quarter_rows : place;
+    const uint32_t key = (quarter_rows ? place % quarter_rows : place) & 7u;  // swizzle key: the row's place in its tile
     const bool real = m < M;
     const float* row = x + (size_t)(real ? m : 0) * K;
     float amax = 0.0f;
@@ -194,7 +201,7 @@ convert_rows_tiled_kernel(const float* __restrict__ x, __half* __restrict__ xt, 
     for (uint32_t k = threadIdx.x; k < kp; k += blockDim.x) {
         const uint32_t seg = k >> 6, c = (k >> 3) & 7u, e = k & 7u;
         const float v = (real && k < K) ? row[k] * pre : 0.0f;
-        xt[((size_t)seg * m_pad + m) * 64 + ((c ^ (m & 7u)) << 3) + e] = __float2half_rn(v);
+        xt[((size_t)seg * m_pad + place) * 64 + ((c ^ key) << 3) + e] = __float2half_rn(v);
     }
 }
 
@@ -459,6 +466,518 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
     }
 }
 
+// ---- weight-streaming form for few activation rows (up to 128) ------------------------------------
+//
+// With few activation rows the product is bound by the weight stream, not by the tensor-core rate. What was
+// measured on the way to this form (vocabulary head, q4_0, 16 activation rows):
+//   * one tcgen05.mma (kind::f16, K = 16) takes 127 cycles whatever its M (64, 128) and N (16 ... 256): with
+//     the weights as the M operand (128 rows per instruction, N = the few activation rows) a 64-K stage costs
+//     four instructions = 0.27 us for 128 weight rows, which alone is 67 us for the head. So the weights are the
+//     N operand here (up to 256 rows per instruction) and the activations the M operand (128 rows, of which
+//     only the first m_rows hold data; the rest of the tile is whatever lies in shared memory, and its
+//     accumulator rows are never read);
+//   * 512 threads fetching their own packed words from global memory put the fetch latency into every stage
+//     hand-over and keep the load/store pipe busy with one wavefront per lane (32 lanes, 32 lines): 134 us;
+//   * one plain bulk copy per row and 256 bytes: 35 ns of the copy engine apiece = 7 GB/s per SM: 195 us.
+// The form that came out:
+//   * the kernel is persistent: CTA b walks the tiles of TN weight rows b, b + grid, ...; every ring, the copies
+//     and the MMA thread run on across tile boundaries;
+//   * the packed quants and the scales come in by tensor copies (cp.async.bulk.tensor.2d over [rows][row bytes]
+//     maps of the weight's two arrays; per chunk of 128 packed bytes per row: one box of TN rows x 128 bytes
+//     with the 128-byte swizzle and one box of scales), issued by a copy warp three chunks ahead, bytes counted
+//     on the chunk's mbarrier; nothing of it passes through the load pipe;
+//   * the 16 converting warps turn a stage (64 K of the TN rows) into the fp16 tile together, reading packed
+//     words and scales from shared memory (conflict-free through the swizzle);
+//   * the stage's activation tile (rows x 128 bytes) is one bulk copy into a ring of its own, issued by the copy
+//     warp well ahead;
+//   * two accumulators in tensor memory take turns; four more warps drain the finished one (tcgen05.ld, scale,
+//     epilogue, 64-byte stores) while the next tile's stages flow.
+// Every wait is bounded; on a timeout the kernel records it, all roles leave their loops and tensor memory is
+// released.
+constexpr int TS_CONVERT_WARPS = 16;
+constexpr int TS_MMA_WARP = TS_CONVERT_WARPS;
+constexpr int TS_EPI_WARP0 = TS_MMA_WARP + 1;   // four warps: their ids mod 4 cover the four lane quarters
+constexpr int TS_COPY_WARP = TS_EPI_WARP0 + 4;
+constexpr int TS_THREADS = (TS_COPY_WARP + 1) * 32;  // 22 warps
+constexpr int TS_MAX_STAGES = 6;    // fp16 weight tiles (TN x 128 bytes each)
+constexpr int TS_MAX_BTILES = 16;   // activation tiles
+constexpr int TS_MAX_CHUNKS = 4;
+constexpr uint32_t TS_CHUNK_ROW = 128;  // packed bytes per row and chunk: 2 quads of q4, 1 of q8_0
+constexpr uint32_t TS_ACT_ROWS = 128;   // rows of the activation operand (UMMA M)
+
+// One box of a 2-D map: rows [y, y + box rows) x bytes [x, x + box bytes) -> shared memory, bytes counted on `bar`.
+__device__ __forceinline__ void tensor_copy_2d(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t saddr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(saddr));
+    return v;
+}
+// Scale bytes of a row in a chunk's scale box: q4_0 16 (two quads), q4_1 32, q8_0 16 (the quad and its neighbour:
+// a box is at least 16 bytes wide).
+template <int TYPE>
+struct StreamScales {
+    static constexpr uint32_t kBox = TYPE == ZQ_TYPE_Q4_1 ? 32u : 16u;
+};
+// The thread's share of quad `ql` of the chunk: (row, half) -> packed words and the quad's scales. `sq` is the
+// quad's place in the row's scale box.
+template <int TYPE>
+__device__ __forceinline__ void read_packed(PackedQuad<TYPE>& p, uint32_t chunk, uint32_t scales, uint32_t row,
+                                            uint32_t half, uint32_t ql, uint32_t sq) {
+    constexpr uint32_t UNITS = TYPE == ZQ_TYPE_Q8_0 ? 8 : 4;   // 16-byte units per quad
+    constexpr uint32_t MINE = UNITS / 2;                        // units of one half
+    const uint32_t u0 = ql * UNITS + half * MINE;
+    p.w0 = lds128(chunk + swz(row, u0));
+    p.w1 = lds128(chunk + swz(row, u0 + 1));
+    if (TYPE == ZQ_TYPE_Q8_0) {
+        p.w2 = lds128(chunk + swz(row, u0 + 2));
+        p.w3 = lds128(chunk + swz(row, u0 + 3));
+    }
+    if (TYPE == ZQ_TYPE_Q4_1) {
+        p.s = lds128(scales + row * 32u + sq * 16u);
+    } else {
+        const uint2 v = lds64(scales + row * 16u + sq * 8u);
+        p.s.x = v.x;
+        p.s.y = v.y;
+    }
+}
+// 32 lanes x 16 consecutive columns of f32
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// TN = weight rows per tile (UMMA N): 256, or 128 for matrices with too few rows to give every SM a 256-row tile.
+template <int TYPE, int TN>
+__global__ void __launch_bounds__(TS_THREADS, 1)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+                   const __half* __restrict__ xt, const float* __restrict__ post, float* __restrict__ y, uint32_t N,
+                   uint32_t M, uint32_t nbp, uint32_t act_rows, uint32_t interleave, uint32_t n_ring, uint32_t n_bring,
+                   uint32_t n_chunk_ring, unsigned int* err_word, TcEpilogue ep) {
+    constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
+    constexpr uint32_t QB = Q8 ? 32 : 16;          // packed bytes per block
+    constexpr uint32_t QUADB = 4 * QB;             // packed bytes per quad
+    constexpr uint32_t CQ = TS_CHUNK_ROW / QUADB;  // quads per chunk: 2 (q4) or 1 (q8_0)
+    constexpr uint32_t SBOX = StreamScales<TYPE>::kBox;
+    constexpr uint32_t W_STAGE = TN * 128u;        // fp16 weight tile of a stage
+    constexpr uint32_t CHUNK_BYTES = TN * 128u + TN * 32u;  // packed box, then the scale box (room for 32 bytes per row)
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int NBARS = 2 * TS_MAX_STAGES + 2 * TS_MAX_BTILES + 2 * TS_MAX_CHUNKS + 4;
+    __shared__ __align__(8) unsigned long long bars[NBARS];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    __shared__ float epi_stage[4][32][17];  // per draining warp: a 32 x 16 block of outputs on its way to row-wise stores
+
+    // shared memory: fp16 weight tiles | activation tiles | packed chunks (the activation operand spans 128 rows
+    // from its tile's start whatever the tile holds: what lies behind the ring must be shared memory too)
+    const uint32_t smem32 = ((uint32_t)__cvta_generic_to_shared(smem) + 1023u) & ~1023u;
+    // Activation tiles. Natural order: tile k at k * rows * 128 bytes. Quarter-interleaved (up to 32 rows): a tile is
+    // four pieces of 1 KB at 0, 4, 8 and 12 KB from its start, and tile k starts k KB into the region, so four tiles
+    // fit into 19 KB.
+    const uint32_t btile_bytes = act_rows * 128u;  // bytes of a stage in the activation image
+    const uint32_t bstride = interleave ? 1024u : btile_bytes;
+    const uint32_t bring_bytes = interleave ? 20u * 1024u : ((n_bring * btile_bytes + 1023u) & ~1023u);
+    const uint32_t bring32 = smem32 + n_ring * W_STAGE;
+    const uint32_t chunk32 = bring32 + bring_bytes;
+    const uint32_t bar32 = (uint32_t)__cvta_generic_to_shared(bars);
+    auto full_bar = [&](uint32_t s) { return bar32 + s * 8; };
+    auto empty_bar = [&](uint32_t s) { return bar32 + (TS_MAX_STAGES + s) * 8; };
+    auto bfull_bar = [&](uint32_t s) { return bar32 + (2 * TS_MAX_STAGES + s) * 8; };
+    auto bempty_bar = [&](uint32_t s) { return bar32 + (2 * TS_MAX_STAGES + TS_MAX_BTILES + s) * 8; };
+    constexpr int CB0 = 2 * TS_MAX_STAGES + 2 * TS_MAX_BTILES;
+    auto cfull_bar = [&](uint32_t c) { return bar32 + (CB0 + c) * 8; };
+    auto cempty_bar = [&](uint32_t c) { return bar32 + (CB0 + TS_MAX_CHUNKS + c) * 8; };
+    auto acc_full = [&](uint32_t a) { return bar32 + (CB0 + 2 * TS_MAX_CHUNKS + a) * 8; };
+    auto acc_empty = [&](uint32_t a) { return bar32 + (CB0 + 2 * TS_MAX_CHUNKS + 2 + a) * 8; };
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t row_tiles = (N + TN - 1) / TN;
+    const uint32_t nt = row_tiles > blockIdx.x ? (row_tiles - blockIdx.x - 1) / gridDim.x + 1 : 0;  // this CTA's tiles
+    const uint32_t n_quads = nbp / 4, n_stages = nbp / 2;
+    const uint32_t n_chunks = (n_quads + CQ - 1) / CQ;  // per tile
+    constexpr uint32_t tmem_cols = 2 * TN;               // two accumulators of TN columns
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < n_ring; ++s) {
+            mbar_init(full_bar(s), TS_CONVERT_WARPS);  // one arrival per converting warp
+            mbar_init(empty_bar(s), 1);
+        }
+        for (uint32_t s = 0; s < n_bring; ++s) {
+            mbar_init(bfull_bar(s), 1);  // the copy warp's arrival with the byte count
+            mbar_init(bempty_bar(s), 1);
+        }
+        for (uint32_t c = 0; c < n_chunk_ring; ++c) {
+            mbar_init(cfull_bar(c), 1);                   // the copy warp's arrival with the byte count
+            mbar_init(cempty_bar(c), TS_CONVERT_WARPS);   // every converting warp, once per chunk
+        }
+        for (uint32_t a = 0; a < 2; ++a) {
+            mbar_init(acc_full(a), 1);
+            mbar_init(acc_empty(a), 4);  // one arrival per draining warp
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TS_MMA_WARP) {
+        const uint32_t slot = (uint32_t)__cvta_generic_to_shared(&tmem_base_slot);
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_p = &abort_flag;
+
+    if (warp < TS_CONVERT_WARPS) {
+        // ================= converting warps =================
+        // TN = 128: thread = (row, half, block of the stage); TN = 256: thread = (row, block), both halves in turn
+        constexpr int HALVES = TN == 256 ? 2 : 1;
+        const uint32_t prow = TN == 256 ? (uint32_t)tid >> 1 : (uint32_t)tid >> 2;
+        const uint32_t phalf0 = TN == 256 ? 0u : ((uint32_t)tid >> 1) & 1u, pjj = (uint32_t)tid & 1u;
+        uint32_t slot = 0, round = 0;      // stage ring
+        uint32_t cslot = 0, cround = 0;    // chunk ring
+        bool alive = true;
+        for (uint32_t ti = 0; ti < nt && alive; ++ti) {
+            for (uint32_t c = 0; c < n_chunks && alive; ++c) {
+                alive = mbar_wait(cfull_bar(cslot), cround & 1u, abort_p, err_word);
+                if (!alive) break;
+                const uint32_t nqc = min(CQ, n_quads - c * CQ);
+                const uint32_t chunk = chunk32 + cslot * CHUNK_BYTES, scales = chunk + TN * 128u;
+                for (uint32_t ql = 0; ql < nqc && alive; ++ql) {
+                    const uint32_t sq = Q8 ? (c & 1u) : ql;  // q8_0: the box holds the scales of quads c & ~1 and c | 1
+                    PackedQuad<TYPE> pk[HALVES];
+#pragma unroll
+                    for (int hh = 0; hh < HALVES; ++hh) read_packed<TYPE>(pk[hh], chunk, scales, prow, phalf0 + hh, ql, sq);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (round > 0) alive = alive && mbar_wait(empty_bar(slot), (round - 1) & 1u, abort_p, err_word);
+                        if (!alive) break;
+                        const uint32_t w_tile = smem32 + slot * W_STAGE;
+#pragma unroll
+                        for (int hh = 0; hh < HALVES; ++hh) {
+                            if (h == 0) store_dequant<TYPE, 0>(pk[hh], w_tile, prow, phalf0 + hh, pjj);
+                            else store_dequant<TYPE, 2>(pk[hh], w_tile, prow, phalf0 + hh, pjj);
+                        }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(full_bar(slot));
+                        if (++slot == n_ring) {
+                            slot = 0;
+                            ++round;
+                        }
+                    }
+                }
+                // this warp has read what it needs of the chunk (its loads have returned: their values were used)
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cempty_bar(cslot));
+                if (++cslot == n_chunk_ring) {
+                    cslot = 0;
+                    ++cround;
+                }
+            }
+        }
+    } else if (warp == TS_COPY_WARP) {
+        // ================= copy warp: packed quants, scales and activation tiles =================
+        uint32_t cslot = 0, cround = 0;
+        uint32_t bslot = 0, bround = 0;
+        bool alive = true;
+        for (uint32_t ti = 0; ti < nt && alive; ++ti) {
+            const uint32_t row0 = (blockIdx.x + ti * gridDim.x) * TN;
+            for (uint32_t c = 0; c < n_chunks && alive; ++c) {
+                if (cround > 0) alive = mbar_wait(cempty_bar(cslot), (cround - 1) & 1u, abort_p, err_word);
+                alive = __all_sync(0xFFFFFFFFu, alive);
+                if (!alive) break;
+                const uint32_t nqc = min(CQ, n_quads - c * CQ);
+                if (lane == 0) {
+                    // boxes are written whole (zeros beyond the map's edges)
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(cfull_bar(cslot)),
+                                 "r"((uint32_t)TN * (128u + SBOX))
+                                 : "memory");
+                    const uint32_t dst0 = chunk32 + cslot * CHUNK_BYTES;
+                    tensor_copy_2d(dst0, &wmap, c * TS_CHUNK_ROW, row0, cfull_bar(cslot));
+                    const uint32_t sx = Q8 ? (c & ~1u) * 8u : c * SBOX;
+                    tensor_copy_2d(dst0 + TN * 128u, &smap, sx, row0, cfull_bar(cslot));
+                }
+                __syncwarp();
+                if (++cslot == n_chunk_ring) {
+                    cslot = 0;
+                    ++cround;
+                }
+                // the activation tiles of the chunk's stages
+                for (uint32_t sg = 2 * c * CQ; sg < 2 * (c * CQ + nqc) && alive; ++sg) {
+                    if (bround > 0) alive = mbar_wait(bempty_bar(bslot), (bround - 1) & 1u, abort_p, err_word);
+                    alive = __all_sync(0xFFFFFFFFu, alive);
+                    if (!alive) break;
+                    if (lane == 0) {
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bfull_bar(bslot)),
+                                     "r"(btile_bytes)
+                                     : "memory");
+                        const unsigned char* src = reinterpret_cast<const unsigned char*>(xt) + (size_t)sg * btile_bytes;
+                        if (interleave) {
+                            for (uint32_t q = 0; q < 4; ++q)
+                                bulk_copy_g2s(bring32 + bslot * bstride + q * 4096u, src + q * 1024u, 1024u, bfull_bar(bslot));
+                        } else {
+                            bulk_copy_g2s(bring32 + bslot * bstride, src, btile_bytes, bfull_bar(bslot));
+                        }
+                    }
+                    __syncwarp();
+                    if (++bslot == n_bring) {
+                        bslot = 0;
+                        ++bround;
+                    }
+                }
+            }
+        }
+        if (!alive) {
+            // copies already issued still land in this CTA's shared memory: wait (bounded) for the newest fill of
+            // every slot before the CTA may retire
+            for (uint32_t s = 0; s < n_chunk_ring; ++s)
+                for (uint32_t i = 0; i < (1u << 16); ++i)
+                    if (mbar_try_wait(cfull_bar(s), 0) || mbar_try_wait(cfull_bar(s), 1)) break;
+            for (uint32_t s = 0; s < n_bring; ++s)
+                for (uint32_t i = 0; i < (1u << 16); ++i)
+                    if (mbar_try_wait(bfull_bar(s), 0) || mbar_try_wait(bfull_bar(s), 1)) break;
+        }
+    } else if (warp == TS_MMA_WARP) {
+        // ================= MMA issuer: D[activation row][weight row] += X . W^T =================
+        if (lane == 0) {
+            const uint32_t idesc = idesc_f16(TS_ACT_ROWS, TN);
+            uint32_t slot = 0, round = 0, bslot = 0, bround = 0;
+            bool alive = true;
+            for (uint32_t i = 0; i < nt && alive; ++i) {
+                const uint32_t acc = i & 1u;
+                if (i >= 2) alive = mbar_wait(acc_empty(acc), ((i >> 1) - 1) & 1u, abort_p, err_word);
+                if (!alive) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * TN;
+                for (uint32_t s = 0; s < n_stages && alive; ++s) {
+                    alive = mbar_wait(bfull_bar(bslot), bround & 1u, abort_p, err_word) &&
+                            mbar_wait(full_bar(slot), round & 1u, abort_p, err_word);
+                    if (!alive) break;
+                    tc_fence_after();
+                    const uint64_t x_desc = smem_desc_sw128(bring32 + bslot * bstride);
+                    const uint64_t w_desc = smem_desc_sw128(smem32 + slot * W_STAGE);
+#pragma unroll
+                    for (uint32_t k16 = 0; k16 < TC_BK / 16; ++k16)
+                        tc_mma_f16(d_tmem, x_desc + 2 * k16, w_desc + 2 * k16, idesc, (s | k16) != 0 ? 1u : 0u);
+                    tc_commit(empty_bar(slot));
+                    tc_commit(bempty_bar(bslot));
+                    if (++slot == n_ring) {
+                        slot = 0;
+                        ++round;
+                    }
+                    if (++bslot == n_bring) {
+                        bslot = 0;
+                        ++bround;
+                    }
+                }
+                if (alive) tc_commit(acc_full(acc));
+            }
+            if (!alive) *abort_p = 1;
+        }
+        __syncwarp();
+    } else {
+        // ================= epilogue warps: lane = activation row, columns = the tile's weight rows =================
+        // A lane holds 16 consecutive outputs of ITS activation row: stored from there, the 32 lanes of a store hit
+        // 32 rows of y, N floats apart, 16 bytes each (measured: 1.7-3 us per 16 columns, 32 us per tile, the whole
+        // kernel waiting for it). So the 32 x 16 block is turned round in shared memory and each half-warp stores one
+        // row's 64 contiguous bytes.
+        const uint32_t lane_base = ((uint32_t)warp & 3u) * 32u;
+        const uint32_t ew = (uint32_t)warp - TS_EPI_WARP0;
+        float(*stage)[17] = epi_stage[ew];
+        const uint32_t quarter = (uint32_t)warp & 3u;
+        // activation row of lane j of this quarter: 4 j + quarter when interleaved, 32 quarter + j otherwise
+        const uint32_t m = interleave ? 4u * (uint32_t)lane + quarter : lane_base + lane;
+        const bool mine = interleave ? quarter < M : lane_base < M;  // this warp's lane quarter holds real rows
+        const uint32_t rows_here = !mine ? 0u : interleave ? min(8u, (M - quarter + 3u) / 4u) : min(32u, M - lane_base);
+        const float scale = (m < M && (!interleave || lane < 8)) ? post[m] : 0.0f;
+        const uint32_t hr = (uint32_t)lane >> 4, hc = (uint32_t)lane & 15u;  // half-warp and column of the store pass
+        const bool plain = !ep.bias && !ep.gelu && !ep.mul && !ep.residual;
+        bool alive = true;
+        for (uint32_t i = 0; i < nt && alive; ++i) {
+            const uint32_t acc = i & 1u;
+            alive = mbar_wait(acc_full(acc), (i >> 1) & 1u, abort_p, err_word);
+            alive = __all_sync(0xFFFFFFFFu, alive);
+            if (!alive) break;
+            tc_fence_after();
+            const uint32_t n0 = (blockIdx.x + i * gridDim.x) * TN;
+            if (mine) {
+                for (uint32_t c = 0; c < (uint32_t)TN; c += 16) {
+                    if (n0 + c >= N) break;  // uniform over the warp
+                    uint32_t v16[16];
+                    tc_ld16(tmem_base + (lane_base << 16) + acc * TN + c, v16);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) stage[lane][k] = __uint_as_float(v16[k]) * scale;
+                    __syncwarp();
+                    const uint32_t n = n0 + c + hc;
+                    if (n < N) {
+                        // half-warp hr takes the block's rows hr, hr + 2, ...: 64 contiguous bytes of one row of y per store
+                        const uint32_t m_step = interleave ? 8u : 2u;
+                        const uint32_t m_first = interleave ? 4u * hr + quarter : lane_base + hr;
+                        if (plain) {
+                            float* dst = y + (size_t)m_first * N + n;
+                            const size_t step = (size_t)m_step * N;
+                            uint32_t r = hr;
+#pragma unroll 1
+                            for (; r + 6 < rows_here; r += 8) {
+                                const float v0 = stage[r][hc], v1 = stage[r + 2][hc], v2 = stage[r + 4][hc], v3 = stage[r + 6][hc];
+                                dst[0] = v0;
+                                dst[step] = v1;
+                                dst[2 * step] = v2;
+                                dst[3 * step] = v3;
+                                dst += 4 * step;
+                            }
+#pragma unroll 1
+                            for (; r < rows_here; r += 2) {
+                                dst[0] = stage[r][hc];
+                                dst += step;
+                            }
+                        } else {
+#pragma unroll 1
+                            for (uint32_t r = hr, mr = m_first; r < rows_here; r += 2, mr += m_step) {
+                                const size_t at = (size_t)mr * N + n;
+                                float v = stage[r][hc];
+                                if (ep.bias) v = __fadd_rn(v, ep.bias[n]);
+                                if (ep.gelu) v = gelu_tanh(v);
+                                if (ep.mul) v = __fmul_rn(v, ep.mul[at]);
+                                if (ep.residual) v = __fadd_rn(ep.residual[at], v);
+                                y[at] = v;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(acc));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TS_MMA_WARP) {
+        if (abort_flag && lane == 0) {  // abandoned: give MMAs in flight a bounded chance to finish
+            tc_commit(acc_full(0));
+            for (uint32_t i = 0; i < kSpinLimit; ++i)
+                if (mbar_try_wait(acc_full(0), 0) || mbar_try_wait(acc_full(0), 1)) break;
+        }
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+constexpr uint32_t kStreamMaxRows = 128;   // activation rows the streaming form takes
+constexpr uint32_t kStreamMinTiles = 96;   // it needs about a tile per SM to pull the weight stream
+
+// Up to 32 activation rows are spread over the four lane quarters of tensor memory (8 places each); more rows lie
+// in their natural order, padded to 16.
+inline uint32_t stream_quarter_rows(uint32_t m_rows) { return m_rows <= 32u ? 8u : 0u; }
+inline uint32_t stream_act_rows(uint32_t m_rows) { return m_rows <= 32u ? 32u : ((m_rows + 15u) / 16u) * 16u; }
+
+// The two arrays of a weight as 2-D maps for tensor copies: [out_dim rows][row bytes] of bytes, zeros beyond the
+// edges. Quants: boxes of `box_rows` rows x 128 bytes with the 128-byte swizzle; scales: boxes of the same rows x
+// the scale bytes of a chunk, as stored. cuTensorMapEncodeTiled is a host-side computation; its entry point is
+// taken from the driver at first use (the library does not link against libcuda).
+int tensor_map_2d(const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes, uint32_t box_rows,
+                  bool swizzle128, CUtensorMap* out) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        ZQ_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return ZQ_ERR_UNSUPPORTED;
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    if (((uintptr_t)base & 15u) || (row_bytes & 15u) || (box_bytes & 15u)) return ZQ_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? ZQ_OK : ZQ_ERR_UNSUPPORTED;
+}
+
+template <int TYPE, int TN>
+int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
+                     cudaStream_t st) {
+    auto kern = gemm_stream_kernel<TYPE, TN>;
+    const uint32_t act_rows = stream_act_rows(M);
+    const uint32_t btile_bytes = act_rows * 128u;
+    constexpr uint32_t W_STAGE = TN * 128u, CHUNK_BYTES = TN * 128u + TN * 32u;
+    int dev = 0, max_smem = 0;
+    ZQ_CUDA(cudaGetDevice(&dev));
+    ZQ_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    // Shared memory: activation tiles (16-32 KB), then fp16 weight tiles, then packed chunks. A weight tile is free
+    // again only when its MMAs have run and their commit has arrived (half a microsecond after issue, measured),
+    // so the ring of weight tiles must be deep: four of 256 rows or six of 128 rows where that leaves two chunks.
+    const uint32_t budget = (uint32_t)max_smem - 1024u - 10240u;  // alignment slack, static shared memory
+    const uint32_t interleave = stream_quarter_rows(M) ? 1u : 0u;
+    uint32_t n_bring = (16u * 1024u) / btile_bytes;
+    if (n_bring > (uint32_t)TS_MAX_BTILES) n_bring = TS_MAX_BTILES;
+    if (n_bring < 2) n_bring = 2;
+    if (n_bring < 3 && btile_bytes <= 8192u) n_bring = 3;
+    if (interleave) n_bring = 4;
+    const uint32_t bring_bytes = interleave ? 20u * 1024u : ((n_bring * btile_bytes + 1023u) & ~1023u);
+    uint32_t n_ring = TN == 256 ? 4 : 6;
+    while (n_ring > 2 && budget < bring_bytes + n_ring * W_STAGE + 2 * CHUNK_BYTES) --n_ring;
+    if (budget < bring_bytes + n_ring * W_STAGE + 2 * CHUNK_BYTES) return ZQ_ERR_UNSUPPORTED;
+    uint32_t n_chunk_ring = (budget - bring_bytes - n_ring * W_STAGE) / CHUNK_BYTES;
+    if (n_chunk_ring > (uint32_t)TS_MAX_CHUNKS) n_chunk_ring = TS_MAX_CHUNKS;
+    const size_t smem = (size_t)n_ring * W_STAGE + bring_bytes + (size_t)n_chunk_ring * CHUNK_BYTES + 1024;
+    ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const uint32_t row_tiles = (w->out_dim + TN - 1) / TN;
+    const uint32_t sms = (uint32_t)sm_count();
+    const uint32_t grid = row_tiles < sms ? row_tiles : sms;
+    unsigned int* err_word = nullptr;
+    int rc = device_error_word(&err_word);
+    if (rc != ZQ_OK) return rc;
+    constexpr uint32_t SB = TYPE == ZQ_TYPE_Q4_1 ? 4 : 2;
+    CUtensorMap wmap, smap;
+    rc = tensor_map_2d(w->qs, (uint64_t)w->nbp * w->qb, w->out_dim, 128, TN, true, &wmap);
+    if (rc == ZQ_OK) rc = tensor_map_2d(w->sc, (uint64_t)w->scp * SB, w->out_dim, StreamScales<TYPE>::kBox, TN, false, &smap);
+    if (rc != ZQ_OK) return rc;
+    kern<<<grid, TS_THREADS, smem, st>>>(wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, interleave, n_ring,
+                                         n_bring, n_chunk_ring, err_word, ep);
+    ZQ_LAUNCH_CHECK();
+    return ZQ_OK;
+}
+
+template <int TYPE>
+int launch_stream(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
+                  cudaStream_t st) {
+    // 256-row tiles do twice the work per tensor-core instruction; 128-row tiles when those would leave SMs idle
+    if ((w->out_dim + 255u) / 256u >= (uint32_t)sm_count()) return launch_stream_tn<TYPE, 256>(w, xt, post, y, M, ep, st);
+    return launch_stream_tn<TYPE, 128>(w, xt, post, y, M, ep, st);
+}
+
+inline bool stream_takes(const zq_weight* w, uint32_t m_rows) {
+    return m_rows <= kStreamMaxRows && (w->out_dim + TC_BN - 1) / TC_BN >= kStreamMinTiles;
+}
+
 // rows per CTA tile and padded row count for m_rows activation rows
 inline void tc_tiling(uint32_t m_rows, uint32_t* n_mma, uint32_t* m_pad) {
     *n_mma = m_rows >= (uint32_t)TC_BM ? (uint32_t)TC_BM : ((m_rows + 63u) / 64u) * 64u;
@@ -503,9 +1022,11 @@ int launch_tc(const zq_weight* w, const __half* xt, const float* post, float* y,
 
 }  // namespace
 
+bool gemm_stream_takes(const zq_weight* w, uint32_t m_rows) { return stream_takes(w, m_rows); }
+
 size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows) {
     uint32_t n_mma, m_pad;
-    tc_tiling(m_rows, &n_mma, &m_pad);
+    tc_tiling(m_rows, &n_mma, &m_pad);  // never less than the streaming form's padding to 16 rows
     const size_t xb = ((size_t)(w->nbp / 2) * m_pad * 64 * sizeof(__half) + 255) & ~(size_t)255;
     const size_t pb = ((size_t)m_rows * sizeof(float) + 255) & ~(size_t)255;
     return xb + pb;
@@ -516,11 +1037,14 @@ int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows
     if (m_rows > 65535u * TC_BM) return ZQ_ERR_LIMIT;
     uint32_t n_mma, m_pad;
     tc_tiling(m_rows, &n_mma, &m_pad);
+    const bool stream = stream_takes(w, m_rows);
+    if (stream) m_pad = stream_act_rows(m_rows);
     const uint32_t n_seg = w->nbp / 2;
     const size_t xb = ((size_t)n_seg * m_pad * 64 * sizeof(__half) + 255) & ~(size_t)255;
     __half* xt = static_cast<__half*>(workspace);
     float* post = reinterpret_cast<float*>(static_cast<char*>(workspace) + xb);
-    convert_rows_tiled_kernel<<<m_pad, 256, 0, st>>>(x, xt, post, m_rows, w->in_dim, m_pad, n_seg);
+    convert_rows_tiled_kernel<<<m_pad, 256, 0, st>>>(x, xt, post, m_rows, w->in_dim, m_pad, n_seg,
+                                                     stream ? stream_quarter_rows(m_rows) : 0u);
     ZQ_LAUNCH_CHECK();
     TcEpilogue a{nullptr, nullptr, nullptr, 0};
     if (ep) {
@@ -528,6 +1052,14 @@ int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows
         a.gelu = ep->gelu;
         a.mul = ep->d_mul;
         a.residual = ep->d_residual;
+    }
+    if (stream) {
+        switch (w->type) {
+            case ZQ_TYPE_Q4_0: return launch_stream<ZQ_TYPE_Q4_0>(w, xt, post, y, m_rows, a, st);
+            case ZQ_TYPE_Q4_1: return launch_stream<ZQ_TYPE_Q4_1>(w, xt, post, y, m_rows, a, st);
+            case ZQ_TYPE_Q8_0: return launch_stream<ZQ_TYPE_Q8_0>(w, xt, post, y, m_rows, a, st);
+            default: return ZQ_ERR_UNSUPPORTED;
+        }
     }
     switch (w->type) {
         case ZQ_TYPE_Q4_0: return launch_tc<ZQ_TYPE_Q4_0>(w, xt, post, y, m_rows, a, st);

@@ -542,6 +542,8 @@ size_t zq_matmul_workspace_bytes(const zq_weight* w, uint32_t m_rows, int act_mo
     if ((act_mode == ZQ_ACT_F32 && m_rows >= kGemmMinRows) || (act_mode == ZQ_ACT_F16 && m_rows > 0)) {
         return gemm_tc_workspace_bytes(w, m_rows);
     }
+    if (act_mode == ZQ_ACT_F32 && m_rows >= kStreamMinRowsF32 && gemm_stream_takes(w, m_rows))
+        return gemm_tc_workspace_bytes(w, m_rows);
     return 0;
 }
 
@@ -569,6 +571,11 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
                 return ZQ_ERR_BAD_ARG;
             return launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
         }
+        // 17-48 rows of a large matrix: the weight-streaming tensor-core form when the caller brought the workspace
+        // that zq_matmul_workspace_bytes asks for (two or three 16-row passes of the decode kernel otherwise)
+        if (m_rows >= kStreamMinRowsF32 && gemm_stream_takes(w, m_rows) && d_workspace &&
+            ((uintptr_t)d_workspace & 255) == 0 && workspace_bytes >= gemm_tc_workspace_bytes(w, m_rows))
+            return launch_gemm_tc(w, d_x, d_y, m_rows, epilogue, d_workspace, st);
         // passes of up to 16 activation rows over the weights
         int rc = launch_gemv_mma_passes_f32(w, d_x, d_y, m_rows, epilogue, st);
         if (rc == ZQ_ERR_LIMIT)  // activation image too large for shared memory: row-at-a-time kernel

@@ -151,6 +151,10 @@ int launch_convert_rows_f16(const float* x, __half* x16, float* post, uint32_t m
 int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
                    void* workspace, cudaStream_t st);
 size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows);
+// True when the weight-streaming form of the tensor-core GEMM (up to 128 activation rows, matrices of 12 288 rows
+// and more) serves the call.
+bool gemm_stream_takes(const zq_weight* w, uint32_t m_rows);
+constexpr uint32_t kStreamMinRowsF32 = 17;  // f32-activation calls from this many rows on take it when they bring a workspace
 
 // ---- fused decode-step launchers (ops.cu). `state` is device memory: state[0] = current token,
 // state[1] = its position. Kernels read the position there, so a captured launch sequence can be
