@@ -304,6 +304,32 @@ def sweep_extra(torch, zq, ggml, m_list=(1,)):
     return out
 
 
+def sweep_stream(torch, zq, ggml):
+    """The weight-streaming tensor-core form: 32 / 64 / 128 f32 activation rows against the vocabulary head and the
+    4096 -> 14336 projection, HBM-cold (every timed call on another weight copy), per call inside a CUDA graph.
+    `gbs` counts the algorithmic bytes (weights once, activations, outputs)."""
+    out = []
+    for qname in ("q4_0", "q8_0"):
+        for k, n in ((1152, 262144), (4096, 14336)):
+            raw = make_weight_bytes(qname, n, k, 42, "cuda")
+            wbytes = n * (k // 32) * BPB[qname]
+            copies = max(2, min(8, int(400e6 // wbytes) + 1))
+            ws = [zq.QuantWeight(raw, ggml.TYPE_IDS[qname], n, k) for _ in range(copies)]
+            for m in (32, 64, 128):
+                x = torch.randn(m, k, device="cuda")
+                y = torch.empty(m, n, device="cuda")
+                need = _lib_ws(zq, ws[0], m, zq.ACT_F32)
+                wsb = torch.empty(max(need, 256), dtype=torch.uint8, device="cuda")
+                fns = [(lambda w=w: zq.quant_matmul_no_grad(x, w, zq.ACT_F32, out=y, workspace=wsb)) for w in ws]
+                us = graph_time_us(torch, fns)
+                nbytes = algorithmic_bytes(qname, n, k, m)
+                out.append({"type": qname, "k": k, "n": n, "m": m, "act": "f32", "us": round(us, 2),
+                            "gbs": round(nbytes / us / 1e3, 1), "weights_gbs": round(wbytes / us / 1e3, 1),
+                            "copies": copies})
+            del ws, raw
+    return out
+
+
 def decode_bytes_per_token(name, cfg, ctx_mid):
     """Algorithmic HBM bytes of one decoded token: every quantised block once (plus GPT-2's f32 embedding
     matrix as the logits head) and the key / value rows the attention reads at context `ctx_mid`."""
@@ -774,6 +800,10 @@ def main():
                 line["extra"]["sweep_hbm_cold"] = sweep_extra(torch, zq, ggml, m_list=(1, 4, 16))
             except Exception as e:
                 line["extra"]["sweep_hbm_cold"] = {"error": repr(e)}
+            try:
+                line["extra"]["sweep_streaming_gemm"] = sweep_stream(torch, zq, ggml)
+            except Exception as e:  # noqa: BLE001
+                line["extra"]["sweep_streaming_gemm"] = {"error": repr(e)}
         print(json.dumps(line), flush=True)
     if use_dist:
         dist.barrier()
