@@ -561,3 +561,27 @@ def test_streaming_gemm_epilogue_and_row_counts(zq):
                                torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     assert rel_l2(y.cpu().numpy(), (x.double() @ wd.double().t()).float().cpu().numpy()) <= REL_L2_GUARD
+
+
+@pytest.mark.parametrize("qt,block_bytes", STREAM_TYPES)
+@pytest.mark.parametrize("m", [129, 256, 300, 520])
+def test_streaming_gemm_wide_sampled_rows(zq, oracle, qt, block_bytes, m):
+    """More than 128 activation rows on a matrix with a 256-row weight tile for every SM: the streaming kernel with
+    two activation tiles per CTA tile (both accumulators of tensor memory in one tile), activation rows tiled in
+    256s with a ragged last tile."""
+    k, n = 1152, 148 * 256 + 40
+    g = torch.Generator(device="cuda").manual_seed(m + int(qt))
+    raw_d = ggml.quantize(qt, torch.randn(n, k, generator=g, device="cuda") * 0.02)
+    qw = zq.QuantWeight(raw_d, qt, n, k)
+    x = torch.randn(m, k, generator=g, device="cuda")
+    bias = torch.randn(n, generator=g, device="cuda")
+    got = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, bias=bias)
+    rows = _sampled_rows(n)
+    sub = raw_d.view(n, k // 32 * block_bytes)[torch.from_numpy(rows).cuda()].cpu().numpy().reshape(-1)
+    want = oracle.linear(qt, sub, x.cpu().numpy(), len(rows), k, act_mode=0, n_threads=16) + bias.cpu().numpy()[rows]
+    got_s = got[:, torch.from_numpy(rows).cuda()].cpu().numpy()
+    assert rel_l2(got_s, want) <= REL_L2_GEMM_GUARD
+    full = x @ qw.dequantize().t() + bias
+    assert bool(((got - full).abs() <= 4e-3 * full.abs().max()).all())
+    from zignn_b200 import _lib
+    assert _lib.device_error() == 0

@@ -566,8 +566,9 @@ template <int TYPE, int TN>
 __global__ void __launch_bounds__(TS_THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                    const __half* __restrict__ xt, const float* __restrict__ post, float* __restrict__ y, uint32_t N,
-                   uint32_t M, uint32_t nbp, uint32_t act_rows, uint32_t interleave, uint32_t n_ring, uint32_t n_bring,
-                   uint32_t n_chunk_ring, unsigned int* err_word, TcEpilogue ep) {
+                   uint32_t M, uint32_t nbp, uint32_t act_rows, uint32_t interleave, uint32_t n_act, uint32_t m_tiles,
+                   uint32_t m_pad, uint32_t n_ring, uint32_t n_bring, uint32_t n_chunk_ring, unsigned int* err_word,
+                   TcEpilogue ep) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr uint32_t QB = Q8 ? 32 : 16;          // packed bytes per block
     constexpr uint32_t QUADB = 4 * QB;             // packed bytes per quad
@@ -605,8 +606,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     auto acc_empty = [&](uint32_t a) { return bar32 + (CB0 + 2 * TS_MAX_CHUNKS + 2 + a) * 8; };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // A CTA tile = TN weight rows x n_act activation tiles of 128 rows (n_act = 2 for more than 128 activation rows:
+    // both accumulators then belong to one tile). Tile t = blockIdx.x + i * gridDim.x covers weight tile t % row_tiles
+    // and activation rows [t / row_tiles * 128 * n_act, ...).
     const uint32_t row_tiles = (N + TN - 1) / TN;
-    const uint32_t nt = row_tiles > blockIdx.x ? (row_tiles - blockIdx.x - 1) / gridDim.x + 1 : 0;  // this CTA's tiles
+    const uint32_t tiles_total = row_tiles * m_tiles;
+    const uint32_t nt = tiles_total > blockIdx.x ? (tiles_total - blockIdx.x - 1) / gridDim.x + 1 : 0;  // this CTA's tiles
     const uint32_t n_quads = nbp / 4, n_stages = nbp / 2;
     const uint32_t n_chunks = (n_quads + CQ - 1) / CQ;  // per tile
     constexpr uint32_t tmem_cols = 2 * TN;               // two accumulators of TN columns
@@ -697,7 +702,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         uint32_t bslot = 0, bround = 0;
         bool alive = true;
         for (uint32_t ti = 0; ti < nt && alive; ++ti) {
-            const uint32_t row0 = (blockIdx.x + ti * gridDim.x) * TN;
+            const uint32_t tile = blockIdx.x + ti * gridDim.x;
+            const uint32_t mt = tile / row_tiles, row0 = (tile - mt * row_tiles) * TN;
             for (uint32_t c = 0; c < n_chunks && alive; ++c) {
                 if (cround > 0) alive = mbar_wait(cempty_bar(cslot), (cround - 1) & 1u, abort_p, err_word);
                 alive = __all_sync(0xFFFFFFFFu, alive);
@@ -727,7 +733,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bfull_bar(bslot)),
                                      "r"(btile_bytes)
                                      : "memory");
-                        const unsigned char* src = reinterpret_cast<const unsigned char*>(xt) + (size_t)sg * btile_bytes;
+                        const unsigned char* src = reinterpret_cast<const unsigned char*>(xt) +
+                                                   ((size_t)sg * m_pad + (size_t)mt * TS_ACT_ROWS * n_act) * 128u;
                         if (interleave) {
                             for (uint32_t q = 0; q < 4; ++q)
                                 bulk_copy_g2s(bring32 + bslot * bstride + q * 4096u, src + q * 1024u, 1024u, bfull_bar(bslot));
@@ -760,8 +767,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             uint32_t slot = 0, round = 0, bslot = 0, bround = 0;
             bool alive = true;
             for (uint32_t i = 0; i < nt && alive; ++i) {
-                const uint32_t acc = i & 1u;
-                if (i >= 2) alive = mbar_wait(acc_empty(acc), ((i >> 1) - 1) & 1u, abort_p, err_word);
+                // one activation tile: the two accumulators take turns; two: both belong to this tile
+                const uint32_t acc = n_act == 1 ? (i & 1u) : 0u;
+                if (n_act == 1) {
+                    if (i >= 2) alive = mbar_wait(acc_empty(acc), ((i >> 1) - 1) & 1u, abort_p, err_word);
+                } else if (i >= 1) {
+                    alive = mbar_wait(acc_empty(0), (i - 1) & 1u, abort_p, err_word);
+                }
                 if (!alive) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * TN;
@@ -772,9 +784,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     tc_fence_after();
                     const uint64_t x_desc = smem_desc_sw128(bring32 + bslot * bstride);
                     const uint64_t w_desc = smem_desc_sw128(smem32 + slot * W_STAGE);
+                    for (uint32_t a = 0; a < n_act; ++a) {
 #pragma unroll
-                    for (uint32_t k16 = 0; k16 < TC_BK / 16; ++k16)
-                        tc_mma_f16(d_tmem, x_desc + 2 * k16, w_desc + 2 * k16, idesc, (s | k16) != 0 ? 1u : 0u);
+                        for (uint32_t k16 = 0; k16 < TC_BK / 16; ++k16)
+                            tc_mma_f16(d_tmem + a * TN, x_desc + a * (16384u >> 4) + 2 * k16, w_desc + 2 * k16, idesc,
+                                       (s | k16) != 0 ? 1u : 0u);
+                    }
                     tc_commit(empty_bar(slot));
                     tc_commit(bempty_bar(bslot));
                     if (++slot == n_ring) {
@@ -801,26 +816,32 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         const uint32_t ew = (uint32_t)warp - TS_EPI_WARP0;
         float(*stage)[17] = epi_stage[ew];
         const uint32_t quarter = (uint32_t)warp & 3u;
-        // activation row of lane j of this quarter: 4 j + quarter when interleaved, 32 quarter + j otherwise
-        const uint32_t m = interleave ? 4u * (uint32_t)lane + quarter : lane_base + lane;
-        const bool mine = interleave ? quarter < M : lane_base < M;  // this warp's lane quarter holds real rows
-        const uint32_t rows_here = !mine ? 0u : interleave ? min(8u, (M - quarter + 3u) / 4u) : min(32u, M - lane_base);
-        const float scale = (m < M && (!interleave || lane < 8)) ? post[m] : 0.0f;
         const uint32_t hr = (uint32_t)lane >> 4, hc = (uint32_t)lane & 15u;  // half-warp and column of the store pass
         const bool plain = !ep.bias && !ep.gelu && !ep.mul && !ep.residual;
         bool alive = true;
         for (uint32_t i = 0; i < nt && alive; ++i) {
-            const uint32_t acc = i & 1u;
-            alive = mbar_wait(acc_full(acc), (i >> 1) & 1u, abort_p, err_word);
+            const uint32_t acc = n_act == 1 ? (i & 1u) : 0u;
+            alive = mbar_wait(acc_full(acc), (n_act == 1 ? (i >> 1) : i) & 1u, abort_p, err_word);
             alive = __all_sync(0xFFFFFFFFu, alive);
             if (!alive) break;
             tc_fence_after();
-            const uint32_t n0 = (blockIdx.x + i * gridDim.x) * TN;
-            if (mine) {
+            const uint32_t tile = blockIdx.x + i * gridDim.x;
+            const uint32_t mt = tile / row_tiles, n0 = (tile - mt * row_tiles) * TN;
+            for (uint32_t a = 0; a < n_act; ++a) {
+                // activation rows of this accumulator: lane j of this quarter holds row m0 + 4 j + quarter when
+                // interleaved (up to 32 rows in all), m0 + 32 quarter + j otherwise
+                const uint32_t m0 = (mt * n_act + a) * TS_ACT_ROWS;
+                const uint32_t m = interleave ? 4u * (uint32_t)lane + quarter : m0 + lane_base + lane;
+                const uint32_t first = interleave ? quarter : m0 + lane_base;  // first row of this quarter
+                if (first >= M) continue;                                         // uniform over the warp
+                const uint32_t rows_here = interleave ? min(8u, (M - quarter + 3u) / 4u) : min(32u, M - first);
+                const float scale = (m < M && (!interleave || lane < 8)) ? post[m] : 0.0f;
+                const uint32_t m_step = interleave ? 8u : 2u;
+                const uint32_t m_first = interleave ? 4u * hr + quarter : first + hr;
                 for (uint32_t c = 0; c < (uint32_t)TN; c += 16) {
                     if (n0 + c >= N) break;  // uniform over the warp
                     uint32_t v16[16];
-                    tc_ld16(tmem_base + (lane_base << 16) + acc * TN + c, v16);
+                    tc_ld16(tmem_base + (lane_base << 16) + (acc + a) * TN + c, v16);
                     tc_wait_ld();
 #pragma unroll
                     for (int k = 0; k < 16; ++k) stage[lane][k] = __uint_as_float(v16[k]) * scale;
@@ -828,8 +849,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     const uint32_t n = n0 + c + hc;
                     if (n < N) {
                         // half-warp hr takes the block's rows hr, hr + 2, ...: 64 contiguous bytes of one row of y per store
-                        const uint32_t m_step = interleave ? 8u : 2u;
-                        const uint32_t m_first = interleave ? 4u * hr + quarter : lane_base + hr;
                         if (plain) {
                             float* dst = y + (size_t)m_first * N + n;
                             const size_t step = (size_t)m_step * N;
@@ -921,21 +940,35 @@ int tensor_map_2d(const void* base, uint64_t row_bytes, uint64_t rows, uint32_t 
     return r == CUDA_SUCCESS ? ZQ_OK : ZQ_ERR_UNSUPPORTED;
 }
 
+// More than 128 activation rows: the same kernel with two activation tiles per CTA tile (256 weight rows x 256
+// activation rows, both accumulators in use). Measured against the large-batch kernel (Q4_0, TFLOP/s): vocabulary
+// head at 512 rows 736 against 654, at 2048 rows 777 against 625; 4096 -> 14336 at 2048 rows 737 against 738;
+// 14336 -> 4096 699 against 776 (128 CTA tiles for 148 SMs). Its two-deep rings (two 32 KB weight tiles, two 32 KB
+// activation tiles and two chunks fill shared memory) leave the commit and copy latencies exposed, so it is taken
+// only where every SM gets whole weight tiles of its own.
+inline bool stream_wide_takes(const zq_weight* w, uint32_t m_rows) {
+    return m_rows > kStreamMaxRows && (w->out_dim + 255u) / 256u >= (uint32_t)sm_count();
+}
+
 template <int TYPE, int TN>
 int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
                      cudaStream_t st) {
     auto kern = gemm_stream_kernel<TYPE, TN>;
-    const uint32_t act_rows = stream_act_rows(M);
+    const bool wide = M > kStreamMaxRows;              // two activation tiles of 128 rows per CTA tile
+    const uint32_t n_act = wide ? 2u : 1u;
+    const uint32_t act_rows = wide ? 256u : stream_act_rows(M);
+    const uint32_t m_tiles = wide ? (M + 255u) / 256u : 1u;
+    const uint32_t m_pad = wide ? m_tiles * 256u : act_rows;
     const uint32_t btile_bytes = act_rows * 128u;
     constexpr uint32_t W_STAGE = TN * 128u, CHUNK_BYTES = TN * 128u + TN * 32u;
     int dev = 0, max_smem = 0;
     ZQ_CUDA(cudaGetDevice(&dev));
     ZQ_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    // Shared memory: activation tiles (16-32 KB), then fp16 weight tiles, then packed chunks. A weight tile is free
+    // Shared memory: activation tiles (16-64 KB), then fp16 weight tiles, then packed chunks. A weight tile is free
     // again only when its MMAs have run and their commit has arrived (half a microsecond after issue, measured),
     // so the ring of weight tiles must be deep: four of 256 rows or six of 128 rows where that leaves two chunks.
     const uint32_t budget = (uint32_t)max_smem - 1024u - 10240u;  // alignment slack, static shared memory
-    const uint32_t interleave = stream_quarter_rows(M) ? 1u : 0u;
+    const uint32_t interleave = (!wide && stream_quarter_rows(M)) ? 1u : 0u;
     uint32_t n_bring = (16u * 1024u) / btile_bytes;
     if (n_bring > (uint32_t)TS_MAX_BTILES) n_bring = TS_MAX_BTILES;
     if (n_bring < 2) n_bring = 2;
@@ -950,8 +983,9 @@ int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, fl
     const size_t smem = (size_t)n_ring * W_STAGE + bring_bytes + (size_t)n_chunk_ring * CHUNK_BYTES + 1024;
     ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const uint32_t row_tiles = (w->out_dim + TN - 1) / TN;
+    const uint64_t tiles_total = (uint64_t)row_tiles * m_tiles;
     const uint32_t sms = (uint32_t)sm_count();
-    const uint32_t grid = row_tiles < sms ? row_tiles : sms;
+    const uint32_t grid = tiles_total < sms ? (uint32_t)tiles_total : sms;
     unsigned int* err_word = nullptr;
     int rc = device_error_word(&err_word);
     if (rc != ZQ_OK) return rc;
@@ -960,8 +994,8 @@ int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, fl
     rc = tensor_map_2d(w->qs, (uint64_t)w->nbp * w->qb, w->out_dim, 128, TN, true, &wmap);
     if (rc == ZQ_OK) rc = tensor_map_2d(w->sc, (uint64_t)w->scp * SB, w->out_dim, StreamScales<TYPE>::kBox, TN, false, &smap);
     if (rc != ZQ_OK) return rc;
-    kern<<<grid, TS_THREADS, smem, st>>>(wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, interleave, n_ring,
-                                         n_bring, n_chunk_ring, err_word, ep);
+    kern<<<grid, TS_THREADS, smem, st>>>(wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, interleave, n_act, m_tiles,
+                                         m_pad, n_ring, n_bring, n_chunk_ring, err_word, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -970,12 +1004,14 @@ template <int TYPE>
 int launch_stream(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
                   cudaStream_t st) {
     // 256-row tiles do twice the work per tensor-core instruction; 128-row tiles when those would leave SMs idle
-    if ((w->out_dim + 255u) / 256u >= (uint32_t)sm_count()) return launch_stream_tn<TYPE, 256>(w, xt, post, y, M, ep, st);
+    if (M > kStreamMaxRows || (w->out_dim + 255u) / 256u >= (uint32_t)sm_count())
+        return launch_stream_tn<TYPE, 256>(w, xt, post, y, M, ep, st);
     return launch_stream_tn<TYPE, 128>(w, xt, post, y, M, ep, st);
 }
 
 inline bool stream_takes(const zq_weight* w, uint32_t m_rows) {
-    return m_rows <= kStreamMaxRows && (w->out_dim + TC_BN - 1) / TC_BN >= kStreamMinTiles;
+    if (m_rows > kStreamMaxRows) return stream_wide_takes(w, m_rows);
+    return (w->out_dim + TC_BN - 1) / TC_BN >= kStreamMinTiles;
 }
 
 // rows per CTA tile and padded row count for m_rows activation rows
@@ -1026,7 +1062,8 @@ bool gemm_stream_takes(const zq_weight* w, uint32_t m_rows) { return stream_take
 
 size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows) {
     uint32_t n_mma, m_pad;
-    tc_tiling(m_rows, &n_mma, &m_pad);  // never less than the streaming form's padding to 16 rows
+    tc_tiling(m_rows, &n_mma, &m_pad);  // never less than the streaming form's padding to 16 rows ...
+    if (m_rows > 128 && m_pad < ((m_rows + 255u) / 256u) * 256u) m_pad = ((m_rows + 255u) / 256u) * 256u;  // ... or to 256
     const size_t xb = ((size_t)(w->nbp / 2) * m_pad * 64 * sizeof(__half) + 255) & ~(size_t)255;
     const size_t pb = ((size_t)m_rows * sizeof(float) + 255) & ~(size_t)255;
     return xb + pb;
@@ -1038,7 +1075,7 @@ int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows
     uint32_t n_mma, m_pad;
     tc_tiling(m_rows, &n_mma, &m_pad);
     const bool stream = stream_takes(w, m_rows);
-    if (stream) m_pad = stream_act_rows(m_rows);
+    if (stream) m_pad = m_rows > kStreamMaxRows ? ((m_rows + 255u) / 256u) * 256u : stream_act_rows(m_rows);
     const uint32_t n_seg = w->nbp / 2;
     const size_t xb = ((size_t)n_seg * m_pad * 64 * sizeof(__half) + 255) & ~(size_t)255;
     __half* xt = static_cast<__half*>(workspace);
