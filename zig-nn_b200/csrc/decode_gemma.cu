@@ -67,7 +67,8 @@ struct DMat {
     uint32_t chunk_quads; // quads per piece (the last piece of a row may be shorter); at most 16
     uint32_t tiles_div, tiles_rem;  // n_tiles / grid and n_tiles % grid: CTA c owns tiles_div + (c < tiles_rem) tiles
     uint32_t chunk_q_pitch;         // bytes between the rows of a piece in a ring slot (chunks > 1)
-    uint32_t pad_[2];
+    uint32_t chunks_magic;          // floor(2^32 / chunks) for fast_divmod
+    uint32_t pad_;
 };
 
 struct alignas(16) DLayer {
@@ -848,7 +849,12 @@ __device__ __noinline__ uint32_t gemv_phase(const DMat& m, uint32_t unit_base, i
     return base + mine * C;
 }
 
-// The producer's side of gemv_phase: issue this CTA's units of `m` into the ring, in the same order.
+// The producer's side of gemv_phase: issue this CTA's units of `m` into the ring. The whole producer warp calls
+// it: lane j takes units j, j + L, ... of the phase (L = min(32, ring slots): the units of one pass lie in different
+// slots, and a slot's uses follow each other in one lane). One thread doing it alone needed half a microsecond
+// per unit, 110 us for the 221 units of the vocabulary head. The warp meets again at the end of a phase: a lane
+// that ran ahead into the next matrix could otherwise wait on a slot whose previous use another lane has not
+// issued yet, and a parity wait cannot tell those two phases apart. Returns false (to every lane) on a timeout.
 __device__ __noinline__ bool produce_phase(const DMat& m, uint32_t* unit_base,
                                            uint32_t* issued) {
     const Cta c = make_cta();
@@ -858,19 +864,26 @@ __device__ __noinline__ bool produce_phase(const DMat& m, uint32_t* unit_base,
     const uint32_t mine = m.tiles_div + (cta < m.tiles_rem ? 1u : 0u);
     const uint32_t base = *unit_base;
     *unit_base = base + mine * C;
+    *issued = base + mine * C;  // (an upper bound while the phase runs; exact once it has ended)
     const uint32_t rqb = m.row_q_bytes, rsb = m.row_s_bytes, N = m.n_rows;
     const uint32_t QUAD = m.type == ZQ_TYPE_Q8_0 ? 128u : 64u, SB = m.type == ZQ_TYPE_Q4_1 ? 4u : 2u;
     const uint32_t n_slots = p.n_slots, slot_magic = p.slot_magic;
+    const uint32_t lanes = n_slots < 32u ? n_slots : 32u;
     const uint8_t* qs = m.qs;
     const uint8_t* sc = m.sc;
-    uint32_t i = 0, ch = 0;
+    bool ok = true;
 #pragma unroll 1
-    for (uint32_t n = 0; n < mine * C; ++n) {
+    for (uint32_t n = (uint32_t)c.lane; ok && (uint32_t)c.lane < lanes && n < mine * C; n += lanes) {
+        uint32_t i, ch;
+        fast_divmod(n, C, m.chunks_magic, i, ch);
         const uint32_t gi = base + n;
         uint32_t slot, use;
         fast_divmod(gi, n_slots, slot_magic, use, slot);
         const uint32_t tile = cta + i * G;
-        if (use > 0 && !slot_wait(c, p, c.empty0 + slot * 8, (use - 1) & 1u)) return false;
+        if (use > 0 && !slot_wait(c, p, c.empty0 + slot * 8, (use - 1) & 1u)) {
+            ok = false;
+            break;
+        }
         const uint32_t dst = c.smem32 + p.off_ring + slot * p.slot_bytes;
         const uint32_t bar = c.full0 + slot * 8;
         const UnitGeom u = unit_geom(m, tile, ch);
@@ -903,13 +916,8 @@ __device__ __noinline__ bool produce_phase(const DMat& m, uint32_t* unit_base,
                 bulk_copy_g2s(dst + u.s_off + r * u.s_pitch, sc + row * rsb + sa, sbytes, bar);
             }
         }
-        *issued = gi + 1;
-        if (++ch == C) {
-            ch = 0;
-            ++i;
-        }
     }
-    return true;
+    return __all_sync(0xFFFFFFFFu, ok);  // also where the warp meets again
 }
 
 // Embedding row of `tok`, dequantised and scaled (gemma3.zig:800-803, 855-871): q*d, then *scale.
@@ -1201,29 +1209,28 @@ gemma3_decode_kernel(const __grid_constant__ DParams p_in, uint32_t n_steps, int
 
     if (c.warp == kConsumerWarps) {
         // ---------------------------------------------------------------- producer warp
-        if (c.lane == 0) {
-            bool ok = true;
-            uint32_t issued = 0;
-            for (uint32_t step = 0; ok && step < n_steps; ++step) {
-                for (uint32_t l = 0; ok && l < p.n_layer; ++l) {
-                    const DLayer& L = layers[l];
-                    ok = produce_phase(L.qkv, &unit_base, &issued) && produce_phase(L.o, &unit_base, &issued) &&
-                         produce_phase(L.gate_up, &unit_base, &issued) &&
-                         produce_phase(L.down, &unit_base, &issued);
-                }
-                if (ok && want_logits) ok = produce_phase(p.head, &unit_base, &issued);
+        bool ok = true;
+        uint32_t issued = 0;
+        for (uint32_t step = 0; ok && step < n_steps; ++step) {
+            for (uint32_t l = 0; ok && l < p.n_layer; ++l) {
+                const DLayer& L = layers[l];
+                ok = produce_phase(L.qkv, &unit_base, &issued) && produce_phase(L.o, &unit_base, &issued) &&
+                     produce_phase(L.gate_up, &unit_base, &issued) &&
+                     produce_phase(L.down, &unit_base, &issued);
             }
-            if (!ok) {
-                // Stopped early: copies already issued still land in this CTA's shared memory. Wait (bounded)
-                // for the newest fill of every slot before the CTA may retire.
-                for (uint32_t s = 0; s < p.n_slots && s < issued; ++s) {
-                    const uint32_t last = issued - 1 - ((issued - 1 - s) % p.n_slots);  // newest unit index in slot s
-                    const uint32_t use = last / p.n_slots;
-                    for (uint32_t i = 0; i < (1u << 16); ++i)
-                        if (mbar_try_wait(c.full0 + s * 8, use & 1u)) break;
-                }
+            if (ok && want_logits) ok = produce_phase(p.head, &unit_base, &issued);
+        }
+        if (!ok && c.lane == 0) {
+            // Stopped early: copies already issued still land in this CTA's shared memory. Wait (bounded)
+            // for the newest fill of every slot before the CTA may retire.
+            for (uint32_t s = 0; s < p.n_slots && s < issued; ++s) {
+                const uint32_t last = issued - 1 - ((issued - 1 - s) % p.n_slots);  // newest unit index in slot s
+                const uint32_t use = last / p.n_slots;
+                for (uint32_t i = 0; i < (1u << 16); ++i)
+                    if (mbar_try_wait(c.full0 + s * 8, use & 1u)) break;
             }
         }
+        __syncwarp();
         return;
     }
 
@@ -1396,7 +1403,7 @@ bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split, uint
     d->nbp = w->nbp;
     d->row_q_bytes = w->nbp * w->qb;
     d->row_s_bytes = w->scp * (w->type == ZQ_TYPE_Q4_1 ? 4u : 2u);
-    d->pad_[0] = d->pad_[1] = 0;
+    d->pad_ = 0;
     d->split = split ? 1u : 0u;
     if (split && (w->out_dim & 1u)) return false;
     const uint32_t n = split ? w->out_dim / 2 : w->out_dim;  // rows to hand out (pairs of rows when split)
@@ -1407,6 +1414,7 @@ bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split, uint
     d->n_tiles = tiles(r);
     d->tiles_div = d->n_tiles / grid;
     d->tiles_rem = d->n_tiles % grid;
+    d->chunks_magic = 0xFFFFFFFFu;  // set below with the chunk count
     const uint32_t QUAD = w->qb * 4, SB = w->type == ZQ_TYPE_Q4_1 ? 4u : 2u, nq = w->nbp / 4;
     // A piece has at most 16 quads (the shared slot release of gemv_phase counts on it). Rows of a piece of a
     // 4-bit matrix lie an odd multiple of 64 bytes apart, so that the eight row segments of one load cover all banks.
@@ -1424,6 +1432,7 @@ bool describe(DMat* d, const zq_weight* w, uint32_t slot_bytes, bool split, uint
         d->chunks = (nq + cq - 1) / cq;
         d->chunk_q_pitch = q_pitch(cq);
     }
+    d->chunks_magic = d->chunks <= 1 ? 0xFFFFFFFFu : (uint32_t)(0x100000000ull / d->chunks);
     return true;
 }
 
