@@ -112,6 +112,19 @@ struct DParams {
 // ---- small device helpers --------------------------------------------------------------------
 
 __device__ __forceinline__ void cbar() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
+// The consumers' barrier with an OR over a flag of every thread: all get the same answer from one barrier.
+__device__ __forceinline__ bool cbar_or(bool v) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)v), "n"(kConsumers)
+        : "memory");
+    return r != 0;
+}
 
 __device__ __noinline__ float exp_f32(float x) { return (float)exp((double)x); }
 __device__ __noinline__ float gelu_tanh(float v) {
@@ -965,6 +978,29 @@ __device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
     (void)p;
     const uint32_t D = p.D, nh = p.n_head, nkv = p.n_kv, group = p.group, kv_dim = nkv * D;
     const uint32_t nvec = nh + nkv, nqk = nvec * D, nall = nqk + kv_dim;
+    // The key rows of this CTA's first tile of (position, head) pairs are old cache rows: requested before the
+    // exchange is polled, they arrive under the wait, the norms and the rotation (one round trip to L2 less).
+    const uint32_t jobs = kv_len * nh, tiles = (jobs + 31) >> 5;
+    const uint32_t l = c.tid & 15u, js = c.tid >> 4;
+    const uint32_t dim16 = D & ~15u;
+    float kpre[16];
+    bool have_kpre = false;
+    if (blockIdx.x < tiles && dim16 <= 256u) {
+        const uint32_t job = blockIdx.x * 32 + js;
+        const uint32_t jc = job < jobs ? job : jobs - 1;
+        uint32_t pi, h, kvh, hrem;
+        fast_divmod(jc, nh, p.magic_nh, pi, h);
+        fast_divmod(h, group, p.magic_group, kvh, hrem);
+        if (pi != kv_len - 1) {
+            const float* kr = L.kc + (size_t)(kv_start + pi) * kv_dim + (size_t)kvh * D;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const uint32_t d = l + 16 * u;
+                kpre[u] = d < dim16 ? __ldcg(kr + d) : 0.0f;
+            }
+            have_kpre = true;
+        }
+    }
     // norm weights of the pairs this thread rotates: requested before the exchange is polled
     const uint32_t half = p.half_d, pairs = nvec * half;
     float2 nw[2];
@@ -1022,9 +1058,6 @@ __device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
             L.vc[(size_t)pos * kv_dim + i] = vnew[i];
         }
     }
-    const uint32_t jobs = kv_len * nh, tiles = (jobs + 31) >> 5;
-    const uint32_t l = c.tid & 15u, js = c.tid >> 4;
-    const uint32_t dim16 = D & ~15u;
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)D));
 #pragma unroll 1
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
@@ -1041,10 +1074,15 @@ __device__ __noinline__ bool scores_phase(const DLayer& L, uint32_t pos,
 #pragma unroll 1
         for (uint32_t d0 = l; d0 < dim16; d0 += 16 * 16) {
             float kv[16];
+            if (have_kpre && tile == blockIdx.x) {
 #pragma unroll
-            for (int u = 0; u < 16; ++u) {
-                const uint32_t d = d0 + 16 * u;
-                kv[u] = d < dim16 ? (from_smem ? kr[d] : __ldcg(kr + d)) : 0.0f;
+                for (int u = 0; u < 16; ++u) kv[u] = kpre[u];
+            } else {
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    const uint32_t d = d0 + 16 * u;
+                    kv[u] = d < dim16 ? (from_smem ? kr[d] : __ldcg(kr + d)) : 0.0f;
+                }
             }
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
@@ -1109,6 +1147,14 @@ __device__ __noinline__ bool softmax_v_phase(const DLayer& L, uint32_t kv_start,
                 }
             }
         };
+        // The first tile's value rows do not depend on the scores: requested now, they arrive under the softmax.
+        const uint32_t n_first = min(kVTile, kv_len);
+        float vpre[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t k = (uint32_t)c.tid + u * kConsumers, q = k >> 3, d = k & 7u;
+            vpre[u] = k < n_first * 8 ? (q + 1 < kv_len ? __ldcg(vbase + (size_t)q * kv_dim + d) : vcur[d]) : 0.0f;
+        }
         {
             const unsigned long long* sh_ = scores_in + (size_t)h * p.max_len;
             float mx = -INFINITY;
@@ -1153,7 +1199,12 @@ __device__ __noinline__ bool softmax_v_phase(const DLayer& L, uint32_t kv_start,
             cbar();
         }
         const uint32_t n_tiles = (kv_len + kVTile - 1) / kVTile;
-        make_products(0, (uint32_t)c.tid, (uint32_t)kConsumers);
+        static_assert(kVTile * 8 == 4 * kConsumers, "the first tile's products: four per thread");
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t k = (uint32_t)c.tid + u * kConsumers, pi = k >> 3, d = k & 7u;
+            if (k < n_first * 8) prod[d * PITCH + pi] = __fmul_rn(w[pi], vpre[u]);
+        }
         cbar();
         float acc = 0.0f;
 #pragma unroll 1
@@ -1252,13 +1303,10 @@ gemma3_decode_kernel(const __grid_constant__ DParams p_in, uint32_t n_steps, int
     do {                                                                                        \
         if (p.prof && c.tid == 0 && n_stamp < p.prof_cap) p.prof[(size_t)blockIdx.x * p.prof_cap + n_stamp++] = clock64(); \
     } while (0)
-    // uniform exit: s_abort is read between two barriers that every consumer thread passes
-#define ZQ_CHECK_ABORT()         \
-    do {                         \
-        cbar();                  \
-        const int a__ = S.abort; \
-        cbar();                  \
-        if (a__) return;         \
+    // uniform exit: every consumer thread brings its view of the abort flag to one barrier and gets their OR
+#define ZQ_CHECK_ABORT()                      \
+    do {                                      \
+        if (cbar_or(S.abort != 0)) return;    \
     } while (0)
 
     for (uint32_t step = 0; step < n_steps; ++step) {
