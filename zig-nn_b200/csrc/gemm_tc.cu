@@ -488,8 +488,8 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
 //     on the chunk's mbarrier; nothing of it passes through the load pipe;
 //   * the 16 converting warps turn a stage (64 K of the TN rows) into the fp16 tile together, reading packed
 //     words and scales from shared memory (conflict-free through the swizzle);
-//   * the stage's activation tile (rows x 128 bytes) is one bulk copy into a ring of its own, issued by the copy
-//     warp well ahead;
+//   * the stage's activation tile (rows x 128 bytes) is one bulk copy into a ring of its own, issued by a second
+//     copy warp well ahead;
 //   * two accumulators in tensor memory take turns; four more warps drain the finished one (tcgen05.ld, scale,
 //     epilogue, 64-byte stores) while the next tile's stages flow.
 // Every wait is bounded; on a timeout the kernel records it, all roles leave their loops and tensor memory is
@@ -497,8 +497,10 @@ gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, c
 constexpr int TS_CONVERT_WARPS = 16;
 constexpr int TS_MMA_WARP = TS_CONVERT_WARPS;
 constexpr int TS_EPI_WARP0 = TS_MMA_WARP + 1;   // four warps: their ids mod 4 cover the four lane quarters
-constexpr int TS_COPY_WARP = TS_EPI_WARP0 + 4;
-constexpr int TS_THREADS = (TS_COPY_WARP + 1) * 32;  // 22 warps
+constexpr int TS_COPY_WARP = TS_EPI_WARP0 + 4;   // packed chunks
+constexpr int TS_XCOPY_WARP = TS_COPY_WARP + 1;  // activation tiles (a warp of its own: one warp serving both rings
+                                                 // waits for a free slot of one while the other runs dry)
+constexpr int TS_THREADS = (TS_XCOPY_WARP + 1) * 32;  // 23 warps
 constexpr int TS_MAX_STAGES = 6;    // fp16 weight tiles (TN x 128 bytes each)
 constexpr int TS_MAX_BTILES = 16;   // activation tiles
 constexpr int TS_MAX_CHUNKS = 4;
@@ -697,9 +699,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             }
         }
     } else if (warp == TS_COPY_WARP) {
-        // ================= copy warp: packed quants, scales and activation tiles =================
+        // ================= copy warp: packed quants and scales =================
         uint32_t cslot = 0, cround = 0;
-        uint32_t bslot = 0, bround = 0;
         bool alive = true;
         for (uint32_t ti = 0; ti < nt && alive; ++ti) {
             const uint32_t tile = blockIdx.x + ti * gridDim.x;
@@ -708,7 +709,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 if (cround > 0) alive = mbar_wait(cempty_bar(cslot), (cround - 1) & 1u, abort_p, err_word);
                 alive = __all_sync(0xFFFFFFFFu, alive);
                 if (!alive) break;
-                const uint32_t nqc = min(CQ, n_quads - c * CQ);
                 if (lane == 0) {
                     // boxes are written whole (zeros beyond the map's edges)
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(cfull_bar(cslot)),
@@ -724,30 +724,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     cslot = 0;
                     ++cround;
                 }
-                // the activation tiles of the chunk's stages
-                for (uint32_t sg = 2 * c * CQ; sg < 2 * (c * CQ + nqc) && alive; ++sg) {
-                    if (bround > 0) alive = mbar_wait(bempty_bar(bslot), (bround - 1) & 1u, abort_p, err_word);
-                    alive = __all_sync(0xFFFFFFFFu, alive);
-                    if (!alive) break;
-                    if (lane == 0) {
-                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bfull_bar(bslot)),
-                                     "r"(btile_bytes)
-                                     : "memory");
-                        const unsigned char* src = reinterpret_cast<const unsigned char*>(xt) +
-                                                   ((size_t)sg * m_pad + (size_t)mt * TS_ACT_ROWS * n_act) * 128u;
-                        if (interleave) {
-                            for (uint32_t q = 0; q < 4; ++q)
-                                bulk_copy_g2s(bring32 + bslot * bstride + q * 4096u, src + q * 1024u, 1024u, bfull_bar(bslot));
-                        } else {
-                            bulk_copy_g2s(bring32 + bslot * bstride, src, btile_bytes, bfull_bar(bslot));
-                        }
-                    }
-                    __syncwarp();
-                    if (++bslot == n_bring) {
-                        bslot = 0;
-                        ++bround;
-                    }
-                }
             }
         }
         if (!alive) {
@@ -756,6 +732,38 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             for (uint32_t s = 0; s < n_chunk_ring; ++s)
                 for (uint32_t i = 0; i < (1u << 16); ++i)
                     if (mbar_try_wait(cfull_bar(s), 0) || mbar_try_wait(cfull_bar(s), 1)) break;
+        }
+    } else if (warp == TS_XCOPY_WARP) {
+        // ================= copy warp: the activation tiles of the stages =================
+        uint32_t bslot = 0, bround = 0;
+        bool alive = true;
+        for (uint32_t ti = 0; ti < nt && alive; ++ti) {
+            const uint32_t mt = (blockIdx.x + ti * gridDim.x) / row_tiles;
+            for (uint32_t sg = 0; sg < n_stages && alive; ++sg) {
+                if (bround > 0) alive = mbar_wait(bempty_bar(bslot), (bround - 1) & 1u, abort_p, err_word);
+                alive = __all_sync(0xFFFFFFFFu, alive);
+                if (!alive) break;
+                if (lane == 0) {
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bfull_bar(bslot)),
+                                 "r"(btile_bytes)
+                                 : "memory");
+                    const unsigned char* src = reinterpret_cast<const unsigned char*>(xt) +
+                                               ((size_t)sg * m_pad + (size_t)mt * TS_ACT_ROWS * n_act) * 128u;
+                    if (interleave) {
+                        for (uint32_t q = 0; q < 4; ++q)
+                            bulk_copy_g2s(bring32 + bslot * bstride + q * 4096u, src + q * 1024u, 1024u, bfull_bar(bslot));
+                    } else {
+                        bulk_copy_g2s(bring32 + bslot * bstride, src, btile_bytes, bfull_bar(bslot));
+                    }
+                }
+                __syncwarp();
+                if (++bslot == n_bring) {
+                    bslot = 0;
+                    ++bround;
+                }
+            }
+        }
+        if (!alive) {
             for (uint32_t s = 0; s < n_bring; ++s)
                 for (uint32_t i = 0; i < (1u << 16); ++i)
                     if (mbar_try_wait(bfull_bar(s), 0) || mbar_try_wait(bfull_bar(s), 1)) break;
