@@ -465,6 +465,12 @@ int zq_gemma3_seq_len_of(const zq_gemma3* m, uint32_t seq, uint32_t* seq_len);
 #define ZQ_DECODE_PERSISTENT 2
 int zq_gemma3_set_decode_mode(zq_gemma3* m, int mode);
 int zq_gemma3_decode_mode(const zq_gemma3* m, int* mode);
+/* The same choice for the GPT-2 engine (gpt2.zig:423-509). Its persistent kernel computes with f32 multiply-adds
+ * and tree reductions in a fixed order: results agree with the launch sequence within this path's tolerance
+ * (about 1e-6 relative L2 on logits, identical greedy tokens), not bit for bit. ZQ_ERR_UNSUPPORTED for
+ * ZQ_DECODE_PERSISTENT when a linear layer of the model is f32 or a row does not fit a ring slot. */
+int zq_gpt2_set_decode_mode(zq_gpt2* m, int mode);
+int zq_gpt2_decode_mode(const zq_gpt2* m, int* mode);
 /* Per-phase timing of one decode step, the device-side counterpart of gemma3.ProfileStats
  * (gemma3.zig:35-92, filled at :417-491): the persistent kernel runs one step (like decode_next) and every
  * CTA records its SM cycle counter at each phase boundary. h_cycles[n_ctas][capacity] receives the stamps of

@@ -286,3 +286,57 @@ def test_engines_from_gguf_files_match_engines_from_memory(zq, oracle, tmp_path)
     r = f.get_tensor_raw_bytes("blk.0.ffn_down.weight")
     want = oracle.dequantize(r.type_, np.asarray(r.data), r.n_elem)
     assert np.array_equal(f.load_tensor_f32("blk.0.ffn_down.weight"), want)
+
+
+@pytest.mark.parametrize("qtype", [ggml.Q4_0, ggml.Q4_1, ggml.Q8_0])
+def test_gpt2_persistent_decode_kernel_against_the_launch_sequence(zq, qtype):
+    """GPT-2 decode as one cooperative kernel per token against the captured launch sequence. This path's bar is
+    a tolerance (f32 activations, no quantiser in the loop): logits agree to 1e-5 relative L2 step by step, the
+    greedy tokens of the on-device loop are the same, and a run repeats itself bit for bit."""
+    host = hostmodel.Gpt2Host.synthetic(GPT2_TINY, qtype=qtype, seed=5, std=0.08).randomize_small_params()
+    prompt = np.random.default_rng(3).integers(0, GPT2_TINY["vocab"], size=13)
+    a, b = zq.Gpt2(host), zq.Gpt2(host)
+    assert a.decode_mode == zq.DECODE_PERSISTENT
+    b.set_decode_mode(zq.DECODE_LAUNCH_SEQUENCE)
+    assert b.decode_mode == zq.DECODE_LAUNCH_SEQUENCE
+    la, lb = a.prefill(prompt), b.prefill(prompt)
+    assert torch.equal(la, lb)  # prefill chunks take the batched path in both
+    tok = int(la.argmax())
+    first = tok
+    for step in range(30):
+        la, lb = a.decode_next(tok), b.decode_next(tok)
+        assert rel_l2(la.cpu().numpy(), lb.cpu().numpy()) <= 1e-5, step
+        assert int(la.argmax()) == int(lb.argmax()), step
+        tok = int(lb.argmax())
+    ta, tb = a.decode_greedy(tok, 25), b.decode_greedy(tok, 25)
+    assert list(ta) == list(tb)
+    assert a.seq_len == b.seq_len == 13 + 30 + 25
+    # the same run again gives the same bits
+    c = zq.Gpt2(host)
+    c.prefill(prompt)
+    tok = first
+    for step in range(30):
+        lc = c.decode_next(tok)
+        tok = int(lc.argmax())
+    assert torch.equal(lc, la)
+    # a single-token prefill and a cache-only step go through the kernel too
+    a.reset_cache(), b.reset_cache()
+    assert rel_l2(a.prefill([5]).cpu().numpy(), b.prefill([5]).cpu().numpy()) <= 1e-5
+    assert rel_l2(a.decode_next(7).cpu().numpy(), b.decode_next(7).cpu().numpy()) <= 1e-5
+    from zignn_b200 import _lib
+    assert _lib.device_error(clear=False) == 0
+
+
+def test_gpt2_persistent_decode_kernel_full_size_greedy(zq):
+    """GPT-2 small, Q4_0: 128 greedy tokens from the on-device loop of the persistent kernel equal those of the
+    launch sequence (the workload of the decode benchmark)."""
+    host = hostmodel.Gpt2Host.synthetic(hostmodel.GPT2_SMALL, qtype=ggml.Q4_0, seed=42, std=0.02, device="cuda")
+    prompt = np.random.default_rng(44).integers(0, 50257, size=32)
+    a, b = zq.Gpt2(host), zq.Gpt2(host)
+    b.set_decode_mode(zq.DECODE_LAUNCH_SEQUENCE)
+    la, lb = a.prefill(prompt), b.prefill(prompt)
+    tok = int(la.argmax())
+    ta, tb = a.decode_greedy(tok, 128), b.decode_greedy(tok, 128)
+    assert list(ta) == list(tb)
+    la, lb = a.decode_next(int(ta[-1])), b.decode_next(int(tb[-1]))
+    assert rel_l2(la.cpu().numpy(), lb.cpu().numpy()) <= 1e-5

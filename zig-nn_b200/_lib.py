@@ -85,6 +85,8 @@ SIGNATURES = {
     "zq_gemma3_decode_next_batch": (i, [vp, vp, vp, P(vp)]),
     "zq_gemma3_seq_len_of": (i, [vp, u32, P(u32)]),
     "zq_gemma3_set_decode_mode": (i, [vp, i]),
+    "zq_gpt2_set_decode_mode": (i, [vp, i]),
+    "zq_gpt2_decode_mode": (i, [vp, P(i)]),
     "zq_gemma3_decode_mode": (i, [vp, P(i)]),
     "zq_gemma3_profile_step": (i, [vp, u32, vp, vp, u32, P(u32)]),
 }

@@ -525,6 +525,16 @@ class Gpt2(_Engine):
     """gpt2(C): init / prefill / decode_next (src/models/gpt2.zig:236,423,443)."""
     _prefix = "zq_gpt2"
 
+    def set_decode_mode(self, mode):
+        """DECODE_AUTO / DECODE_LAUNCH_SEQUENCE / DECODE_PERSISTENT (one cooperative kernel per token)."""
+        _lib.check(_lib.load().zq_gpt2_set_decode_mode(self._h, int(mode)), "zq_gpt2_set_decode_mode")
+
+    @property
+    def decode_mode(self):
+        mode = C.c_int()
+        _lib.check(_lib.load().zq_gpt2_decode_mode(self._h, C.byref(mode)))
+        return mode.value
+
 
 class Gemma3(_Engine):
     """gemma3(C): init / prefill / decode_next (src/models/gemma3.zig:283,551,789)."""

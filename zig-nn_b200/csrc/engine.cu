@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "decode_gemma.h"
+#include "decode_gpt2.h"
 #include "zq_internal.h"
 
 namespace zq {
@@ -151,7 +152,10 @@ struct zq_gpt2 {
     int32_t* d_arg = nullptr;
     uint32_t* d_record = nullptr;  // ctx entries for greedy decoding
     uint32_t seq_len = 0;
+    GptDecoder* decoder = nullptr;  // the persistent decode kernel's view of this engine (nullptr: not available)
+    int decode_mode = ZQ_DECODE_AUTO;
     ~zq_gpt2() {
+        gpt_decoder_free(decoder);
         for (auto& b : blocks) {
             zq_weight_free(b.qkv.qw);
             zq_weight_free(b.proj.qw);
@@ -231,8 +235,56 @@ static int gpt2_forward(zq_gpt2* m, uint32_t T, int variant, cudaStream_t st) {
     return ZQ_OK;
 }
 
+static bool gpt2_persistent(const zq_gpt2* m) {
+    return m->decoder != nullptr && m->decode_mode != ZQ_DECODE_LAUNCH_SEQUENCE;
+}
+
 static int gpt2_run(zq_gpt2* m, int variant, cudaStream_t st) {
+    if (gpt2_persistent(m)) return gpt_decoder_run(m->decoder, 1, variant, st);
     return m->graphs.run(variant, st, [&](cudaStream_t s) { return gpt2_forward(m, 1, variant, s); });
+}
+
+// The persistent decode kernel's view of the engine: built once, after every buffer exists. Engines with an f32
+// linear (the .f32 branch of linear_forward_q) keep the launch sequence.
+static int gpt2_make_decoder(zq_gpt2* m) {
+    const zq_gpt2_config& C = m->c;
+    for (const auto& b : m->blocks)
+        if (!b.qkv.qw || !b.proj.qw || !b.fc.qw || !b.mproj.qw) return ZQ_OK;
+    GptDecoderDesc d;
+    d.embed = C.embed;
+    d.n_head = C.head;
+    d.ffn = C.ffn;
+    d.ctx = C.ctx;
+    d.vocab = C.vocab;
+    d.eps = 1e-5f;
+    d.wte = m->wte;
+    d.wpe = m->wpe;
+    d.ln_f_w = m->ln_f_w;
+    d.ln_f_b = m->ln_f_b;
+    for (uint32_t l = 0; l < C.layer; ++l) {
+        const zq_gpt2::Block& b = m->blocks[l];
+        GptDecoderLayer L;
+        L.qkv = b.qkv.qw;
+        L.proj = b.proj.qw;
+        L.fc = b.fc.qw;
+        L.mproj = b.mproj.qw;
+        L.qkv_b = b.qkv_b;
+        L.proj_b = b.proj_b;
+        L.fc_b = b.fc_b;
+        L.mproj_b = b.mproj_b;
+        L.ln1_w = b.ln1_w;
+        L.ln1_b = b.ln1_b;
+        L.ln2_w = b.ln2_w;
+        L.ln2_b = b.ln2_b;
+        L.kc = m->k[l];
+        L.vc = m->v[l];
+        d.layers.push_back(L);
+    }
+    d.logits = m->logits;
+    d.state = m->d_state;
+    d.record = m->d_record;
+    const int rc = gpt_decoder_create(d, &m->decoder);
+    return rc == ZQ_ERR_UNSUPPORTED ? ZQ_OK : rc;
 }
 
 extern "C" {
@@ -299,6 +351,7 @@ int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_strea
     TRY(m->arena.alloc_n(&m->d_state, 4));
     TRY(m->arena.alloc_n(&m->d_arg, 1));
     TRY(m->arena.alloc_n(&m->d_record, cfg->ctx));
+    TRY(gpt2_make_decoder(m));
 #undef TRY
     cudaError_t e = cudaStreamSynchronize(st);  // host weight buffers may be released after create
     if (e != cudaSuccess) {
@@ -306,6 +359,19 @@ int zq_gpt2_create(const zq_gpt2_config* cfg, const zq_gpt2_weights* w, zq_strea
         return cuda_fail(e);
     }
     *out = m;
+    return ZQ_OK;
+}
+
+int zq_gpt2_set_decode_mode(zq_gpt2* m, int mode) {
+    if (!m || mode < ZQ_DECODE_AUTO || mode > ZQ_DECODE_PERSISTENT) return ZQ_ERR_BAD_ARG;
+    if (mode == ZQ_DECODE_PERSISTENT && !m->decoder) return ZQ_ERR_UNSUPPORTED;
+    m->decode_mode = mode;
+    return ZQ_OK;
+}
+
+int zq_gpt2_decode_mode(const zq_gpt2* m, int* mode) {
+    if (!m || !mode) return ZQ_ERR_BAD_ARG;
+    *mode = gpt2_persistent(m) ? ZQ_DECODE_PERSISTENT : ZQ_DECODE_LAUNCH_SEQUENCE;
     return ZQ_OK;
 }
 
@@ -377,10 +443,16 @@ int zq_gpt2_decode_greedy(zq_gpt2* m, uint32_t first_token, uint32_t n_steps, zq
     cudaStream_t st = as_stream(stream);
     set_state_kernel<<<1, 1, 0, st>>>(m->d_state, first_token, m->seq_len, 0);
     ZQ_LAUNCH_CHECK();
-    for (uint32_t s = 0; s < n_steps; ++s) {
-        int rc = gpt2_run(m, STEP_GREEDY, st);
+    if (gpt2_persistent(m)) {  // every step inside one launch: the argmax feeds the next token on the device
+        int rc = gpt_decoder_run(m->decoder, n_steps, DECODE_GREEDY, st);
         if (rc != ZQ_OK) return rc;
-        m->seq_len += 1;
+        m->seq_len += n_steps;
+    } else {
+        for (uint32_t s = 0; s < n_steps; ++s) {
+            int rc = gpt2_run(m, STEP_GREEDY, st);
+            if (rc != ZQ_OK) return rc;
+            m->seq_len += 1;
+        }
     }
     ZQ_CUDA(cudaMemcpyAsync(h_tokens_out, m->d_record, n_steps * sizeof(uint32_t),
                             cudaMemcpyDeviceToHost, st));
