@@ -580,8 +580,22 @@ __device__ __noinline__ bool g_scores_phase(const GLayer& L, uint32_t pos, float
         const bool cur = pi == pos;
         const float* kr = cur ? knew + h * D : L.kc + (size_t)pi * E + h * D;
         float acc = 0.0f;
+        if (D <= 128u) {  // the lane's key elements all requested before the first is used
+            float kv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t d = l + 16u * u;
+                kv[u] = d < D ? (cur ? kr[d] : __ldcg(kr + d)) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t d = l + 16u * u;
+                if (d < D) acc = __fadd_rn(acc, __fmul_rn(qh[d], kv[u]));
+            }
+        } else {
 #pragma unroll 1
-        for (uint32_t d = l; d < D; d += 16) acc = __fadd_rn(acc, __fmul_rn(qh[d], cur ? kr[d] : __ldcg(kr + d)));
+            for (uint32_t d = l; d < D; d += 16) acc = __fadd_rn(acc, __fmul_rn(qh[d], cur ? kr[d] : __ldcg(kr + d)));
+        }
         float s = __shfl_sync(0xFFFFFFFFu, acc, 0, 16);
 #pragma unroll
         for (int j = 1; j < 16; ++j) s = __fadd_rn(s, __shfl_sync(0xFFFFFFFFu, acc, j, 16));
@@ -638,16 +652,30 @@ __device__ __noinline__ bool g_softmax_v_phase(const GLayer& L, uint32_t pos, co
         const uint32_t col = h * D + dc * 8 + d;
         float acc = 0.0f;
 #pragma unroll 1
-        for (uint32_t pp = grp; pp < n; pp += 64) {
-            const float vv = pp == pos ? vnew[col] : __ldcg(L.vc + (size_t)pp * E + col);
-            acc = fmaf(w[pp] * inv, vv, acc);
+        for (uint32_t p0 = grp; p0 < n; p0 += 64 * 8) {  // eight value rows in flight per thread
+            float vv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t pp = p0 + 64u * u;
+                vv[u] = pp < n ? (pp == pos ? vnew[col] : __ldcg(L.vc + (size_t)pp * E + col)) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t pp = p0 + 64u * u;
+                if (pp < n) acc = fmaf(w[pp] * inv, vv[u], acc);
+            }
         }
-        gsum[grp * 8 + d] = acc;
+        // the 64 group sums of a dimension: four groups meet inside a warp (lanes d, d + 8, d + 16, d + 24), the 16
+        // warps' sums through shared memory
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 8);
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 16);
+        if (c.lane < 8) gsum[c.lane * kConsumerWarps + c.warp] = acc;
         ok = !cbar_or(!ok);
         if (c.tid < 8 && ok) {
-            float o = gsum[c.tid];
-#pragma unroll 1
-            for (uint32_t g2 = 1; g2 < 64; ++g2) o += gsum[g2 * 8 + c.tid];
+            const float4* g4 = reinterpret_cast<const float4*>(gsum + c.tid * kConsumerWarps);
+            const float4 a = g4[0], b = g4[1], cc = g4[2], dd = g4[3];
+            const float o = (((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w))) +
+                            (((cc.x + cc.y) + (cc.z + cc.w)) + ((dd.x + dd.y) + (dd.z + dd.w)));
             xstore(att_out + h * D + dc * 8 + c.tid, o, ep_out);
         }
         cbar();  // w and gsum are rewritten by the next job
