@@ -377,6 +377,10 @@ __device__ __noinline__ uint32_t g_gemv_phase(const GMat& m, uint32_t unit_base,
     float* my = part + (size_t)c.warp * p.part_rows;
     for (uint32_t r = c.lane; r < rows_all; r += 32) my[r] = 0.0f;
     __syncwarp();
+    // the bias of the row this thread finishes below: requested now, it arrives under the dots
+    const uint32_t r_mine = (uint32_t)(c.tid >= kChainTid ? c.tid - kChainTid : c.tid + kConsumers - kChainTid);
+    const uint32_t row_mine = (cta + (r_mine >> 3) * G) * 8 + (r_mine & 7u);
+    const float bias_mine = (r_mine < rows_all && row_mine < m.n_rows) ? __ldg(m.bias + row_mine) : 0.0f;
     const uint32_t total = mine * nq;
     const uint32_t run_lo = ((uint32_t)c.warp * total) >> 4, run_hi = (((uint32_t)c.warp + 1u) * total) >> 4;
     uint32_t i = 0, ch = 0, us = 0;
@@ -409,14 +413,20 @@ __device__ __noinline__ uint32_t g_gemv_phase(const GMat& m, uint32_t unit_base,
     }
     cbar();  // every warp's line of partial sums is complete
 #pragma unroll 1
-    for (uint32_t r = (uint32_t)(c.tid >= kChainTid ? c.tid - kChainTid : c.tid + kConsumers - kChainTid); r < rows_all;
-         r += kConsumers) {
+    for (uint32_t r = r_mine; r < rows_all; r += kConsumers) {
         const uint32_t row = (cta + (r >> 3) * G) * 8 + (r & 7u);
         if (row < m.n_rows) {
-            float v = part[r];
+            const size_t pr = p.part_rows;
+            float a0 = part[r], a1 = part[pr + r], a2 = part[2 * pr + r], a3 = part[3 * pr + r];
 #pragma unroll
-            for (int w = 1; w < kConsumerWarps; ++w) v += part[(size_t)w * p.part_rows + r];
-            v += __ldg(m.bias + row);
+            for (int w = 4; w < kConsumerWarps; w += 4) {  // four running sums: the order is fixed, the adds overlap
+                a0 += part[(size_t)w * pr + r];
+                a1 += part[(size_t)(w + 1) * pr + r];
+                a2 += part[(size_t)(w + 2) * pr + r];
+                a3 += part[(size_t)(w + 3) * pr + r];
+            }
+            float v = (a0 + a1) + (a2 + a3);
+            v += r == r_mine ? bias_mine : __ldg(m.bias + row);
             if (gelu) v = g_gelu(v);
             xstore(xout + row, v, epoch);
         }
@@ -623,6 +633,15 @@ __device__ __noinline__ bool g_softmax_v_phase(const GLayer& L, uint32_t pos, co
         uint32_t h, dc;
         fast_divmod(job, chunks, p.magic_D8, h, dc);
         const unsigned long long* sh_ = scores_in + (size_t)h * p.ctx;
+        // the first eight value rows of this thread do not depend on the scores: requested now
+        const uint32_t grp = (uint32_t)c.tid >> 3, d = (uint32_t)c.tid & 7u;
+        const uint32_t col = h * D + dc * 8 + d;
+        float vfirst[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t pp = grp + 64u * u;
+            vfirst[u] = pp < n ? (pp == pos ? vnew[col] : __ldcg(L.vc + (size_t)pp * E + col)) : 0.0f;
+        }
         float mx = -INFINITY;
 #pragma unroll 1
         for (uint32_t base = 0; base < n; base += kConsumers * 4) {
@@ -648,8 +667,6 @@ __device__ __noinline__ bool g_softmax_v_phase(const GLayer& L, uint32_t pos, co
         }
         const float inv = 1.0f / block_sum(c, s, 1);
         // (the barrier inside block_sum also completes w for every thread)
-        const uint32_t grp = (uint32_t)c.tid >> 3, d = (uint32_t)c.tid & 7u;
-        const uint32_t col = h * D + dc * 8 + d;
         float acc = 0.0f;
 #pragma unroll 1
         for (uint32_t p0 = grp; p0 < n; p0 += 64 * 8) {  // eight value rows in flight per thread
@@ -657,7 +674,8 @@ __device__ __noinline__ bool g_softmax_v_phase(const GLayer& L, uint32_t pos, co
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const uint32_t pp = p0 + 64u * u;
-                vv[u] = pp < n ? (pp == pos ? vnew[col] : __ldcg(L.vc + (size_t)pp * E + col)) : 0.0f;
+                if (p0 == grp) vv[u] = vfirst[u];
+                else vv[u] = pp < n ? (pp == pos ? vnew[col] : __ldcg(L.vc + (size_t)pp * E + col)) : 0.0f;
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
