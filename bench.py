@@ -364,8 +364,7 @@ def decode_extra(torch, zq, ggml):
         host = Host.synthetic(cfg, qtype=qt, seed=42, device="cuda")
         prompt = np.random.default_rng(44).integers(0, cfg["vocab"], size=n_prompt)
         rates = {}
-        modes = [("persistent_kernel", zq.DECODE_AUTO), ("launch_sequence", zq.DECODE_LAUNCH_SEQUENCE)] \
-            if name.startswith("gemma") else [("launch_sequence", None)]
+        modes = [("persistent_kernel", zq.DECODE_AUTO), ("launch_sequence", zq.DECODE_LAUNCH_SEQUENCE)]
         for label, mode in modes:
             eng = Eng(host)
             if mode is not None:
