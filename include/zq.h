@@ -252,6 +252,22 @@ int zq_matmul_gather(const zq_weight* w, const float* d_x, const zq_epilogue* ep
                      float* const* h_y_peers_odd, float* const* h_y_peers_even, uint32_t* const* h_flag_peers,
                      uint32_t world, uint32_t rank, uint32_t row_offset, uint32_t* d_sync, zq_stream stream);
 
+/* The same product and exchange with nothing after the peer stores: what travels is one 64-bit word per
+ * output row, the round number above the float's bits, stored into the peer's inbox. A word tells by itself
+ * whether it belongs to the round, so the sender issues no fence and publishes no counter; each rank's kernel
+ * ends by polling (bounded, zq_set_wait_limit) its own inbox for the other ranks' rows and storing the floats
+ * into its result row. Every rank owns the same number of rows (w->out_dim, even): rank r's rows are
+ * [r * out_dim, (r + 1) * out_dim) of the result.
+ *   h_inbox_peers_*  `world` pointers (host array): every rank's inbox of world * out_dim 64-bit words, zeroed
+ *                    once, entry `rank` being this GPU's own; odd / even rounds use different inboxes
+ *   d_y_*            this GPU's result rows (world * out_dim floats) of odd / even rounds
+ *   d_sync           two uint32 on this GPU, zeroed once: completed rounds, CTA arrivals
+ * Returns ZQ_ERR_UNSUPPORTED when the shard has too few rows for this kernel or an odd number of them. */
+int zq_matmul_gather_tagged(const zq_weight* w, const float* d_x, const zq_epilogue* epilogue,
+                            unsigned long long* const* h_inbox_peers_odd, unsigned long long* const* h_inbox_peers_even,
+                            float* d_y_odd, float* d_y_even, uint32_t world, uint32_t rank, uint32_t* d_sync,
+                            zq_stream stream);
+
 /* --------------------------------------------------- small ops (inference) */
 
 /* rms_norm_rows (src/models/gemma3.zig:906-946; MetalContext.dispatch_rms_norm,

@@ -88,6 +88,53 @@ def test_fused_gather_wait_runs_out(zq, oracle):
     assert torch.equal(zq.quant_matmul_no_grad(x, qw).reshape(-1), want)  # the library still works
 
 
+def test_tagged_gather_wait_runs_out_and_completes_when_the_words_are_there(zq, oracle):
+    """The tagged exchange (64-bit words carrying the round number), both 'ranks' on this GPU and no second rank
+    running: round 1 stores this rank's rows and their words, the poll of the absent rank's words ends after the
+    limit with 'FGAT'. Then the absent rank's words of round 2 are written by hand: round 2 completes without an
+    error and unpacks them."""
+    from zignn_b200 import _lib
+    lib = _lib.load()
+    _lib.device_error(clear=True)
+    n, k = 148 * 2 * 8 * 16, 1152
+    rng = np.random.default_rng(4)
+    raw = oracle.quantize(ggml.Q4_0, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    qw = zq.QuantWeight(raw, ggml.Q4_0, n, k)
+    x = torch.from_numpy(rng.standard_normal((1, k)).astype(np.float32)).cuda()
+    want = zq.quant_matmul_no_grad(x, qw).reshape(-1)
+    inbox_odd = [torch.zeros(2 * n, dtype=torch.int64, device="cuda") for _ in range(2)]
+    inbox_even = [torch.zeros(2 * n, dtype=torch.int64, device="cuda") for _ in range(2)]
+    y_odd, y_even = torch.zeros(2 * n, device="cuda"), torch.zeros(2 * n, device="cuda")
+    sync = torch.zeros(2, dtype=torch.int32, device="cuda")
+
+    def call():
+        return lib.zq_matmul_gather_tagged(qw.handle, C.c_void_p(x.data_ptr()), None, ptr_array(inbox_odd),
+                                           ptr_array(inbox_even), C.c_void_p(y_odd.data_ptr()), C.c_void_p(y_even.data_ptr()),
+                                           2, 0, C.c_void_p(sync.data_ptr()), stream())
+
+    lib.zq_set_wait_limit(1024)
+    try:
+        assert call() == 0
+        torch.cuda.synchronize()
+        assert torch.allclose(y_odd[:n], want, rtol=1e-5, atol=1e-7)        # this rank's own rows
+        words = inbox_odd[1][:n]                                             # what the 'peer' received
+        assert torch.all((words >> 32) == 1)
+        assert torch.equal((words & 0xFFFFFFFF).to(torch.int32).view(torch.float32), y_odd[:n])
+        assert _lib.device_error(clear=False) == FGAT
+        assert lib.zq_device_check(1) == 7
+        assert int(sync[0].item()) == 1 and int(sync[1].item()) == 0        # the round still closed
+        # round 2: the other rank's words are in this rank's even inbox before the call
+        theirs = torch.arange(n, device="cuda", dtype=torch.float32) * 0.5
+        inbox_even[0][n:] = (theirs.view(torch.int32).to(torch.int64) & 0xFFFFFFFF) | (2 << 32)
+        assert call() == 0
+        torch.cuda.synchronize()
+        assert lib.zq_device_check(1) == 0
+        assert torch.allclose(y_even[:n], want, rtol=1e-5, atol=1e-7)
+        assert torch.equal(y_even[n:], theirs)
+    finally:
+        lib.zq_set_wait_limit(0)
+
+
 def test_many_rows_without_workspace_is_refused(zq, oracle):
     from zignn_b200 import _lib
     import zignn_b200.structs as S

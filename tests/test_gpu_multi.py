@@ -39,19 +39,21 @@ def _worker(rank, world, port, out_dim, in_dim, m, result_path):
             raw = ggml.quantize(qt, w)
             full = zq.quant_matmul_no_grad(x, zq.QuantWeight(raw, qt, out_dim, in_dim))
             nccl = sharding.cuda_sharded_linear(raw, qt, out_dim, in_dim, gather="nccl")
-            peer = sharding.cuda_sharded_linear(raw, qt, out_dim, in_dim, gather="peer", m_rows=m)
             want = nccl.forward(x).clone()
-            for it in range(5):  # both result buffers, growing round numbers
-                got = peer.forward(x + float(it)) if it else peer.forward(x)
-                ref = nccl.forward(x + float(it)) if it else want
-                torch.cuda.synchronize()
-                if peer.fused:
-                    # the fused kernel keeps whole rows per warp; the plain shard GEMV may split K over
-                    # warps: same products, another summation order
-                    e = float((got - ref).norm() / ref.norm())
-                    assert e <= 2e-6, "rank %d type %d round %d: %g" % (rank, qt, it, e)
-                else:
-                    assert torch.equal(got, ref), "rank %d type %d round %d" % (rank, qt, it)
+            for tagged in (True, False):  # the fused exchange: words carrying the round number / counters after a fence
+                peer = sharding.cuda_sharded_linear(raw, qt, out_dim, in_dim, gather="peer", m_rows=m)
+                peer.peer.tagged = peer.peer.tagged and tagged
+                for it in range(5):  # both result buffers, growing round numbers
+                    got = peer.forward(x + float(it)) if it else peer.forward(x)
+                    ref = nccl.forward(x + float(it)) if it else want
+                    torch.cuda.synchronize()
+                    if peer.fused:
+                        # the fused kernel keeps whole rows per warp; the plain shard GEMV may split K over
+                        # warps: same products, another summation order
+                        e = float((got - ref).norm() / ref.norm())
+                        assert e <= 2e-6, "rank %d type %d round %d: %g" % (rank, qt, it, e)
+                    else:
+                        assert torch.equal(got, ref), "rank %d type %d round %d" % (rank, qt, it)
             err = (want - full).norm() / full.norm()
             assert float(err) <= 2e-6, float(err)
         from zignn_b200 import _lib

@@ -618,6 +618,15 @@ int zq_matmul_gather(const zq_weight* w, const float* d_x, const zq_epilogue* ep
                                   row_offset, d_sync, as_stream(stream));
 }
 
+int zq_matmul_gather_tagged(const zq_weight* w, const float* d_x, const zq_epilogue* epilogue,
+                            unsigned long long* const* h_inbox_peers_odd, unsigned long long* const* h_inbox_peers_even,
+                            float* d_y_odd, float* d_y_even, uint32_t world, uint32_t rank, uint32_t* d_sync,
+                            zq_stream stream) {
+    if (!w || !d_x || !h_inbox_peers_odd || !h_inbox_peers_even || !d_y_odd || !d_y_even || !d_sync) return ZQ_ERR_BAD_ARG;
+    return launch_gemv_gather_tagged_f32(w, d_x, epilogue, h_inbox_peers_odd, h_inbox_peers_even, d_y_odd, d_y_even, world,
+                                         rank, d_sync, as_stream(stream));
+}
+
 int zq_matvec_f32(const float* d_w, const float* d_x, float* d_y, uint32_t out_dim, uint32_t in_dim,
                   zq_stream stream) {
     if (!d_w || !d_x || !d_y || out_dim == 0 || in_dim == 0) return ZQ_ERR_BAD_ARG;

@@ -647,6 +647,14 @@ __device__ __forceinline__ void lds128_keep(uint4& v, uint32_t addr, uint32_t pr
 // slices happens while the weights are still streaming. When the last CTA of the grid is done it adds 1
 // to this rank's counter on every peer and waits — bounded — until every peer's counter here has
 // reached the round number. world <= 1: an ordinary GEMV into `y`.
+//
+// Tagged form (pa.tagged): what travels to a peer is a 64-bit word per output row, the round number above the
+// float's bits, stored into the peer's inbox; a word says by itself whether it belongs to this round, so no
+// fence, counter or flag follows the stores. When a CTA has finished its own rows it turns to the inbox of
+// this GPU: the grid's threads share the other ranks' rows, poll each pair of words (bounded) until both
+// carry this round's number and store the floats into this rank's result row. Two inboxes alternate: a peer
+// can be at most one round ahead (it needs this rank's words of a round to finish that round), and then it
+// writes into the other one.
 constexpr int kPeerMax = 8;
 constexpr uint32_t kPeerSpinLimit = 1u << 21;               // polls of a local flag before giving up (about a second)
 constexpr unsigned int kErrFusedGatherTimeout = 0x46474154u;  // 'FGAT'
@@ -657,6 +665,8 @@ struct PeerArgs {
     unsigned int* err;           // the library's device-error word
     uint32_t world, rank, row_off;
     uint32_t spin_limit;         // polls of a local flag before giving up
+    unsigned long long* inbox[2][kPeerMax];  // tagged form: [round parity][rank] that rank's inbox, world * per words
+    uint32_t tagged, per;        // tagged form; rows owned by every rank (even)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
@@ -881,9 +891,17 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
             if (t < 2 && row < N) {
                 const float o = apply_epilogue((t == 1 ? vb : va) * ps, ep, row, row);
                 y[row] = o;
-                if (sharded)
+                if (sharded && pa.tagged) {
+                    const unsigned long long word = ((unsigned long long)round << 32) | __float_as_uint(o);
+                    for (uint32_t p = 0; p < pa.world; ++p)
+                        if (p != pa.rank)
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(pa.inbox[round & 1u][p] + pa.row_off + row),
+                                         "l"(word)
+                                         : "memory");
+                } else if (sharded) {
                     for (uint32_t p = 0; p < pa.world; ++p)
                         if (p != pa.rank) pa.y[round & 1u][p][pa.row_off + row] = o;
+                }
             }
             c_q = 0;
             c_tile += gridDim.x;
@@ -912,7 +930,41 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
         consume(r);
     }
 
-    if (sharded) {
+    if (sharded && pa.tagged) {
+        // the other ranks' rows, two words per thread and pass
+        const unsigned long long* in = pa.inbox[round & 1u][pa.rank];
+        float* yfull = pa.y[round & 1u][pa.rank];
+        const uint32_t n_other = pa.per * (pa.world - 1u);
+        bool dead = false;
+        for (uint32_t i = 2u * (blockIdx.x * blockDim.x + tid); i < n_other; i += 2u * gridDim.x * blockDim.x) {
+            const uint32_t pi = i / pa.per;
+            const uint32_t at = i + (pi >= pa.rank ? pa.per : 0u);  // skip this rank's own rows
+            unsigned long long a = 0, b = 0;
+            bool ok = false;
+            for (uint32_t n = 0; n < pa.spin_limit && !dead; ++n) {
+                asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(in + at) : "memory");
+                if ((uint32_t)(a >> 32) == round && (uint32_t)(b >> 32) == round) {
+                    ok = true;
+                    break;
+                }
+            }
+            if (!ok && !dead) {  // one report per thread, and no further waiting by it
+                dead = true;
+                atomicExch(pa.err, kErrFusedGatherTimeout);
+            }
+            *reinterpret_cast<float2*>(yfull + at) = make_float2(__uint_as_float((uint32_t)a), __uint_as_float((uint32_t)b));
+        }
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            const uint32_t ticket = atomicAdd(pa.sync + 1, 1u);
+            if (ticket == gridDim.x - 1) {  // every CTA has stored its rows and its share of the inbox
+                pa.sync[1] = 0;
+                __threadfence();
+                pa.sync[0] = round;
+            }
+        }
+    } else if (sharded) {
         __syncthreads();  // the CTA's peer stores happen before thread 0's fence (fences are cumulative)
         if (tid == 0) {
             // Device-scope fence per CTA (a system-scope fence here costs about 10 us per launch, measured);
@@ -1140,6 +1192,49 @@ int launch_gemv_mma_passes_f32(const zq_weight* w, const float* x, float* y, uin
     return ZQ_OK;
 }
 
+static EpilogueArgs gather_epilogue(const zq_epilogue* ep) {
+    EpilogueArgs a{nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0.0f};
+    if (ep) {
+        a.bias = ep->d_bias;
+        a.gelu = ep->gelu;
+        a.mul = ep->d_mul;
+        a.residual = ep->d_residual;
+    }
+    return a;
+}
+
+// The tagged form: inboxes of 64-bit words on every rank instead of result buffers and counters.
+int launch_gemv_gather_tagged_f32(const zq_weight* w, const float* x, const zq_epilogue* ep,
+                                  unsigned long long* const* inbox_odd, unsigned long long* const* inbox_even,
+                                  float* y_odd, float* y_even, uint32_t world, uint32_t rank, uint32_t* d_sync,
+                                  cudaStream_t st) {
+    if (world < 2 || world > (uint32_t)kPeerMax || rank >= world) return ZQ_ERR_BAD_ARG;
+    if (((uintptr_t)x & 15) != 0 || ((uintptr_t)y_odd & 7) != 0 || ((uintptr_t)y_even & 7) != 0) return ZQ_ERR_BAD_ARG;
+    if ((w->out_dim & 1u) != 0) return ZQ_ERR_UNSUPPORTED;  // words are read in pairs
+    if ((w->out_dim + 15) / 16 < (uint32_t)sm_count() * 4) return ZQ_ERR_UNSUPPORTED;
+    const EpilogueArgs a = gather_epilogue(ep);
+    PeerArgs pa{};
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!inbox_odd[r] || !inbox_even[r]) return ZQ_ERR_PEER;  // a peer's inbox was never mapped
+        if ((((uintptr_t)inbox_odd[r] | (uintptr_t)inbox_even[r]) & 15) != 0) return ZQ_ERR_BAD_ARG;
+        pa.inbox[1][r] = inbox_odd[r];
+        pa.inbox[0][r] = inbox_even[r];
+    }
+    pa.y[1][rank] = y_odd;
+    pa.y[0][rank] = y_even;
+    pa.sync = d_sync;
+    int rc = device_error_word(&pa.err);
+    if (rc != ZQ_OK) return rc;
+    pa.world = world;
+    pa.rank = rank;
+    pa.row_off = rank * w->out_dim;
+    pa.per = w->out_dim;
+    pa.tagged = 1;
+    pa.spin_limit = wait_limit() ? wait_limit() : kPeerSpinLimit;
+    rc = launch_rows1_any(w, x, nullptr, a, pa, st);
+    return rc == ZQ_ERR_LIMIT ? ZQ_ERR_UNSUPPORTED : rc;
+}
+
 // One activation row, row-sharded weight: GEMV with the all-gather of the output slices in its epilogue.
 // ZQ_ERR_UNSUPPORTED when the shard is too small for the whole-rows kernel (the caller then runs the
 // plain GEMV followed by the separate exchange).
@@ -1149,13 +1244,7 @@ int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue
     if (world < 2 || world > (uint32_t)kPeerMax || rank >= world) return ZQ_ERR_BAD_ARG;
     if (((uintptr_t)x & 15) != 0) return ZQ_ERR_BAD_ARG;
     if ((w->out_dim + 15) / 16 < (uint32_t)sm_count() * 4) return ZQ_ERR_UNSUPPORTED;
-    EpilogueArgs a{nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0.0f};
-    if (ep) {
-        a.bias = ep->d_bias;
-        a.gelu = ep->gelu;
-        a.mul = ep->d_mul;
-        a.residual = ep->d_residual;
-    }
+    const EpilogueArgs a = gather_epilogue(ep);
     PeerArgs pa{};
     for (uint32_t r = 0; r < world; ++r) {
         if (!y_odd[r] || !y_even[r] || !flags[r]) return ZQ_ERR_PEER;  // a peer's buffer was never mapped

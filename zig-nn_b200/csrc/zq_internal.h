@@ -132,6 +132,10 @@ int launch_gemv_mma_passes_f32(const zq_weight* w, const float* x, float* y, uin
 int launch_gemv_mma_ln_f32(const zq_weight* w, const float* x, float* y, uint32_t m_rows, const zq_epilogue* ep,
                            const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t st);
 // f32-activation GEMV for one row with the all-gather of row-sharded outputs fused in (gemv_mma.cu).
+int launch_gemv_gather_tagged_f32(const zq_weight* w, const float* x, const zq_epilogue* ep,
+                                  unsigned long long* const* inbox_odd, unsigned long long* const* inbox_even,
+                                  float* y_odd, float* y_even, uint32_t world, uint32_t rank, uint32_t* d_sync,
+                                  cudaStream_t st);
 int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue* ep, float* const* y_odd,
                            float* const* y_even, uint32_t* const* flags, uint32_t world, uint32_t rank,
                            uint32_t row_off, uint32_t* d_sync, cudaStream_t st);

@@ -137,6 +137,18 @@ class PeerGather:
         self._ffptrs = (C.c_void_p * world)(*[int(p) for p in hff.buffer_ptrs])
         self._handles = self._handles + (hff,)
         self.d_sync = torch.zeros(2, dtype=torch.int32, device=device)
+        # tagged form of the fused exchange (one activation row): an inbox of 64-bit words per round parity
+        self._inptrs = None
+        if m == 1 and per % 2 == 0:
+            self.inboxes, self._inptrs = [], []
+            for _ in range(2):
+                t = symm_mem.empty(world * per, dtype=torch.int64, device=device)
+                t.zero_()
+                hi = symm_mem.rendezvous(t, grp)
+                self.inboxes.append(t)
+                self._inptrs.append((C.c_void_p * world)(*[int(p) for p in hi.buffer_ptrs]))
+                self._handles = self._handles + (hi,)
+        self.tagged = self._inptrs is not None
         torch.cuda.synchronize(device)
         dist.barrier(group=group)  # every rank's counters are zero before anybody adds to them
 
@@ -163,9 +175,15 @@ class PeerGather:
         Returns the gathered buffer, or None when the shard is too small for that kernel (nothing ran)."""
         C = self._C
         stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-        rc = self._lib.load().zq_matmul_gather(weight.handle, C.c_void_p(x.data_ptr()), None, self._yptrs[1],
-                                               self._yptrs[0], self._ffptrs, self.world, self.rank,
-                                               self.rank * self.per, C.c_void_p(self.d_sync.data_ptr()), stream)
+        if self.tagged:  # words that carry their round number: nothing follows the peer stores
+            rc = self._lib.load().zq_matmul_gather_tagged(weight.handle, C.c_void_p(x.data_ptr()), None, self._inptrs[1],
+                                                          self._inptrs[0], C.c_void_p(self.bufs[1].data_ptr()),
+                                                          C.c_void_p(self.bufs[0].data_ptr()), self.world, self.rank,
+                                                          C.c_void_p(self.d_sync.data_ptr()), stream)
+        else:
+            rc = self._lib.load().zq_matmul_gather(weight.handle, C.c_void_p(x.data_ptr()), None, self._yptrs[1],
+                                                   self._yptrs[0], self._ffptrs, self.world, self.rank,
+                                                   self.rank * self.per, C.c_void_p(self.d_sync.data_ptr()), stream)
         if rc == 2:  # ZQ_ERR_UNSUPPORTED
             return None
         self._lib.check(rc, "zq_matmul_gather")
