@@ -564,6 +564,30 @@ def test_streaming_gemm_epilogue_and_row_counts(zq):
 
 
 @pytest.mark.parametrize("qt,block_bytes", STREAM_TYPES)
+def test_streaming_gemm_wide_many_activation_tiles_and_epilogue(zq, qt, block_bytes):
+    """Two activation tiles per CTA tile on a small matrix: 11 ragged weight tiles x 9 ragged activation tiles (99 CTA
+    tiles, enough for this form to be taken), K of four stages so that every ring wraps several times within a tile,
+    and the whole epilogue (bias, GELU, multiplier, residual)."""
+    k, n, m = 256, 2600, 2300
+    g = torch.Generator(device="cuda").manual_seed(77 + int(qt))
+    raw_d = ggml.quantize(qt, torch.randn(n, k, generator=g, device="cuda") * 0.05)
+    qw = zq.QuantWeight(raw_d, qt, n, k)
+    x = torch.randn(m, k, generator=g, device="cuda")
+    bias = torch.randn(n, generator=g, device="cuda")
+    mul = torch.randn(m, n, generator=g, device="cuda")
+    res = torch.randn(m, n, generator=g, device="cuda")
+    base = x @ qw.dequantize().t()
+    got = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32)
+    assert torch.allclose(got, base, rtol=0, atol=4e-3 * float(base.abs().max()))
+    assert rel_l2(got.cpu().numpy(), base.cpu().numpy()) <= REL_L2_GEMM_GUARD
+    got = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32, bias=bias, gelu=True, mul=mul, residual=res)
+    want = res + torch.nn.functional.gelu(base + bias, approximate="tanh") * mul
+    assert torch.allclose(got, want, rtol=0, atol=6e-3 * float(want.abs().max()))
+    from zignn_b200 import _lib
+    assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("qt,block_bytes", STREAM_TYPES)
 @pytest.mark.parametrize("m", [129, 256, 300, 520])
 def test_streaming_gemm_wide_sampled_rows(zq, oracle, qt, block_bytes, m):
     """More than 128 activation rows on a matrix with a 256-row weight tile for every SM: the streaming kernel with

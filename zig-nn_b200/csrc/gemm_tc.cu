@@ -500,11 +500,11 @@ constexpr int TS_EPI_WARP0 = TS_MMA_WARP + 1;   // four warps: their ids mod 4 c
 constexpr int TS_COPY_WARP = TS_EPI_WARP0 + 4;   // packed chunks
 constexpr int TS_XCOPY_WARP = TS_COPY_WARP + 1;  // activation tiles (a warp of its own: one warp serving both rings
                                                  // waits for a free slot of one while the other runs dry)
-constexpr int TS_THREADS = (TS_XCOPY_WARP + 1) * 32;  // 23 warps
+constexpr int TS_MMA_WARP2 = TS_XCOPY_WARP + 1;  // the second accumulator's issuer (more than 128 activation rows)
+constexpr int TS_THREADS = (TS_MMA_WARP2 + 1) * 32;  // 24 warps
 constexpr int TS_MAX_STAGES = 6;    // fp16 weight tiles (TN x 128 bytes each)
 constexpr int TS_MAX_BTILES = 16;   // activation tiles
 constexpr int TS_MAX_CHUNKS = 4;
-constexpr uint32_t TS_CHUNK_ROW = 128;  // packed bytes per row and chunk: 2 quads of q4, 1 of q8_0
 constexpr uint32_t TS_ACT_ROWS = 128;   // rows of the activation operand (UMMA M)
 
 // One box of a 2-D map: rows [y, y + box rows) x bytes [x, x + box bytes) -> shared memory, bytes counted on `bar`.
@@ -524,28 +524,36 @@ __device__ __forceinline__ uint2 lds64(uint32_t saddr) {
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(saddr));
     return v;
 }
-// Scale bytes of a row in a chunk's scale box: q4_0 16 (two quads), q4_1 32, q8_0 16 (the quad and its neighbour:
-// a box is at least 16 bytes wide).
-template <int TYPE>
+// Scale bytes of a row in a chunk's scale box. Chunks of 128 packed bytes per row: q4_0 16 (two quads), q4_1 32,
+// q8_0 16 (the quad and its neighbour: a box is at least 16 bytes wide). Chunks of 64 bytes (one quad of q4):
+// q4_0 16 (the quad and its neighbour), q4_1 16.
+template <int TYPE, int CROW>
 struct StreamScales {
-    static constexpr uint32_t kBox = TYPE == ZQ_TYPE_Q4_1 ? 32u : 16u;
+    static constexpr uint32_t kBox = (TYPE == ZQ_TYPE_Q4_1 && CROW == 128) ? 32u : 16u;
 };
+// 16-byte unit c of row r in a box of 64-byte rows written with the 64-byte swizzle
+__device__ __forceinline__ uint32_t swz64(uint32_t r, uint32_t c) { return r * 64u + ((c ^ ((r >> 1) & 3u)) << 4); }
 // The thread's share of quad `ql` of the chunk: (row, half) -> packed words and the quad's scales. `sq` is the
 // quad's place in the row's scale box.
-template <int TYPE>
+template <int TYPE, int CROW>
 __device__ __forceinline__ void read_packed(PackedQuad<TYPE>& p, uint32_t chunk, uint32_t scales, uint32_t row,
                                             uint32_t half, uint32_t ql, uint32_t sq) {
     constexpr uint32_t UNITS = TYPE == ZQ_TYPE_Q8_0 ? 8 : 4;   // 16-byte units per quad
     constexpr uint32_t MINE = UNITS / 2;                        // units of one half
     const uint32_t u0 = ql * UNITS + half * MINE;
-    p.w0 = lds128(chunk + swz(row, u0));
-    p.w1 = lds128(chunk + swz(row, u0 + 1));
+    if (CROW == 64) {
+        p.w0 = lds128(chunk + swz64(row, u0));
+        p.w1 = lds128(chunk + swz64(row, u0 + 1));
+    } else {
+        p.w0 = lds128(chunk + swz(row, u0));
+        p.w1 = lds128(chunk + swz(row, u0 + 1));
+    }
     if (TYPE == ZQ_TYPE_Q8_0) {
         p.w2 = lds128(chunk + swz(row, u0 + 2));
         p.w3 = lds128(chunk + swz(row, u0 + 3));
     }
     if (TYPE == ZQ_TYPE_Q4_1) {
-        p.s = lds128(scales + row * 32u + sq * 16u);
+        p.s = lds128(scales + row * StreamScales<TYPE, CROW>::kBox + sq * 16u);
     } else {
         const uint2 v = lds64(scales + row * 16u + sq * 8u);
         p.s.x = v.x;
@@ -564,7 +572,9 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 
 // TN = weight rows per tile (UMMA N): 256, or 128 for matrices with too few rows to give every SM a 256-row tile.
-template <int TYPE, int TN>
+// CROW = packed bytes per row and chunk: 128 (2 quads of q4, 1 of q8_0) or, for q4, 64 (1 quad: chunks a quarter
+// of a stage pair smaller, which leaves room for a deeper ring of activation tiles).
+template <int TYPE, int TN, int CROW>
 __global__ void __launch_bounds__(TS_THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                    const __half* __restrict__ xt, const float* __restrict__ post, float* __restrict__ y, uint32_t N,
@@ -574,10 +584,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr uint32_t QB = Q8 ? 32 : 16;          // packed bytes per block
     constexpr uint32_t QUADB = 4 * QB;             // packed bytes per quad
-    constexpr uint32_t CQ = TS_CHUNK_ROW / QUADB;  // quads per chunk: 2 (q4) or 1 (q8_0)
-    constexpr uint32_t SBOX = StreamScales<TYPE>::kBox;
+    static_assert(CROW == 128 || (CROW == 64 && !Q8), "chunk rows: 128 bytes, or 64 for the 4-bit types");
+    constexpr uint32_t CQ = CROW / QUADB;          // quads per chunk: 2 (q4) or 1 (q8_0; q4 with 64-byte chunks)
+    constexpr bool PAIRED = CQ == 1 && TYPE != ZQ_TYPE_Q4_1;  // the scale box holds the quad's scales and its neighbour's
+    constexpr uint32_t SBOX = StreamScales<TYPE, CROW>::kBox;
     constexpr uint32_t W_STAGE = TN * 128u;        // fp16 weight tile of a stage
-    constexpr uint32_t CHUNK_BYTES = TN * 128u + TN * 32u;  // packed box, then the scale box (room for 32 bytes per row)
+    constexpr uint32_t CHUNK_BYTES = TN * CROW + TN * SBOX;  // packed box, then the scale box (both multiples of 1 KB)
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int NBARS = 2 * TS_MAX_STAGES + 2 * TS_MAX_BTILES + 2 * TS_MAX_CHUNKS + 4;
     __shared__ __align__(8) unsigned long long bars[NBARS];
@@ -621,7 +633,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     if (tid == 0) {
         for (uint32_t s = 0; s < n_ring; ++s) {
             mbar_init(full_bar(s), TS_CONVERT_WARPS);  // one arrival per converting warp
-            mbar_init(empty_bar(s), 1);
+            mbar_init(empty_bar(s), n_act);            // one commit per issuer
         }
         for (uint32_t s = 0; s < n_bring; ++s) {
             mbar_init(bfull_bar(s), 1);  // the copy warp's arrival with the byte count
@@ -632,7 +644,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             mbar_init(cempty_bar(c), TS_CONVERT_WARPS);   // every converting warp, once per chunk
         }
         for (uint32_t a = 0; a < 2; ++a) {
-            mbar_init(acc_full(a), 1);
+            mbar_init(acc_full(a), a == 0 ? n_act : 1u);  // two activation tiles: both issuers commit to the first
             mbar_init(acc_empty(a), 4);  // one arrival per draining warp
         }
         abort_flag = 0;
@@ -664,12 +676,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 alive = mbar_wait(cfull_bar(cslot), cround & 1u, abort_p, err_word);
                 if (!alive) break;
                 const uint32_t nqc = min(CQ, n_quads - c * CQ);
-                const uint32_t chunk = chunk32 + cslot * CHUNK_BYTES, scales = chunk + TN * 128u;
+                const uint32_t chunk = chunk32 + cslot * CHUNK_BYTES, scales = chunk + TN * CROW;
                 for (uint32_t ql = 0; ql < nqc && alive; ++ql) {
-                    const uint32_t sq = Q8 ? (c & 1u) : ql;  // q8_0: the box holds the scales of quads c & ~1 and c | 1
+                    const uint32_t sq = PAIRED ? (c & 1u) : ql;  // paired: the box holds the scales of quads c & ~1 and c | 1
                     PackedQuad<TYPE> pk[HALVES];
 #pragma unroll
-                    for (int hh = 0; hh < HALVES; ++hh) read_packed<TYPE>(pk[hh], chunk, scales, prow, phalf0 + hh, ql, sq);
+                    for (int hh = 0; hh < HALVES; ++hh)
+                        read_packed<TYPE, CROW>(pk[hh], chunk, scales, prow, phalf0 + hh, ql, sq);
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         if (round > 0) alive = alive && mbar_wait(empty_bar(slot), (round - 1) & 1u, abort_p, err_word);
@@ -712,12 +725,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 if (lane == 0) {
                     // boxes are written whole (zeros beyond the map's edges)
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(cfull_bar(cslot)),
-                                 "r"((uint32_t)TN * (128u + SBOX))
+                                 "r"((uint32_t)TN * ((uint32_t)CROW + SBOX))
                                  : "memory");
                     const uint32_t dst0 = chunk32 + cslot * CHUNK_BYTES;
-                    tensor_copy_2d(dst0, &wmap, c * TS_CHUNK_ROW, row0, cfull_bar(cslot));
-                    const uint32_t sx = Q8 ? (c & ~1u) * 8u : c * SBOX;
-                    tensor_copy_2d(dst0 + TN * 128u, &smap, sx, row0, cfull_bar(cslot));
+                    tensor_copy_2d(dst0, &wmap, c * (uint32_t)CROW, row0, cfull_bar(cslot));
+                    const uint32_t sx = PAIRED ? (c & ~1u) * 8u : c * SBOX;
+                    tensor_copy_2d(dst0 + TN * CROW, &smap, sx, row0, cfull_bar(cslot));
                 }
                 __syncwarp();
                 if (++cslot == n_chunk_ring) {
@@ -739,7 +752,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         bool alive = true;
         for (uint32_t ti = 0; ti < nt && alive; ++ti) {
             const uint32_t mt = (blockIdx.x + ti * gridDim.x) / row_tiles;
-            for (uint32_t sg = 0; sg < n_stages && alive; ++sg) {
+            // one ring entry per stage and activation tile
+            for (uint32_t sa = 0; sa < n_stages * n_act && alive; ++sa) {
+                const uint32_t sg = n_act == 1 ? sa : sa >> 1, a = n_act == 1 ? 0u : sa & 1u;
                 if (bround > 0) alive = mbar_wait(bempty_bar(bslot), (bround - 1) & 1u, abort_p, err_word);
                 alive = __all_sync(0xFFFFFFFFu, alive);
                 if (!alive) break;
@@ -748,7 +763,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                                  "r"(btile_bytes)
                                  : "memory");
                     const unsigned char* src = reinterpret_cast<const unsigned char*>(xt) +
-                                               ((size_t)sg * m_pad + (size_t)mt * TS_ACT_ROWS * n_act) * 128u;
+                                               ((size_t)sg * m_pad + ((size_t)mt * n_act + a) * TS_ACT_ROWS) * 128u;
                     if (interleave) {
                         for (uint32_t q = 0; q < 4; ++q)
                             bulk_copy_g2s(bring32 + bslot * bstride + q * 4096u, src + q * 1024u, 1024u, bfull_bar(bslot));
@@ -768,15 +783,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 for (uint32_t i = 0; i < (1u << 16); ++i)
                     if (mbar_try_wait(bfull_bar(s), 0) || mbar_try_wait(bfull_bar(s), 1)) break;
         }
-    } else if (warp == TS_MMA_WARP) {
-        // ================= MMA issuer: D[activation row][weight row] += X . W^T =================
-        if (lane == 0) {
+    } else if (warp == TS_MMA_WARP || warp == TS_MMA_WARP2) {
+        // ================= MMA issuers: D[activation row][weight row] += X . W^T =================
+        // Up to 128 activation rows: one issuer, the two accumulators take turns between tiles. More: both
+        // accumulators belong to the tile and each has an issuer of its own (a thread of another warp). A look at a
+        // barrier costs the issuing thread some 250 cycles while the tensor pipe holds little work in its queue
+        // (measured: one thread issuing a stage's eight instructions and looking at three barriers spent 1430 + 970
+        // cycles per stage); two threads look at theirs at the same time.
+        const uint32_t me = warp == TS_MMA_WARP ? 0u : 1u;
+        if (lane == 0 && me < n_act) {
             const uint32_t idesc = idesc_f16(TS_ACT_ROWS, TN);
-            uint32_t slot = 0, round = 0, bslot = 0, bround = 0;
-            bool alive = true;
+            uint32_t slot = 0, round = 0, bslot = me, bround = 0;  // this issuer's ring entries: me, me + n_act, ...
+            bool alive = true, ready = false;
             for (uint32_t i = 0; i < nt && alive; ++i) {
-                // one activation tile: the two accumulators take turns; two: both belong to this tile
-                const uint32_t acc = n_act == 1 ? (i & 1u) : 0u;
+                const uint32_t acc = n_act == 1 ? (i & 1u) : me;
                 if (n_act == 1) {
                     if (i >= 2) alive = mbar_wait(acc_empty(acc), ((i >> 1) - 1) & 1u, abort_p, err_word);
                 } else if (i >= 1) {
@@ -786,30 +806,40 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * TN;
                 for (uint32_t s = 0; s < n_stages && alive; ++s) {
-                    alive = mbar_wait(bfull_bar(bslot), bround & 1u, abort_p, err_word) &&
-                            mbar_wait(full_bar(slot), round & 1u, abort_p, err_word);
-                    if (!alive) break;
+                    if (!ready) {
+                        alive = mbar_wait(full_bar(slot), round & 1u, abort_p, err_word);
+                        alive = alive && mbar_wait(bfull_bar(bslot), bround & 1u, abort_p, err_word);
+                        if (!alive) break;
+                    }
                     tc_fence_after();
-                    const uint64_t x_desc = smem_desc_sw128(bring32 + bslot * bstride);
                     const uint64_t w_desc = smem_desc_sw128(smem32 + slot * W_STAGE);
-                    for (uint32_t a = 0; a < n_act; ++a) {
-#pragma unroll
-                        for (uint32_t k16 = 0; k16 < TC_BK / 16; ++k16)
-                            tc_mma_f16(d_tmem + a * TN, x_desc + a * (16384u >> 4) + 2 * k16, w_desc + 2 * k16, idesc,
-                                       (s | k16) != 0 ? 1u : 0u);
+                    const uint64_t x_desc = smem_desc_sw128(bring32 + bslot * bstride);
+                    // the next stage's places in the rings (the rings run on across tiles)
+                    uint32_t nslot = slot + 1, nround = round, nbslot = bslot + n_act, nbround = bround;
+                    if (nslot == n_ring) {
+                        nslot = 0;
+                        ++nround;
                     }
-                    tc_commit(empty_bar(slot));
+                    if (nbslot >= n_bring) {
+                        nbslot -= n_bring;
+                        ++nbround;
+                    }
+                    // A look at a barrier takes this thread a few hundred cycles. Looking at the next stage's two
+                    // barriers between this stage's instructions, while the tensor pipe still has those before
+                    // them to run, keeps the looks off the pipe's critical path; a barrier that is not yet
+                    // complete is waited for at the top of the next stage.
+                    tc_mma_f16(d_tmem, x_desc, w_desc, idesc, s != 0 ? 1u : 0u);
+                    tc_mma_f16(d_tmem, x_desc + 2, w_desc + 2, idesc, 1u);
+                    const bool r1 = mbar_try_wait(full_bar(nslot), nround & 1u);
+                    tc_mma_f16(d_tmem, x_desc + 4, w_desc + 4, idesc, 1u);
+                    const bool r2 = mbar_try_wait(bfull_bar(nbslot), nbround & 1u);
+                    tc_mma_f16(d_tmem, x_desc + 6, w_desc + 6, idesc, 1u);
                     tc_commit(bempty_bar(bslot));
-                    if (++slot == n_ring) {
-                        slot = 0;
-                        ++round;
-                    }
-                    if (++bslot == n_bring) {
-                        bslot = 0;
-                        ++bround;
-                    }
+                    tc_commit(empty_bar(slot));
+                    ready = r1 && r2;
+                    slot = nslot, round = nround, bslot = nbslot, bround = nbround;
                 }
-                if (alive) tc_commit(acc_full(acc));
+                if (alive) tc_commit(acc_full(n_act == 1 ? acc : 0u));
             }
             if (!alive) *abort_p = 1;
         }
@@ -901,7 +931,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     __syncthreads();
     if (warp == TS_MMA_WARP) {
         if (abort_flag && lane == 0) {  // abandoned: give MMAs in flight a bounded chance to finish
-            tc_commit(acc_full(0));
+            for (uint32_t a = 0; a < n_act; ++a) tc_commit(acc_full(0));
             for (uint32_t i = 0; i < kSpinLimit; ++i)
                 if (mbar_try_wait(acc_full(0), 0) || mbar_try_wait(acc_full(0), 1)) break;
         }
@@ -920,11 +950,11 @@ inline uint32_t stream_quarter_rows(uint32_t m_rows) { return m_rows <= 32u ? 8u
 inline uint32_t stream_act_rows(uint32_t m_rows) { return m_rows <= 32u ? 32u : ((m_rows + 15u) / 16u) * 16u; }
 
 // The two arrays of a weight as 2-D maps for tensor copies: [out_dim rows][row bytes] of bytes, zeros beyond the
-// edges. Quants: boxes of `box_rows` rows x 128 bytes with the 128-byte swizzle; scales: boxes of the same rows x
+// edges. Quants: boxes of `box_rows` rows x 128 (64) bytes with the 128-byte (64-byte) swizzle; scales: boxes of the same rows x
 // the scale bytes of a chunk, as stored. cuTensorMapEncodeTiled is a host-side computation; its entry point is
 // taken from the driver at first use (the library does not link against libcuda).
 int tensor_map_2d(const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes, uint32_t box_rows,
-                  bool swizzle128, CUtensorMap* out) {
+                  uint32_t swizzle_bytes, CUtensorMap* out) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -943,51 +973,79 @@ int tensor_map_2d(const void* base, uint64_t row_bytes, uint64_t rows, uint32_t 
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
                               CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                              swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                              : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                    : CU_TENSOR_MAP_SWIZZLE_NONE,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? ZQ_OK : ZQ_ERR_UNSUPPORTED;
 }
 
 // More than 128 activation rows: the same kernel with two activation tiles per CTA tile (256 weight rows x 256
-// activation rows, both accumulators in use). Measured against the large-batch kernel (Q4_0, TFLOP/s): vocabulary
-// head at 512 rows 736 against 654, at 2048 rows 777 against 625; 4096 -> 14336 at 2048 rows 737 against 738;
-// 14336 -> 4096 699 against 776 (128 CTA tiles for 148 SMs). Its two-deep rings (two 32 KB weight tiles, two 32 KB
-// activation tiles and two chunks fill shared memory) leave the commit and copy latencies exposed, so it is taken
-// only where every SM gets whole weight tiles of its own.
+// activation rows, both accumulators in use, an issuing thread for each). What bounds it is shared-memory traffic:
+// per 64-K stage the converters write 32 KB and read 8, the copies write 42 and the eight tensor-core instructions
+// read 96 (each reads its 4 KB of activations and 8 KB of weights), 178 KB = 1390 cycles at 128 bytes a cycle
+// against 1016 cycles of tensor-core time; measured 1800 cycles per stage. Measured against the large-batch
+// kernel (TFLOP/s, q4_0 unless noted): vocabulary head 1152 -> 262144 at 256 / 2048 rows 757 / 843;
+// 4096 -> 14336 at 512 / 2048 / 4096 rows 606 / 776 / 899 against 562 / 707 / 824 (q8_0: 611 / 753 / 864 against
+// 516 / 651 / 679); 1152 -> 6912 at 1024 / 4096 rows 332 / 563 against 276 / 451; 14336 -> 4096 at 2048 rows 738
+// against 744. With fewer CTA tiles than about two thirds of the SMs it loses (4096 -> 14336 at 256 rows: 320
+// against 399), so that is the rule.
 inline bool stream_wide_takes(const zq_weight* w, uint32_t m_rows) {
-    return m_rows > kStreamMaxRows && (w->out_dim + 255u) / 256u >= (uint32_t)sm_count();
+    if (m_rows <= kStreamMaxRows) return false;
+    const uint64_t tiles = (uint64_t)((w->out_dim + 255u) / 256u) * ((m_rows + 255u) / 256u);
+    return tiles >= kStreamMinTiles;
 }
 
-template <int TYPE, int TN>
+template <int TYPE, int TN, int CROW>
 int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
                      cudaStream_t st) {
-    auto kern = gemm_stream_kernel<TYPE, TN>;
+    auto kern = gemm_stream_kernel<TYPE, TN, CROW>;
     const bool wide = M > kStreamMaxRows;              // two activation tiles of 128 rows per CTA tile
     const uint32_t n_act = wide ? 2u : 1u;
-    const uint32_t act_rows = wide ? 256u : stream_act_rows(M);
+    const uint32_t act_rows = wide ? TS_ACT_ROWS : stream_act_rows(M);  // rows of a ring entry
     const uint32_t m_tiles = wide ? (M + 255u) / 256u : 1u;
     const uint32_t m_pad = wide ? m_tiles * 256u : act_rows;
     const uint32_t btile_bytes = act_rows * 128u;
-    constexpr uint32_t W_STAGE = TN * 128u, CHUNK_BYTES = TN * 128u + TN * 32u;
+    constexpr uint32_t SBOX = StreamScales<TYPE, CROW>::kBox;
+    constexpr uint32_t W_STAGE = TN * 128u, CHUNK_BYTES = TN * CROW + TN * SBOX;
     int dev = 0, max_smem = 0;
     ZQ_CUDA(cudaGetDevice(&dev));
     ZQ_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    // Shared memory: activation tiles (16-64 KB), then fp16 weight tiles, then packed chunks. A weight tile is free
-    // again only when its MMAs have run and their commit has arrived (half a microsecond after issue, measured),
-    // so the ring of weight tiles must be deep: four of 256 rows or six of 128 rows where that leaves two chunks.
+    // Shared memory: fp16 weight tiles, activation tiles, packed chunks. A weight tile is free again only when its
+    // MMAs have run and their commit has arrived (half a microsecond after issue, measured), so up to 128
+    // activation rows the ring of weight tiles is deep: four of 256 rows or six of 128 rows where that leaves
+    // two chunks. With two activation tiles per stage the converters refill a weight tile (0.3 us) sooner than a
+    // copy refills an activation tile (about a microsecond): two weight tiles, two chunks, and all the rest
+    // activation tiles (measured with two stages of them: the copies' latency was half of every stage).
     const uint32_t budget = (uint32_t)max_smem - 1024u - 10240u;  // alignment slack, static shared memory
     const uint32_t interleave = (!wide && stream_quarter_rows(M)) ? 1u : 0u;
-    uint32_t n_bring = (16u * 1024u) / btile_bytes;
-    if (n_bring > (uint32_t)TS_MAX_BTILES) n_bring = TS_MAX_BTILES;
-    if (n_bring < 2) n_bring = 2;
-    if (n_bring < 3 && btile_bytes <= 8192u) n_bring = 3;
-    if (interleave) n_bring = 4;
-    const uint32_t bring_bytes = interleave ? 20u * 1024u : ((n_bring * btile_bytes + 1023u) & ~1023u);
-    uint32_t n_ring = TN == 256 ? 4 : 6;
-    while (n_ring > 2 && budget < bring_bytes + n_ring * W_STAGE + 2 * CHUNK_BYTES) --n_ring;
-    if (budget < bring_bytes + n_ring * W_STAGE + 2 * CHUNK_BYTES) return ZQ_ERR_UNSUPPORTED;
-    uint32_t n_chunk_ring = (budget - bring_bytes - n_ring * W_STAGE) / CHUNK_BYTES;
-    if (n_chunk_ring > (uint32_t)TS_MAX_CHUNKS) n_chunk_ring = TS_MAX_CHUNKS;
+    uint32_t n_ring, n_bring, n_chunk_ring, bring_bytes;
+    if (wide) {
+        // An even number of activation tiles: entry e of the ring's sequence belongs to issuer e & 1, so with an
+        // even ring a slot always serves the same issuer, in that issuer's own order. (With an odd ring a slot
+        // changes hands every round, and the issuer that is ahead would find the parity it waits for already
+        // there, left by the round before.)
+        n_ring = 3;  // three weight tiles where that leaves four activation tiles (the 4-bit types), else two
+        n_chunk_ring = 2;
+        if (budget < n_ring * W_STAGE + n_chunk_ring * CHUNK_BYTES + 4u * btile_bytes) n_ring = 2;
+        if (budget < n_ring * W_STAGE + n_chunk_ring * CHUNK_BYTES + 4u * btile_bytes) return ZQ_ERR_UNSUPPORTED;
+        n_bring = (budget - n_ring * W_STAGE - n_chunk_ring * CHUNK_BYTES) / btile_bytes;
+        if (n_bring > (uint32_t)TS_MAX_BTILES) n_bring = TS_MAX_BTILES;
+        n_bring &= ~1u;
+        bring_bytes = n_bring * btile_bytes;  // 16 KB each
+    } else {
+        n_bring = (16u * 1024u) / btile_bytes;
+        if (n_bring > (uint32_t)TS_MAX_BTILES) n_bring = TS_MAX_BTILES;
+        if (n_bring < 2) n_bring = 2;
+        if (n_bring < 3 && btile_bytes <= 8192u) n_bring = 3;
+        if (interleave) n_bring = 4;
+        bring_bytes = interleave ? 20u * 1024u : ((n_bring * btile_bytes + 1023u) & ~1023u);
+        n_ring = TN == 256 ? 4 : 6;
+        while (n_ring > 2 && budget < bring_bytes + n_ring * W_STAGE + 2 * CHUNK_BYTES) --n_ring;
+        if (budget < bring_bytes + n_ring * W_STAGE + 2 * CHUNK_BYTES) return ZQ_ERR_UNSUPPORTED;
+        n_chunk_ring = (budget - bring_bytes - n_ring * W_STAGE) / CHUNK_BYTES;
+        if (n_chunk_ring > (uint32_t)TS_MAX_CHUNKS) n_chunk_ring = TS_MAX_CHUNKS;
+    }
     const size_t smem = (size_t)n_ring * W_STAGE + bring_bytes + (size_t)n_chunk_ring * CHUNK_BYTES + 1024;
     ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const uint32_t row_tiles = (w->out_dim + TN - 1) / TN;
@@ -999,8 +1057,8 @@ int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, fl
     if (rc != ZQ_OK) return rc;
     constexpr uint32_t SB = TYPE == ZQ_TYPE_Q4_1 ? 4 : 2;
     CUtensorMap wmap, smap;
-    rc = tensor_map_2d(w->qs, (uint64_t)w->nbp * w->qb, w->out_dim, 128, TN, true, &wmap);
-    if (rc == ZQ_OK) rc = tensor_map_2d(w->sc, (uint64_t)w->scp * SB, w->out_dim, StreamScales<TYPE>::kBox, TN, false, &smap);
+    rc = tensor_map_2d(w->qs, (uint64_t)w->nbp * w->qb, w->out_dim, CROW, TN, CROW, &wmap);
+    if (rc == ZQ_OK) rc = tensor_map_2d(w->sc, (uint64_t)w->scp * SB, w->out_dim, SBOX, TN, 0, &smap);
     if (rc != ZQ_OK) return rc;
     kern<<<grid, TS_THREADS, smem, st>>>(wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, interleave, n_act, m_tiles,
                                          m_pad, n_ring, n_bring, n_chunk_ring, err_word, ep);
@@ -1011,10 +1069,12 @@ int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, fl
 template <int TYPE>
 int launch_stream(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
                   cudaStream_t st) {
-    // 256-row tiles do twice the work per tensor-core instruction; 128-row tiles when those would leave SMs idle
-    if (M > kStreamMaxRows || (w->out_dim + 255u) / 256u >= (uint32_t)sm_count())
-        return launch_stream_tn<TYPE, 256>(w, xt, post, y, M, ep, st);
-    return launch_stream_tn<TYPE, 128>(w, xt, post, y, M, ep, st);
+    // More than 128 activation rows: 64-byte chunks for the 4-bit types (room for seven activation tiles instead
+    // of four). Otherwise 256-row tiles do twice the work per tensor-core instruction; 128-row tiles when those
+    // would leave SMs idle.
+    if (M > kStreamMaxRows) return launch_stream_tn<TYPE, 256, TYPE == ZQ_TYPE_Q8_0 ? 128 : 64>(w, xt, post, y, M, ep, st);
+    if ((w->out_dim + 255u) / 256u >= (uint32_t)sm_count()) return launch_stream_tn<TYPE, 256, 128>(w, xt, post, y, M, ep, st);
+    return launch_stream_tn<TYPE, 128, 128>(w, xt, post, y, M, ep, st);
 }
 
 inline bool stream_takes(const zq_weight* w, uint32_t m_rows) {
