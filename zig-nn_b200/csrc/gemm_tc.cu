@@ -501,7 +501,8 @@ constexpr int TS_COPY_WARP = TS_EPI_WARP0 + 4;   // packed chunks
 constexpr int TS_XCOPY_WARP = TS_COPY_WARP + 1;  // activation tiles (a warp of its own: one warp serving both rings
                                                  // waits for a free slot of one while the other runs dry)
 constexpr int TS_MMA_WARP2 = TS_XCOPY_WARP + 1;  // the second accumulator's issuer (more than 128 activation rows)
-constexpr int TS_THREADS = (TS_MMA_WARP2 + 1) * 32;  // 24 warps
+constexpr int TS_RELAY_WARP = TS_MMA_WARP2 + 1;  // a pair's second CTA: passes `weight tile full` on to the leader
+constexpr int TS_THREADS = (TS_RELAY_WARP + 1) * 32;  // 25 warps
 constexpr int TS_MAX_STAGES = 6;    // fp16 weight tiles (TN x 128 bytes each)
 constexpr int TS_MAX_BTILES = 16;   // activation tiles
 constexpr int TS_MAX_CHUNKS = 4;
@@ -560,6 +561,69 @@ __device__ __forceinline__ void read_packed(PackedQuad<TYPE>& p, uint32_t chunk,
         p.s.y = v.y;
     }
 }
+// ---- a pair of CTAs (cluster of two) on one tile: tcgen05 with cta_group::2 ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the address, in the cluster's shared window, of this CTA's shared address `addr` in CTA `rank`
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The relays' arrival. What it orders is a tensor-core read of the relaying CTA's own shared memory after that CTA's
+// writes (made visible to the asynchronous proxy by the writers' fences, observed by the relay through its own
+// barrier): the leader's threads never read that memory, so no release of it to the leader is needed, and a
+// releasing arrival at cluster scope costs the relay about a thousand cycles.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a barrier that CTAs of the cluster arrive on
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned int* err_word) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(err_word, kErrGemmTimeout);
+    return false;
+}
+// The leader's commit for the barrier at the same place in both CTAs: one commit per CTA, its own barrier by its
+// shared address (valid in the cluster's window too), the other CTA's through the window.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mapa_shared(bar, 1))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // 32 lanes x 16 consecutive columns of f32
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -574,7 +638,18 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // TN = weight rows per tile (UMMA N): 256, or 128 for matrices with too few rows to give every SM a 256-row tile.
 // CROW = packed bytes per row and chunk: 128 (2 quads of q4, 1 of q8_0) or, for q4, 64 (1 quad: chunks a quarter
 // of a stage pair smaller, which leaves room for a deeper ring of activation tiles).
-template <int TYPE, int TN, int CROW>
+//
+// PAIR: two CTAs (a cluster) share a tile of 256 weight rows x 512 activation rows. Each converts ITS 128 weight
+// rows (TN = 128) and copies ITS 128 rows of each activation tile; the leader's two issuing threads run
+// tcgen05.mma.cta_group::2 (M = 256: 128 activation rows from each CTA; N = 256: 128 weight rows from each), each
+// CTA's tensor memory receives the accumulator rows of its own activation rows. Per stage a CTA then moves 121 KB
+// through its shared memory instead of 178 (it writes half the weight tile and every instruction reads 4 + 4 KB
+// instead of 4 + 8), which is what bounded the single-CTA form. Barriers: the leader's `full` barriers count the
+// converting warps of both CTAs (the other CTA's arrive through the cluster's shared window); the leader's
+// activation barriers count its own copy and a relay thread of the other CTA, which waits for that CTA's copy;
+// the leader commits to both CTAs' barriers; the other CTA's draining warps arrive on the leader's `accumulator
+// free` barrier. Every copy is a plain one into the issuing CTA's own shared memory.
+template <int TYPE, int TN, int CROW, bool PAIR>
 __global__ void __launch_bounds__(TS_THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                    const __half* __restrict__ xt, const float* __restrict__ post, float* __restrict__ y, uint32_t N,
@@ -588,6 +663,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     constexpr uint32_t CQ = CROW / QUADB;          // quads per chunk: 2 (q4) or 1 (q8_0; q4 with 64-byte chunks)
     constexpr bool PAIRED = CQ == 1 && TYPE != ZQ_TYPE_Q4_1;  // the scale box holds the quad's scales and its neighbour's
     constexpr uint32_t SBOX = StreamScales<TYPE, CROW>::kBox;
+    static_assert(!PAIR || TN == 128, "a pair: 128 weight rows from each CTA");
+    constexpr uint32_t ACC_N = PAIR ? 256u : (uint32_t)TN;  // columns of an accumulator = weight rows of a tile
+    constexpr uint32_t ACT_TILE = PAIR ? 256u : TS_ACT_ROWS;  // activation rows of an accumulator (all CTAs together)
     constexpr uint32_t W_STAGE = TN * 128u;        // fp16 weight tile of a stage
     constexpr uint32_t CHUNK_BYTES = TN * CROW + TN * SBOX;  // packed box, then the scale box (both multiples of 1 KB)
     extern __shared__ __align__(16) unsigned char smem[];
@@ -623,20 +701,26 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     // A CTA tile = TN weight rows x n_act activation tiles of 128 rows (n_act = 2 for more than 128 activation rows:
     // both accumulators then belong to one tile). Tile t = blockIdx.x + i * gridDim.x covers weight tile t % row_tiles
     // and activation rows [t / row_tiles * 128 * n_act, ...).
-    const uint32_t row_tiles = (N + TN - 1) / TN;
+    // A pair: the same with tiles of 256 weight rows x 2 activation tiles of 256 rows, walked by the cluster.
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;  // 0: the leader
+    const uint32_t walker = PAIR ? blockIdx.x >> 1 : blockIdx.x, walkers = PAIR ? gridDim.x >> 1 : gridDim.x;
+    const uint32_t row_tiles = (N + ACC_N - 1) / ACC_N;
     const uint32_t tiles_total = row_tiles * m_tiles;
-    const uint32_t nt = tiles_total > blockIdx.x ? (tiles_total - blockIdx.x - 1) / gridDim.x + 1 : 0;  // this CTA's tiles
+    const uint32_t nt = tiles_total > walker ? (tiles_total - walker - 1) / walkers + 1 : 0;  // this CTA's (pair's) tiles
     const uint32_t n_quads = nbp / 4, n_stages = nbp / 2;
     const uint32_t n_chunks = (n_quads + CQ - 1) / CQ;  // per tile
-    constexpr uint32_t tmem_cols = 2 * TN;               // two accumulators of TN columns
+    constexpr uint32_t tmem_cols = 2 * ACC_N;            // two accumulators
 
     if (tid == 0) {
         for (uint32_t s = 0; s < n_ring; ++s) {
-            mbar_init(full_bar(s), TS_CONVERT_WARPS);  // one arrival per converting warp
+            // one arrival per converting warp; a pair: the stage's activation tiles are counted on the same barrier
+            // (the copy warp's arrival with their bytes), and the leader's also counts the other CTA's relay
+            mbar_init(full_bar(s), TS_CONVERT_WARPS + (PAIR ? 1 : 0) + ((PAIR && crank == 0) ? 1 : 0));
             mbar_init(empty_bar(s), n_act);            // one commit per issuer
         }
         for (uint32_t s = 0; s < n_bring; ++s) {
-            mbar_init(bfull_bar(s), 1);  // the copy warp's arrival with the byte count
+            // the copy warp's arrival with the byte count; the leader's also counts the other CTA's relay
+            mbar_init(bfull_bar(s), (PAIR && crank == 0) ? 2 : 1);
             mbar_init(bempty_bar(s), 1);
         }
         for (uint32_t c = 0; c < n_chunk_ring; ++c) {
@@ -645,19 +729,26 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         }
         for (uint32_t a = 0; a < 2; ++a) {
             mbar_init(acc_full(a), a == 0 ? n_act : 1u);  // two activation tiles: both issuers commit to the first
-            mbar_init(acc_empty(a), 4);  // one arrival per draining warp
+            mbar_init(acc_empty(a), PAIR ? 8 : 4);  // one arrival per draining warp (of both CTAs)
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TS_MMA_WARP) {
         const uint32_t slot = (uint32_t)__cvta_generic_to_shared(&tmem_base_slot);
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(tmem_cols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {  // the same warp of both CTAs
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(tmem_cols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(tmem_cols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // both CTAs' barriers are initialised before either arrives on the other's
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_p = &abort_flag;
@@ -716,8 +807,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         uint32_t cslot = 0, cround = 0;
         bool alive = true;
         for (uint32_t ti = 0; ti < nt && alive; ++ti) {
-            const uint32_t tile = blockIdx.x + ti * gridDim.x;
-            const uint32_t mt = tile / row_tiles, row0 = (tile - mt * row_tiles) * TN;
+            const uint32_t tile = walker + ti * walkers;
+            const uint32_t mt = tile / row_tiles, row0 = (tile - mt * row_tiles) * ACC_N + crank * TN;
             for (uint32_t c = 0; c < n_chunks && alive; ++c) {
                 if (cround > 0) alive = mbar_wait(cempty_bar(cslot), (cround - 1) & 1u, abort_p, err_word);
                 alive = __all_sync(0xFFFFFFFFu, alive);
@@ -750,8 +841,43 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         // ================= copy warp: the activation tiles of the stages =================
         uint32_t bslot = 0, bround = 0;
         bool alive = true;
-        for (uint32_t ti = 0; ti < nt && alive; ++ti) {
-            const uint32_t mt = (blockIdx.x + ti * gridDim.x) / row_tiles;
+        if (PAIR) {
+            // A pair keeps one ring: slot s holds the stage's weight tile and, in the activation region, its two
+            // activation tiles (32 KB from s * 32 KB), all counted on the stage's `full` barrier and freed by the
+            // issuers' commits to its `empty` barrier. The issuers then look at one barrier per stage.
+            uint32_t slot = 0, round = 0;
+            for (uint32_t ti = 0; ti < nt && alive; ++ti) {
+                const uint32_t mt = (walker + ti * walkers) / row_tiles;
+                for (uint32_t sg = 0; sg < n_stages && alive; ++sg) {
+                    if (round > 0) alive = mbar_wait(empty_bar(slot), (round - 1) & 1u, abort_p, err_word);
+                    alive = __all_sync(0xFFFFFFFFu, alive);
+                    if (!alive) break;
+                    if (lane == 0) {
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(slot)),
+                                     "r"(2u * btile_bytes)
+                                     : "memory");
+                        for (uint32_t a = 0; a < 2; ++a) {
+                            const unsigned char* src =
+                                reinterpret_cast<const unsigned char*>(xt) +
+                                ((size_t)sg * m_pad + ((size_t)mt * 2 + a) * ACT_TILE + crank * TS_ACT_ROWS) * 128u;
+                            bulk_copy_g2s(bring32 + (slot * 2 + a) * btile_bytes, src, btile_bytes, full_bar(slot));
+                        }
+                    }
+                    __syncwarp();
+                    if (++slot == n_ring) {
+                        slot = 0;
+                        ++round;
+                    }
+                }
+            }
+            if (!alive) {
+                for (uint32_t s = 0; s < n_ring; ++s)
+                    for (uint32_t i = 0; i < (1u << 16); ++i)
+                        if (mbar_try_wait(full_bar(s), 0) || mbar_try_wait(full_bar(s), 1)) break;
+            }
+        }
+        for (uint32_t ti = 0; ti < nt && alive && !PAIR; ++ti) {
+            const uint32_t mt = (walker + ti * walkers) / row_tiles;
             // one ring entry per stage and activation tile
             for (uint32_t sa = 0; sa < n_stages * n_act && alive; ++sa) {
                 const uint32_t sg = n_act == 1 ? sa : sa >> 1, a = n_act == 1 ? 0u : sa & 1u;
@@ -763,7 +889,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                                  "r"(btile_bytes)
                                  : "memory");
                     const unsigned char* src = reinterpret_cast<const unsigned char*>(xt) +
-                                               ((size_t)sg * m_pad + ((size_t)mt * n_act + a) * TS_ACT_ROWS) * 128u;
+                                               ((size_t)sg * m_pad + ((size_t)mt * n_act + a) * ACT_TILE + crank * TS_ACT_ROWS) * 128u;
                     if (interleave) {
                         for (uint32_t q = 0; q < 4; ++q)
                             bulk_copy_g2s(bring32 + bslot * bstride + q * 4096u, src + q * 1024u, 1024u, bfull_bar(bslot));
@@ -778,11 +904,30 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 }
             }
         }
-        if (!alive) {
+        if (!alive && !PAIR) {
             for (uint32_t s = 0; s < n_bring; ++s)
                 for (uint32_t i = 0; i < (1u << 16); ++i)
                     if (mbar_try_wait(bfull_bar(s), 0) || mbar_try_wait(bfull_bar(s), 1)) break;
         }
+    } else if (warp == TS_RELAY_WARP) {
+        // A pair's second CTA: when its 16 converting warps have filled a stage's weight tile and its copies of the
+        // stage's activation tiles have landed, one arrival on the leader's barrier of that stage. (An arrival with cluster-wide release by every converting warp cost each of them
+        // about a thousand cycles per stage, measured.)
+        if (PAIR && crank != 0 && lane == 0) {
+            uint32_t slot = 0, round = 0;
+            bool alive = true;
+            for (uint32_t e = 0; e < nt * n_stages && alive; ++e) {
+                alive = mbar_wait(full_bar(slot), round & 1u, abort_p, err_word);
+                if (!alive) break;
+                mbar_arrive_cluster_relaxed(mapa_shared(full_bar(slot), 0));
+                if (++slot == n_ring) {
+                    slot = 0;
+                    ++round;
+                }
+            }
+            if (!alive) *abort_p = 1;
+        }
+        __syncwarp();
     } else if (warp == TS_MMA_WARP || warp == TS_MMA_WARP2) {
         // ================= MMA issuers: D[activation row][weight row] += X . W^T =================
         // Up to 128 activation rows: one issuer, the two accumulators take turns between tiles. More: both
@@ -791,8 +936,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         // (measured: one thread issuing a stage's eight instructions and looking at three barriers spent 1430 + 970
         // cycles per stage); two threads look at theirs at the same time.
         const uint32_t me = warp == TS_MMA_WARP ? 0u : 1u;
-        if (lane == 0 && me < n_act) {
-            const uint32_t idesc = idesc_f16(TS_ACT_ROWS, TN);
+        if (PAIR && crank != 0) {
+            // the other CTA of a pair issues nothing
+        } else if (lane == 0 && me < n_act) {
+            const uint32_t idesc = idesc_f16(PAIR ? 256u : TS_ACT_ROWS, ACC_N);
             uint32_t slot = 0, round = 0, bslot = me, bround = 0;  // this issuer's ring entries: me, me + n_act, ...
             bool alive = true, ready = false;
             for (uint32_t i = 0; i < nt && alive; ++i) {
@@ -800,20 +947,25 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 if (n_act == 1) {
                     if (i >= 2) alive = mbar_wait(acc_empty(acc), ((i >> 1) - 1) & 1u, abort_p, err_word);
                 } else if (i >= 1) {
-                    alive = mbar_wait(acc_empty(0), (i - 1) & 1u, abort_p, err_word);
+                    alive = PAIR ? mbar_wait_cluster(acc_empty(0), (i - 1) & 1u, abort_p, err_word)
+                                 : mbar_wait(acc_empty(0), (i - 1) & 1u, abort_p, err_word);
                 }
                 if (!alive) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * TN;
+                const uint32_t d_tmem = tmem_base + acc * ACC_N;
                 for (uint32_t s = 0; s < n_stages && alive; ++s) {
                     if (!ready) {
-                        alive = mbar_wait(full_bar(slot), round & 1u, abort_p, err_word);
-                        alive = alive && mbar_wait(bfull_bar(bslot), bround & 1u, abort_p, err_word);
+                        if (PAIR) {
+                            alive = mbar_wait_cluster(full_bar(slot), round & 1u, abort_p, err_word);
+                        } else {
+                            alive = mbar_wait(full_bar(slot), round & 1u, abort_p, err_word);
+                            alive = alive && mbar_wait(bfull_bar(bslot), bround & 1u, abort_p, err_word);
+                        }
                         if (!alive) break;
                     }
                     tc_fence_after();
                     const uint64_t w_desc = smem_desc_sw128(smem32 + slot * W_STAGE);
-                    const uint64_t x_desc = smem_desc_sw128(bring32 + bslot * bstride);
+                    const uint64_t x_desc = smem_desc_sw128(PAIR ? bring32 + (slot * 2 + me) * btile_bytes : bring32 + bslot * bstride);
                     // the next stage's places in the rings (the rings run on across tiles)
                     uint32_t nslot = slot + 1, nround = round, nbslot = bslot + n_act, nbround = bround;
                     if (nslot == n_ring) {
@@ -828,18 +980,32 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     // barriers between this stage's instructions, while the tensor pipe still has those before
                     // them to run, keeps the looks off the pipe's critical path; a barrier that is not yet
                     // complete is waited for at the top of the next stage.
-                    tc_mma_f16(d_tmem, x_desc, w_desc, idesc, s != 0 ? 1u : 0u);
-                    tc_mma_f16(d_tmem, x_desc + 2, w_desc + 2, idesc, 1u);
-                    const bool r1 = mbar_try_wait(full_bar(nslot), nround & 1u);
-                    tc_mma_f16(d_tmem, x_desc + 4, w_desc + 4, idesc, 1u);
-                    const bool r2 = mbar_try_wait(bfull_bar(nbslot), nbround & 1u);
-                    tc_mma_f16(d_tmem, x_desc + 6, w_desc + 6, idesc, 1u);
-                    tc_commit(bempty_bar(bslot));
-                    tc_commit(empty_bar(slot));
+                    bool r1, r2;
+                    if (PAIR) {
+                        tc_mma_f16_pair(d_tmem, x_desc, w_desc, idesc, s != 0 ? 1u : 0u);
+                        tc_mma_f16_pair(d_tmem, x_desc + 2, w_desc + 2, idesc, 1u);
+                        tc_mma_f16_pair(d_tmem, x_desc + 4, w_desc + 4, idesc, 1u);
+                        r1 = mbar_try_wait_cluster(full_bar(nslot), nround & 1u);
+                        r2 = true;
+                        tc_mma_f16_pair(d_tmem, x_desc + 6, w_desc + 6, idesc, 1u);
+                        tc_commit_pair(empty_bar(slot));
+                    } else {
+                        tc_mma_f16(d_tmem, x_desc, w_desc, idesc, s != 0 ? 1u : 0u);
+                        tc_mma_f16(d_tmem, x_desc + 2, w_desc + 2, idesc, 1u);
+                        r1 = mbar_try_wait(full_bar(nslot), nround & 1u);
+                        tc_mma_f16(d_tmem, x_desc + 4, w_desc + 4, idesc, 1u);
+                        r2 = mbar_try_wait(bfull_bar(nbslot), nbround & 1u);
+                        tc_mma_f16(d_tmem, x_desc + 6, w_desc + 6, idesc, 1u);
+                        tc_commit(bempty_bar(bslot));
+                        tc_commit(empty_bar(slot));
+                    }
                     ready = r1 && r2;
                     slot = nslot, round = nround, bslot = nbslot, bround = nbround;
                 }
-                if (alive) tc_commit(acc_full(n_act == 1 ? acc : 0u));
+                if (alive) {
+                    if (PAIR) tc_commit_pair(acc_full(0));
+                    else tc_commit(acc_full(n_act == 1 ? acc : 0u));
+                }
             }
             if (!alive) *abort_p = 1;
         }
@@ -863,12 +1029,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             alive = __all_sync(0xFFFFFFFFu, alive);
             if (!alive) break;
             tc_fence_after();
-            const uint32_t tile = blockIdx.x + i * gridDim.x;
-            const uint32_t mt = tile / row_tiles, n0 = (tile - mt * row_tiles) * TN;
+            const uint32_t tile = walker + i * walkers;
+            const uint32_t mt = tile / row_tiles, n0 = (tile - mt * row_tiles) * ACC_N;
             for (uint32_t a = 0; a < n_act; ++a) {
                 // activation rows of this accumulator: lane j of this quarter holds row m0 + 4 j + quarter when
                 // interleaved (up to 32 rows in all), m0 + 32 quarter + j otherwise
-                const uint32_t m0 = (mt * n_act + a) * TS_ACT_ROWS;
+                const uint32_t m0 = (mt * n_act + a) * ACT_TILE + crank * TS_ACT_ROWS;
                 const uint32_t m = interleave ? 4u * (uint32_t)lane + quarter : m0 + lane_base + lane;
                 const uint32_t first = interleave ? quarter : m0 + lane_base;  // first row of this quarter
                 if (first >= M) continue;                                         // uniform over the warp
@@ -876,10 +1042,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 const float scale = (m < M && (!interleave || lane < 8)) ? post[m] : 0.0f;
                 const uint32_t m_step = interleave ? 8u : 2u;
                 const uint32_t m_first = interleave ? 4u * hr + quarter : first + hr;
-                for (uint32_t c = 0; c < (uint32_t)TN; c += 16) {
+                for (uint32_t c = 0; c < ACC_N; c += 16) {
                     if (n0 + c >= N) break;  // uniform over the warp
                     uint32_t v16[16];
-                    tc_ld16(tmem_base + (lane_base << 16) + (acc + a) * TN + c, v16);
+                    tc_ld16(tmem_base + (lane_base << 16) + (acc + a) * ACC_N + c, v16);
                     tc_wait_ld();
 #pragma unroll
                     for (int k = 0; k < 16; ++k) stage[lane][k] = __uint_as_float(v16[k]) * scale;
@@ -923,13 +1089,16 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(acc));
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(mapa_shared(acc_empty(0), 0));  // the leader's issuers wait for both CTAs
+                else mbar_arrive(acc_empty(acc));
+            }
         }
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == TS_MMA_WARP) {
+    if (warp == TS_MMA_WARP && !PAIR) {
         if (abort_flag && lane == 0) {  // abandoned: give MMAs in flight a bounded chance to finish
             for (uint32_t a = 0; a < n_act; ++a) tc_commit(acc_full(0));
             for (uint32_t i = 0; i < kSpinLimit; ++i)
@@ -938,6 +1107,23 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+    if (PAIR) {
+        if (warp == TS_MMA_WARP && crank == 0 && abort_flag && lane == 0) {
+            // abandoned: the leader gives the pair's instructions in flight a bounded chance to finish (the commits
+            // reach both CTAs; a phase may already be complete, so either parity ends the wait)
+            tc_commit_pair(acc_full(1));
+            for (uint32_t i = 0; i < kSpinLimit; ++i)
+                if (mbar_try_wait(acc_full(1), 0)) break;
+        }
+        __syncwarp();
+        // Neither CTA retires, frees tensor memory or lets go of its shared memory while the other may still arrive
+        // on its barriers or read its tiles: both have left their loops (every wait in them is bounded) first.
+        cluster_sync_all();
+        if (warp == TS_MMA_WARP) {
+            tc_fence_after();
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        }
     }
 }
 
@@ -999,7 +1185,7 @@ inline bool stream_wide_takes(const zq_weight* w, uint32_t m_rows) {
 template <int TYPE, int TN, int CROW>
 int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
                      cudaStream_t st) {
-    auto kern = gemm_stream_kernel<TYPE, TN, CROW>;
+    auto kern = gemm_stream_kernel<TYPE, TN, CROW, false>;
     const bool wide = M > kStreamMaxRows;              // two activation tiles of 128 rows per CTA tile
     const uint32_t n_act = wide ? 2u : 1u;
     const uint32_t act_rows = wide ? TS_ACT_ROWS : stream_act_rows(M);  // rows of a ring entry
@@ -1066,9 +1252,76 @@ int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, fl
     return ZQ_OK;
 }
 
+// A pair of CTAs per tile of 256 weight rows x 512 activation rows (see the kernel). 74 pairs walk the tiles.
+constexpr uint32_t kPairActRows = 512;
+// Measured against the single-CTA form with two activation tiles and the large-batch kernel (TFLOP/s, q4_0 unless
+// noted): 4096 -> 14336 at 512 / 1024 / 2048 / 4096 rows 742 / 868 / 943 / 1081 against 606 / 713 / 776 / 899 and
+// 562 / 638 / 707 / 824 (q8_0 at 4096 rows: 1021 against 864 and 679); 14336 -> 4096 at 2048 / 4096 rows 876 / 928
+// against 738 / 774 and 744 / 788; vocabulary head 1152 -> 262144 at 512 / 2048 rows 917 / 953 against 818 / 843;
+// 1152 -> 6912 at 1024 / 4096 rows 343 / 594 against 332 / 563. It loses where half of its 512-row activation tile
+// is empty (head at 256 rows: 577 against 757), where the pairs get fewer than about 48 tiles (14336 -> 4096 at 1024
+// rows: 32 tiles, 533 against 561 of the large-batch kernel) and by a little on short K, where the drain of the
+// accumulators outweighs the stages (768 -> 50257 at 4096 rows: 611 against 656).
+inline bool stream_pair_takes(const zq_weight* w, uint32_t m_rows) {
+    if (m_rows <= 256u || w->in_dim < 1024u) return false;
+    const uint64_t tiles = (uint64_t)((w->out_dim + 255u) / 256u) * ((m_rows + kPairActRows - 1) / kPairActRows);
+    return tiles >= 48;
+}
+
+template <int TYPE>
+int launch_stream_pair(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
+                       cudaStream_t st) {
+    constexpr int TN = 128, CROW = TYPE == ZQ_TYPE_Q8_0 ? 128 : 64;
+    auto kern = gemm_stream_kernel<TYPE, TN, CROW, true>;
+    const uint32_t n_act = 2, act_rows = TS_ACT_ROWS;
+    const uint32_t m_tiles = (M + kPairActRows - 1) / kPairActRows, m_pad = m_tiles * kPairActRows;
+    const uint32_t btile_bytes = act_rows * 128u;
+    constexpr uint32_t SBOX = StreamScales<TYPE, CROW>::kBox;
+    constexpr uint32_t W_STAGE = TN * 128u, CHUNK_BYTES = TN * CROW + TN * SBOX;
+    int dev = 0, max_smem = 0;
+    ZQ_CUDA(cudaGetDevice(&dev));
+    ZQ_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    const uint32_t budget = (uint32_t)max_smem - 1024u - 10240u;  // alignment slack, static shared memory
+    // one ring: a stage's weight tile (16 KB) and its two activation tiles (32 KB); two chunks (20-36 KB)
+    const uint32_t n_chunk_ring = 2;
+    uint32_t n_ring = (budget - n_chunk_ring * CHUNK_BYTES) / (W_STAGE + 2u * btile_bytes);  // 4 (q4) or 3 (q8_0)
+    if (n_ring > (uint32_t)TS_MAX_STAGES) n_ring = TS_MAX_STAGES;
+    if (n_ring < 2) return ZQ_ERR_UNSUPPORTED;
+    const uint32_t n_bring = 2u * n_ring;
+    const size_t smem = (size_t)n_ring * W_STAGE + (size_t)n_bring * btile_bytes + (size_t)n_chunk_ring * CHUNK_BYTES + 1024;
+    ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const uint64_t tiles_total = (uint64_t)((w->out_dim + 255u) / 256u) * m_tiles;
+    const uint32_t pairs_max = (uint32_t)sm_count() / 2u;
+    const uint32_t pairs = tiles_total < pairs_max ? (uint32_t)tiles_total : pairs_max;
+    unsigned int* err_word = nullptr;
+    int rc = device_error_word(&err_word);
+    if (rc != ZQ_OK) return rc;
+    constexpr uint32_t SB = TYPE == ZQ_TYPE_Q4_1 ? 4 : 2;
+    CUtensorMap wmap, smap;
+    rc = tensor_map_2d(w->qs, (uint64_t)w->nbp * w->qb, w->out_dim, CROW, TN, CROW, &wmap);
+    if (rc == ZQ_OK) rc = tensor_map_2d(w->sc, (uint64_t)w->scp * SB, w->out_dim, SBOX, TN, 0, &smap);
+    if (rc != ZQ_OK) return rc;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2u * pairs);
+    cfg.blockDim = dim3(TS_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ZQ_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, 0u, n_act, m_tiles, m_pad,
+                               n_ring, n_bring, n_chunk_ring, err_word, ep));
+    return ZQ_OK;
+}
+
 template <int TYPE>
 int launch_stream(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
                   cudaStream_t st) {
+    if (stream_pair_takes(w, M)) return launch_stream_pair<TYPE>(w, xt, post, y, M, ep, st);
     // More than 128 activation rows: 64-byte chunks for the 4-bit types (room for seven activation tiles instead
     // of four). Otherwise 256-row tiles do twice the work per tensor-core instruction; 128-row tiles when those
     // would leave SMs idle.
@@ -1078,7 +1331,7 @@ int launch_stream(const zq_weight* w, const __half* xt, const float* post, float
 }
 
 inline bool stream_takes(const zq_weight* w, uint32_t m_rows) {
-    if (m_rows > kStreamMaxRows) return stream_wide_takes(w, m_rows);
+    if (m_rows > kStreamMaxRows) return stream_pair_takes(w, m_rows) || stream_wide_takes(w, m_rows);
     return (w->out_dim + TC_BN - 1) / TC_BN >= kStreamMinTiles;
 }
 
@@ -1131,7 +1384,7 @@ bool gemm_stream_takes(const zq_weight* w, uint32_t m_rows) { return stream_take
 size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows) {
     uint32_t n_mma, m_pad;
     tc_tiling(m_rows, &n_mma, &m_pad);  // never less than the streaming form's padding to 16 rows ...
-    if (m_rows > 128 && m_pad < ((m_rows + 255u) / 256u) * 256u) m_pad = ((m_rows + 255u) / 256u) * 256u;  // ... or to 256
+    if (m_rows > 128 && m_pad < ((m_rows + 511u) / 512u) * 512u) m_pad = ((m_rows + 511u) / 512u) * 512u;  // ... or to 512
     const size_t xb = ((size_t)(w->nbp / 2) * m_pad * 64 * sizeof(__half) + 255) & ~(size_t)255;
     const size_t pb = ((size_t)m_rows * sizeof(float) + 255) & ~(size_t)255;
     return xb + pb;
@@ -1143,7 +1396,11 @@ int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows
     uint32_t n_mma, m_pad;
     tc_tiling(m_rows, &n_mma, &m_pad);
     const bool stream = stream_takes(w, m_rows);
-    if (stream) m_pad = m_rows > kStreamMaxRows ? ((m_rows + 255u) / 256u) * 256u : stream_act_rows(m_rows);
+    if (stream) {
+        m_pad = m_rows <= kStreamMaxRows ? stream_act_rows(m_rows)
+                : stream_pair_takes(w, m_rows) ? ((m_rows + kPairActRows - 1) / kPairActRows) * kPairActRows
+                                               : ((m_rows + 255u) / 256u) * 256u;
+    }
     const uint32_t n_seg = w->nbp / 2;
     const size_t xb = ((size_t)n_seg * m_pad * 64 * sizeof(__half) + 255) & ~(size_t)255;
     __half* xt = static_cast<__half*>(workspace);
