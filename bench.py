@@ -330,6 +330,44 @@ def sweep_stream(torch, zq, ggml):
     return out
 
 
+def sweep_many_rows(torch, zq, ggml):
+    """The tensor-core GEMM at 512 / 2048 / 4096 f32 activation rows (pairs of CTAs, tcgen05 cta_group::2, where the
+    library takes that form): TFLOP/s = 2 M N K / time by CUDA events, activation-conversion launch included,
+    median of 5 after 3 warm-up calls. `of_peak` is against the measured cuBLAS bf16 burst."""
+    peak = 1590.0  # fallback: an earlier measurement on this pool
+    try:
+        peak = float(json.load(open(os.path.join(REPO, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    out = []
+    for qname, k, n in (("q4_0", 4096, 14336), ("q4_0", 14336, 4096), ("q8_0", 4096, 14336), ("q4_0", 1152, 262144)):
+        raw = make_weight_bytes(qname, n, k, 42, "cuda")
+        w = zq.QuantWeight(raw, ggml.TYPE_IDS[qname], n, k)
+        for m in (512, 2048, 4096):
+            if m * n > 600e6:
+                continue
+            x = torch.randn(m, k, device="cuda")
+            y = torch.empty(m, n, device="cuda")
+            wsb = torch.empty(max(_lib_ws(zq, w, m, zq.ACT_F32), 256), dtype=torch.uint8, device="cuda")
+            for _ in range(3):
+                zq.quant_matmul_no_grad(x, w, zq.ACT_F32, out=y, workspace=wsb)
+            times = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                zq.quant_matmul_no_grad(x, w, zq.ACT_F32, out=y, workspace=wsb)
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1) * 1e3)
+            us = sorted(times)[2]
+            tf = 2.0 * m * n * k / us / 1e6
+            out.append({"type": qname, "k": k, "n": n, "m": m, "us": round(us, 1), "tflops": round(tf, 1),
+                        "of_peak": round(tf / peak, 3)})
+            del x, y, wsb
+        del w, raw
+    return out
+
+
 def decode_bytes_per_token(name, cfg, ctx_mid):
     """Algorithmic HBM bytes of one decoded token: every quantised block once (plus GPT-2's f32 embedding
     matrix as the logits head) and the key / value rows the attention reads at context `ctx_mid`."""
@@ -803,6 +841,10 @@ def main():
                 line["extra"]["sweep_streaming_gemm"] = sweep_stream(torch, zq, ggml)
             except Exception as e:  # noqa: BLE001
                 line["extra"]["sweep_streaming_gemm"] = {"error": repr(e)}
+            try:
+                line["extra"]["sweep_many_rows_gemm"] = sweep_many_rows(torch, zq, ggml)
+            except Exception as e:
+                line["extra"]["sweep_many_rows_gemm"] = {"error": repr(e)}
         print(json.dumps(line), flush=True)
     if use_dist:
         dist.barrier()
