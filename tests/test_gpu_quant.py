@@ -564,13 +564,13 @@ def test_streaming_gemm_epilogue_and_row_counts(zq):
 
 
 @pytest.mark.parametrize("qt,block_bytes", STREAM_TYPES)
-@pytest.mark.parametrize("k", [256, 1024])
-def test_streaming_gemm_wide_many_activation_tiles_and_epilogue(zq, qt, block_bytes, k):
-    """More than 128 activation rows on a small matrix, 11 ragged weight tiles, ragged activation tiles, every ring
-    wrapping several times within a tile, and the whole epilogue (bias, GELU, multiplier, residual).
-    K = 256: one CTA per tile of 256 x 256 (99 tiles); K = 1024: a pair of CTAs per tile of 256 weight rows x 512
-    activation rows (55 tiles, tcgen05 with cta_group::2)."""
-    n, m = 2600, 2300
+@pytest.mark.parametrize("k,n,m", [(256, 2600, 2300), (1024, 2600, 2300), (1024, 3880, 2148)])
+def test_streaming_gemm_wide_many_activation_tiles_and_epilogue(zq, qt, block_bytes, k, n, m):
+    """More than 128 activation rows on a small matrix, ragged weight and activation tiles, every ring wrapping
+    several times within a tile, and the whole epilogue (bias, GELU, multiplier, residual).
+    K = 256: one CTA per tile of 256 x 256 (99 tiles). K = 1024: a pair of CTAs per tile of 256 weight rows x 512
+    activation rows (tcgen05 with cta_group::2): 55 tiles, less than a round of the 74 pairs; 80 tiles, whose last
+    six are walked as twelve half tiles of one activation tile."""
     g = torch.Generator(device="cuda").manual_seed(77 + int(qt))
     raw_d = ggml.quantize(qt, torch.randn(n, k, generator=g, device="cuda") * 0.05)
     qw = zq.QuantWeight(raw_d, qt, n, k)

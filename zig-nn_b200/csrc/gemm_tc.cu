@@ -654,8 +654,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                    const __half* __restrict__ xt, const float* __restrict__ post, float* __restrict__ y, uint32_t N,
                    uint32_t M, uint32_t nbp, uint32_t act_rows, uint32_t interleave, uint32_t n_act, uint32_t m_tiles,
-                   uint32_t m_pad, uint32_t n_ring, uint32_t n_bring, uint32_t n_chunk_ring, unsigned int* err_word,
-                   TcEpilogue ep) {
+                   uint32_t m_pad, uint32_t n_ring, uint32_t n_bring, uint32_t n_chunk_ring, uint32_t first_half,
+                   unsigned int* err_word, TcEpilogue ep) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr uint32_t QB = Q8 ? 32 : 16;          // packed bytes per block
     constexpr uint32_t QUADB = 4 * QB;             // packed bytes per quad
@@ -705,7 +705,24 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     const uint32_t crank = PAIR ? cluster_ctarank() : 0u;  // 0: the leader
     const uint32_t walker = PAIR ? blockIdx.x >> 1 : blockIdx.x, walkers = PAIR ? gridDim.x >> 1 : gridDim.x;
     const uint32_t row_tiles = (N + ACC_N - 1) / ACC_N;
-    const uint32_t tiles_total = row_tiles * m_tiles;
+    // A pair's last round: when it would hold tiles for at most half of the pairs, those tiles (from `first_half`
+    // on) are each walked as two half tiles of one activation tile, by twice as many pairs in half the time.
+    const uint32_t tiles_whole = row_tiles * m_tiles;
+    const uint32_t tiles_total = tiles_whole + (PAIR ? tiles_whole - first_half : 0u);
+    // tile t -> weight tile, its first activation tile (of ACT_TILE rows) and how many activation tiles it has
+    auto tile_of = [&](uint32_t t, uint32_t& wt, uint32_t& at0, uint32_t& acnt) {
+        uint32_t whole = t, half = 0;
+        acnt = n_act;
+        if (PAIR && t >= first_half) {
+            const uint32_t h = t - first_half;
+            whole = first_half + (h >> 1);
+            half = h & 1u;
+            acnt = 1;
+        }
+        const uint32_t mt = whole / row_tiles;
+        wt = whole - mt * row_tiles;
+        at0 = mt * n_act + half;
+    };
     const uint32_t nt = tiles_total > walker ? (tiles_total - walker - 1) / walkers + 1 : 0;  // this CTA's (pair's) tiles
     const uint32_t n_quads = nbp / 4, n_stages = nbp / 2;
     const uint32_t n_chunks = (n_quads + CQ - 1) / CQ;  // per tile
@@ -807,8 +824,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         uint32_t cslot = 0, cround = 0;
         bool alive = true;
         for (uint32_t ti = 0; ti < nt && alive; ++ti) {
-            const uint32_t tile = walker + ti * walkers;
-            const uint32_t mt = tile / row_tiles, row0 = (tile - mt * row_tiles) * ACC_N + crank * TN;
+            uint32_t wt, at0, acnt;
+            tile_of(walker + ti * walkers, wt, at0, acnt);
+            const uint32_t row0 = wt * ACC_N + crank * TN;
             for (uint32_t c = 0; c < n_chunks && alive; ++c) {
                 if (cround > 0) alive = mbar_wait(cempty_bar(cslot), (cround - 1) & 1u, abort_p, err_word);
                 alive = __all_sync(0xFFFFFFFFu, alive);
@@ -847,19 +865,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             // issuers' commits to its `empty` barrier. The issuers then look at one barrier per stage.
             uint32_t slot = 0, round = 0;
             for (uint32_t ti = 0; ti < nt && alive; ++ti) {
-                const uint32_t mt = (walker + ti * walkers) / row_tiles;
+                uint32_t wt, at0, acnt;
+                tile_of(walker + ti * walkers, wt, at0, acnt);
                 for (uint32_t sg = 0; sg < n_stages && alive; ++sg) {
                     if (round > 0) alive = mbar_wait(empty_bar(slot), (round - 1) & 1u, abort_p, err_word);
                     alive = __all_sync(0xFFFFFFFFu, alive);
                     if (!alive) break;
                     if (lane == 0) {
                         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(slot)),
-                                     "r"(2u * btile_bytes)
+                                     "r"(acnt * btile_bytes)
                                      : "memory");
-                        for (uint32_t a = 0; a < 2; ++a) {
+                        for (uint32_t a = 0; a < acnt; ++a) {
                             const unsigned char* src =
                                 reinterpret_cast<const unsigned char*>(xt) +
-                                ((size_t)sg * m_pad + ((size_t)mt * 2 + a) * ACT_TILE + crank * TS_ACT_ROWS) * 128u;
+                                ((size_t)sg * m_pad + ((size_t)at0 + a) * ACT_TILE + crank * TS_ACT_ROWS) * 128u;
                             bulk_copy_g2s(bring32 + (slot * 2 + a) * btile_bytes, src, btile_bytes, full_bar(slot));
                         }
                     }
@@ -877,7 +896,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             }
         }
         for (uint32_t ti = 0; ti < nt && alive && !PAIR; ++ti) {
-            const uint32_t mt = (walker + ti * walkers) / row_tiles;
+            uint32_t wt, at0, acnt;
+            tile_of(walker + ti * walkers, wt, at0, acnt);
             // one ring entry per stage and activation tile
             for (uint32_t sa = 0; sa < n_stages * n_act && alive; ++sa) {
                 const uint32_t sg = n_act == 1 ? sa : sa >> 1, a = n_act == 1 ? 0u : sa & 1u;
@@ -889,7 +909,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                                  "r"(btile_bytes)
                                  : "memory");
                     const unsigned char* src = reinterpret_cast<const unsigned char*>(xt) +
-                                               ((size_t)sg * m_pad + ((size_t)mt * n_act + a) * ACT_TILE + crank * TS_ACT_ROWS) * 128u;
+                                               ((size_t)sg * m_pad + ((size_t)at0 + a) * ACT_TILE + crank * TS_ACT_ROWS) * 128u;
                     if (interleave) {
                         for (uint32_t q = 0; q < 4; ++q)
                             bulk_copy_g2s(bring32 + bslot * bstride + q * 4096u, src + q * 1024u, 1024u, bfull_bar(bslot));
@@ -943,6 +963,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             uint32_t slot = 0, round = 0, bslot = me, bround = 0;  // this issuer's ring entries: me, me + n_act, ...
             bool alive = true, ready = false;
             for (uint32_t i = 0; i < nt && alive; ++i) {
+                uint32_t wt, at0, acnt;
+                tile_of(walker + i * walkers, wt, at0, acnt);
+                const bool mine = me < acnt;  // a half tile: the second issuer keeps step with the ring and issues nothing
                 const uint32_t acc = n_act == 1 ? (i & 1u) : me;
                 if (n_act == 1) {
                     if (i >= 2) alive = mbar_wait(acc_empty(acc), ((i >> 1) - 1) & 1u, abort_p, err_word);
@@ -982,12 +1005,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     // complete is waited for at the top of the next stage.
                     bool r1, r2;
                     if (PAIR) {
-                        tc_mma_f16_pair(d_tmem, x_desc, w_desc, idesc, s != 0 ? 1u : 0u);
-                        tc_mma_f16_pair(d_tmem, x_desc + 2, w_desc + 2, idesc, 1u);
-                        tc_mma_f16_pair(d_tmem, x_desc + 4, w_desc + 4, idesc, 1u);
+                        if (mine) {
+                            tc_mma_f16_pair(d_tmem, x_desc, w_desc, idesc, s != 0 ? 1u : 0u);
+                            tc_mma_f16_pair(d_tmem, x_desc + 2, w_desc + 2, idesc, 1u);
+                            tc_mma_f16_pair(d_tmem, x_desc + 4, w_desc + 4, idesc, 1u);
+                        }
                         r1 = mbar_try_wait_cluster(full_bar(nslot), nround & 1u);
                         r2 = true;
-                        tc_mma_f16_pair(d_tmem, x_desc + 6, w_desc + 6, idesc, 1u);
+                        if (mine) tc_mma_f16_pair(d_tmem, x_desc + 6, w_desc + 6, idesc, 1u);
                         tc_commit_pair(empty_bar(slot));
                     } else {
                         tc_mma_f16(d_tmem, x_desc, w_desc, idesc, s != 0 ? 1u : 0u);
@@ -1029,12 +1054,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             alive = __all_sync(0xFFFFFFFFu, alive);
             if (!alive) break;
             tc_fence_after();
-            const uint32_t tile = walker + i * walkers;
-            const uint32_t mt = tile / row_tiles, n0 = (tile - mt * row_tiles) * ACC_N;
-            for (uint32_t a = 0; a < n_act; ++a) {
+            uint32_t wt, at0, acnt;
+            tile_of(walker + i * walkers, wt, at0, acnt);
+            const uint32_t n0 = wt * ACC_N;
+            for (uint32_t a = 0; a < acnt; ++a) {
                 // activation rows of this accumulator: lane j of this quarter holds row m0 + 4 j + quarter when
                 // interleaved (up to 32 rows in all), m0 + 32 quarter + j otherwise
-                const uint32_t m0 = (mt * n_act + a) * ACT_TILE + crank * TS_ACT_ROWS;
+                const uint32_t m0 = (at0 + a) * ACT_TILE + crank * TS_ACT_ROWS;
                 const uint32_t m = interleave ? 4u * (uint32_t)lane + quarter : m0 + lane_base + lane;
                 const uint32_t first = interleave ? quarter : m0 + lane_base;  // first row of this quarter
                 if (first >= M) continue;                                         // uniform over the warp
@@ -1247,7 +1273,7 @@ int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, fl
     if (rc == ZQ_OK) rc = tensor_map_2d(w->sc, (uint64_t)w->scp * SB, w->out_dim, SBOX, TN, 0, &smap);
     if (rc != ZQ_OK) return rc;
     kern<<<grid, TS_THREADS, smem, st>>>(wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, interleave, n_act, m_tiles,
-                                         m_pad, n_ring, n_bring, n_chunk_ring, err_word, ep);
+                                         m_pad, n_ring, n_bring, n_chunk_ring, (uint32_t)tiles_total, err_word, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -1290,8 +1316,13 @@ int launch_stream_pair(const zq_weight* w, const __half* xt, const float* post, 
     const uint32_t n_bring = 2u * n_ring;
     const size_t smem = (size_t)n_ring * W_STAGE + (size_t)n_bring * btile_bytes + (size_t)n_chunk_ring * CHUNK_BYTES + 1024;
     ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const uint64_t tiles_total = (uint64_t)((w->out_dim + 255u) / 256u) * m_tiles;
+    const uint64_t tiles_whole = (uint64_t)((w->out_dim + 255u) / 256u) * m_tiles;
+    if (tiles_whole > 0x7FFFFFFFu) return ZQ_ERR_LIMIT;
     const uint32_t pairs_max = (uint32_t)sm_count() / 2u;
+    // the tiles of a last round that would occupy at most half of the pairs are walked as half tiles (see the kernel)
+    const uint32_t rest = tiles_whole > pairs_max ? (uint32_t)(tiles_whole % pairs_max) : 0u;
+    const uint32_t first_half = (rest > 0 && rest <= pairs_max / 2u) ? (uint32_t)tiles_whole - rest : (uint32_t)tiles_whole;
+    const uint64_t tiles_total = tiles_whole + (tiles_whole - first_half);
     const uint32_t pairs = tiles_total < pairs_max ? (uint32_t)tiles_total : pairs_max;
     unsigned int* err_word = nullptr;
     int rc = device_error_word(&err_word);
@@ -1314,7 +1345,7 @@ int launch_stream_pair(const zq_weight* w, const __half* xt, const float* post, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     ZQ_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, 0u, n_act, m_tiles, m_pad,
-                               n_ring, n_bring, n_chunk_ring, err_word, ep));
+                               n_ring, n_bring, n_chunk_ring, first_half, err_word, ep));
     return ZQ_OK;
 }
 
