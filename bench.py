@@ -781,6 +781,46 @@ def main():
         e2e_ms = float(tmax.item())
     e2e_value = bytes_step / (e2e_ms / args.steps * 1e-3) / 1e9
 
+    # Greedy decoding over the sharded head (N > 1): the same product with only the index of the first largest
+    # logit exchanged (16 bytes per peer instead of the row). Checked against the full gathered row, then timed the
+    # same way as the main leg. Reported beside it; the headline stays the gathered row.
+    greedy = None
+    if use_dist and gather_mode == "peer" and graph is not None and hasattr(lin, "greedy"):
+        try:
+            full_row = step().clone()
+            step()  # an even number of exchanges of the two result buffers
+            idx, val = lin.greedy(x, weight=weights[0])
+            torch.cuda.synchronize()
+            want_idx = int(torch.nonzero(full_row[0] == full_row[0].max())[0, 0].item())
+            gc = [0]
+
+            def gstep():
+                w = weights[gc[0] % copies]
+                gc[0] += 1
+                lin.greedy(x, weight=w)
+            for _ in range(copies):
+                gstep()
+            torch.cuda.synchronize()
+            gg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gg):
+                for _ in range(seq_len):
+                    gstep()
+            gg.replay()
+            sync()
+            reps = max(1, args.steps // seq_len)
+            g_ms = time_region(torch, lambda: [gg.replay() for _ in range(reps)], 1, sync)
+            tg = torch.tensor([g_ms], device="cuda")
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+            greedy = {"us_per_step": round(float(tg.item()) * 1e3 / (reps * seq_len), 2), "index": int(idx.item()),
+                      "matches_first_largest_of_the_gathered_row": int(idx.item()) == want_idx,
+                      "exchange_bytes_per_peer": 16}
+            if int(idx.item()) != want_idx:
+                raise RuntimeError("arg-max exchange: index %d, gathered row says %d" % (int(idx.item()), want_idx))
+        except Exception as e:
+            greedy = {"error": repr(e)}
+            if "arg-max exchange" in repr(e):
+                raise
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         kernel_ms = ms
@@ -808,7 +848,8 @@ def main():
                     world, ", all-gather of outputs: " + gather_mode +
                     (" stores fused into the GEMV epilogue" if getattr(lin, "fused", False) else "")
                     if use_dist else ""),
-                launch=("CUDA graph replay, %d steps per recording" % seq_len) if graph is not None else "plain calls"),
+                launch=("CUDA graph replay, %d steps per recording" % seq_len) if graph is not None else "plain calls",
+                **({"greedy_argmax_exchange": greedy} if greedy is not None else {})),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          # ncu capture of the full matrix; a shard's launch is scaled by its rows
                          "traffic": int(NCU_TRAFFIC_BYTES * local_bytes / algorithmic_bytes(q, n, k)),

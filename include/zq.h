@@ -268,6 +268,25 @@ int zq_matmul_gather_tagged(const zq_weight* w, const float* d_x, const zq_epilo
                             float* d_y_odd, float* d_y_even, uint32_t world, uint32_t rank, uint32_t* d_sync,
                             zq_stream stream);
 
+/* Greedy decoding over a (row-sharded) vocabulary head: one activation row times this rank's rows, and only the
+ * index of the first largest output over ALL ranks leaves the kernel (argmax of src/models/gpt2.zig:980-990: strict
+ * `>`, so the lowest index among equal values; all values NaN or -inf: index 0). Every CTA reduces its rows, the
+ * grid's last CTA reduces the CTAs, sends this rank's (value, row) to every peer as two 64-bit words carrying the
+ * round number (16 bytes per peer instead of the row of zq_matmul_gather_tagged), polls (bounded,
+ * zq_set_wait_limit) for theirs and takes the best in rank order, which is row order. f32 activations.
+ *   w            this rank's rows [rank * out_dim, (rank + 1) * out_dim) of the head (every rank owns as many)
+ *   d_y_local    optional: this rank's out_dim outputs are stored there too
+ *   h_inbox_*    world > 1: `world` pointers (host array) to every rank's inbox of 2 * world 64-bit words, zeroed
+ *                once, odd / even rounds; world = 1: may be null
+ *   d_index      the index (every rank computes the same); d_value, optional, its value
+ *   d_sync       4096 uint32 on this GPU, zeroed once, 8-byte aligned: rounds, arrivals, one slot per CTA
+ * Returns ZQ_ERR_UNSUPPORTED when this rank has too few rows for the kernel (the caller then uses zq_matmul and
+ * zq_argmax). */
+int zq_matmul_argmax(const zq_weight* w, const float* d_x, const zq_epilogue* epilogue, float* d_y_local,
+                     unsigned long long* const* h_inbox_peers_odd, unsigned long long* const* h_inbox_peers_even,
+                     int32_t* d_index, float* d_value, uint32_t world, uint32_t rank, uint32_t* d_sync,
+                     zq_stream stream);
+
 /* --------------------------------------------------- small ops (inference) */
 
 /* rms_norm_rows (src/models/gemma3.zig:906-946; MetalContext.dispatch_rms_norm,

@@ -135,6 +135,83 @@ def test_tagged_gather_wait_runs_out_and_completes_when_the_words_are_there(zq, 
         lib.zq_set_wait_limit(0)
 
 
+def test_argmax_exchange_on_one_gpu(zq, oracle):
+    """zq_matmul_argmax. One rank: the index of the first largest output, also among equal values, with and without
+    the outputs stored. Two 'ranks' with the other rank's words written by hand: the larger value wins, rank order
+    decides between equal values, and without the other rank's words the poll ends with 'FGAT'."""
+    from zignn_b200 import _lib
+    lib = _lib.load()
+    _lib.device_error(clear=True)
+    n, k = 148 * 2 * 8 * 16, 1152
+    rng = np.random.default_rng(6)
+    raw = oracle.quantize(ggml.Q4_0, (rng.standard_normal((n, k)) * 0.02).astype(np.float32)).reshape(n, -1)
+    x = torch.from_numpy(rng.standard_normal((1, k)).astype(np.float32)).cuda()
+    y0 = zq.quant_matmul_no_grad(x, zq.QuantWeight(raw.reshape(-1), ggml.Q4_0, n, k)).reshape(-1)
+    top = int(torch.argmax(y0).item())
+    later, earlier = (top + 12345) % n, (top + n - 777) % n
+    if later < top:
+        later, earlier = earlier, later  # keep `later` above and `earlier` below the winning row
+    index = torch.zeros(1, dtype=torch.int32, device="cuda")
+    value = torch.zeros(1, device="cuda")
+    y_local = torch.zeros(n, device="cuda")
+
+    def run(qw, world=1, rank=0, inbox=None, sync=None, store=False):
+        return lib.zq_matmul_argmax(qw.handle, C.c_void_p(x.data_ptr()), None, C.c_void_p(y_local.data_ptr()) if store else None,
+                                    ptr_array(inbox[1]) if inbox else None, ptr_array(inbox[0]) if inbox else None,
+                                    C.c_void_p(index.data_ptr()), C.c_void_p(value.data_ptr()), world, rank,
+                                    C.c_void_p(sync.data_ptr()), stream())
+
+    sync = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    qw = zq.QuantWeight(raw.reshape(-1), ggml.Q4_0, n, k)
+    for store in (False, True, False):  # three rounds on the same counters
+        assert run(qw, sync=sync, store=store) == 0
+        torch.cuda.synchronize()
+        assert int(index.item()) == top and float(value.item()) == float(y0[top].item())
+        if store:
+            assert torch.equal(y_local, y0)
+    # the winning row's bytes copied to a later row: the first one still wins; to an earlier row: that one wins
+    raw2 = raw.copy()
+    raw2[later] = raw[top]
+    assert run(zq.QuantWeight(raw2.reshape(-1), ggml.Q4_0, n, k), sync=sync) == 0
+    torch.cuda.synchronize()
+    assert int(index.item()) == min(top, later)
+    raw2[earlier] = raw[top]
+    assert run(zq.QuantWeight(raw2.reshape(-1), ggml.Q4_0, n, k), sync=sync) == 0
+    torch.cuda.synchronize()
+    assert int(index.item()) == min(top, later, earlier)
+
+    # two ranks, the other one's words supplied by hand (inbox: two words per rank and round parity)
+    def words(rnd, v, row):
+        vb = int(np.float32(v).view(np.uint32))
+        return torch.tensor([(rnd << 32) | vb, (rnd << 32) | row], dtype=torch.int64, device="cuda")
+
+    best = float(y0[top].item())
+    for rank, their_v, their_row, want in ((0, best * 2, n + 5, n + 5),      # the other rank's value is larger
+                                            (0, best, n + 5, top),            # equal: the lower rank (this one) wins
+                                            (1, best, 7, 7),                  # equal, the other rank is the lower one
+                                            (1, best * 0.5, 7, n + top)):     # this rank's value is larger
+        inbox = [[torch.zeros(4, dtype=torch.int64, device="cuda") for _ in range(2)] for _ in range(2)]
+        sync2 = torch.zeros(4096, dtype=torch.int32, device="cuda")
+        other = 1 - rank
+        inbox[1][rank][2 * other: 2 * other + 2] = words(1, their_v, their_row)  # round 1 uses the odd inboxes
+        assert run(qw, world=2, rank=rank, inbox=inbox, sync=sync2) == 0
+        torch.cuda.synchronize()
+        assert int(index.item()) == want, (rank, their_v, their_row, int(index.item()))
+        sent = inbox[1][other][2 * rank: 2 * rank + 2]                           # what this rank sent
+        assert int(sent[0].item()) >> 32 == 1 and int(sent[1].item()) & 0xFFFFFFFF == rank * n + top
+        assert lib.zq_device_check(1) == 0
+    lib.zq_set_wait_limit(1024)
+    try:
+        inbox = [[torch.zeros(4, dtype=torch.int64, device="cuda") for _ in range(2)] for _ in range(2)]
+        sync2 = torch.zeros(4096, dtype=torch.int32, device="cuda")
+        assert run(qw, world=2, rank=0, inbox=inbox, sync=sync2) == 0
+        torch.cuda.synchronize()
+        assert _lib.device_error(clear=False) == FGAT
+        assert lib.zq_device_check(1) == 7
+    finally:
+        lib.zq_set_wait_limit(0)
+
+
 def test_many_rows_without_workspace_is_refused(zq, oracle):
     from zignn_b200 import _lib
     import zignn_b200.structs as S

@@ -56,6 +56,17 @@ def _worker(rank, world, port, out_dim, in_dim, m, result_path):
                         assert torch.equal(got, ref), "rank %d type %d round %d" % (rank, qt, it)
             err = (want - full).norm() / full.norm()
             assert float(err) <= 2e-6, float(err)
+            # greedy decoding: only the index of the first largest output crosses NVLink
+            if m == 1:
+                for it in range(4):
+                    xi = x + float(it)
+                    idx, val = peer.greedy(xi)
+                    idx, val = idx.clone(), val.clone()
+                    ref = peer.forward(xi).clone()  # the same kernel's rows: the same values bit for bit
+                    torch.cuda.synchronize()
+                    best = ref[0].max()
+                    assert int(idx.item()) == int(torch.nonzero(ref[0] == best)[0, 0].item()), (rank, qt, it)
+                    assert float(val.item()) == float(best.item())
         from zignn_b200 import _lib
         import ctypes as C
         v = C.c_uint()

@@ -627,6 +627,14 @@ int zq_matmul_gather_tagged(const zq_weight* w, const float* d_x, const zq_epilo
                                          rank, d_sync, as_stream(stream));
 }
 
+int zq_matmul_argmax(const zq_weight* w, const float* d_x, const zq_epilogue* epilogue, float* d_y_local,
+                     unsigned long long* const* h_inbox_peers_odd, unsigned long long* const* h_inbox_peers_even,
+                     int32_t* d_index, float* d_value, uint32_t world, uint32_t rank, uint32_t* d_sync, zq_stream stream) {
+    if (!w || !d_x || !d_index || !d_sync) return ZQ_ERR_BAD_ARG;
+    return launch_gemv_argmax_f32(w, d_x, epilogue, d_y_local, h_inbox_peers_odd, h_inbox_peers_even, d_index, d_value,
+                                  world, rank, d_sync, as_stream(stream));
+}
+
 int zq_matvec_f32(const float* d_w, const float* d_x, float* d_y, uint32_t out_dim, uint32_t in_dim,
                   zq_stream stream) {
     if (!d_w || !d_x || !d_y || out_dim == 0 || in_dim == 0) return ZQ_ERR_BAD_ARG;

@@ -655,6 +655,12 @@ __device__ __forceinline__ void lds128_keep(uint4& v, uint32_t addr, uint32_t pr
 // carry this round's number and store the floats into this rank's result row. Two inboxes alternate: a peer
 // can be at most one round ahead (it needs this rank's words of a round to finish that round), and then it
 // writes into the other one.
+//
+// Arg-max form (ARGMAX): for greedy decoding only the index of the first largest logit is needed
+// (gpt2.zig:980-990: strict `>`, so the lowest index among equals). Every lane keeps the best of its rows, a CTA
+// reduces its lanes and writes (value, row) into its slot; the grid's last CTA reduces the slots, sends this
+// rank's (value, row) as two tagged words to every peer, polls (bounded) for theirs and takes the best in rank
+// order, which is row order: 16 bytes per peer instead of the row.
 constexpr int kPeerMax = 8;
 constexpr uint32_t kPeerSpinLimit = 1u << 21;               // polls of a local flag before giving up (about a second)
 constexpr unsigned int kErrFusedGatherTimeout = 0x46474154u;  // 'FGAT'
@@ -667,6 +673,11 @@ struct PeerArgs {
     uint32_t spin_limit;         // polls of a local flag before giving up
     unsigned long long* inbox[2][kPeerMax];  // tagged form: [round parity][rank] that rank's inbox, world * per words
     uint32_t tagged, per;        // tagged form; rows owned by every rank (even)
+    // arg-max form (the ARGMAX instantiation; world = 1 too): what leaves the kernel is the index and value of the
+    // row's first largest element over all ranks. cta_best: one slot per CTA of this GPU; inbox: 2 words per rank.
+    unsigned long long* cta_best;
+    int32_t* out_index;
+    float* out_value;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
@@ -697,7 +708,15 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     return v;
 }
 
-template <int TYPE, int D, int CTAS, int W>
+// (value, row) candidates: the larger value wins, the lower row among equals
+__device__ __forceinline__ void take_better(float& v, uint32_t& r, float ov, uint32_t orow) {
+    if (ov > v || (ov == v && orow < r)) {
+        v = ov;
+        r = orow;
+    }
+}
+
+template <int TYPE, int D, int CTAS, int W, bool ARGMAX>
 __global__ void __launch_bounds__(W * 32, CTAS)
 gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc, const float* __restrict__ x,
                  float* __restrict__ y, uint32_t N, uint32_t K, uint32_t nb, uint32_t scp, uint32_t sc_off,
@@ -782,8 +801,10 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     // this one: wait for it to complete. Sharded: every CTA then reads the round before any CTA can finish
     // it (the counter moves only when all CTAs have arrived at the end of the kernel).
     pdl_wait();
-    const uint32_t round = sharded ? pa.sync[0] + 1 : 0;
-    if (sharded) y = pa.y[round & 1u][pa.rank] + pa.row_off;
+    const uint32_t round = (sharded || ARGMAX) ? pa.sync[0] + 1 : 0;
+    if (sharded && !ARGMAX) y = pa.y[round & 1u][pa.rank] + pa.row_off;
+    float best_v = -INFINITY;       // ARGMAX: the best of this lane's rows (they come in ascending order)
+    uint32_t best_r = 0xFFFFFFFFu;
 
     // ---- activations: range prescale, then the fp16 hi / lo fragment image. Every warp finds the row's
     //      largest magnitude by itself (the row is a few KB and stays in L1): no block-wide exchange ----
@@ -890,8 +911,17 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
             const uint32_t row = (uint32_t)(c_tile * rows_per_cta) + warp * 16 + g + (t == 1 ? 8u : 0u);
             if (t < 2 && row < N) {
                 const float o = apply_epilogue((t == 1 ? vb : va) * ps, ep, row, row);
-                y[row] = o;
-                if (sharded && pa.tagged) {
+                if (ARGMAX) {
+                    if (y) y[row] = o;
+                    if (o > best_v) {
+                        best_v = o;
+                        best_r = row;
+                    }
+                } else {
+                    y[row] = o;
+                }
+                if (ARGMAX) {
+                } else if (sharded && pa.tagged) {
                     const unsigned long long word = ((unsigned long long)round << 32) | __float_as_uint(o);
                     for (uint32_t p = 0; p < pa.world; ++p)
                         if (p != pa.rank)
@@ -930,7 +960,94 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
         consume(r);
     }
 
-    if (sharded && pa.tagged) {
+    if (ARGMAX) {
+        __shared__ float s_v[W];
+        __shared__ uint32_t s_r[W];
+        __shared__ int s_last;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1)
+            take_better(best_v, best_r, __shfl_xor_sync(0xFFFFFFFFu, best_v, off), __shfl_xor_sync(0xFFFFFFFFu, best_r, off));
+        if (lane == 0) {
+            s_v[warp] = best_v;
+            s_r[warp] = best_r;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float v = s_v[0];
+            uint32_t r = s_r[0];
+            for (int i = 1; i < W; ++i) take_better(v, r, s_v[i], s_r[i]);
+            pa.cta_best[blockIdx.x] = ((unsigned long long)__float_as_uint(v) << 32) | r;
+            __threadfence();
+            s_last = atomicAdd(pa.sync + 1, 1u) == gridDim.x - 1;
+        }
+        __syncthreads();
+        if (s_last) {  // every CTA's slot is written: this CTA reduces them
+            __threadfence();
+            float v = -INFINITY;
+            uint32_t r = 0xFFFFFFFFu;
+            for (uint32_t i = tid; i < gridDim.x; i += W * 32) {
+                const unsigned long long s = __ldcg(pa.cta_best + i);
+                take_better(v, r, __uint_as_float((uint32_t)(s >> 32)), (uint32_t)s);
+            }
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1)
+                take_better(v, r, __shfl_xor_sync(0xFFFFFFFFu, v, off), __shfl_xor_sync(0xFFFFFFFFu, r, off));
+            __syncthreads();  // s_v / s_r of the first reduction have been read
+            if (lane == 0) {
+                s_v[warp] = v;
+                s_r[warp] = r;
+            }
+            __syncthreads();
+            if (warp == 0) {
+                v = s_v[0], r = s_r[0];
+                for (int i = 1; i < W; ++i) take_better(v, r, s_v[i], s_r[i]);
+                r = r == 0xFFFFFFFFu ? 0u : r + pa.row_off;  // nothing compared greater than -inf: index 0, as the reference
+                if (sharded) {
+                    // lane q talks to rank q: this rank's two words to q's inbox, q's two words from this rank's inbox
+                    const uint32_t q = (uint32_t)lane;
+                    float qv = v;
+                    uint32_t qr = r;
+                    if (q < pa.world && q != pa.rank) {
+                        unsigned long long* to = pa.inbox[round & 1u][q] + 2u * pa.rank;
+                        const unsigned long long tag = (unsigned long long)round << 32;
+                        asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(to), "l"(tag | __float_as_uint(v)), "l"(tag | r)
+                                     : "memory");
+                        const unsigned long long* from = pa.inbox[round & 1u][pa.rank] + 2u * q;
+                        unsigned long long a = 0, b = 0;
+                        bool ok = false;
+                        for (uint32_t n = 0; n < pa.spin_limit; ++n) {
+                            asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(from) : "memory");
+                            if ((uint32_t)(a >> 32) == round && (uint32_t)(b >> 32) == round) {
+                                ok = true;
+                                break;
+                            }
+                        }
+                        if (!ok) atomicExch(pa.err, kErrFusedGatherTimeout);
+                        qv = __uint_as_float((uint32_t)a);
+                        qr = (uint32_t)b;
+                    }
+                    // ranks in ascending order own ascending rows: strict `>` keeps the first largest
+                    v = __shfl_sync(0xFFFFFFFFu, qv, 0);
+                    r = __shfl_sync(0xFFFFFFFFu, qr, 0);
+                    for (uint32_t p = 1; p < pa.world; ++p) {
+                        const float pv = __shfl_sync(0xFFFFFFFFu, qv, p);
+                        const uint32_t pr = __shfl_sync(0xFFFFFFFFu, qr, p);
+                        if (pv > v) {
+                            v = pv;
+                            r = pr;
+                        }
+                    }
+                }
+                if (lane == 0) {
+                    *pa.out_index = (int32_t)r;
+                    if (pa.out_value) *pa.out_value = v;
+                    pa.sync[1] = 0;
+                    __threadfence();
+                    pa.sync[0] = round;
+                }
+            }
+        }
+    } else if (sharded && pa.tagged) {
         // the other ranks' rows, two words per thread and pass
         const unsigned long long* in = pa.inbox[round & 1u][pa.rank];
         float* yfull = pa.y[round & 1u][pa.rank];
@@ -997,7 +1114,7 @@ gemv_mma1_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ sc,
     }
 }
 
-template <int TYPE, int D, int CTAS, int W>
+template <int TYPE, int D, int CTAS, int W, bool ARGMAX>
 int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
                      cudaStream_t st) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
@@ -1013,7 +1130,7 @@ int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs 
     const uint32_t ring_off = (uint32_t)smem;
     smem += (size_t)W * D * (Q8 ? 2048 : 1024);
     if (smem > (size_t)(227 * 1024) / CTAS - 1024) return ZQ_ERR_LIMIT;  // CTAS CTAs per SM must fit
-    auto kern = gemv_mma1_kernel<TYPE, D, CTAS, W>;
+    auto kern = gemv_mma1_kernel<TYPE, D, CTAS, W, ARGMAX>;
     if (smem > 48 * 1024)
         ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const uint32_t cta_tiles = (w->out_dim + W * 16 - 1) / (W * 16);
@@ -1026,24 +1143,32 @@ int launch_rows1_cfg(const zq_weight* w, const float* x, float* y, EpilogueArgs 
 
 // Whole rows per warp need enough row tiles to occupy the GPU. With fewer tiles the CTAs get smaller (so
 // that every SM still has several) and the ring deeper (fewer warps must keep as many bytes in flight).
-template <int TYPE>
+template <int TYPE, bool ARGMAX>
 int launch_rows1(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
                  cudaStream_t st) {
     const uint32_t tiles = (w->out_dim + 15) / 16, sms = (uint32_t)sm_count();
     constexpr int S = TYPE == ZQ_TYPE_Q8_0 ? 2 : 1;  // q8_0 stages are twice as large
     int rc = ZQ_ERR_LIMIT;
-    if (tiles >= sms * 2 * 8) rc = launch_rows1_cfg<TYPE, kRows1Depth, kCtasPerSm, 8>(w, x, y, ep, pa, st);
-    if (rc == ZQ_ERR_LIMIT && tiles >= sms * 2 * 4) rc = launch_rows1_cfg<TYPE, 8 / S, 4, 4>(w, x, y, ep, pa, st);
-    if (rc == ZQ_ERR_LIMIT && tiles >= sms * 4) rc = launch_rows1_cfg<TYPE, 16 / S, 4, 2>(w, x, y, ep, pa, st);
+    if (tiles >= sms * 2 * 8) rc = launch_rows1_cfg<TYPE, kRows1Depth, kCtasPerSm, 8, ARGMAX>(w, x, y, ep, pa, st);
+    if (rc == ZQ_ERR_LIMIT && tiles >= sms * 2 * 4) rc = launch_rows1_cfg<TYPE, 8 / S, 4, 4, ARGMAX>(w, x, y, ep, pa, st);
+    if (rc == ZQ_ERR_LIMIT && tiles >= sms * 4) rc = launch_rows1_cfg<TYPE, 16 / S, 4, 2, ARGMAX>(w, x, y, ep, pa, st);
     return rc;
 }
 
 int launch_rows1_any(const zq_weight* w, const float* x, float* y, EpilogueArgs ep, const PeerArgs& pa,
-                     cudaStream_t st) {
+                     cudaStream_t st, bool argmax = false) {
+    if (argmax) {
+        switch (w->type) {
+            case ZQ_TYPE_Q4_0: return launch_rows1<ZQ_TYPE_Q4_0, true>(w, x, y, ep, pa, st);
+            case ZQ_TYPE_Q4_1: return launch_rows1<ZQ_TYPE_Q4_1, true>(w, x, y, ep, pa, st);
+            case ZQ_TYPE_Q8_0: return launch_rows1<ZQ_TYPE_Q8_0, true>(w, x, y, ep, pa, st);
+            default: return ZQ_ERR_UNSUPPORTED;
+        }
+    }
     switch (w->type) {
-        case ZQ_TYPE_Q4_0: return launch_rows1<ZQ_TYPE_Q4_0>(w, x, y, ep, pa, st);
-        case ZQ_TYPE_Q4_1: return launch_rows1<ZQ_TYPE_Q4_1>(w, x, y, ep, pa, st);
-        case ZQ_TYPE_Q8_0: return launch_rows1<ZQ_TYPE_Q8_0>(w, x, y, ep, pa, st);
+        case ZQ_TYPE_Q4_0: return launch_rows1<ZQ_TYPE_Q4_0, false>(w, x, y, ep, pa, st);
+        case ZQ_TYPE_Q4_1: return launch_rows1<ZQ_TYPE_Q4_1, false>(w, x, y, ep, pa, st);
+        case ZQ_TYPE_Q8_0: return launch_rows1<ZQ_TYPE_Q8_0, false>(w, x, y, ep, pa, st);
         default: return ZQ_ERR_UNSUPPORTED;
     }
 }
@@ -1238,6 +1363,43 @@ int launch_gemv_gather_tagged_f32(const zq_weight* w, const float* x, const zq_e
 // One activation row, row-sharded weight: GEMV with the all-gather of the output slices in its epilogue.
 // ZQ_ERR_UNSUPPORTED when the shard is too small for the whole-rows kernel (the caller then runs the
 // plain GEMV followed by the separate exchange).
+// The arg-max form. world = 1: no inboxes, the index over this GPU's rows. d_sync: 2 words as above, then one
+// 64-bit slot per CTA (kArgmaxSyncWords uint32 in all).
+int launch_gemv_argmax_f32(const zq_weight* w, const float* x, const zq_epilogue* ep, float* y_local,
+                           unsigned long long* const* inbox_odd, unsigned long long* const* inbox_even,
+                           int32_t* out_index, float* out_value, uint32_t world, uint32_t rank, uint32_t* d_sync,
+                           cudaStream_t st) {
+    if (world < 1 || world > (uint32_t)kPeerMax || rank >= world || !out_index || !d_sync) return ZQ_ERR_BAD_ARG;
+    if (((uintptr_t)x & 15) != 0 || ((uintptr_t)d_sync & 7) != 0) return ZQ_ERR_BAD_ARG;
+    if ((w->out_dim + 15) / 16 < (uint32_t)sm_count() * 4) return ZQ_ERR_UNSUPPORTED;
+    if ((uint64_t)w->out_dim * world > 0xFFFFFFFEull) return ZQ_ERR_LIMIT;
+    const EpilogueArgs a = gather_epilogue(ep);
+    PeerArgs pa{};
+    if (world > 1) {
+        if (!inbox_odd || !inbox_even) return ZQ_ERR_BAD_ARG;
+        for (uint32_t r = 0; r < world; ++r) {
+            if (!inbox_odd[r] || !inbox_even[r]) return ZQ_ERR_PEER;
+            if ((((uintptr_t)inbox_odd[r] | (uintptr_t)inbox_even[r]) & 15) != 0) return ZQ_ERR_BAD_ARG;
+            pa.inbox[1][r] = inbox_odd[r];
+            pa.inbox[0][r] = inbox_even[r];
+        }
+    }
+    pa.sync = d_sync;
+    pa.cta_best = reinterpret_cast<unsigned long long*>(d_sync + 2);
+    pa.out_index = out_index;
+    pa.out_value = out_value;
+    int rc = device_error_word(&pa.err);
+    if (rc != ZQ_OK) return rc;
+    pa.world = world;
+    pa.rank = rank;
+    pa.row_off = rank * w->out_dim;
+    pa.per = w->out_dim;
+    pa.tagged = 2;
+    pa.spin_limit = wait_limit() ? wait_limit() : kPeerSpinLimit;
+    rc = launch_rows1_any(w, x, y_local, a, pa, st, true);
+    return rc == ZQ_ERR_LIMIT ? ZQ_ERR_UNSUPPORTED : rc;
+}
+
 int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue* ep, float* const* y_odd,
                            float* const* y_even, uint32_t* const* flags, uint32_t world, uint32_t rank,
                            uint32_t row_off, uint32_t* d_sync, cudaStream_t st) {

@@ -136,6 +136,10 @@ int launch_gemv_gather_tagged_f32(const zq_weight* w, const float* x, const zq_e
                                   unsigned long long* const* inbox_odd, unsigned long long* const* inbox_even,
                                   float* y_odd, float* y_even, uint32_t world, uint32_t rank, uint32_t* d_sync,
                                   cudaStream_t st);
+int launch_gemv_argmax_f32(const zq_weight* w, const float* x, const zq_epilogue* ep, float* y_local,
+                           unsigned long long* const* inbox_odd, unsigned long long* const* inbox_even,
+                           int32_t* out_index, float* out_value, uint32_t world, uint32_t rank, uint32_t* d_sync,
+                           cudaStream_t st);
 int launch_gemv_gather_f32(const zq_weight* w, const float* x, const zq_epilogue* ep, float* const* y_odd,
                            float* const* y_even, uint32_t* const* flags, uint32_t world, uint32_t rank,
                            uint32_t row_off, uint32_t* d_sync, cudaStream_t st);

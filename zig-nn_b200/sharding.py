@@ -149,6 +149,17 @@ class PeerGather:
                 self._inptrs.append((C.c_void_p * world)(*[int(p) for p in hi.buffer_ptrs]))
                 self._handles = self._handles + (hi,)
         self.tagged = self._inptrs is not None
+        # arg-max form: two words per rank and round parity, its own counters and CTA slots
+        self._amptrs = []
+        for _ in range(2):
+            t = symm_mem.empty(2 * world, dtype=torch.int64, device=device)
+            t.zero_()
+            ha = symm_mem.rendezvous(t, grp)
+            self._amptrs.append((t, (C.c_void_p * world)(*[int(p) for p in ha.buffer_ptrs])))
+            self._handles = self._handles + (ha,)
+        self.d_sync_argmax = torch.zeros(4096, dtype=torch.int32, device=device)
+        self.argmax_index = torch.zeros(1, dtype=torch.int32, device=device)
+        self.argmax_value = torch.zeros(1, dtype=torch.float32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)  # every rank's counters are zero before anybody adds to them
 
@@ -190,6 +201,21 @@ class PeerGather:
         self.round += 1
         return self.bufs[self.round & 1].view(self.world, self.m, self.per)
 
+    def fused_argmax(self, x, weight):
+        """Greedy decoding: x [1][in_dim] times this rank's weight rows; only the index of the first largest output
+        over all ranks is exchanged (16 bytes per peer). Returns (index, value) device tensors of one element, the
+        same on every rank, or None when the shard is too small for that kernel (nothing ran)."""
+        C = self._C
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rc = self._lib.load().zq_matmul_argmax(weight.handle, C.c_void_p(x.data_ptr()), None, None, self._amptrs[1][1],
+                                               self._amptrs[0][1], C.c_void_p(self.argmax_index.data_ptr()),
+                                               C.c_void_p(self.argmax_value.data_ptr()), self.world, self.rank,
+                                               C.c_void_p(self.d_sync_argmax.data_ptr()), stream)
+        if rc == 2:  # ZQ_ERR_UNSUPPORTED
+            return None
+        self._lib.check(rc, "zq_matmul_argmax")
+        return self.argmax_index, self.argmax_value
+
     def check(self, clear=True):
         """Raises when a bounded device-side wait of an exchange ran out since the last check (a peer reached
         its call more than the wait limit later, or never): the buffers returned since then hold stale data.
@@ -212,6 +238,21 @@ class PeerShardedLinear(ShardedQuantLinear):
         self.m_rows = m_rows
         self.fused = None  # None: not tried yet; True / False: the fused kernel does / does not take this shard
         self.peer = PeerGather(self.world, self.rank, m_rows, self.per, device, group=self.group)
+
+    def greedy(self, x, weight=None):
+        """Index (and value) of the first largest output of x [1][in_dim] over all ranks' rows, as one-element device
+        tensors: the exchange carries 16 bytes per peer. Falls back to forward() + argmax for shards the fused kernel
+        does not take."""
+        w = weight if weight is not None else self.weight
+        even = self.out_dim == self.world * self.per
+        if x.shape[0] == 1 and even:
+            r = self.peer.fused_argmax(x, w)
+            if r is not None:
+                return r
+        y = self.forward(x, weight=weight)
+        v, i = torch.max(y[0], dim=0)  # torch.max returns the first index among equal values on CUDA? not guaranteed:
+        i = torch.nonzero(y[0] == v)[0, 0]  # take the lowest index explicitly
+        return i.to(torch.int32).reshape(1), v.reshape(1)
 
     def forward(self, x, weight=None):
         """weight: another device copy of this rank's rows to use instead of the one built at construction."""
