@@ -515,6 +515,65 @@ def run_case(args):
         dt = time.perf_counter() - t0
         print(json.dumps({"case": args.case, "tok_s": int(n_steps) / dt, "last_token": int(toks[-1])}), flush=True)
         return
+    if args.case.startswith("shard:"):
+        # shard:<type>,<in_dim K>,<out_dim N>,<rows M>: the product with the weight's rows split over the ranks this
+        # process was started with (torchrun; one rank without it), every rank ending up with the whole [M][N]
+        # result: M = 1 by the GEMV with the exchange inside, more rows by the local product and the exchange of
+        # column slices. Time by CUDA events over --steps calls, max over ranks; `alone` is this rank's product
+        # without the exchange.
+        import torch.distributed as dist
+        from zignn_b200 import sharding
+        qname, k, n, m = args.case[6:].split(",")
+        k, n, m = int(k), int(n), int(m)
+        rank, local_rank, world = dist_env()
+        torch.cuda.set_device(local_rank)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        raw = make_weight_bytes(qname, n, k, 42, "cuda")
+        x = torch.randn(m, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(43))
+        qt = ggml.TYPE_IDS[qname]
+        if world > 1:
+            lin = sharding.cuda_sharded_linear(raw, qt, n, k, zq.ACT_F32, gather="peer", m_rows=m)
+            w_local, rows = lin.weight, lin.rows
+            call = lambda: lin.forward(x)
+        else:
+            w_local, rows = zq.QuantWeight(raw, qt, n, k), n
+            y = torch.empty(m, n, device="cuda")
+            wsb = torch.empty(max(_lib_ws(zq, w_local, m, zq.ACT_F32), 256), dtype=torch.uint8, device="cuda")
+            call = lambda: zq.quant_matmul_no_grad(x, w_local, zq.ACT_F32, out=y, workspace=wsb)
+        del raw
+        y_alone = torch.empty(m, rows, device="cuda")
+        ws_alone = torch.empty(max(_lib_ws(zq, w_local, m, zq.ACT_F32), 256), dtype=torch.uint8, device="cuda")
+        alone = lambda: zq.quant_matmul_no_grad(x, w_local, zq.ACT_F32, out=y_alone, workspace=ws_alone)
+
+        def sync():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def timed(fn, steps):
+            for _ in range(4):
+                fn()
+            ms = time_region(torch, fn, steps, sync)
+            if world > 1:
+                t = torch.tensor([ms], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms / steps * 1e3
+        steps = max(2, args.steps - args.steps % 2)
+        us = timed(call, steps)
+        us_alone = timed(alone, steps)
+        if world > 1:
+            from zignn_b200 import _lib as zlib
+            zlib.check(zlib.load().zq_device_check(1), "peer exchange")
+        if rank == 0:
+            print(json.dumps({"case": args.case, "n_gpus": world, "us_per_step": round(us, 1), "us_product_alone": round(us_alone, 1),
+                              "exchange_share": round(max(0.0, 1.0 - us_alone / us), 3),
+                              "tflops_whole_job": round(2.0 * m * n * k / us / 1e6, 1),
+                              "gbs_whole_job": round(algorithmic_bytes(qname, n, k, m) / us / 1e3, 1)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.case.startswith("trans:"):
         # trans:<type>,<in_dim K>,<out_dim N>,<rows M>: grad_x[M][K] = grad_out[M][N] . W[N][K]
         qname, k, n, m = args.case[6:].split(",")

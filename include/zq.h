@@ -238,6 +238,16 @@ int zq_peer_gather_step(float* const* h_y_peers_odd, float* const* h_y_peers_eve
                         uint32_t* const* h_flag_peers, uint32_t world, uint32_t rank, size_t slice_offset,
                         size_t slice_len, uint32_t* d_round, zq_stream stream);
 
+/* Several activation rows: this rank owns the columns [col_offset, col_offset + cols) of the row-major
+ * [m_rows][n_total] result and holds them as a contiguous [m_rows][cols] block `d_local`. The block is stored to
+ * that place of every rank's result buffer (this rank's own included), so each rank ends up with the row-major
+ * result itself; counters and rounds as for zq_peer_gather_step (these counters count 32 arrivals per round:
+ * give this entry point flags of its own). Result buffers: [m_rows][n_total] floats, odd / even rounds. */
+int zq_peer_gather_cols_step(float* const* h_y_peers_odd, float* const* h_y_peers_even,
+                             uint32_t* const* h_flag_peers, uint32_t world, uint32_t rank, const float* d_local,
+                             uint32_t m_rows, size_t n_total, size_t col_offset, uint32_t cols, uint32_t* d_round,
+                             zq_stream stream);
+
 /* One activation row times a row-sharded weight with the exchange inside the GEMV kernel: every output
  * row is stored into this rank's result buffer and, in the same epilogue, into every peer's (plain peer
  * stores), so the all-gather overlaps the weight stream; the grid's last CTA then publishes a counter on

@@ -135,6 +135,40 @@ def test_tagged_gather_wait_runs_out_and_completes_when_the_words_are_there(zq, 
         lib.zq_set_wait_limit(0)
 
 
+def test_column_gather_on_one_gpu(zq):
+    """zq_peer_gather_cols_step with both 'ranks' on this GPU: rank 1's [m][cols] block lands in columns
+    [cols, 2 cols) of both row-major result buffers; nobody plays rank 0, so the wait ends with 'GATH'."""
+    from zignn_b200 import _lib
+    lib = _lib.load()
+    _lib.device_error(clear=True)
+    m, cols = 37, 200
+    local = torch.arange(m * cols, device="cuda", dtype=torch.float32).reshape(m, cols)
+    odd = [torch.zeros(m, 2 * cols, device="cuda") for _ in range(2)]
+    even = [torch.zeros(m, 2 * cols, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
+    rnd = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.zq_set_wait_limit(1024)
+    try:
+        rc = lib.zq_peer_gather_cols_step(ptr_array(odd), ptr_array(even), ptr_array(flags), 2, 1, C.c_void_p(local.data_ptr()),
+                                          m, 2 * cols, cols, cols, C.c_void_p(rnd.data_ptr()), stream())
+        assert rc == 0
+        torch.cuda.synchronize()
+        for buf in odd:  # round 1: the odd buffers of both ranks
+            assert torch.equal(buf[:, cols:], local) and torch.all(buf[:, :cols] == 0)
+        assert int(flags[0][1].item()) == 32     # published on the other rank: 32 CTAs per destination
+        assert _lib.device_error(clear=False) == GATH
+        assert lib.zq_device_check(1) == 7
+        flags[1][0] = 64                          # the other rank's arrivals of round 2, by hand
+        rc = lib.zq_peer_gather_cols_step(ptr_array(odd), ptr_array(even), ptr_array(flags), 2, 1, C.c_void_p(local.data_ptr()),
+                                          m, 2 * cols, cols, cols, C.c_void_p(rnd.data_ptr()), stream())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert lib.zq_device_check(1) == 0
+        assert torch.equal(even[0][:, cols:], local)
+    finally:
+        lib.zq_set_wait_limit(0)
+
+
 def test_argmax_exchange_on_one_gpu(zq, oracle):
     """zq_matmul_argmax. One rank: the index of the first largest output, also among equal values, with and without
     the outputs stored. Two 'ranks' with the other rank's words written by hand: the larger value wins, rank order

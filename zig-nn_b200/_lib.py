@@ -48,6 +48,7 @@ SIGNATURES = {
     "zq_argmax": (i, [vp, u32, vp, vp]),
     "zq_peer_gather": (i, [vp, vp, u32, u32, C.c_size_t, C.c_size_t, u32, vp]),
     "zq_peer_gather_step": (i, [vp, vp, vp, u32, u32, C.c_size_t, C.c_size_t, vp, vp]),
+    "zq_peer_gather_cols_step": (i, [vp, vp, vp, u32, u32, vp, u32, C.c_size_t, C.c_size_t, u32, vp, vp]),
     "zq_matmul_gather": (i, [vp, vp, vp, vp, vp, vp, u32, u32, u32, vp, vp]),
     "zq_matmul_gather_tagged": (i, [vp, vp, vp, vp, vp, vp, vp, u32, u32, vp, vp]),
     "zq_matmul_argmax": (i, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, vp, vp]),

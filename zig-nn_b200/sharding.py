@@ -149,6 +149,14 @@ class PeerGather:
                 self._inptrs.append((C.c_void_p * world)(*[int(p) for p in hi.buffer_ptrs]))
                 self._handles = self._handles + (hi,)
         self.tagged = self._inptrs is not None
+        # several activation rows: column slices written straight into the row-major result (own counters)
+        self.cflags = symm_mem.empty(world, dtype=torch.int32, device=device)
+        self.cflags.zero_()
+        hcf = symm_mem.rendezvous(self.cflags, grp)
+        self._cfptrs = (C.c_void_p * world)(*[int(p) for p in hcf.buffer_ptrs])
+        self._handles = self._handles + (hcf,)
+        self.d_round_cols = torch.zeros(1, dtype=torch.int32, device=device)
+        self.round_cols = 0
         # arg-max form: two words per rank and round parity, its own counters and CTA slots
         self._amptrs = []
         for _ in range(2):
@@ -180,6 +188,19 @@ class PeerGather:
                                                   self.rank * n, n, C.c_void_p(self.d_round.data_ptr()), stream)
         self._lib.check(rc, "zq_peer_gather_step")
         return self.bufs[which].view(self.world, self.m, self.per)
+
+    def gather_cols(self, local):
+        """local: this rank's [m][per] block of columns. Stores it into place in every rank's row-major
+        [m][world * per] result buffer and waits for the other ranks' blocks; returns that buffer."""
+        C = self._C
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        n_total = self.world * self.per
+        rc = self._lib.load().zq_peer_gather_cols_step(self._yptrs[1], self._yptrs[0], self._cfptrs, self.world, self.rank,
+                                                       C.c_void_p(local.data_ptr()), self.m, n_total, self.rank * self.per,
+                                                       self.per, C.c_void_p(self.d_round_cols.data_ptr()), stream)
+        self._lib.check(rc, "zq_peer_gather_cols_step")
+        self.round_cols += 1
+        return self.bufs[self.round_cols & 1].view(self.m, n_total)
 
     def fused_matmul(self, x, weight):
         """x [1][in_dim] times this rank's weight rows with the exchange inside the GEMV kernel.
@@ -237,6 +258,8 @@ class PeerShardedLinear(ShardedQuantLinear):
         super().__init__(*args, **kw)
         self.m_rows = m_rows
         self.fused = None  # None: not tried yet; True / False: the fused kernel does / does not take this shard
+        self.cols_exchange = True  # several activation rows: column slices straight into the row-major result
+        self._local = None
         self.peer = PeerGather(self.world, self.rank, m_rows, self.per, device, group=self.group)
 
     def greedy(self, x, weight=None):
@@ -266,6 +289,17 @@ class PeerShardedLinear(ShardedQuantLinear):
             self.fused = g is not None
             if g is not None:
                 return g.reshape(1, self.world * self.per)[:, :self.out_dim]
+        if m > 1 and self.cols_exchange:
+            # the block of columns goes straight into the row-major result on every rank: nothing to permute
+            if self._local is None:
+                self._local = torch.zeros(m, self.per, dtype=torch.float32, device=x.device)
+            if self.rows == self.per:
+                self.compute(x, w, self._local)
+            elif self.rows:
+                tmp = torch.empty(m, self.rows, dtype=torch.float32, device=x.device)
+                self.compute(x, w, tmp)
+                self._local[:, :self.rows] = tmp
+            return self.peer.gather_cols(self._local)[:, :self.out_dim]
         buf = self.peer.next_buffer()
         if self.rows:
             if self.rows == self.per:
