@@ -108,6 +108,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
+// One look, without waiting (try_wait may suspend the thread for a while when the phase is not complete).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
 // Bounded wait. Returns false after kSpinLimit polls or when another thread has already given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned int* err_word) {
@@ -598,6 +610,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
         : "memory");
     return ok;
 }
+__device__ __forceinline__ uint32_t mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   unsigned int* err_word) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
@@ -1010,16 +1033,16 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                             tc_mma_f16_pair(d_tmem, x_desc + 2, w_desc + 2, idesc, 1u);
                             tc_mma_f16_pair(d_tmem, x_desc + 4, w_desc + 4, idesc, 1u);
                         }
-                        r1 = mbar_try_wait_cluster(full_bar(nslot), nround & 1u);
+                        r1 = mbar_test_wait_cluster(full_bar(nslot), nround & 1u);
                         r2 = true;
                         if (mine) tc_mma_f16_pair(d_tmem, x_desc + 6, w_desc + 6, idesc, 1u);
                         tc_commit_pair(empty_bar(slot));
                     } else {
                         tc_mma_f16(d_tmem, x_desc, w_desc, idesc, s != 0 ? 1u : 0u);
                         tc_mma_f16(d_tmem, x_desc + 2, w_desc + 2, idesc, 1u);
-                        r1 = mbar_try_wait(full_bar(nslot), nround & 1u);
+                        r1 = mbar_test_wait(full_bar(nslot), nround & 1u);
                         tc_mma_f16(d_tmem, x_desc + 4, w_desc + 4, idesc, 1u);
-                        r2 = mbar_try_wait(bfull_bar(nbslot), nbround & 1u);
+                        r2 = mbar_test_wait(bfull_bar(nbslot), nbround & 1u);
                         tc_mma_f16(d_tmem, x_desc + 6, w_desc + 6, idesc, 1u);
                         tc_commit(bempty_bar(bslot));
                         tc_commit(empty_bar(slot));
