@@ -795,9 +795,19 @@ def main():
         zlib.check(zlib.load().zq_copy_f32(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), count,
                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)), "zq_copy_f32")
 
+    direct_host = [False]
+
     def e2e_device_part():
-        # pinned x -> device by a copy kernel, the sharded product with its exchange, the full row -> pinned y
+        # pinned x -> device by a copy kernel, the sharded product with its exchange, the full row -> pinned y: the
+        # fused kernel writes this rank's rows and the rows it unpacks from its inbox straight into the pinned
+        # buffer (as the one-GPU host call does); the other routes copy the gathered row out afterwards
         copy_f32(x.data_ptr(), hx.data_ptr(), k)
+        if gather_mode == "peer" and getattr(lin, "fused", False) and lin.peer.tagged and hy.numel() == lin.world * lin.per:
+            w = weights[counter[0] % copies]
+            counter[0] += 1
+            lin.forward(x, weight=w, out=hy)
+            direct_host[0] = True
+            return
         y = step()
         copy_f32(hy.data_ptr(), y.data_ptr(), hy.numel())
 
@@ -839,6 +849,16 @@ def main():
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         e2e_ms = float(tmax.item())
     e2e_value = bytes_step / (e2e_ms / args.steps * 1e-3) / 1e9
+    if use_dist and parity is not None:
+        # what the end-to-end leg left in the pinned buffer is the gathered row
+        torch.cuda.synchronize()
+        ref_row = step().clone()
+        step()  # an even number of exchanges of the two result buffers
+        torch.cuda.synchronize()
+        parity["e2e_host_row_equals_gathered_row"] = bool(torch.equal(hy.reshape(-1)[:n], ref_row.reshape(-1)[:n].cpu()))
+        parity["e2e_row_written_to_pinned_memory_by_the_kernel"] = bool(direct_host[0])
+        if not parity["e2e_host_row_equals_gathered_row"]:
+            parity["ok"] = False
 
     # Greedy decoding over the sharded head (N > 1): the same product with only the index of the first largest
     # logit exchanged (16 bytes per peer instead of the row). Checked against the full gathered row, then timed the

@@ -202,16 +202,24 @@ class PeerGather:
         self.round_cols += 1
         return self.bufs[self.round_cols & 1].view(self.m, n_total)
 
-    def fused_matmul(self, x, weight):
+    def fused_matmul(self, x, weight, out=None):
         """x [1][in_dim] times this rank's weight rows with the exchange inside the GEMV kernel.
-        Returns the gathered buffer, or None when the shard is too small for that kernel (nothing ran)."""
+        Returns the gathered buffer, or None when the shard is too small for that kernel (nothing ran).
+        out (tagged form only): a buffer of world * per floats that receives the row instead of the library's own,
+        e.g. page-locked host memory, which the kernel then writes directly (peers never write result rows in
+        this form, only inboxes, so one buffer serves every round)."""
         C = self._C
         stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         if self.tagged:  # words that carry their round number: nothing follows the peer stores
+            y_odd = out.data_ptr() if out is not None else self.bufs[1].data_ptr()
+            y_even = out.data_ptr() if out is not None else self.bufs[0].data_ptr()
             rc = self._lib.load().zq_matmul_gather_tagged(weight.handle, C.c_void_p(x.data_ptr()), None, self._inptrs[1],
-                                                          self._inptrs[0], C.c_void_p(self.bufs[1].data_ptr()),
-                                                          C.c_void_p(self.bufs[0].data_ptr()), self.world, self.rank,
+                                                          self._inptrs[0], C.c_void_p(y_odd), C.c_void_p(y_even),
+                                                          self.world, self.rank,
                                                           C.c_void_p(self.d_sync.data_ptr()), stream)
+            if rc == 0 and out is not None:
+                self.round += 1
+                return out.view(self.world, self.m, self.per)
         else:
             rc = self._lib.load().zq_matmul_gather(weight.handle, C.c_void_p(x.data_ptr()), None, self._yptrs[1],
                                                    self._yptrs[0], self._ffptrs, self.world, self.rank,
@@ -277,15 +285,18 @@ class PeerShardedLinear(ShardedQuantLinear):
         i = torch.nonzero(y[0] == v)[0, 0]  # take the lowest index explicitly
         return i.to(torch.int32).reshape(1), v.reshape(1)
 
-    def forward(self, x, weight=None):
-        """weight: another device copy of this rank's rows to use instead of the one built at construction."""
+    def forward(self, x, weight=None, out=None):
+        """weight: another device copy of this rank's rows to use instead of the one built at construction.
+        out: one activation row through the fused kernel in its tagged form only: the buffer (device or page-locked
+        host memory, out_dim floats) that receives the row; ignored by the other routes."""
         m = x.shape[0]
         if m != self.m_rows:
             raise ValueError("built for %d activation rows, got %d" % (self.m_rows, m))
         w = weight if weight is not None else self.weight
         even = self.out_dim == self.world * self.per  # every rank owns `per` rows: all ranks take the same branch
         if m == 1 and self.fused is not False and even:
-            g = self.peer.fused_matmul(x, w)
+            direct = out if (out is not None and self.peer.tagged and out.numel() == self.world * self.per) else None
+            g = self.peer.fused_matmul(x, w, out=direct)
             self.fused = g is not None
             if g is not None:
                 return g.reshape(1, self.world * self.per)[:, :self.out_dim]
