@@ -56,6 +56,18 @@ def _worker(rank, world, port, out_dim, in_dim, m, result_path):
                         assert torch.equal(got, ref), "rank %d type %d round %d" % (rank, qt, it)
             err = (want - full).norm() / full.norm()
             assert float(err) <= 2e-6, float(err)
+            # the tagged exchange writing the gathered row straight into page-locked host memory
+            if m == 1:
+                tagged = sharding.cuda_sharded_linear(raw, qt, out_dim, in_dim, gather="peer", m_rows=1)
+                ref = tagged.forward(x).clone()
+                if tagged.fused and tagged.peer.tagged:
+                    host_row = torch.zeros(tagged.world * tagged.per, dtype=torch.float32).pin_memory()
+                    for it in range(3):
+                        tagged.forward(x, out=host_row)
+                        torch.cuda.synchronize()
+                        assert torch.equal(host_row[:out_dim], ref[0].cpu()), (rank, qt, it)
+                        host_row.zero_()
+                    assert torch.equal(tagged.forward(x), ref)  # the library's own buffers still take their turns
             # greedy decoding: only the index of the first largest output crosses NVLink
             if m == 1:
                 for it in range(4):
