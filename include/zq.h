@@ -60,6 +60,11 @@ int zq_device_check(int clear);
  * zq_matmul_gather); 0 restores the kernels' own defaults (about a second). Process-wide; takes effect with the
  * next launch. Lets a host fail fast, and lets a test make a wait run out without hanging anything. */
 int zq_set_wait_limit(unsigned int polls);
+/* The many-row tensor-core GEMM runs on pairs of CTAs (thread-block clusters of two, tcgen05 cta_group::2) where
+ * that is the faster form. enabled = 0 keeps it on single CTAs (about 0.8 of the speed), as the library does by
+ * itself when a cluster launch is refused; for GPUs partitioned so that pairs of SMs cannot be scheduled, and for
+ * tests of that route. Process-wide; default 1. */
+int zq_set_cluster_launch(int enabled);
 
 /* GGML tensor type ids — src/gguf/dequant.zig:9-20. */
 typedef enum zq_type {

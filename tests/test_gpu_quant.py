@@ -589,6 +589,31 @@ def test_streaming_gemm_wide_many_activation_tiles_and_epilogue(zq, qt, block_by
     assert _lib.device_error() == 0
 
 
+def test_many_row_gemm_without_cluster_launches(zq):
+    """zq_set_cluster_launch(0): a shape that runs on pairs of CTAs takes the single-CTA form instead, on the activation
+    image as it is laid out for the pairs; the same result within the path's tolerance, and the pairs are back
+    afterwards."""
+    from zignn_b200 import _lib
+    lib = _lib.load()
+    k, n, m = 1024, 3880, 2148
+    g = torch.Generator(device="cuda").manual_seed(91)
+    raw_d = ggml.quantize(ggml.Q4_0, torch.randn(n, k, generator=g, device="cuda") * 0.05)
+    qw = zq.QuantWeight(raw_d, ggml.Q4_0, n, k)
+    x = torch.randn(m, k, generator=g, device="cuda")
+    base = x @ qw.dequantize().t()
+    pairs = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32)
+    assert lib.zq_set_cluster_launch(0) == 0
+    try:
+        single = zq.quant_matmul_no_grad(x, qw, zq.ACT_F32)
+    finally:
+        lib.zq_set_cluster_launch(1)
+    for got in (pairs, single):
+        assert torch.allclose(got, base, rtol=0, atol=4e-3 * float(base.abs().max()))
+    # both forms multiply the same fp16 operands and add in the same K order
+    assert rel_l2(single.cpu().numpy(), pairs.cpu().numpy()) <= 1e-6
+    assert _lib.device_error() == 0
+
+
 @pytest.mark.parametrize("qt,block_bytes", STREAM_TYPES)
 @pytest.mark.parametrize("m", [129, 256, 300, 520])
 def test_streaming_gemm_wide_sampled_rows(zq, oracle, qt, block_bytes, m):

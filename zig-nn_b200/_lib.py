@@ -51,6 +51,7 @@ SIGNATURES = {
     "zq_peer_gather_cols_step": (i, [vp, vp, vp, u32, u32, vp, u32, C.c_size_t, C.c_size_t, u32, vp, vp]),
     "zq_matmul_gather": (i, [vp, vp, vp, vp, vp, vp, u32, u32, u32, vp, vp]),
     "zq_matmul_gather_tagged": (i, [vp, vp, vp, vp, vp, vp, vp, u32, u32, vp, vp]),
+    "zq_set_cluster_launch": (i, [C.c_int]),
     "zq_matmul_argmax": (i, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, vp, vp]),
     "zq_rms_norm": (i, [vp, vp, vp, u32, u32, f, vp]),
     "zq_rms_norm_residual": (i, [vp, vp, vp, u32, u32, f, vp]),

@@ -1233,13 +1233,14 @@ inline bool stream_wide_takes(const zq_weight* w, uint32_t m_rows) {
 
 template <int TYPE, int TN, int CROW>
 int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
-                     cudaStream_t st) {
+                     cudaStream_t st, uint32_t m_pad_given = 0) {
     auto kern = gemm_stream_kernel<TYPE, TN, CROW, false>;
     const bool wide = M > kStreamMaxRows;              // two activation tiles of 128 rows per CTA tile
     const uint32_t n_act = wide ? 2u : 1u;
     const uint32_t act_rows = wide ? TS_ACT_ROWS : stream_act_rows(M);  // rows of a ring entry
     const uint32_t m_tiles = wide ? (M + 255u) / 256u : 1u;
-    const uint32_t m_pad = wide ? m_tiles * 256u : act_rows;
+    // rows per K segment of the activation image: as this form pads them, or as the caller has laid the image out
+    const uint32_t m_pad = (wide && m_pad_given >= m_tiles * 256u) ? m_pad_given : wide ? m_tiles * 256u : act_rows;
     const uint32_t btile_bytes = act_rows * 128u;
     constexpr uint32_t SBOX = StreamScales<TYPE, CROW>::kBox;
     constexpr uint32_t W_STAGE = TN * 128u, CHUNK_BYTES = TN * CROW + TN * SBOX;
@@ -1303,6 +1304,7 @@ int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, fl
 
 // A pair of CTAs per tile of 256 weight rows x 512 activation rows (see the kernel). 74 pairs walk the tiles.
 constexpr uint32_t kPairActRows = 512;
+int g_cluster_launch = 1;  // zq_set_cluster_launch
 // Measured against the single-CTA form with two activation tiles and the large-batch kernel (TFLOP/s, q4_0 unless
 // noted): 4096 -> 14336 at 512 / 1024 / 2048 / 4096 rows 742 / 868 / 943 / 1081 against 606 / 713 / 776 / 899 and
 // 562 / 638 / 707 / 824 (q8_0 at 4096 rows: 1021 against 864 and 679); 14336 -> 4096 at 2048 / 4096 rows 876 / 928
@@ -1375,7 +1377,16 @@ int launch_stream_pair(const zq_weight* w, const __half* xt, const float* post, 
 template <int TYPE>
 int launch_stream(const zq_weight* w, const __half* xt, const float* post, float* y, uint32_t M, TcEpilogue ep,
                   cudaStream_t st) {
-    if (stream_pair_takes(w, M)) return launch_stream_pair<TYPE>(w, xt, post, y, M, ep, st);
+    if (stream_pair_takes(w, M)) {
+        const int rc = g_cluster_launch ? launch_stream_pair<TYPE>(w, xt, post, y, M, ep, st) : ZQ_ERR_CUDA;
+        if (rc != ZQ_ERR_CUDA) return rc;
+        // The launch of the pairs was refused (nothing ran; a partitioned GPU may not schedule clusters) or is
+        // switched off: the single-CTA form takes the call, on the activation image as it is laid out for the
+        // pairs (rows padded to 512s).
+        if (g_cluster_launch) cudaGetLastError();
+        return launch_stream_tn<TYPE, 256, TYPE == ZQ_TYPE_Q8_0 ? 128 : 64>(w, xt, post, y, M, ep, st,
+                                                                             ((M + kPairActRows - 1) / kPairActRows) * kPairActRows);
+    }
     // More than 128 activation rows: 64-byte chunks for the 4-bit types (room for seven activation tiles instead
     // of four). Otherwise 256-row tiles do twice the work per tensor-core instruction; 128-row tiles when those
     // would leave SMs idle.
@@ -1486,3 +1497,8 @@ int launch_gemm_tc(const zq_weight* w, const float* x, float* y, uint32_t m_rows
 }
 
 }  // namespace zq
+
+extern "C" int zq_set_cluster_launch(int enabled) {
+    zq::g_cluster_launch = enabled ? 1 : 0;
+    return ZQ_OK;
+}
