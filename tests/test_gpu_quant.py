@@ -491,6 +491,41 @@ def test_matmul_transposed_at_full_shapes_sampled_columns(zq, oracle, out_dim, i
     assert err <= REL_L2_TRANS, err
 
 
+@pytest.mark.parametrize("qt", [ggml.Q4_0, ggml.Q4_1, ggml.Q8_0])
+def test_matmul_transposed_many_rows_on_pairs_of_ctas(zq, oracle, qt):
+    """Many rows on a matrix of 1024 weight rows and more: W^T is laid out as fp16 operand tiles and the product runs
+    on the tcgen05 kernel of the forward GEMM (13 ragged tiles of output columns x 5 ragged tiles of rows = 65 tiles
+    for the 74 pairs of CTAs). Sampled rows against the CPU statement; accumulation adds to grad_x exactly; with
+    cluster launches switched off the earlier kernel gives the same within the tolerance."""
+    from zignn_b200 import _lib
+    out_dim, in_dim, m = 1024, 3104, 2100
+    g = torch.Generator(device="cuda").manual_seed(int(qt) + 5)
+    raw_d = ggml.quantize(qt, torch.randn(out_dim, in_dim, generator=g, device="cuda") * 0.02)
+    qw = zq.QuantWeight(raw_d, qt, out_dim, in_dim)
+    go = torch.randn(m, out_dim, generator=g, device="cuda") * 1e-3
+    go[3] = 0.0
+    got = zq.quant_matmul_transposed(go, qw)
+    rows = np.unique(np.concatenate([[0, 1, 3, 255, 256, 511, 512, m - 1], np.random.default_rng(4).choice(m, size=24, replace=False)]))
+    sel = torch.from_numpy(rows).cuda()
+    want = oracle.matmul_transposed(qt, raw_d.cpu().numpy(), go[sel].cpu().numpy(), out_dim, in_dim, n_threads=16)
+    err = rel_l2(got[sel].cpu().numpy(), want)
+    assert err <= REL_L2_TRANS, err
+    assert bool((got[3] == 0).all())
+    full = go @ qw.dequantize()
+    assert torch.allclose(got, full, rtol=0, atol=4e-3 * float(full.abs().max()))
+    base = torch.randn(m, in_dim, generator=g, device="cuda") * 1e-3
+    acc = zq.quant_matmul_transposed(go, qw, grad_x=base.clone(), accumulate=True)
+    assert torch.equal(acc, base + got)
+    lib = _lib.load()
+    lib.zq_set_cluster_launch(0)
+    try:
+        earlier = zq.quant_matmul_transposed(go, qw)
+    finally:
+        lib.zq_set_cluster_launch(1)
+    assert rel_l2(earlier.cpu().numpy(), got.cpu().numpy()) <= 1e-5  # the same fp16 operands, another order of the sums
+    assert _lib.device_error() == 0
+
+
 # ---- the weight-streaming tensor-core form (17-128 activation rows, matrices of 12 288 rows and more) ----
 
 

@@ -678,7 +678,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                    const __half* __restrict__ xt, const float* __restrict__ post, float* __restrict__ y, uint32_t N,
                    uint32_t M, uint32_t nbp, uint32_t act_rows, uint32_t interleave, uint32_t n_act, uint32_t m_tiles,
                    uint32_t m_pad, uint32_t n_ring, uint32_t n_bring, uint32_t n_chunk_ring, uint32_t first_half,
-                   unsigned int* err_word, TcEpilogue ep) {
+                   const __half* __restrict__ wimg, uint32_t wimg_rows, unsigned int* err_word, TcEpilogue ep) {
     constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
     constexpr uint32_t QB = Q8 ? 32 : 16;          // packed bytes per block
     constexpr uint32_t QUADB = 4 * QB;             // packed bytes per quad
@@ -755,7 +755,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         for (uint32_t s = 0; s < n_ring; ++s) {
             // one arrival per converting warp; a pair: the stage's activation tiles are counted on the same barrier
             // (the copy warp's arrival with their bytes), and the leader's also counts the other CTA's relay
-            mbar_init(full_bar(s), TS_CONVERT_WARPS + (PAIR ? 1 : 0) + ((PAIR && crank == 0) ? 1 : 0));
+            // (weights that arrive as fp16 tiles, `wimg`: no converting warps, the copy warp's arrival counts them too)
+            mbar_init(full_bar(s), (wimg ? 0 : TS_CONVERT_WARPS) + (PAIR ? 1 : 0) + ((PAIR && crank == 0) ? 1 : 0));
             mbar_init(empty_bar(s), n_act);            // one commit per issuer
         }
         for (uint32_t s = 0; s < n_bring; ++s) {
@@ -802,7 +803,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         uint32_t slot = 0, round = 0;      // stage ring
         uint32_t cslot = 0, cround = 0;    // chunk ring
         bool alive = true;
-        for (uint32_t ti = 0; ti < nt && alive; ++ti) {
+        for (uint32_t ti = 0; ti < (wimg ? 0u : nt) && alive; ++ti) {
             for (uint32_t c = 0; c < n_chunks && alive; ++c) {
                 alive = mbar_wait(cfull_bar(cslot), cround & 1u, abort_p, err_word);
                 if (!alive) break;
@@ -846,7 +847,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         // ================= copy warp: packed quants and scales =================
         uint32_t cslot = 0, cround = 0;
         bool alive = true;
-        for (uint32_t ti = 0; ti < nt && alive; ++ti) {
+        for (uint32_t ti = 0; ti < (wimg ? 0u : nt) && alive; ++ti) {
             uint32_t wt, at0, acnt;
             tile_of(walker + ti * walkers, wt, at0, acnt);
             const uint32_t row0 = wt * ACC_N + crank * TN;
@@ -896,8 +897,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                     if (!alive) break;
                     if (lane == 0) {
                         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(slot)),
-                                     "r"(acnt * btile_bytes)
+                                     "r"(acnt * btile_bytes + (wimg ? W_STAGE : 0u))
                                      : "memory");
+                        if (wimg) {
+                            // the stage's weight tile, already fp16 and in the operand's layout: this CTA's 128 rows
+                            const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(wimg) +
+                                                        ((size_t)sg * wimg_rows + (size_t)wt * ACC_N + crank * TN) * 128u;
+                            bulk_copy_g2s(smem32 + slot * W_STAGE, wsrc, W_STAGE, full_bar(slot));
+                        }
                         for (uint32_t a = 0; a < acnt; ++a) {
                             const unsigned char* src =
                                 reinterpret_cast<const unsigned char*>(xt) +
@@ -1297,7 +1304,7 @@ int launch_stream_tn(const zq_weight* w, const __half* xt, const float* post, fl
     if (rc == ZQ_OK) rc = tensor_map_2d(w->sc, (uint64_t)w->scp * SB, w->out_dim, SBOX, TN, 0, &smap);
     if (rc != ZQ_OK) return rc;
     kern<<<grid, TS_THREADS, smem, st>>>(wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, interleave, n_act, m_tiles,
-                                         m_pad, n_ring, n_bring, n_chunk_ring, (uint32_t)tiles_total, err_word, ep);
+                                         m_pad, n_ring, n_bring, n_chunk_ring, (uint32_t)tiles_total, nullptr, 0u, err_word, ep);
     ZQ_LAUNCH_CHECK();
     return ZQ_OK;
 }
@@ -1370,7 +1377,7 @@ int launch_stream_pair(const zq_weight* w, const __half* xt, const float* post, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     ZQ_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, smap, xt, post, y, w->out_dim, M, w->nbp, act_rows, 0u, n_act, m_tiles, m_pad,
-                               n_ring, n_bring, n_chunk_ring, first_half, err_word, ep));
+                               n_ring, n_bring, n_chunk_ring, first_half, static_cast<const __half*>(nullptr), 0u, err_word, ep));
     return ZQ_OK;
 }
 
@@ -1442,9 +1449,176 @@ int launch_tc(const zq_weight* w, const __half* xt, const float* post, float* y,
     return launch_tc_rt<TYPE, 1>(w, xt, post, y, M, ep, st);
 }
 
+// ---- the transposed product on the pair form: grad_x[M][K] = grad_out[M][N] . W[N][K] --------------------------
+// The contraction runs over the weight ROWS, so the operand the tensor cores need is W^T: rows = the K output
+// columns, 64 contraction values (weight rows) per stage. It is built once per call as fp16 tiles in the operand's
+// layout (the values the forward kernel's converting warps produce, transposed): segment s = weight rows
+// [64 s, 64 s + 64), row k of the segment = 128 bytes = W[64 s .. 64 s + 63][k], 16-byte pieces swizzled by k & 7.
+// A CTA's weight tile of a stage is then 16 contiguous KB and arrives by one bulk copy on the stage's barrier; the
+// pair kernel runs without converting warps and chunks.
+template <int TYPE>
+__global__ void __launch_bounds__(256)
+weights_to_image_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ sc, __half* __restrict__ wimg, uint32_t N,
+                        uint32_t nb, uint32_t nbp, uint32_t scp, uint32_t rows_pad) {
+    constexpr bool Q8 = TYPE == ZQ_TYPE_Q8_0;
+    constexpr uint32_t QB = Q8 ? 32 : 16;
+    __shared__ __align__(16) __half tile[128][72];  // [k within the quad][weight row within the segment], rows of 144 bytes
+    const uint32_t quad = blockIdx.x, seg = blockIdx.y;
+    const uint32_t t = threadIdx.x, nl = t >> 2, j = t & 3u;  // weight row of the segment, block of the quad
+    const uint32_t n = seg * 64u + nl, blk = quad * 4u + j;
+    if (n < N && blk < nb) {
+        const uint8_t* qrow = qs + (size_t)n * nbp * QB;
+        __half d, mn = __float2half_rn(0.0f);
+        if (TYPE == ZQ_TYPE_Q4_1) {
+            const __half2 dm = reinterpret_cast<const __half2*>(sc)[(size_t)n * scp + blk];
+            d = __low2half(dm);
+            mn = __high2half(dm);
+        } else {
+            d = reinterpret_cast<const __half*>(sc)[(size_t)n * scp + blk];
+        }
+        if (Q8) {
+#pragma unroll
+            for (uint32_t wd = 0; wd < 8; ++wd) {
+                const uint32_t word = *reinterpret_cast<const uint32_t*>(qrow + qs_word_offset(32, blk, wd));
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    const int q = (int)(int8_t)((word >> (8 * i)) & 0xFFu);
+                    tile[j * 32 + wd * 4 + i][nl] = __hmul(__int2half_rn(q), d);
+                }
+            }
+        } else {
+#pragma unroll
+            for (uint32_t wd = 0; wd < 4; ++wd) {
+                const uint32_t word = *reinterpret_cast<const uint32_t*>(qrow + qs_word_offset(16, blk, wd));
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    const int lo = (int)((word >> (8 * i)) & 0xFu), hi = (int)((word >> (8 * i + 4)) & 0xFu);
+                    if (TYPE == ZQ_TYPE_Q4_0) {
+                        tile[j * 32 + wd * 4 + i][nl] = __hmul(__int2half_rn(lo - 8), d);
+                        tile[j * 32 + 16 + wd * 4 + i][nl] = __hmul(__int2half_rn(hi - 8), d);
+                    } else {
+                        tile[j * 32 + wd * 4 + i][nl] = __hfma(__int2half_rn(lo), d, mn);
+                        tile[j * 32 + 16 + wd * 4 + i][nl] = __hfma(__int2half_rn(hi), d, mn);
+                    }
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (uint32_t e = 0; e < 32; ++e) tile[j * 32 + e][nl] = __float2half_rn(0.0f);
+    }
+    __syncthreads();
+    for (uint32_t i = t; i < 128u * 8u; i += 256u) {
+        const uint32_t k = i >> 3, c = i & 7u, krow = quad * 128u + k;
+        if (krow >= rows_pad) continue;
+        const uint4 v = *reinterpret_cast<const uint4*>(&tile[k][c * 8]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(wimg) + ((size_t)seg * rows_pad + krow) * 128u +
+                                  ((c ^ (krow & 7u)) << 4)) = v;
+    }
+}
+
+inline uint32_t trans_rows_pad(const zq_weight* w) { return ((w->in_dim + 255u) / 256u) * 256u; }  // K output columns, in tiles
+inline uint32_t trans_m_pad(uint32_t m_rows) { return ((m_rows + kPairActRows - 1) / kPairActRows) * kPairActRows; }
+
+// Taken where the pair form pays (as in stream_pair_takes, with the roles of the dimensions exchanged) and the
+// weight rows are whole quads of the contraction.
+bool trans_pair_takes(const zq_weight* w, uint32_t m_rows) {
+    if (!g_cluster_launch || m_rows <= 256u || w->out_dim < 1024u || (w->out_dim & 127u) != 0) return false;
+    const uint64_t tiles = (uint64_t)(trans_rows_pad(w) / 256u) * (trans_m_pad(m_rows) / kPairActRows);
+    return tiles >= 48;
+}
+
+size_t trans_pair_workspace_bytes(const zq_weight* w, uint32_t m_rows) {
+    const size_t n_seg = w->out_dim / 64;
+    const size_t xb = n_seg * trans_m_pad(m_rows) * 128;                         // grad_out as activation tiles
+    const size_t pb = ((size_t)m_rows * sizeof(float) + 255) & ~(size_t)255;     // its row scales
+    const size_t wb = n_seg * trans_rows_pad(w) * 128;                           // W^T as weight tiles
+    return xb + pb + wb;
+}
+
+int launch_trans_pair(const zq_weight* w, const float* grad_out, float* grad_x, uint32_t M, int accumulate, void* workspace,
+                      cudaStream_t st) {
+    const uint32_t N = w->out_dim, K = w->in_dim, n_seg = N / 64, m_pad = trans_m_pad(M), rows_pad = trans_rows_pad(w);
+    const size_t xb = (size_t)n_seg * m_pad * 128;
+    const size_t pb = ((size_t)M * sizeof(float) + 255) & ~(size_t)255;
+    __half* xt = static_cast<__half*>(workspace);
+    float* post = reinterpret_cast<float*>(static_cast<char*>(workspace) + xb);
+    __half* wimg = reinterpret_cast<__half*>(static_cast<char*>(workspace) + xb + pb);
+    convert_rows_tiled_kernel<<<m_pad, 256, 0, st>>>(grad_out, xt, post, M, N, m_pad, n_seg, 0u);
+    ZQ_LAUNCH_CHECK();
+    const dim3 wgrid(rows_pad / 128u, n_seg);
+    switch (w->type) {
+        case ZQ_TYPE_Q4_0:
+            weights_to_image_kernel<ZQ_TYPE_Q4_0><<<wgrid, 256, 0, st>>>(w->qs, w->sc, wimg, N, w->nb, w->nbp, w->scp, rows_pad);
+            break;
+        case ZQ_TYPE_Q4_1:
+            weights_to_image_kernel<ZQ_TYPE_Q4_1><<<wgrid, 256, 0, st>>>(w->qs, w->sc, wimg, N, w->nb, w->nbp, w->scp, rows_pad);
+            break;
+        case ZQ_TYPE_Q8_0:
+            weights_to_image_kernel<ZQ_TYPE_Q8_0><<<wgrid, 256, 0, st>>>(w->qs, w->sc, wimg, N, w->nb, w->nbp, w->scp, rows_pad);
+            break;
+        default: return ZQ_ERR_UNSUPPORTED;
+    }
+    ZQ_LAUNCH_CHECK();
+
+    // the pair kernel without converting warps and chunks: any instantiation serves (nothing of the weight's type is
+    // left in it); one ring of weight tile + two activation tiles per stage
+    constexpr int TN = 128;
+    auto kern = gemm_stream_kernel<ZQ_TYPE_Q4_0, TN, 64, true>;
+    const uint32_t m_tiles = m_pad / kPairActRows, btile_bytes = TS_ACT_ROWS * 128u;
+    constexpr uint32_t W_STAGE = TN * 128u;
+    int dev = 0, max_smem = 0;
+    ZQ_CUDA(cudaGetDevice(&dev));
+    ZQ_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    const uint32_t budget = (uint32_t)max_smem - 1024u - 10240u;
+    uint32_t n_ring = budget / (W_STAGE + 2u * btile_bytes);
+    if (n_ring > (uint32_t)TS_MAX_STAGES) n_ring = TS_MAX_STAGES;
+    if (n_ring < 2) return ZQ_ERR_UNSUPPORTED;
+    const uint32_t n_bring = 2u * n_ring;
+    const size_t smem = (size_t)n_ring * W_STAGE + (size_t)n_bring * btile_bytes + 1024;
+    ZQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const uint64_t tiles_whole = (uint64_t)(rows_pad / 256u) * m_tiles;
+    if (tiles_whole > 0x7FFFFFFFu) return ZQ_ERR_LIMIT;
+    const uint32_t pairs_max = (uint32_t)sm_count() / 2u;
+    const uint32_t rest = tiles_whole > pairs_max ? (uint32_t)(tiles_whole % pairs_max) : 0u;
+    const uint32_t first_half = (rest > 0 && rest <= pairs_max / 2u) ? (uint32_t)tiles_whole - rest : (uint32_t)tiles_whole;
+    const uint64_t tiles_total = tiles_whole + (tiles_whole - first_half);
+    const uint32_t pairs = tiles_total < pairs_max ? (uint32_t)tiles_total : pairs_max;
+    unsigned int* err_word = nullptr;
+    int rc = device_error_word(&err_word);
+    if (rc != ZQ_OK) return rc;
+    TcEpilogue ep{nullptr, nullptr, nullptr, 0};
+    if (accumulate) ep.residual = grad_x;  // the reference's kernels add to grad_x
+    CUtensorMap none;
+    memset(&none, 0, sizeof(none));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2u * pairs);
+    cfg.blockDim = dim3(TS_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ZQ_CUDA(cudaLaunchKernelEx(&cfg, kern, none, none, static_cast<const __half*>(xt), static_cast<const float*>(post), grad_x, K, M,
+                               N / 32u, (uint32_t)TS_ACT_ROWS, 0u, 2u, m_tiles, m_pad, n_ring, n_bring, 0u, first_half,
+                               static_cast<const __half*>(wimg), rows_pad, err_word, ep));
+    return ZQ_OK;
+}
+
 }  // namespace
 
 bool gemm_stream_takes(const zq_weight* w, uint32_t m_rows) { return stream_takes(w, m_rows); }
+
+bool gemm_trans_pair_takes(const zq_weight* w, uint32_t m_rows) { return trans_pair_takes(w, m_rows); }
+size_t gemm_trans_pair_workspace_bytes(const zq_weight* w, uint32_t m_rows) { return trans_pair_workspace_bytes(w, m_rows); }
+int launch_gemm_trans_pair(const zq_weight* w, const float* grad_out, float* grad_x, uint32_t m_rows, int accumulate,
+                           void* workspace, cudaStream_t st) {
+    return launch_trans_pair(w, grad_out, grad_x, m_rows, accumulate, workspace, st);
+}
 
 size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows) {
     uint32_t n_mma, m_pad;

@@ -200,7 +200,8 @@ extern "C" size_t zq_matmul_transposed_workspace_bytes(const zq_weight* w, uint3
     if (!w) return 0;
     const size_t gb = ((size_t)m_rows * w->out_dim * sizeof(__half) + 255) & ~(size_t)255;
     const size_t pb = ((size_t)m_rows * sizeof(float) + 255) & ~(size_t)255;
-    return gb + pb;
+    const size_t pair = gemm_trans_pair_takes(w, m_rows) ? gemm_trans_pair_workspace_bytes(w, m_rows) : 0;
+    return gb + pb > pair ? gb + pb : pair;
 }
 
 extern "C" int zq_matmul_transposed(const zq_weight* w, const float* d_grad_out, float* d_grad_x, uint32_t m_rows,
@@ -215,6 +216,14 @@ extern "C" int zq_matmul_transposed(const zq_weight* w, const float* d_grad_out,
         return ZQ_ERR_BAD_ARG;
     if (m_rows > 65535u * TM) return ZQ_ERR_LIMIT;
     cudaStream_t st = as_stream(stream);
+    // Many rows on a large matrix: W^T is laid out once as fp16 operand tiles and the product runs on the tcgen05
+    // kernel of the forward GEMM (pairs of CTAs). ZQ_ERR_CUDA: the cluster launch was refused, nothing of the
+    // product ran: the kernel below takes the call.
+    if (gemm_trans_pair_takes(w, m_rows)) {
+        const int rc = launch_gemm_trans_pair(w, d_grad_out, d_grad_x, m_rows, accumulate, d_workspace, st);
+        if (rc != ZQ_ERR_CUDA) return rc;
+        cudaGetLastError();
+    }
     const size_t gb = ((size_t)m_rows * w->out_dim * sizeof(__half) + 255) & ~(size_t)255;
     __half* g16 = static_cast<__half*>(d_workspace);
     float* post = reinterpret_cast<float*>(static_cast<char*>(d_workspace) + gb);

@@ -162,6 +162,11 @@ size_t gemm_tc_workspace_bytes(const zq_weight* w, uint32_t m_rows);
 // True when the weight-streaming form of the tensor-core GEMM (up to 128 activation rows, matrices of 12 288 rows
 // and more) serves the call.
 bool gemm_stream_takes(const zq_weight* w, uint32_t m_rows);
+// The transposed product on pairs of CTAs (gemm_tc.cu): whether it takes the call, its workspace, the launch.
+bool gemm_trans_pair_takes(const zq_weight* w, uint32_t m_rows);
+size_t gemm_trans_pair_workspace_bytes(const zq_weight* w, uint32_t m_rows);
+int launch_gemm_trans_pair(const zq_weight* w, const float* grad_out, float* grad_x, uint32_t m_rows, int accumulate,
+                           void* workspace, cudaStream_t st);
 constexpr uint32_t kStreamMinRowsF32 = 17;  // f32-activation calls from this many rows on take it when they bring a workspace
 
 // ---- fused decode-step launchers (ops.cu). `state` is device memory: state[0] = current token,
