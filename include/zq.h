@@ -186,7 +186,8 @@ int zq_matmul(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
 int zq_matmul_q8_static(const zq_weight* w, const float* d_x, float* d_y, uint32_t m_rows,
                         const zq_epilogue* epilogue, zq_stream stream);
 
-/* Scratch needed by zq_matmul_transposed for (w, m_rows): the fp16 copy of grad_out and its row scales. */
+/* Scratch needed by zq_matmul_transposed for (w, m_rows): the fp16 copy of grad_out and its row scales; for many
+ * rows on a large matrix also W^T as fp16 tiles (2 bytes per weight), which that form lays out on every call. */
 size_t zq_matmul_transposed_workspace_bytes(const zq_weight* w, uint32_t m_rows);
 
 /* grad_x[m][k] (+)= sum_j grad_out[m][j] * W[j][k]: the backward of zq_matmul with respect to its
@@ -199,8 +200,9 @@ size_t zq_matmul_transposed_workspace_bytes(const zq_weight* w, uint32_t m_rows)
  * out_dim must be a multiple of 8 (ZQ_ERR_UNSUPPORTED otherwise).
  * d_workspace: zq_matmul_transposed_workspace_bytes() bytes, 256-byte aligned.
  * Tensor-core product of fp16 copies (one rounding each for weights and gradients), f32 accumulation:
- * about 3e-4 relative L2 against the f32 statement; sums over the weight rows may be split over CTAs and
- * meet through atomic adds, so the last bits depend on the schedule. */
+ * about 3e-4 relative L2 against the f32 statement. On small shapes the sums over the weight rows may be split
+ * over CTAs and meet through atomic adds, so the last bits depend on the schedule there; more than 256 rows on a
+ * matrix of 1024 weight rows and more run the tcgen05 GEMM on W^T (deterministic). */
 int zq_matmul_transposed(const zq_weight* w, const float* d_grad_out, float* d_grad_x, uint32_t m_rows,
                          int accumulate, void* d_workspace, size_t workspace_bytes, zq_stream stream);
 
